@@ -1,0 +1,71 @@
+"""ctypes binding of the C ABI declared in include/axono_b200.h.
+
+Loading fails loudly when the library is missing: there is no CPU or PyTorch fallback for any
+operator of this package.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+from . import build as _build
+
+_vp, _i, _i64, _sz, _f = C.c_void_p, C.c_int, C.c_int64, C.c_size_t, C.c_float
+
+# name -> (restype, argtypes); mirrors include/axono_b200.h one to one.
+SIGNATURES = {
+    "axb200_version": (C.c_char_p, []),
+    "axb200_last_error": (C.c_uint, []),
+    "axb200_gqa_workspace_bytes": (_sz, [_i, _i, _i, _i, _i64, _i]),
+    "axb200_gqa_decode": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i, _vp, _sz, _vp]),
+    "axb200_gqa_decode_paged": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i64, _i,
+                                     _vp, _sz, _vp]),
+    "axb200_kv_append_rope": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i, _i, _i,
+                                   _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp]),
+    "axb200_rope": (_i, [_vp, _vp, _f, _vp, _i64, _i, _i, _i, _vp]),
+    "axb200_rope_thd": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _i64, _i, _i, _i, _vp]),
+    "axb200_rope_with_cos_sin": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i, _i, _vp]),
+    "axb200_mrope_cos_sin": (_i, [_vp, _vp, _i, _i, _vp, _vp, _i64, _i, _vp]),
+    "axb200_add_rms_norm": (_i, [_vp, _vp, _vp, _f, _vp, _vp, _i64, _i, _i, _vp]),
+    "axb200_silu_mul": (_i, [_vp, _vp, _vp, _i64, _i, _vp]),
+    "axb200_rms_norm": (_i, [_vp, _vp, _f, _vp, _i64, _i, _i, _vp]),
+    "axb200_concat": (_i, [_vp, _vp, _vp, _i64, _sz, _sz, _vp]),
+}
+
+STATUS_NAMES = ["OK", "INVALID_ARGUMENT", "OUT_OF_MEMORY", "UNSUPPORTED_TYPE", "SHAPE_MISMATCH",
+                "INTERNAL_ERROR", "DEVICE_ERROR", "INVALID_PTR", "DEVICE_MISMATCH"]
+
+# axono::core::DataType values (include/axono/core/types.h:18-27 of the reference)
+INT8, INT16, INT32, INT64, FLOAT16, FLOAT32, FLOAT64, BOOLEAN = range(8)
+
+_lib = None
+
+
+def library_path() -> str:
+    return _build.LIB
+
+
+def lib() -> C.CDLL:
+    """The loaded C-ABI library.  Raises when it has not been built."""
+    global _lib
+    if _lib is None:
+        path = library_path()
+        if not os.path.exists(path):
+            raise RuntimeError(
+                f"{path} is missing: build it with `python -m axono_b200.build` (needs nvcc). "
+                "axono_b200 has no fallback path.")
+        handle = C.CDLL(path)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def check(status: int, op: str) -> None:
+    """Status != OK becomes RuntimeError, as the reference's binding does
+    (axono/python/src/nanobind_module.cpp:1022-1024)."""
+    if status != 0:
+        name = STATUS_NAMES[status] if 0 <= status < len(STATUS_NAMES) else "?"
+        raise RuntimeError(f"{op} failed, status {status} ({name})")

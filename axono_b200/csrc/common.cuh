@@ -1,0 +1,172 @@
+// Shared device/host helpers for the sm_100a decode-path kernels: status and dtype codes,
+// the device error word, and thin inline-PTX wrappers (mbarrier, TMA tensor copies,
+// ldmatrix, mma.sync).
+#pragma once
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "axono_b200.h"
+
+namespace axb {
+
+// Set by kernels instead of trapping; read and cleared by axb200_last_error().  Each
+// translation unit has its own copy (no relocatable device code is needed) and registers a
+// reader for it at load time.
+static __device__ unsigned int g_error_word = 0;
+
+using ErrorReader = unsigned int (*)();
+void register_error_reader(ErrorReader fn);  // defined once, beside axb200_last_error()
+
+static unsigned int read_clear_error_word() {
+  unsigned int word = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&word, g_error_word, sizeof(word)) != cudaSuccess) return 0x80000000u;
+  if (word) cudaMemcpyToSymbol(g_error_word, &zero, sizeof(zero));
+  return word;
+}
+
+namespace {
+struct ErrorReaderRegistration {
+  ErrorReaderRegistration() { register_error_reader(&read_clear_error_word); }
+};
+static ErrorReaderRegistration g_error_reader_registration;
+}  // namespace
+
+inline size_t dtype_size(int dtype) {
+  switch (dtype) {
+    case AXB200_FLOAT16: return 2;
+    case AXB200_FLOAT32: return 4;
+    default: return 0;
+  }
+}
+
+inline int launch_status() {
+  return cudaGetLastError() == cudaSuccess ? AXB200_OK : AXB200_DEVICE_ERROR;
+}
+
+// ---- bounded waiting ---------------------------------------------------------------------
+// Every spin in these kernels is limited: a waiter that has polled for kWaitNanos of wall time
+// records AXB200_ERR_WAIT_TIMEOUT, raises the CTA's abort flag and the kernel winds down
+// instead of hanging the GPU.
+constexpr unsigned long long kWaitNanos = 2000000000ull;  // 2 s
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_fence_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.b32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Waits for the phase with the given parity to complete, or until the time limit or the
+// CTA's abort flag ends the wait.  Returns false when it gave up.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity,
+                                                  volatile int *abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_timer_ns();
+  for (uint32_t spin = 1;; ++spin) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spin & 255u) == 0u) {
+      if (*abort_flag) return false;
+      if (global_timer_ns() - t0 > kWaitNanos) break;
+    }
+  }
+  *abort_flag = 1;
+  atomicOr(&g_error_word, AXB200_ERR_WAIT_TIMEOUT);
+  return false;
+}
+
+// ---- TMA (cp.async.bulk.tensor), 4-D tiled load, completion on an mbarrier -----------------
+// The innermost coordinate c0 times the element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_4d(void *smem_dst, const CUtensorMap *map, uint64_t *bar,
+                                            int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)),
+        "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_prefetch_descriptor(const CUtensorMap *map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+
+// ---- tensor-core fragments ------------------------------------------------------------------
+__device__ __forceinline__ void ldmatrix_x4(uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3,
+                                            uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t &r0, uint32_t &r1, uint32_t &r2,
+                                                  uint32_t &r3, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+
+// D(16x8,f32) += A(16x16,f16,row) * B(16x8,f16,col)
+__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
+                                          uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+  __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t *>(&h);
+}
+
+__device__ __forceinline__ void named_bar_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+}  // namespace axb

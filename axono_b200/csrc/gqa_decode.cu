@@ -1,0 +1,936 @@
+// Decode attention for sm_100a: split-K flash-decoding over the KV cache plus the
+// log-sum-exp combine.  Replaces the reference's GqaDecodeAttention and its two kernels
+// (src/ops/cuda/gqa.cu:31-92 split, :95-129 merge, :139-182 launcher).
+//
+// Split kernel: one CTA per (chunk of the sequence, KV head, sequence).  A producer warp
+// streams 32 KB stages (K tile + V tile) from HBM into shared memory with TMA tensor copies
+// that complete on mbarriers; four consumer warps compute, for all query heads that share
+// the KV head, S = q.K^T, an online softmax and O += P.V per tile, so every K/V byte is read
+// from HBM once.  fp16 uses mma.sync m16n8k16 with fp32 accumulators on 128-byte-swizzled
+// tiles (query heads are the M rows); fp32 uses FMA on unswizzled tiles.  Each CTA leaves an
+// unnormalised partial (m, l, O) in the workspace; the combine kernel merges a sequence's
+// partials.  The number of chunks comes from the context length and the SM count.
+//
+// Layouts: q/out (batch,hq,d).  Cache either token-major contiguous (skv,hkv,d) - the
+// reference's layout, one sequence - or paged (num_pages,hkv,page_tokens,d) with a block
+// table, where one (page, head) tile is a contiguous run in HBM.
+#include <math.h>
+
+#include <mutex>
+#include <set>
+#include <utility>
+
+#include "common.cuh"
+
+namespace axb {
+
+namespace {
+constexpr int kMaxErrorReaders = 16;
+ErrorReader g_error_readers[kMaxErrorReaders];
+int g_num_error_readers = 0;
+}  // namespace
+
+void register_error_reader(ErrorReader fn) {
+  if (g_num_error_readers < kMaxErrorReaders) g_error_readers[g_num_error_readers++] = fn;
+}
+
+namespace {
+
+constexpr int kHeadDim = 128;
+constexpr int kConsumerWarps = 4;
+constexpr int kConsumerThreads = kConsumerWarps * 32;
+constexpr int kThreads = kConsumerThreads + 32;  // + one producer warp
+constexpr int kStageBytes = 32768;               // K tile 16 KB + V tile 16 KB
+constexpr int kTileTokensF16 = 64;
+constexpr int kTileTokensF32 = 32;
+constexpr int kMaxGroupMma = 16;
+constexpr int kMaxChunks = 256;  // the reference's kMaxSplits (src/ops/cuda/gqa.cu:27)
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct DecodeParams {
+  const void *q;
+  void *out;
+  float *part_o;   // (batch, hq, max_chunks, d)
+  float *part_ml;  // (batch, hq, max_chunks, 2): running max (log2 domain or raw), sum
+  const int32_t *block_table;
+  const int32_t *seq_lens;  // device lengths, or null -> fixed_len
+  int fixed_len;
+  int batch, hq, hkv, group;
+  int page_tokens, max_blocks, num_pages;
+  int chunk_tokens, max_chunks;
+  float scale;  // 1/sqrt(d)
+  int write_final;  // max_chunks == 1: normalise and write `out` directly
+};
+
+__device__ __forceinline__ int seq_len_of(const DecodeParams &p, int b) {
+  return p.seq_lens ? p.seq_lens[b] : p.fixed_len;
+}
+
+// ---- producer ---------------------------------------------------------------------------
+// Streams tiles [0, ntiles) of this CTA's chunk.  All 32 lanes run the loop (the page ids of
+// the next 32 tiles are fetched one per lane); lane 0 issues the copies.
+template <bool kPaged, int kStages, int kTile, int kBoxes, int kBoxElems>
+__device__ __forceinline__ void produce_tiles(const CUtensorMap *tmK, const CUtensorMap *tmV,
+                                              const DecodeParams &p, uint8_t *stages,
+                                              uint64_t *full, uint64_t *empty,
+                                              volatile int *abort_flag, int b, int hk, int start,
+                                              int ntiles, int lane) {
+  constexpr int kBoxBytes = (kStageBytes / 2) / kBoxes;
+  int page_cache = 0;
+  for (int i = 0; i < ntiles; ++i) {
+    const int s = i % kStages;
+    const uint32_t phase = (i / kStages) & 1;
+    const int tok0 = start + i * kTile;
+    int page = 0, tok_in_page = tok0;
+    if (kPaged) {
+      if ((i & 31) == 0) {
+        const int t = i + lane;
+        const int slot = (start + t * kTile) / p.page_tokens;
+        page_cache = 0;
+        if (t < ntiles && slot < p.max_blocks) {
+          page_cache = p.block_table[(size_t)b * p.max_blocks + slot];
+          if (page_cache < 0 || page_cache >= p.num_pages) {
+            atomicOr(&g_error_word, AXB200_ERR_BAD_PAGE);
+            page_cache = p.num_pages;  // out of range: the copy zero-fills
+          }
+        }
+      }
+      page = __shfl_sync(0xffffffffu, page_cache, i & 31);
+      tok_in_page = tok0 % p.page_tokens;
+    }
+    if (lane == 0) {
+      if (mbar_wait_bounded(&empty[s], phase ^ 1u, abort_flag)) {
+        mbar_arrive_expect_tx(&full[s], kStageBytes);
+        uint8_t *st = stages + (size_t)s * kStageBytes;
+#pragma unroll
+        for (int bx = 0; bx < kBoxes; ++bx) {
+          if (kPaged) {
+            tma_load_4d(st + bx * kBoxBytes, tmK, &full[s], bx * kBoxElems, tok_in_page, hk, page);
+            tma_load_4d(st + kStageBytes / 2 + bx * kBoxBytes, tmV, &full[s], bx * kBoxElems,
+                        tok_in_page, hk, page);
+          } else {
+            tma_load_4d(st + bx * kBoxBytes, tmK, &full[s], bx * kBoxElems, hk, tok0, 0);
+            tma_load_4d(st + kStageBytes / 2 + bx * kBoxBytes, tmV, &full[s], bx * kBoxElems, hk,
+                        tok0, 0);
+          }
+        }
+      }
+    }
+    __syncwarp();
+    if (*abort_flag) break;
+  }
+}
+
+// ---- chunk epilogue shared by both dtypes ---------------------------------------------------
+// Consumer warps have written their per-warp (m, l, O) for each query head of the group into
+// shared memory; thread t owns output dim t.  m is in the exponent domain `dom` (so weights
+// are exp2((m_w - M) * dom)).
+template <typename OutT>
+__device__ __forceinline__ void finalize_chunk(const DecodeParams &p, const float *mO,
+                                               const float *mM, const float *mL, int b, int hk,
+                                               int chunk, int t, float dom) {
+  for (int r = 0; r < p.group; ++r) {
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kConsumerWarps; ++w) M = fmaxf(M, mM[w * kMaxGroupMma + r]);
+    float L = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < kConsumerWarps; ++w) {
+      const float mw = mM[w * kMaxGroupMma + r];
+      const float wgt = (mw == -INFINITY) ? 0.f : exp2f((mw - M) * dom);
+      L += mL[w * kMaxGroupMma + r] * wgt;
+      acc += mO[(w * kMaxGroupMma + r) * kHeadDim + t] * wgt;
+    }
+    const int h = hk * p.group + r;
+    if (p.write_final) {
+      reinterpret_cast<OutT *>(p.out)[((size_t)b * p.hq + h) * kHeadDim + t] =
+          static_cast<OutT>(acc / L);
+    } else {
+      const size_t slot = ((size_t)b * p.hq + h) * p.max_chunks + chunk;
+      p.part_o[slot * kHeadDim + t] = acc;
+      if (t == 0) {
+        p.part_ml[slot * 2 + 0] = M;
+        p.part_ml[slot * 2 + 1] = L;
+      }
+    }
+  }
+}
+
+// Shared-memory carve-up: [stages][full barriers][empty barriers][abort flag]; the merge
+// buffers alias the first two stages once the pipeline has drained.
+template <int kStages>
+struct SmemLayout {
+  static constexpr int kBarOffset = kStages * kStageBytes;
+  static constexpr int kBytes = kBarOffset + 2 * kStages * 8 + 16;
+  static constexpr int kDynamicBytes = kBytes + 1024;  // room to align the base to 1024 B
+};
+
+__device__ __forceinline__ uint8_t *align_1024(uint8_t *p) {
+  return reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(p) + 1023) & ~uintptr_t(1023));
+}
+
+// ---- fp16 split kernel: tensor-core tiles ---------------------------------------------------
+// Byte offset of the 16-byte chunk `c16` (0..15 across the 256-byte row) of token row `row`
+// inside a K or V tile stored as two 128-byte-swizzled boxes [64 tokens][64 halves].
+__device__ __forceinline__ uint32_t swz_off(int row, int c16) {
+  return (uint32_t)((c16 >> 3) * 8192 + row * 128 + (((c16 & 7) ^ (row & 7)) << 4));
+}
+
+template <bool kPaged, int kStages, int kMinCtas>
+__global__ void __launch_bounds__(kThreads, kMinCtas)
+gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
+                     const __grid_constant__ CUtensorMap tmV, const DecodeParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = align_1024(smem_raw);
+  uint64_t *full = reinterpret_cast<uint64_t *>(smem + SmemLayout<kStages>::kBarOffset);
+  uint64_t *empty = full + kStages;
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(empty + kStages);
+
+  const int chunk = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int L = seq_len_of(p, b);
+  const int start = chunk * p.chunk_tokens;
+  if (start >= L) return;
+  const int end = min(L, start + p.chunk_tokens);
+  const int ntiles = (end - start + kTileTokensF16 - 1) / kTileTokensF16;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], kConsumerWarps);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  if (warp == kConsumerWarps) {
+    if (lane == 0) {
+      tma_prefetch_descriptor(&tmK);
+      tma_prefetch_descriptor(&tmV);
+    }
+    produce_tiles<kPaged, kStages, kTileTokensF16, 2, 64>(&tmK, &tmV, p, smem, full, empty,
+                                                          abort_flag, b, hk, start, ntiles, lane);
+    return;
+  }
+
+  // ---- consumers: warp w owns tokens [16w, 16w+16) of every tile ----
+  const int g = lane >> 2, tq = lane & 3;
+  const bool use_hi = p.group > 8;  // rows 8..15 of the M dimension carry query heads too
+  const __half *qh = reinterpret_cast<const __half *>(p.q);
+
+  // Q as the A operand, resident in registers: 8 k-steps x 4 regs.
+  uint32_t qa[8][4];
+  {
+    const __half *q0 = qh + ((size_t)b * p.hq + (size_t)hk * p.group + g) * kHeadDim;
+    const __half *q1 = q0 + 8 * kHeadDim;
+    const bool v0 = g < p.group, v1 = g + 8 < p.group;
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      const int c = ks * 16 + tq * 2;
+      qa[ks][0] = v0 ? *reinterpret_cast<const uint32_t *>(q0 + c) : 0u;
+      qa[ks][1] = v1 ? *reinterpret_cast<const uint32_t *>(q1 + c) : 0u;
+      qa[ks][2] = v0 ? *reinterpret_cast<const uint32_t *>(q0 + c + 8) : 0u;
+      qa[ks][3] = v1 ? *reinterpret_cast<const uint32_t *>(q1 + c + 8) : 0u;
+    }
+  }
+
+  float o[16][4];
+#pragma unroll
+  for (int nt = 0; nt < 16; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
+  float m0 = -INFINITY, m1 = -INFINITY;  // running max (log2 domain) of rows g, g+8
+  float l0 = 0.f, l1 = 0.f;              // this thread's share of the running sums
+  const float sl2 = p.scale * kLog2e;
+
+  // ldmatrix lane roles
+  const int mat = lane >> 3, mrow = lane & 7;
+  const int k_row = warp * 16 + (mat >> 1) * 8 + mrow;  // K: matrices (n-tile, k-half)
+  const int k_c16 = mat & 1;
+  const int v_row = warp * 16 + (mat & 1) * 8 + mrow;   // V: matrices (k-half, n-tile)
+  const int v_c16 = mat >> 1;
+
+  bool ok = true;
+  for (int i = 0; i < ntiles && ok; ++i) {
+    const int s = i % kStages;
+    const uint32_t phase = (i / kStages) & 1;
+    ok = mbar_wait_bounded(&full[s], phase, abort_flag);
+    if (!ok) break;
+    const uint32_t kbase = smem_u32(smem + (size_t)s * kStageBytes);
+    const uint32_t vbase = kbase + kStageBytes / 2;
+
+    // S(16 heads x 16 tokens) = Q . K^T
+    float sc[2][4];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      uint32_t b0, b1, b2, b3;
+      ldmatrix_x4(b0, b1, b2, b3, kbase + swz_off(k_row, ks * 2 + k_c16));
+      mma_16816(sc[0], qa[ks], b0, b1);
+      mma_16816(sc[1], qa[ks], b2, b3);
+    }
+
+    // mask the tokens past the end of the sequence (last tile only)
+    const int tile_tok = start + i * kTileTokensF16 + warp * 16;  // this warp's first token
+    const int valid = end - tile_tok;                              // tokens of the warp that exist
+    if (valid < 16) {
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int t0 = j * 8 + tq * 2;
+        if (t0 >= valid) sc[j][0] = sc[j][2] = -INFINITY;
+        if (t0 + 1 >= valid) sc[j][1] = sc[j][3] = -INFINITY;
+      }
+    }
+
+    // online softmax in the log2 domain; rows are shared by the 4 lanes of a quad
+    float mx0 = fmaxf(fmaxf(sc[0][0], sc[0][1]), fmaxf(sc[1][0], sc[1][1])) * sl2;
+    float mx1 = fmaxf(fmaxf(sc[0][2], sc[0][3]), fmaxf(sc[1][2], sc[1][3])) * sl2;
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+    const float ms0 = (mn0 == -INFINITY) ? 0.f : mn0;  // all-masked rows stay at weight 0
+    const float ms1 = (mn1 == -INFINITY) ? 0.f : mn1;
+    const float corr0 = fast_exp2(m0 - ms0), corr1 = fast_exp2(m1 - ms1);
+    m0 = mn0;
+    m1 = mn1;
+    float pr[2][4];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      pr[j][0] = fast_exp2(fmaf(sc[j][0], sl2, -ms0));
+      pr[j][1] = fast_exp2(fmaf(sc[j][1], sl2, -ms0));
+      pr[j][2] = fast_exp2(fmaf(sc[j][2], sl2, -ms1));
+      pr[j][3] = fast_exp2(fmaf(sc[j][3], sl2, -ms1));
+    }
+    l0 = l0 * corr0 + (pr[0][0] + pr[0][1] + pr[1][0] + pr[1][1]);
+    l1 = l1 * corr1 + (pr[0][2] + pr[0][3] + pr[1][2] + pr[1][3]);
+    const bool rescale = use_hi ? (corr0 != 1.f || corr1 != 1.f) : (corr0 != 1.f);
+    if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll
+      for (int nt = 0; nt < 16; ++nt) {
+        o[nt][0] *= corr0;
+        o[nt][1] *= corr0;
+        o[nt][2] *= corr1;
+        o[nt][3] *= corr1;
+      }
+    }
+
+    // P (fp16) as the A operand of O += P . V
+    uint32_t pa[4];
+    pa[0] = pack_half2(pr[0][0], pr[0][1]);
+    pa[1] = pack_half2(pr[0][2], pr[0][3]);
+    pa[2] = pack_half2(pr[1][0], pr[1][1]);
+    pa[3] = pack_half2(pr[1][2], pr[1][3]);
+#pragma unroll
+    for (int np = 0; np < 8; ++np) {
+      uint32_t b0, b1, b2, b3;
+      ldmatrix_x4_trans(b0, b1, b2, b3, vbase + swz_off(v_row, np * 2 + v_c16));
+      if (valid < 16) {
+        // rows past the end may hold stale bytes: zero them so 0 * NaN cannot appear.
+        // b0/b2 hold tokens 2tq,2tq+1; b1/b3 hold tokens 8+2tq, 8+2tq+1.
+        const int t0 = tq * 2;
+        const uint32_t keep_lo = (t0 < valid ? 0x0000ffffu : 0u) | (t0 + 1 < valid ? 0xffff0000u : 0u);
+        const uint32_t keep_hi =
+            (t0 + 8 < valid ? 0x0000ffffu : 0u) | (t0 + 9 < valid ? 0xffff0000u : 0u);
+        b0 &= keep_lo;
+        b2 &= keep_lo;
+        b1 &= keep_hi;
+        b3 &= keep_hi;
+      }
+      mma_16816(o[np * 2], pa, b0, b1);
+      mma_16816(o[np * 2 + 1], pa, b2, b3);
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty[s]);
+  }
+
+  // ---- merge the four warps' states and emit the chunk's partial ----
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  named_bar_sync(1, kConsumerThreads);  // every stage has been consumed: reuse stage memory
+  if (*abort_flag) return;
+  float *mO = reinterpret_cast<float *>(smem);                     // [4][16][128]
+  float *mM = reinterpret_cast<float *>(smem + kStageBytes);       // [4][16]
+  float *mL = mM + kConsumerWarps * kMaxGroupMma;                  // [4][16]
+  if (g < p.group) {
+    float *dst = mO + (warp * kMaxGroupMma + g) * kHeadDim + tq * 2;
+#pragma unroll
+    for (int nt = 0; nt < 16; ++nt)
+      *reinterpret_cast<float2 *>(dst + nt * 8) = make_float2(o[nt][0], o[nt][1]);
+    if (tq == 0) {
+      mM[warp * kMaxGroupMma + g] = m0;
+      mL[warp * kMaxGroupMma + g] = l0;
+    }
+  }
+  if (g + 8 < p.group) {
+    float *dst = mO + (warp * kMaxGroupMma + g + 8) * kHeadDim + tq * 2;
+#pragma unroll
+    for (int nt = 0; nt < 16; ++nt)
+      *reinterpret_cast<float2 *>(dst + nt * 8) = make_float2(o[nt][2], o[nt][3]);
+    if (tq == 0) {
+      mM[warp * kMaxGroupMma + g + 8] = m1;
+      mL[warp * kMaxGroupMma + g + 8] = l1;
+    }
+  }
+  named_bar_sync(1, kConsumerThreads);
+  finalize_chunk<__half>(p, mO, mM, mL, b, hk, chunk, threadIdx.x, 1.0f);
+}
+
+// ---- fp32 split kernel: FMA on unswizzled tiles ----------------------------------------------
+// Tile = 32 tokens x 128 floats; warp w owns tokens [8w, 8w+8), lane owns dims [4*lane, +4).
+template <bool kPaged, int kStages, int kGroup>
+__global__ void __launch_bounds__(kThreads, 2)
+gqa_split_f32_kernel(const __grid_constant__ CUtensorMap tmK,
+                     const __grid_constant__ CUtensorMap tmV, const DecodeParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = align_1024(smem_raw);
+  uint64_t *full = reinterpret_cast<uint64_t *>(smem + SmemLayout<kStages>::kBarOffset);
+  uint64_t *empty = full + kStages;
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(empty + kStages);
+
+  const int chunk = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int L = seq_len_of(p, b);
+  const int start = chunk * p.chunk_tokens;
+  if (start >= L) return;
+  const int end = min(L, start + p.chunk_tokens);
+  const int ntiles = (end - start + kTileTokensF32 - 1) / kTileTokensF32;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], kConsumerWarps);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  if (warp == kConsumerWarps) {
+    if (lane == 0) {
+      tma_prefetch_descriptor(&tmK);
+      tma_prefetch_descriptor(&tmV);
+    }
+    produce_tiles<kPaged, kStages, kTileTokensF32, 1, 128>(&tmK, &tmV, p, smem, full, empty,
+                                                           abort_flag, b, hk, start, ntiles, lane);
+    return;
+  }
+
+  const float *qf = reinterpret_cast<const float *>(p.q);
+  float4 qr[kGroup];
+#pragma unroll
+  for (int r = 0; r < kGroup; ++r)
+    qr[r] = *reinterpret_cast<const float4 *>(
+        qf + ((size_t)b * p.hq + (size_t)hk * kGroup + r) * kHeadDim + lane * 4);
+
+  float4 o[kGroup];
+  float m[kGroup], l[kGroup];  // m: running max of the raw dot products
+#pragma unroll
+  for (int r = 0; r < kGroup; ++r) {
+    o[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+    m[r] = -INFINITY;
+    l[r] = 0.f;
+  }
+  const float sl2 = p.scale * kLog2e;
+
+  bool ok = true;
+  for (int i = 0; i < ntiles && ok; ++i) {
+    const int s = i % kStages;
+    const uint32_t phase = (i / kStages) & 1;
+    ok = mbar_wait_bounded(&full[s], phase, abort_flag);
+    if (!ok) break;
+    const float *Ks = reinterpret_cast<const float *>(smem + (size_t)s * kStageBytes);
+    const float *Vs = Ks + kTileTokensF32 * kHeadDim;
+    const int valid = end - (start + i * kTileTokensF32 + warp * 8);  // tokens of this warp that exist
+
+    float sc[kGroup][8];
+#pragma unroll
+    for (int t = 0; t < 8; ++t) {
+      const float4 kv = *reinterpret_cast<const float4 *>(Ks + (warp * 8 + t) * kHeadDim + lane * 4);
+#pragma unroll
+      for (int r = 0; r < kGroup; ++r) {
+        float a = qr[r].x * kv.x;
+        a = fmaf(qr[r].y, kv.y, a);
+        a = fmaf(qr[r].z, kv.z, a);
+        a = fmaf(qr[r].w, kv.w, a);
+        sc[r][t] = a;
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < kGroup; ++r) {
+#pragma unroll
+      for (int t = 0; t < 8; ++t) {
+        float a = sc[r][t];
+        a += __shfl_xor_sync(0xffffffffu, a, 16);
+        a += __shfl_xor_sync(0xffffffffu, a, 8);
+        a += __shfl_xor_sync(0xffffffffu, a, 4);
+        a += __shfl_xor_sync(0xffffffffu, a, 2);
+        a += __shfl_xor_sync(0xffffffffu, a, 1);
+        sc[r][t] = (t < valid) ? a : -INFINITY;
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < kGroup; ++r) {
+      float mx = sc[r][0];
+#pragma unroll
+      for (int t = 1; t < 8; ++t) mx = fmaxf(mx, sc[r][t]);
+      const float mn = fmaxf(m[r], mx);
+      const float ms = (mn == -INFINITY) ? 0.f : mn;
+      const float corr = exp2f((m[r] - ms) * sl2);
+      m[r] = mn;
+      float sum = 0.f;
+#pragma unroll
+      for (int t = 0; t < 8; ++t) {
+        sc[r][t] = exp2f((sc[r][t] - ms) * sl2);
+        sum += sc[r][t];
+      }
+      l[r] = l[r] * corr + sum;
+      o[r].x *= corr;
+      o[r].y *= corr;
+      o[r].z *= corr;
+      o[r].w *= corr;
+    }
+#pragma unroll
+    for (int t = 0; t < 8; ++t) {
+      float4 vv = *reinterpret_cast<const float4 *>(Vs + (warp * 8 + t) * kHeadDim + lane * 4);
+      if (t >= valid) vv = make_float4(0.f, 0.f, 0.f, 0.f);  // stale rows past the end
+#pragma unroll
+      for (int r = 0; r < kGroup; ++r) {
+        o[r].x = fmaf(sc[r][t], vv.x, o[r].x);
+        o[r].y = fmaf(sc[r][t], vv.y, o[r].y);
+        o[r].z = fmaf(sc[r][t], vv.z, o[r].z);
+        o[r].w = fmaf(sc[r][t], vv.w, o[r].w);
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty[s]);
+  }
+
+  named_bar_sync(1, kConsumerThreads);
+  if (*abort_flag) return;
+  float *mO = reinterpret_cast<float *>(smem);
+  float *mM = reinterpret_cast<float *>(smem + kStageBytes);
+  float *mL = mM + kConsumerWarps * kMaxGroupMma;
+#pragma unroll
+  for (int r = 0; r < kGroup; ++r) {
+    *reinterpret_cast<float4 *>(mO + (warp * kMaxGroupMma + r) * kHeadDim + lane * 4) = o[r];
+    if (lane == 0) {
+      mM[warp * kMaxGroupMma + r] = m[r];
+      mL[warp * kMaxGroupMma + r] = l[r];
+    }
+  }
+  named_bar_sync(1, kConsumerThreads);
+  finalize_chunk<float>(p, mO, mM, mL, b, hk, chunk, threadIdx.x, sl2);
+}
+
+// ---- generic split kernel: any head_dim <= 256, any group ------------------------------------
+// Plain coalesced loads, one warp per token stride; used for shapes the tiled kernels do not
+// cover (head_dim != 128, unaligned pointers).  Correctness path, not a tuned one.
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+
+template <typename T, bool kPaged>
+__global__ void __launch_bounds__(128)
+gqa_split_generic_kernel(const T *k, const T *v, const DecodeParams p, int d) {
+  __shared__ float sO[kConsumerWarps][256];
+  __shared__ float sM[kConsumerWarps], sL[kConsumerWarps];
+  const int chunk = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int L = seq_len_of(p, b);
+  const int start = chunk * p.chunk_tokens;
+  if (start >= L) return;
+  const int end = min(L, start + p.chunk_tokens);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const T *qp = reinterpret_cast<const T *>(p.q);
+  const float dom = p.scale * kLog2e;
+
+  for (int r = 0; r < p.group; ++r) {
+    const int h = hk * p.group + r;
+    float qv[8], acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int c = lane + 32 * j;
+      qv[j] = c < d ? to_f32(qp[((size_t)b * p.hq + h) * d + c]) : 0.f;
+      acc[j] = 0.f;
+    }
+    float m = -INFINITY, l = 0.f;
+    for (int tok = start + warp; tok < end; tok += kConsumerWarps) {
+      size_t row;
+      if (kPaged) {
+        int page = p.block_table[(size_t)b * p.max_blocks + tok / p.page_tokens];
+        if (page < 0 || page >= p.num_pages) {
+          atomicOr(&g_error_word, AXB200_ERR_BAD_PAGE);
+          continue;
+        }
+        row = (((size_t)page * p.hkv + hk) * p.page_tokens + tok % p.page_tokens) * d;
+      } else {
+        row = ((size_t)tok * p.hkv + hk) * d;
+      }
+      float s = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int c = lane + 32 * j;
+        if (c < d) s = fmaf(qv[j], to_f32(k[row + c]), s);
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+      const float mn = fmaxf(m, s);
+      const float corr = exp2f((m - mn) * dom);
+      const float pw = exp2f((s - mn) * dom);
+      l = l * corr + pw;
+      m = mn;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int c = lane + 32 * j;
+        if (c < d) acc[j] = fmaf(pw, to_f32(v[row + c]), acc[j] * corr);
+      }
+    }
+    __syncthreads();  // previous head's merge has finished reading
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int c = lane + 32 * j;
+      if (c < d) sO[warp][c] = acc[j];
+    }
+    if (lane == 0) {
+      sM[warp] = m;
+      sL[warp] = l;
+    }
+    __syncthreads();
+    float M = -INFINITY;
+    for (int w = 0; w < kConsumerWarps; ++w) M = fmaxf(M, sM[w]);
+    float Lsum = 0.f;
+    float wgt[kConsumerWarps];
+    for (int w = 0; w < kConsumerWarps; ++w) {
+      wgt[w] = sM[w] == -INFINITY ? 0.f : exp2f((sM[w] - M) * dom);
+      Lsum += sL[w] * wgt[w];
+    }
+    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+      float a = 0.f;
+      for (int w = 0; w < kConsumerWarps; ++w) a += sO[w][c] * wgt[w];
+      if (p.write_final) {
+        reinterpret_cast<T *>(p.out)[((size_t)b * p.hq + h) * d + c] = static_cast<T>(a / Lsum);
+      } else {
+        const size_t slot = ((size_t)b * p.hq + h) * p.max_chunks + chunk;
+        p.part_o[slot * d + c] = a;
+      }
+    }
+    if (!p.write_final && threadIdx.x == 0) {
+      const size_t slot = ((size_t)b * p.hq + h) * p.max_chunks + chunk;
+      p.part_ml[slot * 2 + 0] = M;
+      p.part_ml[slot * 2 + 1] = Lsum;
+    }
+  }
+}
+
+// ---- combine: log-sum-exp merge of a sequence's chunk partials --------------------------------
+// One CTA per (sequence, query head); thread t owns output dims t, t+blockDim, ...  `dom` is the
+// exponent domain of the stored maxima.  A sequence of length 0 yields zeros.
+template <typename OutT>
+__global__ void __launch_bounds__(128)
+gqa_combine_kernel(const DecodeParams p, int d, float dom) {
+  const int h = blockIdx.x, b = blockIdx.y;
+  const int L = seq_len_of(p, b);
+  int n = (L + p.chunk_tokens - 1) / p.chunk_tokens;
+  n = max(0, min(n, p.max_chunks));
+  const size_t base = ((size_t)b * p.hq + h) * p.max_chunks;
+  OutT *out = reinterpret_cast<OutT *>(p.out) + ((size_t)b * p.hq + h) * d;
+  if (n == 0) {
+    for (int c = threadIdx.x; c < d; c += blockDim.x) out[c] = static_cast<OutT>(0.f);
+    return;
+  }
+  float M = -INFINITY;
+  for (int c = 0; c < n; ++c) M = fmaxf(M, p.part_ml[(base + c) * 2]);
+  float Lsum = 0.f;
+  for (int c = 0; c < n; ++c)
+    Lsum += p.part_ml[(base + c) * 2 + 1] * exp2f((p.part_ml[(base + c) * 2] - M) * dom);
+  const float inv = 1.0f / Lsum;
+  for (int c0 = threadIdx.x; c0 < d; c0 += blockDim.x) {
+    float acc = 0.f;
+    for (int c = 0; c < n; ++c) {
+      const float w = exp2f((p.part_ml[(base + c) * 2] - M) * dom);
+      acc = fmaf(w, p.part_o[(base + c) * d + c0], acc);
+    }
+    out[c0] = static_cast<OutT>(acc * inv);
+  }
+}
+
+// ---- host side ----------------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                   const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                   const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void *sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  });
+  return fn;
+}
+
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+// 4-D tensor map over a cache.  Paged: dims (d, page_tokens, hkv, num_pages), box
+// (box_d, tile, 1, 1).  Token-major: dims (d, hkv, skv, 1), box (box_d, 1, tile, 1).
+bool make_map(CUtensorMap *map, const void *base, int dtype, bool paged, int d, int hkv,
+              int64_t tokens_or_page_tokens, int64_t num_pages, int tile) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const size_t es = dtype_size(dtype);
+  const bool f16 = dtype == AXB200_FLOAT16;
+  cuuint64_t dims[4], strides[3];
+  cuuint32_t box[4], estr[4] = {1, 1, 1, 1};
+  const cuuint32_t box_d = f16 ? 64 : 128;
+  if (paged) {
+    dims[0] = d; dims[1] = tokens_or_page_tokens; dims[2] = hkv; dims[3] = num_pages;
+    strides[0] = d * es;
+    strides[1] = tokens_or_page_tokens * d * es;
+    strides[2] = (cuuint64_t)hkv * tokens_or_page_tokens * d * es;
+    box[0] = box_d; box[1] = tile; box[2] = 1; box[3] = 1;
+  } else {
+    dims[0] = d; dims[1] = hkv; dims[2] = tokens_or_page_tokens; dims[3] = 1;
+    strides[0] = d * es;
+    strides[1] = (cuuint64_t)hkv * d * es;
+    strides[2] = (cuuint64_t)tokens_or_page_tokens * hkv * d * es;
+    box[0] = box_d; box[1] = 1; box[2] = tile; box[3] = 1;
+  }
+  CUresult r = fn(map, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4,
+                  const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  f16 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+// Chunk length (tokens) from the context length and the SM count: enough CTAs to fill every SM
+// several times over, each long enough to amortise its pipeline fill, and at most kMaxChunks
+// per sequence.  Always a multiple of 64 tokens.
+int pick_chunk_tokens(int batch, int hkv, int64_t max_len) {
+  const int64_t tiles = (max_len + 63) / 64;
+  const int64_t target_ctas = (int64_t)sm_count() * 2 * 8;
+  int64_t per_seq = target_ctas / ((int64_t)batch * hkv);  // chunks wanted per (sequence, head)
+  if (per_seq < 1) per_seq = 1;
+  int64_t chunk_tiles = (tiles + per_seq - 1) / per_seq;
+  if (chunk_tiles < 4) chunk_tiles = 4;    // >= 256 tokens per CTA
+  if (chunk_tiles > 64) chunk_tiles = 64;  // <= 4096 tokens per CTA
+  while ((tiles + chunk_tiles - 1) / chunk_tiles > kMaxChunks) chunk_tiles *= 2;
+  return (int)(chunk_tiles * 64);
+}
+
+struct Plan {
+  int chunk_tokens, max_chunks;
+  size_t part_o_bytes, part_ml_bytes;
+};
+
+Plan make_plan(int batch, int hq, int hkv, int d, int64_t max_len) {
+  Plan pl;
+  pl.chunk_tokens = pick_chunk_tokens(batch, hkv, max_len < 1 ? 1 : max_len);
+  pl.max_chunks = (int)((max_len + pl.chunk_tokens - 1) / pl.chunk_tokens);
+  if (pl.max_chunks < 1) pl.max_chunks = 1;
+  pl.part_o_bytes = (size_t)batch * hq * pl.max_chunks * d * sizeof(float);
+  pl.part_ml_bytes = (size_t)batch * hq * pl.max_chunks * 2 * sizeof(float);
+  return pl;
+}
+
+// Opts a kernel in to more than 48 KB of dynamic shared memory, once per (kernel, device).
+bool set_smem(const void *kernel, int bytes) {
+  static std::mutex mu;
+  static std::set<std::pair<const void *, int>> done;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return false;
+  std::lock_guard<std::mutex> lock(mu);
+  if (done.count({kernel, dev})) return true;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) !=
+      cudaSuccess)
+    return false;
+  done.insert({kernel, dev});
+  return true;
+}
+
+constexpr int kStagesDefault = 3;
+
+template <bool kPaged>
+int launch_f16(const CUtensorMap &mk, const CUtensorMap &mv, const DecodeParams &p, dim3 grid,
+               cudaStream_t st) {
+  auto kern = gqa_split_f16_kernel<kPaged, kStagesDefault, 2>;
+  constexpr int smem = SmemLayout<kStagesDefault>::kDynamicBytes;
+  if (!set_smem(reinterpret_cast<const void *>(kern), smem)) return AXB200_DEVICE_ERROR;
+  kern<<<grid, kThreads, smem, st>>>(mk, mv, p);
+  return launch_status();
+}
+
+template <bool kPaged, int kGroup>
+int launch_f32_g(const CUtensorMap &mk, const CUtensorMap &mv, const DecodeParams &p, dim3 grid,
+                 cudaStream_t st) {
+  auto kern = gqa_split_f32_kernel<kPaged, kStagesDefault, kGroup>;
+  constexpr int smem = SmemLayout<kStagesDefault>::kDynamicBytes;
+  if (!set_smem(reinterpret_cast<const void *>(kern), smem)) return AXB200_DEVICE_ERROR;
+  kern<<<grid, kThreads, smem, st>>>(mk, mv, p);
+  return launch_status();
+}
+
+template <bool kPaged>
+int launch_f32(const CUtensorMap &mk, const CUtensorMap &mv, const DecodeParams &p, dim3 grid,
+               cudaStream_t st) {
+  switch (p.group) {
+    case 1: return launch_f32_g<kPaged, 1>(mk, mv, p, grid, st);
+    case 2: return launch_f32_g<kPaged, 2>(mk, mv, p, grid, st);
+    case 4: return launch_f32_g<kPaged, 4>(mk, mv, p, grid, st);
+    case 8: return launch_f32_g<kPaged, 8>(mk, mv, p, grid, st);
+    default: return AXB200_UNSUPPORTED_TYPE;
+  }
+}
+
+bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Common launcher.  `paged` selects the cache layout; for the token-major layout `tokens` is skv.
+int decode_impl(bool paged, const void *q, void *out, const void *k, const void *v,
+                const int32_t *block_table, const int32_t *seq_lens, int fixed_len, int batch,
+                int hq, int hkv, int d, int page_tokens, int max_blocks, int num_pages,
+                int64_t max_len, int dtype, void *workspace, size_t workspace_bytes,
+                cudaStream_t st) {
+  if (dtype != AXB200_FLOAT16 && dtype != AXB200_FLOAT32) return AXB200_UNSUPPORTED_TYPE;
+  if (!q || !out || !k || !v) return AXB200_INVALID_PTR;
+  if (batch <= 0 || hq <= 0 || hkv <= 0 || d <= 0 || max_len <= 0) return AXB200_INVALID_ARGUMENT;
+  if (hq % hkv != 0) return AXB200_SHAPE_MISMATCH;
+  if (d > 256 || max_len > (int64_t)INT32_MAX - 4096) return AXB200_INVALID_ARGUMENT;
+  if (paged && (!block_table || !seq_lens)) return AXB200_INVALID_PTR;
+  if (paged && (page_tokens <= 0 || page_tokens % 64 != 0 || max_blocks <= 0 || num_pages <= 0))
+    return AXB200_INVALID_ARGUMENT;
+  if (paged && (int64_t)max_blocks * page_tokens < max_len) return AXB200_INVALID_ARGUMENT;
+  if (batch > 65535 || hkv > 65535) return AXB200_INVALID_ARGUMENT;
+
+  const Plan pl = make_plan(batch, hq, hkv, d, max_len);
+  DecodeParams p{};
+  p.q = q;
+  p.out = out;
+  p.block_table = block_table;
+  p.seq_lens = seq_lens;
+  p.fixed_len = fixed_len;
+  p.batch = batch;
+  p.hq = hq;
+  p.hkv = hkv;
+  p.group = hq / hkv;
+  p.page_tokens = paged ? page_tokens : 1;
+  p.max_blocks = max_blocks;
+  p.num_pages = num_pages;
+  p.chunk_tokens = pl.chunk_tokens;
+  p.max_chunks = pl.max_chunks;
+  p.scale = 1.0f / sqrtf((float)d);
+  p.write_final = pl.max_chunks == 1;
+  if (!p.write_final) {
+    if (!workspace || workspace_bytes < pl.part_o_bytes + pl.part_ml_bytes)
+      return AXB200_INVALID_ARGUMENT;
+    if (!aligned16(workspace)) return AXB200_INVALID_PTR;
+    p.part_o = reinterpret_cast<float *>(workspace);
+    p.part_ml = reinterpret_cast<float *>(static_cast<uint8_t *>(workspace) + pl.part_o_bytes);
+  }
+  const dim3 grid(pl.max_chunks, hkv, batch);
+  const bool f16 = dtype == AXB200_FLOAT16;
+  const float dom = p.scale * kLog2e;
+
+  bool tiled = d == kHeadDim && aligned16(k) && aligned16(v) && aligned16(q) && encode_fn();
+  if (tiled && f16 && p.group > kMaxGroupMma) tiled = false;
+  if (tiled && !f16 && !(p.group == 1 || p.group == 2 || p.group == 4 || p.group == 8))
+    tiled = false;
+
+  int status;
+  if (tiled) {
+    CUtensorMap mk, mv;
+    const int tile = f16 ? kTileTokensF16 : kTileTokensF32;
+    const int64_t tok = paged ? page_tokens : max_len;
+    if (!make_map(&mk, k, dtype, paged, d, hkv, tok, num_pages, tile) ||
+        !make_map(&mv, v, dtype, paged, d, hkv, tok, num_pages, tile))
+      return AXB200_INTERNAL_ERROR;
+    if (f16)
+      status = paged ? launch_f16<true>(mk, mv, p, grid, st) : launch_f16<false>(mk, mv, p, grid, st);
+    else
+      status = paged ? launch_f32<true>(mk, mv, p, grid, st) : launch_f32<false>(mk, mv, p, grid, st);
+  } else {
+    if (f16) {
+      auto kk = reinterpret_cast<const __half *>(k), vv = reinterpret_cast<const __half *>(v);
+      if (paged) gqa_split_generic_kernel<__half, true><<<grid, 128, 0, st>>>(kk, vv, p, d);
+      else gqa_split_generic_kernel<__half, false><<<grid, 128, 0, st>>>(kk, vv, p, d);
+    } else {
+      auto kk = reinterpret_cast<const float *>(k), vv = reinterpret_cast<const float *>(v);
+      if (paged) gqa_split_generic_kernel<float, true><<<grid, 128, 0, st>>>(kk, vv, p, d);
+      else gqa_split_generic_kernel<float, false><<<grid, 128, 0, st>>>(kk, vv, p, d);
+    }
+    status = launch_status();
+  }
+  if (status != AXB200_OK) return status;
+  if (!p.write_final) {
+    // The fp16 tiled kernel keeps its maxima in the log2 domain (already scaled); the fp32 and
+    // generic kernels keep raw dot products and scale inside the exponent.
+    const float cdom = (tiled && f16) ? 1.0f : dom;
+    const dim3 cgrid(hq, batch);
+    if (f16) gqa_combine_kernel<__half><<<cgrid, 128, 0, st>>>(p, d, cdom);
+    else gqa_combine_kernel<float><<<cgrid, 128, 0, st>>>(p, d, cdom);
+    status = launch_status();
+  }
+  return status;
+}
+
+}  // namespace
+}  // namespace axb
+
+extern "C" {
+
+const char *axb200_version(void) { return "axono_b200 0.1 (sm_100a)"; }
+
+unsigned int axb200_last_error(void) {
+  if (cudaDeviceSynchronize() != cudaSuccess) return 0x80000000u;
+  unsigned int word = 0;
+  for (int i = 0; i < axb::g_num_error_readers; ++i) word |= axb::g_error_readers[i]();
+  return word;
+}
+
+size_t axb200_gqa_workspace_bytes(int batch, int hq, int hkv, int d, int64_t max_seq_len,
+                                  int dtype) {
+  (void)dtype;
+  if (batch <= 0 || hq <= 0 || hkv <= 0 || d <= 0 || max_seq_len <= 0) return 0;
+  const axb::Plan pl = axb::make_plan(batch, hq, hkv, d, max_seq_len);
+  return pl.part_o_bytes + pl.part_ml_bytes;
+}
+
+int axb200_gqa_decode(const void *q, const void *k, const void *v, void *out, int hq, int hkv,
+                      int d, int64_t skv, int dtype, void *workspace, size_t workspace_bytes,
+                      void *stream) {
+  return axb::decode_impl(false, q, out, k, v, nullptr, nullptr, (int)skv, 1, hq, hkv, d, 0, 0, 1,
+                          skv, dtype, workspace, workspace_bytes,
+                          static_cast<cudaStream_t>(stream));
+}
+
+int axb200_gqa_decode_paged(const void *q, void *out, const void *k_pages, const void *v_pages,
+                            const int32_t *block_table, const int32_t *seq_lens, int batch, int hq,
+                            int hkv, int d, int page_tokens, int max_blocks, int num_pages,
+                            int64_t max_seq_len, int dtype, void *workspace,
+                            size_t workspace_bytes, void *stream) {
+  return axb::decode_impl(true, q, out, k_pages, v_pages, block_table, seq_lens, 0, batch, hq, hkv,
+                          d, page_tokens, max_blocks, num_pages, max_seq_len, dtype, workspace,
+                          workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,343 @@
+// RoPE / M-RoPE and the KV-cache append for sm_100a.  Replaces the reference's Rope
+// (src/ops/cuda/sequence.cu:84-101,318-342), RopeThd (:186-212,421-449), RopeWithCosSin
+// (:166-183,344-367), MropeCosSin (:372-419) and, for the decode step, the concat-based cache
+// update (axono/python/axono/nn/kv_cache.py:96-102 -> src/ops/cuda/sequence.cu:474-521).
+//
+// Arithmetic follows the reference's CPU twins (src/ops/cpu/sequence.cpp:54-234): the angle is
+// float(position) * inv_freq[i] in fp32, cos/sin are the full-range functions (positions reach
+// tens of thousands, so the fast intrinsics would be wrong), and pair (i, i + dim/2) rotates as
+// (a*c - b*s, b*c + a*s).  For plain rope the inverse frequencies theta^(-2i/dim) are computed
+// on the host with the C library's powf - the function the reference's CPU op calls - and
+// passed to the kernel by value, so the table is bit-identical to the reference's.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace axb {
+namespace {
+
+constexpr int kMaxHalf = 128;  // head_dim <= 256
+
+struct InvFreqTable {
+  float f[kMaxHalf];
+};
+
+template <typename T>
+__device__ __forceinline__ float ld(const T *p);
+template <>
+__device__ __forceinline__ float ld<float>(const float *p) { return *p; }
+template <>
+__device__ __forceinline__ float ld<__half>(const __half *p) { return __half2float(*p); }
+template <typename T>
+__device__ __forceinline__ void st(T *p, float v);
+template <>
+__device__ __forceinline__ void st<float>(float *p, float v) { *p = v; }
+template <>
+__device__ __forceinline__ void st<__half>(__half *p, float v) { *p = __float2half_rn(v); }
+
+// Position of rotary pair i: the stride-3 M-RoPE rule (src/ops/cpu/sequence.cpp:222-227).
+__device__ __forceinline__ float pair_position(int i, float pt, float ph, float pw, int h_lim,
+                                               int w_lim) {
+  if (i % 3 == 1 && i < h_lim) return ph;
+  if (i % 3 == 2 && i < w_lim) return pw;
+  return pt;
+}
+
+enum RopeMode { kModeTheta = 0, kModeMrope = 1, kModeCosSin = 2 };
+
+// One thread per (row, head, pair).  out may alias x: each thread reads its pair before writing.
+template <typename T, int kMode>
+__global__ void __launch_bounds__(256)
+rope_kernel(const T *x, T *out, const int64_t *pos, const float *inv_freq_dev,
+            const InvFreqTable table, const float *cos_t, const float *sin_t, int64_t rows,
+            int heads, int dim, int h_lim, int w_lim) {
+  const int half = dim / 2;
+  const int64_t total = rows * heads * half;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int i = (int)(idx % half);
+    const int64_t rh = idx / half;
+    const int64_t r = rh / heads;
+    const T *src = x + rh * dim;
+    T *dst = out + rh * dim;
+    const float a = ld(src + i), b = ld(src + i + half);
+    float c0, s0, c1, s1;
+    if (kMode == kModeCosSin) {
+      c0 = cos_t[r * dim + i];
+      s0 = sin_t[r * dim + i];
+      c1 = cos_t[r * dim + i + half];
+      s1 = sin_t[r * dim + i + half];
+    } else {
+      float p, f;
+      if (kMode == kModeMrope) {
+        p = pair_position(i, (float)pos[r], (float)pos[rows + r], (float)pos[2 * rows + r], h_lim,
+                          w_lim);
+        f = inv_freq_dev[i];
+      } else {
+        p = (float)pos[r];
+        f = table.f[i];
+      }
+      const float ang = p * f;
+      sincosf(ang, &s0, &c0);
+      c1 = c0;
+      s1 = s0;
+    }
+    st(dst + i, a * c0 - b * s0);
+    st(dst + i + half, b * c1 + a * s1);
+  }
+}
+
+__global__ void __launch_bounds__(256)
+mrope_cos_sin_kernel(const int64_t *pos, const float *inv_freq, float *cos_out, float *sin_out,
+                     int64_t rows, int half, int h_lim, int w_lim) {
+  const int64_t total = rows * half;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int i = (int)(idx % half);
+    const int64_t r = idx / half;
+    const float p = pair_position(i, (float)pos[r], (float)pos[rows + r], (float)pos[2 * rows + r],
+                                  h_lim, w_lim);
+    float s, c;
+    sincosf(p * inv_freq[i], &s, &c);
+    cos_out[r * 2 * half + i] = c;
+    cos_out[r * 2 * half + i + half] = c;
+    sin_out[r * 2 * half + i] = s;
+    sin_out[r * 2 * half + i + half] = s;
+  }
+}
+
+// ---- append + rotate ------------------------------------------------------------------------
+struct AppendParams {
+  void *q;
+  const void *k_new, *v_new;
+  void *k_pages, *v_pages;
+  const int32_t *block_table;
+  int32_t *seq_lens;
+  const int64_t *pos;
+  const float *inv_freq_dev;
+  int rotate, mrope, h_lim, w_lim;
+  int batch, hq, hkv, d;
+  int page_tokens, max_blocks, num_pages;
+  int advance;
+};
+
+// One CTA per sequence: rotates q in place, rotates k and copies v into slot seq_lens[b] of the
+// sequence's pages (page layout (hkv, page_tokens, d)), then - as the CTA's last act - bumps
+// seq_lens[b].  The slot index is read before any thread of the CTA can have bumped it.
+template <typename T>
+__global__ void __launch_bounds__(256)
+kv_append_rope_kernel(const AppendParams p, const InvFreqTable table) {
+  __shared__ int s_len;
+  const int b = blockIdx.x;
+  if (threadIdx.x == 0) s_len = p.seq_lens[b];
+  __syncthreads();
+  const int len = s_len;
+  const int half = p.d / 2;
+
+  float pt, ph, pw;
+  if (p.pos == nullptr) {
+    pt = ph = pw = (float)len;
+  } else if (p.mrope) {
+    pt = (float)p.pos[b];
+    ph = (float)p.pos[p.batch + b];
+    pw = (float)p.pos[2 * p.batch + b];
+  } else {
+    pt = ph = pw = (float)p.pos[b];
+  }
+
+  const int slot = len / p.page_tokens;
+  int page = -1;
+  if (len >= 0 && slot < p.max_blocks) page = p.block_table[(size_t)b * p.max_blocks + slot];
+  const bool page_ok = page >= 0 && page < p.num_pages;
+  if (!page_ok && threadIdx.x == 0)
+    atomicOr(&g_error_word, (len >= 0 && slot < p.max_blocks) ? AXB200_ERR_BAD_PAGE
+                                                              : AXB200_ERR_CAPACITY);
+  const int tok = len % p.page_tokens;
+
+  T *q = reinterpret_cast<T *>(p.q) + (size_t)b * p.hq * p.d;
+  const T *kn = reinterpret_cast<const T *>(p.k_new) + (size_t)b * p.hkv * p.d;
+  const T *vn = reinterpret_cast<const T *>(p.v_new) + (size_t)b * p.hkv * p.d;
+
+  const int q_pairs = p.hq * half, k_pairs = p.hkv * half;
+  for (int idx = threadIdx.x; idx < q_pairs + k_pairs; idx += blockDim.x) {
+    const bool is_q = idx < q_pairs;
+    const int j = is_q ? idx : idx - q_pairs;
+    const int h = j / half, i = j % half;
+    float c = 1.f, s = 0.f;
+    if (p.rotate) {
+      const float f = p.mrope || p.inv_freq_dev ? p.inv_freq_dev[i] : table.f[i];
+      const float posv = p.mrope ? pair_position(i, pt, ph, pw, p.h_lim, p.w_lim) : pt;
+      sincosf(posv * f, &s, &c);
+    }
+    if (is_q) {
+      if (p.rotate) {
+        T *row = q + (size_t)h * p.d;
+        const float a = ld(row + i), bb = ld(row + i + half);
+        st(row + i, a * c - bb * s);
+        st(row + i + half, bb * c + a * s);
+      }
+    } else if (page_ok) {
+      const T *row = kn + (size_t)h * p.d;
+      T *dst = reinterpret_cast<T *>(p.k_pages) +
+               (((size_t)page * p.hkv + h) * p.page_tokens + tok) * p.d;
+      if (p.rotate) {
+        const float a = ld(row + i), bb = ld(row + i + half);
+        st(dst + i, a * c - bb * s);
+        st(dst + i + half, bb * c + a * s);
+      } else {
+        dst[i] = row[i];
+        dst[i + half] = row[i + half];
+      }
+    }
+  }
+  if (page_ok) {
+    for (int idx = threadIdx.x; idx < p.hkv * p.d; idx += blockDim.x) {
+      const int h = idx / p.d, c = idx % p.d;
+      reinterpret_cast<T *>(p.v_pages)[(((size_t)page * p.hkv + h) * p.page_tokens + tok) * p.d + c] =
+          vn[idx];
+    }
+  }
+  if (p.advance && page_ok) {
+    __syncthreads();
+    if (threadIdx.x == 0) p.seq_lens[b] = len + 1;
+  }
+}
+
+// theta^(-2i/dim) with the host C library's powf, as src/ops/cpu/sequence.cpp:83-84 computes it.
+void fill_table(InvFreqTable *t, float theta, int dim) {
+  for (int i = 0; i < dim / 2 && i < kMaxHalf; ++i)
+    t->f[i] = powf(theta, -2.0f * static_cast<float>(i) / static_cast<float>(dim));
+}
+
+int grid_for(int64_t total) {
+  int64_t blocks = (total + 255) / 256;
+  if (blocks < 1) blocks = 1;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  return (int)blocks;
+}
+
+template <int kMode>
+int rope_dispatch(const void *x, void *out, const int64_t *pos, const float *inv_freq,
+                  const InvFreqTable &table, const float *cos_t, const float *sin_t, int64_t rows,
+                  int heads, int dim, int h_lim, int w_lim, int dtype, cudaStream_t st) {
+  const int64_t total = rows * heads * (dim / 2);
+  if (total == 0) return AXB200_OK;
+  const int grid = grid_for(total);
+  if (dtype == AXB200_FLOAT32)
+    rope_kernel<float, kMode><<<grid, 256, 0, st>>>(
+        reinterpret_cast<const float *>(x), reinterpret_cast<float *>(out), pos, inv_freq, table,
+        cos_t, sin_t, rows, heads, dim, h_lim, w_lim);
+  else
+    rope_kernel<__half, kMode><<<grid, 256, 0, st>>>(
+        reinterpret_cast<const __half *>(x), reinterpret_cast<__half *>(out), pos, inv_freq, table,
+        cos_t, sin_t, rows, heads, dim, h_lim, w_lim);
+  return launch_status();
+}
+
+int check_rope_args(const void *x, const void *out, int64_t rows, int heads, int dim, int dtype) {
+  if (dtype != AXB200_FLOAT32 && dtype != AXB200_FLOAT16) return AXB200_UNSUPPORTED_TYPE;
+  if (!x || !out) return AXB200_INVALID_PTR;
+  if (rows < 0 || heads <= 0 || dim <= 0 || dim % 2 != 0 || dim / 2 > kMaxHalf)
+    return AXB200_INVALID_ARGUMENT;
+  return AXB200_OK;
+}
+
+}  // namespace
+}  // namespace axb
+
+extern "C" {
+
+int axb200_rope(const void *x, const int64_t *pos, float theta, void *out, int64_t rows, int heads,
+                int dim, int dtype, void *stream) {
+  int st = axb::check_rope_args(x, out, rows, heads, dim, dtype);
+  if (st != AXB200_OK) return st;
+  if (!pos) return AXB200_INVALID_PTR;
+  axb::InvFreqTable table{};
+  axb::fill_table(&table, theta, dim);
+  return axb::rope_dispatch<axb::kModeTheta>(x, out, pos, nullptr, table, nullptr, nullptr, rows,
+                                             heads, dim, 0, 0, dtype,
+                                             static_cast<cudaStream_t>(stream));
+}
+
+int axb200_rope_thd(const void *x, const int64_t *pos, const float *inv_freq, int t_sec, int h_sec,
+                    int w_sec, void *out, int64_t rows, int heads, int dim, int dtype,
+                    void *stream) {
+  (void)t_sec;
+  int st = axb::check_rope_args(x, out, rows, heads, dim, dtype);
+  if (st != AXB200_OK) return st;
+  if (!pos || !inv_freq) return AXB200_INVALID_PTR;
+  axb::InvFreqTable table{};
+  return axb::rope_dispatch<axb::kModeMrope>(x, out, pos, inv_freq, table, nullptr, nullptr, rows,
+                                             heads, dim, h_sec * 3, w_sec * 3, dtype,
+                                             static_cast<cudaStream_t>(stream));
+}
+
+int axb200_rope_with_cos_sin(const void *x, const float *cos_t, const float *sin_t, void *out,
+                             int64_t rows, int heads, int dim, int dtype, void *stream) {
+  int st = axb::check_rope_args(x, out, rows, heads, dim, dtype);
+  if (st != AXB200_OK) return st;
+  if (!cos_t || !sin_t) return AXB200_INVALID_PTR;
+  axb::InvFreqTable table{};
+  return axb::rope_dispatch<axb::kModeCosSin>(x, out, nullptr, nullptr, table, cos_t, sin_t, rows,
+                                              heads, dim, 0, 0, dtype,
+                                              static_cast<cudaStream_t>(stream));
+}
+
+int axb200_mrope_cos_sin(const int64_t *pos, const float *inv_freq, int h_sec, int w_sec,
+                         float *cos_out, float *sin_out, int64_t rows, int half, void *stream) {
+  if (!pos || !inv_freq || !cos_out || !sin_out) return AXB200_INVALID_PTR;
+  if (half <= 0 || rows < 0) return AXB200_INVALID_ARGUMENT;
+  if (rows == 0) return AXB200_OK;
+  axb::mrope_cos_sin_kernel<<<axb::grid_for(rows * half), 256, 0,
+                              static_cast<cudaStream_t>(stream)>>>(
+      pos, inv_freq, cos_out, sin_out, rows, half, h_sec * 3, w_sec * 3);
+  return axb::launch_status();
+}
+
+int axb200_kv_append_rope(void *q, const void *k_new, const void *v_new, void *k_pages,
+                          void *v_pages, const int32_t *block_table, int32_t *seq_lens,
+                          const int64_t *pos, const float *inv_freq, float theta, int rotate,
+                          int mrope, int h_sec, int w_sec, int batch, int hq, int hkv, int d,
+                          int page_tokens, int max_blocks, int num_pages, int dtype, int advance,
+                          void *stream) {
+  if (dtype != AXB200_FLOAT32 && dtype != AXB200_FLOAT16) return AXB200_UNSUPPORTED_TYPE;
+  if (!k_new || !v_new || !k_pages || !v_pages || !block_table || !seq_lens)
+    return AXB200_INVALID_PTR;
+  if (rotate && !q && hq > 0) return AXB200_INVALID_PTR;
+  if (batch <= 0 || hq < 0 || hkv <= 0 || d <= 0 || d % 2 != 0 || d / 2 > axb::kMaxHalf ||
+      page_tokens <= 0 || max_blocks <= 0 || num_pages <= 0)
+    return AXB200_INVALID_ARGUMENT;
+  if (rotate && mrope && !inv_freq) return AXB200_INVALID_PTR;
+  axb::AppendParams p{};
+  p.q = q;
+  p.k_new = k_new;
+  p.v_new = v_new;
+  p.k_pages = k_pages;
+  p.v_pages = v_pages;
+  p.block_table = block_table;
+  p.seq_lens = seq_lens;
+  p.pos = pos;
+  p.inv_freq_dev = inv_freq;
+  p.rotate = rotate;
+  p.mrope = mrope;
+  p.h_lim = h_sec * 3;
+  p.w_lim = w_sec * 3;
+  p.batch = batch;
+  p.hq = q ? hq : 0;
+  p.hkv = hkv;
+  p.d = d;
+  p.page_tokens = page_tokens;
+  p.max_blocks = max_blocks;
+  p.num_pages = num_pages;
+  p.advance = advance;
+  axb::InvFreqTable table{};
+  if (rotate && !inv_freq) axb::fill_table(&table, theta, d);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == AXB200_FLOAT32)
+    axb::kv_append_rope_kernel<float><<<batch, 256, 0, st>>>(p, table);
+  else
+    axb::kv_append_rope_kernel<__half><<<batch, 256, 0, st>>>(p, table);
+  return axb::launch_status();
+}
+
+}  // extern "C"

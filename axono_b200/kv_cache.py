@@ -1,0 +1,128 @@
+"""KV-cache components behind the reference's `KVCache` interface
+(axono/python/axono/nn/kv_cache.py:41-68: update / get / reset / __len__).
+
+`PagedKVCache` replaces `DynamicKVCache` (kv_cache.py:71-117), whose `update` re-copies the whole
+cache with `concat` every step: here pages have fixed addresses, an append writes one token per
+sequence, and the sequence lengths live in device memory so a captured CUDA graph follows the
+growing cache.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import ops
+
+
+class KVCache:
+    """Abstract cache: subclasses implement update / get / reset / __len__."""
+
+    def update(self, layer_idx: int, k_new, v_new):  # pragma: no cover
+        raise NotImplementedError
+
+    def get(self, layer_idx: int):  # pragma: no cover
+        raise NotImplementedError
+
+    def reset(self):  # pragma: no cover
+        raise NotImplementedError
+
+    def __len__(self) -> int:  # pragma: no cover
+        raise NotImplementedError
+
+
+class PagedKVCache(KVCache):
+    """Per-layer page pools (num_pages, n_kv_heads, page_tokens, head_dim) shared by `batch`
+    sequences, one block table and one device-resident length vector per cache.
+
+    All layers share the block table; `seq_lens` advances once per decode step (on the last
+    layer's append, or by `advance()`), so every layer of a step writes the same slot.
+    """
+
+    def __init__(self, n_layers, batch, n_kv_heads, head_dim, max_seq_len, dtype=torch.float16,
+                 device="cuda", page_tokens=64, page_order=None):
+        if page_tokens % 64 != 0:
+            raise RuntimeError("PagedKVCache: page_tokens must be a multiple of 64")
+        self.n_layers, self.batch = n_layers, batch
+        self.n_kv_heads, self.head_dim = n_kv_heads, head_dim
+        self.page_tokens = page_tokens
+        self.max_blocks = (max_seq_len + page_tokens - 1) // page_tokens
+        self.max_seq_len = self.max_blocks * page_tokens
+        self.num_pages = batch * self.max_blocks
+        self.dtype, self.device = dtype, torch.device(device)
+        shape = (self.num_pages, n_kv_heads, page_tokens, head_dim)
+        # zero-filled like every new reference tensor (src/core/cuda/detail.cu:217-247)
+        self.k_pages = [torch.zeros(shape, dtype=dtype, device=device) for _ in range(n_layers)]
+        self.v_pages = [torch.zeros(shape, dtype=dtype, device=device) for _ in range(n_layers)]
+        if page_order is None:
+            page_order = torch.arange(self.num_pages, dtype=torch.int32)
+        self.block_table = page_order.to(torch.int32).reshape(batch, self.max_blocks).contiguous().to(device)
+        self.seq_lens = torch.zeros(batch, dtype=torch.int32, device=device)
+        self._host_len_bound = 0  # host-side upper bound of seq_lens (sizes grids, no sync)
+
+    # -- reference interface ------------------------------------------------------------------
+    def update(self, layer_idx: int, k_new, v_new):
+        """Appends one token per sequence: k_new/v_new (batch, n_kv_heads, head_dim), no rotation."""
+        last = layer_idx == self.n_layers - 1
+        ops.kv_append_rope(None, k_new, v_new, self.k_pages[layer_idx], self.v_pages[layer_idx],
+                           self.block_table, self.seq_lens, rotate=False, advance=last)
+        if last:
+            self._host_len_bound += 1
+
+    def append_rope(self, layer_idx: int, q, k_new, v_new, pos=None, inv_freq=None, theta=10000.0,
+                    mrope_section=None):
+        """rope(q) in place + rope(k_new) + append of (k_new, v_new) in one launch."""
+        last = layer_idx == self.n_layers - 1
+        ops.kv_append_rope(q, k_new, v_new, self.k_pages[layer_idx], self.v_pages[layer_idx],
+                           self.block_table, self.seq_lens, pos=pos, inv_freq=inv_freq, theta=theta,
+                           mrope_section=mrope_section, rotate=True, advance=last)
+        if last:
+            self._host_len_bound += 1
+        return q
+
+    def get(self, layer_idx: int):
+        """(k_pages, v_pages, block_table, seq_lens) of the layer - the paged equivalent of the
+        reference's (k_full, v_full)."""
+        return self.k_pages[layer_idx], self.v_pages[layer_idx], self.block_table, self.seq_lens
+
+    def attend(self, layer_idx: int, q, out=None, extra_tokens: int = 0):
+        """Decode attention of q (batch, hq, d) over the layer's cache.  `extra_tokens` widens the
+        host-side length bound for layers that have appended this step before seq_lens advanced."""
+        bound = min(self.max_seq_len, self._host_len_bound + extra_tokens)
+        return ops.gqa_decode_attention_paged(q, self.k_pages[layer_idx], self.v_pages[layer_idx],
+                                              self.block_table, self.seq_lens, max(bound, 1), out=out)
+
+    def reset(self):
+        self.seq_lens.zero_()
+        self._host_len_bound = 0
+
+    def __len__(self) -> int:
+        return int(self.seq_lens.max().item()) if self.batch else 0
+
+    # -- bulk fill (prefill stand-in for tests and benchmarks) -----------------------------------
+    def fill(self, layer_idx: int, k, v, lens):
+        """Writes k/v (batch, L, n_kv_heads, head_dim) token-major into the pages and sets the
+        lengths (host list or tensor).  Data movement only; not a hot-path operator."""
+        lens_t = torch.as_tensor(lens, dtype=torch.int32)
+        L = k.shape[1]
+        nb = (L + self.page_tokens - 1) // self.page_tokens
+        pad = nb * self.page_tokens - L
+        for src, pool in ((k, self.k_pages[layer_idx]), (v, self.v_pages[layer_idx])):
+            if pad:
+                src = torch.nn.functional.pad(src, (0, 0, 0, 0, 0, pad))
+            blk = src.reshape(self.batch, nb, self.page_tokens, self.n_kv_heads, self.head_dim)
+            blk = blk.permute(0, 1, 3, 2, 4).reshape(self.batch * nb, self.n_kv_heads, self.page_tokens,
+                                                     self.head_dim)
+            idx = self.block_table[:, :nb].reshape(-1).long()
+            pool[idx] = blk.to(pool.dtype)
+        self.seq_lens.copy_(lens_t)
+        self._host_len_bound = int(lens_t.max().item())
+
+    def gather(self, layer_idx: int, b: int):
+        """Sequence b's cache as token-major (len, n_kv_heads, head_dim) tensors (for checks)."""
+        n = int(self.seq_lens[b].item())
+        nb = (n + self.page_tokens - 1) // self.page_tokens
+        idx = self.block_table[b, :nb].long()
+        outs = []
+        for pool in (self.k_pages[layer_idx], self.v_pages[layer_idx]):
+            t = pool[idx].permute(0, 2, 1, 3).reshape(nb * self.page_tokens, self.n_kv_heads, self.head_dim)
+            outs.append(t[:n].contiguous())
+        return outs[0], outs[1]

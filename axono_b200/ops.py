@@ -1,0 +1,268 @@
+"""Host-side mirror of the reference's operator API for the decode path.
+
+Function names, argument order and meaning, and error behaviour (RuntimeError on a non-OK
+status) follow the reference's Python surface:
+
+    gqa_decode_attention(q, k, v)              axono/python/axono/gqa.py:13-33
+    silu_mul(gate, up)                         axono/python/axono/fused.py:19-36
+    add_rms_norm(x, residual, weight, eps)     axono/python/axono/fused.py:39-44
+    rope / rope_thd / rope_with_cos_sin / mrope_cos_sin / concat
+                                               axono/python/axono/core/ops/sequence.py
+    rms_norm(x, weight, eps=1e-5)              axono/python/axono/core/ops/llm.py:99-109
+
+Tensors are CUDA `torch.Tensor`s: PyTorch supplies device memory and the current stream and
+nothing else - every operator is one call into the C ABI (include/axono_b200.h), and there is
+no fallback when the library is missing.  Outputs are allocated here, as the reference's
+binding allocates them (nanobind_module.cpp:1019).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _capi
+
+_DTYPES = {torch.float16: _capi.FLOAT16, torch.float32: _capi.FLOAT32}
+_workspaces: dict = {}
+
+
+def _dt(t: torch.Tensor, op: str) -> int:
+    if not t.is_cuda:
+        raise RuntimeError(f"{op}: expected a CUDA tensor (this package has no CPU path)")
+    code = _DTYPES.get(t.dtype)
+    if code is None:
+        _capi.check(3, op)  # UNSUPPORTED_TYPE
+    return code
+
+
+def _c(t: torch.Tensor) -> torch.Tensor:
+    return t if t.is_contiguous() else t.contiguous()
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def last_error() -> int:
+    return int(_capi.lib().axb200_last_error())
+
+
+def workspace(device, nbytes: int) -> torch.Tensor:
+    """Scratch for the decode-attention partials, cached per device and grown on demand.
+    Call once with the largest size before capturing a CUDA graph."""
+    key = torch.device(device)
+    if key.index is None:
+        key = torch.device("cuda", torch.cuda.current_device())
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=key)
+        _workspaces[key] = buf
+    return buf
+
+
+def gqa_workspace_bytes(batch, hq, hkv, d, max_seq_len, dtype=torch.float16) -> int:
+    return int(_capi.lib().axb200_gqa_workspace_bytes(batch, hq, hkv, d, int(max_seq_len), _DTYPES[dtype]))
+
+
+def gqa_decode_attention(q, k, v):
+    """q (1, n_q_heads, head_dim); k/v (seq_len, n_kv_heads, head_dim) -> (1, n_q_heads, head_dim).
+    Equals scaled_dot_product_attention(q, k, v, is_causal=False); scale 1/sqrt(head_dim)."""
+    op = "gqa_decode_attention"
+    dt = _dt(q, op)
+    if q.dim() != 3 or k.dim() != 3 or v.dim() != 3:
+        _capi.check(3, op)
+    if k.dtype != q.dtype or v.dtype != q.dtype:
+        _capi.check(3, op)
+    sq, hq, d = q.shape
+    skv, hkv, dk = k.shape
+    if sq != 1:
+        _capi.check(1, op)
+    if dk != d or tuple(v.shape) != (skv, hkv, d) or hkv == 0 or hq % hkv != 0:
+        _capi.check(4, op)
+    q, k, v = _c(q), _c(k), _c(v)
+    out = torch.empty_like(q)
+    lib = _capi.lib()
+    ws_bytes = lib.axb200_gqa_workspace_bytes(1, hq, hkv, d, skv, dt)
+    ws = workspace(q.device, ws_bytes)
+    _capi.check(lib.axb200_gqa_decode(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), hq, hkv, d,
+                                      skv, dt, ws.data_ptr(), ws.numel(), _stream(q)), op)
+    return out
+
+
+def gqa_decode_attention_paged(q, k_pages, v_pages, block_table, seq_lens, max_seq_len, out=None):
+    """Batched decode over a paged cache (extension of the reference op to a batch).
+    q (batch, hq, d); k_pages/v_pages (num_pages, hkv, page_tokens, d); block_table int32
+    (batch, max_blocks); seq_lens int32 (batch) on the device; max_seq_len a host upper bound."""
+    op = "gqa_decode_attention_paged"
+    dt = _dt(q, op)
+    batch, hq, d = q.shape
+    num_pages, hkv, page_tokens, dk = k_pages.shape
+    if dk != d or v_pages.shape != k_pages.shape:
+        _capi.check(4, op)
+    if block_table.dtype != torch.int32 or seq_lens.dtype != torch.int32:
+        _capi.check(3, op)
+    q = _c(q)
+    if out is None:
+        out = torch.empty_like(q)
+    lib = _capi.lib()
+    ws_bytes = lib.axb200_gqa_workspace_bytes(batch, hq, hkv, d, int(max_seq_len), dt)
+    ws = workspace(q.device, ws_bytes)
+    _capi.check(lib.axb200_gqa_decode_paged(
+        q.data_ptr(), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
+        seq_lens.data_ptr(), batch, hq, hkv, d, page_tokens, block_table.shape[1], num_pages,
+        int(max_seq_len), dt, ws.data_ptr(), ws.numel(), _stream(q)), op)
+    return out
+
+
+def kv_append_rope(q, k_new, v_new, k_pages, v_pages, block_table, seq_lens, pos=None, inv_freq=None,
+                   theta=10000.0, mrope_section=None, rotate=True, advance=True):
+    """One decode step's rope(q), rope(k) and cache append in one launch.  q (batch,hq,d) is rotated
+    in place; k_new/v_new (batch,hkv,d) land in slot seq_lens[b]; seq_lens advances when asked.
+    pos: int64 (batch), or (3,batch) with mrope_section=(t,h,w); None = the cache length."""
+    op = "kv_append_rope"
+    dt = _dt(k_new, op)
+    batch, hkv, d = k_new.shape
+    hq = q.shape[1] if q is not None else 0
+    num_pages, _, page_tokens, _ = k_pages.shape
+    mrope = mrope_section is not None
+    h_sec, w_sec = (mrope_section[1], mrope_section[2]) if mrope else (0, 0)
+    for t in (q, k_new, v_new):
+        if t is not None and not t.is_contiguous():
+            raise RuntimeError(f"{op}: tensors must be contiguous (q is updated in place)")
+    _capi.check(_capi.lib().axb200_kv_append_rope(
+        _ptr(q), k_new.data_ptr(), v_new.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(),
+        block_table.data_ptr(), seq_lens.data_ptr(), _ptr(pos), _ptr(inv_freq), float(theta),
+        int(rotate), int(mrope), h_sec, w_sec, batch, hq, hkv, d, page_tokens, block_table.shape[1],
+        num_pages, dt, int(advance), _stream(k_new)), op)
+    return q
+
+
+def rope(x, pos_ids, theta: float = 10000.0):
+    op = "rope"
+    dt = _dt(x, op)
+    if x.dim() != 3:
+        _capi.check(3, op)
+    rows, heads, dim = x.shape
+    if pos_ids.dtype != torch.int64 or pos_ids.numel() != rows:
+        _capi.check(3, op)
+    x = _c(x)
+    out = torch.empty_like(x)
+    _capi.check(_capi.lib().axb200_rope(x.data_ptr(), _c(pos_ids).data_ptr(), float(theta), out.data_ptr(),
+                                        rows, heads, dim, dt, _stream(x)), op)
+    return out
+
+
+def rope_thd(x, pos, inv_freq, mrope_section):
+    op = "rope_thd"
+    dt = _dt(x, op)
+    if x.dim() != 3:
+        _capi.check(3, op)
+    rows, heads, dim = x.shape
+    if pos.dtype != torch.int64 or tuple(pos.shape) != (3, rows):
+        _capi.check(4, op)
+    if inv_freq.dtype != torch.float32 or tuple(inv_freq.shape) != (dim // 2,):
+        _capi.check(4, op)
+    x = _c(x)
+    out = torch.empty_like(x)
+    t, h, w = mrope_section
+    _capi.check(_capi.lib().axb200_rope_thd(x.data_ptr(), _c(pos).data_ptr(), _c(inv_freq).data_ptr(), t, h, w,
+                                            out.data_ptr(), rows, heads, dim, dt, _stream(x)), op)
+    return out
+
+
+def rope_with_cos_sin(x, cos, sin):
+    op = "rope_with_cos_sin"
+    dt = _dt(x, op)
+    rows, heads, dim = x.shape
+    if tuple(cos.shape) != (rows, dim) or tuple(sin.shape) != (rows, dim) or cos.dtype != torch.float32:
+        _capi.check(4, op)
+    x = _c(x)
+    out = torch.empty_like(x)
+    _capi.check(_capi.lib().axb200_rope_with_cos_sin(x.data_ptr(), _c(cos).data_ptr(), _c(sin).data_ptr(),
+                                                     out.data_ptr(), rows, heads, dim, dt, _stream(x)), op)
+    return out
+
+
+def mrope_cos_sin(pos, inv_freq, h_sec: int, w_sec: int):
+    op = "mrope_cos_sin"
+    if pos.dim() != 2 or pos.shape[0] != 3 or pos.dtype != torch.int64:
+        _capi.check(4, op)
+    rows, half = pos.shape[1], inv_freq.shape[0]
+    cos = torch.empty((rows, 2 * half), dtype=torch.float32, device=pos.device)
+    sin = torch.empty_like(cos)
+    _capi.check(_capi.lib().axb200_mrope_cos_sin(_c(pos).data_ptr(), _c(inv_freq).data_ptr(), h_sec, w_sec,
+                                                 cos.data_ptr(), sin.data_ptr(), rows, half, _stream(pos)), op)
+    return cos, sin
+
+
+def add_rms_norm(x, residual, weight, eps: float = 1e-6):
+    """y = x + residual; out = y * rsqrt(mean(y^2) + eps) * weight.  Returns (y, out)."""
+    op = "add_rms_norm"
+    dt = _dt(x, op)
+    if x.shape != residual.shape or x.dtype != residual.dtype:
+        _capi.check(4, op)
+    hidden = x.shape[-1]
+    if weight.dim() != 1 or weight.shape[0] != hidden or weight.dtype != x.dtype:
+        _capi.check(4, op)
+    x, residual, weight = _c(x), _c(residual), _c(weight)
+    y = torch.empty_like(x)
+    out = torch.empty_like(x)
+    _capi.check(_capi.lib().axb200_add_rms_norm(x.data_ptr(), residual.data_ptr(), weight.data_ptr(), float(eps),
+                                                y.data_ptr(), out.data_ptr(), x.numel() // hidden, hidden, dt,
+                                                _stream(x)), op)
+    return y, out
+
+
+def silu_mul(gate, up):
+    op = "silu_mul"
+    dt = _dt(gate, op)
+    if gate.shape != up.shape or gate.dtype != up.dtype:
+        _capi.check(4, op)
+    gate, up = _c(gate), _c(up)
+    out = torch.empty_like(gate)
+    _capi.check(_capi.lib().axb200_silu_mul(gate.data_ptr(), up.data_ptr(), out.data_ptr(), gate.numel(), dt,
+                                            _stream(gate)), op)
+    return out
+
+
+def rms_norm(x, weight, eps: float = 1e-5):
+    op = "rms_norm"
+    dt = _dt(x, op)
+    cols = x.shape[-1]
+    has_w = weight is not None and weight.numel() != 0
+    if has_w and (weight.dim() != 1 or weight.shape[0] != cols or weight.dtype != x.dtype):
+        _capi.check(4, op)
+    x = _c(x)
+    out = torch.empty_like(x)
+    _capi.check(_capi.lib().axb200_rms_norm(x.data_ptr(), _c(weight).data_ptr() if has_w else None, float(eps),
+                                            out.data_ptr(), x.numel() // cols, cols, dt, _stream(x)), op)
+    return out
+
+
+def concat(a, b, axis: int):
+    op = "concat"
+    if a.dim() < 1 or a.dim() != b.dim() or a.dtype != b.dtype:
+        _capi.check(1, op)
+    nd = a.dim()
+    ax = axis + nd if axis < 0 else axis
+    if ax < 0 or ax >= nd:
+        _capi.check(1, op)
+    for i in range(nd):
+        if i != ax and a.shape[i] != b.shape[i]:
+            _capi.check(4, op)
+    a, b = _c(a), _c(b)
+    shape = list(a.shape)
+    shape[ax] += b.shape[ax]
+    out = torch.empty(shape, dtype=a.dtype, device=a.device)
+    outer = 1
+    for i in range(ax):
+        outer *= a.shape[i]
+    es = a.element_size()
+    a_bytes = (a.numel() // max(outer, 1)) * es
+    b_bytes = (b.numel() // max(outer, 1)) * es
+    _capi.check(_capi.lib().axb200_concat(a.data_ptr(), b.data_ptr(), out.data_ptr(), outer, a_bytes, b_bytes,
+                                          _stream(a)), op)
+    return out

@@ -1,0 +1,169 @@
+/*
+ * axono_b200 - C ABI of the B200 (sm_100a) decode hot path for Axono.
+ *
+ * Every entry point takes raw device pointers, explicit sizes, a dtype code and a CUDA
+ * stream (cudaStream_t passed as void*; NULL = the legacy default stream, which is
+ * what the reference's ops launch on outside capture, src/core/cuda/graph.cu:58-62).
+ * Every entry point returns an int whose values are those of axono::core::Status
+ * (include/axono/core/types.h:54-64); no exception crosses this boundary.  dtype codes
+ * are the values of axono::core::DataType (include/axono/core/types.h:18-27).
+ *
+ * No entry point synchronises the stream, and none allocates device memory, so all of
+ * them may be recorded into a CUDA graph (the reference's compile()/CUDAGraph contract,
+ * axono/python/axono/core/compile.py:69-174).  Scratch memory is passed in by the caller
+ * (see axb200_gqa_workspace_bytes).
+ */
+#ifndef AXONO_B200_H_
+#define AXONO_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* axono::core::Status, include/axono/core/types.h:54-64 */
+enum {
+  AXB200_OK = 0,
+  AXB200_INVALID_ARGUMENT = 1,
+  AXB200_OUT_OF_MEMORY = 2,
+  AXB200_UNSUPPORTED_TYPE = 3,
+  AXB200_SHAPE_MISMATCH = 4,
+  AXB200_INTERNAL_ERROR = 5,
+  AXB200_DEVICE_ERROR = 6,
+  AXB200_INVALID_PTR = 7,
+  AXB200_DEVICE_MISMATCH = 8
+};
+
+/* axono::core::DataType, include/axono/core/types.h:18-27 */
+enum {
+  AXB200_INT8 = 0,
+  AXB200_INT16 = 1,
+  AXB200_INT32 = 2,
+  AXB200_INT64 = 3,
+  AXB200_FLOAT16 = 4,
+  AXB200_FLOAT32 = 5,
+  AXB200_FLOAT64 = 6,
+  AXB200_BOOLEAN = 7
+};
+
+/* Bits of the device error word returned by axb200_last_error(). */
+enum {
+  AXB200_ERR_WAIT_TIMEOUT = 1u,   /* a bounded mbarrier wait inside a kernel gave up */
+  AXB200_ERR_BAD_PAGE = 2u,       /* a block-table entry was outside [0, num_pages) */
+  AXB200_ERR_CAPACITY = 4u        /* an append found its sequence at capacity */
+};
+
+const char *axb200_version(void);
+
+/* Reads and clears the error word kernels set instead of trapping (bounded waits that ran
+ * out, page ids out of range).  Synchronises the device.  No counterpart in the reference,
+ * whose kernels never report (src/ops/cuda/gqa.cu:132-135 ignores launch errors). */
+unsigned int axb200_last_error(void);
+
+/* ---- decode attention ------------------------------------------------------------------
+ * Replaces axono::ops::cuda::GqaDecodeAttention (include/axono/ops/cuda/gqa.h:16-20,
+ * src/ops/cuda/gqa.cu:139-182) and its two kernels (split :31-92, merge :95-129).
+ * out = softmax(q.K^T / sqrt(d)).V per query head, head h reads KV head h / (hq/hkv);
+ * every one of the skv cached tokens is visible (no mask).  fp32 accumulation.
+ * dtype: AXB200_FLOAT32 or AXB200_FLOAT16 (q, k, v, out share it).
+ */
+
+/* Bytes of scratch the decode calls need for `batch` sequences of up to `max_seq_len` tokens. */
+size_t axb200_gqa_workspace_bytes(int batch, int hq, int hkv, int d, int64_t max_seq_len, int dtype);
+
+/* Reference layout, one sequence: q (1,hq,d), k/v (skv,hkv,d) token-major contiguous,
+ * out (1,hq,d).  Same contract as libaxono.gqa_decode_attention(q,k,v)
+ * (axono/python/src/nanobind_module.cpp:1016-1029). */
+int axb200_gqa_decode(const void *q, const void *k, const void *v, void *out,
+                      int hq, int hkv, int d, int64_t skv, int dtype,
+                      void *workspace, size_t workspace_bytes, void *stream);
+
+/* Batched, paged cache (extension; the reference op has no batch dimension).
+ * q/out (batch,hq,d).  k_pages/v_pages: (num_pages, hkv, page_tokens, d), page_tokens a
+ * multiple of 64.  block_table int32 (batch, max_blocks): page ids of each sequence in
+ * token order.  seq_lens int32 (batch), device memory, read by the kernel (so a captured
+ * graph follows a growing cache).  max_seq_len: host-side upper bound of seq_lens, sizes
+ * the grid and the scratch.  Result b equals axb200_gqa_decode on sequence b's first
+ * seq_lens[b] tokens. */
+int axb200_gqa_decode_paged(const void *q, void *out, const void *k_pages, const void *v_pages,
+                            const int32_t *block_table, const int32_t *seq_lens,
+                            int batch, int hq, int hkv, int d,
+                            int page_tokens, int max_blocks, int num_pages,
+                            int64_t max_seq_len, int dtype,
+                            void *workspace, size_t workspace_bytes, void *stream);
+
+/* ---- KV-cache append with RoPE / M-RoPE --------------------------------------------------
+ * Replaces, for one decode step of `batch` sequences, the reference's per-layer sequence
+ *   rope|rope_thd(q), rope|rope_thd(k)      (src/ops/cuda/sequence.cu:318-342, 421-449)
+ *   cache.update -> concat(old, new, axis 0) (axono/python/axono/nn/kv_cache.py:96-102,
+ *                                             src/ops/cuda/sequence.cu:474-521)
+ * by one launch: q (batch,hq,d) is rotated in place, k_new (batch,hkv,d) is rotated and
+ * written, v_new copied, into slot seq_lens[b] of sequence b's pages; when `advance` is
+ * non-zero seq_lens[b] is then incremented.  Rotation: rotate-half pairs (i, i+d/2).
+ *   mrope == 0: angle_i = float(pos[b]) * inv_freq[i];   pos int64 (batch)
+ *   mrope != 0: pos int64 (3,batch) rows T,H,W; pair i uses H when i%3==1 && i<3*h_sec,
+ *               W when i%3==2 && i<3*w_sec, else T (src/ops/cpu/sequence.cpp:222-227).
+ * pos == NULL: the position is the cache length seq_lens[b] on every axis.
+ * inv_freq: device float (d/2), or NULL to use theta^(-2i/d) computed on the host with the
+ * C library's powf, exactly as the reference's CPU Rope does (src/ops/cpu/sequence.cpp:83-84).
+ * rotate == 0 skips the rotation (plain append).
+ */
+int axb200_kv_append_rope(void *q, const void *k_new, const void *v_new,
+                          void *k_pages, void *v_pages,
+                          const int32_t *block_table, int32_t *seq_lens,
+                          const int64_t *pos, const float *inv_freq, float theta,
+                          int rotate, int mrope, int h_sec, int w_sec,
+                          int batch, int hq, int hkv, int d,
+                          int page_tokens, int max_blocks, int num_pages,
+                          int dtype, int advance, void *stream);
+
+/* ---- RoPE family (stand-alone ops) --------------------------------------------------------
+ * x/out (rows,heads,dim); out may alias x. */
+
+/* axono::ops::cuda::Rope, include/axono/ops/cuda/sequence.h, src/ops/cuda/sequence.cu:318-342;
+ * pos int64 (rows). */
+int axb200_rope(const void *x, const int64_t *pos, float theta, void *out,
+                int64_t rows, int heads, int dim, int dtype, void *stream);
+
+/* axono::ops::cuda::RopeThd, src/ops/cuda/sequence.cu:421-449; pos int64 (3,rows),
+ * inv_freq float (dim/2); t_sec is accepted and ignored as in the reference (:425). */
+int axb200_rope_thd(const void *x, const int64_t *pos, const float *inv_freq,
+                    int t_sec, int h_sec, int w_sec, void *out,
+                    int64_t rows, int heads, int dim, int dtype, void *stream);
+
+/* axono::ops::cuda::RopeWithCosSin, src/ops/cuda/sequence.cu:344-367; cos/sin float (rows,dim). */
+int axb200_rope_with_cos_sin(const void *x, const float *cos_t, const float *sin_t, void *out,
+                             int64_t rows, int heads, int dim, int dtype, void *stream);
+
+/* axono::ops::cuda::MropeCosSin, src/ops/cuda/sequence.cu:372-419; pos int64 (3,rows),
+ * inv_freq float (half); cos/sin out float (rows, 2*half). */
+int axb200_mrope_cos_sin(const int64_t *pos, const float *inv_freq, int h_sec, int w_sec,
+                         float *cos_out, float *sin_out, int64_t rows, int half, void *stream);
+
+/* ---- fused norm / activation ---------------------------------------------------------------*/
+
+/* axono::ops::cuda::AddRmsNorm, include/axono/ops/cuda/fused.h:14-25, src/ops/cuda/fused.cu:91-110:
+ * y = x + residual; out = y * rsqrt(mean(y^2) + eps) * weight.  x/residual/y/out (rows,hidden),
+ * weight (hidden), all of `dtype`; fp32 math. */
+int axb200_add_rms_norm(const void *x, const void *residual, const void *weight, float eps,
+                        void *y, void *out, int64_t rows, int hidden, int dtype, void *stream);
+
+/* axono::ops::cuda::SiluMul, src/ops/cuda/fused.cu:76-89: out = gate / (1 + exp(-gate)) * up. */
+int axb200_silu_mul(const void *gate, const void *up, void *out, int64_t n, int dtype, void *stream);
+
+/* axono::ops::cuda::RmsNorm, include/axono/ops/cuda/llm.h:33-36, src/ops/cuda/llm.cu:345-373:
+ * out = x * rsqrt(mean(x^2) + eps) * weight over the last dim; weight may be NULL. */
+int axb200_rms_norm(const void *x, const void *weight, float eps, void *out,
+                    int64_t rows, int cols, int dtype, void *stream);
+
+/* axono::ops::cuda::Concat, src/ops/cuda/sequence.cu:474-521, on bytes: out (outer, a_bytes +
+ * b_bytes) = a (outer, a_bytes) ++ b (outer, b_bytes).  Axis 0 is outer == 1. */
+int axb200_concat(const void *a, const void *b, void *out, int64_t outer,
+                  size_t a_bytes, size_t b_bytes, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AXONO_B200_H_ */
