@@ -16,6 +16,8 @@ _vp, _i, _i64, _sz, _f = C.c_void_p, C.c_int, C.c_int64, C.c_size_t, C.c_float
 SIGNATURES = {
     "axb200_version": (C.c_char_p, []),
     "axb200_last_error": (C.c_uint, []),
+    "axb200_profile_enable": (_i, [_i]),
+    "axb200_profile_collect": (_i, [C.POINTER(C.c_double), C.POINTER(C.c_int)]),
     "axb200_gqa_workspace_bytes": (_sz, [_i, _i, _i, _i, _i64, _i]),
     "axb200_gqa_decode": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i, _vp, _sz, _vp]),
     "axb200_gqa_decode_paged": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i64, _i,

@@ -803,6 +803,27 @@ int launch_f32(const CUtensorMap &mk, const CUtensorMap &mv, const DecodeParams 
   }
 }
 
+// ---- optional timing of the split kernel alone ---------------------------------------------------
+// When enabled (axb200_profile_enable), every decode call brackets its split-kernel launch with
+// a pair of CUDA events on the launching stream; axb200_profile_collect sums them.  Off by
+// default; not for use during stream capture.
+constexpr int kProfilePairs = 4096;
+struct ProfileState {
+  bool enabled = false;
+  int used = 0;
+  cudaEvent_t start[kProfilePairs];
+  cudaEvent_t stop[kProfilePairs];
+  bool created = false;
+};
+ProfileState g_profile;
+std::mutex g_profile_mu;
+
+int profile_slot() {
+  std::lock_guard<std::mutex> lock(g_profile_mu);
+  if (!g_profile.enabled || g_profile.used >= kProfilePairs) return -1;
+  return g_profile.used++;
+}
+
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // Common launcher.  `paged` selects the cache layout; for the token-major layout `tokens` is skv.
@@ -857,6 +878,8 @@ int decode_impl(bool paged, const void *q, void *out, const void *k, const void 
     tiled = false;
 
   int status;
+  const int prof = profile_slot();
+  if (prof >= 0) cudaEventRecord(g_profile.start[prof], st);
   if (tiled) {
     CUtensorMap mk, mv;
     const int tile = f16 ? kTileTokensF16 : kTileTokensF32;
@@ -880,6 +903,7 @@ int decode_impl(bool paged, const void *q, void *out, const void *k, const void 
     }
     status = launch_status();
   }
+  if (prof >= 0) cudaEventRecord(g_profile.stop[prof], st);
   if (status != AXB200_OK) return status;
   if (!p.write_final) {
     // The fp16 tiled kernel keeps its maxima in the log2 domain (already scaled); the fp32 and
@@ -905,6 +929,39 @@ unsigned int axb200_last_error(void) {
   unsigned int word = 0;
   for (int i = 0; i < axb::g_num_error_readers; ++i) word |= axb::g_error_readers[i]();
   return word;
+}
+
+int axb200_profile_enable(int on) {
+  std::lock_guard<std::mutex> lock(axb::g_profile_mu);
+  axb::ProfileState &ps = axb::g_profile;
+  if (on && !ps.created) {
+    for (int i = 0; i < axb::kProfilePairs; ++i) {
+      if (cudaEventCreate(&ps.start[i]) != cudaSuccess || cudaEventCreate(&ps.stop[i]) != cudaSuccess)
+        return AXB200_DEVICE_ERROR;
+    }
+    ps.created = true;
+  }
+  ps.enabled = on != 0;
+  ps.used = 0;
+  return AXB200_OK;
+}
+
+int axb200_profile_collect(double *split_ms_total, int *launches) {
+  if (!split_ms_total || !launches) return AXB200_INVALID_PTR;
+  if (cudaDeviceSynchronize() != cudaSuccess) return AXB200_DEVICE_ERROR;
+  std::lock_guard<std::mutex> lock(axb::g_profile_mu);
+  axb::ProfileState &ps = axb::g_profile;
+  double total = 0.0;
+  for (int i = 0; i < ps.used; ++i) {
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, ps.start[i], ps.stop[i]) != cudaSuccess)
+      return AXB200_DEVICE_ERROR;
+    total += ms;
+  }
+  *split_ms_total = total;
+  *launches = ps.used;
+  ps.used = 0;
+  return AXB200_OK;
 }
 
 size_t axb200_gqa_workspace_bytes(int batch, int hq, int hkv, int d, int64_t max_seq_len,

@@ -1,0 +1,435 @@
+"""Benchmark of the decode hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Workload (default `c3_ragged`): long-context split-K decode attention in fp16 with fp32
+accumulation - batch 64 per GPU, 16 query / 8 KV heads, head_dim 128, per-sequence KV lengths
+uniform in [16384, 32768], K/V = 0.5 * N(0,1), q = N(0,1), all seeded and synthetic.  `b64_l32k`
+is the same with every sequence at 32768 tokens.  A step is one decode step of the path for the
+whole batch: RoPE + KV-cache append of the new token (1 kernel), then the split-K decode attention
+(split kernel + combine kernel) over the paged cache.
+
+One JSON line on rank 0.  `value` = KV-cache GB/s of the whole job with inputs resident in HBM:
+algorithmic bytes (K and V read once, q read, out written) of all ranks / device time of the timed
+steps (CUDA events, max over ranks).  `e2e` = the same metric through the public API with host
+buffers: each step copies q, k_new, v_new from pinned host memory and reads the attention output
+back.  `roofline` = the split kernel alone (event pairs recorded around its launches by the
+library) against the measured HBM peak.  `cpu_baseline` = the reference's CPU SDPA-GQA on the
+host cores, on a bounded sample of the same sequences.
+
+`--impl reference` times only that CPU path (oracle/_ref when built, else the C restatement).
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+HQ, HKV, D = 16, 8, 128
+PAGE_TOKENS = 64
+METRIC = "gqa_decode_kv_cache_bandwidth"
+UNIT = "GB/s"
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_HBM_GBS = 6650.0
+# DRAM bytes moved per algorithmic byte by the split kernel, from the ncu capture summarised in
+# profiles/gqa_split_f16_paged.c2_b8_l8k.ncu.md: (dram read + write) / algorithmic bytes on a small case
+# of the same kernel, taken to scale in proportion to the tokens a launch processes.
+TRAFFIC_PER_ALGO_BYTE = 1.026
+
+WORKLOADS = {
+    "c3_ragged": dict(batch=64, lo=16384, hi=32768),
+    "b64_l32k": dict(batch=64, lo=32768, hi=32768),
+    "c2_b8_l8k": dict(batch=8, lo=8192, hi=8192),
+}
+
+
+def seq_lengths(workload: str, rank: int) -> np.ndarray:
+    w = WORKLOADS[workload]
+    rng = np.random.default_rng(3000 + rank)
+    return rng.integers(w["lo"], w["hi"] + 1, w["batch"]).astype(np.int64)
+
+
+def algo_bytes(lens: np.ndarray, elem: int = 2) -> float:
+    """K and V read once + q read + out written."""
+    return float(2 * lens.sum() * HKV * D * elem + 2 * len(lens) * HQ * D * elem)
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+# ---- clocks ------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML (read-only) on a thread."""
+
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+               0x4: "sw_power_cap", 0x80: "hw_power_brake_slowdown"}
+
+    def __init__(self, torch_index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._active = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            import torch
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            try:
+                uuid = str(torch.cuda.get_device_properties(torch_index).uuid)
+                if not uuid.startswith("GPU-"):
+                    uuid = "GPU-" + uuid
+                self.h = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            except Exception:
+                self.h = pynvml.nvmlDeviceGetHandleByIndex(torch_index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            if self._active.is_set():
+                try:
+                    self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                    mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))
+                    for bit, name in self.REASONS.items():
+                        if mask & bit:
+                            self.reasons.add(name)
+                except Exception:
+                    pass
+            time.sleep(0.004)
+
+    def start(self):
+        self._active.set()
+
+    def pause(self):
+        self._active.clear()
+
+    def summary(self):
+        self._stop.set()
+        if self.nv is None or not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        return {"sm_mhz": int(statistics.median(self.samples)), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ---- CPU reference arm ---------------------------------------------------------------------------
+def cpu_attention_sample(workload: str, budget_s: float, max_seqs: int):
+    """Times the reference's CPU SDPA-GQA (fp32, the only type it supports) on the first sequences
+    of rank 0's batch, one call per sequence as the reference evaluates a batch, until the time
+    budget is spent.  Returns (GB/s in the workload's fp16 byte accounting, tokens/s, info)."""
+    import oracle
+
+    orc = oracle.best()
+    lens = seq_lengths(workload, 0)
+    rng = np.random.default_rng(4000)
+    done_bytes, done_seqs, spent, reps = 0.0, 0, 0.0, 4
+    for b in range(min(max_seqs, len(lens))):
+        L = int(lens[b])
+        q = rng.standard_normal((1, HQ, D)).astype(np.float32)
+        k = (0.5 * rng.standard_normal((L, HKV, D))).astype(np.float32)
+        v = (0.5 * rng.standard_normal((L, HKV, D))).astype(np.float32)
+        run, _, release = orc.prepare_sdpa(q, k, v)
+        run()
+        best = float("inf")
+        for _ in range(reps):
+            t0 = time.perf_counter()
+            run()
+            best = min(best, time.perf_counter() - t0)
+        release()
+        dt = best
+        spent += dt
+        done_bytes += algo_bytes(np.asarray([L]))
+        done_seqs += 1
+        if spent >= budget_s:
+            break
+    cores = os.cpu_count() or 1
+    threads = int(os.environ.get("OMP_NUM_THREADS", cores))
+    info = {"kind": orc.kind, "cores": threads,
+            "sample": f"{done_seqs} sequences of workload {workload} (lengths {int(lens[:done_seqs].min())}.."
+                      f"{int(lens[:done_seqs].max())}), one fp32 SDPA call per sequence on exactly-widened inputs; "
+                      f"bytes counted as the workload's fp16 KV bytes; best of {reps} calls per sequence, buffers wrapped once outside the timed region; "
+                      f"the reference parallelises over its 16 query heads only"}
+    return done_bytes / spent / 1e9, done_seqs / spent, spent, info
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    # a step = the first `per_step` sequences of the batch, one CPU SDPA call each
+    import oracle
+
+    orc = oracle.best()
+    lens = seq_lengths(args.workload, 0)
+    per_step = 2
+    rng = np.random.default_rng(4000)
+    calls = []
+    for b in range(per_step):
+        L = int(lens[b])
+        calls.append(orc.prepare_sdpa(rng.standard_normal((1, HQ, D)).astype(np.float32),
+                                      (0.5 * rng.standard_normal((L, HKV, D))).astype(np.float32),
+                                      (0.5 * rng.standard_normal((L, HKV, D))).astype(np.float32)))
+    step_bytes = algo_bytes(lens[:per_step])
+    for _ in range(args.warmup):
+        for run, _, _ in calls:
+            run()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        for run, _, _ in calls:
+            run()
+    dt = time.perf_counter() - t0
+    for _, _, release in calls:
+        release()
+    value = step_bytes * args.steps / dt / 1e9
+    cores = int(os.environ.get("OMP_NUM_THREADS", os.cpu_count() or 1))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": args.workload, "batch_per_gpu": WORKLOADS[args.workload]["batch"],
+                   "hq": HQ, "hkv": HKV, "head_dim": D,
+                   "note": "CPU reference: each step = the first 2 sequences of the batch, one fp32 SDPA call each, tensors wrapped once outside the timed region"},
+        "tokens_per_s": per_step * args.steps / dt,
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": orc.kind,
+                         "sample": f"{per_step} sequences per step (lengths {lens[:per_step].tolist()}), fp32 SDPA, "
+                                   f"bytes counted as the workload's fp16 KV bytes"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---- our arm ---------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from axono_b200 import _capi, ops
+    from axono_b200.kv_cache import PagedKVCache
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the decode path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def sum_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return float(t.item())
+
+    lib = _capi.lib()
+    w = WORKLOADS[args.workload]
+    B = w["batch"]
+    lens = seq_lengths(args.workload, rank)
+    total_steps = args.warmup + args.steps
+    capacity = int(w["hi"]) + 2 * total_steps + 64
+    gen = torch.Generator(device=device).manual_seed(1234 + rank)
+
+    cache = PagedKVCache(1, B, HKV, D, capacity, dtype=torch.float16, device=device, page_tokens=PAGE_TOKENS)
+    for pool in (cache.k_pages[0], cache.v_pages[0]):  # K, V = 0.5 * N(0,1), generated in slabs
+        step_pages = 512
+        for p0 in range(0, pool.shape[0], step_pages):
+            n = min(step_pages, pool.shape[0] - p0)
+            pool[p0 : p0 + n] = (0.5 * torch.randn((n,) + tuple(pool.shape[1:]), generator=gen, device=device)).half()
+    # a scattered page table: sequences do not own contiguous runs of pages
+    perm = torch.randperm(cache.num_pages, generator=torch.Generator().manual_seed(99 + rank)).to(torch.int32)
+    cache.block_table = perm.reshape(B, cache.max_blocks).contiguous().to(device)
+
+    def set_lengths():
+        cache.seq_lens.copy_(torch.from_numpy(lens.astype(np.int32)))
+        cache._host_len_bound = int(lens.max())
+
+    q = torch.randn((B, HQ, D), generator=gen, device=device).half()
+    k_new = (0.5 * torch.randn((B, HKV, D), generator=gen, device=device)).half()
+    v_new = (0.5 * torch.randn((B, HKV, D), generator=gen, device=device)).half()
+    out = torch.empty_like(q)
+    ops.workspace(device, ops.gqa_workspace_bytes(B, HQ, HKV, D, capacity))
+
+    def step(qt):
+        cache.append_rope(0, qt, k_new, v_new, theta=1e6)
+        cache.attend(0, qt, out=out)
+
+    def bytes_of_steps(first: int, count: int) -> float:
+        return sum(algo_bytes(lens + first + s + 1) for s in range(count))
+
+    sampler = ClockSampler(local_rank)
+
+    # ---- value: inputs resident, CUDA events around K steps ----
+    set_lengths()
+    for _ in range(args.warmup):
+        step(q)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    sampler.start()
+    ev0.record()
+    for _ in range(args.steps):
+        step(q)
+    ev1.record()
+    barrier()
+    sampler.pause()
+    dev_ms = max_over_ranks(ev0.elapsed_time(ev1))
+    my_bytes = bytes_of_steps(args.warmup, args.steps)
+    all_bytes = sum_over_ranks(my_bytes)
+    value = all_bytes / (dev_ms / 1e3) / 1e9
+    tokens_per_s = B * world * args.steps / (dev_ms / 1e3)
+    err = ops.last_error()
+    if err:
+        raise SystemExit(f"device error word {err:#x} after the timed steps")
+
+    # ---- roofline: the split kernel alone, event pairs around its launches ----
+    set_lengths()
+    prof_steps = min(args.steps, 2000)
+    lib.axb200_profile_enable(1)
+    barrier()
+    for _ in range(prof_steps):
+        cache.attend(0, q, out=out)
+    ms_total, launches = ctypes.c_double(0), ctypes.c_int(0)
+    lib.axb200_profile_collect(ctypes.byref(ms_total), ctypes.byref(launches))
+    lib.axb200_profile_enable(0)
+    kern_ms = ms_total.value / max(launches.value, 1)
+    launch_bytes = algo_bytes(lens)
+    achieved = launch_bytes / (kern_ms / 1e3) / 1e9
+    peak, peak_kind = measured_peak()
+    roofline = {"bound": "hbm", "kernel": "gqa_split_f16_kernel<paged>", "achieved": achieved, "peak": peak,
+                "unit": "GB/s", "frac": achieved / peak, "peak_source": f"of {peak_kind}",
+                "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS, "kernel_ms": kern_ms,
+                "launches_timed": launches.value, "algorithmic_bytes_per_launch": launch_bytes,
+                "traffic": None if TRAFFIC_PER_ALGO_BYTE is None else TRAFFIC_PER_ALGO_BYTE * launch_bytes}
+
+    # ---- e2e: public API with host buffers, copies inside the timed region ----
+    set_lengths()
+    pin = lambda t: t.cpu().pin_memory()  # noqa: E731
+    q_h, k_h, v_h = pin(q), pin(k_new), pin(v_new)
+    out_h = torch.empty_like(q_h).pin_memory()
+    q_d, k_d, v_d = torch.empty_like(q), torch.empty_like(k_new), torch.empty_like(v_new)
+    h2d = (q_h.numel() + k_h.numel() + v_h.numel()) * 2
+    d2h = out_h.numel() * 2
+
+    def e2e_step():
+        q_d.copy_(q_h, non_blocking=True)
+        k_d.copy_(k_h, non_blocking=True)
+        v_d.copy_(v_h, non_blocking=True)
+        cache.append_rope(0, q_d, k_d, v_d, theta=1e6)
+        o = cache.attend(0, q_d, out=out)
+        out_h.copy_(o, non_blocking=True)
+        torch.cuda.current_stream().synchronize()  # the host reads the result every step
+
+    for _ in range(max(3, args.warmup // 2)):
+        e2e_step()
+    base = int(cache._host_len_bound - int(lens.max()))
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_step()
+    barrier()
+    e2e_s = max_over_ranks(time.perf_counter() - t0)
+    e2e_bytes = sum_over_ranks(sum(algo_bytes(lens + base + s + 1) for s in range(args.steps)))
+    e2e = {"value": e2e_bytes / e2e_s / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+           "ms_per_step": e2e_s / args.steps * 1e3, "tokens_per_s": B * world * args.steps / e2e_s}
+
+    clocks = sampler.summary()
+
+    # ---- the other single-GPU case of the same kernel, for the record ----
+    extra = {}
+    if world == 1 and args.workload == "c3_ragged" and not args.no_extra:
+        lens32 = np.full(B, 32768, np.int64)
+        cache.seq_lens.copy_(torch.from_numpy(lens32.astype(np.int32)))
+        cache._host_len_bound = 32768
+        lib.axb200_profile_enable(1)
+        for _ in range(20):
+            cache.attend(0, q, out=out)
+        lib.axb200_profile_collect(ctypes.byref(ms_total), ctypes.byref(launches))
+        for _ in range(100):
+            cache.attend(0, q, out=out)
+        lib.axb200_profile_collect(ctypes.byref(ms_total), ctypes.byref(launches))
+        lib.axb200_profile_enable(0)
+        ms32 = ms_total.value / max(launches.value, 1)
+        gbs32 = algo_bytes(lens32) / (ms32 / 1e3) / 1e9
+        extra["b64_l32k"] = {"split_kernel_ms": ms32, "kv_gbs": gbs32, "frac_of_measured": gbs32 / peak,
+                             "frac_of_nominal_8TBs": gbs32 / NOMINAL_HBM_GBS, "tokens_per_s": B / (ms32 / 1e3)}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        gbs, tps, spent, info = cpu_attention_sample(args.workload, args.cpu_budget, 64)
+        cpu = {"value": gbs, "unit": UNIT, "tokens_per_s": tps, "seconds": spent, **info}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": args.workload, "batch_per_gpu": B, "hq": HQ, "hkv": HKV, "head_dim": D,
+                       "kv_len": [int(w["lo"]), int(w["hi"])], "page_tokens": PAGE_TOKENS,
+                       "sharding": f"batch x{world}, no collective on the attention path",
+                       "l2": "inputs larger than L2 (several GB of KV per step)",
+                       "step": "kv_append_rope + gqa_decode_paged (split + combine)"},
+            "tokens_per_s": tokens_per_s,
+            "frac_of_nominal_8TBs": value / (NOMINAL_HBM_GBS * world),
+            "e2e": e2e, "gpu_launches": 3 * args.steps, "clocks": clocks, "roofline": roofline,
+            "cpu_baseline": cpu, "extra": extra,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c3_ragged", choices=sorted(WORKLOADS))
+    ap.add_argument("--cpu-budget", type=float, default=10.0, help="seconds of CPU work for cpu_baseline")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-extra", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

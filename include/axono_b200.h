@@ -62,6 +62,14 @@ const char *axb200_version(void);
  * whose kernels never report (src/ops/cuda/gqa.cu:132-135 ignores launch errors). */
 unsigned int axb200_last_error(void);
 
+/* Timing of the dominant kernel alone, for the benchmark's roofline figure: while enabled,
+ * every decode call records a CUDA-event pair around its split-kernel launch on the launching
+ * stream (up to 4096 calls); collect synchronises the device, returns the summed kernel time and
+ * the number of launches, and resets the count.  Not for use during stream capture.  No
+ * counterpart in the reference (it has no profiling hooks). */
+int axb200_profile_enable(int on);
+int axb200_profile_collect(double *split_ms_total, int *launches);
+
 /* ---- decode attention ------------------------------------------------------------------
  * Replaces axono::ops::cuda::GqaDecodeAttention (include/axono/ops/cuda/gqa.h:16-20,
  * src/ops/cuda/gqa.cu:139-182) and its two kernels (split :31-92, merge :95-129).

@@ -201,6 +201,19 @@ class _Port(_Checker):
         fn(pos3, n, img_start, want, llm_h, llm_w)
         return pos3
 
+    def prepare_sdpa(self, q, k, v):
+        """Same interface as the reference checker's: (run, out, release)."""
+        q, k, v = _f32(q), _f32(k), _f32(v)
+        sq, hq, d = q.shape
+        skv, hkv, _ = k.shape
+        out = np.empty_like(q)
+        fn = self._fn("sdpa_f32", [_f32p, _f32p, _f32p, _f32p, _sz, _sz, _sz, _sz, _sz, C.c_int])
+
+        def _run():
+            self._check(fn(q, k, v, out, sq, hq, hkv, d, skv, 0), "sdpa")
+
+        return _run, out, (lambda: None)
+
     def num_threads(self):
         fn = self._fn("num_threads", [], C.c_int)
         return int(fn())
@@ -222,6 +235,29 @@ class _Reference(_Checker):
         )
         self._check(fn(q, k, v, out, sq, hq, hkv, d, skv, iters, ms), "sdpa_timed")
         return out, ms
+
+
+    def prepare_sdpa(self, q, k, v):
+        """Wraps the buffers once; returns (run, out, release): run() executes the reference's
+        non-causal SDPA into `out`."""
+        q, k, v = _f32(q), _f32(k), _f32(v)
+        sq, hq, d = q.shape
+        skv, hkv, _ = k.shape
+        out = np.empty_like(q)
+        prep = self._fn("sdpa_prepare", [_f32p, _f32p, _f32p, _f32p, _sz, _sz, _sz, _sz, _sz], C.c_void_p)
+        run = self._fn("sdpa_run", [C.c_void_p])
+        rel = self._fn("sdpa_release", [C.c_void_p], None)
+        handle = C.c_void_p(prep(q, k, v, out, sq, hq, hkv, d, skv))
+        keep = [q, k, v, out]  # the wrapped buffers must outlive the handle
+
+        def _run():
+            self._check(run(handle), "sdpa_run")
+
+        def _release():
+            rel(handle)
+            keep.clear()
+
+        return _run, out, _release
 
 
 _port = None

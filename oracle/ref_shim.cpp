@@ -67,6 +67,27 @@ int ref_sdpa_f32_timed(const float *q, const float *k, const float *v,
   return 0;
 }
 
+// A prepared call: the four tensors wrapped once, so repeated runs pay only for the op itself
+// (FromBorrowed allocates and zero-fills a same-sized buffer before it adopts the caller's
+// pointer, src/core/tensor.cpp:138-144, which would otherwise dominate a timed call).
+struct SdpaCall {
+  Tensor q, k, v, out;
+};
+
+void *ref_sdpa_prepare(const float *q, const float *k, const float *v, float *out, size_t sq,
+                       size_t hq, size_t hkv, size_t d, size_t skv) {
+  return new SdpaCall{Wrap(DataType::FLOAT32, {sq, hq, d}, q), Wrap(DataType::FLOAT32, {skv, hkv, d}, k),
+                      Wrap(DataType::FLOAT32, {skv, hkv, d}, v), Wrap(DataType::FLOAT32, {sq, hq, d}, out)};
+}
+
+int ref_sdpa_run(void *call) {
+  SdpaCall *c = static_cast<SdpaCall *>(call);
+  Context ctx;
+  return Code(axono::ops::cpu::ScaledDotProductAttention(ctx, c->q, c->k, c->v, false, c->out));
+}
+
+void ref_sdpa_release(void *call) { delete static_cast<SdpaCall *>(call); }
+
 int ref_rope_f32(const float *x, const int64_t *pos, float theta, float *out,
                  size_t rows, size_t heads, size_t dim) {
   Context ctx;
