@@ -20,6 +20,8 @@ SIGNATURES = {
     "axb200_profile_collect": (_i, [C.POINTER(C.c_double), C.POINTER(C.c_int)]),
     "axb200_gqa_workspace_bytes": (_sz, [_i, _i, _i, _i, _i64, _i]),
     "axb200_gqa_decode": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i, _vp, _sz, _vp]),
+    "axb200_static_scratch_bytes": (_sz, []),
+    "axb200_gqa_decode_static": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i, _vp]),
     "axb200_gqa_decode_paged": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i64, _i,
                                      _vp, _sz, _vp]),
     "axb200_kv_append_rope": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i, _i, _i,

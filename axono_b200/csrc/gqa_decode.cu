@@ -917,10 +917,52 @@ int decode_impl(bool paged, const void *q, void *out, const void *k, const void 
   return status;
 }
 
+// ---- built-in scratch for callers that cannot allocate device memory -------------------------------
+// One fixed array per GPU, part of the library image: every GPU that loads the library holds these
+// bytes until the process exits.  Host code must not pass `g_static_scratch` to a kernel - in host
+// code that name is only a handle for the runtime - so the device address is looked up once per
+// device with cudaGetSymbolAddress and cached.
+constexpr size_t kStaticScratchBytes = 4u << 20;  // 4 MiB
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// Device address of the array on the current device, or null after a failed lookup.
+void *static_scratch_ptr() {
+  static std::mutex mu;
+  static void *ptrs[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!ptrs[dev]) {
+    void *ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess) {
+      cudaGetLastError();  // leave no sticky error behind
+      return nullptr;
+    }
+    ptrs[dev] = ptr;
+  }
+  return ptrs[dev];
+}
+
 }  // namespace
 }  // namespace axb
 
 extern "C" {
+
+size_t axb200_static_scratch_bytes(void) { return axb::kStaticScratchBytes; }
+
+int axb200_gqa_decode_static(const void *q, const void *k, const void *v, void *out, int hq,
+                             int hkv, int d, int64_t skv, int dtype, void *stream) {
+  if (hq <= 0 || hkv <= 0 || d <= 0 || skv <= 0) return AXB200_INVALID_ARGUMENT;
+  const axb::Plan pl = axb::make_plan(1, hq, hkv, d, skv);
+  if (pl.part_o_bytes + pl.part_ml_bytes > axb::kStaticScratchBytes) return AXB200_OUT_OF_MEMORY;
+  void *scratch = axb::static_scratch_ptr();
+  if (!scratch) return AXB200_DEVICE_ERROR;
+  // Nothing in the array has to start at zero: the combine kernel reads only the partial records
+  // that this call's split kernel has written.
+  return axb::decode_impl(false, q, out, k, v, nullptr, nullptr, (int)skv, 1, hq, hkv, d, 0, 0, 1,
+                          skv, dtype, scratch, axb::kStaticScratchBytes,
+                          static_cast<cudaStream_t>(stream));
+}
 
 const char *axb200_version(void) { return "axono_b200 0.1 (sm_100a)"; }
 

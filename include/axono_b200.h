@@ -88,6 +88,29 @@ int axb200_gqa_decode(const void *q, const void *k, const void *v, void *out,
                       int hq, int hkv, int d, int64_t skv, int dtype,
                       void *workspace, size_t workspace_bytes, void *stream);
 
+/* axb200_gqa_decode without a workspace argument, for callers that must not allocate device
+ * memory: a plugin loaded into a host whose allocator owns every byte of the GPU (as the
+ * reference's budgeted caching pool does), a serving loop where cudaMalloc's implicit device-wide
+ * synchronisation would stall the other streams, or a binding that has the C ABI but no allocator
+ * handle.  The split-K partials go into a fixed array inside the library image instead
+ * (axb200_static_scratch_bytes() = 4 MiB; each GPU that loads the library holds it until the process
+ * exits).  The caller still passes q, k, v and out; same layouts and result as axb200_gqa_decode.
+ * Limits and rules:
+ *  - returns AXB200_OUT_OF_MEMORY when axb200_gqa_workspace_bytes(1, hq, hkv, d, skv, dtype) exceeds
+ *    axb200_static_scratch_bytes() (for 16 query heads and head_dim 128 any skv fits);
+ *  - the first call on each device looks up the array's device address (cudaGetSymbolAddress) with
+ *    that device current; make that first call before any stream capture;
+ *  - it calls no cudaMalloc / cudaFree and no allocating library routine;
+ *  - all calls share the one array, which keeps the previous call's contents.  Nothing in it has
+ *    to start at zero (only records written by the same call are read back), but two calls that
+ *    overlap on the GPU - different streams, or graphs replayed concurrently - race on it: keep
+ *    calls of this entry point ordered on one stream per device.
+ * No counterpart in the reference, whose op allocates three workspace tensors per call
+ * (src/ops/cuda/gqa.cu:166-168). */
+size_t axb200_static_scratch_bytes(void);
+int axb200_gqa_decode_static(const void *q, const void *k, const void *v, void *out,
+                             int hq, int hkv, int d, int64_t skv, int dtype, void *stream);
+
 /* Batched, paged cache (extension; the reference op has no batch dimension).
  * q/out (batch,hq,d).  k_pages/v_pages: (num_pages, hkv, page_tokens, d), page_tokens a
  * multiple of 64.  block_table int32 (batch, max_blocks): page ids of each sequence in
