@@ -244,24 +244,19 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def max_over_ranks(x: float) -> float:
-        if world == 1:
-            return x
-        t = torch.tensor([x], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+    from axono_b200 import sharding
 
-    def sum_over_ranks(x: float) -> float:
-        if world == 1:
-            return x
-        t = torch.tensor([x], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.SUM)
-        return float(t.item())
+    max_over_ranks, sum_over_ranks = sharding.max_over_ranks, sharding.sum_over_ranks
 
     lib = _capi.lib()
     w = WORKLOADS[args.workload]
-    B = w["batch"]
-    lens = seq_lengths(args.workload, rank)
+    if args.scaling == "strong":
+        # one global batch, sequences assigned to ranks by KV bytes (longest first)
+        all_lens = seq_lengths(args.workload, 0)
+        lens = all_lens[sharding.shard_sequences(all_lens.tolist(), world)[rank]]
+    else:
+        lens = seq_lengths(args.workload, rank)
+    B = len(lens)
     total_steps = args.warmup + args.steps
     capacity = int(w["hi"]) + 2 * total_steps + 64
     gen = torch.Generator(device=device).manual_seed(1234 + rank)
@@ -312,7 +307,8 @@ def run_ours(args):
     my_bytes = bytes_of_steps(args.warmup, args.steps)
     all_bytes = sum_over_ranks(my_bytes)
     value = all_bytes / (dev_ms / 1e3) / 1e9
-    tokens_per_s = B * world * args.steps / (dev_ms / 1e3)
+    total_seqs = sum_over_ranks(B)
+    tokens_per_s = total_seqs * args.steps / (dev_ms / 1e3)
     err = ops.last_error()
     if err:
         raise SystemExit(f"device error word {err:#x} after the timed steps")
@@ -366,7 +362,7 @@ def run_ours(args):
     e2e_s = max_over_ranks(time.perf_counter() - t0)
     e2e_bytes = sum_over_ranks(sum(algo_bytes(lens + base + s + 1) for s in range(args.steps)))
     e2e = {"value": e2e_bytes / e2e_s / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-           "ms_per_step": e2e_s / args.steps * 1e3, "tokens_per_s": B * world * args.steps / e2e_s}
+           "ms_per_step": e2e_s / args.steps * 1e3, "tokens_per_s": total_seqs * args.steps / e2e_s}
 
     clocks = sampler.summary()
 
@@ -398,8 +394,9 @@ def run_ours(args):
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": args.workload, "batch_per_gpu": B, "hq": HQ, "hkv": HKV, "head_dim": D,
+            "scaling": args.scaling, "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": args.workload, "batch_per_gpu": w["batch"] if args.scaling == "weak" else None,
+                       "global_batch": int(total_seqs), "hq": HQ, "hkv": HKV, "head_dim": D,
                        "kv_len": [int(w["lo"]), int(w["hi"])], "page_tokens": PAGE_TOKENS,
                        "sharding": f"batch x{world}, no collective on the attention path",
                        "l2": "inputs larger than L2 (several GB of KV per step)",
@@ -421,6 +418,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c3_ragged", choices=sorted(WORKLOADS))
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="weak: every GPU gets its own batch; strong: one batch sharded over the GPUs")
     ap.add_argument("--cpu-budget", type=float, default=10.0, help="seconds of CPU work for cpu_baseline")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-extra", action="store_true")
