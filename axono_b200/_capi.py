@@ -25,7 +25,7 @@ SIGNATURES = {
     "axb200_gqa_decode_paged": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i64, _i,
                                      _vp, _sz, _vp]),
     "axb200_kv_append_rope": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i, _i, _i,
-                                   _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp]),
+                                   _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "axb200_rope": (_i, [_vp, _vp, _f, _vp, _i64, _i, _i, _i, _vp]),
     "axb200_rope_thd": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _i64, _i, _i, _i, _vp]),
     "axb200_rope_with_cos_sin": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i, _i, _vp]),

@@ -118,20 +118,23 @@ struct AppendParams {
   int rotate, mrope, h_lim, w_lim;
   int batch, hq, hkv, d;
   int page_tokens, max_blocks, num_pages;
+  int slot_delta;  // the token goes to slot seq_lens[b] + slot_delta (0, or -1 once a layer advanced)
   int advance;
 };
 
 // One CTA per sequence: rotates q in place, rotates k and copies v into slot seq_lens[b] of the
 // sequence's pages (page layout (hkv, page_tokens, d)), then - as the CTA's last act - bumps
-// seq_lens[b].  The slot index is read before any thread of the CTA can have bumped it.
+// seq_lens[b].  The slot index is read before any thread of the CTA can have bumped it.  In a
+// multi-layer step the first layer appends with slot_delta 0 and advances, so that every layer's
+// attention sees the new token; the later layers append with slot_delta -1 and do not advance.
 template <typename T>
 __global__ void __launch_bounds__(256)
 kv_append_rope_kernel(const AppendParams p, const InvFreqTable table) {
   __shared__ int s_len;
   const int b = blockIdx.x;
-  if (threadIdx.x == 0) s_len = p.seq_lens[b];
+  if (threadIdx.x == 0) s_len = p.seq_lens[b] + p.slot_delta;
   __syncthreads();
-  const int len = s_len;
+  const int len = s_len;  // slot of the new token = number of tokens cached before it
   const int half = p.d / 2;
 
   float pt, ph, pw;
@@ -199,7 +202,7 @@ kv_append_rope_kernel(const AppendParams p, const InvFreqTable table) {
   }
   if (p.advance && page_ok) {
     __syncthreads();
-    if (threadIdx.x == 0) p.seq_lens[b] = len + 1;
+    if (threadIdx.x == 0) p.seq_lens[b] = len - p.slot_delta + 1;
   }
 }
 
@@ -298,14 +301,14 @@ int axb200_kv_append_rope(void *q, const void *k_new, const void *v_new, void *k
                           void *v_pages, const int32_t *block_table, int32_t *seq_lens,
                           const int64_t *pos, const float *inv_freq, float theta, int rotate,
                           int mrope, int h_sec, int w_sec, int batch, int hq, int hkv, int d,
-                          int page_tokens, int max_blocks, int num_pages, int dtype, int advance,
-                          void *stream) {
+                          int page_tokens, int max_blocks, int num_pages, int dtype, int slot_delta,
+                          int advance, void *stream) {
   if (dtype != AXB200_FLOAT32 && dtype != AXB200_FLOAT16) return AXB200_UNSUPPORTED_TYPE;
   if (!k_new || !v_new || !k_pages || !v_pages || !block_table || !seq_lens)
     return AXB200_INVALID_PTR;
   if (rotate && !q && hq > 0) return AXB200_INVALID_PTR;
   if (batch <= 0 || hq < 0 || hkv <= 0 || d <= 0 || d % 2 != 0 || d / 2 > axb::kMaxHalf ||
-      page_tokens <= 0 || max_blocks <= 0 || num_pages <= 0)
+      page_tokens <= 0 || max_blocks <= 0 || num_pages <= 0 || slot_delta > 0 || slot_delta < -1)
     return AXB200_INVALID_ARGUMENT;
   if (rotate && mrope && !inv_freq) return AXB200_INVALID_PTR;
   axb::AppendParams p{};
@@ -329,6 +332,7 @@ int axb200_kv_append_rope(void *q, const void *k_new, const void *v_new, void *k
   p.page_tokens = page_tokens;
   p.max_blocks = max_blocks;
   p.num_pages = num_pages;
+  p.slot_delta = slot_delta;
   p.advance = advance;
   axb::InvFreqTable table{};
   if (rotate && !inv_freq) axb::fill_table(&table, theta, d);

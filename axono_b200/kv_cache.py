@@ -33,8 +33,9 @@ class PagedKVCache(KVCache):
     """Per-layer page pools (num_pages, n_kv_heads, page_tokens, head_dim) shared by `batch`
     sequences, one block table and one device-resident length vector per cache.
 
-    All layers share the block table; `seq_lens` advances once per decode step (on the last
-    layer's append, or by `advance()`), so every layer of a step writes the same slot.
+    All layers share the block table and `seq_lens`, which advances once per decode step: layer 0's
+    append writes slot `len` and advances, so that every layer's attention sees the new token; the
+    other layers write slot `len - 1` and leave the lengths alone.
     """
 
     def __init__(self, n_layers, batch, n_kv_heads, head_dim, max_seq_len, dtype=torch.float16,
@@ -61,20 +62,22 @@ class PagedKVCache(KVCache):
     # -- reference interface ------------------------------------------------------------------
     def update(self, layer_idx: int, k_new, v_new):
         """Appends one token per sequence: k_new/v_new (batch, n_kv_heads, head_dim), no rotation."""
-        last = layer_idx == self.n_layers - 1
+        first = layer_idx == 0
         ops.kv_append_rope(None, k_new, v_new, self.k_pages[layer_idx], self.v_pages[layer_idx],
-                           self.block_table, self.seq_lens, rotate=False, advance=last)
-        if last:
+                           self.block_table, self.seq_lens, rotate=False, advance=first,
+                           slot_delta=0 if first else -1)
+        if first:
             self._host_len_bound += 1
 
     def append_rope(self, layer_idx: int, q, k_new, v_new, pos=None, inv_freq=None, theta=10000.0,
                     mrope_section=None):
         """rope(q) in place + rope(k_new) + append of (k_new, v_new) in one launch."""
-        last = layer_idx == self.n_layers - 1
+        first = layer_idx == 0
         ops.kv_append_rope(q, k_new, v_new, self.k_pages[layer_idx], self.v_pages[layer_idx],
                            self.block_table, self.seq_lens, pos=pos, inv_freq=inv_freq, theta=theta,
-                           mrope_section=mrope_section, rotate=True, advance=last)
-        if last:
+                           mrope_section=mrope_section, rotate=True, advance=first,
+                           slot_delta=0 if first else -1)
+        if first:
             self._host_len_bound += 1
         return q
 
@@ -83,12 +86,20 @@ class PagedKVCache(KVCache):
         reference's (k_full, v_full)."""
         return self.k_pages[layer_idx], self.v_pages[layer_idx], self.block_table, self.seq_lens
 
-    def attend(self, layer_idx: int, q, out=None, extra_tokens: int = 0):
-        """Decode attention of q (batch, hq, d) over the layer's cache.  `extra_tokens` widens the
-        host-side length bound for layers that have appended this step before seq_lens advanced."""
-        bound = min(self.max_seq_len, self._host_len_bound + extra_tokens)
+    def attend(self, layer_idx: int, q, out=None):
+        """Decode attention of q (batch, hq, d) over the layer's cache.  The grid is sized from a
+        host-side upper bound of the lengths; while a CUDA graph is being captured that bound is the
+        capacity, so replays stay correct as the cache grows."""
+        bound = self._host_len_bound
+        if torch.cuda.is_current_stream_capturing():
+            bound = self.max_seq_len
+        bound = min(self.max_seq_len, bound)
         return ops.gqa_decode_attention_paged(q, self.k_pages[layer_idx], self.v_pages[layer_idx],
                                               self.block_table, self.seq_lens, max(bound, 1), out=out)
+
+    def note_replayed(self, steps: int = 1):
+        """Tells the host-side bound that `steps` captured decode steps have been replayed."""
+        self._host_len_bound = min(self.max_seq_len, self._host_len_bound + steps)
 
     def reset(self):
         self.seq_lens.zero_()

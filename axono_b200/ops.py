@@ -23,6 +23,17 @@ from . import _capi
 
 _DTYPES = {torch.float16: _capi.FLOAT16, torch.float32: _capi.FLOAT32}
 _workspaces: dict = {}
+_launches = 0  # operator calls that reached the C ABI (used to tell an empty graph capture)
+
+
+def launch_count() -> int:
+    return _launches
+
+
+def _call(status: int, op: str) -> None:
+    global _launches
+    _capi.check(status, op)
+    _launches += 1
 
 
 def _dt(t: torch.Tensor, op: str) -> int:
@@ -87,7 +98,7 @@ def gqa_decode_attention(q, k, v):
     lib = _capi.lib()
     ws_bytes = lib.axb200_gqa_workspace_bytes(1, hq, hkv, d, skv, dt)
     ws = workspace(q.device, ws_bytes)
-    _capi.check(lib.axb200_gqa_decode(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), hq, hkv, d,
+    _call(lib.axb200_gqa_decode(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), hq, hkv, d,
                                       skv, dt, ws.data_ptr(), ws.numel(), _stream(q)), op)
     return out
 
@@ -110,7 +121,7 @@ def gqa_decode_attention_paged(q, k_pages, v_pages, block_table, seq_lens, max_s
     lib = _capi.lib()
     ws_bytes = lib.axb200_gqa_workspace_bytes(batch, hq, hkv, d, int(max_seq_len), dt)
     ws = workspace(q.device, ws_bytes)
-    _capi.check(lib.axb200_gqa_decode_paged(
+    _call(lib.axb200_gqa_decode_paged(
         q.data_ptr(), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
         seq_lens.data_ptr(), batch, hq, hkv, d, page_tokens, block_table.shape[1], num_pages,
         int(max_seq_len), dt, ws.data_ptr(), ws.numel(), _stream(q)), op)
@@ -118,9 +129,10 @@ def gqa_decode_attention_paged(q, k_pages, v_pages, block_table, seq_lens, max_s
 
 
 def kv_append_rope(q, k_new, v_new, k_pages, v_pages, block_table, seq_lens, pos=None, inv_freq=None,
-                   theta=10000.0, mrope_section=None, rotate=True, advance=True):
+                   theta=10000.0, mrope_section=None, rotate=True, advance=True, slot_delta=0):
     """One decode step's rope(q), rope(k) and cache append in one launch.  q (batch,hq,d) is rotated
-    in place; k_new/v_new (batch,hkv,d) land in slot seq_lens[b]; seq_lens advances when asked.
+    in place; k_new/v_new (batch,hkv,d) land in slot seq_lens[b] + slot_delta; seq_lens advances when
+    asked (first layer of a step: slot_delta 0, advance; later layers: slot_delta -1, no advance).
     pos: int64 (batch), or (3,batch) with mrope_section=(t,h,w); None = the cache length."""
     op = "kv_append_rope"
     dt = _dt(k_new, op)
@@ -132,11 +144,11 @@ def kv_append_rope(q, k_new, v_new, k_pages, v_pages, block_table, seq_lens, pos
     for t in (q, k_new, v_new):
         if t is not None and not t.is_contiguous():
             raise RuntimeError(f"{op}: tensors must be contiguous (q is updated in place)")
-    _capi.check(_capi.lib().axb200_kv_append_rope(
+    _call(_capi.lib().axb200_kv_append_rope(
         _ptr(q), k_new.data_ptr(), v_new.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(),
         block_table.data_ptr(), seq_lens.data_ptr(), _ptr(pos), _ptr(inv_freq), float(theta),
         int(rotate), int(mrope), h_sec, w_sec, batch, hq, hkv, d, page_tokens, block_table.shape[1],
-        num_pages, dt, int(advance), _stream(k_new)), op)
+        num_pages, dt, int(slot_delta), int(advance), _stream(k_new)), op)
     return q
 
 
@@ -150,7 +162,7 @@ def rope(x, pos_ids, theta: float = 10000.0):
         _capi.check(3, op)
     x = _c(x)
     out = torch.empty_like(x)
-    _capi.check(_capi.lib().axb200_rope(x.data_ptr(), _c(pos_ids).data_ptr(), float(theta), out.data_ptr(),
+    _call(_capi.lib().axb200_rope(x.data_ptr(), _c(pos_ids).data_ptr(), float(theta), out.data_ptr(),
                                         rows, heads, dim, dt, _stream(x)), op)
     return out
 
@@ -168,7 +180,7 @@ def rope_thd(x, pos, inv_freq, mrope_section):
     x = _c(x)
     out = torch.empty_like(x)
     t, h, w = mrope_section
-    _capi.check(_capi.lib().axb200_rope_thd(x.data_ptr(), _c(pos).data_ptr(), _c(inv_freq).data_ptr(), t, h, w,
+    _call(_capi.lib().axb200_rope_thd(x.data_ptr(), _c(pos).data_ptr(), _c(inv_freq).data_ptr(), t, h, w,
                                             out.data_ptr(), rows, heads, dim, dt, _stream(x)), op)
     return out
 
@@ -181,7 +193,7 @@ def rope_with_cos_sin(x, cos, sin):
         _capi.check(4, op)
     x = _c(x)
     out = torch.empty_like(x)
-    _capi.check(_capi.lib().axb200_rope_with_cos_sin(x.data_ptr(), _c(cos).data_ptr(), _c(sin).data_ptr(),
+    _call(_capi.lib().axb200_rope_with_cos_sin(x.data_ptr(), _c(cos).data_ptr(), _c(sin).data_ptr(),
                                                      out.data_ptr(), rows, heads, dim, dt, _stream(x)), op)
     return out
 
@@ -193,7 +205,7 @@ def mrope_cos_sin(pos, inv_freq, h_sec: int, w_sec: int):
     rows, half = pos.shape[1], inv_freq.shape[0]
     cos = torch.empty((rows, 2 * half), dtype=torch.float32, device=pos.device)
     sin = torch.empty_like(cos)
-    _capi.check(_capi.lib().axb200_mrope_cos_sin(_c(pos).data_ptr(), _c(inv_freq).data_ptr(), h_sec, w_sec,
+    _call(_capi.lib().axb200_mrope_cos_sin(_c(pos).data_ptr(), _c(inv_freq).data_ptr(), h_sec, w_sec,
                                                  cos.data_ptr(), sin.data_ptr(), rows, half, _stream(pos)), op)
     return cos, sin
 
@@ -210,7 +222,7 @@ def add_rms_norm(x, residual, weight, eps: float = 1e-6):
     x, residual, weight = _c(x), _c(residual), _c(weight)
     y = torch.empty_like(x)
     out = torch.empty_like(x)
-    _capi.check(_capi.lib().axb200_add_rms_norm(x.data_ptr(), residual.data_ptr(), weight.data_ptr(), float(eps),
+    _call(_capi.lib().axb200_add_rms_norm(x.data_ptr(), residual.data_ptr(), weight.data_ptr(), float(eps),
                                                 y.data_ptr(), out.data_ptr(), x.numel() // hidden, hidden, dt,
                                                 _stream(x)), op)
     return y, out
@@ -223,7 +235,7 @@ def silu_mul(gate, up):
         _capi.check(4, op)
     gate, up = _c(gate), _c(up)
     out = torch.empty_like(gate)
-    _capi.check(_capi.lib().axb200_silu_mul(gate.data_ptr(), up.data_ptr(), out.data_ptr(), gate.numel(), dt,
+    _call(_capi.lib().axb200_silu_mul(gate.data_ptr(), up.data_ptr(), out.data_ptr(), gate.numel(), dt,
                                             _stream(gate)), op)
     return out
 
@@ -237,7 +249,7 @@ def rms_norm(x, weight, eps: float = 1e-5):
         _capi.check(4, op)
     x = _c(x)
     out = torch.empty_like(x)
-    _capi.check(_capi.lib().axb200_rms_norm(x.data_ptr(), _c(weight).data_ptr() if has_w else None, float(eps),
+    _call(_capi.lib().axb200_rms_norm(x.data_ptr(), _c(weight).data_ptr() if has_w else None, float(eps),
                                             out.data_ptr(), x.numel() // cols, cols, dt, _stream(x)), op)
     return out
 
@@ -263,6 +275,6 @@ def concat(a, b, axis: int):
     es = a.element_size()
     a_bytes = (a.numel() // max(outer, 1)) * es
     b_bytes = (b.numel() // max(outer, 1)) * es
-    _capi.check(_capi.lib().axb200_concat(a.data_ptr(), b.data_ptr(), out.data_ptr(), outer, a_bytes, b_bytes,
+    _call(_capi.lib().axb200_concat(a.data_ptr(), b.data_ptr(), out.data_ptr(), outer, a_bytes, b_bytes,
                                           _stream(a)), op)
     return out

@@ -131,12 +131,14 @@ int axb200_gqa_decode_paged(const void *q, void *out, const void *k_pages, const
  *   cache.update -> concat(old, new, axis 0) (axono/python/axono/nn/kv_cache.py:96-102,
  *                                             src/ops/cuda/sequence.cu:474-521)
  * by one launch: q (batch,hq,d) is rotated in place, k_new (batch,hkv,d) is rotated and
- * written, v_new copied, into slot seq_lens[b] of sequence b's pages; when `advance` is
- * non-zero seq_lens[b] is then incremented.  Rotation: rotate-half pairs (i, i+d/2).
+ * written, v_new copied, into slot seq_lens[b] + slot_delta of sequence b's pages; when `advance`
+ * is non-zero seq_lens[b] is then incremented.  All layers of a model share seq_lens: the first
+ * layer of a step appends with slot_delta 0 and advance 1 (so every layer's attention sees the new
+ * token), the other layers with slot_delta -1 and advance 0.  Rotation: rotate-half pairs (i, i+d/2).
  *   mrope == 0: angle_i = float(pos[b]) * inv_freq[i];   pos int64 (batch)
  *   mrope != 0: pos int64 (3,batch) rows T,H,W; pair i uses H when i%3==1 && i<3*h_sec,
  *               W when i%3==2 && i<3*w_sec, else T (src/ops/cpu/sequence.cpp:222-227).
- * pos == NULL: the position is the cache length seq_lens[b] on every axis.
+ * pos == NULL: the position is the slot index (the cache length before the append) on every axis.
  * inv_freq: device float (d/2), or NULL to use theta^(-2i/d) computed on the host with the
  * C library's powf, exactly as the reference's CPU Rope does (src/ops/cpu/sequence.cpp:83-84).
  * rotate == 0 skips the rotation (plain append).
@@ -148,7 +150,7 @@ int axb200_kv_append_rope(void *q, const void *k_new, const void *v_new,
                           int rotate, int mrope, int h_sec, int w_sec,
                           int batch, int hq, int hkv, int d,
                           int page_tokens, int max_blocks, int num_pages,
-                          int dtype, int advance, void *stream);
+                          int dtype, int slot_delta, int advance, void *stream);
 
 /* ---- RoPE family (stand-alone ops) --------------------------------------------------------
  * x/out (rows,heads,dim); out may alias x. */
