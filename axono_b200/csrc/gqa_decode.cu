@@ -724,17 +724,28 @@ bool make_map(CUtensorMap *map, const void *base, int dtype, bool paged, int d, 
   return r == CUDA_SUCCESS;
 }
 
-// Chunk length (tokens) from the context length and the SM count: enough CTAs to fill every SM
-// several times over, each long enough to amortise its pipeline fill, and at most kMaxChunks
-// per sequence.  Always a multiple of 64 tokens.
+// Chunk length (tokens) from the context length and the SM count.  `slots` CTAs are resident at
+// once (2 per SM).  A large problem is cut so that about 8 waves of CTAs, each 16..64 tiles long,
+// cover it: long enough to amortise a CTA's pipeline fill, many enough for the hardware scheduler
+// to balance ragged lengths.  A small problem (less than that) is cut into at most one wave, so
+// each CTA streams as long a run as possible.  At most kMaxChunks chunks per sequence; always a
+// multiple of 64 tokens.
 int pick_chunk_tokens(int batch, int hkv, int64_t max_len) {
   const int64_t tiles = (max_len + 63) / 64;
-  const int64_t target_ctas = (int64_t)sm_count() * 2 * 8;
-  int64_t per_seq = target_ctas / ((int64_t)batch * hkv);  // chunks wanted per (sequence, head)
-  if (per_seq < 1) per_seq = 1;
-  int64_t chunk_tiles = (tiles + per_seq - 1) / per_seq;
-  if (chunk_tiles < 4) chunk_tiles = 4;    // >= 256 tokens per CTA
-  if (chunk_tiles > 64) chunk_tiles = 64;  // <= 4096 tokens per CTA
+  const int64_t slots = (int64_t)sm_count() * 2;
+  const int64_t items = (int64_t)batch * hkv;
+  const int64_t total = items * tiles;
+  int64_t chunk_tiles;
+  if (total >= 16 * 8 * slots) {
+    chunk_tiles = (total + 8 * slots - 1) / (8 * slots);
+    if (chunk_tiles < 16) chunk_tiles = 16;
+    if (chunk_tiles > 64) chunk_tiles = 64;
+  } else {
+    int64_t per_item = slots / items;  // chunks each (sequence, head) may have within one wave
+    if (per_item < 1) per_item = 1;
+    chunk_tiles = (tiles + per_item - 1) / per_item;
+    if (chunk_tiles < 4) chunk_tiles = 4;
+  }
   while ((tiles + chunk_tiles - 1) / chunk_tiles > kMaxChunks) chunk_tiles *= 2;
   return (int)(chunk_tiles * 64);
 }

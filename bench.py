@@ -134,6 +134,17 @@ class ClockSampler:
 
 
 # ---- CPU reference arm ---------------------------------------------------------------------------
+def use_all_host_threads() -> int:
+    """The CPU legs use every host core this process may run on, also under torchrun, which exports
+    OMP_NUM_THREADS=1 for its children."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    try:
+        ctypes.CDLL("libgomp.so.1").omp_set_num_threads(int(n))
+    except OSError:
+        pass
+    return int(n)
+
+
 def cpu_attention_sample(workload: str, budget_s: float, max_seqs: int):
     """Times the reference's CPU SDPA-GQA (fp32, the only type it supports) on the first sequences
     of rank 0's batch, one call per sequence as the reference evaluates a batch, until the time
@@ -141,6 +152,7 @@ def cpu_attention_sample(workload: str, budget_s: float, max_seqs: int):
     import oracle
 
     orc = oracle.best()
+    threads = use_all_host_threads()
     lens = seq_lengths(workload, 0)
     rng = np.random.default_rng(4000)
     done_bytes, done_seqs, spent, reps = 0.0, 0, 0.0, 4
@@ -163,8 +175,6 @@ def cpu_attention_sample(workload: str, budget_s: float, max_seqs: int):
         done_seqs += 1
         if spent >= budget_s:
             break
-    cores = os.cpu_count() or 1
-    threads = int(os.environ.get("OMP_NUM_THREADS", cores))
     info = {"kind": orc.kind, "cores": threads,
             "sample": f"{done_seqs} sequences of workload {workload} (lengths {int(lens[:done_seqs].min())}.."
                       f"{int(lens[:done_seqs].max())}), one fp32 SDPA call per sequence on exactly-widened inputs; "
@@ -181,6 +191,7 @@ def run_reference_arm(args):
     import oracle
 
     orc = oracle.best()
+    cores = use_all_host_threads()
     lens = seq_lengths(args.workload, 0)
     per_step = 2
     rng = np.random.default_rng(4000)
@@ -202,7 +213,6 @@ def run_reference_arm(args):
     for _, _, release in calls:
         release()
     value = step_bytes * args.steps / dt / 1e9
-    cores = int(os.environ.get("OMP_NUM_THREADS", os.cpu_count() or 1))
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
@@ -411,13 +421,133 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# ---- the callers of the path: fused decode block and text-tower step under CUDA-graph replay ----------
+def run_tower(args):
+    """`c5_tower`: full 28-layer text-tower decode step (hidden 2048, intermediate 6144, 16 q / 8 KV
+    heads, head_dim 128, vocab 151936, random fp16 weights), batch 32, context 16384, one CUDA graph per
+    step; KV heads sharded over the GPUs with an all-gather of attention outputs per layer.
+    `c2_block`: the fused decode block (add_rms_norm -> RoPE -> append -> attention -> silu_mul) at batch 8,
+    KV length 8192, one CUDA graph.  Reports decode tokens/s and the KV-cache GB/s inside the step."""
+    import torch
+    import torch.distributed as dist
+
+    from axono_b200 import ops, sharding
+    from axono_b200.cuda_graph import CUDAGraph
+    from axono_b200.decode import TextTower, TextTowerConfig, decode_block
+    from axono_b200.kv_cache import PagedKVCache
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def fill_random(pool, gen):
+        for p0 in range(0, pool.shape[0], 512):
+            n = min(512, pool.shape[0] - p0)
+            pool[p0 : p0 + n] = (0.5 * torch.randn((n,) + tuple(pool.shape[1:]), generator=gen, device=device)).half()
+
+    gen = torch.Generator(device=device).manual_seed(77 + rank)
+    total_steps = args.warmup + args.steps + 2
+    if args.workload == "c5_tower":
+        B, L = 32, 16384
+        cfg = TextTowerConfig()
+        tower = TextTower(cfg, B, L + total_steps + 64, device=device, world=world, rank=rank, seed=5)
+        for li in range(cfg.n_layers):
+            fill_random(tower.cache.k_pages[li], gen)
+            fill_random(tower.cache.v_pages[li], gen)
+        lens = [L] * B
+        tower.set_state(np.arange(B) % cfg.vocab, lens)
+        ops.workspace(device, ops.gqa_workspace_bytes(B, tower.local_q, tower.local_kv, cfg.head_dim, tower.cache.max_seq_len))
+        body = tower.decode_step
+        cache = tower.cache
+        kv_bytes = tower.kv_bytes_per_step(lens)
+        launches_note = "28 x (rms/add_rms_norm x2, rms_norm x2, kv_append_rope, split, combine, silu_mul) + library GEMMs"
+        other_bytes = tower.weight_bytes()
+    else:
+        B, L = 8, 8192
+        cache = PagedKVCache(1, B, HKV, D, L + total_steps + 64, dtype=torch.float16, device=device)
+        fill_random(cache.k_pages[0], gen)
+        fill_random(cache.v_pages[0], gen)
+        lens = [L] * B
+        cache.seq_lens.fill_(L)
+        cache._host_len_bound = L
+        rn = lambda *s: torch.randn(s, generator=gen, device=device).half()  # noqa: E731
+        x, res, w = rn(B, 2048), rn(B, 2048), (1 + 0.02 * torch.randn(2048, generator=gen, device=device)).half()
+        q0, kn, vn, gate, up = rn(B, HQ, D), rn(B, HKV, D), rn(B, HKV, D), rn(B, 6144), rn(B, 6144)
+        ops.workspace(device, ops.gqa_workspace_bytes(B, HQ, HKV, D, cache.max_seq_len))
+
+        def body():
+            return decode_block(x, res, w, q0.clone(), kn, vn, cache, 0, gate, up, theta=1e6)
+
+        kv_bytes = algo_bytes(np.asarray(lens) + 1)
+        launches_note = "add_rms_norm, q copy, kv_append_rope, split, combine, silu_mul"
+        other_bytes = 0.0
+
+    g = CUDAGraph().capture(body)
+    cache.note_replayed()
+    for _ in range(args.warmup):
+        g.replay_async()
+    sampler = ClockSampler(local_rank)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    sampler.start()
+    ev0.record()
+    for _ in range(args.steps):
+        g.replay_async()
+    ev1.record()
+    barrier()
+    sampler.pause()
+    ms = sharding.max_over_ranks(ev0.elapsed_time(ev1))
+    err = ops.last_error()
+    if err:
+        raise SystemExit(f"device error word {err:#x}")
+    # e2e: the host reads the step's result (next tokens / attention output) after every replay
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        g.replay()
+        _ = g.output.cpu()
+    barrier()
+    e2e_s = sharding.max_over_ranks(time.perf_counter() - t0)
+    all_kv = sharding.sum_over_ranks(kv_bytes)
+    if rank == 0:
+        step_ms = ms / args.steps
+        peak, kind = measured_peak()
+        line = {
+            "metric": "decode_tokens_per_s", "value": B * args.steps / (ms / 1e3), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": args.workload, "batch": B, "kv_len": L, "cuda_graph": True, "graph_nodes": g.num_nodes,
+                       "sharding": f"KV heads x{world}" + (", all-gather of attention outputs per layer" if world > 1 else ""),
+                       "kernels": launches_note, "l2": "KV per step larger than L2"},
+            "kv_cache_gbs": all_kv / (step_ms / 1e3) / 1e9,
+            "kv_frac_of_measured_peak": all_kv / (step_ms / 1e3) / 1e9 / (peak * world),
+            "hbm_bytes_per_step": {"kv": all_kv, "weights_per_gpu": other_bytes},
+            "hbm_floor_ms": (kv_bytes + other_bytes) / (peak * 1e9) * 1e3,
+            "e2e": {"value": B * args.steps / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": 0,
+                    "d2h_bytes_per_step": int(g.output.numel() * g.output.element_size()), "ms_per_step": e2e_s / args.steps * 1e3},
+            "gpu_launches": g.num_nodes * args.steps, "clocks": sampler.summary(),
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c3_ragged", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c3_ragged", choices=sorted(WORKLOADS) + ["c2_block", "c5_tower"])
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="weak: every GPU gets its own batch; strong: one batch sharded over the GPUs")
     ap.add_argument("--cpu-budget", type=float, default=10.0, help="seconds of CPU work for cpu_baseline")
@@ -425,7 +555,11 @@ def main():
     ap.add_argument("--no-extra", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
+        if args.workload in ("c2_block", "c5_tower"):
+            args.workload = "c2_b8_l8k" if args.workload == "c2_block" else "c3_ragged"
         run_reference_arm(args)
+    elif args.workload in ("c2_block", "c5_tower"):
+        run_tower(args)
     else:
         run_ours(args)
 

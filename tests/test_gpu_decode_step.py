@@ -97,8 +97,14 @@ def test_decode_block_eager_matches_oracle_and_graph_replays():
         gcache.note_replayed()
         e = body(ecache)
         torch.cuda.synchronize()
-        for a, b_ in zip(g.outputs, e):
-            assert torch.equal(a, b_), f"replay {step} differs from eager"
+        # y, xn and act are bit-identical; the attention output is computed with the chunk plan of the
+        # cache's capacity under capture and of its current length in eager mode, so the two differ
+        # by fp32 summation order before the fp16 rounding
+        for idx, (a, b_) in enumerate(zip(g.outputs, e)):
+            if idx == 2:
+                assert oracle.rel_err(host(a), host(b_)) <= 1e-3, f"replay {step}: attention differs from eager"
+            else:
+                assert torch.equal(a, b_), f"replay {step}: output {idx} differs from eager"
     assert gcache.seq_lens.cpu().tolist() == [n + 4 for n in lens]
     kb, vb = gcache.gather(0, 2)
     ke, ve = ecache.gather(0, 2)
