@@ -24,6 +24,12 @@ SIGNATURES = {
     "axb200_gqa_decode_static": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i, _vp]),
     "axb200_gqa_decode_paged": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i64, _i,
                                      _vp, _sz, _vp]),
+    "axb200_gqa_decode_paged_gather": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i64, _i, _vp, _sz,
+                                            _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "axb200_p2p_alloc": (_i, [_sz, C.POINTER(_vp), _vp]),
+    "axb200_p2p_open": (_i, [_vp, C.POINTER(_vp)]),
+    "axb200_p2p_close": (_i, [_vp]),
+    "axb200_p2p_free": (_i, [_vp]),
     "axb200_kv_append_rope": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i, _i, _i,
                                    _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "axb200_rope": (_i, [_vp, _vp, _f, _vp, _i64, _i, _i, _i, _vp]),

@@ -15,6 +15,7 @@
 // reference's layout, one sequence - or paged (num_pages,hkv,page_tokens,d) with a block
 // table, where one (page, head) tile is a contiguous run in HBM.
 #include <math.h>
+#include <string.h>
 
 #include <mutex>
 #include <set>
@@ -660,6 +661,89 @@ gqa_combine_kernel(const DecodeParams p, int d, float dom) {
   }
 }
 
+// ---- combine fused with the all-gather of per-head outputs (KV heads sharded across GPUs) ----------
+// Each rank attends its own heads; before the output projection every rank needs all heads.  This
+// kernel is the combine kernel with its store redirected: the merged row of (sequence b, local head
+// h) is written straight into every rank's gathered buffer (batch, hq_total, d) at head
+// rank*hq + h, over NVLink with plain stores to peer-mapped pointers.  The last CTA to finish then
+// publishes this rank's generation number in every peer's flag array and waits (bounded) until all
+// peers have published theirs, so when the kernel completes the local gathered buffer is whole
+// and the next kernel in the stream may read it.  Only local memory is ever read.
+constexpr int kMaxPeers = 8;
+struct GatherParams {
+  void *peer_out[kMaxPeers];           // each rank's gathered buffer for this call's slot
+  unsigned int *peer_flags[kMaxPeers]; // each rank's flag array [world]; entry r = rank r's generation
+  unsigned int *local_state;           // [0] CTAs finished in this call, [1] this rank's generation
+  int world, rank, hq_total;
+};
+
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int *p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned int *p, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(128)
+gqa_combine_gather_kernel(const DecodeParams p, const GatherParams g, int d, float dom) {
+  __shared__ int s_last;
+  __shared__ unsigned int s_gen;
+  const int h = blockIdx.x, b = blockIdx.y;
+  const int L = seq_len_of(p, b);
+  int n = (L + p.chunk_tokens - 1) / p.chunk_tokens;
+  n = max(0, min(n, p.max_chunks));
+  const size_t base = ((size_t)b * p.hq + h) * p.max_chunks;
+  const size_t row = ((size_t)b * g.hq_total + (size_t)g.rank * p.hq + h) * d;
+  float M = -INFINITY, inv = 0.f;
+  if (n > 0) {
+    for (int c = 0; c < n; ++c) M = fmaxf(M, p.part_ml[(base + c) * 2]);
+    float Lsum = 0.f;
+    for (int c = 0; c < n; ++c)
+      Lsum += p.part_ml[(base + c) * 2 + 1] * exp2f((p.part_ml[(base + c) * 2] - M) * dom);
+    inv = 1.0f / Lsum;
+  }
+  for (int c0 = threadIdx.x; c0 < d; c0 += blockDim.x) {
+    float acc = 0.f;
+    for (int c = 0; c < n; ++c) {
+      const float w = exp2f((p.part_ml[(base + c) * 2] - M) * dom);
+      acc = fmaf(w, p.part_o[(base + c) * d + c0], acc);
+    }
+    const OutT val = static_cast<OutT>(acc * inv);
+    for (int r = 0; r < g.world; ++r) reinterpret_cast<OutT *>(g.peer_out[r])[row + c0] = val;
+  }
+  // last-CTA-done: every thread fences its stores system-wide before its CTA counts itself in
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int total = gridDim.x * gridDim.y;
+    s_last = atomicAdd(&g.local_state[0], 1u) == total - 1;
+    if (s_last) {
+      __threadfence_system();
+      s_gen = g.local_state[1] + 1;  // only the last CTA of a call touches the generation
+      g.local_state[0] = 0;
+      g.local_state[1] = s_gen;
+    }
+  }
+  __syncthreads();
+  if (!s_last) return;
+  const unsigned int gen = s_gen;
+  if (threadIdx.x < g.world) {
+    st_release_sys(g.peer_flags[threadIdx.x] + g.rank, gen);
+    const unsigned int *flag = g.peer_flags[g.rank] + threadIdx.x;
+    const unsigned long long t0 = global_timer_ns();
+    // generations only grow; the signed difference keeps the comparison right across wrap-around
+    while ((int)(ld_acquire_sys(flag) - gen) < 0) {
+      if (global_timer_ns() - t0 > kWaitNanos) {
+        atomicOr(&g_error_word, AXB200_ERR_WAIT_TIMEOUT);
+        break;
+      }
+    }
+  }
+}
+
 // ---- host side ----------------------------------------------------------------------------------
 using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
                                    const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
@@ -842,9 +926,9 @@ int decode_impl(bool paged, const void *q, void *out, const void *k, const void 
                 const int32_t *block_table, const int32_t *seq_lens, int fixed_len, int batch,
                 int hq, int hkv, int d, int page_tokens, int max_blocks, int num_pages,
                 int64_t max_len, int dtype, void *workspace, size_t workspace_bytes,
-                cudaStream_t st) {
+                cudaStream_t st, const GatherParams *gather = nullptr) {
   if (dtype != AXB200_FLOAT16 && dtype != AXB200_FLOAT32) return AXB200_UNSUPPORTED_TYPE;
-  if (!q || !out || !k || !v) return AXB200_INVALID_PTR;
+  if (!q || (!out && !gather) || !k || !v) return AXB200_INVALID_PTR;
   if (batch <= 0 || hq <= 0 || hkv <= 0 || d <= 0 || max_len <= 0) return AXB200_INVALID_ARGUMENT;
   if (hq % hkv != 0) return AXB200_SHAPE_MISMATCH;
   if (d > 256 || max_len > (int64_t)INT32_MAX - 4096) return AXB200_INVALID_ARGUMENT;
@@ -871,7 +955,7 @@ int decode_impl(bool paged, const void *q, void *out, const void *k, const void 
   p.chunk_tokens = pl.chunk_tokens;
   p.max_chunks = pl.max_chunks;
   p.scale = 1.0f / sqrtf((float)d);
-  p.write_final = pl.max_chunks == 1;
+  p.write_final = pl.max_chunks == 1 && !gather;  // the gather epilogue lives in the combine kernel
   if (!p.write_final) {
     if (!workspace || workspace_bytes < pl.part_o_bytes + pl.part_ml_bytes)
       return AXB200_INVALID_ARGUMENT;
@@ -921,8 +1005,13 @@ int decode_impl(bool paged, const void *q, void *out, const void *k, const void 
     // generic kernels keep raw dot products and scale inside the exponent.
     const float cdom = (tiled && f16) ? 1.0f : dom;
     const dim3 cgrid(hq, batch);
-    if (f16) gqa_combine_kernel<__half><<<cgrid, 128, 0, st>>>(p, d, cdom);
-    else gqa_combine_kernel<float><<<cgrid, 128, 0, st>>>(p, d, cdom);
+    if (gather) {
+      if (f16) gqa_combine_gather_kernel<__half><<<cgrid, 128, 0, st>>>(p, *gather, d, cdom);
+      else gqa_combine_gather_kernel<float><<<cgrid, 128, 0, st>>>(p, *gather, d, cdom);
+    } else {
+      if (f16) gqa_combine_kernel<__half><<<cgrid, 128, 0, st>>>(p, d, cdom);
+      else gqa_combine_kernel<float><<<cgrid, 128, 0, st>>>(p, d, cdom);
+    }
     status = launch_status();
   }
   return status;
@@ -973,6 +1062,68 @@ int axb200_gqa_decode_static(const void *q, const void *k, const void *v, void *
   return axb::decode_impl(false, q, out, k, v, nullptr, nullptr, (int)skv, 1, hq, hkv, d, 0, 0, 1,
                           skv, dtype, scratch, axb::kStaticScratchBytes,
                           static_cast<cudaStream_t>(stream));
+}
+
+int axb200_gqa_decode_paged_gather(const void *q, const void *k_pages, const void *v_pages,
+                                   const int32_t *block_table, const int32_t *seq_lens, int batch,
+                                   int hq, int hkv, int d, int page_tokens, int max_blocks,
+                                   int num_pages, int64_t max_seq_len, int dtype, void *workspace,
+                                   size_t workspace_bytes, void *const *peer_out,
+                                   void *const *peer_flags, void *local_state, int world, int rank,
+                                   int hq_total, void *stream) {
+  if (!peer_out || !peer_flags || !local_state) return AXB200_INVALID_PTR;
+  if (world < 1 || world > axb::kMaxPeers || rank < 0 || rank >= world || hq_total != hq * world)
+    return AXB200_INVALID_ARGUMENT;
+  axb::GatherParams g{};
+  for (int r = 0; r < world; ++r) {
+    if (!peer_out[r] || !peer_flags[r]) return AXB200_INVALID_PTR;
+    g.peer_out[r] = peer_out[r];
+    g.peer_flags[r] = static_cast<unsigned int *>(peer_flags[r]);
+  }
+  g.local_state = static_cast<unsigned int *>(local_state);
+  g.world = world;
+  g.rank = rank;
+  g.hq_total = hq_total;
+  return axb::decode_impl(true, q, nullptr, k_pages, v_pages, block_table, seq_lens, 0, batch, hq,
+                          hkv, d, page_tokens, max_blocks, num_pages, max_seq_len, dtype, workspace,
+                          workspace_bytes, static_cast<cudaStream_t>(stream), &g);
+}
+
+int axb200_p2p_alloc(size_t bytes, void **dev_ptr, void *handle64) {
+  if (!dev_ptr || !handle64 || bytes == 0) return AXB200_INVALID_ARGUMENT;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  void *ptr = nullptr;
+  if (cudaMalloc(&ptr, bytes) != cudaSuccess) return AXB200_OUT_OF_MEMORY;
+  if (cudaMemset(ptr, 0, bytes) != cudaSuccess) return AXB200_DEVICE_ERROR;
+  cudaIpcMemHandle_t h;
+  if (cudaIpcGetMemHandle(&h, ptr) != cudaSuccess) {
+    cudaFree(ptr);
+    return AXB200_DEVICE_ERROR;
+  }
+  memcpy(handle64, &h, sizeof(h));
+  *dev_ptr = ptr;
+  return AXB200_OK;
+}
+
+int axb200_p2p_open(const void *handle64, void **dev_ptr) {
+  if (!handle64 || !dev_ptr) return AXB200_INVALID_PTR;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  void *ptr = nullptr;
+  if (cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+    cudaGetLastError();
+    return AXB200_DEVICE_ERROR;
+  }
+  *dev_ptr = ptr;
+  return AXB200_OK;
+}
+
+int axb200_p2p_close(void *dev_ptr) {
+  return cudaIpcCloseMemHandle(dev_ptr) == cudaSuccess ? AXB200_OK : AXB200_DEVICE_ERROR;
+}
+
+int axb200_p2p_free(void *dev_ptr) {
+  return cudaFree(dev_ptr) == cudaSuccess ? AXB200_OK : AXB200_DEVICE_ERROR;
 }
 
 const char *axb200_version(void) { return "axono_b200 0.1 (sm_100a)"; }

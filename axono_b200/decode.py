@@ -57,9 +57,16 @@ class TextTower:
     """Random-init text tower with a paged KV cache; `decode_step` is capturable in one CUDA graph."""
 
     def __init__(self, cfg: TextTowerConfig, batch: int, max_seq_len: int, device="cuda",
-                 dtype=torch.float16, world: int = 1, rank: int = 0, seed: int = 0, page_tokens: int = 64):
+                 dtype=torch.float16, world: int = 1, rank: int = 0, seed: int = 0, page_tokens: int = 64,
+                 fused_gather: bool = True):
         self.cfg, self.batch, self.device, self.dtype = cfg, batch, torch.device(device), dtype
         self.world, self.rank = world, rank
+        self.peer_gather = None
+        if world > 1 and fused_gather:
+            from .p2p import PeerGather
+
+            # one gathered buffer per layer (at least two): successive calls never share a buffer
+            self.peer_gather = PeerGather(batch, cfg.n_q_heads, cfg.head_dim, dtype, slots=max(2, cfg.n_layers))
         kv_heads, q_heads = sharding.shard_kv_heads(cfg.n_q_heads, cfg.n_kv_heads, world, rank)
         self.local_kv, self.local_q = len(kv_heads), len(q_heads)
         g = torch.Generator(device=self.device).manual_seed(seed)  # same seed on every rank: replicas agree
@@ -116,9 +123,12 @@ class TextTower:
                                    mrope_section=cfg.mrope_section)
         else:
             self.cache.append_rope(li, q, k, v, pos=self.pos3[0], theta=cfg.rope_theta)
-        attn = self.cache.attend(li, q)  # (batch, local_q, d)
-        if self.world > 1:
-            attn = sharding.all_gather_heads(attn)
+        if self.peer_gather is not None:  # attention fused with the all-gather over peer memory
+            attn = self.cache.attend(li, q, gather=(self.peer_gather, li % self.peer_gather.slots))
+        else:
+            attn = self.cache.attend(li, q)  # (batch, local_q, d)
+            if self.world > 1:
+                attn = sharding.all_gather_heads(attn)  # library collective (NCCL): the baseline
         return torch.matmul(attn.reshape(self.batch, cfg.n_q_heads * d), lw["o"].t())
 
     def decode_step(self) -> torch.Tensor:
@@ -139,6 +149,7 @@ class TextTower:
             mlp_out = torch.matmul(act, lw["down"].t())
         _, xf = ops.add_rms_norm(mlp_out, h, self.final_ln, cfg.eps)
         logits = torch.matmul(xf, self.embed.t())
+        self.last_logits = logits
         nxt = torch.argmax(logits, dim=-1)
         self.token_ids.copy_(nxt)
         self.pos3.add_(1)

@@ -103,10 +103,12 @@ def gqa_decode_attention(q, k, v):
     return out
 
 
-def gqa_decode_attention_paged(q, k_pages, v_pages, block_table, seq_lens, max_seq_len, out=None):
+def gqa_decode_attention_paged(q, k_pages, v_pages, block_table, seq_lens, max_seq_len, out=None, gather=None):
     """Batched decode over a paged cache (extension of the reference op to a batch).
     q (batch, hq, d); k_pages/v_pages (num_pages, hkv, page_tokens, d); block_table int32
-    (batch, max_blocks); seq_lens int32 (batch) on the device; max_seq_len a host upper bound."""
+    (batch, max_blocks); seq_lens int32 (batch) on the device; max_seq_len a host upper bound.
+    gather=(PeerGather, slot): heads are sharded across ranks; the kernel writes this rank's heads into
+    every rank's gathered buffer and the full (batch, hq_total, d) tensor of this rank is returned."""
     op = "gqa_decode_attention_paged"
     dt = _dt(q, op)
     batch, hq, d = q.shape
@@ -116,11 +118,21 @@ def gqa_decode_attention_paged(q, k_pages, v_pages, block_table, seq_lens, max_s
     if block_table.dtype != torch.int32 or seq_lens.dtype != torch.int32:
         _capi.check(3, op)
     q = _c(q)
-    if out is None:
-        out = torch.empty_like(q)
     lib = _capi.lib()
     ws_bytes = lib.axb200_gqa_workspace_bytes(batch, hq, hkv, d, int(max_seq_len), dt)
     ws = workspace(q.device, ws_bytes)
+    if gather is not None:
+        pg, slot = gather
+        if pg.batch != batch or pg.d != d or pg.hq_total != hq * pg.world or pg.dtype != q.dtype:
+            _capi.check(4, op)
+        _call(lib.axb200_gqa_decode_paged_gather(
+            q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(), seq_lens.data_ptr(),
+            batch, hq, hkv, d, page_tokens, block_table.shape[1], num_pages, int(max_seq_len), dt,
+            ws.data_ptr(), ws.numel(), pg.out_ptrs(slot), pg.flag_ptrs, pg.state_ptr, pg.world, pg.rank,
+            pg.hq_total, _stream(q)), op)
+        return pg.tensor(slot)
+    if out is None:
+        out = torch.empty_like(q)
     _call(lib.axb200_gqa_decode_paged(
         q.data_ptr(), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
         seq_lens.data_ptr(), batch, hq, hkv, d, page_tokens, block_table.shape[1], num_pages,

@@ -125,6 +125,37 @@ int axb200_gqa_decode_paged(const void *q, void *out, const void *k_pages, const
                             int64_t max_seq_len, int dtype,
                             void *workspace, size_t workspace_bytes, void *stream);
 
+/* ---- decode attention fused with the all-gather of per-head outputs ------------------------------
+ * For KV heads sharded over `world` GPUs of one node (one process per GPU): rank `rank` holds hkv KV
+ * heads and the hq matching query heads of every sequence.  Same computation as
+ * axb200_gqa_decode_paged on the local heads, but the combine kernel stores each merged row straight
+ * into EVERY rank's gathered buffer (batch, hq_total, d) at head rank*hq + h - plain stores through
+ * peer-mapped pointers over NVLink - then exchanges generation flags with the peers (bounded wait,
+ * AXB200_ERR_WAIT_TIMEOUT on expiry), so that when the call's last kernel completes the local
+ * gathered buffer holds all heads.  It replaces "attention, then ncclAllGather" by one kernel pair.
+ *   peer_out[r], peer_flags[r]: host arrays of `world` device pointers - rank r's gathered buffer for
+ *     this call and rank r's flag array (world x uint32), mapped into this process (own entries are
+ *     local pointers); local_state: 2 x uint32 of this rank.  All zero-initialised once.
+ *   Successive calls must alternate between at least two gathered buffers (e.g. one per layer), and
+ *   every rank must make the same sequence of calls.  No counterpart in the reference (single GPU). */
+int axb200_gqa_decode_paged_gather(const void *q, const void *k_pages, const void *v_pages,
+                                   const int32_t *block_table, const int32_t *seq_lens,
+                                   int batch, int hq, int hkv, int d,
+                                   int page_tokens, int max_blocks, int num_pages,
+                                   int64_t max_seq_len, int dtype,
+                                   void *workspace, size_t workspace_bytes,
+                                   void *const *peer_out, void *const *peer_flags, void *local_state,
+                                   int world, int rank, int hq_total, void *stream);
+
+/* Peer-mappable device memory for the call above (CUDA IPC): alloc returns zero-filled memory and a
+ * 64-byte handle to send to the other processes of the node; open maps a peer's handle; close
+ * unmaps it; free releases an allocation.  These four are set-up calls: they allocate and
+ * synchronise, unlike every other entry point.  No counterpart in the reference. */
+int axb200_p2p_alloc(size_t bytes, void **dev_ptr, void *handle64);
+int axb200_p2p_open(const void *handle64, void **dev_ptr);
+int axb200_p2p_close(void *dev_ptr);
+int axb200_p2p_free(void *dev_ptr);
+
 /* ---- KV-cache append with RoPE / M-RoPE --------------------------------------------------
  * Replaces, for one decode step of `batch` sequences, the reference's per-layer sequence
  *   rope|rope_thd(q), rope|rope_thd(k)      (src/ops/cuda/sequence.cu:318-342, 421-449)

@@ -270,3 +270,27 @@ def test_text_tower_step_matches_cpu_restatement_and_replays():
         assert torch.equal(g.output, seq_e[-1])
     assert torch.equal(tg.cache.seq_lens, te.cache.seq_lens)
     assert ops.last_error() == 0
+
+
+def test_gather_epilogue_single_rank_matches_plain():
+    """World of one: the fused combine + all-gather kernel stores into the local gathered buffer and
+    must give exactly the plain kernel's output (same chunk plan, same merge order)."""
+    from axono_b200 import ops
+    from axono_b200.kv_cache import PagedKVCache
+    from axono_b200.p2p import PeerGather
+
+    rng = np.random.default_rng(8000)
+    B, hq, hkv, d, L = 6, 16, 8, 128, 2600
+    lens = [L, 1, 64, 65, 2048, 700]
+    for dtype in (torch.float16, torch.float32):
+        cache = PagedKVCache(1, B, hkv, d, L, dtype=dtype)
+        cache.fill(0, dev((0.5 * rng.standard_normal((B, L, hkv, d))).astype(np.float32), dtype),
+                   dev((0.5 * rng.standard_normal((B, L, hkv, d))).astype(np.float32), dtype), lens)
+        q = dev(rng.standard_normal((B, hq, d)).astype(np.float32), dtype)
+        pg = PeerGather(B, hq, d, dtype, slots=2)
+        want = cache.attend(0, q)
+        for it in range(4):
+            got = cache.attend(0, q, gather=(pg, it % 2))
+            assert torch.equal(got, want)
+        assert ops.last_error() == 0
+        pg.close()

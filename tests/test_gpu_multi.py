@@ -1,0 +1,116 @@
+"""Two-GPU tests of the head-sharded path: attention fused with the all-gather over peer memory, and
+the text-tower step built on it.  Each rank is its own process on its own GPU (ranks that wait on one
+another never share a GPU).  Skipped on a single-GPU box."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _widen(a):
+    return a.astype(np.float16).astype(np.float32)
+
+
+def _worker(rank, world, port, out_dir):
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)  # host-side exchange only
+    try:
+        from axono_b200 import ops, sharding
+        from axono_b200.cuda_graph import CUDAGraph
+        from axono_b200.decode import TextTower, TextTowerConfig
+        from axono_b200.kv_cache import PagedKVCache
+        from axono_b200.p2p import PeerGather
+
+        h = torch.float16
+        dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda().to(h)  # noqa: E731
+
+        # ---- fused attention + all-gather against the same attention on all heads locally ----
+        rng = np.random.default_rng(7000)
+        B, hq, hkv, d, L = 5, 8, 4, 128, 3000
+        lens = [L, L - 1, 64, 1000, 2049]
+        q = _widen(rng.standard_normal((B, hq, d)).astype(np.float32))
+        k = _widen((0.5 * rng.standard_normal((B, L, hkv, d))).astype(np.float32))
+        v = _widen((0.5 * rng.standard_normal((B, L, hkv, d))).astype(np.float32))
+        full = PagedKVCache(1, B, hkv, d, L, dtype=h)
+        full.fill(0, dev(k), dev(v), lens)
+        kvh, qh = sharding.shard_kv_heads(hq, hkv, world, rank)
+        local = PagedKVCache(1, B, len(kvh), d, L, dtype=h)
+        local.fill(0, dev(k[:, :, kvh.start:kvh.stop]), dev(v[:, :, kvh.start:kvh.stop]), lens)
+        pg = PeerGather(B, hq, d, h, slots=2)
+        for it in range(40):  # many generations, alternating buffers, a different q every time
+            qi = dev(q * (1.0 + 0.01 * it))
+            want = full.attend(0, qi)
+            got = local.attend(0, qi[:, qh.start:qh.stop].contiguous(), gather=(pg, it % 2))
+            torch.cuda.synchronize()
+            err = (got.float() - want.float()).abs().max().item() / want.float().abs().max().item()
+            assert err <= 1e-3, f"rank {rank} iteration {it}: {err:.3e}"
+        assert ops.last_error() == 0
+
+        # ---- text tower: sharded ranks agree with each other and with the unsharded tower ----
+        cfg = TextTowerConfig(hidden=256, intermediate=512, n_q_heads=4, n_kv_heads=2, head_dim=128, vocab=1000,
+                              n_layers=4)
+        Bt, L0 = 4, 300
+        r = np.random.default_rng(7001)
+        k0 = [_widen((0.5 * r.standard_normal((Bt, L0, 2, 128))).astype(np.float32)) for _ in range(cfg.n_layers)]
+        v0 = [_widen((0.5 * r.standard_normal((Bt, L0, 2, 128))).astype(np.float32)) for _ in range(cfg.n_layers)]
+        tlens = [L0, L0 - 7, 64, 129]
+        tok = r.integers(0, cfg.vocab, Bt)
+
+        def make(w, rk):
+            tw = TextTower(cfg, Bt, 512, dtype=h, seed=3, world=w, rank=rk)
+            kv, _ = sharding.shard_kv_heads(4, 2, w, rk)
+            for li in range(cfg.n_layers):
+                tw.cache.fill(li, dev(k0[li][:, :, kv.start:kv.stop]), dev(v0[li][:, :, kv.start:kv.stop]), tlens)
+            tw.set_state(tok, tlens)
+            return tw
+
+        single, shard = make(1, 0), make(world, rank)
+        ops.workspace("cuda", ops.gqa_workspace_bytes(Bt, 4, 2, 128, 512))
+        g = None
+        for step in range(4):
+            if step == 0:
+                shard.decode_step()  # eager
+            else:
+                if g is None:  # capture after the eager step; a capture run executes nothing
+                    g = CUDAGraph().capture(shard.decode_step, warmup=False)
+                g.replay()
+                shard.cache.note_replayed()
+            single.decode_step()
+            torch.cuda.synchronize()
+            a, b = shard.last_logits.float(), single.last_logits.float()
+            err = (a - b).abs().max().item() / b.abs().max().item()
+            assert err <= 2e-2, f"rank {rank} step {step}: logits differ {err:.3e}"
+            toks = [None] * world
+            dist.all_gather_object(toks, shard.token_ids.cpu().tolist())
+            assert all(t == toks[0] for t in toks), "ranks disagree on the next tokens"
+            single.token_ids.copy_(shard.token_ids)  # keep the two on the same trajectory
+        assert ops.last_error() == 0
+        shard.peer_gather.close()
+        pg.close()
+        open(os.path.join(out_dir, f"ok{rank}"), "w").close()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.timeout(240)
+def test_fused_gather_and_sharded_tower_two_gpus(tmp_path):
+    import torch.multiprocessing as mp
+
+    world = 2
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    assert all((tmp_path / f"ok{r}").exists() for r in range(world))
