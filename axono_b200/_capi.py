@@ -32,6 +32,9 @@ SIGNATURES = {
     "axb200_p2p_free": (_i, [_vp]),
     "axb200_kv_append_rope": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i, _i, _i,
                                    _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp]),
+    "axb200_qkv_norm_rope_append": (_i, [_vp, _i64, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i, _i,
+                                         _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp]),
+    "axb200_silu_mul_rows": (_i, [_vp, _i64, _i, _i64, _vp, _i, _vp]),
     "axb200_rope": (_i, [_vp, _vp, _f, _vp, _i64, _i, _i, _i, _vp]),
     "axb200_rope_thd": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _i64, _i, _i, _i, _vp]),
     "axb200_rope_with_cos_sin": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i, _i, _vp]),

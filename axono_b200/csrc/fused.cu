@@ -210,6 +210,37 @@ silu_mul_scalar_kernel(const T *gate, const T *up, T *out, int64_t begin, int64_
     stf(out + i, silu_mul1(ldf(gate + i), ldf(up + i)));
 }
 
+// silu(gate) * up where gate and up are the two halves of each row of one matrix (the output of a
+// fused gate|up projection): in (rows, ld) with gate = in[r, 0:n], up = in[r, n:2n]; out (rows, n).
+template <typename T>
+__global__ void __launch_bounds__(256)
+silu_mul_rows_kernel(const T *in, long long ld, int n, long long rows, T *out, bool vec) {
+  using V = Vec<T>;
+  if (vec) {
+    const int nv = n / V::kN;
+    const long long total = rows * nv;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+      const long long r = i / nv;
+      const int c = (int)(i % nv);
+      const V g = reinterpret_cast<const V *>(in + r * ld)[c];
+      const V u = reinterpret_cast<const V *>(in + r * ld + n)[c];
+      V o;
+#pragma unroll
+      for (int e = 0; e < V::kN; ++e) o.set(e, silu_mul1(g.get(e), u.get(e)));
+      reinterpret_cast<V *>(out + r * n)[c] = o;
+    }
+  } else {
+    const long long total = rows * n;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+      const long long r = i / n;
+      const int c = (int)(i % n);
+      stf(out + i, silu_mul1(ldf(in + r * ld + c), ldf(in + r * ld + n + c)));
+    }
+  }
+}
+
 // ---- concat (bytes) -----------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 concat_bytes_kernel(const uint8_t *a, const uint8_t *b, uint8_t *out, int64_t outer, size_t a_bytes,
@@ -311,6 +342,25 @@ int axb200_silu_mul(const void *gate, const void *up, void *out, int64_t n, int 
     if (nvec) axb::silu_mul_vec_kernel<__half><<<axb::blocks_for(nvec, 256), 256, 0, st>>>(g, u, o, nvec);
     if (nvec * 8 < n)
       axb::silu_mul_scalar_kernel<__half><<<axb::blocks_for(n - nvec * 8, 256), 256, 0, st>>>(g, u, o, nvec * 8, n);
+  }
+  return axb::launch_status();
+}
+
+int axb200_silu_mul_rows(const void *gate_up, int64_t ld, int n, int64_t rows, void *out, int dtype,
+                         void *stream) {
+  if (dtype != AXB200_FLOAT32 && dtype != AXB200_FLOAT16) return AXB200_UNSUPPORTED_TYPE;
+  if (!gate_up || !out) return AXB200_INVALID_PTR;
+  if (n <= 0 || rows < 0 || ld < 2 * (int64_t)n) return AXB200_INVALID_ARGUMENT;
+  if (rows == 0) return AXB200_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == AXB200_FLOAT32) {
+    const bool vec = n % 4 == 0 && ld % 4 == 0 && axb::al16(gate_up) && axb::al16(out);
+    axb::silu_mul_rows_kernel<float><<<axb::blocks_for(rows * n / (vec ? 4 : 1), 256), 256, 0, st>>>(
+        static_cast<const float *>(gate_up), ld, n, rows, static_cast<float *>(out), vec);
+  } else {
+    const bool vec = n % 8 == 0 && ld % 8 == 0 && axb::al16(gate_up) && axb::al16(out);
+    axb::silu_mul_rows_kernel<__half><<<axb::blocks_for(rows * n / (vec ? 8 : 1), 256), 256, 0, st>>>(
+        static_cast<const __half *>(gate_up), ld, n, rows, static_cast<__half *>(out), vec);
   }
   return axb::launch_status();
 }

@@ -206,6 +206,113 @@ kv_append_rope_kernel(const AppendParams p, const InvFreqTable table) {
   }
 }
 
+// ---- per-head norm + rotate + append straight from the QKV projection output ----------------------
+// The reference's layer runs, after the QKV GEMM: reshape, rms_norm(q), rms_norm(k) over head_dim
+// (examples/vlm/qwen3vl/model.py:353-357), rope on both (:358-359), cache.update (:362).  Here one
+// launch does all of it: one CTA per sequence, one warp per head; the warp reads its head's row from
+// the GEMM output (row stride `ld`), reduces the sum of squares with shuffles, scales by the norm
+// weight, rotates, and writes q to a contiguous (batch,hq,d) buffer and k/v into the page slot.
+struct FusedQkvParams {
+  const void *qkv;  // (batch, ld): [q heads | k heads | v heads] per row
+  long long ld;
+  const void *q_norm_w, *k_norm_w;  // (d) or null
+  float eps;
+  void *q_out;  // (batch, hq, d)
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+qkv_norm_rope_append_kernel(const AppendParams p, const FusedQkvParams f, const InvFreqTable table) {
+  __shared__ int s_len;
+  const int b = blockIdx.x;
+  if (threadIdx.x == 0) s_len = p.seq_lens[b] + p.slot_delta;
+  __syncthreads();
+  const int len = s_len;
+  const int half = p.d / 2;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+
+  float pt, ph, pw;
+  if (p.pos == nullptr) {
+    pt = ph = pw = (float)len;
+  } else if (p.mrope) {
+    pt = (float)p.pos[b];
+    ph = (float)p.pos[p.batch + b];
+    pw = (float)p.pos[2 * p.batch + b];
+  } else {
+    pt = ph = pw = (float)p.pos[b];
+  }
+  const int slot = len / p.page_tokens;
+  int page = -1;
+  if (len >= 0 && slot < p.max_blocks) page = p.block_table[(size_t)b * p.max_blocks + slot];
+  const bool page_ok = page >= 0 && page < p.num_pages;
+  if (!page_ok && threadIdx.x == 0)
+    atomicOr(&g_error_word, (len >= 0 && slot < p.max_blocks) ? AXB200_ERR_BAD_PAGE
+                                                              : AXB200_ERR_CAPACITY);
+  const int tok = len % p.page_tokens;
+  const T *row = reinterpret_cast<const T *>(f.qkv) + (size_t)b * f.ld;
+
+  for (int head = warp; head < p.hq + 2 * p.hkv; head += nwarps) {
+    const bool is_q = head < p.hq, is_k = !is_q && head < p.hq + p.hkv;
+    const T *src = row + (size_t)head * p.d;
+    T *dst;
+    if (is_q) {
+      dst = reinterpret_cast<T *>(f.q_out) + ((size_t)b * p.hq + head) * p.d;
+    } else {
+      if (!page_ok) continue;
+      const int h = is_k ? head - p.hq : head - p.hq - p.hkv;
+      dst = reinterpret_cast<T *>(is_k ? p.k_pages : p.v_pages) +
+            (((size_t)page * p.hkv + h) * p.page_tokens + tok) * p.d;
+    }
+    if (!is_q && !is_k) {  // v: copy
+      for (int c = lane; c < p.d; c += 32) dst[c] = src[c];
+      continue;
+    }
+    // pairs (i, i+half), i = lane + 32*j
+    float a[4], bb[4];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int i = lane + 32 * j;
+      a[j] = i < half ? ld(src + i) : 0.f;
+      bb[j] = i < half ? ld(src + i + half) : 0.f;
+      ss = fmaf(a[j], a[j], ss);
+      ss = fmaf(bb[j], bb[j], ss);
+    }
+    const T *w = reinterpret_cast<const T *>(is_q ? f.q_norm_w : f.k_norm_w);
+    float inv = 1.f;
+    if (w) {
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+      inv = 1.0f / sqrtf(ss / (float)p.d + f.eps);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int i = lane + 32 * j;
+      if (i >= half) continue;
+      float x0 = a[j], x1 = bb[j];
+      if (w) {
+        x0 = x0 * inv * ld(w + i);
+        x1 = x1 * inv * ld(w + i + half);
+      }
+      if (p.rotate) {
+        const float fr = p.mrope || p.inv_freq_dev ? p.inv_freq_dev[i] : table.f[i];
+        const float posv = p.mrope ? pair_position(i, pt, ph, pw, p.h_lim, p.w_lim) : pt;
+        float sn, cs;
+        sincosf(posv * fr, &sn, &cs);
+        const float r0 = x0 * cs - x1 * sn, r1 = x1 * cs + x0 * sn;
+        x0 = r0;
+        x1 = r1;
+      }
+      st(dst + i, x0);
+      st(dst + i + half, x1);
+    }
+  }
+  if (p.advance && page_ok) {
+    __syncthreads();
+    if (threadIdx.x == 0) p.seq_lens[b] = len - p.slot_delta + 1;
+  }
+}
+
 // theta^(-2i/dim) with the host C library's powf, as src/ops/cpu/sequence.cpp:83-84 computes it.
 void fill_table(InvFreqTable *t, float theta, int dim) {
   for (int i = 0; i < dim / 2 && i < kMaxHalf; ++i)
@@ -341,6 +448,57 @@ int axb200_kv_append_rope(void *q, const void *k_new, const void *v_new, void *k
     axb::kv_append_rope_kernel<float><<<batch, 256, 0, st>>>(p, table);
   else
     axb::kv_append_rope_kernel<__half><<<batch, 256, 0, st>>>(p, table);
+  return axb::launch_status();
+}
+
+int axb200_qkv_norm_rope_append(const void *qkv, int64_t ld, const void *q_norm_w,
+                                const void *k_norm_w, float eps, void *q_out, void *k_pages,
+                                void *v_pages, const int32_t *block_table, int32_t *seq_lens,
+                                const int64_t *pos, const float *inv_freq, float theta, int rotate,
+                                int mrope, int h_sec, int w_sec, int batch, int hq, int hkv, int d,
+                                int page_tokens, int max_blocks, int num_pages, int dtype,
+                                int slot_delta, int advance, void *stream) {
+  if (dtype != AXB200_FLOAT32 && dtype != AXB200_FLOAT16) return AXB200_UNSUPPORTED_TYPE;
+  if (!qkv || !q_out || !k_pages || !v_pages || !block_table || !seq_lens) return AXB200_INVALID_PTR;
+  if (batch <= 0 || hq <= 0 || hkv <= 0 || d <= 0 || d % 2 != 0 || d / 2 > axb::kMaxHalf ||
+      page_tokens <= 0 || max_blocks <= 0 || num_pages <= 0 || slot_delta > 0 || slot_delta < -1 ||
+      ld < (int64_t)(hq + 2 * hkv) * d)
+    return AXB200_INVALID_ARGUMENT;
+  if (rotate && mrope && !inv_freq) return AXB200_INVALID_PTR;
+  axb::AppendParams p{};
+  p.k_pages = k_pages;
+  p.v_pages = v_pages;
+  p.block_table = block_table;
+  p.seq_lens = seq_lens;
+  p.pos = pos;
+  p.inv_freq_dev = inv_freq;
+  p.rotate = rotate;
+  p.mrope = mrope;
+  p.h_lim = h_sec * 3;
+  p.w_lim = w_sec * 3;
+  p.batch = batch;
+  p.hq = hq;
+  p.hkv = hkv;
+  p.d = d;
+  p.page_tokens = page_tokens;
+  p.max_blocks = max_blocks;
+  p.num_pages = num_pages;
+  p.slot_delta = slot_delta;
+  p.advance = advance;
+  axb::FusedQkvParams f{};
+  f.qkv = qkv;
+  f.ld = ld;
+  f.q_norm_w = q_norm_w;
+  f.k_norm_w = k_norm_w;
+  f.eps = eps;
+  f.q_out = q_out;
+  axb::InvFreqTable table{};
+  if (rotate && !inv_freq) axb::fill_table(&table, theta, d);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == AXB200_FLOAT32)
+    axb::qkv_norm_rope_append_kernel<float><<<batch, 256, 0, st>>>(p, f, table);
+  else
+    axb::qkv_norm_rope_append_kernel<__half><<<batch, 256, 0, st>>>(p, f, table);
   return axb::launch_status();
 }
 

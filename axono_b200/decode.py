@@ -58,8 +58,9 @@ class TextTower:
 
     def __init__(self, cfg: TextTowerConfig, batch: int, max_seq_len: int, device="cuda",
                  dtype=torch.float16, world: int = 1, rank: int = 0, seed: int = 0, page_tokens: int = 64,
-                 fused_gather: bool = True):
+                 fused_gather: bool = True, fused_qkv: bool = True):
         self.cfg, self.batch, self.device, self.dtype = cfg, batch, torch.device(device), dtype
+        self.fused_qkv = fused_qkv
         self.world, self.rank = world, rank
         self.peer_gather = None
         if world > 1 and fused_gather:
@@ -109,20 +110,27 @@ class TextTower:
     def _attention(self, li: int, xn: torch.Tensor) -> torch.Tensor:
         cfg, lw, d = self.cfg, self.layers[li], self.cfg.head_dim
         qkv = torch.matmul(xn, lw["qkv"].t())  # library GEMM
-        nq, nk = self.local_q * d, self.local_kv * d
-        q = qkv[:, :nq].reshape(self.batch, self.local_q, d)
-        k = qkv[:, nq:nq + nk].reshape(self.batch, self.local_kv, d)
-        v = qkv[:, nq + nk:].reshape(self.batch, self.local_kv, d).contiguous()
-        if cfg.qk_norm:  # per-head norm over head_dim (model.py:356-357)
-            q = ops.rms_norm(q, lw["q_norm"], cfg.eps)
-            k = ops.rms_norm(k, lw["k_norm"], cfg.eps)
-        else:
-            q, k = q.contiguous(), k.contiguous()
-        if cfg.use_mrope:
-            self.cache.append_rope(li, q, k, v, pos=self.pos3, inv_freq=self.inv_freq,
-                                   mrope_section=cfg.mrope_section)
-        else:
-            self.cache.append_rope(li, q, k, v, pos=self.pos3[0], theta=cfg.rope_theta)
+        if self.fused_qkv:  # per-head norms + rope + append in one launch, straight from the GEMM output
+            q = self.cache.append_qkv(li, qkv, self.local_q, lw["q_norm"] if cfg.qk_norm else None,
+                                      lw["k_norm"] if cfg.qk_norm else None, cfg.eps,
+                                      pos=self.pos3 if cfg.use_mrope else self.pos3[0],
+                                      inv_freq=self.inv_freq if cfg.use_mrope else None, theta=cfg.rope_theta,
+                                      mrope_section=cfg.mrope_section if cfg.use_mrope else None)
+        else:  # the reference's operator sequence (model.py:353-362)
+            nq, nk = self.local_q * d, self.local_kv * d
+            q = qkv[:, :nq].reshape(self.batch, self.local_q, d)
+            k = qkv[:, nq:nq + nk].reshape(self.batch, self.local_kv, d)
+            v = qkv[:, nq + nk:].reshape(self.batch, self.local_kv, d).contiguous()
+            if cfg.qk_norm:  # per-head norm over head_dim (model.py:356-357)
+                q = ops.rms_norm(q, lw["q_norm"], cfg.eps)
+                k = ops.rms_norm(k, lw["k_norm"], cfg.eps)
+            else:
+                q, k = q.contiguous(), k.contiguous()
+            if cfg.use_mrope:
+                self.cache.append_rope(li, q, k, v, pos=self.pos3, inv_freq=self.inv_freq,
+                                       mrope_section=cfg.mrope_section)
+            else:
+                self.cache.append_rope(li, q, k, v, pos=self.pos3[0], theta=cfg.rope_theta)
         if self.peer_gather is not None:  # attention fused with the all-gather over peer memory
             attn = self.cache.attend(li, q, gather=(self.peer_gather, li % self.peer_gather.slots))
         else:
@@ -145,7 +153,10 @@ class TextTower:
             attn_out = self._attention(li, xn)
             h, xn2 = ops.add_rms_norm(attn_out, h, lw["post_ln"], cfg.eps)
             gu = torch.matmul(xn2, lw["gate_up"].t())
-            act = ops.silu_mul(gu[:, :cfg.intermediate].contiguous(), gu[:, cfg.intermediate:].contiguous())
+            if self.fused_qkv:
+                act = ops.silu_mul_rows(gu, cfg.intermediate)
+            else:
+                act = ops.silu_mul(gu[:, :cfg.intermediate].contiguous(), gu[:, cfg.intermediate:].contiguous())
             mlp_out = torch.matmul(act, lw["down"].t())
         _, xf = ops.add_rms_norm(mlp_out, h, self.final_ln, cfg.eps)
         logits = torch.matmul(xf, self.embed.t())

@@ -19,6 +19,18 @@ class KVCache:
     def update(self, layer_idx: int, k_new, v_new):  # pragma: no cover
         raise NotImplementedError
 
+    def append_qkv(self, layer_idx: int, qkv, n_q_heads, q_norm_weight=None, k_norm_weight=None, eps=1e-6,
+                   pos=None, inv_freq=None, theta=10000.0, mrope_section=None):
+        """Per-head norm + rope + append straight from the QKV projection output; returns q (batch,hq,d)."""
+        first = layer_idx == 0
+        q = ops.qkv_norm_rope_append(qkv, n_q_heads, q_norm_weight, k_norm_weight, eps, self.k_pages[layer_idx],
+                                     self.v_pages[layer_idx], self.block_table, self.seq_lens, pos=pos,
+                                     inv_freq=inv_freq, theta=theta, mrope_section=mrope_section, rotate=True,
+                                     advance=first, slot_delta=0 if first else -1)
+        if first:
+            self._host_len_bound += 1
+        return q
+
     def get(self, layer_idx: int):  # pragma: no cover
         raise NotImplementedError
 

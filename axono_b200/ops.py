@@ -164,6 +164,47 @@ def kv_append_rope(q, k_new, v_new, k_pages, v_pages, block_table, seq_lens, pos
     return q
 
 
+def qkv_norm_rope_append(qkv, n_q_heads, q_norm_weight, k_norm_weight, eps, k_pages, v_pages, block_table, seq_lens,
+                         pos=None, inv_freq=None, theta=10000.0, mrope_section=None, rotate=True, advance=True,
+                         slot_delta=0):
+    """Per-head rms_norm(q), rms_norm(k), rope on both and the cache append, straight from the QKV
+    projection output qkv (batch, (hq + 2*hkv) * d) (rows may be strided).  Returns the normed, rotated
+    q as a new (batch, hq, d) tensor."""
+    op = "qkv_norm_rope_append"
+    dt = _dt(qkv, op)
+    if qkv.dim() != 2 or qkv.stride(1) != 1:
+        _capi.check(4, op)
+    num_pages, hkv, page_tokens, d = k_pages.shape
+    batch = qkv.shape[0]
+    if qkv.shape[1] != (n_q_heads + 2 * hkv) * d:
+        _capi.check(4, op)
+    for w in (q_norm_weight, k_norm_weight):
+        if w is not None and (w.dtype != qkv.dtype or tuple(w.shape) != (d,) or not w.is_contiguous()):
+            _capi.check(4, op)
+    mrope = mrope_section is not None
+    h_sec, w_sec = (mrope_section[1], mrope_section[2]) if mrope else (0, 0)
+    q_out = torch.empty((batch, n_q_heads, d), dtype=qkv.dtype, device=qkv.device)
+    _call(_capi.lib().axb200_qkv_norm_rope_append(
+        qkv.data_ptr(), qkv.stride(0), _ptr(q_norm_weight), _ptr(k_norm_weight), float(eps), q_out.data_ptr(),
+        k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(), seq_lens.data_ptr(), _ptr(pos),
+        _ptr(inv_freq), float(theta), int(rotate), int(mrope), h_sec, w_sec, batch, n_q_heads, hkv, d,
+        page_tokens, block_table.shape[1], num_pages, dt, int(slot_delta), int(advance), _stream(qkv)), op)
+    return q_out
+
+
+def silu_mul_rows(gate_up, n: int):
+    """silu(gate) * up for gate = gate_up[:, :n], up = gate_up[:, n:2n] (one fused gate|up projection
+    output, rows may be strided) -> (rows, n)."""
+    op = "silu_mul_rows"
+    dt = _dt(gate_up, op)
+    if gate_up.dim() != 2 or gate_up.stride(1) != 1 or gate_up.shape[1] != 2 * n:
+        _capi.check(4, op)
+    out = torch.empty((gate_up.shape[0], n), dtype=gate_up.dtype, device=gate_up.device)
+    _call(_capi.lib().axb200_silu_mul_rows(gate_up.data_ptr(), gate_up.stride(0), n, gate_up.shape[0],
+                                           out.data_ptr(), dt, _stream(gate_up)), op)
+    return out
+
+
 def rope(x, pos_ids, theta: float = 10000.0):
     op = "rope"
     dt = _dt(x, op)

@@ -459,7 +459,8 @@ def run_tower(args):
     if args.workload == "c5_tower":
         B, L = 32, 16384
         cfg = TextTowerConfig()
-        tower = TextTower(cfg, B, L + total_steps + 64, device=device, world=world, rank=rank, seed=5)
+        tower = TextTower(cfg, B, L + total_steps + 64, device=device, world=world, rank=rank, seed=5,
+                          fused_gather=args.gather == "fused")
         for li in range(cfg.n_layers):
             fill_random(tower.cache.k_pages[li], gen)
             fill_random(tower.cache.v_pages[li], gen)
@@ -491,8 +492,28 @@ def run_tower(args):
         launches_note = "add_rms_norm, q copy, kv_append_rope, split, combine, silu_mul"
         other_bytes = 0.0
 
-    g = CUDAGraph().capture(body)
-    cache.note_replayed()
+    use_graph = not (world > 1 and args.workload == "c5_tower" and args.gather == "nccl")
+    if use_graph:
+        g = CUDAGraph().capture(body)
+        cache.note_replayed()
+    else:
+        # baseline with the library collective: eager launches (a torch.distributed collective is not
+        # put inside a captured graph here)
+        class _Eager:
+            num_nodes = 0
+            output = None
+
+            def replay_async(self):
+                self.output = body()
+
+            def replay(self):
+                self.output = body()
+                torch.cuda.current_stream().synchronize()
+
+        g = _Eager()
+        before = ops.launch_count()
+        g.replay()
+        g.num_nodes = ops.launch_count() - before
     for _ in range(args.warmup):
         g.replay_async()
     sampler = ClockSampler(local_rank)
@@ -525,8 +546,11 @@ def run_tower(args):
             "metric": "decode_tokens_per_s", "value": B * args.steps / (ms / 1e3), "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": args.workload, "batch": B, "kv_len": L, "cuda_graph": True, "graph_nodes": g.num_nodes,
-                       "sharding": f"KV heads x{world}" + (", all-gather of attention outputs per layer" if world > 1 else ""),
+            "config": {"workload": args.workload, "batch": B, "kv_len": L, "cuda_graph": use_graph, "graph_nodes": g.num_nodes,
+                       "sharding": f"KV heads x{world}" + ((", attention fused with the all-gather over peer memory"
+                                                            if args.gather == "fused" else
+                                                            ", NCCL all-gather of attention outputs per layer")
+                                                           if world > 1 and args.workload == "c5_tower" else ""),
                        "kernels": launches_note, "l2": "KV per step larger than L2"},
             "kv_cache_gbs": all_kv / (step_ms / 1e3) / 1e9,
             "kv_frac_of_measured_peak": all_kv / (step_ms / 1e3) / 1e9 / (peak * world),
@@ -550,6 +574,8 @@ def main():
     ap.add_argument("--workload", default="c3_ragged", choices=sorted(WORKLOADS) + ["c2_block", "c5_tower"])
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="weak: every GPU gets its own batch; strong: one batch sharded over the GPUs")
+    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
+                    help="c5_tower on >1 GPU: fused = attention kernel writes into peers' buffers; nccl = library all-gather")
     ap.add_argument("--cpu-budget", type=float, default=10.0, help="seconds of CPU work for cpu_baseline")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-extra", action="store_true")

@@ -183,6 +183,21 @@ int axb200_kv_append_rope(void *q, const void *k_new, const void *v_new,
                           int page_tokens, int max_blocks, int num_pages,
                           int dtype, int slot_delta, int advance, void *stream);
 
+/* The same step taken straight from the QKV projection's output, with the per-head RMS norms the
+ * reference's text tower applies in between (axono/python/examples/vlm/qwen3vl/model.py:353-362:
+ * reshape, rms_norm(q, q_norm), rms_norm(k, k_norm), rope_thd / rope on q and k, cache.update): one
+ * launch replaces those six.  qkv (batch, ld): each row holds hq query heads, then hkv key heads, then
+ * hkv value heads of d elements; q_norm_w / k_norm_w (d) or NULL (no norm); the normed, rotated q
+ * goes to q_out (batch,hq,d), k and v into the page slot.  Other arguments as above. */
+int axb200_qkv_norm_rope_append(const void *qkv, int64_t ld, const void *q_norm_w, const void *k_norm_w,
+                                float eps, void *q_out, void *k_pages, void *v_pages,
+                                const int32_t *block_table, int32_t *seq_lens,
+                                const int64_t *pos, const float *inv_freq, float theta,
+                                int rotate, int mrope, int h_sec, int w_sec,
+                                int batch, int hq, int hkv, int d,
+                                int page_tokens, int max_blocks, int num_pages,
+                                int dtype, int slot_delta, int advance, void *stream);
+
 /* ---- RoPE family (stand-alone ops) --------------------------------------------------------
  * x/out (rows,heads,dim); out may alias x. */
 
@@ -216,6 +231,12 @@ int axb200_add_rms_norm(const void *x, const void *residual, const void *weight,
 
 /* axono::ops::cuda::SiluMul, src/ops/cuda/fused.cu:76-89: out = gate / (1 + exp(-gate)) * up. */
 int axb200_silu_mul(const void *gate, const void *up, void *out, int64_t n, int dtype, void *stream);
+
+/* SiluMul on the two halves of one matrix - the output of a fused gate|up projection
+ * (model.py:383-384 calls silu_mul(gate_proj(x), up_proj(x))): gate = in[r, 0:n], up = in[r, n:2n],
+ * row stride ld; out (rows, n).  Saves the two slicing copies. */
+int axb200_silu_mul_rows(const void *gate_up, int64_t ld, int n, int64_t rows, void *out, int dtype,
+                         void *stream);
 
 /* axono::ops::cuda::RmsNorm, include/axono/ops/cuda/llm.h:33-36, src/ops/cuda/llm.cu:345-373:
  * out = x * rsqrt(mean(x^2) + eps) * weight over the last dim; weight may be NULL. */

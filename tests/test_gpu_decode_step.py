@@ -294,3 +294,66 @@ def test_gather_epilogue_single_rank_matches_plain():
             assert torch.equal(got, want)
         assert ops.last_error() == 0
         pg.close()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("mrope", [False, True])
+def test_qkv_norm_rope_append_matches_oracle_chain(dtype, mrope):
+    """One launch against the oracle's rms_norm -> rope/rope_thd -> concat chain."""
+    from axono_b200 import ops
+    from axono_b200.kv_cache import PagedKVCache
+
+    orc = oracle.best()
+    rng = np.random.default_rng(9000 + int(mrope))
+    B, hq, hkv, d = 6, 16, 8, 128
+    lens = [0, 1, 63, 64, 500, 2000]
+    conv = widen if dtype == torch.float16 else (lambda a: a)
+    qkv = conv(rng.standard_normal((B, (hq + 2 * hkv) * d)).astype(np.float32))
+    wq = conv((1 + 0.1 * rng.standard_normal(d)).astype(np.float32))
+    wk = conv((1 + 0.1 * rng.standard_normal(d)).astype(np.float32))
+    k0 = conv(rng.standard_normal((B, 2000, hkv, d)).astype(np.float32))
+    cache = PagedKVCache(1, B, hkv, d, 2048 + 64, dtype=dtype)
+    cache.fill(0, dev(k0, dtype), dev(k0, dtype), lens)
+    inv = cases.inv_freq(1e6)
+    # a padded (strided) GEMM output: rows are longer than the data
+    padded = torch.zeros((B, qkv.shape[1] + 64), dtype=dtype, device="cuda")
+    padded[:, : qkv.shape[1]] = dev(qkv, dtype)
+    view = padded[:, : qkv.shape[1]]
+    if mrope:
+        pos3 = rng.integers(0, 40000, (3, B)).astype(np.int64)
+        q = cache.append_qkv(0, view, hq, dev(wq, dtype), dev(wk, dtype), 1e-6, pos=dev(pos3), inv_freq=dev(inv),
+                             mrope_section=(24, 20, 20))
+    else:
+        pos = rng.integers(0, 40000, B).astype(np.int64)
+        q = cache.append_qkv(0, view, hq, dev(wq, dtype), dev(wk, dtype), 1e-6, pos=dev(pos), theta=1e6)
+    qn = orc.rms_norm(qkv[:, : hq * d].reshape(B * hq, d), wq, 1e-6).reshape(B, hq, d)
+    kn = orc.rms_norm(qkv[:, hq * d : (hq + hkv) * d].reshape(B * hkv, d), wk, 1e-6).reshape(B, hkv, d)
+    vn = qkv[:, (hq + hkv) * d :].reshape(B, hkv, d)
+    if mrope:
+        q_ref, k_ref = orc.rope_thd(qn, pos3, inv, (24, 20, 20)), orc.rope_thd(kn, pos3, inv, (24, 20, 20))
+    else:
+        q_ref, k_ref = orc.rope(qn, pos, 1e6), orc.rope(kn, pos, 1e6)
+    tol = 1e-5 if dtype == torch.float32 else F16_TOL
+    assert oracle.rel_err(host(q), q_ref) <= tol
+    assert cache.seq_lens.cpu().tolist() == [n + 1 for n in lens]
+    for b, n in enumerate(lens):
+        kb, vb = cache.gather(0, b)
+        assert torch.equal(kb[:n], dev(k0[b, :n], dtype))
+        assert oracle.rel_err(host(kb[n]), k_ref[b]) <= tol
+        assert torch.equal(vb[n], dev(vn[b], dtype))  # a byte copy
+    assert ops.last_error() == 0
+
+
+def test_silu_mul_rows():
+    from axono_b200 import ops
+
+    orc = oracle.best()
+    rng = np.random.default_rng(9100)
+    for rows, n, pad in ((8, 6144, 0), (3, 53, 0), (5, 64, 8)):
+        gu = rng.standard_normal((rows, 2 * n + pad)).astype(np.float32)
+        ref = orc.silu_mul(gu[:, :n], gu[:, n : 2 * n])
+        t = dev(gu)[:, : 2 * n]
+        np.testing.assert_allclose(host(ops.silu_mul_rows(t, n)), ref, rtol=1e-5, atol=1e-6)
+        t16 = dev(widen(gu), torch.float16)[:, : 2 * n]
+        ref16 = orc.silu_mul(widen(gu)[:, :n], widen(gu)[:, n : 2 * n])
+        assert oracle.rel_err(host(ops.silu_mul_rows(t16, n)), ref16) <= F16_TOL
