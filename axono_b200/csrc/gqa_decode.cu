@@ -629,6 +629,37 @@ gqa_split_generic_kernel(const T *k, const T *v, const DecodeParams p, int d) {
   }
 }
 
+// Merge weights of a (sequence, head)'s chunk partials, computed once by the CTA: w_c =
+// 2^((m_c - M) * dom) / sum_c l_c 2^((m_c - M) * dom), left in s_w[0..n).  n <= kMaxChunks.
+__device__ __forceinline__ void combine_weights(const float *part_ml, size_t base, int n, float dom,
+                                                float *s_w, float *s_red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  float m_loc = -INFINITY;
+  for (int c = threadIdx.x; c < n; c += blockDim.x) m_loc = fmaxf(m_loc, part_ml[(base + c) * 2]);
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) m_loc = fmaxf(m_loc, __shfl_xor_sync(0xffffffffu, m_loc, off));
+  if (lane == 0) s_red[warp] = m_loc;
+  __syncthreads();
+  float M = s_red[0];
+  for (int w = 1; w < nwarps; ++w) M = fmaxf(M, s_red[w]);
+  __syncthreads();
+  float l_loc = 0.f;
+  for (int c = threadIdx.x; c < n; c += blockDim.x) {
+    const float w = exp2f((part_ml[(base + c) * 2] - M) * dom);
+    s_w[c] = w;
+    l_loc = fmaf(part_ml[(base + c) * 2 + 1], w, l_loc);
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) l_loc += __shfl_xor_sync(0xffffffffu, l_loc, off);
+  if (lane == 0) s_red[warp] = l_loc;
+  __syncthreads();
+  float Lsum = 0.f;
+  for (int w = 0; w < nwarps; ++w) Lsum += s_red[w];
+  const float inv = 1.0f / Lsum;
+  for (int c = threadIdx.x; c < n; c += blockDim.x) s_w[c] *= inv;
+  __syncthreads();
+}
+
 // ---- combine: log-sum-exp merge of a sequence's chunk partials --------------------------------
 // One CTA per (sequence, query head); thread t owns output dims t, t+blockDim, ...  `dom` is the
 // exponent domain of the stored maxima.  A sequence of length 0 yields zeros.
@@ -645,19 +676,12 @@ gqa_combine_kernel(const DecodeParams p, int d, float dom) {
     for (int c = threadIdx.x; c < d; c += blockDim.x) out[c] = static_cast<OutT>(0.f);
     return;
   }
-  float M = -INFINITY;
-  for (int c = 0; c < n; ++c) M = fmaxf(M, p.part_ml[(base + c) * 2]);
-  float Lsum = 0.f;
-  for (int c = 0; c < n; ++c)
-    Lsum += p.part_ml[(base + c) * 2 + 1] * exp2f((p.part_ml[(base + c) * 2] - M) * dom);
-  const float inv = 1.0f / Lsum;
+  __shared__ float s_w[kMaxChunks], s_red[4];
+  combine_weights(p.part_ml, base, n, dom, s_w, s_red);
   for (int c0 = threadIdx.x; c0 < d; c0 += blockDim.x) {
     float acc = 0.f;
-    for (int c = 0; c < n; ++c) {
-      const float w = exp2f((p.part_ml[(base + c) * 2] - M) * dom);
-      acc = fmaf(w, p.part_o[(base + c) * d + c0], acc);
-    }
-    out[c0] = static_cast<OutT>(acc * inv);
+    for (int c = 0; c < n; ++c) acc = fmaf(s_w[c], p.part_o[(base + c) * d + c0], acc);
+    out[c0] = static_cast<OutT>(acc);
   }
 }
 
@@ -697,21 +721,12 @@ gqa_combine_gather_kernel(const DecodeParams p, const GatherParams g, int d, flo
   n = max(0, min(n, p.max_chunks));
   const size_t base = ((size_t)b * p.hq + h) * p.max_chunks;
   const size_t row = ((size_t)b * g.hq_total + (size_t)g.rank * p.hq + h) * d;
-  float M = -INFINITY, inv = 0.f;
-  if (n > 0) {
-    for (int c = 0; c < n; ++c) M = fmaxf(M, p.part_ml[(base + c) * 2]);
-    float Lsum = 0.f;
-    for (int c = 0; c < n; ++c)
-      Lsum += p.part_ml[(base + c) * 2 + 1] * exp2f((p.part_ml[(base + c) * 2] - M) * dom);
-    inv = 1.0f / Lsum;
-  }
+  __shared__ float s_w[kMaxChunks], s_red[4];
+  if (n > 0) combine_weights(p.part_ml, base, n, dom, s_w, s_red);
   for (int c0 = threadIdx.x; c0 < d; c0 += blockDim.x) {
     float acc = 0.f;
-    for (int c = 0; c < n; ++c) {
-      const float w = exp2f((p.part_ml[(base + c) * 2] - M) * dom);
-      acc = fmaf(w, p.part_o[(base + c) * d + c0], acc);
-    }
-    const OutT val = static_cast<OutT>(acc * inv);
+    for (int c = 0; c < n; ++c) acc = fmaf(s_w[c], p.part_o[(base + c) * d + c0], acc);
+    const OutT val = static_cast<OutT>(acc);
     for (int r = 0; r < g.world; ++r) reinterpret_cast<OutT *>(g.peer_out[r])[row + c0] = val;
   }
   // last-CTA-done: every thread fences its stores system-wide before its CTA counts itself in

@@ -161,6 +161,17 @@ kv_append_rope_kernel(const AppendParams p, const InvFreqTable table) {
   const T *kn = reinterpret_cast<const T *>(p.k_new) + (size_t)b * p.hkv * p.d;
   const T *vn = reinterpret_cast<const T *>(p.v_new) + (size_t)b * p.hkv * p.d;
 
+  // cos/sin of each rotary pair once per sequence; every head reuses them
+  __shared__ float s_cos[kMaxHalf], s_sin[kMaxHalf];
+  if (p.rotate) {
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+      const float f = p.mrope || p.inv_freq_dev ? p.inv_freq_dev[i] : table.f[i];
+      const float posv = p.mrope ? pair_position(i, pt, ph, pw, p.h_lim, p.w_lim) : pt;
+      sincosf(posv * f, &s_sin[i], &s_cos[i]);
+    }
+    __syncthreads();
+  }
+
   const int q_pairs = p.hq * half, k_pairs = p.hkv * half;
   for (int idx = threadIdx.x; idx < q_pairs + k_pairs; idx += blockDim.x) {
     const bool is_q = idx < q_pairs;
@@ -168,9 +179,8 @@ kv_append_rope_kernel(const AppendParams p, const InvFreqTable table) {
     const int h = j / half, i = j % half;
     float c = 1.f, s = 0.f;
     if (p.rotate) {
-      const float f = p.mrope || p.inv_freq_dev ? p.inv_freq_dev[i] : table.f[i];
-      const float posv = p.mrope ? pair_position(i, pt, ph, pw, p.h_lim, p.w_lim) : pt;
-      sincosf(posv * f, &s, &c);
+      c = s_cos[i];
+      s = s_sin[i];
     }
     if (is_q) {
       if (p.rotate) {
@@ -251,6 +261,17 @@ qkv_norm_rope_append_kernel(const AppendParams p, const FusedQkvParams f, const 
   const int tok = len % p.page_tokens;
   const T *row = reinterpret_cast<const T *>(f.qkv) + (size_t)b * f.ld;
 
+  // cos/sin of each rotary pair once per sequence; every head reuses them
+  __shared__ float s_cos[kMaxHalf], s_sin[kMaxHalf];
+  if (p.rotate) {
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+      const float fr = p.mrope || p.inv_freq_dev ? p.inv_freq_dev[i] : table.f[i];
+      const float posv = p.mrope ? pair_position(i, pt, ph, pw, p.h_lim, p.w_lim) : pt;
+      sincosf(posv * fr, &s_sin[i], &s_cos[i]);
+    }
+    __syncthreads();
+  }
+
   for (int head = warp; head < p.hq + 2 * p.hkv; head += nwarps) {
     const bool is_q = head < p.hq, is_k = !is_q && head < p.hq + p.hkv;
     const T *src = row + (size_t)head * p.d;
@@ -295,10 +316,7 @@ qkv_norm_rope_append_kernel(const AppendParams p, const FusedQkvParams f, const 
         x1 = x1 * inv * ld(w + i + half);
       }
       if (p.rotate) {
-        const float fr = p.mrope || p.inv_freq_dev ? p.inv_freq_dev[i] : table.f[i];
-        const float posv = p.mrope ? pair_position(i, pt, ph, pw, p.h_lim, p.w_lim) : pt;
-        float sn, cs;
-        sincosf(posv * fr, &sn, &cs);
+        const float sn = s_sin[i], cs = s_cos[i];
         const float r0 = x0 * cs - x1 * sn, r1 = x1 * cs + x0 * sn;
         x0 = r0;
         x1 = r1;

@@ -259,6 +259,8 @@ def run_ours(args):
     max_over_ranks, sum_over_ranks = sharding.max_over_ranks, sharding.sum_over_ranks
 
     lib = _capi.lib()
+    tdtype = torch.float16 if args.dtype == "f16" else torch.float32
+    elem = 2 if args.dtype == "f16" else 4
     w = WORKLOADS[args.workload]
     if args.scaling == "strong":
         # one global batch, sequences assigned to ranks by KV bytes (longest first)
@@ -271,12 +273,12 @@ def run_ours(args):
     capacity = int(w["hi"]) + 2 * total_steps + 64
     gen = torch.Generator(device=device).manual_seed(1234 + rank)
 
-    cache = PagedKVCache(1, B, HKV, D, capacity, dtype=torch.float16, device=device, page_tokens=PAGE_TOKENS)
+    cache = PagedKVCache(1, B, HKV, D, capacity, dtype=tdtype, device=device, page_tokens=PAGE_TOKENS)
     for pool in (cache.k_pages[0], cache.v_pages[0]):  # K, V = 0.5 * N(0,1), generated in slabs
         step_pages = 512
         for p0 in range(0, pool.shape[0], step_pages):
             n = min(step_pages, pool.shape[0] - p0)
-            pool[p0 : p0 + n] = (0.5 * torch.randn((n,) + tuple(pool.shape[1:]), generator=gen, device=device)).half()
+            pool[p0 : p0 + n] = (0.5 * torch.randn((n,) + tuple(pool.shape[1:]), generator=gen, device=device)).to(tdtype)
     # a scattered page table: sequences do not own contiguous runs of pages
     perm = torch.randperm(cache.num_pages, generator=torch.Generator().manual_seed(99 + rank)).to(torch.int32)
     cache.block_table = perm.reshape(B, cache.max_blocks).contiguous().to(device)
@@ -285,18 +287,18 @@ def run_ours(args):
         cache.seq_lens.copy_(torch.from_numpy(lens.astype(np.int32)))
         cache._host_len_bound = int(lens.max())
 
-    q = torch.randn((B, HQ, D), generator=gen, device=device).half()
-    k_new = (0.5 * torch.randn((B, HKV, D), generator=gen, device=device)).half()
-    v_new = (0.5 * torch.randn((B, HKV, D), generator=gen, device=device)).half()
+    q = torch.randn((B, HQ, D), generator=gen, device=device).to(tdtype)
+    k_new = (0.5 * torch.randn((B, HKV, D), generator=gen, device=device)).to(tdtype)
+    v_new = (0.5 * torch.randn((B, HKV, D), generator=gen, device=device)).to(tdtype)
     out = torch.empty_like(q)
-    ops.workspace(device, ops.gqa_workspace_bytes(B, HQ, HKV, D, capacity))
+    ops.workspace(device, ops.gqa_workspace_bytes(B, HQ, HKV, D, capacity, tdtype))
 
     def step(qt):
         cache.append_rope(0, qt, k_new, v_new, theta=1e6)
         cache.attend(0, qt, out=out)
 
     def bytes_of_steps(first: int, count: int) -> float:
-        return sum(algo_bytes(lens + first + s + 1) for s in range(count))
+        return sum(algo_bytes(lens + first + s + 1, elem) for s in range(count))
 
     sampler = ClockSampler(local_rank)
 
@@ -307,11 +309,13 @@ def run_ours(args):
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     sampler.start()
+    torch.cuda.profiler.start()  # lets `ncu --profile-from-start off` see only the timed steps
     ev0.record()
     for _ in range(args.steps):
         step(q)
     ev1.record()
     barrier()
+    torch.cuda.profiler.stop()
     sampler.pause()
     dev_ms = max_over_ranks(ev0.elapsed_time(ev1))
     my_bytes = bytes_of_steps(args.warmup, args.steps)
@@ -334,10 +338,10 @@ def run_ours(args):
     lib.axb200_profile_collect(ctypes.byref(ms_total), ctypes.byref(launches))
     lib.axb200_profile_enable(0)
     kern_ms = ms_total.value / max(launches.value, 1)
-    launch_bytes = algo_bytes(lens)
+    launch_bytes = algo_bytes(lens, elem)
     achieved = launch_bytes / (kern_ms / 1e3) / 1e9
     peak, peak_kind = measured_peak()
-    roofline = {"bound": "hbm", "kernel": "gqa_split_f16_kernel<paged>", "achieved": achieved, "peak": peak,
+    roofline = {"bound": "hbm", "kernel": f"gqa_split_{args.dtype}_kernel<paged>", "achieved": achieved, "peak": peak,
                 "unit": "GB/s", "frac": achieved / peak, "peak_source": f"of {peak_kind}",
                 "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS, "kernel_ms": kern_ms,
                 "launches_timed": launches.value, "algorithmic_bytes_per_launch": launch_bytes,
@@ -349,8 +353,8 @@ def run_ours(args):
     q_h, k_h, v_h = pin(q), pin(k_new), pin(v_new)
     out_h = torch.empty_like(q_h).pin_memory()
     q_d, k_d, v_d = torch.empty_like(q), torch.empty_like(k_new), torch.empty_like(v_new)
-    h2d = (q_h.numel() + k_h.numel() + v_h.numel()) * 2
-    d2h = out_h.numel() * 2
+    h2d = (q_h.numel() + k_h.numel() + v_h.numel()) * elem
+    d2h = out_h.numel() * elem
 
     def e2e_step():
         q_d.copy_(q_h, non_blocking=True)
@@ -370,7 +374,7 @@ def run_ours(args):
         e2e_step()
     barrier()
     e2e_s = max_over_ranks(time.perf_counter() - t0)
-    e2e_bytes = sum_over_ranks(sum(algo_bytes(lens + base + s + 1) for s in range(args.steps)))
+    e2e_bytes = sum_over_ranks(sum(algo_bytes(lens + base + s + 1, elem) for s in range(args.steps)))
     e2e = {"value": e2e_bytes / e2e_s / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
            "ms_per_step": e2e_s / args.steps * 1e3, "tokens_per_s": total_seqs * args.steps / e2e_s}
 
@@ -378,7 +382,7 @@ def run_ours(args):
 
     # ---- the other single-GPU case of the same kernel, for the record ----
     extra = {}
-    if world == 1 and args.workload == "c3_ragged" and not args.no_extra:
+    if world == 1 and args.workload == "c3_ragged" and not args.no_extra and args.dtype == "f16":
         lens32 = np.full(B, 32768, np.int64)
         cache.seq_lens.copy_(torch.from_numpy(lens32.astype(np.int32)))
         cache._host_len_bound = 32768
@@ -404,7 +408,7 @@ def run_ours(args):
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True,
-            "scaling": args.scaling, "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "scaling": args.scaling, "vs_baseline": None, "dtype": args.dtype, "data": "synthetic",
             "config": {"workload": args.workload, "batch_per_gpu": w["batch"] if args.scaling == "weak" else None,
                        "global_batch": int(total_seqs), "hq": HQ, "hkv": HKV, "head_dim": D,
                        "kv_len": [int(w["lo"]), int(w["hi"])], "page_tokens": PAGE_TOKENS,
@@ -520,11 +524,13 @@ def run_tower(args):
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     sampler.start()
+    torch.cuda.profiler.start()  # lets `ncu --profile-from-start off` see only the timed steps
     ev0.record()
     for _ in range(args.steps):
         g.replay_async()
     ev1.record()
     barrier()
+    torch.cuda.profiler.stop()
     sampler.pause()
     ms = sharding.max_over_ranks(ev0.elapsed_time(ev1))
     err = ops.last_error()
@@ -574,6 +580,7 @@ def main():
     ap.add_argument("--workload", default="c3_ragged", choices=sorted(WORKLOADS) + ["c2_block", "c5_tower"])
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="weak: every GPU gets its own batch; strong: one batch sharded over the GPUs")
+    ap.add_argument("--dtype", default="f16", choices=["f16", "f32"], help="storage type of q/K/V (fp32 accumulation either way)")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="c5_tower on >1 GPU: fused = attention kernel writes into peers' buffers; nccl = library all-gather")
     ap.add_argument("--cpu-budget", type=float, default=10.0, help="seconds of CPU work for cpu_baseline")
