@@ -571,12 +571,63 @@ def run_tower(args):
         dist.destroy_process_group()
 
 
+def run_reference_cuda(args):
+    """`--impl reference-cuda`: the reference's own CUDA kernels, compiled for sm_100, timed on this GPU
+    next to this package's kernel on the same inputs - the reference's op is fp32 and takes one
+    sequence, so the comparison is single-sequence fp32 in the reference's layout."""
+    import torch
+
+    import oracle
+    from axono_b200 import _capi
+
+    if not oracle.have_reference_cuda():
+        print(json.dumps({"impl": "reference-cuda", "unavailable": "oracle/_ref/libaxono_ref_cuda.so is not built"}))
+        return
+    ref = oracle.reference_cuda()
+    lib = _capi.lib()
+    rows = []
+    for skv in (4096, 8192, 32768):
+        rng = np.random.default_rng(5000 + skv)
+        q = rng.standard_normal((1, HQ, D)).astype(np.float32)
+        k = (0.5 * rng.standard_normal((skv, HKV, D))).astype(np.float32)
+        v = (0.5 * rng.standard_normal((skv, HKV, D))).astype(np.float32)
+        want, ref_ms = ref.gqa_decode(q, k, v, iters=args.steps)
+        qd, kd, vd = (torch.from_numpy(a).cuda() for a in (q, k, v))
+        out = torch.empty_like(qd)
+        ws = torch.empty(max(lib.axb200_gqa_workspace_bytes(1, HQ, HKV, D, skv, _capi.FLOAT32), 256), dtype=torch.uint8,
+                         device="cuda")
+        st = torch.cuda.current_stream().cuda_stream
+
+        def call():
+            return lib.axb200_gqa_decode(qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), out.data_ptr(), HQ, HKV, D, skv,
+                                         _capi.FLOAT32, ws.data_ptr(), ws.numel(), st)
+
+        for _ in range(max(3, args.warmup)):
+            call()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(args.steps):
+            call()
+        e1.record()
+        torch.cuda.synchronize()
+        ours_ms = e0.elapsed_time(e1) / args.steps
+        nbytes = algo_bytes(np.asarray([skv]), 4)
+        err = oracle.rel_err(out.cpu().numpy(), want)
+        rows.append({"skv": skv, "reference_ms": ref_ms, "ours_ms": ours_ms, "reference_gbs": nbytes / ref_ms / 1e6,
+                     "ours_gbs": nbytes / ours_ms / 1e6, "speedup": ref_ms / ours_ms, "rel_err": err})
+    print(json.dumps({"impl": "reference-cuda", "metric": METRIC, "unit": UNIT, "dtype": "f32",
+                      "config": {"workload": "single sequence, 16 q / 8 kv heads, head_dim 128, reference layout",
+                                 "note": "KV of one short sequence fits in L2 after the first call"},
+                      "steps": args.steps, "cases": rows}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-cuda"])
     ap.add_argument("--workload", default="c3_ragged", choices=sorted(WORKLOADS) + ["c2_block", "c5_tower"])
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="weak: every GPU gets its own batch; strong: one batch sharded over the GPUs")
@@ -587,7 +638,10 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-extra", action="store_true")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.impl == "reference-cuda":
+        if int(os.environ.get("RANK", "0")) == 0:
+            run_reference_cuda(args)
+    elif args.impl == "reference":
         if args.workload in ("c2_block", "c5_tower"):
             args.workload = "c2_b8_l8k" if args.workload == "c2_block" else "c3_ragged"
         run_reference_arm(args)

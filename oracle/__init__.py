@@ -21,6 +21,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 PORT_LIB = os.path.join(_HERE, "_build", "libaxono_oracle.so")
 REF_LIB = os.path.join(_HERE, "_ref", "libaxono_ref_cpu.so")
+REF_CUDA_LIB = os.path.join(_HERE, "_ref", "libaxono_ref_cuda.so")
 
 _sz = C.c_size_t
 _f32p = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
@@ -35,6 +36,7 @@ def build(ref_root: str = "/root/reference") -> None:
     subprocess.check_call(["make", "-s", "-C", _HERE, "oracle"])
     if os.path.isdir(os.path.join(ref_root, "src")):
         subprocess.check_call(["make", "-s", "-C", _HERE, "ref", f"REF={ref_root}"])
+        subprocess.check_call(["make", "-s", "-C", _HERE, "refcuda", f"REF={ref_root}"])
 
 
 def _f32(a):
@@ -260,8 +262,77 @@ class _Reference(_Checker):
         return _run, out, _release
 
 
+class _ReferenceCuda:
+    """The reference's own CUDA operators (fp32), compiled for sm_100: host arrays in and out, with
+    an optional timed loop (`iters` calls between CUDA events; returns milliseconds per call)."""
+
+    kind = "reference-cuda"
+
+    def __init__(self, path):
+        self.lib = C.CDLL(path)
+        self._ms = C.c_double(0.0)
+
+    def _run(self, name, argtypes, *args, iters=0):
+        fn = getattr(self.lib, "refcu_" + name)
+        fn.argtypes = argtypes + [C.c_int, C.POINTER(C.c_double)]
+        fn.restype = C.c_int
+        self._ms.value = 0.0
+        st = fn(*args, int(iters), C.byref(self._ms))
+        if st != 0:
+            raise RuntimeError(f"reference CUDA {name} failed, status {st}")
+        return self._ms.value
+
+    def gqa_decode(self, q, k, v, iters=0):
+        q, k, v = _f32(q), _f32(k), _f32(v)
+        _, hq, d = q.shape
+        skv, hkv, _ = k.shape
+        out = np.empty_like(q)
+        ms = self._run("gqa_decode_f32", [_f32p, _f32p, _f32p, _f32p, _sz, _sz, _sz, _sz], q, k, v, out, hq, hkv, d,
+                       skv, iters=iters)
+        return out, ms
+
+    def add_rms_norm(self, x, residual, weight, eps=1e-6, iters=0):
+        x, residual, weight = _f32(x), _f32(residual), _f32(weight)
+        hidden = x.shape[-1]
+        y, out = np.empty_like(x), np.empty_like(x)
+        ms = self._run("add_rms_norm_f32", [_f32p, _f32p, _f32p, C.c_float, _f32p, _f32p, _sz, _sz],
+                       x.reshape(-1), residual.reshape(-1), weight, eps, y.reshape(-1), out.reshape(-1),
+                       x.size // hidden, hidden, iters=iters)
+        return y, out, ms
+
+    def silu_mul(self, gate, up, iters=0):
+        gate, up = _f32(gate), _f32(up)
+        out = np.empty_like(gate)
+        ms = self._run("silu_mul_f32", [_f32p, _f32p, _f32p, _sz], gate.reshape(-1), up.reshape(-1), out.reshape(-1),
+                       gate.size, iters=iters)
+        return out, ms
+
+    def rope(self, x, pos, theta, iters=0):
+        x = _f32(x)
+        pos = np.ascontiguousarray(pos, dtype=np.int64).reshape(-1)
+        rows, heads, dim = x.shape
+        out = np.empty_like(x)
+        ms = self._run("rope_f32", [_f32p, _i64p, C.c_float, _f32p, _sz, _sz, _sz], x, pos, theta, out, rows, heads,
+                       dim, iters=iters)
+        return out, ms
+
+
 _port = None
 _reference = None
+_reference_cuda = None
+
+
+def have_reference_cuda() -> bool:
+    return os.path.exists(REF_CUDA_LIB)
+
+
+def reference_cuda() -> _ReferenceCuda:
+    global _reference_cuda
+    if _reference_cuda is None:
+        if not have_reference_cuda():
+            raise FileNotFoundError(f"{REF_CUDA_LIB} is not built (make -C oracle refcuda)")
+        _reference_cuda = _ReferenceCuda(REF_CUDA_LIB)
+    return _reference_cuda
 
 
 def port() -> _Port:
