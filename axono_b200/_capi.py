@@ -35,6 +35,8 @@ SIGNATURES = {
     "axb200_qkv_norm_rope_append": (_i, [_vp, _i64, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i, _i,
                                          _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "axb200_silu_mul_rows": (_i, [_vp, _i64, _i, _i64, _vp, _i, _vp]),
+    "axb200_decode_step_host": (_i, [_vp] * 12 + [_vp, _vp, _f, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i64, _i,
+                                          _vp, _sz, _vp]),
     "axb200_rope": (_i, [_vp, _vp, _f, _vp, _i64, _i, _i, _i, _vp]),
     "axb200_rope_thd": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _i64, _i, _i, _i, _vp]),
     "axb200_rope_with_cos_sin": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i, _i, _vp]),

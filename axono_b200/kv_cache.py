@@ -31,6 +31,21 @@ class KVCache:
             self._host_len_bound += 1
         return q
 
+    def step_host(self, q_host, k_new_host, v_new_host, out_host, theta=10000.0, pos=None, inv_freq=None,
+                  mrope_section=None, layer_idx: int = 0):
+        """One decode step with host activations (pinned CPU tensors): stage in, rope + append, attend,
+        copy the output back and wait - a single C-ABI call.  Returns out_host."""
+        st = getattr(self, "_staging", None)
+        if st is None or st[0].dtype != q_host.dtype or st[0].shape != q_host.shape:
+            mk = lambda t: torch.empty(t.shape, dtype=t.dtype, device=self.device)  # noqa: E731
+            st = (mk(q_host), mk(k_new_host), mk(v_new_host), mk(q_host))
+            self._staging = st
+        self._host_len_bound = min(self.max_seq_len, self._host_len_bound + 1)
+        ops.decode_step_host(q_host, k_new_host, v_new_host, out_host, st, self.k_pages[layer_idx],
+                             self.v_pages[layer_idx], self.block_table, self.seq_lens, self._host_len_bound,
+                             theta=theta, pos=pos, inv_freq=inv_freq, mrope_section=mrope_section)
+        return out_host
+
     def get(self, layer_idx: int):  # pragma: no cover
         raise NotImplementedError
 

@@ -205,6 +205,33 @@ def silu_mul_rows(gate_up, n: int):
     return out
 
 
+def decode_step_host(q_host, k_new_host, v_new_host, out_host, staging, k_pages, v_pages, block_table, seq_lens,
+                     max_seq_len, theta=10000.0, pos=None, inv_freq=None, mrope_section=None, rotate=True):
+    """One decode step whose activations live on the host: q/k_new/v_new/out are CPU tensors (pinned for
+    asynchronous copies), `staging` = (q_dev, k_dev, v_dev, out_dev) device buffers of the same shapes.
+    Copies in, rope + append, paged decode attention, copies out and waits; a single C-ABI call."""
+    op = "decode_step_host"
+    q_dev, k_dev, v_dev, out_dev = staging
+    dt = _dt(q_dev, op)
+    for t in (q_host, k_new_host, v_new_host, out_host):
+        if t.is_cuda or not t.is_contiguous() or t.dtype != q_dev.dtype:
+            _capi.check(1, op)
+    batch, hq, d = q_dev.shape
+    num_pages, hkv, page_tokens, _ = k_pages.shape
+    mrope = mrope_section is not None
+    h_sec, w_sec = (mrope_section[1], mrope_section[2]) if mrope else (0, 0)
+    lib = _capi.lib()
+    ws_bytes = lib.axb200_gqa_workspace_bytes(batch, hq, hkv, d, int(max_seq_len), dt)
+    ws = workspace(q_dev.device, ws_bytes)
+    _call(lib.axb200_decode_step_host(
+        q_host.data_ptr(), k_new_host.data_ptr(), v_new_host.data_ptr(), out_host.data_ptr(), q_dev.data_ptr(),
+        k_dev.data_ptr(), v_dev.data_ptr(), out_dev.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(),
+        block_table.data_ptr(), seq_lens.data_ptr(), _ptr(pos), _ptr(inv_freq), float(theta), int(rotate),
+        int(mrope), h_sec, w_sec, batch, hq, hkv, d, page_tokens, block_table.shape[1], num_pages,
+        int(max_seq_len), dt, ws.data_ptr(), ws.numel(), _stream(q_dev)), op)
+    return out_host
+
+
 def rope(x, pos_ids, theta: float = 10000.0):
     op = "rope"
     dt = _dt(x, op)

@@ -198,6 +198,23 @@ int axb200_qkv_norm_rope_append(const void *qkv, int64_t ld, const void *q_norm_
                                 int page_tokens, int max_blocks, int num_pages,
                                 int dtype, int slot_delta, int advance, void *stream);
 
+/* One decode step with HOST activations: copies q (batch,hq,d), k_new, v_new (batch,hkv,d) from host
+ * (pinned memory for asynchronous copies) into the device staging buffers q_dev / k_new_dev /
+ * v_new_dev, runs axb200_kv_append_rope (slot_delta 0, advance 1) and axb200_gqa_decode_paged, copies
+ * the attention output (batch,hq,d) to out_host and waits for it on `stream`.  This is the step the
+ * reference's host loop performs through its binding each token
+ * (axono/python/examples/vlm/qwen3vl/model.py:738-761), as a single call.  The cache, block table,
+ * lengths, positions and scratch stay device-resident as in the two calls it composes. */
+int axb200_decode_step_host(const void *q_host, const void *k_new_host, const void *v_new_host,
+                            void *out_host, void *q_dev, void *k_new_dev, void *v_new_dev, void *out_dev,
+                            void *k_pages, void *v_pages, const int32_t *block_table, int32_t *seq_lens,
+                            const int64_t *pos, const float *inv_freq, float theta,
+                            int rotate, int mrope, int h_sec, int w_sec,
+                            int batch, int hq, int hkv, int d,
+                            int page_tokens, int max_blocks, int num_pages,
+                            int64_t max_seq_len, int dtype,
+                            void *workspace, size_t workspace_bytes, void *stream);
+
 /* ---- RoPE family (stand-alone ops) --------------------------------------------------------
  * x/out (rows,heads,dim); out may alias x. */
 

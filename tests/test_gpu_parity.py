@@ -408,3 +408,31 @@ def test_concat_bit_exact(ops, golden):
     assert np.array_equal(ops.concat(dev(a), dev(b), -1).cpu().numpy(), np.concatenate([a, b], -1))
     b1 = rng.standard_normal((2, 7, 4)).astype(np.float32)
     assert np.array_equal(ops.concat(dev(a), dev(b1), 1).cpu().numpy(), np.concatenate([a, b1], 1))
+
+
+def test_decode_step_host_matches_separate_calls(ops):
+    """The host-buffer step (one C-ABI call: copy in, rope + append, attend, copy out, wait) gives the
+    same bits as the device-resident calls it composes."""
+    from axono_b200.kv_cache import PagedKVCache
+
+    rng = np.random.default_rng(61)
+    B, hq, hkv, d, L = 4, 16, 8, 128, 3000
+    lens = [L, 1, 64, 2049]
+    k0 = dev((0.5 * rng.standard_normal((B, L, hkv, d))).astype(np.float32), torch.float16)
+    v0 = dev((0.5 * rng.standard_normal((B, L, hkv, d))).astype(np.float32), torch.float16)
+    caches = []
+    for _ in range(2):
+        c = PagedKVCache(1, B, hkv, d, L + 64, dtype=torch.float16)
+        c.fill(0, k0, v0, lens)
+        caches.append(c)
+    host = lambda *s: torch.from_numpy(rng.standard_normal(s).astype(np.float16)).pin_memory()  # noqa: E731
+    for step in range(3):
+        q_h, k_h, v_h = host(B, hq, d), host(B, hkv, d), host(B, hkv, d)
+        out_h = torch.empty_like(q_h).pin_memory()
+        caches[0].step_host(q_h, k_h, v_h, out_h, theta=1e6)
+        qd = q_h.cuda()
+        caches[1].append_rope(0, qd, k_h.cuda(), v_h.cuda(), theta=1e6)
+        want = caches[1].attend(0, qd).cpu()
+        assert torch.equal(out_h, want), f"step {step}"
+    assert torch.equal(caches[0].seq_lens, caches[1].seq_lens)
+    assert ops.last_error() == 0
