@@ -37,6 +37,18 @@ SIGNATURES = {
     "axb200_silu_mul_rows": (_i, [_vp, _i64, _i, _i64, _vp, _i, _vp]),
     "axb200_decode_step_host": (_i, [_vp] * 12 + [_vp, _vp, _f, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i64, _i,
                                           _vp, _sz, _vp]),
+    "axb200_kv_arena_create": (_i, [_i, _i, _i, _i, _i, _i, _i, _i, _i, C.POINTER(_vp)]),
+    "axb200_kv_arena_destroy": (_i, [_vp]),
+    "axb200_kv_arena_alloc_seq": (_i, [_vp, _i64, C.POINTER(_i)]),
+    "axb200_kv_arena_reserve": (_i, [_vp, _i, _i64]),
+    "axb200_kv_arena_free_seq": (_i, [_vp, _i, _vp]),
+    "axb200_kv_arena_sync": (_i, [_vp, _vp]),
+    "axb200_kv_arena_stats": (_i, [_vp, C.POINTER(_i64), C.POINTER(_i64), C.POINTER(_i64), C.POINTER(_i64)]),
+    "axb200_kv_arena_seq_pages": (_i, [_vp, _i, _vp, _i]),
+    "axb200_kv_arena_k_pages": (_vp, [_vp, _i]),
+    "axb200_kv_arena_v_pages": (_vp, [_vp, _i]),
+    "axb200_kv_arena_block_table": (_vp, [_vp]),
+    "axb200_kv_arena_seq_lens": (_vp, [_vp]),
     "axb200_rope": (_i, [_vp, _vp, _f, _vp, _i64, _i, _i, _i, _vp]),
     "axb200_rope_thd": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _i64, _i, _i, _i, _vp]),
     "axb200_rope_with_cos_sin": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i, _i, _vp]),

@@ -8,9 +8,11 @@ growing cache.
 """
 from __future__ import annotations
 
+import ctypes as C
+
 import torch
 
-from . import ops
+from . import _capi, ops
 
 
 class KVCache:
@@ -165,3 +167,96 @@ class PagedKVCache(KVCache):
             t = pool[idx].permute(0, 2, 1, 3).reshape(nb * self.page_tokens, self.n_kv_heads, self.head_dim)
             outs.append(t[:n].contiguous())
         return outs[0], outs[1]
+
+
+class _DeviceView:
+    """__cuda_array_interface__ carrier: lets torch alias device memory the library allocated."""
+
+    def __init__(self, ptr: int, shape, typestr: str):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False),
+                                         "version": 2, "strides": None}
+
+
+class KVArena:
+    """Page allocator of the paged cache (C ABI axb200_kv_arena_*): fixed per-layer pools, a free list
+    of pages, sequence slots that own pages through one shared block table.  `cache()` gives the
+    `PagedKVCache` view the operators run on; `alloc_seq` / `reserve` / `free_seq` manage sequences
+    between steps and `sync()` uploads the changed block-table rows.
+
+    With `device_memory=False` only the host-side bookkeeping exists (usable without a GPU)."""
+
+    def __init__(self, n_layers, num_pages, n_kv_heads, head_dim, max_seqs, max_seq_len, dtype=torch.float16,
+                 page_tokens=64, device_memory=True):
+        self.n_layers, self.num_pages, self.n_kv_heads, self.head_dim = n_layers, num_pages, n_kv_heads, head_dim
+        self.max_seqs, self.page_tokens, self.dtype = max_seqs, page_tokens, dtype
+        self.max_blocks = (max_seq_len + page_tokens - 1) // page_tokens
+        self.device_memory = device_memory
+        code = {torch.float16: _capi.FLOAT16, torch.float32: _capi.FLOAT32}[dtype]
+        h = C.c_void_p()
+        _capi.check(_capi.lib().axb200_kv_arena_create(n_layers, num_pages, n_kv_heads, page_tokens, head_dim, code,
+                                                       max_seqs, self.max_blocks, int(device_memory), C.byref(h)),
+                    "kv_arena_create")
+        self._h = h
+        self._cache = None
+
+    def _stream(self):
+        return torch.cuda.current_stream().cuda_stream if self.device_memory else None
+
+    def alloc_seq(self, reserve_tokens: int = 0) -> int:
+        sid = C.c_int(-1)
+        _capi.check(_capi.lib().axb200_kv_arena_alloc_seq(self._h, int(reserve_tokens), C.byref(sid)), "kv_arena_alloc_seq")
+        return sid.value
+
+    def reserve(self, seq_id: int, tokens: int) -> None:
+        _capi.check(_capi.lib().axb200_kv_arena_reserve(self._h, seq_id, int(tokens)), "kv_arena_reserve")
+
+    def free_seq(self, seq_id: int) -> None:
+        _capi.check(_capi.lib().axb200_kv_arena_free_seq(self._h, seq_id, self._stream()), "kv_arena_free_seq")
+
+    def sync(self) -> None:
+        _capi.check(_capi.lib().axb200_kv_arena_sync(self._h, self._stream()), "kv_arena_sync")
+
+    def stats(self) -> dict:
+        vals = [C.c_int64(0) for _ in range(4)]
+        _capi.check(_capi.lib().axb200_kv_arena_stats(self._h, *[C.byref(v) for v in vals]), "kv_arena_stats")
+        return dict(zip(("pages_total", "pages_free", "seqs_live", "device_bytes"), (v.value for v in vals)))
+
+    def seq_pages(self, seq_id: int):
+        buf = (C.c_int32 * self.max_blocks)()
+        n = _capi.lib().axb200_kv_arena_seq_pages(self._h, seq_id, buf, self.max_blocks)
+        if n < 0:
+            raise RuntimeError("kv_arena_seq_pages: no such live sequence")
+        return list(buf[:n])
+
+    def cache(self) -> "PagedKVCache":
+        """The operator-facing view: a PagedKVCache whose pools, block table and lengths alias the
+        arena's device memory (batch = max_seqs rows)."""
+        if not self.device_memory:
+            raise RuntimeError("KVArena was created without device memory")
+        if self._cache is None:
+            lib = _capi.lib()
+            dev = torch.device("cuda", torch.cuda.current_device())
+            ts = {torch.float16: "<f2", torch.float32: "<f4"}[self.dtype]
+            shape = (self.num_pages, self.n_kv_heads, self.page_tokens, self.head_dim)
+            c = PagedKVCache.__new__(PagedKVCache)
+            c.n_layers, c.batch = self.n_layers, self.max_seqs
+            c.n_kv_heads, c.head_dim, c.page_tokens = self.n_kv_heads, self.head_dim, self.page_tokens
+            c.max_blocks, c.max_seq_len, c.num_pages = self.max_blocks, self.max_blocks * self.page_tokens, self.num_pages
+            c.dtype, c.device = self.dtype, dev
+            c.k_pages = [torch.as_tensor(_DeviceView(lib.axb200_kv_arena_k_pages(self._h, l), shape, ts), device=dev)
+                         for l in range(self.n_layers)]
+            c.v_pages = [torch.as_tensor(_DeviceView(lib.axb200_kv_arena_v_pages(self._h, l), shape, ts), device=dev)
+                         for l in range(self.n_layers)]
+            c.block_table = torch.as_tensor(_DeviceView(lib.axb200_kv_arena_block_table(self._h),
+                                                        (self.max_seqs, self.max_blocks), "<i4"), device=dev)
+            c.seq_lens = torch.as_tensor(_DeviceView(lib.axb200_kv_arena_seq_lens(self._h), (self.max_seqs,), "<i4"),
+                                         device=dev)
+            c._host_len_bound = 0
+            self._cache = c
+        return self._cache
+
+    def close(self) -> None:
+        if self._h:
+            self._cache = None
+            _capi.lib().axb200_kv_arena_destroy(self._h)
+            self._h = None

@@ -16,16 +16,9 @@ import torch
 import torch.distributed as dist
 
 from . import _capi
+from .kv_cache import _DeviceView
 
 _ALIGN = 256
-
-
-class _DeviceView:
-    """Minimal __cuda_array_interface__ carrier so torch can alias memory this library allocated."""
-
-    def __init__(self, ptr: int, shape, typestr: str):
-        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False),
-                                         "version": 2, "strides": None}
 
 
 class PeerGather:

@@ -265,6 +265,38 @@ int axb200_rms_norm(const void *x, const void *weight, float eps, void *out,
 int axb200_concat(const void *a, const void *b, void *out, int64_t outer,
                   size_t a_bytes, size_t b_bytes, void *stream);
 
+/* ---- KV page arena ---------------------------------------------------------------------------------
+ * The allocator side of the paged cache: fixed per-layer K/V pools of pages with a free list, one
+ * block table (max_seqs, max_blocks) and one length vector (max_seqs) shared by all layers.  It
+ * replaces the reference's handling of KV tensors - a fresh, ever larger allocation from the
+ * size-bucketed caching pool on every concat (axono/python/axono/nn/kv_cache.py:96-102,
+ * src/core/cuda/detail.cu:41-146,153-275).  Pools are allocated and zero-filled once, keep their
+ * addresses (graph replay), are never evicted and never re-zeroed on reuse.  A sequence slot is the
+ * batch row the decode kernels see: pass batch = max_seqs; rows not in use have length 0.
+ * Host-side and thread-safe; with device_memory == 0 only the bookkeeping exists (no CUDA calls).
+ * These are set-up / between-step calls: create and destroy allocate and synchronise. */
+typedef struct axb200_kv_arena axb200_kv_arena;
+int axb200_kv_arena_create(int n_layers, int num_pages, int hkv, int page_tokens, int d, int dtype,
+                           int max_seqs, int max_blocks, int device_memory, axb200_kv_arena **out);
+int axb200_kv_arena_destroy(axb200_kv_arena *arena);
+/* Takes the lowest free sequence slot and pages for reserve_tokens; OUT_OF_MEMORY when slots or
+ * pages run out (nothing is taken then). */
+int axb200_kv_arena_alloc_seq(axb200_kv_arena *arena, int64_t reserve_tokens, int *seq_id);
+/* Grows the sequence to hold `tokens` tokens in total (all or nothing). */
+int axb200_kv_arena_reserve(axb200_kv_arena *arena, int seq_id, int64_t tokens);
+/* Returns the pages to the free list and zeroes the device-side length on `stream`. */
+int axb200_kv_arena_free_seq(axb200_kv_arena *arena, int seq_id, void *stream);
+/* Uploads the block-table rows changed since the last sync (one H2D copy on `stream`). */
+int axb200_kv_arena_sync(axb200_kv_arena *arena, void *stream);
+int axb200_kv_arena_stats(axb200_kv_arena *arena, int64_t *pages_total, int64_t *pages_free,
+                          int64_t *seqs_live, int64_t *device_bytes);
+/* Copies the sequence's page ids (host view) into pages_out; returns how many it holds, -1 on error. */
+int axb200_kv_arena_seq_pages(axb200_kv_arena *arena, int seq_id, int32_t *pages_out, int capacity);
+void *axb200_kv_arena_k_pages(axb200_kv_arena *arena, int layer);
+void *axb200_kv_arena_v_pages(axb200_kv_arena *arena, int layer);
+int32_t *axb200_kv_arena_block_table(axb200_kv_arena *arena);
+int32_t *axb200_kv_arena_seq_lens(axb200_kv_arena *arena);
+
 #ifdef __cplusplus
 }
 #endif
