@@ -24,6 +24,8 @@ SIGNATURES = {
     "axb200_gqa_decode_static": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i, _vp]),
     "axb200_gqa_decode_paged": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i64, _i,
                                      _vp, _sz, _vp]),
+    "axb200_gqa_decode_paged_window": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i64, _i, _i,
+                                            _vp, _sz, _vp]),
     "axb200_gqa_decode_paged_gather": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i64, _i, _vp, _sz,
                                             _vp, _vp, _vp, _i, _i, _i, _vp]),
     "axb200_p2p_alloc": (_i, [_sz, C.POINTER(_vp), _vp]),
@@ -56,6 +58,8 @@ SIGNATURES = {
     "axb200_add_rms_norm": (_i, [_vp, _vp, _vp, _f, _vp, _vp, _i64, _i, _i, _vp]),
     "axb200_silu_mul": (_i, [_vp, _vp, _vp, _i64, _i, _vp]),
     "axb200_rms_norm": (_i, [_vp, _vp, _f, _vp, _i64, _i, _i, _vp]),
+    "axb200_embedding": (_i, [_vp, _i, _vp, _vp, _i64, _i64, _i, _i, _vp]),
+    "axb200_argmax_last_dim": (_i, [_vp, _vp, _i64, _i, _i, _vp]),
     "axb200_concat": (_i, [_vp, _vp, _vp, _i64, _sz, _sz, _vp]),
 }
 

@@ -241,6 +241,64 @@ silu_mul_rows_kernel(const T *in, long long ld, int n, long long rows, T *out, b
   }
 }
 
+// ---- embedding gather and argmax over the last dim (the ends of a decode step) -----------------
+// Replaces the reference's EmbeddingKernel and ArgmaxKernel (src/ops/cuda/sequence.cu:75-81,262-292).
+// Embedding: one CTA per id, 16-byte copies of the table row; an id outside [0, vocab) sets
+// AXB200_ERR_BAD_INDEX and yields a zero row.
+template <typename IdT>
+__global__ void __launch_bounds__(256)
+embedding_kernel(const IdT *ids, const uint8_t *table, uint8_t *out, long long vocab, size_t row_bytes,
+                 bool vec) {
+  const long long id = (long long)ids[blockIdx.x];
+  const bool ok = id >= 0 && id < vocab;
+  if (!ok && threadIdx.x == 0) atomicOr(&g_error_word, AXB200_ERR_BAD_INDEX);
+  const uint8_t *src = table + (size_t)(ok ? id : 0) * row_bytes;
+  uint8_t *dst = out + (size_t)blockIdx.x * row_bytes;
+  if (vec) {
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    for (size_t i = threadIdx.x; i < row_bytes / 16; i += blockDim.x)
+      reinterpret_cast<uint4 *>(dst)[i] = ok ? reinterpret_cast<const uint4 *>(src)[i] : zero;
+  } else {
+    for (size_t i = threadIdx.x; i < row_bytes; i += blockDim.x) dst[i] = ok ? src[i] : 0;
+  }
+}
+
+// Argmax with the reference's CPU rule (src/ops/cpu/sequence.cpp:370-400): best = 0, then
+// `if (row[c] > row[best]) best = c` left to right, i.e. the lowest index among equal maxima and a
+// NaN at index 0 is never displaced.  One CTA per row.
+struct ArgBest {
+  float v;
+  int i;
+};
+__device__ __forceinline__ ArgBest arg_better(ArgBest a, ArgBest b) {
+  return (b.v > a.v || (b.v == a.v && b.i < a.i)) ? b : a;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(1024)
+argmax_kernel(const T *x, int64_t *out, int cols) {
+  __shared__ ArgBest s_best[32];
+  const T *row = x + (size_t)blockIdx.x * cols;
+  ArgBest best{-INFINITY, 0x7fffffff};
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    const float v = ldf(row + c);
+    if (v > best.v || (v == best.v && c < best.i)) best = ArgBest{v, c};  // NaN never wins
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    ArgBest o{__shfl_xor_sync(0xffffffffu, best.v, off), __shfl_xor_sync(0xffffffffu, best.i, off)};
+    best = arg_better(best, o);
+  }
+  if ((threadIdx.x & 31) == 0) s_best[threadIdx.x >> 5] = best;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w) best = arg_better(best, s_best[w]);
+    const float first = ldf(row);
+    // row[0] NaN: nothing compares greater; every value -inf or NaN: index 0 stays
+    out[blockIdx.x] = (first != first || best.i == 0x7fffffff) ? 0 : best.i;
+  }
+}
+
 // ---- concat (bytes) -----------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 concat_bytes_kernel(const uint8_t *a, const uint8_t *b, uint8_t *out, int64_t outer, size_t a_bytes,
@@ -362,6 +420,40 @@ int axb200_silu_mul_rows(const void *gate_up, int64_t ld, int n, int64_t rows, v
     axb::silu_mul_rows_kernel<__half><<<axb::blocks_for(rows * n / (vec ? 8 : 1), 256), 256, 0, st>>>(
         static_cast<const __half *>(gate_up), ld, n, rows, static_cast<__half *>(out), vec);
   }
+  return axb::launch_status();
+}
+
+int axb200_embedding(const void *ids, int ids_dtype, const void *table, void *out, int64_t n,
+                     int64_t vocab, int hidden, int dtype, void *stream) {
+  const size_t es = axb::dtype_size(dtype);
+  if (es == 0 || (ids_dtype != AXB200_INT32 && ids_dtype != AXB200_INT64)) return AXB200_UNSUPPORTED_TYPE;
+  if (!ids || !table || !out) return AXB200_INVALID_PTR;
+  if (n < 0 || vocab <= 0 || hidden <= 0 || n > 0x7fffffff) return AXB200_INVALID_ARGUMENT;
+  if (n == 0) return AXB200_OK;
+  const size_t row_bytes = (size_t)hidden * es;
+  const bool vec = row_bytes % 16 == 0 && axb::al16(table) && axb::al16(out);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (ids_dtype == AXB200_INT64)
+    axb::embedding_kernel<int64_t><<<(unsigned)n, 256, 0, st>>>(
+        static_cast<const int64_t *>(ids), static_cast<const uint8_t *>(table), static_cast<uint8_t *>(out), vocab,
+        row_bytes, vec);
+  else
+    axb::embedding_kernel<int32_t><<<(unsigned)n, 256, 0, st>>>(
+        static_cast<const int32_t *>(ids), static_cast<const uint8_t *>(table), static_cast<uint8_t *>(out), vocab,
+        row_bytes, vec);
+  return axb::launch_status();
+}
+
+int axb200_argmax_last_dim(const void *x, int64_t *out, int64_t rows, int cols, int dtype, void *stream) {
+  if (dtype != AXB200_FLOAT32 && dtype != AXB200_FLOAT16) return AXB200_UNSUPPORTED_TYPE;
+  if (!x || !out) return AXB200_INVALID_PTR;
+  if (rows < 0 || cols <= 0 || rows > 0x7fffffff) return AXB200_INVALID_ARGUMENT;
+  if (rows == 0) return AXB200_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == AXB200_FLOAT32)
+    axb::argmax_kernel<float><<<(unsigned)rows, cols >= 8192 ? 1024 : 256, 0, st>>>(static_cast<const float *>(x), out, cols);
+  else
+    axb::argmax_kernel<__half><<<(unsigned)rows, cols >= 8192 ? 1024 : 256, 0, st>>>(static_cast<const __half *>(x), out, cols);
   return axb::launch_status();
 }
 

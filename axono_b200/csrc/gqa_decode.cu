@@ -61,10 +61,16 @@ struct DecodeParams {
   int chunk_tokens, max_chunks;
   float scale;  // 1/sqrt(d)
   int write_final;  // max_chunks == 1: normalise and write `out` directly
+  int window;       // > 0: only the last `window` tokens of each sequence are visible (sliding window)
 };
 
 __device__ __forceinline__ int seq_len_of(const DecodeParams &p, int b) {
   return p.seq_lens ? p.seq_lens[b] : p.fixed_len;
+}
+
+// First visible token of a sequence of length L: 0, or L - window under a sliding window.
+__device__ __forceinline__ int first_visible(const DecodeParams &p, int L) {
+  return (p.window > 0 && L > p.window) ? L - p.window : 0;
 }
 
 // ---- producer ---------------------------------------------------------------------------
@@ -189,9 +195,12 @@ gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
 
   const int chunk = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
   const int L = seq_len_of(p, b);
-  const int start = chunk * p.chunk_tokens;
+  const int first = first_visible(p, L);
+  int start = chunk * p.chunk_tokens;
   if (start >= L) return;
   const int end = min(L, start + p.chunk_tokens);
+  if (end <= first) return;  // the whole chunk lies before the window
+  if (start < first) start = first / kTileTokensF16 * kTileTokensF16;  // skip whole tiles before it
   const int ntiles = (end - start + kTileTokensF16 - 1) / kTileTokensF16;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -274,12 +283,14 @@ gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
     // mask the tokens past the end of the sequence (last tile only)
     const int tile_tok = start + i * kTileTokensF16 + warp * 16;  // this warp's first token
     const int valid = end - tile_tok;                              // tokens of the warp that exist
-    if (valid < 16) {
+    const int lo = first - tile_tok;                               // tokens below lo precede the window
+    const bool edge = valid < 16 || lo > 0;
+    if (edge) {
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
         const int t0 = j * 8 + tq * 2;
-        if (t0 >= valid) sc[j][0] = sc[j][2] = -INFINITY;
-        if (t0 + 1 >= valid) sc[j][1] = sc[j][3] = -INFINITY;
+        if (t0 >= valid || t0 < lo) sc[j][0] = sc[j][2] = -INFINITY;
+        if (t0 + 1 >= valid || t0 + 1 < lo) sc[j][1] = sc[j][3] = -INFINITY;
       }
     }
 
@@ -327,13 +338,13 @@ gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
     for (int np = 0; np < 8; ++np) {
       uint32_t b0, b1, b2, b3;
       ldmatrix_x4_trans(b0, b1, b2, b3, vbase + swz_off(v_row, np * 2 + v_c16));
-      if (valid < 16) {
-        // rows past the end may hold stale bytes: zero them so 0 * NaN cannot appear.
+      if (edge) {
+        // rows outside [lo, valid) may hold stale bytes: zero them so 0 * NaN cannot appear.
         // b0/b2 hold tokens 2tq,2tq+1; b1/b3 hold tokens 8+2tq, 8+2tq+1.
         const int t0 = tq * 2;
-        const uint32_t keep_lo = (t0 < valid ? 0x0000ffffu : 0u) | (t0 + 1 < valid ? 0xffff0000u : 0u);
-        const uint32_t keep_hi =
-            (t0 + 8 < valid ? 0x0000ffffu : 0u) | (t0 + 9 < valid ? 0xffff0000u : 0u);
+        auto in = [&](int t) { return t < valid && t >= lo; };
+        const uint32_t keep_lo = (in(t0) ? 0x0000ffffu : 0u) | (in(t0 + 1) ? 0xffff0000u : 0u);
+        const uint32_t keep_hi = (in(t0 + 8) ? 0x0000ffffu : 0u) | (in(t0 + 9) ? 0xffff0000u : 0u);
         b0 &= keep_lo;
         b2 &= keep_lo;
         b1 &= keep_hi;
@@ -394,9 +405,12 @@ gqa_split_f32_kernel(const __grid_constant__ CUtensorMap tmK,
 
   const int chunk = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
   const int L = seq_len_of(p, b);
-  const int start = chunk * p.chunk_tokens;
+  const int first = first_visible(p, L);
+  int start = chunk * p.chunk_tokens;
   if (start >= L) return;
   const int end = min(L, start + p.chunk_tokens);
+  if (end <= first) return;  // the whole chunk lies before the window
+  if (start < first) start = first / kTileTokensF32 * kTileTokensF32;  // skip whole tiles before it
   const int ntiles = (end - start + kTileTokensF32 - 1) / kTileTokensF32;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -446,6 +460,7 @@ gqa_split_f32_kernel(const __grid_constant__ CUtensorMap tmK,
     const float *Ks = reinterpret_cast<const float *>(smem + (size_t)s * kStageBytes);
     const float *Vs = Ks + kTileTokensF32 * kHeadDim;
     const int valid = end - (start + i * kTileTokensF32 + warp * 8);  // tokens of this warp that exist
+    const int lo = first - (start + i * kTileTokensF32 + warp * 8);   // tokens below lo precede the window
 
     float sc[kGroup][8];
 #pragma unroll
@@ -470,7 +485,7 @@ gqa_split_f32_kernel(const __grid_constant__ CUtensorMap tmK,
         a += __shfl_xor_sync(0xffffffffu, a, 4);
         a += __shfl_xor_sync(0xffffffffu, a, 2);
         a += __shfl_xor_sync(0xffffffffu, a, 1);
-        sc[r][t] = (t < valid) ? a : -INFINITY;
+        sc[r][t] = (t < valid && t >= lo) ? a : -INFINITY;
       }
     }
 #pragma unroll
@@ -497,7 +512,7 @@ gqa_split_f32_kernel(const __grid_constant__ CUtensorMap tmK,
 #pragma unroll
     for (int t = 0; t < 8; ++t) {
       float4 vv = *reinterpret_cast<const float4 *>(Vs + (warp * 8 + t) * kHeadDim + lane * 4);
-      if (t >= valid) vv = make_float4(0.f, 0.f, 0.f, 0.f);  // stale rows past the end
+      if (t >= valid || t < lo) vv = make_float4(0.f, 0.f, 0.f, 0.f);  // stale rows outside the range
 #pragma unroll
       for (int r = 0; r < kGroup; ++r) {
         o[r].x = fmaf(sc[r][t], vv.x, o[r].x);
@@ -544,9 +559,12 @@ gqa_split_generic_kernel(const T *k, const T *v, const DecodeParams p, int d) {
   __shared__ float sM[kConsumerWarps], sL[kConsumerWarps];
   const int chunk = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
   const int L = seq_len_of(p, b);
-  const int start = chunk * p.chunk_tokens;
+  const int first = first_visible(p, L);
+  int start = chunk * p.chunk_tokens;
   if (start >= L) return;
   const int end = min(L, start + p.chunk_tokens);
+  if (end <= first) return;
+  if (start < first) start = first;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const T *qp = reinterpret_cast<const T *>(p.q);
   const float dom = p.scale * kLog2e;
@@ -629,13 +647,14 @@ gqa_split_generic_kernel(const T *k, const T *v, const DecodeParams p, int d) {
   }
 }
 
-// Merge weights of a (sequence, head)'s chunk partials, computed once by the CTA: w_c =
-// 2^((m_c - M) * dom) / sum_c l_c 2^((m_c - M) * dom), left in s_w[0..n).  n <= kMaxChunks.
-__device__ __forceinline__ void combine_weights(const float *part_ml, size_t base, int n, float dom,
-                                                float *s_w, float *s_red) {
+// Merge weights of a (sequence, head)'s chunk partials c0..n-1 (chunks before c0 lie wholly before a
+// sliding window and were never written), computed once by the CTA: w_c = 2^((m_c - M) * dom) /
+// sum_c l_c 2^((m_c - M) * dom), left in s_w[c0..n).  n <= kMaxChunks.
+__device__ __forceinline__ void combine_weights(const float *part_ml, size_t base, int c0, int n,
+                                                float dom, float *s_w, float *s_red) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   float m_loc = -INFINITY;
-  for (int c = threadIdx.x; c < n; c += blockDim.x) m_loc = fmaxf(m_loc, part_ml[(base + c) * 2]);
+  for (int c = c0 + threadIdx.x; c < n; c += blockDim.x) m_loc = fmaxf(m_loc, part_ml[(base + c) * 2]);
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) m_loc = fmaxf(m_loc, __shfl_xor_sync(0xffffffffu, m_loc, off));
   if (lane == 0) s_red[warp] = m_loc;
@@ -644,7 +663,7 @@ __device__ __forceinline__ void combine_weights(const float *part_ml, size_t bas
   for (int w = 1; w < nwarps; ++w) M = fmaxf(M, s_red[w]);
   __syncthreads();
   float l_loc = 0.f;
-  for (int c = threadIdx.x; c < n; c += blockDim.x) {
+  for (int c = c0 + threadIdx.x; c < n; c += blockDim.x) {
     const float w = exp2f((part_ml[(base + c) * 2] - M) * dom);
     s_w[c] = w;
     l_loc = fmaf(part_ml[(base + c) * 2 + 1], w, l_loc);
@@ -656,7 +675,7 @@ __device__ __forceinline__ void combine_weights(const float *part_ml, size_t bas
   float Lsum = 0.f;
   for (int w = 0; w < nwarps; ++w) Lsum += s_red[w];
   const float inv = 1.0f / Lsum;
-  for (int c = threadIdx.x; c < n; c += blockDim.x) s_w[c] *= inv;
+  for (int c = c0 + threadIdx.x; c < n; c += blockDim.x) s_w[c] *= inv;
   __syncthreads();
 }
 
@@ -677,10 +696,11 @@ gqa_combine_kernel(const DecodeParams p, int d, float dom) {
     return;
   }
   __shared__ float s_w[kMaxChunks], s_red[4];
-  combine_weights(p.part_ml, base, n, dom, s_w, s_red);
+  const int cf = first_visible(p, L) / p.chunk_tokens;  // first chunk that holds visible tokens
+  combine_weights(p.part_ml, base, cf, n, dom, s_w, s_red);
   for (int c0 = threadIdx.x; c0 < d; c0 += blockDim.x) {
     float acc = 0.f;
-    for (int c = 0; c < n; ++c) acc = fmaf(s_w[c], p.part_o[(base + c) * d + c0], acc);
+    for (int c = cf; c < n; ++c) acc = fmaf(s_w[c], p.part_o[(base + c) * d + c0], acc);
     out[c0] = static_cast<OutT>(acc);
   }
 }
@@ -722,10 +742,11 @@ gqa_combine_gather_kernel(const DecodeParams p, const GatherParams g, int d, flo
   const size_t base = ((size_t)b * p.hq + h) * p.max_chunks;
   const size_t row = ((size_t)b * g.hq_total + (size_t)g.rank * p.hq + h) * d;
   __shared__ float s_w[kMaxChunks], s_red[4];
-  if (n > 0) combine_weights(p.part_ml, base, n, dom, s_w, s_red);
+  const int cf = first_visible(p, L) / p.chunk_tokens;  // first chunk that holds visible tokens
+  if (n > 0) combine_weights(p.part_ml, base, cf, n, dom, s_w, s_red);
   for (int c0 = threadIdx.x; c0 < d; c0 += blockDim.x) {
     float acc = 0.f;
-    for (int c = 0; c < n; ++c) acc = fmaf(s_w[c], p.part_o[(base + c) * d + c0], acc);
+    for (int c = cf; c < n; ++c) acc = fmaf(s_w[c], p.part_o[(base + c) * d + c0], acc);
     const OutT val = static_cast<OutT>(acc);
     for (int r = 0; r < g.world; ++r) reinterpret_cast<OutT *>(g.peer_out[r])[row + c0] = val;
   }
@@ -941,7 +962,7 @@ int decode_impl(bool paged, const void *q, void *out, const void *k, const void 
                 const int32_t *block_table, const int32_t *seq_lens, int fixed_len, int batch,
                 int hq, int hkv, int d, int page_tokens, int max_blocks, int num_pages,
                 int64_t max_len, int dtype, void *workspace, size_t workspace_bytes,
-                cudaStream_t st, const GatherParams *gather = nullptr) {
+                cudaStream_t st, const GatherParams *gather = nullptr, int window = 0) {
   if (dtype != AXB200_FLOAT16 && dtype != AXB200_FLOAT32) return AXB200_UNSUPPORTED_TYPE;
   if (!q || (!out && !gather) || !k || !v) return AXB200_INVALID_PTR;
   if (batch <= 0 || hq <= 0 || hkv <= 0 || d <= 0 || max_len <= 0) return AXB200_INVALID_ARGUMENT;
@@ -970,6 +991,8 @@ int decode_impl(bool paged, const void *q, void *out, const void *k, const void 
   p.chunk_tokens = pl.chunk_tokens;
   p.max_chunks = pl.max_chunks;
   p.scale = 1.0f / sqrtf((float)d);
+  if (window < 0) return AXB200_INVALID_ARGUMENT;
+  p.window = window;
   p.write_final = pl.max_chunks == 1 && !gather;  // the gather epilogue lives in the combine kernel
   if (!p.write_final) {
     if (!workspace || workspace_bytes < pl.part_o_bytes + pl.part_ml_bytes)
@@ -1102,6 +1125,17 @@ int axb200_gqa_decode_paged_gather(const void *q, const void *k_pages, const voi
   return axb::decode_impl(true, q, nullptr, k_pages, v_pages, block_table, seq_lens, 0, batch, hq,
                           hkv, d, page_tokens, max_blocks, num_pages, max_seq_len, dtype, workspace,
                           workspace_bytes, static_cast<cudaStream_t>(stream), &g);
+}
+
+int axb200_gqa_decode_paged_window(const void *q, void *out, const void *k_pages,
+                                   const void *v_pages, const int32_t *block_table,
+                                   const int32_t *seq_lens, int batch, int hq, int hkv, int d,
+                                   int page_tokens, int max_blocks, int num_pages,
+                                   int64_t max_seq_len, int window, int dtype, void *workspace,
+                                   size_t workspace_bytes, void *stream) {
+  return axb::decode_impl(true, q, out, k_pages, v_pages, block_table, seq_lens, 0, batch, hq, hkv,
+                          d, page_tokens, max_blocks, num_pages, max_seq_len, dtype, workspace,
+                          workspace_bytes, static_cast<cudaStream_t>(stream), nullptr, window);
 }
 
 int axb200_p2p_alloc(size_t bytes, void **dev_ptr, void *handle64) {

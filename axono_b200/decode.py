@@ -143,7 +143,7 @@ class TextTower:
         """One token for every row: reads `token_ids` / `pos3`, appends to every layer's cache, writes
         the greedy next token back into `token_ids`, advances `pos3`, and returns the next ids."""
         cfg = self.cfg
-        h = torch.nn.functional.embedding(self.token_ids, self.embed)
+        h = ops.embedding(self.token_ids, self.embed)
         mlp_out: Optional[torch.Tensor] = None
         for li, lw in enumerate(self.layers):
             if mlp_out is None:
@@ -161,7 +161,7 @@ class TextTower:
         _, xf = ops.add_rms_norm(mlp_out, h, self.final_ln, cfg.eps)
         logits = torch.matmul(xf, self.embed.t())
         self.last_logits = logits
-        nxt = torch.argmax(logits, dim=-1)
+        nxt = ops.argmax_last_dim(logits)
         self.token_ids.copy_(nxt)
         self.pos3.add_(1)
         return nxt

@@ -115,7 +115,7 @@ class PagedKVCache(KVCache):
         reference's (k_full, v_full)."""
         return self.k_pages[layer_idx], self.v_pages[layer_idx], self.block_table, self.seq_lens
 
-    def attend(self, layer_idx: int, q, out=None, gather=None):
+    def attend(self, layer_idx: int, q, out=None, gather=None, window: int = 0):
         """Decode attention of q (batch, hq, d) over the layer's cache.  The grid is sized from a
         host-side upper bound of the lengths; while a CUDA graph is being captured that bound is the
         capacity, so replays stay correct as the cache grows."""
@@ -125,7 +125,7 @@ class PagedKVCache(KVCache):
         bound = min(self.max_seq_len, bound)
         return ops.gqa_decode_attention_paged(q, self.k_pages[layer_idx], self.v_pages[layer_idx],
                                               self.block_table, self.seq_lens, max(bound, 1), out=out,
-                                              gather=gather)
+                                              gather=gather, window=window or getattr(self, "window", 0))
 
     def note_replayed(self, steps: int = 1):
         """Tells the host-side bound that `steps` captured decode steps have been replayed."""
@@ -167,6 +167,23 @@ class PagedKVCache(KVCache):
             t = pool[idx].permute(0, 2, 1, 3).reshape(nb * self.page_tokens, self.n_kv_heads, self.head_dim)
             outs.append(t[:n].contiguous())
         return outs[0], outs[1]
+
+
+class SlidingWindowKVCache(PagedKVCache):
+    """A KVCache whose attention sees only the last `window` tokens of each sequence - the custom
+    component the reference's interface is designed for (axono/python/axono/nn/kv_cache.py:27-34 and
+    the sliding-window subclass in axono/python/tests/nn/test_kv_cache.py:75-114).  Appends go to the
+    paged pools as usual; `attend` passes the window to the kernel, which never reads the pages that
+    lie wholly before it."""
+
+    def __init__(self, window: int, *args, **kwargs):
+        super().__init__(*args, **kwargs)
+        if window <= 0:
+            raise RuntimeError("SlidingWindowKVCache: window must be positive")
+        self.window = int(window)
+
+    def __len__(self) -> int:
+        return min(super().__len__(), self.window)
 
 
 class _DeviceView:

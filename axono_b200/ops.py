@@ -103,12 +103,14 @@ def gqa_decode_attention(q, k, v):
     return out
 
 
-def gqa_decode_attention_paged(q, k_pages, v_pages, block_table, seq_lens, max_seq_len, out=None, gather=None):
+def gqa_decode_attention_paged(q, k_pages, v_pages, block_table, seq_lens, max_seq_len, out=None, gather=None,
+                               window: int = 0):
     """Batched decode over a paged cache (extension of the reference op to a batch).
     q (batch, hq, d); k_pages/v_pages (num_pages, hkv, page_tokens, d); block_table int32
     (batch, max_blocks); seq_lens int32 (batch) on the device; max_seq_len a host upper bound.
     gather=(PeerGather, slot): heads are sharded across ranks; the kernel writes this rank's heads into
-    every rank's gathered buffer and the full (batch, hq_total, d) tensor of this rank is returned."""
+    every rank's gathered buffer and the full (batch, hq_total, d) tensor of this rank is returned.
+    window > 0: each sequence attends only its last `window` tokens."""
     op = "gqa_decode_attention_paged"
     dt = _dt(q, op)
     batch, hq, d = q.shape
@@ -133,6 +135,12 @@ def gqa_decode_attention_paged(q, k_pages, v_pages, block_table, seq_lens, max_s
         return pg.tensor(slot)
     if out is None:
         out = torch.empty_like(q)
+    if window:
+        _call(lib.axb200_gqa_decode_paged_window(
+            q.data_ptr(), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
+            seq_lens.data_ptr(), batch, hq, hkv, d, page_tokens, block_table.shape[1], num_pages,
+            int(max_seq_len), int(window), dt, ws.data_ptr(), ws.numel(), _stream(q)), op)
+        return out
     _call(lib.axb200_gqa_decode_paged(
         q.data_ptr(), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
         seq_lens.data_ptr(), batch, hq, hkv, d, page_tokens, block_table.shape[1], num_pages,
@@ -357,4 +365,33 @@ def concat(a, b, axis: int):
     b_bytes = (b.numel() // max(outer, 1)) * es
     _call(_capi.lib().axb200_concat(a.data_ptr(), b.data_ptr(), out.data_ptr(), outer, a_bytes, b_bytes,
                                           _stream(a)), op)
+    return out
+
+
+def embedding(ids, table):
+    """table[ids]: ids int32/int64 of any shape, table (vocab, hidden) -> ids.shape + (hidden,)."""
+    op = "embedding"
+    dt = _dt(table, op)
+    if table.dim() != 2 or ids.dim() < 1:
+        _capi.check(1, op)
+    code = {torch.int64: _capi.INT64, torch.int32: _capi.INT32}.get(ids.dtype)
+    if code is None:
+        _capi.check(3, op)
+    ids, table = _c(ids), _c(table)
+    out = torch.empty(tuple(ids.shape) + (table.shape[1],), dtype=table.dtype, device=table.device)
+    _call(_capi.lib().axb200_embedding(ids.data_ptr(), code, table.data_ptr(), out.data_ptr(), ids.numel(),
+                                       table.shape[0], table.shape[1], dt, _stream(table)), op)
+    return out
+
+
+def argmax_last_dim(x):
+    """Index of the first maximum along the last dim -> int64 tensor of shape x.shape[:-1]."""
+    op = "argmax_last_dim"
+    dt = _dt(x, op)
+    if x.dim() < 1:
+        _capi.check(1, op)
+    x = _c(x)
+    cols = x.shape[-1]
+    out = torch.empty(x.shape[:-1], dtype=torch.int64, device=x.device)
+    _call(_capi.lib().axb200_argmax_last_dim(x.data_ptr(), out.data_ptr(), x.numel() // cols, cols, dt, _stream(x)), op)
     return out

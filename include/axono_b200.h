@@ -52,7 +52,8 @@ enum {
 enum {
   AXB200_ERR_WAIT_TIMEOUT = 1u,   /* a bounded mbarrier wait inside a kernel gave up */
   AXB200_ERR_BAD_PAGE = 2u,       /* a block-table entry was outside [0, num_pages) */
-  AXB200_ERR_CAPACITY = 4u        /* an append found its sequence at capacity */
+  AXB200_ERR_CAPACITY = 4u,       /* an append found its sequence at capacity */
+  AXB200_ERR_BAD_INDEX = 8u       /* an embedding id was outside [0, vocab) */
 };
 
 const char *axb200_version(void);
@@ -124,6 +125,18 @@ int axb200_gqa_decode_paged(const void *q, void *out, const void *k_pages, const
                             int page_tokens, int max_blocks, int num_pages,
                             int64_t max_seq_len, int dtype,
                             void *workspace, size_t workspace_bytes, void *stream);
+
+/* axb200_gqa_decode_paged under a sliding window: sequence b attends only its last `window` tokens,
+ * [max(0, len - window), len); window == 0 means all.  Whole tiles and chunks before the window are
+ * never read.  This serves the custom caches the reference's KVCache interface invites (the
+ * sliding-window subclass of axono/python/tests/nn/test_kv_cache.py:75-114, which keeps the last W
+ * tokens and attends over them). */
+int axb200_gqa_decode_paged_window(const void *q, void *out, const void *k_pages, const void *v_pages,
+                                   const int32_t *block_table, const int32_t *seq_lens,
+                                   int batch, int hq, int hkv, int d,
+                                   int page_tokens, int max_blocks, int num_pages,
+                                   int64_t max_seq_len, int window, int dtype,
+                                   void *workspace, size_t workspace_bytes, void *stream);
 
 /* ---- decode attention fused with the all-gather of per-head outputs ------------------------------
  * For KV heads sharded over `world` GPUs of one node (one process per GPU): rank `rank` holds hkv KV
@@ -259,6 +272,17 @@ int axb200_silu_mul_rows(const void *gate_up, int64_t ld, int n, int64_t rows, v
  * out = x * rsqrt(mean(x^2) + eps) * weight over the last dim; weight may be NULL. */
 int axb200_rms_norm(const void *x, const void *weight, float eps, void *out,
                     int64_t rows, int cols, int dtype, void *stream);
+
+/* axono::ops::cuda::Embedding, src/ops/cuda/sequence.cu:75-81,294-316: out[i] = table[ids[i]];
+ * ids int32 or int64 (n), table (vocab, hidden) of `dtype`, out (n, hidden).  An id outside the table
+ * sets AXB200_ERR_BAD_INDEX and gives a zero row (the reference reads out of bounds). */
+int axb200_embedding(const void *ids, int ids_dtype, const void *table, void *out, int64_t n,
+                     int64_t vocab, int hidden, int dtype, void *stream);
+
+/* axono::ops::cuda::ArgmaxLastDim, src/ops/cuda/sequence.cu:262-292,560-581, with the tie rule of the
+ * reference's CPU op (src/ops/cpu/sequence.cpp:370-400): the lowest index among equal maxima.
+ * x (rows, cols) of `dtype`, out int64 (rows). */
+int axb200_argmax_last_dim(const void *x, int64_t *out, int64_t rows, int cols, int dtype, void *stream);
 
 /* axono::ops::cuda::Concat, src/ops/cuda/sequence.cu:474-521, on bytes: out (outer, a_bytes +
  * b_bytes) = a (outer, a_bytes) ++ b (outer, b_bytes).  Axis 0 is outer == 1. */

@@ -174,6 +174,28 @@ class _Checker:
         self._check(fn(x.reshape(-1), weight, eps, out.reshape(-1), rows, cols), "rms_norm")
         return out
 
+    # embedding / argmax ------------------------------------------------------
+    def embedding(self, ids, table):
+        ids = np.ascontiguousarray(ids, dtype=np.int64)
+        table = _f32(table)
+        out = np.empty(ids.shape + (table.shape[1],), np.float32)
+        if self.prefix == "orc_":
+            fn = self._fn("embedding_f32", [_i64p, _f32p, _f32p, _sz, _sz])
+            self._check(fn(ids.reshape(-1), table, out.reshape(-1), ids.size, table.shape[1]), "embedding")
+        else:
+            fn = self._fn("embedding_f32", [_i64p, _f32p, _f32p, _sz, _sz, _sz])
+            self._check(fn(ids.reshape(-1), table, out.reshape(-1), ids.size, table.shape[0], table.shape[1]),
+                        "embedding")
+        return out
+
+    def argmax_last_dim(self, x):
+        x = _f32(x)
+        cols = x.shape[-1]
+        out = np.empty(x.shape[:-1], np.int64)
+        fn = self._fn("argmax_last_dim_f32", [_f32p, _i64p, _sz, _sz])
+        self._check(fn(x.reshape(-1), out.reshape(-1), x.size // cols, cols), "argmax")
+        return out
+
     # fp16 bits ---------------------------------------------------------------
     def half_to_float(self, bits):
         bits = np.ascontiguousarray(bits, dtype=np.uint16)

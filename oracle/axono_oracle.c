@@ -11,9 +11,10 @@
  * (oracle/_ref, built by oracle/Makefile) and with committed golden vectors
  * produced by that library.
  *
- * Build: gcc -O2 -fopenmp -ffp-contract=off -shared -fPIC (see oracle/Makefile).
- * -ffp-contract=off keeps `a * c - b * s` as separate multiplies and adds, as
- * the reference's default x86-64 build evaluates them.
+ * Build: gcc -O3 -fopenmp -mavx2 -mfma -shared -fPIC (oracle/Makefile): the flags
+ * of the reference's own x86-64 build (CMakeLists.txt:40-70), floating-point
+ * contraction left at the compiler default in both, so the same expressions
+ * contract to the same FMAs.
  */
 #include <math.h>
 #include <stddef.h>
@@ -394,4 +395,25 @@ void orc_build_mrope_pos3(int64_t *pos3, size_t n, size_t img_start, size_t want
   for (size_t ax = 0; ax < 3; ++ax)
     for (size_t i = img_start + want; i < n; ++i)
       pos3[ax * n + i] = after + (int64_t)(i - (img_start + want));
+}
+
+/* ---- Embedding / ArgmaxLastDim: src/ops/cpu/sequence.cpp:18-52, 370-400 ---------------------- */
+
+/* table (vocab,hidden) fp32; ids int64[n]; out (n,hidden): row copy per id. */
+int orc_embedding_f32(const int64_t *ids, const float *table, float *out, size_t n, size_t hidden) {
+  for (size_t i = 0; i < n; ++i)
+    memcpy(out + i * hidden, table + (size_t)ids[i] * hidden, hidden * sizeof(float));
+  return ORC_OK;
+}
+
+/* First maximum wins: best = 0; for c >= 1: if (row[c] > row[best]) best = c. */
+int orc_argmax_last_dim_f32(const float *x, int64_t *out, size_t rows, size_t cols) {
+  for (size_t r = 0; r < rows; ++r) {
+    const float *row = x + r * cols;
+    int64_t best = 0;
+    for (size_t c = 1; c < cols; ++c)
+      if (row[c] > row[best]) best = (int64_t)c;
+    out[r] = best;
+  }
+  return ORC_OK;
 }

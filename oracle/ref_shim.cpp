@@ -171,6 +171,22 @@ int ref_rms_norm_f32(const float *x, const float *w, float eps, float *out,
   return Code(axono::ops::cpu::RmsNorm(ctx, tx, tw, eps, to));
 }
 
+int ref_embedding_f32(const int64_t *ids, const float *table, float *out, size_t n, size_t vocab,
+                      size_t hidden) {
+  Context ctx;
+  Tensor ti = Wrap(DataType::INT64, {n}, ids);
+  Tensor tt = Wrap(DataType::FLOAT32, {vocab, hidden}, table);
+  Tensor to = Wrap(DataType::FLOAT32, {n, hidden}, out);
+  return Code(axono::ops::cpu::Embedding(ctx, ti, tt, to));
+}
+
+int ref_argmax_last_dim_f32(const float *x, int64_t *out, size_t rows, size_t cols) {
+  Context ctx;
+  Tensor tx = Wrap(DataType::FLOAT32, {rows, cols}, x);
+  Tensor to = Wrap(DataType::INT64, {rows}, out);
+  return Code(axono::ops::cpu::ArgmaxLastDim(ctx, tx, to));
+}
+
 void ref_half_to_float(const uint16_t *h, float *out, size_t n) {
   for (size_t i = 0; i < n; ++i) out[i] = axono::core::detail::Half2Float(h[i]);
 }

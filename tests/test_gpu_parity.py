@@ -436,3 +436,62 @@ def test_decode_step_host_matches_separate_calls(ops):
         assert torch.equal(out_h, want), f"step {step}"
     assert torch.equal(caches[0].seq_lens, caches[1].seq_lens)
     assert ops.last_error() == 0
+
+
+def test_embedding_and_argmax(ops, orc):
+    rng = np.random.default_rng(91)
+    table = rng.standard_normal((1000, 2048)).astype(np.float32)
+    ids = rng.integers(0, 1000, (4, 8))
+    for dtype in (torch.float32, torch.float16):
+        t = dev(table, dtype)
+        for idt in (torch.int64, torch.int32):
+            out = ops.embedding(dev(ids).to(idt), t)
+            assert torch.equal(out, t[dev(ids)])  # a row copy: bit-exact
+    assert np.array_equal(host(ops.embedding(dev(ids), dev(table))), orc.embedding(ids, table))
+    odd = rng.standard_normal((7, 37)).astype(np.float32)  # rows that are not 16-byte multiples
+    assert torch.equal(ops.embedding(dev(np.array([6, 0, 3])), dev(odd)), dev(odd)[[6, 0, 3]])
+    bad = ops.embedding(dev(np.array([1, 1000, -1])), dev(table))
+    assert ops.last_error() == 8 and torch.all(bad[1:] == 0) and torch.equal(bad[0], dev(table)[1])
+    x = rng.standard_normal((6, 151936)).astype(np.float32)
+    x[1, 10] = x[1, 90000] = 99.0
+    x[2, :] = -np.inf
+    x[3, 0] = np.nan
+    x[4, 5] = np.nan
+    want = orc.argmax_last_dim(x)
+    assert np.array_equal(ops.argmax_last_dim(dev(x)).cpu().numpy(), want)
+    x16 = widen(x)
+    assert np.array_equal(ops.argmax_last_dim(dev(x16, torch.float16)).cpu().numpy(), orc.argmax_last_dim(x16))
+    assert ops.last_error() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("window", [1, 63, 64, 100, 1000, 4096])
+def test_sliding_window_attention(ops, orc, dtype, window):
+    """Only the last `window` tokens are visible; equals the oracle on the sliced cache."""
+    from axono_b200.kv_cache import SlidingWindowKVCache
+
+    rng = np.random.default_rng(window)
+    B, hq, hkv, d, Lmax = 6, 16, 8, 128, 5000
+    lens = [5000, 1, 64, 65, 2049, 777]
+    q = rng.standard_normal((B, hq, d)).astype(np.float32)
+    k = (0.5 * rng.standard_normal((B, Lmax, hkv, d))).astype(np.float32)
+    v = (0.5 * rng.standard_normal((B, Lmax, hkv, d))).astype(np.float32)
+    if dtype == torch.float16:
+        q, k, v = widen(q), widen(k), widen(v)
+    cache = SlidingWindowKVCache(window, 1, B, hkv, d, Lmax, dtype=dtype)
+    cache.fill(0, dev(k, dtype), dev(v, dtype), lens)
+    # poison everything before each window: those tokens must not be read into the result
+    for b, n in enumerate(lens):
+        lo = max(0, n - window)
+        for t0 in range(0, lo, 64):
+            page = int(cache.block_table[b, t0 // 64])
+            hi = min(64, lo - t0)
+            cache.k_pages[0][page, :, :hi, :] = float("nan")
+            cache.v_pages[0][page, :, :hi, :] = float("nan")
+    out = host(cache.attend(0, dev(q, dtype)))
+    tol = F32_TOL if dtype == torch.float32 else F16_TOL
+    for b, n in enumerate(lens):
+        lo = max(0, n - window)
+        assert_close(out[b : b + 1], orc.gqa_decode(q[b : b + 1], k[b, lo:n], v[b, lo:n]), tol)
+    assert len(cache) == min(max(lens), window)
+    assert ops.last_error() == 0

@@ -210,3 +210,22 @@ def test_port_equals_reference_library(port):
     cc, ss = port.mrope_cos_sin(np.stack([pos] * 3), inv_t, 0, 0)
     _close(c[:, 0, :64], cc[:, :64] - ss[:, :64], 0.0)
     assert ang.dtype == np.float32
+
+
+def test_embedding_and_argmax(port):
+    rng = np.random.default_rng(1080)
+    table = rng.standard_normal((50, 16)).astype(np.float32)
+    ids = rng.integers(0, 50, (3, 4))
+    assert np.array_equal(port.embedding(ids, table), table[ids])  # tests/core/test_sequence_ops.py:51-55
+    x = rng.standard_normal((6, 1000)).astype(np.float32)
+    x[1, 10] = x[1, 900] = 99.0  # a tie: the first maximum wins
+    x[2, :] = -np.inf
+    x[3, 0] = np.nan  # nothing compares greater than NaN: index 0 stays
+    x[4, 5] = np.nan
+    got = port.argmax_last_dim(x)
+    assert got[0] == x[0].argmax() and got[1] == 10 and got[2] == 0 and got[3] == 0
+    assert got[4] == np.nanargmax(x[4]) and got[5] == x[5].argmax()
+    if oracle.have_reference():
+        ref = oracle.reference()
+        assert np.array_equal(ref.embedding(ids, table), port.embedding(ids, table))
+        assert np.array_equal(ref.argmax_last_dim(x), got)
