@@ -28,6 +28,8 @@ SIGNATURES = {
                                             _vp, _sz, _vp]),
     "axb200_gqa_decode_paged_gather": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i64, _i, _vp, _sz,
                                             _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "axb200_gqa_decode_paged_cp": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i64, _i, _vp, _sz,
+                                        _vp, _vp, _vp, _i, _i, _vp]),
     "axb200_p2p_alloc": (_i, [_sz, C.POINTER(_vp), _vp]),
     "axb200_p2p_open": (_i, [_vp, C.POINTER(_vp)]),
     "axb200_p2p_close": (_i, [_vp]),

@@ -719,6 +719,7 @@ struct GatherParams {
   unsigned int *peer_flags[kMaxPeers]; // each rank's flag array [world]; entry r = rank r's generation
   unsigned int *local_state;           // [0] CTAs finished in this call, [1] this rank's generation
   int world, rank, hq_total;
+  int mode;  // 0: all-gather of head outputs; 1: context-parallel exchange of (O, m, l) records
 };
 
 __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int *p) {
@@ -730,27 +731,12 @@ __device__ __forceinline__ void st_release_sys(unsigned int *p, unsigned int v) 
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-template <typename OutT>
-__global__ void __launch_bounds__(128)
-gqa_combine_gather_kernel(const DecodeParams p, const GatherParams g, int d, float dom) {
+// Tail of a kernel that has stored into every peer's buffer: every thread fences its stores
+// system-wide, the CTA counts itself in, and the last CTA of the call publishes this rank's new
+// generation to every peer and waits (bounded) until every peer's generation has arrived here.
+__device__ __forceinline__ void publish_and_wait(const GatherParams &g) {
   __shared__ int s_last;
   __shared__ unsigned int s_gen;
-  const int h = blockIdx.x, b = blockIdx.y;
-  const int L = seq_len_of(p, b);
-  int n = (L + p.chunk_tokens - 1) / p.chunk_tokens;
-  n = max(0, min(n, p.max_chunks));
-  const size_t base = ((size_t)b * p.hq + h) * p.max_chunks;
-  const size_t row = ((size_t)b * g.hq_total + (size_t)g.rank * p.hq + h) * d;
-  __shared__ float s_w[kMaxChunks], s_red[4];
-  const int cf = first_visible(p, L) / p.chunk_tokens;  // first chunk that holds visible tokens
-  if (n > 0) combine_weights(p.part_ml, base, cf, n, dom, s_w, s_red);
-  for (int c0 = threadIdx.x; c0 < d; c0 += blockDim.x) {
-    float acc = 0.f;
-    for (int c = cf; c < n; ++c) acc = fmaf(s_w[c], p.part_o[(base + c) * d + c0], acc);
-    const OutT val = static_cast<OutT>(acc);
-    for (int r = 0; r < g.world; ++r) reinterpret_cast<OutT *>(g.peer_out[r])[row + c0] = val;
-  }
-  // last-CTA-done: every thread fences its stores system-wide before its CTA counts itself in
   __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -777,6 +763,91 @@ gqa_combine_gather_kernel(const DecodeParams p, const GatherParams g, int d, flo
         break;
       }
     }
+  }
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(128)
+gqa_combine_gather_kernel(const DecodeParams p, const GatherParams g, int d, float dom) {
+  const int h = blockIdx.x, b = blockIdx.y;
+  const int L = seq_len_of(p, b);
+  int n = (L + p.chunk_tokens - 1) / p.chunk_tokens;
+  n = max(0, min(n, p.max_chunks));
+  const size_t base = ((size_t)b * p.hq + h) * p.max_chunks;
+  const size_t row = ((size_t)b * g.hq_total + (size_t)g.rank * p.hq + h) * d;
+  __shared__ float s_w[kMaxChunks], s_red[4];
+  const int cf = first_visible(p, L) / p.chunk_tokens;  // first chunk that holds visible tokens
+  if (n > 0) combine_weights(p.part_ml, base, cf, n, dom, s_w, s_red);
+  for (int c0 = threadIdx.x; c0 < d; c0 += blockDim.x) {
+    float acc = 0.f;
+    for (int c = cf; c < n; ++c) acc = fmaf(s_w[c], p.part_o[(base + c) * d + c0], acc);
+    const OutT val = static_cast<OutT>(acc);
+    for (int r = 0; r < g.world; ++r) reinterpret_cast<OutT *>(g.peer_out[r])[row + c0] = val;
+  }
+  publish_and_wait(g);
+}
+
+// ---- context-parallel decode: one sequence's tokens spread over the GPUs --------------------------
+// Each rank caches a share of every sequence's tokens (softmax does not care which) and attends its
+// share.  Exchange kernel: merges the local chunk partials of (sequence b, head h) WITHOUT normalising
+// - O_loc = sum_c w_c O_c, l_loc = sum_c w_c l_c relative to the local maximum m_loc - and stores the
+// record [O_loc(d), m_loc, l_loc] into every rank's record buffer (batch, hq, world, d + 2) at index
+// `rank`, then exchanges generation flags as above.  Merge kernel (next launch, local reads only):
+// the log-sum-exp merge of the `world` records gives the same output on every rank.
+template <typename OutT>
+__global__ void __launch_bounds__(128)
+gqa_combine_exchange_kernel(const DecodeParams p, const GatherParams g, int d, float dom) {
+  const int h = blockIdx.x, b = blockIdx.y;
+  const int L = seq_len_of(p, b);
+  int n = (L + p.chunk_tokens - 1) / p.chunk_tokens;
+  n = max(0, min(n, p.max_chunks));
+  const size_t base = ((size_t)b * p.hq + h) * p.max_chunks;
+  const size_t rec = (((size_t)b * p.hq + h) * g.world + g.rank) * (d + 2);
+  __shared__ float s_w[kMaxChunks], s_red[4];
+  const int cf = first_visible(p, L) / p.chunk_tokens;
+  float m_loc = -INFINITY, l_loc = 0.f;
+  if (n > cf) {
+    // un-normalised weights: w_c = 2^((m_c - M) dom); combine_weights divides by l, so undo it
+    combine_weights(p.part_ml, base, cf, n, dom, s_w, s_red);
+    for (int c = cf; c < n; ++c) m_loc = fmaxf(m_loc, p.part_ml[(base + c) * 2]);
+    for (int c = cf; c < n; ++c)
+      l_loc = fmaf(p.part_ml[(base + c) * 2 + 1], exp2f((p.part_ml[(base + c) * 2] - m_loc) * dom), l_loc);
+  }
+  for (int c0 = threadIdx.x; c0 < d; c0 += blockDim.x) {
+    float acc = 0.f;
+    for (int c = cf; c < n; ++c) acc = fmaf(s_w[c], p.part_o[(base + c) * d + c0], acc);
+    acc *= l_loc;  // back to the un-normalised sum
+    for (int r = 0; r < g.world; ++r) reinterpret_cast<float *>(g.peer_out[r])[rec + c0] = acc;
+  }
+  if (threadIdx.x == 0) {
+    for (int r = 0; r < g.world; ++r) {
+      reinterpret_cast<float *>(g.peer_out[r])[rec + d] = m_loc;
+      reinterpret_cast<float *>(g.peer_out[r])[rec + d + 1] = l_loc;
+    }
+  }
+  publish_and_wait(g);
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(128)
+cp_merge_kernel(const float *records, OutT *out, int world, int d, float dom) {
+  const size_t bh = (size_t)blockIdx.y * gridDim.x + blockIdx.x;  // (b, h) row
+  const float *rec = records + bh * world * (d + 2);
+  float M = -INFINITY;
+  for (int r = 0; r < world; ++r) M = fmaxf(M, rec[r * (d + 2) + d]);
+  float L = 0.f;
+  for (int r = 0; r < world; ++r) {
+    const float m = rec[r * (d + 2) + d];
+    if (m != -INFINITY) L = fmaf(rec[r * (d + 2) + d + 1], exp2f((m - M) * dom), L);
+  }
+  const float inv = L > 0.f ? 1.0f / L : 0.f;
+  for (int c0 = threadIdx.x; c0 < d; c0 += blockDim.x) {
+    float acc = 0.f;
+    for (int r = 0; r < world; ++r) {
+      const float m = rec[r * (d + 2) + d];
+      if (m != -INFINITY) acc = fmaf(exp2f((m - M) * dom), rec[r * (d + 2) + c0], acc);
+    }
+    out[bh * d + c0] = static_cast<OutT>(acc * inv);
   }
 }
 
@@ -964,7 +1035,7 @@ int decode_impl(bool paged, const void *q, void *out, const void *k, const void 
                 int64_t max_len, int dtype, void *workspace, size_t workspace_bytes,
                 cudaStream_t st, const GatherParams *gather = nullptr, int window = 0) {
   if (dtype != AXB200_FLOAT16 && dtype != AXB200_FLOAT32) return AXB200_UNSUPPORTED_TYPE;
-  if (!q || (!out && !gather) || !k || !v) return AXB200_INVALID_PTR;
+  if (!q || (!out && !(gather && gather->mode == 0)) || !k || !v) return AXB200_INVALID_PTR;
   if (batch <= 0 || hq <= 0 || hkv <= 0 || d <= 0 || max_len <= 0) return AXB200_INVALID_ARGUMENT;
   if (hq % hkv != 0) return AXB200_SHAPE_MISMATCH;
   if (d > 256 || max_len > (int64_t)INT32_MAX - 4096) return AXB200_INVALID_ARGUMENT;
@@ -1043,7 +1114,16 @@ int decode_impl(bool paged, const void *q, void *out, const void *k, const void 
     // generic kernels keep raw dot products and scale inside the exponent.
     const float cdom = (tiled && f16) ? 1.0f : dom;
     const dim3 cgrid(hq, batch);
-    if (gather) {
+    if (gather && gather->mode == 1) {
+      const float *records = static_cast<const float *>(gather->peer_out[gather->rank]);
+      if (f16) {
+        gqa_combine_exchange_kernel<__half><<<cgrid, 128, 0, st>>>(p, *gather, d, cdom);
+        cp_merge_kernel<__half><<<cgrid, 128, 0, st>>>(records, static_cast<__half *>(out), gather->world, d, cdom);
+      } else {
+        gqa_combine_exchange_kernel<float><<<cgrid, 128, 0, st>>>(p, *gather, d, cdom);
+        cp_merge_kernel<float><<<cgrid, 128, 0, st>>>(records, static_cast<float *>(out), gather->world, d, cdom);
+      }
+    } else if (gather) {
       if (f16) gqa_combine_gather_kernel<__half><<<cgrid, 128, 0, st>>>(p, *gather, d, cdom);
       else gqa_combine_gather_kernel<float><<<cgrid, 128, 0, st>>>(p, *gather, d, cdom);
     } else {
@@ -1124,6 +1204,31 @@ int axb200_gqa_decode_paged_gather(const void *q, const void *k_pages, const voi
   g.hq_total = hq_total;
   return axb::decode_impl(true, q, nullptr, k_pages, v_pages, block_table, seq_lens, 0, batch, hq,
                           hkv, d, page_tokens, max_blocks, num_pages, max_seq_len, dtype, workspace,
+                          workspace_bytes, static_cast<cudaStream_t>(stream), &g);
+}
+
+int axb200_gqa_decode_paged_cp(const void *q, void *out, const void *k_pages, const void *v_pages,
+                               const int32_t *block_table, const int32_t *seq_lens, int batch,
+                               int hq, int hkv, int d, int page_tokens, int max_blocks,
+                               int num_pages, int64_t max_seq_len, int dtype, void *workspace,
+                               size_t workspace_bytes, void *const *peer_records,
+                               void *const *peer_flags, void *local_state, int world, int rank,
+                               void *stream) {
+  if (!peer_records || !peer_flags || !local_state || !out) return AXB200_INVALID_PTR;
+  if (world < 1 || world > axb::kMaxPeers || rank < 0 || rank >= world) return AXB200_INVALID_ARGUMENT;
+  axb::GatherParams g{};
+  for (int r = 0; r < world; ++r) {
+    if (!peer_records[r] || !peer_flags[r]) return AXB200_INVALID_PTR;
+    g.peer_out[r] = peer_records[r];
+    g.peer_flags[r] = static_cast<unsigned int *>(peer_flags[r]);
+  }
+  g.local_state = static_cast<unsigned int *>(local_state);
+  g.world = world;
+  g.rank = rank;
+  g.hq_total = hq;
+  g.mode = 1;
+  return axb::decode_impl(true, q, out, k_pages, v_pages, block_table, seq_lens, 0, batch, hq, hkv,
+                          d, page_tokens, max_blocks, num_pages, max_seq_len, dtype, workspace,
                           workspace_bytes, static_cast<cudaStream_t>(stream), &g);
 }
 

@@ -115,7 +115,7 @@ class PagedKVCache(KVCache):
         reference's (k_full, v_full)."""
         return self.k_pages[layer_idx], self.v_pages[layer_idx], self.block_table, self.seq_lens
 
-    def attend(self, layer_idx: int, q, out=None, gather=None, window: int = 0):
+    def attend(self, layer_idx: int, q, out=None, gather=None, window: int = 0, context_parallel=None):
         """Decode attention of q (batch, hq, d) over the layer's cache.  The grid is sized from a
         host-side upper bound of the lengths; while a CUDA graph is being captured that bound is the
         capacity, so replays stay correct as the cache grows."""
@@ -125,7 +125,8 @@ class PagedKVCache(KVCache):
         bound = min(self.max_seq_len, bound)
         return ops.gqa_decode_attention_paged(q, self.k_pages[layer_idx], self.v_pages[layer_idx],
                                               self.block_table, self.seq_lens, max(bound, 1), out=out,
-                                              gather=gather, window=window or getattr(self, "window", 0))
+                                              gather=gather, window=window or getattr(self, "window", 0),
+                                              context_parallel=context_parallel)
 
     def note_replayed(self, steps: int = 1):
         """Tells the host-side bound that `steps` captured decode steps have been replayed."""

@@ -104,13 +104,15 @@ def gqa_decode_attention(q, k, v):
 
 
 def gqa_decode_attention_paged(q, k_pages, v_pages, block_table, seq_lens, max_seq_len, out=None, gather=None,
-                               window: int = 0):
+                               window: int = 0, context_parallel=None):
     """Batched decode over a paged cache (extension of the reference op to a batch).
     q (batch, hq, d); k_pages/v_pages (num_pages, hkv, page_tokens, d); block_table int32
     (batch, max_blocks); seq_lens int32 (batch) on the device; max_seq_len a host upper bound.
     gather=(PeerGather, slot): heads are sharded across ranks; the kernel writes this rank's heads into
     every rank's gathered buffer and the full (batch, hq_total, d) tensor of this rank is returned.
-    window > 0: each sequence attends only its last `window` tokens."""
+    window > 0: each sequence attends only its last `window` tokens.
+    context_parallel=(PeerGather(kind="records"), slot): every rank caches a share of each sequence's
+    tokens; the ranks exchange un-normalised partials over peer memory and all return the full result."""
     op = "gqa_decode_attention_paged"
     dt = _dt(q, op)
     batch, hq, d = q.shape
@@ -135,6 +137,16 @@ def gqa_decode_attention_paged(q, k_pages, v_pages, block_table, seq_lens, max_s
         return pg.tensor(slot)
     if out is None:
         out = torch.empty_like(q)
+    if context_parallel is not None:
+        pg, slot = context_parallel
+        if pg.kind != "records" or pg.batch != batch or pg.d != d or pg.hq_total != hq:
+            _capi.check(4, op)
+        _call(lib.axb200_gqa_decode_paged_cp(
+            q.data_ptr(), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
+            seq_lens.data_ptr(), batch, hq, hkv, d, page_tokens, block_table.shape[1], num_pages,
+            int(max_seq_len), dt, ws.data_ptr(), ws.numel(), pg.out_ptrs(slot), pg.flag_ptrs, pg.state_ptr,
+            pg.world, pg.rank, _stream(q)), op)
+        return out
     if window:
         _call(lib.axb200_gqa_decode_paged_window(
             q.data_ptr(), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),

@@ -22,7 +22,13 @@ _ALIGN = 256
 
 
 class PeerGather:
-    def __init__(self, batch: int, hq_total: int, d: int, dtype=torch.float16, slots: int = 2, group=None):
+    def __init__(self, batch: int, hq_total: int, d: int, dtype=torch.float16, slots: int = 2, group=None,
+                 kind: str = "heads"):
+        """kind "heads": slots hold gathered head outputs (batch, hq_total, d) of `dtype`;
+        kind "records": slots hold context-parallel records (batch, hq_total, world, d + 2) fp32."""
+        if kind not in ("heads", "records"):
+            raise ValueError(kind)
+        self.kind = kind
         if slots < 2:
             raise RuntimeError("PeerGather needs at least two slots (successive calls must alternate)")
         self.group = group
@@ -32,7 +38,8 @@ class PeerGather:
             raise RuntimeError("PeerGather supports up to 8 ranks (one NVSwitch node)")
         self.batch, self.hq_total, self.d, self.dtype, self.slots = batch, hq_total, d, dtype, slots
         es = torch.tensor([], dtype=dtype).element_size()
-        self.slot_bytes = (batch * hq_total * d * es + _ALIGN - 1) // _ALIGN * _ALIGN
+        raw = batch * hq_total * d * es if kind == "heads" else batch * hq_total * self.world * (d + 2) * 4
+        self.slot_bytes = (raw + _ALIGN - 1) // _ALIGN * _ALIGN
         self.flags_off = self.slot_bytes * slots
         self.state_off = self.flags_off + _ALIGN
         total = self.state_off + _ALIGN
@@ -60,7 +67,8 @@ class PeerGather:
         self._flags = arr(*[p + self.flags_off for p in self.peer_ptrs])
         self._outs = [arr(*[p + s * self.slot_bytes for p in self.peer_ptrs]) for s in range(slots)]
         typestr = {torch.float16: "<f2", torch.float32: "<f4"}[dtype]
-        self._views = [torch.as_tensor(_DeviceView(self.local_ptr + s * self.slot_bytes, (batch, hq_total, d), typestr),
+        shape, ts = ((batch, hq_total, d), typestr) if kind == "heads" else ((batch, hq_total, self.world, d + 2), "<f4")
+        self._views = [torch.as_tensor(_DeviceView(self.local_ptr + s * self.slot_bytes, shape, ts),
                                        device=torch.device("cuda", torch.cuda.current_device()))
                        for s in range(slots)]
 

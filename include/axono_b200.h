@@ -160,7 +160,24 @@ int axb200_gqa_decode_paged_gather(const void *q, const void *k_pages, const voi
                                    void *const *peer_out, void *const *peer_flags, void *local_state,
                                    int world, int rank, int hq_total, void *stream);
 
-/* Peer-mappable device memory for the call above (CUDA IPC): alloc returns zero-filled memory and a
+/* Context-parallel decode: the tokens of every sequence are spread over `world` GPUs (any split -
+ * softmax does not depend on token order; keys are rotated with their global positions before they are
+ * cached).  Each rank attends its share; its combine kernel stores an un-normalised record
+ * [O(d), m, l] per (sequence, head) into every rank's record buffer (batch, hq, world, d + 2) fp32
+ * and exchanges generation flags as above; a merge kernel then forms the same `out` (batch,hq,d) on
+ * every rank from local memory.  For one very long sequence that neither batch nor head sharding
+ * can spread.  peer_records / peer_flags / local_state as in axb200_gqa_decode_paged_gather; successive
+ * calls must alternate between at least two record buffers.  No counterpart in the reference. */
+int axb200_gqa_decode_paged_cp(const void *q, void *out, const void *k_pages, const void *v_pages,
+                               const int32_t *block_table, const int32_t *seq_lens,
+                               int batch, int hq, int hkv, int d,
+                               int page_tokens, int max_blocks, int num_pages,
+                               int64_t max_seq_len, int dtype,
+                               void *workspace, size_t workspace_bytes,
+                               void *const *peer_records, void *const *peer_flags, void *local_state,
+                               int world, int rank, void *stream);
+
+/* Peer-mappable device memory for the calls above (CUDA IPC): alloc returns zero-filled memory and a
  * 64-byte handle to send to the other processes of the node; open maps a peer's handle; close
  * unmaps it; free releases an allocation.  These four are set-up calls: they allocate and
  * synchronise, unlike every other entry point.  No counterpart in the reference. */

@@ -357,3 +357,27 @@ def test_silu_mul_rows():
         t16 = dev(widen(gu), torch.float16)[:, : 2 * n]
         ref16 = orc.silu_mul(widen(gu)[:, :n], widen(gu)[:, n : 2 * n])
         assert oracle.rel_err(host(ops.silu_mul_rows(t16, n)), ref16) <= F16_TOL
+
+
+def test_context_parallel_single_rank_matches_plain():
+    """World of one: exchange + merge kernels on local records give the plain result."""
+    from axono_b200 import ops
+    from axono_b200.kv_cache import PagedKVCache
+    from axono_b200.p2p import PeerGather
+
+    rng = np.random.default_rng(8100)
+    B, hq, hkv, d, L = 5, 16, 8, 128, 2600
+    lens = [L, 0, 64, 65, 2048]
+    for dtype, tol in ((torch.float16, 1e-3), (torch.float32, 1e-6)):
+        cache = PagedKVCache(1, B, hkv, d, L, dtype=dtype)
+        cache.fill(0, dev((0.5 * rng.standard_normal((B, L, hkv, d))).astype(np.float32), dtype),
+                   dev((0.5 * rng.standard_normal((B, L, hkv, d))).astype(np.float32), dtype), lens)
+        q = dev(rng.standard_normal((B, hq, d)).astype(np.float32), dtype)
+        pe = PeerGather(B, hq, d, dtype, slots=2, kind="records")
+        want = cache.attend(0, q)
+        for it in range(3):
+            got = cache.attend(0, q, context_parallel=(pe, it % 2))
+            assert oracle.rel_err(host(got), host(want)) <= tol
+            assert torch.all(got[1] == 0)  # the empty sequence
+        assert ops.last_error() == 0
+        pe.close()

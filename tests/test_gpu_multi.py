@@ -60,6 +60,29 @@ def _worker(rank, world, port, out_dir):
             assert err <= 1e-3, f"rank {rank} iteration {it}: {err:.3e}"
         assert ops.last_error() == 0
 
+        # ---- context-parallel decode: pages of every sequence dealt round-robin to the ranks ----
+        Lc = 3000
+        clens = [Lc, 40, 64, 65, 1500]  # 40 tokens: only rank 0 holds any
+        pe = PeerGather(B, hq, d, h, slots=2, kind="records")
+        cp = PagedKVCache(1, B, hkv, d, Lc, dtype=h)
+        local_lens, kl, vl = [], np.zeros_like(k), np.zeros_like(v)
+        for b_, n in enumerate(clens):
+            mine = [t for t in range(n) if (t // 64) % world == rank]
+            local_lens.append(len(mine))
+            kl[b_, : len(mine)] = k[b_, mine]
+            vl[b_, : len(mine)] = v[b_, mine]
+        cp.fill(0, dev(kl), dev(vl), local_lens)
+        full2 = PagedKVCache(1, B, hkv, d, Lc, dtype=h)
+        full2.fill(0, dev(k), dev(v), clens)
+        for it in range(6):
+            qi = dev(q * (1.0 + 0.02 * it))
+            want = full2.attend(0, qi)
+            got = cp.attend(0, qi, context_parallel=(pe, it % 2))
+            torch.cuda.synchronize()
+            err = (got.float() - want.float()).abs().max().item() / want.float().abs().max().item()
+            assert err <= 1e-3, f"rank {rank} context-parallel iteration {it}: {err:.3e}"
+        assert ops.last_error() == 0
+
         # ---- text tower: sharded ranks agree with each other and with the unsharded tower ----
         cfg = TextTowerConfig(hidden=256, intermediate=512, n_q_heads=4, n_kv_heads=2, head_dim=128, vocab=1000,
                               n_layers=4)
@@ -100,6 +123,7 @@ def _worker(rank, world, port, out_dir):
             single.token_ids.copy_(shard.token_ids)  # keep the two on the same trajectory
         assert ops.last_error() == 0
         shard.peer_gather.close()
+        pe.close()
         pg.close()
         open(os.path.join(out_dir, f"ok{rank}"), "w").close()
     finally:
