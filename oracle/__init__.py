@@ -31,12 +31,21 @@ _u16p = np.ctypeslib.ndpointer(np.uint16, flags="C_CONTIGUOUS")
 _u8p = np.ctypeslib.ndpointer(np.uint8, flags="C_CONTIGUOUS")
 
 
-def build(ref_root: str = "/root/reference") -> None:
-    """Compile the C restatement, and the reference library when its sources are present."""
+def build(ref_root: str = "") -> None:
+    """Compile the C restatement, and the reference libraries when its sources are present (their
+    location: argument, else $AXONO_REFERENCE_ROOT, else the Makefile's default)."""
+    ref_root = ref_root or os.environ.get("AXONO_REFERENCE_ROOT", "") or _makefile_default_ref()
     subprocess.check_call(["make", "-s", "-C", _HERE, "oracle"])
     if os.path.isdir(os.path.join(ref_root, "src")):
         subprocess.check_call(["make", "-s", "-C", _HERE, "ref", f"REF={ref_root}"])
         subprocess.check_call(["make", "-s", "-C", _HERE, "refcuda", f"REF={ref_root}"])
+
+
+def _makefile_default_ref() -> str:
+    for line in open(os.path.join(_HERE, "Makefile")):
+        if line.startswith("REF ?="):
+            return line.split("=", 1)[1].strip()
+    return ""
 
 
 def _f32(a):
