@@ -24,6 +24,8 @@ SIGNATURES = {
     "axb200_gqa_decode_static": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i, _vp]),
     "axb200_gqa_decode_paged": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i64, _i,
                                      _vp, _sz, _vp]),
+    "axb200_sdpa_workspace_bytes": (_sz, [_i, _i, _i, _i, _i64, _i]),
+    "axb200_sdpa": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i64, _i, _i, _vp, _sz, _vp]),
     "axb200_gqa_decode_paged_window": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i64, _i, _i,
                                             _vp, _sz, _vp]),
     "axb200_gqa_decode_paged_gather": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i64, _i, _vp, _sz,

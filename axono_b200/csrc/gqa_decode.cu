@@ -62,10 +62,12 @@ struct DecodeParams {
   float scale;  // 1/sqrt(d)
   int write_final;  // max_chunks == 1: normalise and write `out` directly
   int window;       // > 0: only the last `window` tokens of each sequence are visible (sliding window)
+  int causal_rows;  // rows are the queries of one sequence: row b sees min(b + 1, fixed_len) keys
 };
 
 __device__ __forceinline__ int seq_len_of(const DecodeParams &p, int b) {
-  return p.seq_lens ? p.seq_lens[b] : p.fixed_len;
+  if (p.seq_lens) return p.seq_lens[b];
+  return p.causal_rows ? min(b + 1, p.fixed_len) : p.fixed_len;
 }
 
 // First visible token of a sequence of length L: 0, or L - window under a sliding window.
@@ -1033,7 +1035,8 @@ int decode_impl(bool paged, const void *q, void *out, const void *k, const void 
                 const int32_t *block_table, const int32_t *seq_lens, int fixed_len, int batch,
                 int hq, int hkv, int d, int page_tokens, int max_blocks, int num_pages,
                 int64_t max_len, int dtype, void *workspace, size_t workspace_bytes,
-                cudaStream_t st, const GatherParams *gather = nullptr, int window = 0) {
+                cudaStream_t st, const GatherParams *gather = nullptr, int window = 0,
+                int causal_rows = 0) {
   if (dtype != AXB200_FLOAT16 && dtype != AXB200_FLOAT32) return AXB200_UNSUPPORTED_TYPE;
   if (!q || (!out && !(gather && gather->mode == 0)) || !k || !v) return AXB200_INVALID_PTR;
   if (batch <= 0 || hq <= 0 || hkv <= 0 || d <= 0 || max_len <= 0) return AXB200_INVALID_ARGUMENT;
@@ -1064,6 +1067,7 @@ int decode_impl(bool paged, const void *q, void *out, const void *k, const void 
   p.scale = 1.0f / sqrtf((float)d);
   if (window < 0) return AXB200_INVALID_ARGUMENT;
   p.window = window;
+  p.causal_rows = causal_rows;
   p.write_final = pl.max_chunks == 1 && !gather;  // the gather epilogue lives in the combine kernel
   if (!p.write_final) {
     if (!workspace || workspace_bytes < pl.part_o_bytes + pl.part_ml_bytes)
@@ -1162,6 +1166,24 @@ void *static_scratch_ptr() {
 }
 
 }  // namespace
+
+// Prefill attention evaluated row by row on the decode kernels: query row t of q (sq,hq,d) is a
+// "sequence" that sees min(t + 1, skv) keys (causal) or all skv keys of the one token-major cache.
+// Correct for every dtype and head size the decode kernels take; K/V are re-read per row, so this is
+// the parity path, not the fast one.
+size_t sdpa_rows_workspace_bytes(int sq, int hq, int hkv, int d, int64_t skv) {
+  if (sq <= 0 || hq <= 0 || hkv <= 0 || d <= 0 || skv <= 0) return 0;
+  const Plan pl = make_plan(sq, hq, hkv, d, skv);
+  return pl.part_o_bytes + pl.part_ml_bytes;
+}
+
+int sdpa_rows_fallback(const void *q, const void *k, const void *v, void *out, int sq, int hq, int hkv,
+                       int d, int64_t skv, int is_causal, int dtype, void *workspace,
+                       size_t workspace_bytes, cudaStream_t st) {
+  return decode_impl(false, q, out, k, v, nullptr, nullptr, (int)skv, sq, hq, hkv, d, 0, 0, 1, skv, dtype,
+                     workspace, workspace_bytes, st, nullptr, 0, is_causal ? 1 : 0);
+}
+
 }  // namespace axb
 
 extern "C" {

@@ -1,0 +1,384 @@
+// Prefill attention (many queries, optional causal mask) for sm_100a on the 5th-generation tensor
+// cores.  Replaces the reference's ScaledDotProductAttention / SdpaKernel
+// (src/ops/cuda/sequence.cu:105-163,451-472), whose scores live in shared memory (skv*4 bytes, so it
+// cannot pass ~12 K keys) and whose P.V loop is thread-serial.
+//
+// fp16, head_dim 128: one CTA per (block of 128 query rows, query head).  Q, K and V tiles are
+// staged by TMA with 128-byte swizzle; S = Q.K^T and O += P.V are tcgen05.mma (M = N = 128,
+// cta_group::1, kind::f16) with both accumulators in tensor memory (S in columns 0..127, O in
+// 128..255); thread t owns query row t: it reads its S row with tcgen05.ld, does the online softmax
+// in registers, writes P (fp16) into shared memory in the swizzled K-major layout the MMA expects
+// and rescales its O row in tensor memory when the running maximum moves.  K/V tiles are double
+// buffered; completion of the MMAs is tracked with tcgen05.commit on mbarriers.  Every wait is
+// bounded.  Other dtypes and head sizes run row by row on the decode kernels (correct, not fast).
+//
+// Semantics as the reference's CPU op (src/ops/cpu/sequence.cpp:236-301): q (sq,hq,d), k/v
+// (skv,hkv,d) token-major, head h reads KV head h / (hq/hkv), scale 1/sqrt(d); with is_causal row t
+// sees keys [0, t] when skv >= t+1 and all keys otherwise.
+#include <math.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+namespace axb {
+
+// Row-by-row evaluation on the decode kernels (defined beside them).
+int sdpa_rows_fallback(const void *q, const void *k, const void *v, void *out, int sq, int hq, int hkv,
+                       int d, int64_t skv, int is_causal, int dtype, void *workspace,
+                       size_t workspace_bytes, cudaStream_t st);
+size_t sdpa_rows_workspace_bytes(int sq, int hq, int hkv, int d, int64_t skv);
+
+namespace {
+
+constexpr int kBlockM = 128, kBlockN = 128, kD = 128;
+constexpr int kTileBytes = 32768;  // 128 rows x 128 halves, as two swizzled boxes of 16 KB
+constexpr int kOffQ = 0, kOffK = kTileBytes, kOffV = 3 * kTileBytes, kOffP = 5 * kTileBytes;
+constexpr int kOffBar = 6 * kTileBytes;
+constexpr int kSmemBytes = kOffBar + 128 + 1024;
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct PrefillParams {
+  void *out;
+  int sq, hq, hkv, skv, causal;
+  float scale_log2;
+};
+
+__device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, uint64_t *bar, int c0, int c1,
+                                            int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor: start address, leading / stride byte offsets (all >> 4),
+// descriptor version 1, 128-byte swizzle.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+  return (uint64_t)((addr >> 4) & 0x3FFF) | ((uint64_t)((lbo >> 4) & 0x3FFF) << 16) |
+         ((uint64_t)((sbo >> 4) & 0x3FFF) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, bool accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"((uint32_t)accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__global__ void __launch_bounds__(128, 1)
+prefill_attn_f16_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                        const __grid_constant__ CUtensorMap tmV, const PrefillParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kOffBar);
+  uint64_t *bar_q = bars, *bar_k = bars + 1, *bar_v = bars + 3, *bar_s = bars + 5, *bar_o = bars + 6;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 7);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + 8);
+
+  const int qb = blockIdx.x, h = blockIdx.y;
+  const int hk = h / (p.hq / p.hkv);
+  const int q0 = qb * kBlockM;
+  const int warp = threadIdx.x >> 5;
+  const int t_row = q0 + threadIdx.x;  // the query row this thread owns
+  const int t_last = min(q0 + kBlockM, p.sq) - 1;
+  const int kv_end_max = p.causal ? min(t_last + 1, p.skv) : p.skv;  // reference rule: min(t+1, skv)
+  const int nkv = (kv_end_max + kBlockN - 1) / kBlockN;
+  const int kv_end = p.causal ? min(t_row + 1, p.skv) : p.skv;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 7; ++i) mbar_init(&bars[i], 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 256;" ::"r"(smem_u32(tmem_slot)) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_s = *tmem_slot, tmem_o = tmem_s + 128;
+  const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+  // instruction descriptors: fp32 accumulate, fp16 operands, M = N = 128; B is K-major for Q.K^T and
+  // MN-major for P.V (a V tile is [keys][d], d contiguous)
+  const uint32_t idesc_qk = (1u << 4) | ((kBlockN >> 3) << 17) | ((kBlockM >> 4) << 24);
+  const uint32_t idesc_pv = idesc_qk | (1u << 16);
+
+  auto load_kv = [&](int j) {
+    const int s = j & 1;
+    uint8_t *ks = smem + kOffK + s * kTileBytes, *vs = smem + kOffV + s * kTileBytes;
+    mbar_arrive_expect_tx(&bar_k[s], kTileBytes);
+    tma_load_3d(ks, &tmK, &bar_k[s], 0, hk, j * kBlockN);
+    tma_load_3d(ks + 16384, &tmK, &bar_k[s], 64, hk, j * kBlockN);
+    mbar_arrive_expect_tx(&bar_v[s], kTileBytes);
+    tma_load_3d(vs, &tmV, &bar_v[s], 0, hk, j * kBlockN);
+    tma_load_3d(vs + 16384, &tmV, &bar_v[s], 64, hk, j * kBlockN);
+  };
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_descriptor(&tmQ);
+    tma_prefetch_descriptor(&tmK);
+    tma_prefetch_descriptor(&tmV);
+    mbar_arrive_expect_tx(bar_q, kTileBytes);
+    tma_load_3d(smem + kOffQ, &tmQ, bar_q, 0, h, q0);
+    tma_load_3d(smem + kOffQ + 16384, &tmQ, bar_q, 64, h, q0);
+    load_kv(0);
+  }
+
+  float m_run = -INFINITY, l_run = 0.f;
+  const uint32_t q_addr = smem_u32(smem + kOffQ), p_addr = smem_u32(smem + kOffP);
+  uint8_t *p_row = smem + kOffP + threadIdx.x * 128;
+  bool ok = true;
+
+  for (int j = 0; j < nkv && ok; ++j) {
+    const int s = j & 1;
+    const uint32_t kv_phase = (j >> 1) & 1;
+    if (threadIdx.x == 0) {
+      // S = Q . K_j^T
+      if (j == 0) ok = mbar_wait_bounded(bar_q, 0, abort_flag);
+      ok = ok && mbar_wait_bounded(&bar_k[s], kv_phase, abort_flag);
+      if (ok) {
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(smem + kOffK + s * kTileBytes);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
+          umma_f16(tmem_s, smem_desc(q_addr + off, 16, 1024), smem_desc(k_addr + off, 16, 1024), idesc_qk, ks > 0);
+        }
+        umma_commit(bar_s);
+        // the other K/V stage is free once P.V of the previous tile has completed
+        if (j + 1 < nkv) {
+          if (j > 0) ok = mbar_wait_bounded(bar_o, (j - 1) & 1, abort_flag);
+          if (ok) load_kv(j + 1);
+        }
+      }
+    }
+    __syncwarp();
+    ok = mbar_wait_bounded(bar_s, j & 1, abort_flag);
+    if (!ok) break;
+    tc_fence_after();
+
+    // ---- online softmax on this thread's row ----
+    const int n0 = j * kBlockN;
+    const bool edge = n0 + kBlockN > kv_end;
+    float mx = -INFINITY;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      uint32_t r[32];
+      tmem_ld32(tmem_s + lane_base + c * 32, r);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        float v = __uint_as_float(r[i]);
+        if (edge && n0 + c * 32 + i >= kv_end) v = -INFINITY;
+        mx = fmaxf(mx, v);
+      }
+    }
+    const float m_new = fmaxf(m_run, mx * p.scale_log2);
+    const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
+    const float corr = fast_exp2(m_run - m_safe);
+    float row_sum = 0.f;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      uint32_t r[32];
+      tmem_ld32(tmem_s + lane_base + c * 32, r);
+      uint32_t packed[16];
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) {
+        float a = fast_exp2(fmaf(__uint_as_float(r[i]), p.scale_log2, -m_safe));
+        float b = fast_exp2(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, -m_safe));
+        if (edge) {
+          if (n0 + c * 32 + i >= kv_end) a = 0.f;
+          if (n0 + c * 32 + i + 1 >= kv_end) b = 0.f;
+        }
+        row_sum += a + b;
+        packed[i >> 1] = pack_half2(a, b);
+      }
+      // 32 keys = four 16-byte chunks of this row; chunk cc of the 256-byte row sits in box cc/8 at
+      // swizzled position (cc%8) ^ (row%8)
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int cc = c * 4 + u;
+        uint8_t *dst = p_row + (cc >> 3) * 16384 + (((cc & 7) ^ (threadIdx.x & 7)) << 4);
+        *reinterpret_cast<uint4 *>(dst) = make_uint4(packed[u * 4], packed[u * 4 + 1], packed[u * 4 + 2], packed[u * 4 + 3]);
+      }
+    }
+    l_run = l_run * corr + row_sum;
+    m_run = m_new;
+    // rescale this row of O in tensor memory when some row of the warp moved its maximum
+    if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem_o + lane_base + c * 32, r);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * corr);
+        tmem_st32(tmem_o + lane_base + c * 32, r);
+      }
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P is read by the tensor core
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      // O += P . V_j
+      ok = mbar_wait_bounded(&bar_v[s], kv_phase, abort_flag);
+      if (ok) {
+        tc_fence_after();
+        const uint32_t v_addr = smem_u32(smem + kOffV + s * kTileBytes);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint32_t a_off = (ks >> 2) * 16384 + (ks & 3) * 32;  // 16 keys along K of the P tile
+          // V as the MN-major B operand: 64-wide d atoms 16 KB apart, 8-key groups 1 KB apart,
+          // 16 keys per instruction = 2 KB
+          umma_f16(tmem_o, smem_desc(p_addr + a_off, 16, 1024), smem_desc(v_addr + ks * 2048, 16384, 1024), idesc_pv,
+                   j > 0 || ks > 0);
+        }
+        umma_commit(bar_o);
+      }
+    }
+    __syncwarp();
+  }
+
+  // ---- epilogue: O / l -> out ----
+  if (nkv > 0) ok = ok && mbar_wait_bounded(bar_o, (nkv - 1) & 1, abort_flag);
+  tc_fence_after();
+  if (ok && !*abort_flag) {
+    const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+    __half *dst = reinterpret_cast<__half *>(p.out) + ((size_t)t_row * p.hq + h) * kD;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      uint32_t r[32];
+      tmem_ld32(tmem_o + lane_base + c * 32, r);
+      if (t_row < p.sq) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          uint4 w;
+          w.x = pack_half2(__uint_as_float(r[u * 8 + 0]) * inv, __uint_as_float(r[u * 8 + 1]) * inv);
+          w.y = pack_half2(__uint_as_float(r[u * 8 + 2]) * inv, __uint_as_float(r[u * 8 + 3]) * inv);
+          w.z = pack_half2(__uint_as_float(r[u * 8 + 4]) * inv, __uint_as_float(r[u * 8 + 5]) * inv);
+          w.w = pack_half2(__uint_as_float(r[u * 8 + 6]) * inv, __uint_as_float(r[u * 8 + 7]) * inv);
+          *reinterpret_cast<uint4 *>(dst + c * 32 + u * 8) = w;
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;" ::"r"(tmem_s) : "memory");
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encoder() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void *sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  });
+  return fn;
+}
+
+// (rows, heads, 128) fp16 token-major -> tensor map with boxes of [128 rows][64 halves], 128-byte swizzle
+bool rows_map(CUtensorMap *map, const void *base, int64_t rows, int heads) {
+  EncodeTiledFn fn = encoder();
+  if (!fn) return false;
+  cuuint64_t dims[3] = {(cuuint64_t)kD, (cuuint64_t)heads, (cuuint64_t)rows};
+  cuuint64_t strides[2] = {(cuuint64_t)kD * 2, (cuuint64_t)heads * kD * 2};
+  cuuint32_t box[3] = {64, 1, 128}, es[3] = {1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(base), dims, strides, box, es,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace
+}  // namespace axb
+
+extern "C" {
+
+size_t axb200_sdpa_workspace_bytes(int sq, int hq, int hkv, int d, int64_t skv, int dtype) {
+  if (dtype == AXB200_FLOAT16 && d == axb::kD) return 0;
+  return axb::sdpa_rows_workspace_bytes(sq, hq, hkv, d, skv);
+}
+
+int axb200_sdpa(const void *q, const void *k, const void *v, void *out, int sq, int hq, int hkv, int d,
+                int64_t skv, int is_causal, int dtype, void *workspace, size_t workspace_bytes, void *stream) {
+  if (dtype != AXB200_FLOAT16 && dtype != AXB200_FLOAT32) return AXB200_UNSUPPORTED_TYPE;
+  if (!q || !k || !v || !out) return AXB200_INVALID_PTR;
+  if (sq <= 0 || hq <= 0 || hkv <= 0 || d <= 0 || skv <= 0 || skv > 0x7fffffff - 4096) return AXB200_INVALID_ARGUMENT;
+  if (hq % hkv != 0) return AXB200_SHAPE_MISMATCH;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool tensor_path = dtype == AXB200_FLOAT16 && d == axb::kD && hq <= 65535 && axb::aligned16(q) &&
+                           axb::aligned16(k) && axb::aligned16(v) && axb::aligned16(out) && axb::encoder();
+  if (!tensor_path)
+    return axb::sdpa_rows_fallback(q, k, v, out, sq, hq, hkv, d, skv, is_causal, dtype, workspace, workspace_bytes, st);
+  CUtensorMap mq, mk, mv;
+  if (!axb::rows_map(&mq, q, sq, hq) || !axb::rows_map(&mk, k, skv, hkv) || !axb::rows_map(&mv, v, skv, hkv))
+    return AXB200_INTERNAL_ERROR;
+  static std::mutex mu;
+  static bool opted[64] = {false};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return AXB200_DEVICE_ERROR;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (!opted[dev]) {
+      if (cudaFuncSetAttribute(axb::prefill_attn_f16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               axb::kSmemBytes) != cudaSuccess)
+        return AXB200_DEVICE_ERROR;
+      opted[dev] = true;
+    }
+  }
+  axb::PrefillParams p{};
+  p.out = out;
+  p.sq = sq;
+  p.hq = hq;
+  p.hkv = hkv;
+  p.skv = (int)skv;
+  p.causal = is_causal != 0;
+  p.scale_log2 = (1.0f / sqrtf((float)d)) * axb::kLog2e;
+  const dim3 grid((sq + axb::kBlockM - 1) / axb::kBlockM, hq);
+  axb::prefill_attn_f16_kernel<<<grid, 128, axb::kSmemBytes, st>>>(mq, mk, mv, p);
+  return axb::launch_status();
+}
+
+}  // extern "C"

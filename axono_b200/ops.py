@@ -407,3 +407,25 @@ def argmax_last_dim(x):
     out = torch.empty(x.shape[:-1], dtype=torch.int64, device=x.device)
     _call(_capi.lib().axb200_argmax_last_dim(x.data_ptr(), out.data_ptr(), x.numel() // cols, cols, dt, _stream(x)), op)
     return out
+
+
+def scaled_dot_product_attention(q, k, v, is_causal: bool = False):
+    """q (sq, hq, d), k/v (skv, hkv, d) -> (sq, hq, d); with is_causal row t sees keys [0, t]
+    (axono/python/axono/core/ops/sequence.py scaled_dot_product_attention of the reference)."""
+    op = "scaled_dot_product_attention"
+    dt = _dt(q, op)
+    if q.dim() != 3 or k.dim() != 3 or v.dim() != 3:
+        _capi.check(1, op)
+    if k.dtype != q.dtype or v.dtype != q.dtype:
+        _capi.check(3, op)
+    sq, hq, d = q.shape
+    skv, hkv, dk = k.shape
+    if dk != d or tuple(v.shape) != (skv, hkv, d) or hkv == 0 or hq % hkv != 0:
+        _capi.check(4, op)
+    q, k, v = _c(q), _c(k), _c(v)
+    out = torch.empty_like(q)
+    lib = _capi.lib()
+    ws = workspace(q.device, lib.axb200_sdpa_workspace_bytes(sq, hq, hkv, d, skv, dt))
+    _call(lib.axb200_sdpa(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), sq, hq, hkv, d, skv,
+                          int(bool(is_causal)), dt, ws.data_ptr(), ws.numel(), _stream(q)), op)
+    return out

@@ -616,13 +616,61 @@ def run_reference_cuda(args):
                       "steps": args.steps, "cases": rows}), flush=True)
 
 
+def run_prefill(args):
+    """`prefill`: causal fp16 prefill attention (sq = skv = 8192, 16 q / 8 kv heads, head_dim 128) on the
+    tcgen05 kernel; a tensor-bound kernel, so the roofline is the measured dense GEMM peak."""
+    import torch
+
+    from axono_b200 import ops
+
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    S = args.prefill_len
+    gen = torch.Generator(device="cuda").manual_seed(11)
+    q = torch.randn((S, HQ, D), generator=gen, device="cuda").half()
+    k = torch.randn((S, HKV, D), generator=gen, device="cuda").half()
+    v = torch.randn((S, HKV, D), generator=gen, device="cuda").half()
+    for _ in range(max(3, args.warmup)):
+        ops.scaled_dot_product_attention(q, k, v, True)
+    sampler = ClockSampler(torch.cuda.current_device())
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    sampler.start()
+    torch.cuda.profiler.start()
+    e0.record()
+    for _ in range(args.steps):
+        ops.scaled_dot_product_attention(q, k, v, True)
+    e1.record()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    sampler.pause()
+    ms = e0.elapsed_time(e1) / args.steps
+    flops = 4.0 * HQ * D * (S * (S + 1) / 2)  # causal: QK^T and PV on the lower triangle
+    tflops = flops / (ms / 1e3) / 1e12
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            peak, kind = float(json.load(f)["bf16_tflops"]), "measured"
+    except Exception:
+        peak, kind = 1590.0, "fallback"
+    err = ops.last_error()
+    print(json.dumps({
+        "metric": "prefill_attention_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "prefill", "sq": S, "skv": S, "hq": HQ, "hkv": HKV, "head_dim": D, "causal": True},
+        "tokens_per_s": S / (ms / 1e3), "gpu_launches": args.steps, "error_word": err, "clocks": sampler.summary(),
+        "roofline": {"bound": "tensor", "kernel": "prefill_attn_f16_kernel", "achieved": tflops, "peak": peak,
+                     "unit": "TFLOP/s", "frac": tflops / peak, "peak_source": f"of {kind}", "traffic": None},
+    }), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-cuda"])
-    ap.add_argument("--workload", default="c3_ragged", choices=sorted(WORKLOADS) + ["c2_block", "c5_tower"])
+    ap.add_argument("--workload", default="c3_ragged", choices=sorted(WORKLOADS) + ["c2_block", "c5_tower", "prefill"])
+    ap.add_argument("--prefill-len", type=int, default=8192)
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="weak: every GPU gets its own batch; strong: one batch sharded over the GPUs")
     ap.add_argument("--dtype", default="f16", choices=["f16", "f32"], help="storage type of q/K/V (fp32 accumulation either way)")
@@ -636,9 +684,12 @@ def main():
         if int(os.environ.get("RANK", "0")) == 0:
             run_reference_cuda(args)
     elif args.impl == "reference":
-        if args.workload in ("c2_block", "c5_tower"):
+        if args.workload in ("c2_block", "c5_tower", "prefill"):
             args.workload = "c2_b8_l8k" if args.workload == "c2_block" else "c3_ragged"
         run_reference_arm(args)
+    elif args.workload == "prefill":
+        if int(os.environ.get("RANK", "0")) == 0:
+            run_prefill(args)
     elif args.workload in ("c2_block", "c5_tower"):
         run_tower(args)
     else:

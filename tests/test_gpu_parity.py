@@ -495,3 +495,57 @@ def test_sliding_window_attention(ops, orc, dtype, window):
         assert_close(out[b : b + 1], orc.gqa_decode(q[b : b + 1], k[b, lo:n], v[b, lo:n]), tol)
     assert len(cache) == min(max(lens), window)
     assert ops.last_error() == 0
+
+
+# ---- prefill attention (the SDPA op) ------------------------------------------------------------------------
+
+
+def test_sdpa_reference_shapes_fp32(ops, golden):
+    """The reference's own SDPA test shape (sq 4, skv 6, 4 q / 2 kv heads, d 8), causal and not:
+    tests/core/test_sequence_ops.py:85-111 -> golden vectors from the reference's CPU library."""
+    q, k, v = cases.sdpa_causal_case()
+    assert_close(host(ops.scaled_dot_product_attention(dev(q), dev(k), dev(v), True)), golden["sdpa_causal"], F32_TOL)
+    assert_close(host(ops.scaled_dot_product_attention(dev(q), dev(k), dev(v), False)), golden["sdpa_noncausal"], F32_TOL)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("sq,skv", [(1, 1), (5, 5), (127, 127), (128, 128), (129, 129), (300, 300), (1000, 1000),
+                                    (64, 700), (700, 64), (257, 2049)])
+def test_sdpa_fp16_tensor_core_path(ops, orc, causal, sq, skv):
+    """fp16, head_dim 128: the tcgen05 kernel against the oracle (causal rule: row t sees min(t+1, skv) keys
+    when skv >= t+1, else all)."""
+    rng = np.random.default_rng(sq * 7 + skv)
+    q = widen(rng.standard_normal((sq, 16, 128)).astype(np.float32))
+    k = widen(rng.standard_normal((skv, 8, 128)).astype(np.float32))
+    v = widen(rng.standard_normal((skv, 8, 128)).astype(np.float32))
+    ref = orc.sdpa(q, k, v, causal)
+    out = host(ops.scaled_dot_product_attention(dev(q, torch.float16), dev(k, torch.float16), dev(v, torch.float16), causal))
+    assert_close(out, ref, F16_TOL)
+    assert ops.last_error() == 0
+
+
+@pytest.mark.parametrize("dtype,hq,hkv,d", [(torch.float32, 16, 8, 128), (torch.float32, 4, 2, 64), (torch.float16, 4, 4, 64)])
+def test_sdpa_row_fallback(ops, orc, dtype, hq, hkv, d):
+    rng = np.random.default_rng(d + hq)
+    sq, skv = 70, 300
+    q = rng.standard_normal((sq, hq, d)).astype(np.float32)
+    k = rng.standard_normal((skv, hkv, d)).astype(np.float32)
+    v = rng.standard_normal((skv, hkv, d)).astype(np.float32)
+    if dtype == torch.float16:
+        q, k, v = widen(q), widen(k), widen(v)
+    for causal in (False, True):
+        out = host(ops.scaled_dot_product_attention(dev(q, dtype), dev(k, dtype), dev(v, dtype), causal))
+        assert_close(out, orc.sdpa(q, k, v, causal), F32_TOL if dtype == torch.float32 else F16_TOL)
+
+
+def test_sdpa_prefill_then_decode_consistency(ops, orc):
+    """Prefill's last causal row equals decode attention of that query over the same cache
+    (tests/nn/test_kv_cache.py:117-148 of the reference, at a length its SDPA kernel cannot reach)."""
+    rng = np.random.default_rng(123)
+    s = 2500
+    q = dev(rng.standard_normal((s, 16, 128)).astype(np.float32), torch.float16)
+    k = dev(rng.standard_normal((s, 8, 128)).astype(np.float32), torch.float16)
+    v = dev(rng.standard_normal((s, 8, 128)).astype(np.float32), torch.float16)
+    full = ops.scaled_dot_product_attention(q, k, v, True)
+    last = ops.gqa_decode_attention(q[s - 1 : s].contiguous(), k, v)
+    assert_close(host(full[s - 1 : s]), host(last), 1e-3)
