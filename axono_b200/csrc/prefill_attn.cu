@@ -3,16 +3,16 @@
 // (src/ops/cuda/sequence.cu:105-163,451-472), whose scores live in shared memory (skv*4 bytes, so it
 // cannot pass ~12 K keys) and whose P.V loop is thread-serial.
 //
-// fp16, head_dim 128: one CTA (128 threads, two CTAs per SM) per (block of 128 query rows, query
-// head).  Q, K and V tiles are staged by TMA with 128-byte swizzle; S = Q.K^T (128 x 64 per tile of 64
-// keys) and O += P.V are tcgen05.mma (cta_group::1, kind::f16) with the accumulators in tensor memory
-// (two S buffers and O: 256 columns per CTA); thread t owns query row t: it reads its scores with
-// tcgen05.ld, does the online softmax in registers, writes P (fp16) into shared memory in the
-// swizzled K-major layout the MMA expects and rescales its O row in tensor memory when the running
-// maximum moves.  K/V tiles are double buffered and the next tile's S is issued before the current
-// softmax, so tensor core and softmax overlap; completion of the MMAs is tracked with tcgen05.commit
-// on mbarriers.  Every wait is bounded.  Other dtypes and head sizes run row by row on the decode
-// kernels (correct, not fast).
+// fp16, head_dim 128: one CTA (four softmax warps + one issue warp, two CTAs per SM) per (block of 128
+// query rows, query head).  Q, K and V tiles are staged by TMA with 128-byte swizzle; S = Q.K^T (128 x
+// 64 per tile of 64 keys) and O += P.V are tcgen05.mma (cta_group::1, kind::f16) with the accumulators
+// in tensor memory (two S buffers and O: 256 columns per CTA); thread t owns query row t: it reads
+// its scores with tcgen05.ld, does the online softmax in registers, writes P (fp16) into shared memory
+// in the swizzled K-major layout the MMA expects and rescales its O row in tensor memory when the
+// running maximum moves.  One lane of the issue warp launches every TMA load and MMA; the two sides
+// meet only on mbarriers (tcgen05.commit for MMA completion).  K/V tiles are double buffered and S is
+// computed two tiles ahead, so tensor core and softmax overlap.  Every wait is bounded.  Other dtypes
+// and head sizes run row by row on the decode kernels (correct, not fast).
 //
 // Semantics as the reference's CPU op (src/ops/cpu/sequence.cpp:236-301): q (sq,hq,d), k/v
 // (skv,hkv,d) token-major, head h reads KV head h / (hq/hkv), scale 1/sqrt(d); with is_causal row t
@@ -34,7 +34,8 @@ size_t sdpa_rows_workspace_bytes(int sq, int hq, int hkv, int d, int64_t skv);
 namespace {
 
 constexpr int kBlockM = 128, kBlockN = 64, kD = 128;
-constexpr int kThreads = 128;
+constexpr int kSoftmaxWarps = 4;
+constexpr int kThreads = (kSoftmaxWarps + 1) * 32;  // + the issue warp
 constexpr int kQTileBytes = kBlockM * kD * 2;   // 32 KB: two swizzled boxes of [128 rows][64 halves]
 constexpr int kKvTileBytes = kBlockN * kD * 2;  // 16 KB: two swizzled boxes of [64 rows][64 halves]
 constexpr int kPTileBytes = kBlockM * kBlockN * 2;  // 16 KB: one swizzled box of [128 rows][64 keys]
@@ -103,43 +104,43 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-// 128 threads: thread t owns query row t of the block (tensor-memory lane t) and all 64 key columns of
-// a tile, so the row maximum and sum need no exchange.  Two CTAs share an SM (112 KB of shared
-// memory and 256 tensor-memory columns each), which hides one CTA's dependency chain - TMEM read,
-// exponentials, P store, barrier - behind the other's.  Software pipeline over the KV tiles:
-// S_{j+1} = Q.K_{j+1}^T is issued before the softmax of tile j starts (two S buffers), and
-// O += P_j.V_j right after it.
+// 160 threads.  Warps 0-3 (softmax): thread t owns query row t of the block (tensor-memory lane t)
+// and all 64 key columns of a tile, so the row maximum and sum need no exchange.  Warp 4 (one lane):
+// issues every TMA load and every MMA, so the softmax warps never wait behind issue work; the two
+// sides meet only on mbarriers (bar_s: S_j ready; bar_p: P_j written and S buffer j&1 free; bar_o:
+// P_j.V_j done).  Software pipeline: S_{j+2} = Q.K_{j+2}^T is issued right after P_j.V_j, while the
+// softmax warps are already in tile j+1 (two S buffers).  Two CTAs share an SM (112 KB of shared
+// memory and 256 tensor-memory columns each).
 __global__ void __launch_bounds__(kThreads, 2)
 prefill_attn_f16_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                         const __grid_constant__ CUtensorMap tmV, const PrefillParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kOffBar);
-  uint64_t *bar_q = bars, *bar_k = bars + 1, *bar_v = bars + 3, *bar_s = bars + 5, *bar_o = bars + 7;
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 8);
-  volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + 9);
+  uint64_t *bar_q = bars, *bar_k = bars + 1, *bar_v = bars + 3, *bar_s = bars + 5, *bar_o = bars + 7, *bar_p = bars + 8;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 9);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + 10);
 
   // the swizzled tiles need a 1024-byte aligned base; refuse to run otherwise (nothing is written)
   if ((smem_u32(smem) & 1023u) != 0) {
     if (threadIdx.x == 0) atomicOr(&g_error_word, AXB200_ERR_WAIT_TIMEOUT);
     return;
   }
-  const int qb = blockIdx.x, h = blockIdx.y;
+  // heaviest blocks first: under a causal mask the last query block has the most key tiles
+  const int qb = gridDim.x - 1 - blockIdx.x, h = blockIdx.y;
   const int hk = h / (p.hq / p.hkv);
   const int q0 = qb * kBlockM;
-  const int warp = threadIdx.x >> 5;
-  const int row = threadIdx.x;
-  const int t_row = q0 + row;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t_last = min(q0 + kBlockM, p.sq) - 1;
   const int kv_end_max = p.causal ? min(t_last + 1, p.skv) : p.skv;  // reference rule: min(t+1, skv)
   const int nkv = (kv_end_max + kBlockN - 1) / kBlockN;
-  const int kv_end = p.causal ? min(t_row + 1, p.skv) : p.skv;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < 8; ++i) mbar_init(&bars[i], 1);
+    mbar_init(bar_p, kSoftmaxWarps);
     *abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 0) {
+  if (warp == kSoftmaxWarps) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 256;" ::"r"(smem_u32(tmem_slot)) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -147,146 +148,63 @@ prefill_attn_f16_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot, tmem_o = tmem_base + 128;  // S buffers at columns 0 and 64
-  const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-  // instruction descriptors: fp32 accumulate, fp16 operands, M = 128.  Q.K^T: N = 64 keys, B K-major;
-  // P.V: N = 128 dims, B MN-major (a V tile is [keys][d], d contiguous)
-  const uint32_t idesc_qk = (1u << 4) | ((kBlockN >> 3) << 17) | ((kBlockM >> 4) << 24);
-  const uint32_t idesc_pv = (1u << 4) | (1u << 16) | ((kD >> 3) << 17) | ((kBlockM >> 4) << 24);
-  const uint32_t q_addr = smem_u32(smem + kOffQ), p_addr = smem_u32(smem + kOffP);
 
-  auto load_k = [&](int j) {
-    const int s = j & 1;
-    uint8_t *ks = smem + kOffK + s * kKvTileBytes;
-    mbar_arrive_expect_tx(&bar_k[s], kKvTileBytes);
-    tma_load_3d(ks, &tmK, &bar_k[s], 0, hk, j * kBlockN);
-    tma_load_3d(ks + kKvTileBytes / 2, &tmK, &bar_k[s], 64, hk, j * kBlockN);
-  };
-  auto load_v = [&](int j) {
-    const int s = j & 1;
-    uint8_t *vs = smem + kOffV + s * kKvTileBytes;
-    mbar_arrive_expect_tx(&bar_v[s], kKvTileBytes);
-    tma_load_3d(vs, &tmV, &bar_v[s], 0, hk, j * kBlockN);
-    tma_load_3d(vs + kKvTileBytes / 2, &tmV, &bar_v[s], 64, hk, j * kBlockN);
-  };
-  // S_j = Q . K_j^T into S buffer j&1; arrives on bar_s[j&1]
-  auto issue_s = [&](int j) -> bool {
-    const int s = j & 1;
-    if (!mbar_wait_bounded(&bar_k[s], (j >> 1) & 1, abort_flag)) return false;
-    tc_fence_after();
-    const uint32_t k_addr = smem_u32(smem + kOffK + s * kKvTileBytes);
+  if (warp == kSoftmaxWarps) {
+    // ================= issue warp: TMA loads and MMAs, one lane =================
+    if (lane == 0) {
+      // instruction descriptors: fp32 accumulate, fp16 operands, M = 128.  Q.K^T: N = 64 keys, B
+      // K-major; P.V: N = 128 dims, B MN-major (a V tile is [keys][d], d contiguous)
+      const uint32_t idesc_qk = (1u << 4) | ((kBlockN >> 3) << 17) | ((kBlockM >> 4) << 24);
+      const uint32_t idesc_pv = (1u << 4) | (1u << 16) | ((kD >> 3) << 17) | ((kBlockM >> 4) << 24);
+      const uint32_t q_addr = smem_u32(smem + kOffQ), p_addr = smem_u32(smem + kOffP);
+      auto load_k = [&](int j) {
+        const int s = j & 1;
+        uint8_t *ks = smem + kOffK + s * kKvTileBytes;
+        mbar_arrive_expect_tx(&bar_k[s], kKvTileBytes);
+        tma_load_3d(ks, &tmK, &bar_k[s], 0, hk, j * kBlockN);
+        tma_load_3d(ks + kKvTileBytes / 2, &tmK, &bar_k[s], 64, hk, j * kBlockN);
+      };
+      auto load_v = [&](int j) {
+        const int s = j & 1;
+        uint8_t *vs = smem + kOffV + s * kKvTileBytes;
+        mbar_arrive_expect_tx(&bar_v[s], kKvTileBytes);
+        tma_load_3d(vs, &tmV, &bar_v[s], 0, hk, j * kBlockN);
+        tma_load_3d(vs + kKvTileBytes / 2, &tmV, &bar_v[s], 64, hk, j * kBlockN);
+      };
+      // S_j = Q . K_j^T into S buffer j&1; arrives on bar_s[j&1]
+      auto issue_s = [&](int j) -> bool {
+        const int s = j & 1;
+        if (!mbar_wait_bounded(&bar_k[s], (j >> 1) & 1, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(smem + kOffK + s * kKvTileBytes);
 #pragma unroll
-    for (int ks = 0; ks < 8; ++ks) {  // head_dim 128 = 8 steps of 16; each 64-wide half of d is one box
-      const uint32_t q_off = (ks >> 2) * (kQTileBytes / 2) + (ks & 3) * 32;
-      const uint32_t k_off = (ks >> 2) * (kKvTileBytes / 2) + (ks & 3) * 32;
-      umma_f16(tmem_base + s * kBlockN, smem_desc(q_addr + q_off, 16, 1024), smem_desc(k_addr + k_off, 16, 1024),
-               idesc_qk, ks > 0);
-    }
-    umma_commit(&bar_s[s]);
-    return true;
-  };
-
-  bool ok = true;
-  if (threadIdx.x == 0) {
-    tma_prefetch_descriptor(&tmQ);
-    tma_prefetch_descriptor(&tmK);
-    tma_prefetch_descriptor(&tmV);
-    mbar_arrive_expect_tx(bar_q, kQTileBytes);
-    tma_load_3d(smem + kOffQ, &tmQ, bar_q, 0, h, q0);
-    tma_load_3d(smem + kOffQ + kQTileBytes / 2, &tmQ, bar_q, 64, h, q0);
-    load_k(0);
-    load_v(0);
-    if (nkv > 1) {
-      load_k(1);
-      load_v(1);
-    }
-    ok = mbar_wait_bounded(bar_q, 0, abort_flag) && issue_s(0);
-  }
-  __syncwarp();
-  // Loop control is uniform: a failed (timed-out) wait raises the CTA's abort flag, and the loop is
-  // left only at the one point where every thread has just passed the same __syncthreads.
-
-  float m_run = -INFINITY, l_run = 0.f;
-  uint8_t *p_row = smem + kOffP + row * 128;
-
-  for (int j = 0; j < nkv; ++j) {
-    const int sb = j & 1;
-    if (threadIdx.x == 0 && ok && j + 1 < nkv) ok = issue_s(j + 1);  // runs under the softmax below
-    __syncwarp();
-    const bool s_ready = mbar_wait_bounded(&bar_s[sb], (j >> 1) & 1, abort_flag);
-    tc_fence_after();
-    if (threadIdx.x == 0 && ok && s_ready && j + 2 < nkv) load_k(j + 2);  // K stage j&1 is free: S_j is done
-    __syncwarp();
-
-    // ---- this thread's row of scores: 64 keys ----
-    const int n0 = j * kBlockN;
-    const bool edge = n0 + kBlockN > kv_end;
-    uint32_t sr[2][32];
-    tmem_ld32(tmem_base + sb * kBlockN + lane_base, sr[0]);
-    tmem_ld32(tmem_base + sb * kBlockN + lane_base + 32, sr[1]);
-    if (edge) {
-#pragma unroll
-      for (int c = 0; c < 2; ++c)
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (n0 + c * 32 + i >= kv_end) sr[c][i] = 0xff800000u;  // -inf
-    }
-    // four independent chains keep the 64-long reductions off the critical path
-    float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-    for (int c = 0; c < 2; ++c)
-#pragma unroll
-      for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sr[c][i]));
-    const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-    const float m_new = fmaxf(m_run, mx * p.scale_log2);
-    const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
-    const float corr = fast_exp2(m_run - m_safe);
-    m_run = m_new;
-    uint32_t packed[32];
-    float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int c = 0; c < 2; ++c)
-#pragma unroll
-      for (int i = 0; i < 32; i += 2) {
-        const float a = fast_exp2(fmaf(__uint_as_float(sr[c][i]), p.scale_log2, -m_safe));
-        const float b = fast_exp2(fmaf(__uint_as_float(sr[c][i + 1]), p.scale_log2, -m_safe));
-        sum4[(i >> 1) & 3] += a + b;
-        packed[c * 16 + (i >> 1)] = pack_half2(a, b);
+        for (int ks = 0; ks < 8; ++ks) {  // head_dim 128 = 8 steps of 16; each 64-wide half of d is one box
+          const uint32_t q_off = (ks >> 2) * (kQTileBytes / 2) + (ks & 3) * 32;
+          const uint32_t k_off = (ks >> 2) * (kKvTileBytes / 2) + (ks & 3) * 32;
+          umma_f16(tmem_base + s * kBlockN, smem_desc(q_addr + q_off, 16, 1024), smem_desc(k_addr + k_off, 16, 1024),
+                   idesc_qk, ks > 0);
+        }
+        umma_commit(&bar_s[s]);
+        return true;
+      };
+      tma_prefetch_descriptor(&tmQ);
+      tma_prefetch_descriptor(&tmK);
+      tma_prefetch_descriptor(&tmV);
+      mbar_arrive_expect_tx(bar_q, kQTileBytes);
+      tma_load_3d(smem + kOffQ, &tmQ, bar_q, 0, h, q0);
+      tma_load_3d(smem + kOffQ + kQTileBytes / 2, &tmQ, bar_q, 64, h, q0);
+      load_k(0);
+      load_v(0);
+      if (nkv > 1) {
+        load_k(1);
+        load_v(1);
       }
-    l_run = l_run * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
-
-    // P and O are still in use by P_{j-1}.V_{j-1} until it completes
-    if (j > 0) {
-      const bool o_ready = mbar_wait_bounded(bar_o, (j - 1) & 1, abort_flag);
-      tc_fence_after();
-      if (threadIdx.x == 0 && ok && o_ready && j + 1 < nkv) load_v(j + 1);  // V stage (j+1)&1 is free now
-      __syncwarp();
-    }
-    // the row's 64 keys = eight 16-byte chunks, swizzled by row % 8 (K-major A operand of P.V)
-#pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      uint8_t *dst = p_row + ((u ^ (row & 7)) << 4);
-      *reinterpret_cast<uint4 *>(dst) = make_uint4(packed[u * 4], packed[u * 4 + 1], packed[u * 4 + 2], packed[u * 4 + 3]);
-    }
-    // rescale this row of O in tensor memory when some row of the warp moved its maximum
-    if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tmem_o + lane_base + c * 32, r);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * corr);
-        tmem_st32(tmem_o + lane_base + c * 32, r);
-      }
-      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-    }
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P is read by the tensor core
-    tc_fence_before();
-    __syncthreads();
-    if (*abort_flag) break;  // uniform: every thread reads the flag after the same barrier
-    if (threadIdx.x == 0 && ok) {
-      // O += P_j . V_j
-      ok = mbar_wait_bounded(&bar_v[j & 1], (j >> 1) & 1, abort_flag);
-      if (ok) {
+      bool ok = mbar_wait_bounded(bar_q, 0, abort_flag) && issue_s(0);
+      if (ok && nkv > 1) ok = issue_s(1);
+      for (int j = 0; j < nkv && ok; ++j) {
+        // P_j is written and S buffer j&1 has been read: O += P_j . V_j, then S_{j+2} into that buffer
+        ok = mbar_wait_bounded(bar_p, j & 1, abort_flag) && mbar_wait_bounded(&bar_v[j & 1], (j >> 1) & 1, abort_flag);
+        if (!ok) break;
         tc_fence_after();
         const uint32_t v_addr = smem_u32(smem + kOffV + (j & 1) * kKvTileBytes);
 #pragma unroll
@@ -297,37 +215,126 @@ prefill_attn_f16_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
                    smem_desc(v_addr + ks * 2048, kKvTileBytes / 2, 1024), idesc_pv, j > 0 || ks > 0);
         }
         umma_commit(bar_o);
+        if (j + 2 < nkv) {
+          // K stage j&1 was consumed by S_j long ago: its next tile may already be in flight
+          if (j == 0) load_k(2);
+          ok = issue_s(j + 2);
+          if (!ok) break;
+          // V stage j&1 and K stage (j+1)&1 are free once P_j.V_j (and S_{j+1}) have completed
+          ok = mbar_wait_bounded(bar_o, j & 1, abort_flag);
+          if (!ok) break;
+          load_v(j + 2);
+          if (j + 3 < nkv) load_k(j + 3);
+        }
       }
     }
-    __syncwarp();
-  }
+  } else {
+    // ================= softmax warps =================
+    const int row = threadIdx.x;
+    const int t_row = q0 + row;
+    const int kv_end = p.causal ? min(t_row + 1, p.skv) : p.skv;
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    float m_run = -INFINITY, l_run = 0.f;
+    uint8_t *p_row = smem + kOffP + row * 128;
+    bool ok = true;
+    for (int j = 0; j < nkv && ok; ++j) {
+      const int sb = j & 1;
+      ok = mbar_wait_bounded(&bar_s[sb], (j >> 1) & 1, abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      // ---- this thread's row of scores: 64 keys ----
+      const int n0 = j * kBlockN;
+      uint32_t sr[2][32];
+      tmem_ld32(tmem_base + sb * kBlockN + lane_base, sr[0]);
+      tmem_ld32(tmem_base + sb * kBlockN + lane_base + 32, sr[1]);
+      if (n0 + kBlockN > kv_end) {
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (n0 + c * 32 + i >= kv_end) sr[c][i] = 0xff800000u;  // -inf
+      }
+      // four independent chains keep the 64-long reductions off the critical path
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < 2; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sr[c][i]));
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      const float m_new = fmaxf(m_run, mx * p.scale_log2);
+      const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
+      const float corr = fast_exp2(m_run - m_safe);
+      m_run = m_new;
+      uint32_t packed[32];
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int c = 0; c < 2; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float a = fast_exp2(fmaf(__uint_as_float(sr[c][i]), p.scale_log2, -m_safe));
+          const float b = fast_exp2(fmaf(__uint_as_float(sr[c][i + 1]), p.scale_log2, -m_safe));
+          sum4[(i >> 1) & 3] += a + b;
+          packed[c * 16 + (i >> 1)] = pack_half2(a, b);
+        }
+      l_run = l_run * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
 
-  // ---- epilogue: O / l -> out ----
-  if (!*abort_flag) mbar_wait_bounded(bar_o, (nkv - 1) & 1, abort_flag);
-  tc_fence_after();
-  if (!*abort_flag) {
-    const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
-    __half *dst = reinterpret_cast<__half *>(p.out) + ((size_t)t_row * p.hq + h) * kD;
+      // P and O are still in use by P_{j-1}.V_{j-1} until it completes
+      if (j > 0) {
+        ok = mbar_wait_bounded(bar_o, (j - 1) & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+      }
+      // the row's 64 keys = eight 16-byte chunks, swizzled by row % 8 (K-major A operand of P.V)
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      uint32_t r[32];
-      tmem_ld32(tmem_o + lane_base + c * 32, r);
-      if (t_row < p.sq) {
+      for (int u = 0; u < 8; ++u) {
+        uint8_t *dst = p_row + ((u ^ (row & 7)) << 4);
+        *reinterpret_cast<uint4 *>(dst) = make_uint4(packed[u * 4], packed[u * 4 + 1], packed[u * 4 + 2], packed[u * 4 + 3]);
+      }
+      // rescale this row of O in tensor memory when some row of the warp moved its maximum
+      if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          uint4 w;
-          w.x = pack_half2(__uint_as_float(r[u * 8 + 0]) * inv, __uint_as_float(r[u * 8 + 1]) * inv);
-          w.y = pack_half2(__uint_as_float(r[u * 8 + 2]) * inv, __uint_as_float(r[u * 8 + 3]) * inv);
-          w.z = pack_half2(__uint_as_float(r[u * 8 + 4]) * inv, __uint_as_float(r[u * 8 + 5]) * inv);
-          w.w = pack_half2(__uint_as_float(r[u * 8 + 6]) * inv, __uint_as_float(r[u * 8 + 7]) * inv);
-          *reinterpret_cast<uint4 *>(dst + c * 32 + u * 8) = w;
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          tmem_ld32(tmem_o + lane_base + c * 32, r);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * corr);
+          tmem_st32(tmem_o + lane_base + c * 32, r);
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P is read by the tensor core
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_p);
+    }
+    // ---- epilogue: O / l -> out ----
+    if (ok) ok = mbar_wait_bounded(bar_o, (nkv - 1) & 1, abort_flag);
+    tc_fence_after();
+    if (ok) {
+      const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+      __half *dst = reinterpret_cast<__half *>(p.out) + ((size_t)t_row * p.hq + h) * kD;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem_o + lane_base + c * 32, r);
+        if (t_row < p.sq) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            uint4 w;
+            w.x = pack_half2(__uint_as_float(r[u * 8 + 0]) * inv, __uint_as_float(r[u * 8 + 1]) * inv);
+            w.y = pack_half2(__uint_as_float(r[u * 8 + 2]) * inv, __uint_as_float(r[u * 8 + 3]) * inv);
+            w.z = pack_half2(__uint_as_float(r[u * 8 + 4]) * inv, __uint_as_float(r[u * 8 + 5]) * inv);
+            w.w = pack_half2(__uint_as_float(r[u * 8 + 6]) * inv, __uint_as_float(r[u * 8 + 7]) * inv);
+            *reinterpret_cast<uint4 *>(dst + c * 32 + u * 8) = w;
+          }
         }
       }
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;" ::"r"(tmem_base) : "memory");
+  if (warp == kSoftmaxWarps)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;" ::"r"(tmem_base) : "memory");
 }
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
