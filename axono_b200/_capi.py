@@ -38,6 +38,8 @@ SIGNATURES = {
     "axb200_p2p_free": (_i, [_vp]),
     "axb200_kv_append_rope": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i, _i, _i,
                                    _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp]),
+    "axb200_kv_prefill_write": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i, _i, _i, _i64, _i, _i, _i,
+                                     _i, _i, _i, _i64, _i, _vp]),
     "axb200_qkv_norm_rope_append": (_i, [_vp, _i64, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i, _i,
                                          _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "axb200_silu_mul_rows": (_i, [_vp, _i64, _i, _i64, _vp, _i, _vp]),

@@ -216,6 +216,93 @@ kv_append_rope_kernel(const AppendParams p, const InvFreqTable table) {
   }
 }
 
+// ---- prefill write: many tokens of ONE sequence into its pages -------------------------------------
+// After a prefill the reference stores the whole (seq,hkv,d) K/V of the prompt as the cache
+// (axono/python/axono/nn/kv_cache.py:96-100) with K already rotated by rope / rope_thd
+// (examples/vlm/qwen3vl/model.py:358-362).  Here: one CTA per token; rotates q (in place, optional) and
+// k with the token's own position(s) and scatters k/v into the sequence's pages at slots
+// start .. start + n - 1.  The length is set by the host side afterwards (one store).
+struct PrefillWriteParams {
+  void *q;  // (n, hq, d) or null
+  const void *k, *v;  // (n, hkv, d)
+  void *k_pages, *v_pages;
+  const int32_t *block_row;  // this sequence's row of the block table
+  const int64_t *pos;        // (n) or (3, n) or null -> start + i
+  const float *inv_freq_dev;
+  int rotate, mrope, h_lim, w_lim;
+  int n, hq, hkv, d, page_tokens, max_blocks, num_pages, start;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+kv_prefill_write_kernel(const PrefillWriteParams p, const InvFreqTable table) {
+  const int i_tok = blockIdx.x;
+  const int slot_tok = p.start + i_tok;
+  const int half = p.d / 2;
+  float pt, ph, pw;
+  if (p.pos == nullptr) {
+    pt = ph = pw = (float)slot_tok;
+  } else if (p.mrope) {
+    pt = (float)p.pos[i_tok];
+    ph = (float)p.pos[p.n + i_tok];
+    pw = (float)p.pos[2 * p.n + i_tok];
+  } else {
+    pt = ph = pw = (float)p.pos[i_tok];
+  }
+  const int blk = slot_tok / p.page_tokens;
+  int page = -1;
+  if (blk < p.max_blocks) page = p.block_row[blk];
+  const bool page_ok = page >= 0 && page < p.num_pages;
+  if (!page_ok && threadIdx.x == 0)
+    atomicOr(&g_error_word, blk < p.max_blocks ? AXB200_ERR_BAD_PAGE : AXB200_ERR_CAPACITY);
+  const int tok = slot_tok % p.page_tokens;
+
+  __shared__ float s_cos[kMaxHalf], s_sin[kMaxHalf];
+  if (p.rotate) {
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+      const float f = p.mrope || p.inv_freq_dev ? p.inv_freq_dev[i] : table.f[i];
+      const float posv = p.mrope ? pair_position(i, pt, ph, pw, p.h_lim, p.w_lim) : pt;
+      sincosf(posv * f, &s_sin[i], &s_cos[i]);
+    }
+    __syncthreads();
+  }
+  T *q = p.q ? reinterpret_cast<T *>(p.q) + (size_t)i_tok * p.hq * p.d : nullptr;
+  const T *kn = reinterpret_cast<const T *>(p.k) + (size_t)i_tok * p.hkv * p.d;
+  const T *vn = reinterpret_cast<const T *>(p.v) + (size_t)i_tok * p.hkv * p.d;
+  const int q_pairs = q ? p.hq * half : 0, k_pairs = p.hkv * half;
+  for (int idx = threadIdx.x; idx < q_pairs + k_pairs; idx += blockDim.x) {
+    const bool is_q = idx < q_pairs;
+    const int j = is_q ? idx : idx - q_pairs;
+    const int h = j / half, i = j % half;
+    const float c = p.rotate ? s_cos[i] : 1.f, sn = p.rotate ? s_sin[i] : 0.f;
+    if (is_q) {
+      if (p.rotate) {
+        T *row = q + (size_t)h * p.d;
+        const float a = ld(row + i), bb = ld(row + i + half);
+        st(row + i, a * c - bb * sn);
+        st(row + i + half, bb * c + a * sn);
+      }
+    } else if (page_ok) {
+      const T *row = kn + (size_t)h * p.d;
+      T *dst = reinterpret_cast<T *>(p.k_pages) + (((size_t)page * p.hkv + h) * p.page_tokens + tok) * p.d;
+      if (p.rotate) {
+        const float a = ld(row + i), bb = ld(row + i + half);
+        st(dst + i, a * c - bb * sn);
+        st(dst + i + half, bb * c + a * sn);
+      } else {
+        dst[i] = row[i];
+        dst[i + half] = row[i + half];
+      }
+    }
+  }
+  if (page_ok) {
+    for (int idx = threadIdx.x; idx < p.hkv * p.d; idx += blockDim.x) {
+      const int h = idx / p.d, c = idx % p.d;
+      reinterpret_cast<T *>(p.v_pages)[(((size_t)page * p.hkv + h) * p.page_tokens + tok) * p.d + c] = vn[idx];
+    }
+  }
+}
+
 // ---- per-head norm + rotate + append straight from the QKV projection output ----------------------
 // The reference's layer runs, after the QKV GEMM: reshape, rms_norm(q), rms_norm(k) over head_dim
 // (examples/vlm/qwen3vl/model.py:353-357), rope on both (:358-359), cache.update (:362).  Here one
@@ -466,6 +553,49 @@ int axb200_kv_append_rope(void *q, const void *k_new, const void *v_new, void *k
     axb::kv_append_rope_kernel<float><<<batch, 256, 0, st>>>(p, table);
   else
     axb::kv_append_rope_kernel<__half><<<batch, 256, 0, st>>>(p, table);
+  return axb::launch_status();
+}
+
+int axb200_kv_prefill_write(void *q, const void *k, const void *v, void *k_pages, void *v_pages,
+                            const int32_t *block_row, const int64_t *pos, const float *inv_freq,
+                            float theta, int rotate, int mrope, int h_sec, int w_sec, int64_t n, int hq,
+                            int hkv, int d, int page_tokens, int max_blocks, int num_pages,
+                            int64_t start, int dtype, void *stream) {
+  if (dtype != AXB200_FLOAT32 && dtype != AXB200_FLOAT16) return AXB200_UNSUPPORTED_TYPE;
+  if (!k || !v || !k_pages || !v_pages || !block_row) return AXB200_INVALID_PTR;
+  if (n < 0 || n > 0x7fffffff || hq < 0 || hkv <= 0 || d <= 0 || d % 2 != 0 || d / 2 > axb::kMaxHalf ||
+      page_tokens <= 0 || max_blocks <= 0 || num_pages <= 0 || start < 0 || start + n > 0x7fffffff)
+    return AXB200_INVALID_ARGUMENT;
+  if (rotate && mrope && !inv_freq) return AXB200_INVALID_PTR;
+  if (n == 0) return AXB200_OK;
+  axb::PrefillWriteParams p{};
+  p.q = q;
+  p.k = k;
+  p.v = v;
+  p.k_pages = k_pages;
+  p.v_pages = v_pages;
+  p.block_row = block_row;
+  p.pos = pos;
+  p.inv_freq_dev = inv_freq;
+  p.rotate = rotate;
+  p.mrope = mrope;
+  p.h_lim = h_sec * 3;
+  p.w_lim = w_sec * 3;
+  p.n = (int)n;
+  p.hq = hq;
+  p.hkv = hkv;
+  p.d = d;
+  p.page_tokens = page_tokens;
+  p.max_blocks = max_blocks;
+  p.num_pages = num_pages;
+  p.start = (int)start;
+  axb::InvFreqTable table{};
+  if (rotate && !inv_freq) axb::fill_table(&table, theta, d);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == AXB200_FLOAT32)
+    axb::kv_prefill_write_kernel<float><<<(unsigned)n, 256, 0, st>>>(p, table);
+  else
+    axb::kv_prefill_write_kernel<__half><<<(unsigned)n, 256, 0, st>>>(p, table);
   return axb::launch_status();
 }
 

@@ -48,6 +48,17 @@ class KVCache:
                              theta=theta, pos=pos, inv_freq=inv_freq, mrope_section=mrope_section)
         return out_host
 
+    def prefill(self, layer_idx: int, b: int, q, k, v, pos=None, inv_freq=None, theta=10000.0, mrope_section=None,
+                rotate=True, set_length=True):
+        """Stores a prompt: k, v (n,hkv,d) of sequence `b` go to slots 0..n-1 with k rotated (q (n,hq,d)
+        too, in place, when given).  With set_length the sequence's length becomes n."""
+        ops.kv_prefill_write(q, k, v, self.k_pages[layer_idx], self.v_pages[layer_idx], self.block_table[b], 0,
+                             pos=pos, inv_freq=inv_freq, theta=theta, mrope_section=mrope_section, rotate=rotate)
+        if set_length:
+            self.seq_lens[b : b + 1].fill_(k.shape[0])
+            self._host_len_bound = max(self._host_len_bound, int(k.shape[0]))
+        return q
+
     def get(self, layer_idx: int):  # pragma: no cover
         raise NotImplementedError
 

@@ -184,6 +184,27 @@ def kv_append_rope(q, k_new, v_new, k_pages, v_pages, block_table, seq_lens, pos
     return q
 
 
+def kv_prefill_write(q, k, v, k_pages, v_pages, block_row, start=0, pos=None, inv_freq=None, theta=10000.0,
+                     mrope_section=None, rotate=True):
+    """Writes the n tokens k, v (n,hkv,d) of one sequence into its pages at slots start.., rotating k (and
+    q (n,hq,d) in place when given) with each token's position: pos int64 (n) / (3,n) / None = start+i."""
+    op = "kv_prefill_write"
+    dt = _dt(k, op)
+    n, hkv, d = k.shape
+    num_pages, _, page_tokens, _ = k_pages.shape
+    mrope = mrope_section is not None
+    h_sec, w_sec = (mrope_section[1], mrope_section[2]) if mrope else (0, 0)
+    for t in (q, k, v):
+        if t is not None and not t.is_contiguous():
+            raise RuntimeError(f"{op}: tensors must be contiguous")
+    _call(_capi.lib().axb200_kv_prefill_write(
+        _ptr(q), k.data_ptr(), v.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_row.data_ptr(),
+        _ptr(pos), _ptr(inv_freq), float(theta), int(rotate), int(mrope), h_sec, w_sec, n,
+        q.shape[1] if q is not None else 0, hkv, d, page_tokens, block_row.numel(), num_pages, int(start), dt,
+        _stream(k)), op)
+    return q
+
+
 def qkv_norm_rope_append(qkv, n_q_heads, q_norm_weight, k_norm_weight, eps, k_pages, v_pages, block_table, seq_lens,
                          pos=None, inv_freq=None, theta=10000.0, mrope_section=None, rotate=True, advance=True,
                          slot_delta=0):

@@ -455,7 +455,7 @@ def run_tower(args):
     gen = torch.Generator(device=device).manual_seed(77 + rank)
     total_steps = args.warmup + args.steps + 2
     if args.workload == "c5_tower":
-        B, L = 32, 16384
+        B, L = args.tower_batch, args.tower_len
         cfg = TextTowerConfig()
         tower = TextTower(cfg, B, L + total_steps + 64, device=device, world=world, rank=rank, seed=5,
                           fused_gather=args.gather == "fused")
@@ -671,6 +671,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-cuda"])
     ap.add_argument("--workload", default="c3_ragged", choices=sorted(WORKLOADS) + ["c2_block", "c5_tower", "prefill"])
     ap.add_argument("--prefill-len", type=int, default=8192)
+    ap.add_argument("--tower-batch", type=int, default=32, help="c5_tower: batch (default: the configuration's 32)")
+    ap.add_argument("--tower-len", type=int, default=16384, help="c5_tower: context length (default 16384)")
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="weak: every GPU gets its own batch; strong: one batch sharded over the GPUs")
     ap.add_argument("--dtype", default="f16", choices=["f16", "f32"], help="storage type of q/K/V (fp32 accumulation either way)")

@@ -225,6 +225,19 @@ int axb200_kv_append_rope(void *q, const void *k_new, const void *v_new,
                           int page_tokens, int max_blocks, int num_pages,
                           int dtype, int slot_delta, int advance, void *stream);
 
+/* Prefill side of the cache: writes n tokens of ONE sequence - k, v (n,hkv,d) token-major - into its
+ * pages at slots start .. start+n-1 (block_row = the sequence's row of the block table), rotating k
+ * (and q (n,hq,d) in place, when given) with each token's own position: pos int64 (n), or (3,n) with
+ * mrope, or NULL for start + i.  It replaces rope|rope_thd over the prompt followed by the first
+ * cache.update (axono/python/examples/vlm/qwen3vl/model.py:358-362,
+ * axono/python/axono/nn/kv_cache.py:96-100).  The caller sets the sequence's length afterwards. */
+int axb200_kv_prefill_write(void *q, const void *k, const void *v, void *k_pages, void *v_pages,
+                            const int32_t *block_row, const int64_t *pos, const float *inv_freq,
+                            float theta, int rotate, int mrope, int h_sec, int w_sec,
+                            int64_t n, int hq, int hkv, int d,
+                            int page_tokens, int max_blocks, int num_pages, int64_t start,
+                            int dtype, void *stream);
+
 /* The same step taken straight from the QKV projection's output, with the per-head RMS norms the
  * reference's text tower applies in between (axono/python/examples/vlm/qwen3vl/model.py:353-362:
  * reshape, rms_norm(q, q_norm), rms_norm(k, k_norm), rope_thd / rope on q and k, cache.update): one

@@ -381,3 +381,50 @@ def test_context_parallel_single_rank_matches_plain():
             assert torch.all(got[1] == 0)  # the empty sequence
         assert ops.last_error() == 0
         pe.close()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_prefill_then_decode_flow(dtype):
+    """Prompt -> causal prefill attention (tensor-core kernel for fp16) -> rotated K and V written to the
+    pages -> one decode step; every stage against the oracle, M-RoPE positions of the multimodal prefix."""
+    from axono_b200 import ops
+    from axono_b200.kv_cache import PagedKVCache
+
+    orc = oracle.best()
+    rng = np.random.default_rng(9500)
+    n, hq, hkv, d = 600, 16, 8, 128
+    sec = (24, 20, 20)
+    inv = cases.inv_freq(1e6)
+    pos3 = cases.build_mrope_pos3(n, 10, 400, 20, 20)
+    conv = widen if dtype == torch.float16 else (lambda a: a)
+    tol = F16_TOL if dtype == torch.float16 else 1e-5
+    q = conv(rng.standard_normal((n, hq, d)).astype(np.float32))
+    k = conv(rng.standard_normal((n, hkv, d)).astype(np.float32))
+    v = conv(rng.standard_normal((n, hkv, d)).astype(np.float32))
+    cache = PagedKVCache(1, 2, hkv, d, 1024, dtype=dtype,
+                         page_order=torch.from_numpy(rng.permutation(32).astype(np.int32)))
+    qd = dev(q, dtype)
+    cache.prefill(0, 1, qd, dev(k, dtype), dev(v, dtype), pos=dev(pos3), inv_freq=dev(inv), mrope_section=sec)
+    q_ref, k_ref = orc.rope_thd(q, pos3, inv, sec), orc.rope_thd(k, pos3, inv, sec)
+    assert oracle.rel_err(host(qd), q_ref) <= tol
+    kb, vb = cache.gather(0, 1)
+    assert kb.shape[0] == n and oracle.rel_err(host(kb), k_ref) <= tol
+    assert torch.equal(vb, dev(v, dtype))  # values are a byte copy
+    assert cache.seq_lens.cpu().tolist() == [0, n]
+    # prefill attention over the rotated tensors, as the model computes it before caching
+    attn = ops.scaled_dot_product_attention(qd, kb, vb, True)
+    ref_attn = orc.sdpa(conv(q_ref), conv(k_ref) if dtype == torch.float16 else host(kb), v, True)
+    assert oracle.rel_err(host(attn), ref_attn) <= (4e-3 if dtype == torch.float16 else 1e-5)
+    # one decode step on top
+    rope_delta = 20 - 400
+    dec = np.full((3, 2), n + rope_delta, np.int64)
+    qn = conv(rng.standard_normal((2, hq, d)).astype(np.float32))
+    kn = conv(rng.standard_normal((2, hkv, d)).astype(np.float32))
+    vn = conv(rng.standard_normal((2, hkv, d)).astype(np.float32))
+    qn_d = dev(qn, dtype)
+    cache.append_rope(0, qn_d, dev(kn, dtype), dev(vn, dtype), pos=dev(dec), inv_freq=dev(inv), mrope_section=sec)
+    out = host(cache.attend(0, qn_d))
+    kk = np.concatenate([host(kb), conv(orc.rope_thd(kn, dec, inv, sec))[1:2]])
+    vv = np.concatenate([v, vn[1:2]])
+    assert oracle.rel_err(out[1:2], orc.gqa_decode(host(qn_d)[1:2], kk, vv)) <= tol
+    assert cache.seq_lens.cpu().tolist() == [1, n + 1] and ops.last_error() == 0
