@@ -23,6 +23,7 @@ from . import _capi
 
 _DTYPES = {torch.float16: _capi.FLOAT16, torch.float32: _capi.FLOAT32}
 _workspaces: dict = {}
+_retired: list = []  # outgrown workspaces, never freed (graphs captured earlier may still write to them)
 _launches = 0  # operator calls that reached the C ABI (used to tell an empty graph capture)
 
 
@@ -69,6 +70,9 @@ def workspace(device, nbytes: int) -> torch.Tensor:
         key = torch.device("cuda", torch.cuda.current_device())
     buf = _workspaces.get(key)
     if buf is None or buf.numel() < nbytes:
+        if buf is not None:
+            # a captured graph may have the old buffer's address baked in: keep it alive for good
+            _retired.append(buf)
         buf = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=key)
         _workspaces[key] = buf
     return buf
