@@ -53,6 +53,7 @@ SIGNATURES = {
     "axb200_kv_arena_sync": (_i, [_vp, _vp]),
     "axb200_kv_arena_stats": (_i, [_vp, C.POINTER(_i64), C.POINTER(_i64), C.POINTER(_i64), C.POINTER(_i64)]),
     "axb200_kv_arena_seq_pages": (_i, [_vp, _i, _vp, _i]),
+    "axb200_kv_arena_geometry": (_i, [_vp] + [C.POINTER(_i)] * 8),
     "axb200_kv_arena_k_pages": (_vp, [_vp, _i]),
     "axb200_kv_arena_v_pages": (_vp, [_vp, _i]),
     "axb200_kv_arena_block_table": (_vp, [_vp]),
@@ -66,6 +67,7 @@ SIGNATURES = {
     "axb200_rms_norm": (_i, [_vp, _vp, _f, _vp, _i64, _i, _i, _vp]),
     "axb200_embedding": (_i, [_vp, _i, _vp, _vp, _i64, _i64, _i, _i, _vp]),
     "axb200_argmax_last_dim": (_i, [_vp, _vp, _i64, _i, _i, _vp]),
+    "axb200_cast": (_i, [_vp, _i, _vp, _i, _i64, _vp]),
     "axb200_concat": (_i, [_vp, _vp, _vp, _i64, _sz, _sz, _vp]),
 }
 

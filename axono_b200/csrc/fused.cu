@@ -299,6 +299,14 @@ argmax_kernel(const T *x, int64_t *out, int cols) {
   }
 }
 
+// ---- fp16 <-> fp32 cast (IEEE, round to nearest even) -------------------------------------------
+template <typename Src, typename Dst>
+__global__ void __launch_bounds__(256)
+cast_kernel(const Src *src, Dst *dst, long long n) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    stf(dst + i, ldf(src + i));
+}
+
 // ---- concat (bytes) -----------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 concat_bytes_kernel(const uint8_t *a, const uint8_t *b, uint8_t *out, int64_t outer, size_t a_bytes,
@@ -454,6 +462,21 @@ int axb200_argmax_last_dim(const void *x, int64_t *out, int64_t rows, int cols, 
     axb::argmax_kernel<float><<<(unsigned)rows, cols >= 8192 ? 1024 : 256, 0, st>>>(static_cast<const float *>(x), out, cols);
   else
     axb::argmax_kernel<__half><<<(unsigned)rows, cols >= 8192 ? 1024 : 256, 0, st>>>(static_cast<const __half *>(x), out, cols);
+  return axb::launch_status();
+}
+
+int axb200_cast(const void *src, int src_dtype, void *dst, int dst_dtype, int64_t n, void *stream) {
+  if (!src || !dst) return AXB200_INVALID_PTR;
+  if (n < 0) return AXB200_INVALID_ARGUMENT;
+  if (n == 0) return AXB200_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = axb::blocks_for(n, 256);
+  if (src_dtype == AXB200_FLOAT16 && dst_dtype == AXB200_FLOAT32)
+    axb::cast_kernel<__half, float><<<grid, 256, 0, st>>>(static_cast<const __half *>(src), static_cast<float *>(dst), n);
+  else if (src_dtype == AXB200_FLOAT32 && dst_dtype == AXB200_FLOAT16)
+    axb::cast_kernel<float, __half><<<grid, 256, 0, st>>>(static_cast<const float *>(src), static_cast<__half *>(dst), n);
+  else
+    return AXB200_UNSUPPORTED_TYPE;
   return axb::launch_status();
 }
 

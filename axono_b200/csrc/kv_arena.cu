@@ -214,6 +214,20 @@ int axb200_kv_arena_seq_pages(axb200_kv_arena *a, int seq_id, int32_t *pages_out
   return n;
 }
 
+int axb200_kv_arena_geometry(axb200_kv_arena *a, int *n_layers, int *num_pages, int *hkv, int *page_tokens,
+                             int *d, int *dtype, int *max_seqs, int *max_blocks) {
+  if (!a) return AXB200_INVALID_PTR;
+  if (n_layers) *n_layers = a->n_layers;
+  if (num_pages) *num_pages = a->num_pages;
+  if (hkv) *hkv = a->hkv;
+  if (page_tokens) *page_tokens = a->page_tokens;
+  if (d) *d = a->d;
+  if (dtype) *dtype = a->dtype;
+  if (max_seqs) *max_seqs = a->max_seqs;
+  if (max_blocks) *max_blocks = a->max_blocks;
+  return AXB200_OK;
+}
+
 void *axb200_kv_arena_k_pages(axb200_kv_arena *a, int layer) {
   return (a && a->device && layer >= 0 && layer < a->n_layers) ? a->k_pools[layer] : nullptr;
 }

@@ -326,6 +326,10 @@ int axb200_embedding(const void *ids, int ids_dtype, const void *table, void *ou
  * x (rows, cols) of `dtype`, out int64 (rows). */
 int axb200_argmax_last_dim(const void *x, int64_t *out, int64_t rows, int cols, int dtype, void *stream);
 
+/* Half2FloatKernel / Float2HalfKernel (src/core/cuda/tensor/kernel.cu:175-193), the device side of
+ * Tensor::CastTo: FLOAT16 <-> FLOAT32, IEEE round to nearest even. */
+int axb200_cast(const void *src, int src_dtype, void *dst, int dst_dtype, int64_t n, void *stream);
+
 /* axono::ops::cuda::Concat, src/ops/cuda/sequence.cu:474-521, on bytes: out (outer, a_bytes +
  * b_bytes) = a (outer, a_bytes) ++ b (outer, b_bytes).  Axis 0 is outer == 1. */
 int axb200_concat(const void *a, const void *b, void *out, int64_t outer,
@@ -358,6 +362,8 @@ int axb200_kv_arena_stats(axb200_kv_arena *arena, int64_t *pages_total, int64_t 
                           int64_t *seqs_live, int64_t *device_bytes);
 /* Copies the sequence's page ids (host view) into pages_out; returns how many it holds, -1 on error. */
 int axb200_kv_arena_seq_pages(axb200_kv_arena *arena, int seq_id, int32_t *pages_out, int capacity);
+int axb200_kv_arena_geometry(axb200_kv_arena *arena, int *n_layers, int *num_pages, int *hkv, int *page_tokens,
+                             int *d, int *dtype, int *max_seqs, int *max_blocks);
 void *axb200_kv_arena_k_pages(axb200_kv_arena *arena, int layer);
 void *axb200_kv_arena_v_pages(axb200_kv_arena *arena, int layer);
 int32_t *axb200_kv_arena_block_table(axb200_kv_arena *arena);
