@@ -1,4 +1,5 @@
-"""Builds the C-ABI library (axono_b200/lib/libaxono_b200.so) for sm_100a with nvcc.
+"""Builds the C-ABI library (axono_b200/lib/libaxono_b200.so) for sm_100a with nvcc, and the native
+Python module `libaxono` (host runtime + operator adapters + pybind11 binding) that links against it.
 
     python -m axono_b200.build [--force] [--verbose]
 
@@ -51,5 +52,39 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+HOST = os.path.join(CSRC, "host")
+
+
+def native_module_path() -> str:
+    import sysconfig
+
+    return os.path.join(LIB_DIR, "libaxono" + sysconfig.get_config_var("EXT_SUFFIX"))
+
+
+def build_native(force: bool = False) -> str:
+    """The `libaxono` extension module: csrc/host/*.cpp compiled with g++ against pybind11, the CUDA
+    runtime and the C-ABI library beside it (rpath $ORIGIN)."""
+    import sysconfig
+
+    import pybind11
+
+    lib = build(force=force)
+    out = native_module_path()
+    srcs = sorted(glob.glob(os.path.join(HOST, "*.cpp")))
+    deps = srcs + glob.glob(os.path.join(HOST, "*.h")) + glob.glob(os.path.join(ROOT, "include", "*.h")) + [lib]
+    if not force and os.path.exists(out) and all(os.path.getmtime(d) <= os.path.getmtime(out) for d in deps):
+        return out
+    cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    cmd = [os.environ.get("CXX", "g++"), "-std=c++17", "-O2", "-fPIC", "-shared", "-fvisibility=hidden",
+           "-I", os.path.join(ROOT, "include"), "-I", HOST, "-I", pybind11.get_include(),
+           "-I", sysconfig.get_paths()["include"], "-I", os.path.join(cuda_home, "include"),
+           "-o", out, *srcs,
+           "-L", LIB_DIR, "-laxono_b200", "-L", os.path.join(cuda_home, "lib64"), "-lcudart",
+           "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + os.path.join(cuda_home, "lib64")]
+    subprocess.check_call(cmd)
+    return out
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build_native(force="--force" in sys.argv))

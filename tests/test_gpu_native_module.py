@@ -1,0 +1,245 @@
+"""The native `libaxono` module on the GPU, written the way the reference tests its binding
+(axono/python/tests/core/{test_gqa,test_fused,test_llm_ops,test_sequence_ops,test_cuda_graph}.py):
+numpy in, Tensor through the operators, numpy out, checked against the CPU oracle.  No PyTorch in
+these tests' data path; tolerances: fp32 1e-5, fp16 2e-3 (max|out - ref| / max|ref|)."""
+import numpy as np
+import pytest
+
+import oracle
+from axono_b200 import native
+
+pytestmark = pytest.mark.gpu
+TOL = {np.float32: 1e-5, np.float16: 2e-3}
+
+
+@pytest.fixture(scope="module")
+def lx():
+    m = native.load()
+    assert m.cuda_available(), "no CUDA device"
+    return m
+
+
+@pytest.fixture(scope="module")
+def chk():
+    return oracle.best()
+
+
+def dev(lx, a):
+    return lx.Tensor.from_numpy(np.ascontiguousarray(a), "cuda")
+
+
+def f32(a):
+    return np.asarray(a, dtype=np.float32)
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+@pytest.mark.parametrize("hq,hkv,d,skv", [(16, 8, 128, 777), (32, 8, 128, 4096), (8, 8, 64, 33), (12, 4, 80, 300)])
+def test_gqa_decode_attention(lx, chk, dtype, hq, hkv, d, skv):
+    rng = np.random.default_rng(hq * 1000 + skv)
+    q = rng.standard_normal((1, hq, d), dtype=np.float32).astype(dtype)
+    k = rng.standard_normal((skv, hkv, d), dtype=np.float32).astype(dtype)
+    v = rng.standard_normal((skv, hkv, d), dtype=np.float32).astype(dtype)
+    out = lx.gqa_decode_attention(dev(lx, q), dev(lx, k), dev(lx, v))
+    assert out.shape == (1, hq, d) and out.is_cuda and out.dtype == (lx.DataType.FLOAT32 if dtype is np.float32 else lx.DataType.FLOAT16)
+    ref = chk.gqa_decode(f32(q), f32(k), f32(v))
+    assert oracle.rel_err(f32(out.numpy()), ref) <= TOL[dtype]
+
+
+def test_gqa_decode_attention_status_codes(lx):
+    """Argument checks in the reference's order (src/ops/cuda/gqa.cu:143-154)."""
+    rng = np.random.default_rng(0)
+    q = dev(lx, rng.standard_normal((1, 8, 64), dtype=np.float32))
+    k = dev(lx, rng.standard_normal((16, 2, 64), dtype=np.float32))
+    with pytest.raises(RuntimeError, match="status 1"):  # Sq must be 1
+        lx.gqa_decode_attention(dev(lx, np.zeros((2, 8, 64), np.float32)), k, k)
+    with pytest.raises(RuntimeError, match="status 4"):  # Hq not a multiple of Hkv
+        lx.gqa_decode_attention(dev(lx, np.zeros((1, 7, 64), np.float32)), k, k)
+    with pytest.raises(RuntimeError, match="status 3"):  # dtype
+        lx.gqa_decode_attention(dev(lx, np.zeros((1, 8, 64), np.int32)), k, k)
+    with pytest.raises(RuntimeError, match="status 8"):  # device
+        lx.gqa_decode_attention(q, k.to("cpu"), k)
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+def test_fused_elementwise(lx, chk, dtype):
+    rng = np.random.default_rng(1)
+    x = rng.standard_normal((5, 2048), dtype=np.float32).astype(dtype)
+    r = rng.standard_normal((5, 2048), dtype=np.float32).astype(dtype)
+    w = (1 + 0.1 * rng.standard_normal(2048, dtype=np.float32)).astype(dtype)
+    y, out = lx.add_rms_norm(dev(lx, x), dev(lx, r), dev(lx, w), 1e-6)
+    y_ref, out_ref = chk.add_rms_norm(f32(x), f32(r), f32(w), 1e-6)
+    if dtype is np.float32:
+        assert np.array_equal(y.numpy(), y_ref)  # one rounded add
+    assert oracle.rel_err(f32(y.numpy()), y_ref) <= TOL[dtype]
+    assert oracle.rel_err(f32(out.numpy()), out_ref) <= TOL[dtype]
+    act = lx.silu_mul(dev(lx, x), dev(lx, r))
+    assert oracle.rel_err(f32(act.numpy()), chk.silu_mul(f32(x), f32(r))) <= TOL[dtype]
+    n = lx.rms_norm(dev(lx, x), dev(lx, w), 1e-5)
+    assert oracle.rel_err(f32(n.numpy()), chk.rms_norm(f32(x), f32(w), 1e-5)) <= TOL[dtype]
+
+
+def test_rope_family(lx, chk):
+    rng = np.random.default_rng(2)
+    s, h, d = 9, 4, 128
+    x = rng.standard_normal((s, h, d), dtype=np.float32)
+    pos = rng.integers(0, 40000, size=s).astype(np.int64)
+    out = lx.rope(dev(lx, x), dev(lx, pos), 1e6)
+    assert oracle.rel_err(out.numpy(), chk.rope(x, pos, 1e6)) <= 1e-5
+    pos3 = rng.integers(0, 5000, size=(3, s)).astype(np.int64)
+    inv = oracle.port().rope_inv_freq(1e6, d)
+    cos, sin = lx.mrope_cos_sin(dev(lx, pos3), dev(lx, inv), 20, 20)
+    cos_ref, sin_ref = chk.mrope_cos_sin(pos3, inv, 20, 20)
+    assert cos.shape == (s, d) and oracle.rel_err(cos.numpy(), cos_ref) <= 1e-5
+    assert oracle.rel_err(sin.numpy(), sin_ref) <= 1e-5
+    rot = lx.rope_with_cos_sin(dev(lx, x), cos, sin)
+    assert oracle.rel_err(rot.numpy(), chk.rope_with_cos_sin(x, cos_ref, sin_ref)) <= 1e-5
+    thd = lx.rope_thd(dev(lx, x), dev(lx, pos3), dev(lx, inv), 24, 20, 20)
+    assert oracle.rel_err(thd.numpy(), chk.rope_thd(x, pos3, inv, (24, 20, 20))) <= 1e-5
+
+
+def test_sequence_ops_bit_exact(lx, chk):
+    rng = np.random.default_rng(3)
+    a = rng.standard_normal((7, 4, 64), dtype=np.float32)
+    b = rng.standard_normal((1, 4, 64), dtype=np.float32)
+    cat = lx.concat(dev(lx, a), dev(lx, b), 0)
+    assert cat.shape == (8, 4, 64) and np.array_equal(cat.numpy(), np.concatenate([a, b], 0))
+    cat2 = lx.concat(dev(lx, a), dev(lx, a), -1)
+    assert np.array_equal(cat2.numpy(), np.concatenate([a, a], -1))
+    table = rng.standard_normal((1000, 96), dtype=np.float32)
+    ids = rng.integers(0, 1000, size=(3, 5)).astype(np.int64)
+    emb = lx.embedding(dev(lx, ids), dev(lx, table))
+    assert emb.shape == (3, 5, 96) and np.array_equal(emb.numpy(), table[ids])
+    logits = rng.standard_normal((6, 151936), dtype=np.float32)
+    logits[2, 77] = logits[2, 150000] = 99.0  # a tie: the lowest index wins
+    am = lx.argmax(dev(lx, logits))
+    assert am.dtype == lx.DataType.INT64 and np.array_equal(am.numpy(), chk.argmax_last_dim(logits))
+    assert am.numpy()[2] == 77
+
+
+def test_cast_and_device_moves(lx):
+    a = np.random.default_rng(4).standard_normal((33, 65), dtype=np.float32)
+    t = dev(lx, a)
+    assert t.device == "cuda" and t.is_cuda and np.array_equal(t.to("cpu").numpy(), a)
+    h = t.cast_to(lx.DataType.FLOAT16)
+    assert h.dtype == lx.DataType.FLOAT16 and np.array_equal(h.numpy(), a.astype(np.float16))
+    assert np.array_equal(h.cast_to(lx.DataType.FLOAT32).numpy(), a.astype(np.float16).astype(np.float32))
+    fresh = lx.Tensor(lx.DataType.FLOAT32, [1000], "cuda")
+    assert not fresh.numpy().any()  # device storage starts at zero, also when it comes from the pool
+
+
+def test_caching_allocator_reuses_and_respects_budget(lx):
+    lx.clear_cache()
+    assert lx.cached_bytes() == 0
+    t = lx.Tensor(lx.DataType.INT8, [1 << 20], "cuda")
+    ptr = t.data_ptr
+    t.copy_from_numpy(np.full(1 << 20, 7, np.int8))
+    del t
+    assert lx.cached_bytes() == 1 << 20
+    u = lx.Tensor(lx.DataType.INT8, [1 << 20], "cuda")  # exact-size hit, zeroed again
+    assert u.data_ptr == ptr and lx.cached_bytes() == 0 and not u.numpy().any()
+    del u
+    old = lx.cache_budget()
+    try:
+        lx.set_cache_budget(1 << 19)  # below what is cached: evicted
+        assert lx.cached_bytes() == 0
+        v = lx.Tensor(lx.DataType.INT8, [1 << 20], "cuda")
+        del v
+        assert lx.cached_bytes() == 0  # larger than the budget: freed, not cached
+    finally:
+        lx.set_cache_budget(old)
+
+
+def _decode_chain(lx, x, r, w, q, k, v):
+    y, xn = lx.add_rms_norm(x, r, w, 1e-6)
+    attn = lx.gqa_decode_attention(q, k, v)
+    return y, xn, attn, lx.silu_mul(xn, y)
+
+
+def test_cuda_graph_capture_replay(lx, chk):
+    """capture(fn) warms up, records allocations, captures; replays rewrite the same output buffers
+    and follow in-place changes of the inputs (axono/python/tests/core/test_cuda_graph.py:26-80)."""
+    rng = np.random.default_rng(5)
+    x_np, r_np = rng.standard_normal((4, 1024), dtype=np.float32), rng.standard_normal((4, 1024), dtype=np.float32)
+    w_np = np.ones(1024, np.float32)
+    q_np = rng.standard_normal((1, 16, 128), dtype=np.float32)
+    k_np, v_np = (rng.standard_normal((2000, 8, 128), dtype=np.float32) for _ in range(2))
+    x, r, w, q, k, v = (dev(lx, a) for a in (x_np, r_np, w_np, q_np, k_np, v_np))
+    g = native.CUDAGraph()
+    g.capture(lambda: _decode_chain(lx, x, r, w, q, k, v))
+    assert g.is_captured and g.num_nodes >= 4
+    y, xn, attn, act = g.outputs
+    for _ in range(3):
+        g.replay()
+        g.sync()
+        assert oracle.rel_err(attn.numpy(), chk.gqa_decode(q_np, k_np, v_np)) <= 1e-5
+        assert np.array_equal(y.numpy(), x_np + r_np)
+    q2 = rng.standard_normal((1, 16, 128), dtype=np.float32)
+    q.copy_from_numpy(q2)  # same address, new contents
+    g.replay()
+    g.sync()
+    assert oracle.rel_err(attn.numpy(), chk.gqa_decode(q2, k_np, v_np)) <= 1e-5
+    eager = _decode_chain(lx, x, r, w, q, k, v)
+    assert np.array_equal(eager[3].numpy(), act.numpy())
+    g.reset()
+    assert not g.is_captured
+
+
+def test_cuda_graph_block_form_and_errors(lx):
+    rng = np.random.default_rng(6)
+    a_np, b_np = rng.standard_normal((8, 512), dtype=np.float32), rng.standard_normal((8, 512), dtype=np.float32)
+    a, b = dev(lx, a_np), dev(lx, b_np)
+    with native.cuda_graph() as g:
+        tmp = lx.silu_mul(a, b)  # a temporary allocated inside the graph
+        g.output = lx.silu_mul(tmp, b)
+        del tmp
+    assert g.is_captured and g.num_nodes >= 2
+    ref = None
+    for _ in range(4):
+        g.replay()
+        g.sync()
+        cur = g.output.numpy()
+        ref = cur if ref is None else ref
+        assert np.array_equal(cur, ref)
+    s1 = oracle.port().silu_mul(a_np, b_np)
+    assert oracle.rel_err(ref, oracle.port().silu_mul(s1, b_np)) <= 1e-5
+    g.reset()
+    with pytest.raises(RuntimeError):  # replay before capture
+        native.CUDAGraph().replay()
+    with pytest.raises(RuntimeError):  # nothing launched: an empty graph is an error
+        native.CUDAGraph().capture(lambda: None)
+    # the runtime is usable after the failed capture
+    assert np.array_equal(lx.silu_mul(a, b).numpy(), lx.silu_mul(a, b).numpy())
+
+
+def test_kv_arena_decode_steps(lx, chk):
+    """Append-with-rope into arena pages, then paged attention, for three sequences over five steps;
+    the oracle runs rope -> concat -> gqa_decode per sequence on contiguous arrays."""
+    hq, hkv, d, page = 8, 2, 128, 64
+    lens = [130, 5, 64]
+    rng = np.random.default_rng(7)
+    arena = lx.KVArena(1, 32, hkv, page, d, lx.DataType.FLOAT32, 3, 8)
+    hist_k = [np.zeros((0, hkv, d), np.float32) for _ in lens]
+    hist_v = [np.zeros((0, hkv, d), np.float32) for _ in lens]
+    for n in lens:
+        arena.alloc_seq(n + 3)
+    arena.sync()
+    assert list(arena.seq_lens()) == [0, 0, 0]
+    st = arena.stats()
+    assert st["seqs_live"] == 3 and st["pages_total"] == 32 and st["pages_free"] == 32 - sum((n + 3 + page - 1) // page for n in lens)
+    for step in range(5):
+        k_new = rng.standard_normal((3, hkv, d), dtype=np.float32)
+        v_new = rng.standard_normal((3, hkv, d), dtype=np.float32)
+        q = rng.standard_normal((3, hq, d), dtype=np.float32)
+        qd = dev(lx, q)
+        lx.kv_append_rope(arena, 0, qd, dev(lx, k_new), dev(lx, v_new), theta=1e6)
+        out = lx.gqa_decode_attention_paged(qd, arena, 0, 64)
+        pos = np.full(1, step, np.int64)
+        for b in range(3):
+            hist_k[b] = np.concatenate([hist_k[b], chk.rope(k_new[b:b + 1], pos, 1e6)], 0)
+            hist_v[b] = np.concatenate([hist_v[b], v_new[b:b + 1]], 0)
+            q_rot = chk.rope(q[b:b + 1], pos, 1e6)
+            ref = chk.gqa_decode(q_rot, hist_k[b], hist_v[b])
+            assert oracle.rel_err(out.numpy()[b:b + 1], ref) <= 1e-5
+    assert list(arena.seq_lens()) == [5, 5, 5]
+    arena.free_seq(1)
+    assert arena.stats()["seqs_live"] == 2 and list(arena.seq_lens()) == [5, 0, 5]

@@ -1,0 +1,87 @@
+"""CPU-side checks of the native `libaxono` module: it imports without PyTorch, the host Tensor keeps
+the reference's container semantics (include/axono/core/tensor.h:24-129), and operators refuse CPU
+tensors instead of falling back to host code."""
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+from axono_b200 import native
+
+
+@pytest.fixture(scope="module")
+def lx():
+    return native.load()
+
+
+def test_import_without_torch():
+    code = ("import sys; from axono_b200 import native; lx = native.load(); "
+            "assert 'torch' not in sys.modules, 'torch was imported'; "
+            "print(lx.version(), int(lx.DataType.FLOAT16), int(lx.Status.DEVICE_MISMATCH))")
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=120)
+    assert out.returncode == 0, out.stderr
+    assert out.stdout.split()[-2:] == ["4", "8"]  # enum values of include/axono/core/types.h:18-43
+
+
+def test_enums_match_reference_values(lx):
+    assert [int(getattr(lx.DataType, n)) for n in
+            ("INT8", "INT16", "INT32", "INT64", "FLOAT16", "FLOAT32", "FLOAT64", "BOOLEAN")] == list(range(8))
+    assert int(lx.Status.OK) == 0 and int(lx.Status.SHAPE_MISMATCH) == 4 and int(lx.Status.DEVICE_ERROR) == 6
+
+
+def test_host_tensor_semantics(lx):
+    t = lx.Tensor(lx.DataType.FLOAT32, [2, 3])
+    assert t.shape == (2, 3) and t.ndim == 2 and t.num_elements == 6 and t.num_bytes == 24
+    assert t.device == "cpu" and not t.is_cuda
+    assert np.array_equal(t.numpy(), np.zeros((2, 3), np.float32))  # new storage is zero-filled
+    a = np.arange(6, dtype=np.float32).reshape(2, 3)
+    u = lx.Tensor.from_numpy(a)
+    assert np.array_equal(u.data_float32(), a)
+    t.copy_from(u)
+    assert np.array_equal(t.numpy(), a)
+    t.reshape([3, 2])
+    assert t.shape == (3, 2) and np.array_equal(t.numpy().ravel(), a.ravel())
+    with pytest.raises(RuntimeError):
+        t.reshape([4, 2])
+    t.resize([4])
+    assert t.num_elements == 4 and np.array_equal(t.numpy(), np.zeros(4, np.float32))
+    with pytest.raises(RuntimeError):  # element counts differ
+        t.copy_from(u)
+    empty = lx.Tensor(lx.DataType.FLOAT32, [])
+    assert empty.num_elements == 0  # an empty shape holds nothing, as in the reference
+
+
+def test_half_tensors_carry_raw_bits(lx):
+    a = np.array([1.0, -2.5, 65504.0, 6e-8], dtype=np.float16)
+    t = lx.Tensor.from_numpy(a)
+    assert t.dtype == lx.DataType.FLOAT16
+    assert np.array_equal(t.data_float16().view(np.float16), a)
+    f = t.cast_to(lx.DataType.FLOAT32)
+    assert np.array_equal(f.numpy(), a.astype(np.float32))
+    assert np.array_equal(f.cast_to(lx.DataType.FLOAT16).numpy(), a)
+    b = lx.Tensor.from_borrowed(a.view(np.uint16))
+    assert b.dtype == lx.DataType.FLOAT16 and np.array_equal(b.numpy(), a)
+
+
+def test_copy_shares_storage_deepcopy_does_not(lx):
+    import copy
+
+    t = lx.Tensor.from_numpy(np.ones(4, np.float32))
+    s, d = copy.copy(t), copy.deepcopy(t)
+    t.fill_zero()
+    assert np.array_equal(s.numpy(), np.zeros(4, np.float32))
+    assert np.array_equal(d.numpy(), np.ones(4, np.float32))
+
+
+def test_operators_refuse_cpu_tensors(lx):
+    x = lx.Tensor.from_numpy(np.ones((2, 8), np.float32))
+    w = lx.Tensor.from_numpy(np.ones(8, np.float32))
+    for call in (lambda: lx.silu_mul(x, x), lambda: lx.add_rms_norm(x, x, w, 1e-6), lambda: lx.rms_norm(x, w),
+                 lambda: lx.argmax(x), lambda: lx.concat(x, x, 0)):
+        with pytest.raises(RuntimeError):
+            call()
+    q = lx.Tensor.from_numpy(np.ones((1, 4, 64), np.float32))
+    kv = lx.Tensor.from_numpy(np.ones((16, 2, 64), np.float32))
+    with pytest.raises(RuntimeError, match="status 8"):  # DEVICE_MISMATCH, src/ops/cuda/gqa.cu:143-154
+        lx.gqa_decode_attention(q, kv, kv)
