@@ -3,16 +3,17 @@
 // (src/ops/cuda/sequence.cu:105-163,451-472), whose scores live in shared memory (skv*4 bytes, so it
 // cannot pass ~12 K keys) and whose P.V loop is thread-serial.
 //
-// fp16, head_dim 128: one CTA (four softmax warps + one issue warp, two CTAs per SM) per (block of 128
-// query rows, query head).  Q, K and V tiles are staged by TMA with 128-byte swizzle; S = Q.K^T (128 x
-// 64 per tile of 64 keys) and O += P.V are tcgen05.mma (cta_group::1, kind::f16) with the accumulators
-// in tensor memory (two S buffers and O: 256 columns per CTA); thread t owns query row t: it reads
-// its scores with tcgen05.ld, does the online softmax in registers, writes P (fp16) into shared memory
-// in the swizzled K-major layout the MMA expects and rescales its O row in tensor memory when the
-// running maximum moves.  One lane of the issue warp launches every TMA load and MMA; the two sides
-// meet only on mbarriers (tcgen05.commit for MMA completion).  K/V tiles are double buffered and S is
-// computed two tiles ahead, so tensor core and softmax overlap.  Every wait is bounded.  Other dtypes
-// and head sizes run row by row on the decode kernels (correct, not fast).
+// fp16, head_dim 128: one CTA (four softmax warps + an MMA warp + a TMA warp, two CTAs per SM) per
+// (block of 128 query rows, query head).  Q, K and V tiles are staged by TMA with 128-byte swizzle;
+// S = Q.K^T (128 x 64 per tile of 64 keys) and O += P.V are tcgen05.mma (cta_group::1, kind::f16) with
+// the accumulators in tensor memory (two S buffers and O: 256 columns per CTA); thread t owns query
+// row t: it reads its scores with tcgen05.ld, does the online softmax in registers, writes P (fp16
+// pairs) back over the first half of its S row with tcgen05.st - P.V takes its A operand from tensor
+// memory, so P never crosses shared memory - and rescales its O row in tensor memory when the running
+// maximum moves by more than a threshold.  One lane each of two more warps launches the MMAs and the
+// TMA loads; the sides meet only on mbarriers (tcgen05.commit for MMA completion).  K/V tiles are
+// multi-buffered and S is computed two tiles ahead, so tensor core and softmax overlap.  Every wait
+// is bounded.  Other dtypes and head sizes run row by row on the decode kernels (correct, not fast).
 //
 // Semantics as the reference's CPU op (src/ops/cpu/sequence.cpp:236-301): q (sq,hq,d), k/v
 // (skv,hkv,d) token-major, head h reads KV head h / (hq/hkv), scale 1/sqrt(d); with is_causal row t
@@ -35,13 +36,14 @@ namespace {
 
 constexpr int kBlockM = 128, kBlockN = 64, kD = 128;
 constexpr int kSoftmaxWarps = 4;
-constexpr int kThreads = (kSoftmaxWarps + 1) * 32;  // + the issue warp
+constexpr int kMmaWarp = kSoftmaxWarps, kLoadWarp = kSoftmaxWarps + 1;
+constexpr int kThreads = (kSoftmaxWarps + 2) * 32;  // + the MMA warp and the TMA warp
 constexpr int kQTileBytes = kBlockM * kD * 2;   // 32 KB: two swizzled boxes of [128 rows][64 halves]
 constexpr int kKvTileBytes = kBlockN * kD * 2;  // 16 KB: two swizzled boxes of [64 rows][64 halves]
-constexpr int kPTileBytes = kBlockM * kBlockN * 2;  // 16 KB: one swizzled box of [128 rows][64 keys]
-constexpr int kOffQ = 0, kOffK = kQTileBytes, kOffV = kOffK + 2 * kKvTileBytes, kOffP = kOffV + 2 * kKvTileBytes;
-constexpr int kOffBar = kOffP + kPTileBytes;
-constexpr int kSmemBytes = kOffBar + 128;  // 112 KB + barriers: two CTAs per SM
+constexpr int kKStages = 3, kVStages = 2;  // K runs ahead of V: S is computed two tiles before P.V
+constexpr int kOffQ = 0, kOffK = kQTileBytes, kOffV = kOffK + kKStages * kKvTileBytes;
+constexpr int kOffBar = kOffV + kVStages * kKvTileBytes;
+constexpr int kSmemBytes = kOffBar + 256;  // 112 KB + barriers: two CTAs per SM
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct PrefillParams {
@@ -70,6 +72,16 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t da, uint64_t 
       "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
       ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"((uint32_t)accumulate)
+      : "memory");
+}
+
+// The same with the A operand read from tensor memory (lane = row, one 32-bit column = two fp16
+// elements along K, so 16 keys = 8 columns).
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, bool accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"((uint32_t)accumulate)
       : "memory");
 }
 
@@ -104,21 +116,43 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-// 160 threads.  Warps 0-3 (softmax): thread t owns query row t of the block (tensor-memory lane t)
-// and all 64 key columns of a tile, so the row maximum and sum need no exchange.  Warp 4 (one lane):
-// issues every TMA load and every MMA, so the softmax warps never wait behind issue work; the two
-// sides meet only on mbarriers (bar_s: S_j ready; bar_p: P_j written and S buffer j&1 free; bar_o:
-// P_j.V_j done).  Software pipeline: S_{j+2} = Q.K_{j+2}^T is issued right after P_j.V_j, while the
-// softmax warps are already in tile j+1 (two S buffers).  Two CTAs share an SM (112 KB of shared
-// memory and 256 tensor-memory columns each).
+constexpr float kLazyLog2 = 8.0f;
+
+// 2^x on the FMA pipe for x <= kLazyLog2: round-to-nearest split x = n + f, f in [-0.5, 0.5], a cubic
+// for 2^f (max relative error 7.5e-5, below the fp16 rounding of P), n added into the exponent field.
+// Inputs below -125 (masked keys are -inf) clamp to 2^-125.
+__device__ __forceinline__ float poly_exp2(float x) {
+  x = fmaxf(x, -125.f);
+  const float xf = x + 12582912.f;  // 1.5 * 2^23: the low mantissa bits now hold n
+  const float f = x - (xf - 12582912.f);
+  float r = fmaf(0.05517162f, f, 0.24261113f);
+  r = fmaf(r, f, 0.69326097f);
+  r = fmaf(r, f, 0.99992806f);
+  return __int_as_float(__float_as_int(r) + (__float_as_int(xf) << 23));
+}
+
+// 192 threads.  Warps 0-3 (softmax): thread t owns query row t of the block (tensor-memory lane t)
+// and all 64 key columns of a tile, so the row maximum and sum need no exchange.  Warp 4 (one lane)
+// issues every MMA from descriptors built once; warp 5 (one lane) issues every TMA load, K and V tiles
+// in rings of 3 and 2 stages freed by tcgen05.commit - a single thread doing both spent two thirds of
+// a tile's time on instruction issue.  The sides meet only on mbarriers (full/empty per stage; bar_s:
+// S_j ready; bar_p: P_j written; bar_o: P_j.V_j done; bar_fin: the last P.V done).  Software pipeline:
+// S_{j+2} = Q.K_{j+2}^T is issued once P_j.V_j has completed, while the softmax warps are already in
+// tile j+1 (two S buffers).  Two CTAs share an SM (112 KB of shared memory and 256 tensor-memory
+// columns each).
 __global__ void __launch_bounds__(kThreads, 2)
 prefill_attn_f16_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                         const __grid_constant__ CUtensorMap tmV, const PrefillParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kOffBar);
-  uint64_t *bar_q = bars, *bar_k = bars + 1, *bar_v = bars + 3, *bar_s = bars + 5, *bar_o = bars + 7, *bar_p = bars + 8;
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 9);
-  volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + 10);
+  uint64_t *bar_q = bars;                                    // Q landed
+  uint64_t *full_k = bars + 1, *empty_k = bars + 4;          // per K stage: tile landed / S that read it done
+  uint64_t *full_v = bars + 7, *empty_v = bars + 9;          // per V stage: tile landed / P.V that read it done
+  uint64_t *bar_s = bars + 11, *bar_o = bars + 13;           // S_j ready (per S buffer); P_j.V_j done
+  uint64_t *bar_fin = bars + 14;  // the last P.V: the softmax warps skip phases of bar_o, a parity wait there would alias
+  uint64_t *bar_p = bars + 15;    // P_j written (per S buffer), one arrival per softmax warp
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 17);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + 18);
 
   // the swizzled tiles need a 1024-byte aligned base; refuse to run otherwise (nothing is written)
   if ((smem_u32(smem) & 1023u) != 0) {
@@ -135,12 +169,15 @@ prefill_attn_f16_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   const int nkv = (kv_end_max + kBlockN - 1) / kBlockN;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 8; ++i) mbar_init(&bars[i], 1);
-    mbar_init(bar_p, kSoftmaxWarps);
+    for (int i = 0; i < 15; ++i) mbar_init(&bars[i], 1);
+    // one per S buffer: a softmax warp may run a tile ahead of the others, and with a single barrier
+    // its second arrival would complete the phase the slower warps have not reached
+    mbar_init(&bar_p[0], kSoftmaxWarps);
+    mbar_init(&bar_p[1], kSoftmaxWarps);
     *abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == kSoftmaxWarps) {
+  if (warp == kMmaWarp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 256;" ::"r"(smem_u32(tmem_slot)) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -149,82 +186,97 @@ prefill_attn_f16_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot, tmem_o = tmem_base + 128;  // S buffers at columns 0 and 64
 
-  if (warp == kSoftmaxWarps) {
-    // ================= issue warp: TMA loads and MMAs, one lane =================
+  if (warp == kLoadWarp) {
+    // ================= TMA warp (one lane): Q, then K and V tiles in the order they are consumed =====
     if (lane == 0) {
-      // instruction descriptors: fp32 accumulate, fp16 operands, M = 128.  Q.K^T: N = 64 keys, B
-      // K-major; P.V: N = 128 dims, B MN-major (a V tile is [keys][d], d contiguous)
-      const uint32_t idesc_qk = (1u << 4) | ((kBlockN >> 3) << 17) | ((kBlockM >> 4) << 24);
-      const uint32_t idesc_pv = (1u << 4) | (1u << 16) | ((kD >> 3) << 17) | ((kBlockM >> 4) << 24);
-      const uint32_t q_addr = smem_u32(smem + kOffQ), p_addr = smem_u32(smem + kOffP);
-      auto load_k = [&](int j) {
-        const int s = j & 1;
-        uint8_t *ks = smem + kOffK + s * kKvTileBytes;
-        mbar_arrive_expect_tx(&bar_k[s], kKvTileBytes);
-        tma_load_3d(ks, &tmK, &bar_k[s], 0, hk, j * kBlockN);
-        tma_load_3d(ks + kKvTileBytes / 2, &tmK, &bar_k[s], 64, hk, j * kBlockN);
-      };
-      auto load_v = [&](int j) {
-        const int s = j & 1;
-        uint8_t *vs = smem + kOffV + s * kKvTileBytes;
-        mbar_arrive_expect_tx(&bar_v[s], kKvTileBytes);
-        tma_load_3d(vs, &tmV, &bar_v[s], 0, hk, j * kBlockN);
-        tma_load_3d(vs + kKvTileBytes / 2, &tmV, &bar_v[s], 64, hk, j * kBlockN);
-      };
-      // S_j = Q . K_j^T into S buffer j&1; arrives on bar_s[j&1]
-      auto issue_s = [&](int j) -> bool {
-        const int s = j & 1;
-        if (!mbar_wait_bounded(&bar_k[s], (j >> 1) & 1, abort_flag)) return false;
-        tc_fence_after();
-        const uint32_t k_addr = smem_u32(smem + kOffK + s * kKvTileBytes);
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {  // head_dim 128 = 8 steps of 16; each 64-wide half of d is one box
-          const uint32_t q_off = (ks >> 2) * (kQTileBytes / 2) + (ks & 3) * 32;
-          const uint32_t k_off = (ks >> 2) * (kKvTileBytes / 2) + (ks & 3) * 32;
-          umma_f16(tmem_base + s * kBlockN, smem_desc(q_addr + q_off, 16, 1024), smem_desc(k_addr + k_off, 16, 1024),
-                   idesc_qk, ks > 0);
-        }
-        umma_commit(&bar_s[s]);
-        return true;
-      };
       tma_prefetch_descriptor(&tmQ);
       tma_prefetch_descriptor(&tmK);
       tma_prefetch_descriptor(&tmV);
       mbar_arrive_expect_tx(bar_q, kQTileBytes);
       tma_load_3d(smem + kOffQ, &tmQ, bar_q, 0, h, q0);
       tma_load_3d(smem + kOffQ + kQTileBytes / 2, &tmQ, bar_q, 64, h, q0);
+      bool ok = true;
+      auto load_k = [&](int j) {
+        const int s = j % kKStages;
+        if (j >= kKStages) ok = mbar_wait_bounded(&empty_k[s], (j / kKStages - 1) & 1, abort_flag);
+        if (!ok) return;
+        uint8_t *dst = smem + kOffK + s * kKvTileBytes;
+        mbar_arrive_expect_tx(&full_k[s], kKvTileBytes);
+        tma_load_3d(dst, &tmK, &full_k[s], 0, hk, j * kBlockN);
+        tma_load_3d(dst + kKvTileBytes / 2, &tmK, &full_k[s], 64, hk, j * kBlockN);
+      };
+      auto load_v = [&](int j) {
+        const int s = j % kVStages;
+        if (j >= kVStages) ok = mbar_wait_bounded(&empty_v[s], (j / kVStages - 1) & 1, abort_flag);
+        if (!ok) return;
+        uint8_t *dst = smem + kOffV + s * kKvTileBytes;
+        mbar_arrive_expect_tx(&full_v[s], kKvTileBytes);
+        tma_load_3d(dst, &tmV, &full_v[s], 0, hk, j * kBlockN);
+        tma_load_3d(dst + kKvTileBytes / 2, &tmV, &full_v[s], 64, hk, j * kBlockN);
+      };
+      // consumption order is S_0 S_1 (PV_0 S_2) (PV_1 S_3) ...: K_0 K_1 K_2 V_0 K_3 V_1 ...
       load_k(0);
-      load_v(0);
-      if (nkv > 1) {
-        load_k(1);
-        load_v(1);
+      if (nkv > 1) load_k(1);
+      for (int j = 0; j < nkv && ok; ++j) {
+        if (j + 2 < nkv) load_k(j + 2);
+        if (ok) load_v(j);
       }
+    }
+  } else if (warp == kMmaWarp) {
+    // ================= MMA warp (one lane) =================
+    if (lane == 0) {
+      // instruction descriptors: fp32 accumulate, fp16 operands, M = 128.  Q.K^T: N = 64 keys, B
+      // K-major; P.V: N = 128 dims, B MN-major (a V tile is [keys][d], d contiguous)
+      const uint32_t idesc_qk = (1u << 4) | ((kBlockN >> 3) << 17) | ((kBlockM >> 4) << 24);
+      const uint32_t idesc_pv = (1u << 4) | (1u << 16) | ((kD >> 3) << 17) | ((kBlockM >> 4) << 24);
+      // Shared-memory descriptors are built once: stepping a tile, a stage or 16 elements along K only
+      // adds to the 14-bit address field (bytes >> 4), which cannot carry out of it (addresses < 256 KB).
+      const uint64_t dq = smem_desc(smem_u32(smem + kOffQ), 16, 1024);
+      const uint64_t dk = smem_desc(smem_u32(smem + kOffK), 16, 1024);
+      const uint64_t dv = smem_desc(smem_u32(smem + kOffV), kKvTileBytes / 2, 1024);
+      // S_j = Q . K_j^T into S buffer j&1; arrives on bar_s[j&1], and frees the K stage when done
+      auto issue_s = [&](int j) -> bool {
+        const int s = j & 1, sk = j % kKStages;
+        if (!mbar_wait_bounded(&full_k[sk], (j / kKStages) & 1, abort_flag)) return false;
+        tc_fence_after();
+        const uint64_t dks = dk + (uint64_t)(sk * (kKvTileBytes >> 4));
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {  // head_dim 128 = 8 steps of 16; each 64-wide half of d is one box
+          const uint32_t q_off = (ks >> 2) * (kQTileBytes / 2) + (ks & 3) * 32;
+          const uint32_t k_off = (ks >> 2) * (kKvTileBytes / 2) + (ks & 3) * 32;
+          umma_f16(tmem_base + s * kBlockN, dq + (q_off >> 4), dks + (k_off >> 4), idesc_qk, ks > 0);
+        }
+        umma_commit(&bar_s[s]);
+        umma_commit(&empty_k[sk]);
+        return true;
+      };
       bool ok = mbar_wait_bounded(bar_q, 0, abort_flag) && issue_s(0);
       if (ok && nkv > 1) ok = issue_s(1);
       for (int j = 0; j < nkv && ok; ++j) {
-        // P_j is written and S buffer j&1 has been read: O += P_j . V_j, then S_{j+2} into that buffer
-        ok = mbar_wait_bounded(bar_p, j & 1, abort_flag) && mbar_wait_bounded(&bar_v[j & 1], (j >> 1) & 1, abort_flag);
+        // P_j stands in the first 32 columns of S buffer j&1: O += P_j . V_j
+        const int sv = j % kVStages;
+        ok = mbar_wait_bounded(&bar_p[j & 1], (j >> 1) & 1, abort_flag) &&
+             mbar_wait_bounded(&full_v[sv], (j / kVStages) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t v_addr = smem_u32(smem + kOffV + (j & 1) * kKvTileBytes);
+        const uint64_t dvs = dv + (uint64_t)(sv * (kKvTileBytes >> 4));
+        const uint32_t p_tmem = tmem_base + (j & 1) * kBlockN;
 #pragma unroll
         for (int ks = 0; ks < kBlockN / 16; ++ks) {
-          // P: 16 keys along K of the one-box P tile; V as the MN-major B operand: the two 64-wide d
-          // atoms are one box (8 KB) apart, 8-key groups 1 KB apart, 16 keys per instruction = 2 KB
-          umma_f16(tmem_o, smem_desc(p_addr + ks * 32, 16, 1024),
-                   smem_desc(v_addr + ks * 2048, kKvTileBytes / 2, 1024), idesc_pv, j > 0 || ks > 0);
+          // V as the MN-major B operand: the two 64-wide d atoms are one box (8 KB) apart, 8-key
+          // groups 1 KB apart, 16 keys per instruction = 2 KB
+          umma_f16_ts(tmem_o, p_tmem + ks * 8, dvs + (uint64_t)(ks * (2048 >> 4)), idesc_pv, j > 0 || ks > 0);
         }
         umma_commit(bar_o);
+        umma_commit(&empty_v[sv]);
+        if (j == nkv - 1) umma_commit(bar_fin);
         if (j + 2 < nkv) {
-          // K stage j&1 was consumed by S_j long ago: its next tile may already be in flight
-          if (j == 0) load_k(2);
-          ok = issue_s(j + 2);
-          if (!ok) break;
-          // V stage j&1 and K stage (j+1)&1 are free once P_j.V_j (and S_{j+1}) have completed
+          // P_j.V_j complete: P_j is consumed, so S_{j+2} may overwrite S buffer j&1 (queueing it behind
+          // P_j.V_j instead would lean on issue-order execution, which is documented only for MMAs of
+          // one shape; measured no faster)
           ok = mbar_wait_bounded(bar_o, j & 1, abort_flag);
           if (!ok) break;
-          load_v(j + 2);
-          if (j + 3 < nkv) load_k(j + 3);
+          ok = issue_s(j + 2);
         }
       }
     }
@@ -235,7 +287,6 @@ prefill_attn_f16_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     const int kv_end = p.causal ? min(t_row + 1, p.skv) : p.skv;
     const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
     float m_run = -INFINITY, l_run = 0.f;
-    uint8_t *p_row = smem + kOffP + row * 128;
     bool ok = true;
     for (int j = 0; j < nkv && ok; ++j) {
       const int sb = j & 1;
@@ -261,37 +312,44 @@ prefill_attn_f16_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
 #pragma unroll
         for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sr[c][i]));
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      const float m_new = fmaxf(m_run, mx * p.scale_log2);
-      const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
-      const float corr = fast_exp2(m_run - m_safe);
-      m_run = m_new;
+      // Lazy maximum: the running maximum (and with it the rescale of O in tensor memory) moves only
+      // when some row of the warp found a score more than kLazyLog2 above it; until then p = 2^(s - m)
+      // may reach 2^kLazyLog2, which fp16 P and the fp32 sums hold without loss.
+      const float m_tile = mx * p.scale_log2;
+      float corr = 1.f;
+      const bool corr_any = __any_sync(0xffffffffu, m_tile > m_run + kLazyLog2);
+      if (corr_any) {
+        const float m_new = fmaxf(m_run, m_tile);
+        corr = fast_exp2(m_run - ((m_new == -INFINITY) ? 0.f : m_new));
+        m_run = m_new;
+      }
+      const float m_safe = (m_run == -INFINITY) ? 0.f : m_run;
       uint32_t packed[32];
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c = 0; c < 2; ++c)
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const float a = fast_exp2(fmaf(__uint_as_float(sr[c][i]), p.scale_log2, -m_safe));
-          const float b = fast_exp2(fmaf(__uint_as_float(sr[c][i + 1]), p.scale_log2, -m_safe));
+          const float xa = fmaf(__uint_as_float(sr[c][i]), p.scale_log2, -m_safe);
+          const float xb = fmaf(__uint_as_float(sr[c][i + 1]), p.scale_log2, -m_safe);
+          // one pair in four takes the polynomial on the FMA pipe instead of the special-function unit
+          const bool emulate = ((i >> 1) & 3) == 3;
+          const float a = emulate ? poly_exp2(xa) : fast_exp2(xa);
+          const float b = emulate ? poly_exp2(xb) : fast_exp2(xb);
           sum4[(i >> 1) & 3] += a + b;
           packed[c * 16 + (i >> 1)] = pack_half2(a, b);
         }
       l_run = l_run * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
 
-      // P and O are still in use by P_{j-1}.V_{j-1} until it completes
-      if (j > 0) {
+      // P_j (fp16 pairs, 32 columns) over the first half of this thread's own S row
+      tmem_st32(tmem_base + sb * kBlockN + lane_base, packed);
+      // rescale this row of O in tensor memory when the warp moved a maximum; O is in use by
+      // P_{j-1}.V_{j-1} until that completes (P_j.V_j is not issued before this warp arrives below,
+      // so the barrier cannot be more than one phase ahead of the parity asked for)
+      if (j > 0 && corr_any) {
         ok = mbar_wait_bounded(bar_o, (j - 1) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
-      }
-      // the row's 64 keys = eight 16-byte chunks, swizzled by row % 8 (K-major A operand of P.V)
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        uint8_t *dst = p_row + ((u ^ (row & 7)) << 4);
-        *reinterpret_cast<uint4 *>(dst) = make_uint4(packed[u * 4], packed[u * 4 + 1], packed[u * 4 + 2], packed[u * 4 + 3]);
-      }
-      // rescale this row of O in tensor memory when some row of the warp moved its maximum
-      if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t r[32];
@@ -300,15 +358,14 @@ prefill_attn_f16_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
           for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * corr);
           tmem_st32(tmem_o + lane_base + c * 32, r);
         }
-        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P is read by the tensor core
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_p);
+      if (lane == 0) mbar_arrive(&bar_p[sb]);
     }
     // ---- epilogue: O / l -> out ----
-    if (ok) ok = mbar_wait_bounded(bar_o, (nkv - 1) & 1, abort_flag);
+    if (ok) ok = mbar_wait_bounded(bar_fin, 0, abort_flag);
     tc_fence_after();
     if (ok) {
       const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
@@ -333,7 +390,7 @@ prefill_attn_f16_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == kSoftmaxWarps)
+  if (warp == kMmaWarp)
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;" ::"r"(tmem_base) : "memory");
 }
 
