@@ -102,6 +102,27 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// The same load without the wait: several may be in flight before one tcgen05.wait::ld.
+__device__ __forceinline__ void tmem_ld32_async(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -118,18 +139,6 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 
 constexpr float kLazyLog2 = 8.0f;
 
-// 2^x on the FMA pipe for x <= kLazyLog2: round-to-nearest split x = n + f, f in [-0.5, 0.5], a cubic
-// for 2^f (max relative error 7.5e-5, below the fp16 rounding of P), n added into the exponent field.
-// Inputs below -125 (masked keys are -inf) clamp to 2^-125.
-__device__ __forceinline__ float poly_exp2(float x) {
-  x = fmaxf(x, -125.f);
-  const float xf = x + 12582912.f;  // 1.5 * 2^23: the low mantissa bits now hold n
-  const float f = x - (xf - 12582912.f);
-  float r = fmaf(0.05517162f, f, 0.24261113f);
-  r = fmaf(r, f, 0.69326097f);
-  r = fmaf(r, f, 0.99992806f);
-  return __int_as_float(__float_as_int(r) + (__float_as_int(xf) << 23));
-}
 
 // 192 threads.  Warps 0-3 (softmax): thread t owns query row t of the block (tensor-memory lane t)
 // and all 64 key columns of a tile, so the row maximum and sum need no exchange.  Warp 4 (one lane)
@@ -332,10 +341,7 @@ prefill_attn_f16_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
         for (int i = 0; i < 32; i += 2) {
           const float xa = fmaf(__uint_as_float(sr[c][i]), p.scale_log2, -m_safe);
           const float xb = fmaf(__uint_as_float(sr[c][i + 1]), p.scale_log2, -m_safe);
-          // one pair in four takes the polynomial on the FMA pipe instead of the special-function unit
-          const bool emulate = ((i >> 1) & 3) == 3;
-          const float a = emulate ? poly_exp2(xa) : fast_exp2(xa);
-          const float b = emulate ? poly_exp2(xb) : fast_exp2(xb);
+          const float a = fast_exp2(xa), b = fast_exp2(xb);
           sum4[(i >> 1) & 3] += a + b;
           packed[c * 16 + (i >> 1)] = pack_half2(a, b);
         }
@@ -394,6 +400,258 @@ prefill_attn_f16_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;" ::"r"(tmem_base) : "memory");
 }
 
+// ---------------------------------------------------------------------------------------------------
+// The 256-row form, for sq >= 256: one CTA per SM works on two query tiles of 128 rows against key
+// tiles of 128, so that every MMA is 128 x 128 x 16 - at N = 64 the Q.K^T products re-read their A
+// operand from shared memory so often that shared-memory bandwidth, not the tensor core, sets their
+// pace - and each K/V tile staged in shared memory serves both query tiles.  Tensor memory (all 512
+// columns): S_0, S_1, O_0, O_1, 128 columns each; P_g overwrites the first 64 columns of S_g.
+// 320 threads: warps 0-3 own query tile 0 (thread t = row t), warps 4-7 tile 1, warp 8 issues the
+// MMAs, warp 9 the TMA loads.  Per tile g the chain is S_g(j) -> softmax -> P_g(j) -> O_g += P_g(j).V_j
+// -> S_g(j+1); the two tiles alternate on the tensor core, one computing while the other's softmax
+// runs.  S_g(j+1) is queued directly behind P_g(j).V_j, whose A operand it overwrites: MMAs of one
+// shape issued by one thread execute in issue order.  Its completion (bar_s) therefore also tells the
+// softmax warps that P_g(j).V_j is done and O_g may be rescaled.
+constexpr int kPairN = 128, kPairTileBytes = 128 * kD * 2;  // 32 KB: two swizzled boxes of [128 rows][64 halves]
+constexpr int kPairThreads = 320, kPairMmaWarp = 8, kPairLoadWarp = 9;
+constexpr int kPairOffQ = 0, kPairOffK = 2 * kPairTileBytes, kPairOffV = kPairOffK + 2 * kPairTileBytes;
+constexpr int kPairOffBar = kPairOffV + 2 * kPairTileBytes;
+constexpr int kPairSmemBytes = kPairOffBar + 256;  // 192 KB + barriers
+
+__global__ void __launch_bounds__(kPairThreads, 1)
+prefill_attn_f16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                             const __grid_constant__ CUtensorMap tmV, const PrefillParams p) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kPairOffBar);
+  uint64_t *bar_q = bars;
+  uint64_t *full_k = bars + 1, *empty_k = bars + 3, *full_v = bars + 5, *empty_v = bars + 7;  // two stages each
+  uint64_t *bar_s = bars + 9, *bar_fin = bars + 11;  // per query tile: S_g(j) ready; last P.V done
+  uint64_t *bar_p = bars + 13;                       // per query tile: P_g(j) written, one arrival per warp
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 15);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + 16);
+
+  if ((smem_u32(smem) & 1023u) != 0) {
+    if (threadIdx.x == 0) atomicOr(&g_error_word, AXB200_ERR_WAIT_TIMEOUT);
+    return;
+  }
+  // heaviest blocks first: under a causal mask the last query block has the most key tiles
+  const int qb = gridDim.x - 1 - blockIdx.x, h = blockIdx.y;
+  const int hk = h / (p.hq / p.hkv);
+  const int q0 = qb * 2 * kBlockM;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // key tiles per query tile: none for a tile past the last query row; under the causal rule
+  // min(t+1, skv) keys for its last row
+  int nkv_g[2];
+#pragma unroll
+  for (int g = 0; g < 2; ++g) {
+    const int first = q0 + g * kBlockM;
+    const int t_last = min(first + kBlockM, p.sq) - 1;
+    const int kv_end_max = p.causal ? min(t_last + 1, p.skv) : p.skv;
+    nkv_g[g] = first < p.sq ? (kv_end_max + kPairN - 1) / kPairN : 0;
+  }
+  const int nkv = max(nkv_g[0], nkv_g[1]);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 13; ++i) mbar_init(&bars[i], 1);
+    mbar_init(&bar_p[0], 4);
+    mbar_init(&bar_p[1], 4);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == kPairMmaWarp) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(tmem_slot)) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;  // S_g at g * 128, O_g at 256 + g * 128
+
+  if (warp == kPairLoadWarp) {
+    // ================= TMA warp (one lane) =================
+    if (lane == 0) {
+      tma_prefetch_descriptor(&tmQ);
+      tma_prefetch_descriptor(&tmK);
+      tma_prefetch_descriptor(&tmV);
+      mbar_arrive_expect_tx(bar_q, 2 * kPairTileBytes);
+#pragma unroll
+      for (int g = 0; g < 2; ++g) {  // rows past sq are zero-filled
+        tma_load_3d(smem + kPairOffQ + g * kPairTileBytes, &tmQ, bar_q, 0, h, q0 + g * kBlockM);
+        tma_load_3d(smem + kPairOffQ + g * kPairTileBytes + kPairTileBytes / 2, &tmQ, bar_q, 64, h, q0 + g * kBlockM);
+      }
+      bool ok = true;
+      auto load = [&](const CUtensorMap *map, int off, uint64_t *full, uint64_t *empty, int j) {
+        const int s = j & 1;
+        if (j >= 2) ok = mbar_wait_bounded(&empty[s], ((j >> 1) - 1) & 1, abort_flag);
+        if (!ok) return;
+        uint8_t *dst = smem + off + s * kPairTileBytes;
+        mbar_arrive_expect_tx(&full[s], kPairTileBytes);
+        tma_load_3d(dst, map, &full[s], 0, hk, j * kPairN);
+        tma_load_3d(dst + kPairTileBytes / 2, map, &full[s], 64, hk, j * kPairN);
+      };
+      // consumption order: K_0, then V_j and K_{j+1} per key tile
+      load(&tmK, kPairOffK, full_k, empty_k, 0);
+      for (int j = 0; j < nkv && ok; ++j) {
+        if (j + 1 < nkv) load(&tmK, kPairOffK, full_k, empty_k, j + 1);
+        if (ok) load(&tmV, kPairOffV, full_v, empty_v, j);
+      }
+    }
+  } else if (warp == kPairMmaWarp) {
+    // ================= MMA warp (one lane) =================
+    if (lane == 0) {
+      // fp32 accumulate, fp16 operands, M = 128, N = 128; Q.K^T: B K-major; P.V: B MN-major
+      const uint32_t idesc_qk = (1u << 4) | ((kPairN >> 3) << 17) | ((kBlockM >> 4) << 24);
+      const uint32_t idesc_pv = idesc_qk | (1u << 16);
+      const uint64_t dq = smem_desc(smem_u32(smem + kPairOffQ), 16, 1024);
+      const uint64_t dk = smem_desc(smem_u32(smem + kPairOffK), 16, 1024);
+      const uint64_t dv = smem_desc(smem_u32(smem + kPairOffV), kPairTileBytes / 2, 1024);
+      auto issue_s = [&](int g, int j) {  // S_g(j) = Q_g . K_j^T; K_j is known to have landed
+        const uint64_t dqg = dq + (uint64_t)(g * (kPairTileBytes >> 4));
+        const uint64_t dks = dk + (uint64_t)((j & 1) * (kPairTileBytes >> 4));
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {  // head_dim 128 = 8 steps of 16; each 64-wide half of d is one box
+          const uint32_t off = ((ks >> 2) * (kPairTileBytes / 2) + (ks & 3) * 32) >> 4;
+          umma_f16(tmem_base + g * 128, dqg + off, dks + off, idesc_qk, ks > 0);
+        }
+        umma_commit(&bar_s[g]);
+      };
+      bool ok = mbar_wait_bounded(bar_q, 0, abort_flag) && mbar_wait_bounded(&full_k[0], 0, abort_flag);
+      if (ok) {
+        tc_fence_after();
+        if (nkv_g[0] > 0) issue_s(0, 0);
+        if (nkv_g[1] > 0) issue_s(1, 0);
+        umma_commit(&empty_k[0]);
+      }
+      for (int j = 0; j < nkv && ok; ++j) {
+        ok = mbar_wait_bounded(&full_v[j & 1], (j >> 1) & 1, abort_flag);
+        if (ok && j + 1 < nkv) ok = mbar_wait_bounded(&full_k[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag);
+        if (!ok) break;
+        const uint64_t dvs = dv + (uint64_t)((j & 1) * (kPairTileBytes >> 4));
+#pragma unroll
+        for (int g = 0; g < 2; ++g) {
+          if (j >= nkv_g[g]) continue;
+          ok = mbar_wait_bounded(&bar_p[g], j & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          // O_g += P_g(j) . V_j: P from tensor memory (16 keys = 8 columns); V as the MN-major B
+          // operand: the two 64-wide d atoms are one box (16 KB) apart, 8-key groups 1 KB apart
+#pragma unroll
+          for (int ks = 0; ks < kPairN / 16; ++ks)
+            umma_f16_ts(tmem_base + 256 + g * 128, tmem_base + g * 128 + ks * 8, dvs + (uint64_t)(ks * (2048 >> 4)),
+                        idesc_pv, j > 0 || ks > 0);
+          if (j == nkv_g[g] - 1) umma_commit(&bar_fin[g]);
+          if (j + 1 < nkv_g[g]) issue_s(g, j + 1);
+        }
+        if (!ok) break;
+        umma_commit(&empty_v[j & 1]);
+        if (j + 1 < nkv) umma_commit(&empty_k[(j + 1) & 1]);
+      }
+    }
+  } else {
+    // ================= softmax warps: query tile g, thread = row =================
+    const int g = warp >> 2, row = threadIdx.x & (kBlockM - 1);
+    const int my_nkv = g ? nkv_g[1] : nkv_g[0];
+    const int t_row = q0 + g * kBlockM + row;
+    const int kv_end = p.causal ? min(t_row + 1, p.skv) : p.skv;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t tmem_s = tmem_base + g * 128 + lane_base, tmem_o = tmem_base + 256 + g * 128 + lane_base;
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    for (int j = 0; j < my_nkv && ok; ++j) {
+      ok = __all_sync(0xffffffffu, mbar_wait_bounded(&bar_s[g], j & 1, abort_flag));
+      if (!ok) break;
+      tc_fence_after();
+      // ---- this thread's row of scores: 128 keys ----
+      uint32_t sr[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32_async(tmem_s + c * 32, sr[c]);
+      tmem_wait_ld();
+      const int n0 = j * kPairN;
+      if (n0 + kPairN > kv_end) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (n0 + c * 32 + i >= kv_end) sr[c][i] = 0xff800000u;  // -inf
+      }
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sr[c][i]));
+      const float m_tile = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
+      // lazy maximum, as in the 128-row kernel
+      float corr = 1.f;
+      const bool moved = __any_sync(0xffffffffu, m_tile > m_run + kLazyLog2);
+      if (moved) {
+        const float m_new = fmaxf(m_run, m_tile);
+        corr = fast_exp2(m_run - ((m_new == -INFINITY) ? 0.f : m_new));
+        m_run = m_new;
+      }
+      const float m_safe = (m_run == -INFINITY) ? 0.f : m_run;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float xa = fmaf(__uint_as_float(sr[c][i]), p.scale_log2, -m_safe);
+          const float xb = fmaf(__uint_as_float(sr[c][i + 1]), p.scale_log2, -m_safe);
+          const float a = fast_exp2(xa), b = fast_exp2(xb);
+          sum4[(i >> 1) & 3] += a + b;
+          packed[i >> 1] = pack_half2(a, b);
+        }
+        // P: 32 keys = 16 columns over the front of this thread's own S row (all scores are in registers)
+        tmem_st16(tmem_s + c * 16, packed);
+      }
+      l_run = l_run * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+      // S_g(j) was queued behind P_g(j-1).V_{j-1}, so that product is complete: O_g may be rescaled
+      if (j > 0 && moved) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          tmem_ld32(tmem_o + c * 32, r);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * corr);
+          tmem_st32(tmem_o + c * 32, r);
+        }
+      }
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar_p[g]);
+    }
+    // ---- epilogue: O / l -> out ----
+    if (ok && my_nkv > 0) ok = __all_sync(0xffffffffu, mbar_wait_bounded(&bar_fin[g], 0, abort_flag));
+    tc_fence_after();
+    if (ok && my_nkv > 0) {
+      const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+      __half *dst = reinterpret_cast<__half *>(p.out) + ((size_t)t_row * p.hq + h) * kD;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem_o + c * 32, r);
+        if (t_row < p.sq) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            uint4 w;
+            w.x = pack_half2(__uint_as_float(r[u * 8 + 0]) * inv, __uint_as_float(r[u * 8 + 1]) * inv);
+            w.y = pack_half2(__uint_as_float(r[u * 8 + 2]) * inv, __uint_as_float(r[u * 8 + 3]) * inv);
+            w.z = pack_half2(__uint_as_float(r[u * 8 + 4]) * inv, __uint_as_float(r[u * 8 + 5]) * inv);
+            w.w = pack_half2(__uint_as_float(r[u * 8 + 6]) * inv, __uint_as_float(r[u * 8 + 7]) * inv);
+            *reinterpret_cast<uint4 *>(dst + c * 32 + u * 8) = w;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kPairMmaWarp)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+}
+
+
 using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                    const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -446,9 +704,12 @@ int axb200_sdpa(const void *q, const void *k, const void *v, void *out, int sq, 
                            axb::aligned16(k) && axb::aligned16(v) && axb::aligned16(out) && axb::encoder();
   if (!tensor_path)
     return axb::sdpa_rows_fallback(q, k, v, out, sq, hq, hkv, d, skv, is_causal, dtype, workspace, workspace_bytes, st);
+  // 256 query rows per CTA once there are that many; the 128-row form below that
+  const bool pair = sq >= 2 * axb::kBlockM;
+  const int kv_box = pair ? axb::kPairN : axb::kBlockN;
   CUtensorMap mq, mk, mv;
-  if (!axb::rows_map(&mq, q, sq, hq, axb::kBlockM) || !axb::rows_map(&mk, k, skv, hkv, axb::kBlockN) ||
-      !axb::rows_map(&mv, v, skv, hkv, axb::kBlockN))
+  if (!axb::rows_map(&mq, q, sq, hq, axb::kBlockM) || !axb::rows_map(&mk, k, skv, hkv, kv_box) ||
+      !axb::rows_map(&mv, v, skv, hkv, kv_box))
     return AXB200_INTERNAL_ERROR;
   static std::mutex mu;
   static bool opted[64] = {false};
@@ -458,7 +719,9 @@ int axb200_sdpa(const void *q, const void *k, const void *v, void *out, int sq, 
     std::lock_guard<std::mutex> lock(mu);
     if (!opted[dev]) {
       if (cudaFuncSetAttribute(axb::prefill_attn_f16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               axb::kSmemBytes) != cudaSuccess)
+                               axb::kSmemBytes) != cudaSuccess ||
+          cudaFuncSetAttribute(axb::prefill_attn_f16_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               axb::kPairSmemBytes) != cudaSuccess)
         return AXB200_DEVICE_ERROR;
       opted[dev] = true;
     }
@@ -471,8 +734,13 @@ int axb200_sdpa(const void *q, const void *k, const void *v, void *out, int sq, 
   p.skv = (int)skv;
   p.causal = is_causal != 0;
   p.scale_log2 = (1.0f / sqrtf((float)d)) * axb::kLog2e;
-  const dim3 grid((sq + axb::kBlockM - 1) / axb::kBlockM, hq);
-  axb::prefill_attn_f16_kernel<<<grid, axb::kThreads, axb::kSmemBytes, st>>>(mq, mk, mv, p);
+  if (pair) {
+    const dim3 grid((sq + 2 * axb::kBlockM - 1) / (2 * axb::kBlockM), hq);
+    axb::prefill_attn_f16_pair_kernel<<<grid, axb::kPairThreads, axb::kPairSmemBytes, st>>>(mq, mk, mv, p);
+  } else {
+    const dim3 grid((sq + axb::kBlockM - 1) / axb::kBlockM, hq);
+    axb::prefill_attn_f16_kernel<<<grid, axb::kThreads, axb::kSmemBytes, st>>>(mq, mk, mv, p);
+  }
   return axb::launch_status();
 }
 
