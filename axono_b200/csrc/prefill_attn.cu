@@ -423,12 +423,14 @@ prefill_attn_f16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
                              const __grid_constant__ CUtensorMap tmV, const PrefillParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kPairOffBar);
-  uint64_t *bar_q = bars;
-  uint64_t *full_k = bars + 1, *empty_k = bars + 3, *full_v = bars + 5, *empty_v = bars + 7;  // two stages each
-  uint64_t *bar_s = bars + 9, *bar_fin = bars + 11;  // per query tile: S_g(j) ready; last P.V done
-  uint64_t *bar_p = bars + 13;                       // per query tile: P_g(j) written, one arrival per warp
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 15);
-  volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + 16);
+  // K/V tiles travel in pairs (V_j, K_{j+1}) - what one key-tile step of the MMA warp consumes - under
+  // one full and one empty barrier per pair slot j & 1, so that the MMA warp, which can do nothing else
+  // while it waits, makes one wait and one commit per step instead of two.  Q and K_0 share bar_q.
+  uint64_t *bar_q = bars, *full_kv = bars + 1, *empty_kv = bars + 3;
+  uint64_t *bar_s = bars + 5, *bar_fin = bars + 7;  // per query tile: S_g(j) ready; last P.V done
+  uint64_t *bar_p = bars + 9;                       // per query tile: P_g(j) written, one arrival per warp
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 11);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + 12);
 
   if ((smem_u32(smem) & 1023u) != 0) {
     if (threadIdx.x == 0) atomicOr(&g_error_word, AXB200_ERR_WAIT_TIMEOUT);
@@ -452,7 +454,7 @@ prefill_attn_f16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
   const int nkv = max(nkv_g[0], nkv_g[1]);
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 13; ++i) mbar_init(&bars[i], 1);
+    for (int i = 0; i < 9; ++i) mbar_init(&bars[i], 1);
     mbar_init(&bar_p[0], 4);
     mbar_init(&bar_p[1], 4);
     *abort_flag = 0;
@@ -473,27 +475,31 @@ prefill_attn_f16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
       tma_prefetch_descriptor(&tmQ);
       tma_prefetch_descriptor(&tmK);
       tma_prefetch_descriptor(&tmV);
-      mbar_arrive_expect_tx(bar_q, 2 * kPairTileBytes);
+      mbar_arrive_expect_tx(bar_q, 3 * kPairTileBytes);
 #pragma unroll
       for (int g = 0; g < 2; ++g) {  // rows past sq are zero-filled
         tma_load_3d(smem + kPairOffQ + g * kPairTileBytes, &tmQ, bar_q, 0, h, q0 + g * kBlockM);
         tma_load_3d(smem + kPairOffQ + g * kPairTileBytes + kPairTileBytes / 2, &tmQ, bar_q, 64, h, q0 + g * kBlockM);
       }
+      tma_load_3d(smem + kPairOffK, &tmK, bar_q, 0, hk, 0);
+      tma_load_3d(smem + kPairOffK + kPairTileBytes / 2, &tmK, bar_q, 64, hk, 0);
       bool ok = true;
-      auto load = [&](const CUtensorMap *map, int off, uint64_t *full, uint64_t *empty, int j) {
+      for (int j = 0; j < nkv && ok; ++j) {  // pair j: V_j into V stage j & 1, K_{j+1} into K stage (j+1) & 1
         const int s = j & 1;
-        if (j >= 2) ok = mbar_wait_bounded(&empty[s], ((j >> 1) - 1) & 1, abort_flag);
-        if (!ok) return;
-        uint8_t *dst = smem + off + s * kPairTileBytes;
-        mbar_arrive_expect_tx(&full[s], kPairTileBytes);
-        tma_load_3d(dst, map, &full[s], 0, hk, j * kPairN);
-        tma_load_3d(dst + kPairTileBytes / 2, map, &full[s], 64, hk, j * kPairN);
-      };
-      // consumption order: K_0, then V_j and K_{j+1} per key tile
-      load(&tmK, kPairOffK, full_k, empty_k, 0);
-      for (int j = 0; j < nkv && ok; ++j) {
-        if (j + 1 < nkv) load(&tmK, kPairOffK, full_k, empty_k, j + 1);
-        if (ok) load(&tmV, kPairOffV, full_v, empty_v, j);
+        // slot s was last committed by step j - 2; for j = 1 by the prologue, which read K_0 out of the
+        // K stage that K_2 goes to (so slot 1 is one phase further on than slot 0)
+        if (j >= 1) ok = mbar_wait_bounded(&empty_kv[s], s ? ((j - 1) >> 1) & 1 : ((j >> 1) - 1) & 1, abort_flag);
+        if (!ok) break;
+        const bool with_k = j + 1 < nkv;
+        mbar_arrive_expect_tx(&full_kv[s], with_k ? 2 * kPairTileBytes : kPairTileBytes);
+        if (with_k) {  // first: S_g(j+1) is what the softmax warps wait for
+          uint8_t *kd = smem + kPairOffK + (s ^ 1) * kPairTileBytes;
+          tma_load_3d(kd, &tmK, &full_kv[s], 0, hk, (j + 1) * kPairN);
+          tma_load_3d(kd + kPairTileBytes / 2, &tmK, &full_kv[s], 64, hk, (j + 1) * kPairN);
+        }
+        uint8_t *vd = smem + kPairOffV + s * kPairTileBytes;
+        tma_load_3d(vd, &tmV, &full_kv[s], 0, hk, j * kPairN);
+        tma_load_3d(vd + kPairTileBytes / 2, &tmV, &full_kv[s], 64, hk, j * kPairN);
       }
     }
   } else if (warp == kPairMmaWarp) {
@@ -515,16 +521,15 @@ prefill_attn_f16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
         }
         umma_commit(&bar_s[g]);
       };
-      bool ok = mbar_wait_bounded(bar_q, 0, abort_flag) && mbar_wait_bounded(&full_k[0], 0, abort_flag);
+      bool ok = mbar_wait_bounded(bar_q, 0, abort_flag);
       if (ok) {
         tc_fence_after();
         if (nkv_g[0] > 0) issue_s(0, 0);
         if (nkv_g[1] > 0) issue_s(1, 0);
-        umma_commit(&empty_k[0]);
+        umma_commit(&empty_kv[1]);  // K_0 has been read: the stage may take K_2
       }
       for (int j = 0; j < nkv && ok; ++j) {
-        ok = mbar_wait_bounded(&full_v[j & 1], (j >> 1) & 1, abort_flag);
-        if (ok && j + 1 < nkv) ok = mbar_wait_bounded(&full_k[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag);
+        ok = mbar_wait_bounded(&full_kv[j & 1], (j >> 1) & 1, abort_flag);
         if (!ok) break;
         const uint64_t dvs = dv + (uint64_t)((j & 1) * (kPairTileBytes >> 4));
 #pragma unroll
@@ -543,8 +548,7 @@ prefill_attn_f16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
           if (j + 1 < nkv_g[g]) issue_s(g, j + 1);
         }
         if (!ok) break;
-        umma_commit(&empty_v[j & 1]);
-        if (j + 1 < nkv) umma_commit(&empty_k[(j + 1) & 1]);
+        umma_commit(&empty_kv[j & 1]);
       }
     }
   } else {
