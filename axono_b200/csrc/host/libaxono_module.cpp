@@ -170,6 +170,7 @@ PYBIND11_MODULE(libaxono, m) {
       .def_property_readonly("num_bytes", &Tensor::num_bytes)
       .def_property_readonly("data_ptr", [](const Tensor &t) { return reinterpret_cast<uintptr_t>(t.data()); })
       .def("numpy", &ToNumpy)
+      .def("to_numpy", &ToNumpy)
       .def("data_int8", [](const Tensor &t) { return Accessor<int8_t>(t, DataType::INT8, "data_int8"); })
       .def("data_int16", [](const Tensor &t) { return Accessor<int16_t>(t, DataType::INT16, "data_int16"); })
       .def("data_int32", [](const Tensor &t) { return Accessor<int32_t>(t, DataType::INT32, "data_int32"); })

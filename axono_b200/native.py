@@ -7,7 +7,8 @@ decode path - Tensor, DataType, Status, the operators, CUDAGraph, the allocator 
     q = lx.Tensor.from_numpy(q_np, "cuda")
     out = lx.gqa_decode_attention(q, k, v).numpy()
 
-`cuda_graph()` mirrors the reference's context manager (axono/python/axono/core/cuda_graph.py).
+`CUDAGraph` / `cuda_graph()` mirror the reference's wrappers (axono/python/axono/core/cuda_graph.py),
+`compile()` its graph-replay model wrapper (axono/python/axono/core/compile.py:69-174).
 """
 from __future__ import annotations
 
@@ -99,3 +100,75 @@ def cuda_graph():
         g.outputs, g.output = list(out), out[0]
     elif out is not None:
         g.outputs = [out]
+
+
+def _is_tensor(a) -> bool:
+    return hasattr(a, "shape") and hasattr(a, "dtype") and hasattr(a, "copy_from")
+
+
+def _signature(args, kwargs):
+    """Call signature that selects a cached graph: shape / dtype / device of tensors, repr of the rest."""
+    parts = []
+    for a in args:
+        parts.append(("T", tuple(a.shape), str(a.dtype), str(a.device)) if _is_tensor(a) else ("S", repr(a)))
+    for k in sorted(kwargs):
+        v = kwargs[k]
+        parts.append((k, "T", tuple(v.shape), str(v.dtype), str(v.device)) if _is_tensor(v) else (k, "S", repr(v)))
+    return tuple(parts)
+
+
+class CompiledModel:
+    """`model` wrapped for graph replay.  The first call with a new signature runs the model once
+    eagerly on the real inputs, then captures it (capture's own warm-up run records the allocations);
+    that call's tensors become the static inputs and later calls copy their inputs into them; outputs
+    are static buffers that the next replay overwrites.  Attribute access passes through to the model."""
+
+    def __init__(self, model, mode: str = "normal"):
+        if mode != "normal":
+            raise ValueError(f"compile: unsupported mode {mode!r} (only 'normal')")
+        if not load().cuda_available():
+            raise RuntimeError("compile needs a CUDA device")
+        object.__setattr__(self, "_model", model)
+        object.__setattr__(self, "_mode", mode)
+        object.__setattr__(self, "_graphs", {})
+
+    def __getattr__(self, name):
+        return getattr(object.__getattribute__(self, "_model"), name)
+
+    def __setattr__(self, name, value):
+        if name.startswith("_"):
+            object.__setattr__(self, name, value)
+        else:
+            setattr(object.__getattribute__(self, "_model"), name, value)
+
+    def __call__(self, *args, **kwargs):
+        sig = _signature(args, kwargs)
+        entry = self._graphs.get(sig)
+        if entry is None:
+            self._model(*args, **kwargs)
+            g = CUDAGraph().capture(lambda: self._model(*args, **kwargs))
+            entry = (g, args, kwargs)
+            self._graphs[sig] = entry
+        g, s_args, s_kwargs = entry
+        for s, a in zip(s_args, args):
+            if _is_tensor(s) and s is not a:
+                s.copy_from(a)
+        for k, s in s_kwargs.items():
+            if _is_tensor(s) and s is not kwargs[k]:
+                s.copy_from(kwargs[k])
+        g.replay()
+        outs = g.outputs
+        return outs[0] if len(outs) == 1 else tuple(outs)
+
+    forward = __call__
+
+    @property
+    def num_graphs(self) -> int:
+        return len(self._graphs)
+
+    def __repr__(self):
+        return f"CompiledModel(mode={self._mode!r}, graphs={len(self._graphs)}, model={self._model!r})"
+
+
+def compile(model, mode: str = "normal") -> CompiledModel:  # noqa: A001 - the reference's name
+    return CompiledModel(model, mode=mode)
