@@ -85,3 +85,33 @@ def test_operators_refuse_cpu_tensors(lx):
     kv = lx.Tensor.from_numpy(np.ones((16, 2, 64), np.float32))
     with pytest.raises(RuntimeError, match="status 8"):  # DEVICE_MISMATCH, src/ops/cuda/gqa.cu:143-154
         lx.gqa_decode_attention(q, kv, kv)
+
+
+def test_axono_compat_package_host_side():
+    """`import axono` resolves to the compatibility package; host tensors, default device and the
+    KV-cache contract need no GPU; operators on host tensors raise instead of falling back."""
+    import axono_b200.compat as compat
+
+    compat.install()
+    import axono
+    from axono import nn
+
+    assert axono.get_default_device() == "cpu" and axono.get_backend() == "cpu"
+    with pytest.raises(ValueError):
+        axono.set_default_device("tpu")
+    t = axono.Tensor.from_numpy(np.arange(6).reshape(2, 3))  # ints stay ints
+    assert t.dtype == axono.DataType.INT64 and np.array_equal(t.to_numpy(), np.arange(6).reshape(2, 3))
+    assert np.array_equal(axono.Tensor.ones([2, 2]).to_numpy(), np.ones((2, 2), np.float32))
+    assert np.array_equal(axono.Tensor.zeros([3]).fill(2.5).to_numpy(), np.full(3, 2.5, np.float32))
+    cache = nn.DynamicKVCache(2)
+    assert len(cache) == 0
+    with pytest.raises(RuntimeError):
+        cache.get(0)
+    k = axono.Tensor.from_numpy(np.zeros((3, 2, 4), np.float32))
+    cache.update(0, k, k)
+    assert len(cache) == 3 and cache.get(0)[0] is k
+    with pytest.raises(RuntimeError):  # second update concatenates: a CUDA operator, refused for host tensors
+        cache.update(0, k, k)
+    with pytest.raises(RuntimeError):
+        axono.fused.silu_mul(k, k)
+    assert not hasattr(axono, "matmul")  # outside this library
