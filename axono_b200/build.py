@@ -79,7 +79,7 @@ def build_native(force: bool = False) -> str:
            "-I", os.path.join(ROOT, "include"), "-I", HOST, "-I", pybind11.get_include(),
            "-I", sysconfig.get_paths()["include"], "-I", os.path.join(cuda_home, "include"),
            "-o", out, *srcs,
-           "-L", LIB_DIR, "-laxono_b200", "-L", os.path.join(cuda_home, "lib64"), "-lcudart",
+           "-L", LIB_DIR, "-laxono_b200", "-L", os.path.join(cuda_home, "lib64"), "-lcudart", "-ldl",
            "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + os.path.join(cuda_home, "lib64")]
     subprocess.check_call(cmd)
     return out

@@ -136,6 +136,10 @@ Status CopyToHost(void *dst, const void *device_src, size_t bytes) {
   return cudaMemcpy(dst, device_src, bytes, cudaMemcpyDeviceToHost) == cudaSuccess ? Status::OK : Status::DEVICE_ERROR;
 }
 
+Status CopyToDevice(void *device_dst, const void *src, size_t bytes) {
+  return cudaMemcpy(device_dst, src, bytes, cudaMemcpyHostToDevice) == cudaSuccess ? Status::OK : Status::DEVICE_ERROR;
+}
+
 void SetCacheBudget(size_t bytes) {
   Cache &c = cache();
   std::lock_guard<std::mutex> lock(c.mu);
@@ -306,6 +310,21 @@ Status GraphExec::Replay() {
   cudaStream_t st = static_cast<cudaStream_t>(stream_);
   if (cudaGraphLaunch(static_cast<cudaGraphExec_t>(exec_), st) != cudaSuccess) return Status::DEVICE_ERROR;
   return cudaStreamSynchronize(st) == cudaSuccess ? Status::OK : Status::DEVICE_ERROR;
+}
+Status GraphExec::ReplayTimed(int times, float *ms_per_launch) {
+  if (!exec_ || times <= 0 || !ms_per_launch) return Status::INVALID_ARGUMENT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream_);
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess) return Status::DEVICE_ERROR;
+  bool ok = cudaStreamSynchronize(st) == cudaSuccess && cudaEventRecord(e0, st) == cudaSuccess;
+  for (int i = 0; i < times && ok; ++i) ok = cudaGraphLaunch(static_cast<cudaGraphExec_t>(exec_), st) == cudaSuccess;
+  ok = ok && cudaEventRecord(e1, st) == cudaSuccess && cudaEventSynchronize(e1) == cudaSuccess;
+  float ms = 0.f;
+  ok = ok && cudaEventElapsedTime(&ms, e0, e1) == cudaSuccess;
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  *ms_per_launch = ms / (float)times;
+  return ok ? Status::OK : Status::DEVICE_ERROR;
 }
 Status GraphExec::Sync() {
   if (!stream_) return Status::OK;

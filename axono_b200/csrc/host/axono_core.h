@@ -80,6 +80,7 @@ namespace cuda {
 bool Available();
 Status DeviceSynchronize();
 Status CopyToHost(void *dst, const void *device_src, size_t bytes);  // blocking, legacy default stream
+Status CopyToDevice(void *device_dst, const void *src, size_t bytes);  // blocking, legacy default stream
 // --- caching allocator ---
 void SetCacheBudget(size_t bytes);
 size_t GetCacheBudget();
@@ -100,6 +101,8 @@ class GraphExec {
   GraphExec(const GraphExec &) = delete;
   GraphExec &operator=(const GraphExec &) = delete;
   Status Replay();  // launch on the capture stream and wait for it
+  // `times` launches back to back between two events on the capture stream; milliseconds per launch
+  Status ReplayTimed(int times, float *ms_per_launch);
   Status Sync();
   void Reset();
   bool IsCaptured() const { return exec_ != nullptr; }

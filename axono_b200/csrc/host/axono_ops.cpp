@@ -2,6 +2,14 @@
 
 #include <algorithm>
 
+#include <cublasLt.h>
+#include <cuda_runtime.h>
+#include <dlfcn.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
 #include "axono_b200.h"
 
 namespace axono {
@@ -183,6 +191,151 @@ Status ArgmaxLastDim(const Context &, const Tensor &x, Tensor &result) {
   if (st != Status::OK) return st;
   if (result.dtype() != DataType::INT64 || !Float(x.dtype())) return Status::UNSUPPORTED_TYPE;
   return St(axb200_argmax_last_dim(x.data(), result.data<int64_t>(), (int64_t)rows, (int)cols, Dt(x.dtype()), Stream()));
+}
+
+namespace {
+
+// cuBLASLt is opened on first use, by its soname first: a process that also holds PyTorch then shares
+// the copy PyTorch loaded (two different builds under one soname cannot live side by side - import
+// torch before the first projection in such a process), and a process without it gets the toolkit's.
+struct LtApi {
+  decltype(&cublasLtCreate) Create = nullptr;
+  decltype(&cublasLtMatmulDescCreate) DescCreate = nullptr;
+  decltype(&cublasLtMatmulDescSetAttribute) DescSet = nullptr;
+  decltype(&cublasLtMatrixLayoutCreate) LayoutCreate = nullptr;
+  decltype(&cublasLtMatmulPreferenceCreate) PrefCreate = nullptr;
+  decltype(&cublasLtMatmulPreferenceSetAttribute) PrefSet = nullptr;
+  decltype(&cublasLtMatmulPreferenceDestroy) PrefDestroy = nullptr;
+  decltype(&cublasLtMatmulAlgoGetHeuristic) Heuristic = nullptr;
+  decltype(&cublasLtMatmul) Matmul = nullptr;
+  bool ok = false;
+};
+const LtApi &lt_api() {
+  static LtApi api = [] {
+    LtApi a;
+    void *h = dlopen("libcublasLt.so.12", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) h = dlopen("/usr/local/cuda/lib64/libcublasLt.so.12", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) return a;
+#define AXONO_LT_SYM(field, name) a.field = reinterpret_cast<decltype(a.field)>(dlsym(h, #name))
+    AXONO_LT_SYM(Create, cublasLtCreate);
+    AXONO_LT_SYM(DescCreate, cublasLtMatmulDescCreate);
+    AXONO_LT_SYM(DescSet, cublasLtMatmulDescSetAttribute);
+    AXONO_LT_SYM(LayoutCreate, cublasLtMatrixLayoutCreate);
+    AXONO_LT_SYM(PrefCreate, cublasLtMatmulPreferenceCreate);
+    AXONO_LT_SYM(PrefSet, cublasLtMatmulPreferenceSetAttribute);
+    AXONO_LT_SYM(PrefDestroy, cublasLtMatmulPreferenceDestroy);
+    AXONO_LT_SYM(Heuristic, cublasLtMatmulAlgoGetHeuristic);
+    AXONO_LT_SYM(Matmul, cublasLtMatmul);
+#undef AXONO_LT_SYM
+    a.ok = a.Create && a.DescCreate && a.DescSet && a.LayoutCreate && a.PrefCreate && a.PrefSet && a.PrefDestroy &&
+           a.Heuristic && a.Matmul;
+    return a;
+  }();
+  return api;
+}
+
+// One cuBLASLt handle and one 32 MB workspace per device, made on first use (outside graph capture:
+// the warm-up run of CUDAGraph.capture makes that first call); one matmul plan per (rows, out, in, dtype).
+struct LtState {
+  cublasLtHandle_t handle = nullptr;
+  void *workspace = nullptr;
+  size_t workspace_bytes = size_t(32) << 20;
+  struct Plan {
+    cublasLtMatmulDesc_t op = nullptr;
+    cublasLtMatrixLayout_t a = nullptr, b = nullptr, c = nullptr;
+    cublasLtMatmulAlgo_t algo;
+  };
+  std::map<std::tuple<int64_t, int64_t, int64_t, int>, Plan> plans;
+};
+std::mutex g_lt_mu;
+LtState g_lt[64];
+
+}  // namespace
+
+Status LinearNoBias(const Context &, const Tensor &x, const Tensor &w, Tensor &result) {
+  if (x.ndim() != 2 || w.ndim() != 2 || x.shape()[1] != w.shape()[1]) return Status::SHAPE_MISMATCH;
+  if (!Float(x.dtype()) || w.dtype() != x.dtype()) return Status::UNSUPPORTED_TYPE;
+  if (!Cuda(x) || !Cuda(w)) return Status::DEVICE_MISMATCH;
+  const int64_t rows = (int64_t)x.shape()[0], in = (int64_t)x.shape()[1], out = (int64_t)w.shape()[0];
+  Status st = result.Resize({(size_t)rows, (size_t)out});
+  if (st != Status::OK) return st;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return Status::DEVICE_ERROR;
+  const LtApi &api = lt_api();
+  if (!api.ok) return Status::INTERNAL_ERROR;
+  std::lock_guard<std::mutex> lock(g_lt_mu);
+  LtState &lt = g_lt[dev];
+  if (!lt.handle) {
+    if (core::cuda::IsCapturing()) return Status::INVALID_ARGUMENT;  // first use must be outside a capture
+    if (api.Create(&lt.handle) != CUBLAS_STATUS_SUCCESS) return Status::DEVICE_ERROR;
+    if (cudaMalloc(&lt.workspace, lt.workspace_bytes) != cudaSuccess) return Status::OUT_OF_MEMORY;
+  }
+  const bool half = x.dtype() == DataType::FLOAT16;
+  const cudaDataType_t dt = half ? CUDA_R_16F : CUDA_R_32F;
+  auto key = std::make_tuple(rows, out, in, (int)half);
+  auto it = lt.plans.find(key);
+  if (it == lt.plans.end()) {
+    if (core::cuda::IsCapturing()) return Status::INVALID_ARGUMENT;  // plans are made in the warm-up run
+    // Row-major result (rows, out) = x . w^T is column-major (out, rows) = w_cm^T . x_cm, where the
+    // row-major buffers read column-major are w_cm (in, out) and x_cm (in, rows).
+    LtState::Plan pl;
+    const cublasOperation_t ta = CUBLAS_OP_T, tb = CUBLAS_OP_N;
+    bool ok = api.DescCreate(&pl.op, CUBLAS_COMPUTE_32F, CUDA_R_32F) == CUBLAS_STATUS_SUCCESS;
+    ok = ok && api.DescSet(pl.op, CUBLASLT_MATMUL_DESC_TRANSA, &ta, sizeof(ta)) == CUBLAS_STATUS_SUCCESS;
+    ok = ok && api.DescSet(pl.op, CUBLASLT_MATMUL_DESC_TRANSB, &tb, sizeof(tb)) == CUBLAS_STATUS_SUCCESS;
+    ok = ok && api.LayoutCreate(&pl.a, dt, in, out, in) == CUBLAS_STATUS_SUCCESS;    // w_cm
+    ok = ok && api.LayoutCreate(&pl.b, dt, in, rows, in) == CUBLAS_STATUS_SUCCESS;   // x_cm
+    ok = ok && api.LayoutCreate(&pl.c, dt, out, rows, out) == CUBLAS_STATUS_SUCCESS; // result_cm
+    cublasLtMatmulPreference_t pref = nullptr;
+    ok = ok && api.PrefCreate(&pref) == CUBLAS_STATUS_SUCCESS;
+    ok = ok && api.PrefSet(pref, CUBLASLT_MATMUL_PREF_MAX_WORKSPACE_BYTES, &lt.workspace_bytes,
+                                                    sizeof(lt.workspace_bytes)) == CUBLAS_STATUS_SUCCESS;
+    cublasLtMatmulHeuristicResult_t heur{};
+    int found = 0;
+    ok = ok && api.Heuristic(lt.handle, pl.op, pl.a, pl.b, pl.c, pl.c, pref, 1, &heur, &found) ==
+                   CUBLAS_STATUS_SUCCESS && found > 0;
+    if (pref) api.PrefDestroy(pref);
+    if (!ok) return Status::INTERNAL_ERROR;
+    pl.algo = heur.algo;
+    it = lt.plans.emplace(key, pl).first;
+  }
+  const LtState::Plan &pl = it->second;
+  const float alpha = 1.f, beta = 0.f;
+  const cublasStatus_t cs = api.Matmul(lt.handle, pl.op, &alpha, w.data(), pl.a, x.data(), pl.b, &beta, result.data(),
+                                           pl.c, result.data(), pl.c, &pl.algo, lt.workspace, lt.workspace_bytes,
+                                           static_cast<cudaStream_t>(Stream()));
+  return cs == CUBLAS_STATUS_SUCCESS ? Status::OK : Status::DEVICE_ERROR;
+}
+
+Status SiluMulRows(const Context &, const Tensor &gate_up, int n, Tensor &result) {
+  if (gate_up.ndim() != 2 || n <= 0 || gate_up.shape()[1] != (size_t)(2 * n)) return Status::SHAPE_MISMATCH;
+  if (!Float(gate_up.dtype())) return Status::UNSUPPORTED_TYPE;
+  Status st = result.Resize({gate_up.shape()[0], (size_t)n});
+  if (st != Status::OK) return st;
+  return St(axb200_silu_mul_rows(gate_up.data(), (int64_t)gate_up.shape()[1], n, (int64_t)gate_up.shape()[0],
+                                 result.data(), Dt(gate_up.dtype()), Stream()));
+}
+
+Status QkvNormRopeAppend(const Context &, const Tensor &qkv, int hq, const Tensor *q_norm_w, const Tensor *k_norm_w,
+                         float eps, axb200_kv_arena *arena, int layer, const Tensor *pos, const Tensor *inv_freq,
+                         float theta, bool rotate, bool mrope, int h_sec, int w_sec, int slot_delta, bool advance,
+                         Tensor &q_out) {
+  if (!arena || qkv.ndim() != 2 || !Float(qkv.dtype())) return Status::UNSUPPORTED_TYPE;
+  int n_layers, num_pages, hkv, page_tokens, d, dtype, max_seqs, max_blocks;
+  if (axb200_kv_arena_geometry(arena, &n_layers, &num_pages, &hkv, &page_tokens, &d, &dtype, &max_seqs, &max_blocks) != 0)
+    return Status::INVALID_PTR;
+  if ((int)qkv.shape()[0] != max_seqs || qkv.shape()[1] != (size_t)((hq + 2 * hkv) * d) || Dt(qkv.dtype()) != dtype ||
+      layer < 0 || layer >= n_layers)
+    return Status::SHAPE_MISMATCH;
+  Status st = q_out.Resize({(size_t)max_seqs, (size_t)hq, (size_t)d});
+  if (st != Status::OK) return st;
+  return St(axb200_qkv_norm_rope_append(qkv.data(), (int64_t)qkv.shape()[1], q_norm_w ? q_norm_w->data() : nullptr,
+                                        k_norm_w ? k_norm_w->data() : nullptr, eps, q_out.data(),
+                                        axb200_kv_arena_k_pages(arena, layer), axb200_kv_arena_v_pages(arena, layer),
+                                        axb200_kv_arena_block_table(arena), axb200_kv_arena_seq_lens(arena),
+                                        pos ? pos->data<int64_t>() : nullptr, inv_freq ? inv_freq->data<float>() : nullptr,
+                                        theta, rotate, mrope, h_sec, w_sec, max_seqs, hq, hkv, d, page_tokens, max_blocks,
+                                        num_pages, dtype, slot_delta, advance, Stream()));
 }
 
 Status KvAppendRope(const Context &, Tensor *q, const Tensor &k_new, const Tensor &v_new, axb200_kv_arena *arena,

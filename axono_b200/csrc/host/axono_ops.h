@@ -32,6 +32,19 @@ Status Concat(const Context &ctx, const Tensor &a, const Tensor &b, int axis, Te
 Status Embedding(const Context &ctx, const Tensor &ids, const Tensor &table, Tensor &result);
 Status ArgmaxLastDim(const Context &ctx, const Tensor &x, Tensor &result);
 
+// x (rows, in) . w (out, in)^T -> (rows, out): the projection GEMM of the text tower, a plain cuBLASLt
+// call as in the reference (src/ops/cuda/linear.cu:105-203, Python linear_nobias); FLOAT16 with fp32
+// accumulation, or FLOAT32.  A library GEMM, outside the rewritten path.
+Status LinearNoBias(const Context &ctx, const Tensor &x, const Tensor &w, Tensor &result);
+
+// Glue kernels of the tower (new): silu_mul on the halves of a fused gate|up projection, and per-head
+// norm + rope + append straight from the QKV projection's output.
+Status SiluMulRows(const Context &ctx, const Tensor &gate_up, int n, Tensor &result);
+Status QkvNormRopeAppend(const Context &ctx, const Tensor &qkv, int hq, const Tensor *q_norm_w, const Tensor *k_norm_w,
+                         float eps, axb200_kv_arena *arena, int layer, const Tensor *pos, const Tensor *inv_freq,
+                         float theta, bool rotate, bool mrope, int h_sec, int w_sec, int slot_delta, bool advance,
+                         Tensor &q_out);
+
 // Paged cache (new operators; the cache lives in a KV arena).
 Status KvAppendRope(const Context &ctx, Tensor *q, const Tensor &k_new, const Tensor &v_new, axb200_kv_arena *arena,
                     int layer, const Tensor *pos, const Tensor *inv_freq, float theta, bool rotate, bool mrope,

@@ -303,6 +303,22 @@ PYBIND11_MODULE(libaxono, m) {
         },
         py::arg("x"));
 
+  m.def("linear_nobias",
+        [](const Tensor &x, const Tensor &w) {
+          Tensor result(x.dtype(), {}, x.device());
+          Check("linear_nobias", aops::LinearNoBias(Context(), x, w, result));
+          return result;
+        },
+        py::arg("x"), py::arg("weight"));
+  m.def("silu_mul_rows",
+        [](const Tensor &gate_up, int n) {
+          NeedCuda("silu_mul_rows", gate_up);
+          Tensor result(gate_up.dtype(), {}, gate_up.device());
+          Check("silu_mul_rows", aops::SiluMulRows(Context(), gate_up, n, result));
+          return result;
+        },
+        py::arg("gate_up"), py::arg("n"));
+
   // ---- paged KV arena (new operators) ----
   py::class_<Arena>(m, "KVArena")
       .def(py::init([](int n_layers, int num_pages, int hkv, int page_tokens, int d, DataType dtype, int max_seqs,
@@ -340,6 +356,16 @@ PYBIND11_MODULE(libaxono, m) {
              d["device_bytes"] = bytes;
              return d;
            })
+      .def("set_seq_lens",  // overwrites the device-side lengths (a cache filled by other means, tests, benchmarks)
+           [](Arena &a, py::array_t<int32_t, py::array::c_style | py::array::forcecast> lens) {
+             int nl, np, hkv, pt, d, dt, ms, mb;
+             axb200_kv_arena_geometry(a.h, &nl, &np, &hkv, &pt, &d, &dt, &ms, &mb);
+             if (lens.size() != ms) throw std::runtime_error("set_seq_lens: one length per sequence slot");
+             for (py::ssize_t i = 0; i < lens.size(); ++i)
+               if (lens.data()[i] < 0 || lens.data()[i] > (int64_t)mb * pt) throw std::runtime_error("set_seq_lens: length out of range");
+             Check("set_seq_lens", acuda::CopyToDevice(axb200_kv_arena_seq_lens(a.h), lens.data(), ms * sizeof(int32_t)));
+           },
+           py::arg("lens"))
       .def("seq_lens", [](Arena &a) {  // host copy of the device-side lengths
         int nl, np, hkv, pt, d, dt, ms, mb;
         axb200_kv_arena_geometry(a.h, &nl, &np, &hkv, &pt, &d, &dt, &ms, &mb);
@@ -368,6 +394,32 @@ PYBIND11_MODULE(libaxono, m) {
         py::arg("pos") = py::none(), py::arg("inv_freq") = py::none(), py::arg("theta") = 1e6f,
         py::arg("rotate") = true, py::arg("mrope_section") = py::none(), py::arg("slot_delta") = 0,
         py::arg("advance") = true);
+  m.def("qkv_norm_rope_append",
+        [](Arena &arena, int layer, const Tensor &qkv, int hq, py::object q_norm_w, py::object k_norm_w, float eps,
+           py::object pos, py::object inv_freq, float theta, bool rotate, py::object mrope_section, int slot_delta,
+           bool advance) {
+          const Tensor *qn = q_norm_w.is_none() ? nullptr : q_norm_w.cast<const Tensor *>();
+          const Tensor *kn = k_norm_w.is_none() ? nullptr : k_norm_w.cast<const Tensor *>();
+          const Tensor *pp = pos.is_none() ? nullptr : pos.cast<const Tensor *>();
+          const Tensor *fp = inv_freq.is_none() ? nullptr : inv_freq.cast<const Tensor *>();
+          int h_sec = 0, w_sec = 0;
+          const bool mrope = !mrope_section.is_none();
+          if (mrope) {
+            auto sec = mrope_section.cast<std::vector<int>>();
+            if (sec.size() != 3) throw std::runtime_error("mrope_section: (t, h, w)");
+            h_sec = sec[1];
+            w_sec = sec[2];
+          }
+          Tensor q_out(qkv.dtype(), {}, qkv.device());
+          Check("qkv_norm_rope_append",
+                aops::QkvNormRopeAppend(Context(), qkv, hq, qn, kn, eps, arena.h, layer, pp, fp, theta, rotate, mrope,
+                                        h_sec, w_sec, slot_delta, advance, q_out));
+          return q_out;
+        },
+        py::arg("arena"), py::arg("layer"), py::arg("qkv"), py::arg("hq"), py::arg("q_norm_w") = py::none(),
+        py::arg("k_norm_w") = py::none(), py::arg("eps") = 1e-6f, py::arg("pos") = py::none(),
+        py::arg("inv_freq") = py::none(), py::arg("theta") = 1e6f, py::arg("rotate") = true,
+        py::arg("mrope_section") = py::none(), py::arg("slot_delta") = 0, py::arg("advance") = true);
   m.def("gqa_decode_attention_paged",
         [](const Tensor &q, Arena &arena, int layer, int64_t max_seq_len) {
           Tensor result(q.dtype(), q.shape(), q.device());
@@ -423,6 +475,13 @@ PYBIND11_MODULE(libaxono, m) {
       .def("sync", [](acuda::GraphExec &self) {
         if (self.Sync() != Status::OK) throw std::runtime_error("CUDAGraph.sync failed");
       })
+      .def("replay_timed",  // `times` launches between two CUDA events on the capture stream: ms per launch
+           [](acuda::GraphExec &self, int times) {
+             float ms = 0.f;
+             if (self.ReplayTimed(times, &ms) != Status::OK) throw std::runtime_error("CUDAGraph.replay_timed failed");
+             return ms;
+           },
+           py::arg("times"))
       .def("reset", [](acuda::GraphExec &self) {
         self.Reset();
         acuda::ResetCapturePool();

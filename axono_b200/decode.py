@@ -15,7 +15,6 @@ collective of the step.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
 from typing import Optional, Tuple
 
 import torch
@@ -23,6 +22,7 @@ import torch.distributed as dist
 
 from . import ops, sharding
 from .kv_cache import PagedKVCache
+from .tower_config import TextTowerConfig  # noqa: F401 - re-exported
 
 
 def decode_block(x, residual, norm_weight, q, k_new, v_new, cache: PagedKVCache, layer: int, gate, up,
@@ -35,22 +35,6 @@ def decode_block(x, residual, norm_weight, q, k_new, v_new, cache: PagedKVCache,
     attn = cache.attend(layer, q)
     act = ops.silu_mul(gate, up)
     return y, xn, attn, act
-
-
-@dataclass
-class TextTowerConfig:
-    hidden: int = 2048
-    intermediate: int = 6144
-    n_q_heads: int = 16
-    n_kv_heads: int = 8
-    head_dim: int = 128
-    vocab: int = 151936
-    n_layers: int = 28
-    eps: float = 1e-6
-    rope_theta: float = 1e6
-    mrope_section: Tuple[int, int, int] = (24, 20, 20)
-    use_mrope: bool = True
-    qk_norm: bool = True
 
 
 class TextTower:

@@ -69,6 +69,10 @@ class CUDAGraph:
     def sync(self):
         self._impl.sync()
 
+    def replay_timed(self, times: int) -> float:
+        """`times` launches back to back between two CUDA events on the capture stream: ms per launch."""
+        return self._impl.replay_timed(times)
+
     def reset(self):
         self._impl.reset()
         self.output, self.outputs = None, []

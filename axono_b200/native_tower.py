@@ -1,0 +1,104 @@
+"""The text tower's decode step on the native runtime (no PyTorch): the caller of the path that the
+full-step configuration names, written over `libaxono` tensors exactly as the reference's model is
+written over its own (axono/python/examples/vlm/qwen3vl/model.py:330-373 attention, :408-436 layer,
+:483-486 final norm + tied lm_head, :729-761 decode_step), batched, with the two fusions of this
+library (per-head norm + rope + append in one launch after the QKV projection; the residual add that
+ends a layer folded into the next add_rms_norm).  Projections are cuBLASLt calls (`linear_nobias`).
+One GPU; the multi-GPU tower lives in `axono_b200.decode` on torch.distributed plumbing."""
+from __future__ import annotations
+
+import numpy as np
+
+from . import native
+from .tower_config import TextTowerConfig
+
+
+class NativeTextTower:
+    """Random-init weights (numpy, fp16), KV pages in an arena, one token per row and step.
+    `decode_step()` is capturable: positions are the cache lengths on the device, the next token ids are
+    written back into `token_ids` on the device."""
+
+    def __init__(self, cfg: TextTowerConfig, batch: int, max_seq_len: int, seed: int = 0, page_tokens: int = 64,
+                 weights=None):
+        lx = native.load()
+        self.lx, self.cfg, self.batch, self.max_seq_len = lx, cfg, batch, max_seq_len
+        d = cfg.head_dim
+        rng = np.random.default_rng(seed)
+        pool = (0.02 * rng.standard_normal(1 << 24, dtype=np.float32)).astype(np.float16)
+
+        def w(rows, cols):  # N(0, 0.02) drawn from a pool at a random offset: cheap for 1.7 G parameters
+            n = rows * cols
+            off = int(rng.integers(0, pool.size))
+            return np.resize(np.roll(pool, -off), n).reshape(rows, cols)
+
+        def ones(n):
+            return (1.0 + 0.02 * rng.standard_normal(n, dtype=np.float32)).astype(np.float16)
+
+        if weights is None:
+            weights = {"embed": w(cfg.vocab, cfg.hidden), "final_ln": ones(cfg.hidden), "layers": []}
+            for _ in range(cfg.n_layers):
+                weights["layers"].append({
+                    "input_ln": ones(cfg.hidden), "post_ln": ones(cfg.hidden),
+                    "qkv": w((cfg.n_q_heads + 2 * cfg.n_kv_heads) * d, cfg.hidden),
+                    "q_norm": ones(d), "k_norm": ones(d),
+                    "o": w(cfg.hidden, cfg.n_q_heads * d),
+                    "gate_up": w(2 * cfg.intermediate, cfg.hidden),
+                    "down": w(cfg.hidden, cfg.intermediate),
+                })
+        self.host_weights = weights
+
+        def dev(a):
+            return lx.Tensor.from_numpy(np.ascontiguousarray(a), "cuda")
+
+        self.embed, self.final_ln = dev(weights["embed"]), dev(weights["final_ln"])
+        self.layers = [{k: dev(v) for k, v in lw.items()} for lw in weights["layers"]]
+        self.inv_freq = dev((1.0 / (cfg.rope_theta ** (np.arange(0, d, 2, dtype=np.float32) / d))).astype(np.float32))
+        blocks = (max_seq_len + page_tokens - 1) // page_tokens
+        self.arena = lx.KVArena(cfg.n_layers, batch * blocks, cfg.n_kv_heads, page_tokens, d, lx.DataType.FLOAT16,
+                                batch, blocks)
+        for _ in range(batch):
+            self.arena.alloc_seq(max_seq_len)
+        self.arena.sync()
+        self.token_ids = dev(np.zeros(batch, np.int64))
+        self.last_logits = None
+
+    def set_state(self, token_ids, lens) -> None:
+        """Starts decoding at cache lengths `lens` (one per row); positions are the lengths."""
+        self.token_ids.copy_from_numpy(np.asarray(token_ids, dtype=np.int64))
+        self.arena.set_seq_lens(np.asarray(lens, dtype=np.int32))
+
+    def decode_step(self):
+        lx, cfg = self.lx, self.cfg
+        h = lx.embedding(self.token_ids, self.embed)
+        mlp_out = None
+        for li, lw in enumerate(self.layers):
+            if mlp_out is None:
+                xn = lx.rms_norm(h, lw["input_ln"], cfg.eps)
+            else:  # previous layer's h + mlp folded into this layer's input norm
+                h, xn = lx.add_rms_norm(mlp_out, h, lw["input_ln"], cfg.eps)
+            qkv = lx.linear_nobias(xn, lw["qkv"])
+            q = lx.qkv_norm_rope_append(
+                self.arena, li, qkv, cfg.n_q_heads, lw["q_norm"] if cfg.qk_norm else None,
+                lw["k_norm"] if cfg.qk_norm else None, cfg.eps, inv_freq=self.inv_freq, theta=cfg.rope_theta,
+                mrope_section=list(cfg.mrope_section) if cfg.use_mrope else None,
+                slot_delta=0 if li == 0 else -1, advance=li == 0)
+            attn = lx.gqa_decode_attention_paged(q, self.arena, li, self.max_seq_len)
+            attn.reshape([self.batch, cfg.n_q_heads * cfg.head_dim])
+            h, xn2 = lx.add_rms_norm(lx.linear_nobias(attn, lw["o"]), h, lw["post_ln"], cfg.eps)
+            act = lx.silu_mul_rows(lx.linear_nobias(xn2, lw["gate_up"]), cfg.intermediate)
+            mlp_out = lx.linear_nobias(act, lw["down"])
+        _, xf = lx.add_rms_norm(mlp_out, h, self.final_ln, cfg.eps)
+        self.last_logits = lx.linear_nobias(xf, self.embed)  # tied lm_head
+        nxt = lx.argmax(self.last_logits)
+        self.token_ids.copy_from(nxt)
+        return nxt
+
+    def kv_bytes_per_step(self, lens) -> float:
+        """Algorithmic KV bytes attention reads in one step at cache lengths `lens`."""
+        return float(2 * sum(int(n) + 1 for n in lens) * self.cfg.n_kv_heads * self.cfg.head_dim * 2 * self.cfg.n_layers)
+
+    def weight_bytes(self) -> float:
+        n = self.host_weights["embed"].size + self.host_weights["final_ln"].size
+        for lw in self.host_weights["layers"]:
+            n += sum(v.size for v in lw.values())
+        return float(2 * n)

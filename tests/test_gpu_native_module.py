@@ -1,9 +1,11 @@
 """The native `libaxono` module on the GPU, written the way the reference tests its binding
 (axono/python/tests/core/{test_gqa,test_fused,test_llm_ops,test_sequence_ops,test_cuda_graph}.py):
-numpy in, Tensor through the operators, numpy out, checked against the CPU oracle.  No PyTorch in
-these tests' data path; tolerances: fp32 1e-5, fp16 2e-3 (max|out - ref| / max|ref|)."""
+numpy in, Tensor through the operators, numpy out, checked against the CPU oracle.  PyTorch appears only in
+the tower comparison (and is imported first: one cuBLASLt per process); tolerances: fp32 1e-5, fp16 2e-3
+(max|out - ref| / max|ref|)."""
 import numpy as np
 import pytest
+import torch  # noqa: F401 - before the native module's first projection: one process, one cuBLASLt (see axono_ops.cpp)
 
 import oracle
 from axono_b200 import native
@@ -274,3 +276,60 @@ def test_compile_caches_one_graph_per_signature(lx, chk):
     assert m.num_graphs == 2
     with pytest.raises(ValueError):
         native.compile(Block(), mode="max")
+
+
+def test_linear_nobias_and_glue(lx):
+    """linear_nobias is a cuBLASLt call (x . w^T, row-major); silu_mul_rows works on the halves of a
+    fused gate|up output."""
+    rng = np.random.default_rng(10)
+    for dtype, tol in ((np.float32, 1e-4), (np.float16, 4e-3)):  # fp32 runs as TF32-free SGEMM; fp16 accumulates in fp32
+        x = rng.standard_normal((5, 192), dtype=np.float32).astype(dtype)
+        w = (0.1 * rng.standard_normal((320, 192), dtype=np.float32)).astype(dtype)
+        y = lx.linear_nobias(dev(lx, x), dev(lx, w))
+        assert y.shape == (5, 320)
+        ref = f32(x) @ f32(w).T
+        assert oracle.rel_err(f32(y.numpy()), ref) <= tol
+    gu = rng.standard_normal((4, 256), dtype=np.float32)
+    act = lx.silu_mul_rows(dev(lx, gu), 128)
+    assert oracle.rel_err(act.numpy(), oracle.port().silu_mul(gu[:, :128].copy(), gu[:, 128:].copy())) <= 1e-5
+    with pytest.raises(RuntimeError):
+        lx.linear_nobias(dev(lx, np.zeros((2, 8), np.float32)), dev(lx, np.zeros((4, 9), np.float32)))
+
+
+def test_native_tower_matches_torch_tower():
+    """The tower's decode step on the native runtime against the same step on the torch-tensor mirror,
+    same weights, three steps eagerly and three more as one captured graph."""
+    import torch
+
+    from axono_b200.decode import TextTower
+    from axono_b200.native_tower import NativeTextTower
+    from axono_b200.tower_config import TextTowerConfig
+
+    cfg = TextTowerConfig(hidden=256, intermediate=512, n_q_heads=4, n_kv_heads=2, head_dim=128, vocab=1000, n_layers=3)
+    batch, lens = 3, [70, 5, 129]
+    nt = NativeTextTower(cfg, batch, 256, seed=3)
+    tt = TextTower(cfg, batch, 256, page_tokens=64)
+    hw = nt.host_weights
+    tt.embed.copy_(torch.from_numpy(hw["embed"]))
+    tt.final_ln.copy_(torch.from_numpy(hw["final_ln"]))
+    for lw_t, lw_n in zip(tt.layers, hw["layers"]):
+        for k in lw_t:
+            lw_t[k].copy_(torch.from_numpy(lw_n[k]))
+    ids = [1, 2, 3]
+    nt.set_state(ids, lens)
+    tt.set_state(ids, lens)
+    for _ in range(3):
+        n_ids, t_ids = nt.decode_step().numpy(), tt.decode_step().cpu().numpy()
+        ref = tt.last_logits.float().cpu().numpy()
+        assert oracle.rel_err(nt.last_logits.numpy().astype(np.float32), ref) <= 2e-2
+        assert np.array_equal(n_ids, t_ids)
+    assert list(nt.arena.seq_lens()) == [n + 3 for n in lens]
+    g = native.CUDAGraph().capture(nt.decode_step)
+    # capture's warm-up run was a real step: put the state back one token
+    nt.set_state(t_ids, [n + 3 for n in lens])
+    for _ in range(3):
+        g.replay()
+        t_ids = tt.decode_step().cpu().numpy()
+        assert oracle.rel_err(nt.last_logits.numpy().astype(np.float32), tt.last_logits.float().cpu().numpy()) <= 2e-2
+        assert np.array_equal(g.output.numpy(), t_ids)
+    assert g.replay_timed(5) > 0
