@@ -140,6 +140,10 @@ Status CopyToDevice(void *device_dst, const void *src, size_t bytes) {
   return cudaMemcpy(device_dst, src, bytes, cudaMemcpyHostToDevice) == cudaSuccess ? Status::OK : Status::DEVICE_ERROR;
 }
 
+Status CopyOnDevice(void *device_dst, const void *device_src, size_t bytes) {
+  return cudaMemcpy(device_dst, device_src, bytes, cudaMemcpyDeviceToDevice) == cudaSuccess ? Status::OK : Status::DEVICE_ERROR;
+}
+
 void SetCacheBudget(size_t bytes) {
   Cache &c = cache();
   std::lock_guard<std::mutex> lock(c.mu);
@@ -175,7 +179,7 @@ void SetCapturePoolRecording(bool on) {
   for (auto &e : p.entries) e.used = false;
 }
 
-std::shared_ptr<void> AllocateStorage(size_t bytes, const std::string &device) {
+std::shared_ptr<void> AllocateStorage(size_t bytes, const std::string &device, bool zero) {
   const int dev = ParseDevice(device);
   if (dev < 0) throw std::runtime_error("bad device string: " + device);
   int count = 0;
@@ -190,7 +194,7 @@ std::shared_ptr<void> AllocateStorage(size_t bytes, const std::string &device) {
     for (auto &e : cp.entries)
       if (!e.used && e.dev == dev && e.bytes == bytes) {
         e.used = true;
-        cudaMemsetAsync(e.ptr, 0, bytes, st);  // recorded as a memset node: storage starts at zero on every replay
+        if (zero) cudaMemsetAsync(e.ptr, 0, bytes, st);  // a memset node: storage starts at zero on every replay
         return std::shared_ptr<void>(e.ptr, [](void *) {});  // pool-owned
       }
   }
@@ -204,7 +208,7 @@ std::shared_ptr<void> AllocateStorage(size_t bytes, const std::string &device) {
       cudaGetLastError();
       throw std::runtime_error("stream-ordered allocation failed during graph capture");
     }
-    cudaMemsetAsync(p, 0, bytes, st);
+    if (zero) cudaMemsetAsync(p, 0, bytes, st);
     const uint64_t gen = t_capture_gen;
     return std::shared_ptr<void>(p, [gen, st](void *q) {
       if (t_capturing && t_capture_gen == gen) cudaFreeAsync(q, st);
@@ -212,7 +216,7 @@ std::shared_ptr<void> AllocateStorage(size_t bytes, const std::string &device) {
   }
   void *p = CacheAcquire(dev, bytes);
   if (p) {
-    cudaMemsetAsync(p, 0, bytes, st);
+    if (zero) cudaMemsetAsync(p, 0, bytes, st);
   } else {
     if (cudaMalloc(&p, bytes) != cudaSuccess) {
       cudaGetLastError();
@@ -222,7 +226,7 @@ std::shared_ptr<void> AllocateStorage(size_t bytes, const std::string &device) {
         throw std::bad_alloc();
       }
     }
-    cudaMemsetAsync(p, 0, bytes, st);
+    if (zero) cudaMemsetAsync(p, 0, bytes, st);
   }
   bool recorded = false;
   {
@@ -349,12 +353,22 @@ void Tensor::Allocate() {
   const size_t bytes = num_bytes();
   if (bytes == 0) return;
   if (is_cuda()) {
-    data_ = cuda::AllocateStorage(bytes, device_);
+    data_ = cuda::AllocateStorage(bytes, device_, zero_fill_);
   } else {
     void *p = std::calloc(1, bytes);  // new storage is zero-filled
     if (!p) throw std::bad_alloc();
     data_ = std::shared_ptr<void>(p, std::free);
   }
+}
+
+Tensor Tensor::Uninitialized(DataType dtype, const Shape &shape, const std::string &device) {
+  Tensor t(dtype);
+  t.device_ = device;
+  t.zero_fill_ = !t.is_cuda();  // host storage stays calloc'ed
+  t.shape_ = shape;
+  t.num_elements_ = CalculateNumElements(shape);
+  t.Allocate();
+  return t;
 }
 
 Tensor Tensor::FromBorrowed(DataType dtype, const Shape &shape, const void *data) {

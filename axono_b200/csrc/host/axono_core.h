@@ -42,6 +42,10 @@ class Tensor {
   // copy = share storage; move = take storage (defaults do exactly that)
 
   static Tensor FromBorrowed(DataType dtype, const Shape &shape, const void *data);  // host memory, not owned
+  // Device storage without the zero fill, for results an operator overwrites completely (the binding
+  // layer's outputs): the fill would be one more memset per operator in every captured graph.  Storage
+  // the tensor takes later through Resize is not filled either.
+  static Tensor Uninitialized(DataType dtype, const Shape &shape, const std::string &device);
 
   const std::string &device() const { return device_; }
   bool is_cuda() const { return device_.compare(0, 4, "cuda") == 0; }
@@ -72,6 +76,7 @@ class Tensor {
   Shape shape_;
   std::string device_ = "cpu";
   size_t num_elements_ = 0;
+  bool zero_fill_ = true;
   std::shared_ptr<void> data_;
 };
 
@@ -81,12 +86,13 @@ bool Available();
 Status DeviceSynchronize();
 Status CopyToHost(void *dst, const void *device_src, size_t bytes);  // blocking, legacy default stream
 Status CopyToDevice(void *device_dst, const void *src, size_t bytes);  // blocking, legacy default stream
+Status CopyOnDevice(void *device_dst, const void *device_src, size_t bytes);  // blocking, legacy default stream
 // --- caching allocator ---
 void SetCacheBudget(size_t bytes);
 size_t GetCacheBudget();
 size_t GetCachedBytes();
 void ClearDeviceCache();
-std::shared_ptr<void> AllocateStorage(size_t bytes, const std::string &device);  // zero-filled
+std::shared_ptr<void> AllocateStorage(size_t bytes, const std::string &device, bool zero = true);
 
 // --- current stream and graph capture ---
 void *CurrentStream();  // cudaStream_t: legacy default stream, or this thread's capture stream

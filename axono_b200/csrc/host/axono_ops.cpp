@@ -29,7 +29,7 @@ bool Cuda(const Tensor &t) { return t.is_cuda(); }
 // Scratch comes from the caching pool, like the reference's three workspace tensors
 // (src/ops/cuda/gqa.cu:166-168); after the first call of a shape it is a pool hit.
 Tensor Scratch(size_t bytes, const std::string &device) {
-  return Tensor(DataType::INT8, {std::max<size_t>(bytes, 16)}, device);
+  return Tensor::Uninitialized(DataType::INT8, {std::max<size_t>(bytes, 16)}, device);
 }
 
 }  // namespace

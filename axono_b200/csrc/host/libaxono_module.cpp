@@ -204,7 +204,7 @@ PYBIND11_MODULE(libaxono, m) {
   // ---- operators ----
   m.def("gqa_decode_attention",
         [](const Tensor &q, const Tensor &k, const Tensor &v) {
-          Tensor result(q.dtype(), q.shape(), q.device());
+          Tensor result = Tensor::Uninitialized(q.dtype(), q.shape(), q.device());
           Check("gqa_decode_attention", aops::GqaDecodeAttention(Context(), q, k, v, result));
           return result;
         },
@@ -212,7 +212,7 @@ PYBIND11_MODULE(libaxono, m) {
   m.def("scaled_dot_product_attention",
         [](const Tensor &q, const Tensor &k, const Tensor &v, bool is_causal) {
           NeedCuda("scaled_dot_product_attention", q);
-          Tensor result(q.dtype(), q.shape(), q.device());
+          Tensor result = Tensor::Uninitialized(q.dtype(), q.shape(), q.device());
           Check("scaled_dot_product_attention", aops::ScaledDotProductAttention(Context(), q, k, v, is_causal, result));
           return result;
         },
@@ -220,7 +220,7 @@ PYBIND11_MODULE(libaxono, m) {
   m.def("silu_mul",
         [](const Tensor &gate, const Tensor &up) {
           NeedCuda("silu_mul", gate);
-          Tensor result(gate.dtype(), gate.shape(), gate.device());
+          Tensor result = Tensor::Uninitialized(gate.dtype(), gate.shape(), gate.device());
           Check("silu_mul", aops::SiluMul(Context(), gate, up, result));
           return result;
         },
@@ -228,7 +228,7 @@ PYBIND11_MODULE(libaxono, m) {
   m.def("add_rms_norm",
         [](const Tensor &x, const Tensor &residual, const Tensor &weight, float eps) {
           NeedCuda("add_rms_norm", x);
-          Tensor y(x.dtype(), x.shape(), x.device()), out(x.dtype(), x.shape(), x.device());
+          Tensor y = Tensor::Uninitialized(x.dtype(), x.shape(), x.device()), out = Tensor::Uninitialized(x.dtype(), x.shape(), x.device());
           Check("add_rms_norm", aops::AddRmsNorm(Context(), x, residual, weight, eps, y, out));
           return py::make_tuple(y, out);
         },
@@ -238,7 +238,7 @@ PYBIND11_MODULE(libaxono, m) {
           NeedCuda("rms_norm", x);
           if (x.is_cuda() != weight.is_cuda() || x.dtype() != weight.dtype())
             throw std::runtime_error("rms_norm: inputs differ in device or dtype");
-          Tensor result(x.dtype(), x.shape(), x.device());
+          Tensor result = Tensor::Uninitialized(x.dtype(), x.shape(), x.device());
           Check("rms_norm", aops::RmsNorm(Context(), x, weight, eps, result));
           return result;
         },
@@ -246,7 +246,7 @@ PYBIND11_MODULE(libaxono, m) {
   m.def("rope",
         [](const Tensor &x, const Tensor &pos_ids, float theta) {
           NeedCuda("rope", x);
-          Tensor result(x.dtype(), x.shape(), x.device());
+          Tensor result = Tensor::Uninitialized(x.dtype(), x.shape(), x.device());
           Check("rope", aops::Rope(Context(), x, pos_ids, theta, result));
           return result;
         },
@@ -254,7 +254,7 @@ PYBIND11_MODULE(libaxono, m) {
   m.def("rope_with_cos_sin",
         [](const Tensor &x, const Tensor &cos, const Tensor &sin) {
           NeedCuda("rope_with_cos_sin", x);
-          Tensor result(x.dtype(), x.shape(), x.device());
+          Tensor result = Tensor::Uninitialized(x.dtype(), x.shape(), x.device());
           Check("rope_with_cos_sin", aops::RopeWithCosSin(Context(), x, cos, sin, result));
           return result;
         },
@@ -262,7 +262,7 @@ PYBIND11_MODULE(libaxono, m) {
   m.def("rope_thd",
         [](const Tensor &x, const Tensor &pos, const Tensor &inv_freq, int t_sec, int h_sec, int w_sec) {
           NeedCuda("rope_thd", x);
-          Tensor result(x.dtype(), x.shape(), x.device());
+          Tensor result = Tensor::Uninitialized(x.dtype(), x.shape(), x.device());
           Check("rope_thd", aops::RopeThd(Context(), x, pos, inv_freq, t_sec, h_sec, w_sec, result));
           return result;
         },
@@ -270,7 +270,7 @@ PYBIND11_MODULE(libaxono, m) {
   m.def("mrope_cos_sin",
         [](const Tensor &pos, const Tensor &inv_freq, int h_sec, int w_sec) {
           NeedCuda("mrope_cos_sin", pos);
-          Tensor cos_out(DataType::FLOAT32, {}, pos.device()), sin_out(DataType::FLOAT32, {}, pos.device());
+          Tensor cos_out = Tensor::Uninitialized(DataType::FLOAT32, {}, pos.device()), sin_out = Tensor::Uninitialized(DataType::FLOAT32, {}, pos.device());
           Check("mrope_cos_sin", aops::MropeCosSin(Context(), pos, inv_freq, h_sec, w_sec, cos_out, sin_out));
           return py::make_tuple(cos_out, sin_out);
         },
@@ -280,7 +280,7 @@ PYBIND11_MODULE(libaxono, m) {
           NeedCuda("concat", a);
           if (a.is_cuda() != b.is_cuda() || a.dtype() != b.dtype())
             throw std::runtime_error("concat: inputs differ in device or dtype");
-          Tensor result(a.dtype(), {}, a.device());
+          Tensor result = Tensor::Uninitialized(a.dtype(), {}, a.device());
           Check("concat", aops::Concat(Context(), a, b, axis, result));
           return result;
         },
@@ -289,7 +289,7 @@ PYBIND11_MODULE(libaxono, m) {
         [](const Tensor &ids, const Tensor &table) {
           NeedCuda("embedding", table);
           if (ids.is_cuda() != table.is_cuda()) throw std::runtime_error("embedding: inputs are on different devices");
-          Tensor result(table.dtype(), {}, table.device());
+          Tensor result = Tensor::Uninitialized(table.dtype(), {}, table.device());
           Check("embedding", aops::Embedding(Context(), ids, table, result));
           return result;
         },
@@ -297,7 +297,7 @@ PYBIND11_MODULE(libaxono, m) {
   m.def("argmax",
         [](const Tensor &x) {
           NeedCuda("argmax", x);
-          Tensor result(DataType::INT64, {}, x.device());
+          Tensor result = Tensor::Uninitialized(DataType::INT64, {}, x.device());
           Check("argmax", aops::ArgmaxLastDim(Context(), x, result));
           return result;
         },
@@ -305,7 +305,7 @@ PYBIND11_MODULE(libaxono, m) {
 
   m.def("linear_nobias",
         [](const Tensor &x, const Tensor &w) {
-          Tensor result(x.dtype(), {}, x.device());
+          Tensor result = Tensor::Uninitialized(x.dtype(), {}, x.device());
           Check("linear_nobias", aops::LinearNoBias(Context(), x, w, result));
           return result;
         },
@@ -313,7 +313,7 @@ PYBIND11_MODULE(libaxono, m) {
   m.def("silu_mul_rows",
         [](const Tensor &gate_up, int n) {
           NeedCuda("silu_mul_rows", gate_up);
-          Tensor result(gate_up.dtype(), {}, gate_up.device());
+          Tensor result = Tensor::Uninitialized(gate_up.dtype(), {}, gate_up.device());
           Check("silu_mul_rows", aops::SiluMulRows(Context(), gate_up, n, result));
           return result;
         },
@@ -356,6 +356,23 @@ PYBIND11_MODULE(libaxono, m) {
              d["device_bytes"] = bytes;
              return d;
            })
+      .def("fill_pages",  // every K and V pool of every layer <- repetitions of `chunk` (benchmarks: non-zero cache contents)
+           [](Arena &a, py::array chunk) {
+             int nl, np, hkv, pt, d, dt, ms, mb;
+             axb200_kv_arena_geometry(a.h, &nl, &np, &hkv, &pt, &d, &dt, &ms, &mb);
+             py::array c = py::array::ensure(chunk, py::array::c_style);
+             const size_t es = dt == static_cast<int>(DataType::FLOAT16) ? 2 : 4;
+             const size_t pool = (size_t)np * hkv * pt * d * es, cb = (size_t)c.nbytes();
+             if (!c || (size_t)c.itemsize() != es || cb == 0 || cb > pool) throw std::runtime_error("fill_pages: bad chunk");
+             for (int l = 0; l < nl; ++l)
+               for (int kv = 0; kv < 2; ++kv) {
+                 char *base = static_cast<char *>(kv ? axb200_kv_arena_v_pages(a.h, l) : axb200_kv_arena_k_pages(a.h, l));
+                 Check("fill_pages", acuda::CopyToDevice(base, c.data(), cb));
+                 for (size_t have = cb; have < pool; have *= 2)  // doubling device-to-device copies
+                   Check("fill_pages", acuda::CopyOnDevice(base + have, base, std::min(have, pool - have)));
+               }
+           },
+           py::arg("chunk"))
       .def("set_seq_lens",  // overwrites the device-side lengths (a cache filled by other means, tests, benchmarks)
            [](Arena &a, py::array_t<int32_t, py::array::c_style | py::array::forcecast> lens) {
              int nl, np, hkv, pt, d, dt, ms, mb;
@@ -410,7 +427,7 @@ PYBIND11_MODULE(libaxono, m) {
             h_sec = sec[1];
             w_sec = sec[2];
           }
-          Tensor q_out(qkv.dtype(), {}, qkv.device());
+          Tensor q_out = Tensor::Uninitialized(qkv.dtype(), {}, qkv.device());
           Check("qkv_norm_rope_append",
                 aops::QkvNormRopeAppend(Context(), qkv, hq, qn, kn, eps, arena.h, layer, pp, fp, theta, rotate, mrope,
                                         h_sec, w_sec, slot_delta, advance, q_out));
@@ -422,7 +439,7 @@ PYBIND11_MODULE(libaxono, m) {
         py::arg("mrope_section") = py::none(), py::arg("slot_delta") = 0, py::arg("advance") = true);
   m.def("gqa_decode_attention_paged",
         [](const Tensor &q, Arena &arena, int layer, int64_t max_seq_len) {
-          Tensor result(q.dtype(), q.shape(), q.device());
+          Tensor result = Tensor::Uninitialized(q.dtype(), q.shape(), q.device());
           Check("gqa_decode_attention_paged", aops::GqaDecodeAttentionPaged(Context(), q, arena.h, layer, max_seq_len, result));
           return result;
         },

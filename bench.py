@@ -81,18 +81,21 @@ class ClockSampler:
     REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
                0x4: "sw_power_cap", 0x80: "hw_power_brake_slowdown"}
 
-    def __init__(self, torch_index: int):
+    def __init__(self, torch_index: int, use_torch: bool = True):
         self.samples, self.reasons, self.max_mhz = [], set(), None
         self._stop = threading.Event()
         self._active = threading.Event()
         self._thread = None
         try:
             import pynvml
-            import torch
 
             pynvml.nvmlInit()
             self.nv = pynvml
             try:
+                if not use_torch:  # a process without PyTorch: NVML's own index (no CUDA_VISIBLE_DEVICES remapping)
+                    raise LookupError
+                import torch
+
                 uuid = str(torch.cuda.get_device_properties(torch_index).uuid)
                 if not uuid.startswith("GPU-"):
                     uuid = "GPU-" + uuid
@@ -565,6 +568,61 @@ def run_tower(args):
         dist.destroy_process_group()
 
 
+def run_tower_native(args):
+    """`c5_tower --runtime native`: the same 28-layer decode step on the native runtime - libaxono tensors,
+    cuBLASLt projections, one captured graph - with no PyTorch in the process.  One GPU."""
+    from axono_b200 import native
+    from axono_b200.native_tower import NativeTextTower
+    from axono_b200.tower_config import TextTowerConfig
+
+    if int(os.environ.get("WORLD_SIZE", "1")) != 1:
+        raise SystemExit("--runtime native runs on one GPU")
+    lx = native.load()
+    B, L = args.tower_batch, args.tower_len
+    cfg = TextTowerConfig()
+    total_steps = args.warmup + 2 * args.steps + 4
+    tower = NativeTextTower(cfg, B, L + total_steps + 64, seed=5)
+    rng = np.random.default_rng(77)
+    tower.arena.fill_pages((0.5 * rng.standard_normal(1 << 22, dtype=np.float32)).astype(np.float16))
+    lens = [L] * B
+    tower.set_state(np.arange(B) % cfg.vocab, lens)
+    g = native.CUDAGraph().capture(tower.decode_step)
+    tower.set_state(np.arange(B) % cfg.vocab, lens)  # the capture's warm-up run was a real step
+    for _ in range(args.warmup):
+        g.replay()
+    sampler = ClockSampler(0, use_torch=False)
+    sampler.start()
+    step_ms = g.replay_timed(args.steps)  # CUDA events on the capture stream around the K replays
+    sampler.pause()
+    err = lx.device_error_bits()
+    if err:
+        raise SystemExit(f"device error word {err:#x}")
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        g.replay()
+        out = g.output.numpy()  # the host reads the next token ids after every step
+    e2e_s = time.perf_counter() - t0
+    assert "torch" not in sys.modules
+    kv_bytes, other_bytes = tower.kv_bytes_per_step(lens), tower.weight_bytes()
+    peak, kind = measured_peak()
+    line = {
+        "metric": "decode_tokens_per_s", "value": B / (step_ms / 1e3), "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": args.workload, "runtime": "native (libaxono tensors, cuBLASLt projections, no PyTorch)",
+                   "batch": B, "kv_len": L, "cuda_graph": True, "graph_nodes": g.num_nodes, "sharding": "KV heads x1",
+                   "l2": "KV per step larger than L2"},
+        "kv_cache_gbs": kv_bytes / (step_ms / 1e3) / 1e9,
+        "kv_frac_of_measured_peak": kv_bytes / (step_ms / 1e3) / 1e9 / peak,
+        "hbm_bytes_per_step": {"kv": kv_bytes, "weights_per_gpu": other_bytes},
+        "hbm_floor_ms": (kv_bytes + other_bytes) / (peak * 1e9) * 1e3,
+        "e2e": {"value": B * args.steps / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": int(out.nbytes), "ms_per_step": e2e_s / args.steps * 1e3},
+        "gpu_launches": g.num_nodes * args.steps, "clocks": sampler.summary(),
+    }
+    print(json.dumps(line), flush=True)
+
+
 def run_reference_cuda(args):
     """`--impl reference-cuda`: the reference's own CUDA kernels, compiled for sm_100, timed on this GPU
     next to this package's kernel on the same inputs - the reference's op is fp32 and takes one
@@ -671,6 +729,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-cuda"])
     ap.add_argument("--workload", default="c3_ragged", choices=sorted(WORKLOADS) + ["c2_block", "c5_tower", "prefill"])
     ap.add_argument("--prefill-len", type=int, default=8192)
+    ap.add_argument("--runtime", default="torch", choices=["torch", "native"],
+                    help="c5_tower: torch = torch-tensor mirror (any N); native = libaxono runtime, no PyTorch (N = 1)")
     ap.add_argument("--tower-batch", type=int, default=32, help="c5_tower: batch (default: the configuration's 32)")
     ap.add_argument("--tower-len", type=int, default=16384, help="c5_tower: context length (default 16384)")
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
@@ -692,6 +752,9 @@ def main():
     elif args.workload == "prefill":
         if int(os.environ.get("RANK", "0")) == 0:
             run_prefill(args)
+    elif args.workload == "c5_tower" and args.runtime == "native":
+        if int(os.environ.get("RANK", "0")) == 0:
+            run_tower_native(args)
     elif args.workload in ("c2_block", "c5_tower"):
         run_tower(args)
     else:
