@@ -544,9 +544,15 @@ gqa_split_f32_kernel(const __grid_constant__ CUtensorMap tmK,
   finalize_chunk<float>(p, mO, mM, mL, b, hk, chunk, threadIdx.x, sl2);
 }
 
-// ---- generic split kernel: any head_dim <= 256, any group ------------------------------------
-// Plain coalesced loads, one warp per token stride; used for shapes the tiled kernels do not
-// cover (head_dim != 128, unaligned pointers).  Correctness path, not a tuned one.
+// ---- generic split kernel: any head_dim <= 256, any group, any alignment ---------------------------
+// For the shapes the TMA kernels do not take (head_dim != 128, pointers off 16 bytes, odd groups).
+// Same split-K scheme and partial format; tiles of keys are staged in shared memory as fp32 with plain
+// coalesced loads (a warp reads a row), every query head of the KV head works on the staged tile:
+//   scores   thread = (key, head subset): one K value from shared memory feeds all its heads
+//   softmax  warp = head: tile maximum and sum by shuffles, once per tile instead of once per key
+//   P.V      thread = (output column, head subset): one V value feeds all its heads
+// Rows are padded to d + 1 floats so that "thread = key" reads are conflict-free.  Maxima are raw dot
+// products; the scale enters inside the exponent (combine is told so).
 template <typename T>
 __device__ __forceinline__ float to_f32(T v);
 template <>
@@ -554,11 +560,67 @@ __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 template <>
 __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
 
+constexpr int kGenThreads = 128, kGenMaxHeads = 16, kGenMaxAcc = 16, kGenLoadBatch = 8;
+__host__ __device__ inline int gen_tile_tokens(int d) { return d <= 128 ? 64 : 32; }
+__host__ __device__ inline int gen_head_batch(int d, int group) {
+  const int cap = d <= 128 ? kGenMaxHeads : kGenMaxHeads / 2;
+  return group < cap ? group : cap;
+}
+inline size_t gen_smem_bytes(int d, int group) {
+  const int tt = gen_tile_tokens(d), gb = gen_head_batch(d, group);
+  return sizeof(float) * ((size_t)2 * tt * (d + 1) + (size_t)gb * d + (size_t)gb * tt + 3 * kGenMaxHeads) +
+         sizeof(long long) * 64 + 8;
+}
+
+// Scores of one key against kNh query heads (sub, sub + nsub, ...): the K value is read once per
+// head_dim element; heads past `gb` are computed on a clamped index and not stored.
+template <int kNh>
+__device__ __forceinline__ void gen_scores(const float *Ks, const float *q_s, float *p_s, int key, int nt, int sub,
+                                           int nsub, int gb, int d, int dp, int tt) {
+  float sc[kNh];
+  const float *qr[kNh];
+#pragma unroll
+  for (int hh = 0; hh < kNh; ++hh) {
+    sc[hh] = 0.f;
+    qr[hh] = q_s + min(sub + hh * nsub, gb - 1) * d;
+  }
+  if (key < nt) {
+    const float *kr = Ks + key * dp;
+#pragma unroll 4
+    for (int c = 0; c < d; ++c) {
+      const float kv = kr[c];
+#pragma unroll
+      for (int hh = 0; hh < kNh; ++hh) sc[hh] = fmaf(qr[hh][c], kv, sc[hh]);
+    }
+  }
+#pragma unroll
+  for (int hh = 0; hh < kNh; ++hh)
+    if (sub + hh * nsub < gb) p_s[(sub + hh * nsub) * tt + key] = key < nt ? sc[hh] : -INFINITY;
+}
+
+// acc[0..kNh) = acc * corr + P . V for one output column and kNh heads (sub, sub + nsub, ...).
+template <int kNh>
+__device__ __forceinline__ void gen_pv(const float *Vs, const float *p_s, const float *corr_s, float *acc, int c,
+                                       int nt, int sub, int nsub, int gb, int dp, int tt) {
+  const float *pr[kNh];
+#pragma unroll
+  for (int hh = 0; hh < kNh; ++hh) {
+    const int r = min(sub + hh * nsub, gb - 1);
+    pr[hh] = p_s + r * tt;
+    acc[hh] *= corr_s[r];
+  }
+#pragma unroll 4
+  for (int t = 0; t < nt; ++t) {
+    const float vv = Vs[t * dp + c];
+#pragma unroll
+    for (int hh = 0; hh < kNh; ++hh) acc[hh] = fmaf(pr[hh][t], vv, acc[hh]);
+  }
+}
+
 template <typename T, bool kPaged>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(kGenThreads)
 gqa_split_generic_kernel(const T *k, const T *v, const DecodeParams p, int d) {
-  __shared__ float sO[kConsumerWarps][256];
-  __shared__ float sM[kConsumerWarps], sL[kConsumerWarps];
+  extern __shared__ float gsm[];
   const int chunk = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
   const int L = seq_len_of(p, b);
   const int first = first_visible(p, L);
@@ -567,84 +629,177 @@ gqa_split_generic_kernel(const T *k, const T *v, const DecodeParams p, int d) {
   const int end = min(L, start + p.chunk_tokens);
   if (end <= first) return;
   if (start < first) start = first;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tt = gen_tile_tokens(d), gb_max = gen_head_batch(d, p.group), dp = d + 1;
+  float *Ks = gsm, *Vs = Ks + tt * dp, *q_s = Vs + tt * dp, *p_s = q_s + gb_max * d;
+  float *m_s = p_s + gb_max * tt, *l_s = m_s + kGenMaxHeads, *corr_s = l_s + kGenMaxHeads;
+  long long *row_s = reinterpret_cast<long long *>(
+      (reinterpret_cast<uintptr_t>(corr_s + kGenMaxHeads) + 7) & ~uintptr_t(7));  // [tt] element offsets of the tile's rows
   const T *qp = reinterpret_cast<const T *>(p.q);
   const float dom = p.scale * kLog2e;
+  // thread roles
+  const int nsub_qk = kGenThreads / tt, key = tid % tt, sub_qk = tid / tt;
+  const int d_eff = d < kGenThreads ? d : kGenThreads;
+  const int nsub_pv = kGenThreads / d_eff, col = tid % d_eff, sub_pv = tid / d_eff;
+  const bool pv_active = sub_pv < nsub_pv;
+  const int passes = (d + kGenThreads - 1) / kGenThreads;  // 1, or 2 for head_dim > 128
 
-  for (int r = 0; r < p.group; ++r) {
-    const int h = hk * p.group + r;
-    float qv[8], acc[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int c = lane + 32 * j;
-      qv[j] = c < d ? to_f32(qp[((size_t)b * p.hq + h) * d + c]) : 0.f;
-      acc[j] = 0.f;
+  for (int h0 = 0; h0 < p.group; h0 += gb_max) {  // head batches: one unless group > 16 (8 for head_dim > 128)
+    const int gb = min(gb_max, p.group - h0);
+    __syncthreads();  // the previous batch is done with shared memory
+    for (int i = tid; i < gb * d; i += kGenThreads)
+      q_s[i] = to_f32(qp[((size_t)b * p.hq + hk * p.group + h0 + i / d) * d + i % d]);
+    if (tid < kGenMaxHeads) {
+      m_s[tid] = -INFINITY;
+      l_s[tid] = 0.f;
+      corr_s[tid] = 1.f;
     }
-    float m = -INFINITY, l = 0.f;
-    for (int tok = start + warp; tok < end; tok += kConsumerWarps) {
-      size_t row;
-      if (kPaged) {
-        int page = p.block_table[(size_t)b * p.max_blocks + tok / p.page_tokens];
-        if (page < 0 || page >= p.num_pages) {
-          atomicOr(&g_error_word, AXB200_ERR_BAD_PAGE);
-          continue;
+    float acc[kGenMaxAcc];
+#pragma unroll
+    for (int a = 0; a < kGenMaxAcc; ++a) acc[a] = 0.f;
+    const int nh_pv = pv_active ? (gb - sub_pv + nsub_pv - 1) / nsub_pv : 0;  // heads sub_pv, sub_pv + nsub_pv, ...
+    const int nh_qk = (gb - sub_qk + nsub_qk - 1) / nsub_qk;
+
+    for (int t0 = start; t0 < end; t0 += tt) {
+      const int nt = min(tt, end - t0);
+      // ---- stage the tile ----
+      // Row offsets first (one page lookup per key), then the nt * d elements of K and of V spread
+      // over the threads, consecutive threads on consecutive elements; eight loads of each are issued
+      // before the first shared-memory store so that a CTA keeps ~8 KB in flight.
+      if (tid < tt) {
+        long long off = -1;
+        if (tid < nt) {
+          const int tok = t0 + tid;
+          if (kPaged) {
+            const int page = p.block_table[(size_t)b * p.max_blocks + tok / p.page_tokens];
+            if (page >= 0 && page < p.num_pages)
+              off = (long long)((((size_t)page * p.hkv + hk) * p.page_tokens + tok % p.page_tokens) * d);
+            else
+              atomicOr(&g_error_word, AXB200_ERR_BAD_PAGE);
+          } else {
+            off = (long long)(((size_t)tok * p.hkv + hk) * d);
+          }
         }
-        row = (((size_t)page * p.hkv + hk) * p.page_tokens + tok % p.page_tokens) * d;
+        row_s[tid] = off;
+      }
+      __syncthreads();
+      const int n_elem = nt * d;
+      int er = tid / d, ec = tid % d;  // row and column of this thread's next element; they advance by 128
+      for (int e0 = 0; e0 < n_elem; e0 += kGenThreads * kGenLoadBatch) {
+        float kr[kGenLoadBatch], vr[kGenLoadBatch];
+        int at[kGenLoadBatch];
+#pragma unroll
+        for (int u = 0; u < kGenLoadBatch; ++u) {
+          kr[u] = vr[u] = 0.f;
+          at[u] = -1;
+          if (e0 + u * kGenThreads + tid < n_elem) {
+            at[u] = er * dp + ec;
+            const long long off = row_s[er];
+            if (off >= 0) {
+              kr[u] = to_f32(k[off + ec]);
+              vr[u] = to_f32(v[off + ec]);
+            }
+          }
+          ec += kGenThreads;
+          while (ec >= d) {
+            ec -= d;
+            ++er;
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < kGenLoadBatch; ++u)
+          if (at[u] >= 0) {
+            Ks[at[u]] = kr[u];
+            Vs[at[u]] = vr[u];
+          }
+      }
+      __syncthreads();
+      // ---- scores ----
+      if (nh_qk > 4) gen_scores<8>(Ks, q_s, p_s, key, nt, sub_qk, nsub_qk, gb, d, dp, tt);
+      else if (nh_qk > 2) gen_scores<4>(Ks, q_s, p_s, key, nt, sub_qk, nsub_qk, gb, d, dp, tt);
+      else if (nh_qk == 2) gen_scores<2>(Ks, q_s, p_s, key, nt, sub_qk, nsub_qk, gb, d, dp, tt);
+      else if (nh_qk == 1) gen_scores<1>(Ks, q_s, p_s, key, nt, sub_qk, nsub_qk, gb, d, dp, tt);
+      __syncthreads();
+      // ---- online softmax of the tile, one warp per head ----
+      for (int r = warp; r < gb; r += kGenThreads / 32) {
+        float s0 = p_s[r * tt + lane], s1 = tt > 32 ? p_s[r * tt + 32 + lane] : -INFINITY;
+        float mx = fmaxf(s0, s1);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+        const float m_old = m_s[r], m_new = fmaxf(m_old, mx);
+        const float corr = m_old == -INFINITY ? 0.f : exp2f((m_old - m_new) * dom);
+        const float p0 = s0 == -INFINITY ? 0.f : exp2f((s0 - m_new) * dom);
+        const float p1 = s1 == -INFINITY ? 0.f : exp2f((s1 - m_new) * dom);
+        p_s[r * tt + lane] = p0;
+        if (tt > 32) p_s[r * tt + 32 + lane] = p1;
+        float ps = p0 + p1;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, off);
+        __syncwarp();
+        if (lane == 0) {
+          m_s[r] = m_new;
+          l_s[r] = l_s[r] * corr + ps;
+          corr_s[r] = corr;
+        }
+      }
+      __syncthreads();
+      // ---- O = O * corr + P . V ----
+      // accumulators: head_dim <= 128: acc[hh], up to 16 heads; above: acc[pass * 8 + hh], up to 8 heads.
+      // A head past the batch is computed on a clamped index; its accumulator is never written out.
+      if (pv_active && passes == 1) {
+        if (col < d) {
+          if (nh_pv > 8) gen_pv<16>(Vs, p_s, corr_s, acc, col, nt, sub_pv, nsub_pv, gb, dp, tt);
+          else if (nh_pv > 4) gen_pv<8>(Vs, p_s, corr_s, acc, col, nt, sub_pv, nsub_pv, gb, dp, tt);
+          else if (nh_pv > 2) gen_pv<4>(Vs, p_s, corr_s, acc, col, nt, sub_pv, nsub_pv, gb, dp, tt);
+          else if (nh_pv == 2) gen_pv<2>(Vs, p_s, corr_s, acc, col, nt, sub_pv, nsub_pv, gb, dp, tt);
+          else if (nh_pv == 1) gen_pv<1>(Vs, p_s, corr_s, acc, col, nt, sub_pv, nsub_pv, gb, dp, tt);
+        }
+      } else if (pv_active) {
+#pragma unroll
+        for (int ps = 0; ps < 2; ++ps) {
+          const int c = col + ps * kGenThreads;
+          if (c < d) {
+            float *a = acc + ps * (kGenMaxAcc / 2);
+            if (nh_pv > 4) gen_pv<8>(Vs, p_s, corr_s, a, c, nt, 0, 1, gb, dp, tt);
+            else if (nh_pv > 2) gen_pv<4>(Vs, p_s, corr_s, a, c, nt, 0, 1, gb, dp, tt);
+            else if (nh_pv == 2) gen_pv<2>(Vs, p_s, corr_s, a, c, nt, 0, 1, gb, dp, tt);
+            else if (nh_pv == 1) gen_pv<1>(Vs, p_s, corr_s, a, c, nt, 0, 1, gb, dp, tt);
+          }
+        }
+      }
+      __syncthreads();  // the tile buffers and p_s are free again
+    }
+    // ---- this chunk's result for the batch's heads ----
+    if (pv_active) {
+      auto emit = [&](int r, int c, float a) {
+        const int h = hk * p.group + h0 + r;
+        if (p.write_final) {
+          reinterpret_cast<T *>(p.out)[((size_t)b * p.hq + h) * d + c] = static_cast<T>(a / l_s[r]);
+        } else {
+          const size_t slot = ((size_t)b * p.hq + h) * p.max_chunks + chunk;
+          p.part_o[slot * d + c] = a;
+        }
+      };
+      if (passes == 1) {
+        if (col < d) {
+#pragma unroll
+          for (int hh = 0; hh < kGenMaxAcc; ++hh)
+            if (hh < nh_pv) emit(sub_pv + hh * nsub_pv, col, acc[hh]);
+        }
       } else {
-        row = ((size_t)tok * p.hkv + hk) * d;
-      }
-      float s = 0.f;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int c = lane + 32 * j;
-        if (c < d) s = fmaf(qv[j], to_f32(k[row + c]), s);
-      }
+        for (int ps = 0; ps < 2; ++ps) {
+          const int c = col + ps * kGenThreads;
 #pragma unroll
-      for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-      const float mn = fmaxf(m, s);
-      const float corr = exp2f((m - mn) * dom);
-      const float pw = exp2f((s - mn) * dom);
-      l = l * corr + pw;
-      m = mn;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int c = lane + 32 * j;
-        if (c < d) acc[j] = fmaf(pw, to_f32(v[row + c]), acc[j] * corr);
+          for (int hh = 0; hh < kGenMaxAcc / 2; ++hh)
+            if (c < d && hh < nh_pv) emit(hh, c, acc[ps * (kGenMaxAcc / 2) + hh]);
+        }
       }
     }
-    __syncthreads();  // previous head's merge has finished reading
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int c = lane + 32 * j;
-      if (c < d) sO[warp][c] = acc[j];
-    }
-    if (lane == 0) {
-      sM[warp] = m;
-      sL[warp] = l;
-    }
-    __syncthreads();
-    float M = -INFINITY;
-    for (int w = 0; w < kConsumerWarps; ++w) M = fmaxf(M, sM[w]);
-    float Lsum = 0.f;
-    float wgt[kConsumerWarps];
-    for (int w = 0; w < kConsumerWarps; ++w) {
-      wgt[w] = sM[w] == -INFINITY ? 0.f : exp2f((sM[w] - M) * dom);
-      Lsum += sL[w] * wgt[w];
-    }
-    for (int c = threadIdx.x; c < d; c += blockDim.x) {
-      float a = 0.f;
-      for (int w = 0; w < kConsumerWarps; ++w) a += sO[w][c] * wgt[w];
-      if (p.write_final) {
-        reinterpret_cast<T *>(p.out)[((size_t)b * p.hq + h) * d + c] = static_cast<T>(a / Lsum);
-      } else {
-        const size_t slot = ((size_t)b * p.hq + h) * p.max_chunks + chunk;
-        p.part_o[slot * d + c] = a;
-      }
-    }
-    if (!p.write_final && threadIdx.x == 0) {
-      const size_t slot = ((size_t)b * p.hq + h) * p.max_chunks + chunk;
-      p.part_ml[slot * 2 + 0] = M;
-      p.part_ml[slot * 2 + 1] = Lsum;
+    if (!p.write_final && tid < gb) {
+      const size_t slot = ((size_t)b * p.hq + hk * p.group + h0 + tid) * p.max_chunks + chunk;
+      p.part_ml[slot * 2 + 0] = m_s[tid];
+      p.part_ml[slot * 2 + 1] = l_s[tid];
     }
   }
 }
@@ -1100,15 +1255,32 @@ int decode_impl(bool paged, const void *q, void *out, const void *k, const void 
     else
       status = paged ? launch_f32<true>(mk, mv, p, grid, st) : launch_f32<false>(mk, mv, p, grid, st);
   } else {
+    const int gsmem = (int)gen_smem_bytes(d, p.group);
+    bool ok_attr = true;
     if (f16) {
       auto kk = reinterpret_cast<const __half *>(k), vv = reinterpret_cast<const __half *>(v);
-      if (paged) gqa_split_generic_kernel<__half, true><<<grid, 128, 0, st>>>(kk, vv, p, d);
-      else gqa_split_generic_kernel<__half, false><<<grid, 128, 0, st>>>(kk, vv, p, d);
+      if (paged) {
+        auto kern = gqa_split_generic_kernel<__half, true>;
+        ok_attr = set_smem(reinterpret_cast<const void *>(kern), 100 * 1024);
+        if (ok_attr) kern<<<grid, kGenThreads, gsmem, st>>>(kk, vv, p, d);
+      } else {
+        auto kern = gqa_split_generic_kernel<__half, false>;
+        ok_attr = set_smem(reinterpret_cast<const void *>(kern), 100 * 1024);
+        if (ok_attr) kern<<<grid, kGenThreads, gsmem, st>>>(kk, vv, p, d);
+      }
     } else {
       auto kk = reinterpret_cast<const float *>(k), vv = reinterpret_cast<const float *>(v);
-      if (paged) gqa_split_generic_kernel<float, true><<<grid, 128, 0, st>>>(kk, vv, p, d);
-      else gqa_split_generic_kernel<float, false><<<grid, 128, 0, st>>>(kk, vv, p, d);
+      if (paged) {
+        auto kern = gqa_split_generic_kernel<float, true>;
+        ok_attr = set_smem(reinterpret_cast<const void *>(kern), 100 * 1024);
+        if (ok_attr) kern<<<grid, kGenThreads, gsmem, st>>>(kk, vv, p, d);
+      } else {
+        auto kern = gqa_split_generic_kernel<float, false>;
+        ok_attr = set_smem(reinterpret_cast<const void *>(kern), 100 * 1024);
+        if (ok_attr) kern<<<grid, kGenThreads, gsmem, st>>>(kk, vv, p, d);
+      }
     }
+    if (!ok_attr) return AXB200_DEVICE_ERROR;
     status = launch_status();
   }
   if (prof >= 0) cudaEventRecord(g_profile.stop[prof], st);

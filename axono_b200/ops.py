@@ -379,6 +379,22 @@ def rms_norm(x, weight, eps: float = 1e-5):
     return out
 
 
+def cast(x, dtype):
+    """Tensor.cast_to on the device (src/core/cuda/tensor/kernel.cu:175-193): float16 <-> float32."""
+    op = "cast"
+    src = _dt(x, op)
+    if dtype == x.dtype:
+        return x
+    if {x.dtype, dtype} != {torch.float16, torch.float32}:
+        raise RuntimeError(f"{op}: only float16 <-> float32")
+    if not x.is_contiguous():
+        raise RuntimeError(f"{op}: tensor must be contiguous")
+    out = torch.empty(x.shape, dtype=dtype, device=x.device)
+    dst = _DTYPES[dtype]
+    _call(_capi.lib().axb200_cast(x.data_ptr(), src, out.data_ptr(), dst, x.numel(), _stream(x)), op)
+    return out
+
+
 def concat(a, b, axis: int):
     op = "concat"
     if a.dim() < 1 or a.dim() != b.dim() or a.dtype != b.dtype:

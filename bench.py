@@ -721,14 +721,114 @@ def run_prefill(args):
     }), flush=True)
 
 
+def run_small_ops(args):
+    """`ops`: the standalone operators of the path at the multimodal configuration's shapes (1536-token
+    prompt = 1024 image + 512 text tokens, batch 16 decode, 16 q / 8 kv heads, head_dim 128, sections
+    24/20/20) plus the byte-copy and fallback kernels, each timed alone with CUDA events.  Most are
+    launch-latency kernels (a few hundred KB): the line reports microseconds per call, and GB/s where
+    the operator moves enough bytes for that to mean something."""
+    import torch
+
+    from axono_b200 import ops
+    from axono_b200.kv_cache import PagedKVCache
+
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    gen = torch.Generator(device="cuda").manual_seed(21)
+    rn = lambda *sh, dt=torch.float16: torch.randn(sh, generator=gen, device="cuda").to(dt)  # noqa: E731
+    n_prompt, B = 1536, 16
+    sec = (24, 20, 20)
+    inv = (1.0 / (1e6 ** (torch.arange(0, D, 2, dtype=torch.float32) / D))).cuda()
+    pos1 = torch.arange(n_prompt, dtype=torch.int64, device="cuda")
+    pos3 = torch.stack([pos1, pos1 // 32, pos1 % 32])
+    xq, xk, xv = rn(n_prompt, HQ, D), rn(n_prompt, HKV, D), rn(n_prompt, HKV, D)
+    cos, sin = ops.mrope_cos_sin(pos3, inv, sec[1], sec[2])
+    cache = PagedKVCache(1, 2, HKV, D, 2048, dtype=torch.float16, device="cuda")
+    big_a, big_b = rn(16384, HKV, D), rn(1, HKV, D)            # the reference's cache.update at 16 K tokens
+    half_src, wn = rn(B, 2048), torch.ones(D, dtype=torch.float16, device="cuda")
+    q80, k80, v80 = rn(1, 16, 80), rn(8192, 8, 80), rn(8192, 8, 80)  # a head size the TMA kernels do not take
+    qf, kf, vf = rn(1, HQ, D, dt=torch.float32), rn(8192, HKV, D, dt=torch.float32), rn(8192, HKV, D, dt=torch.float32)
+    elem = 2
+    cases = [
+        ("rope q [1536,16,128]", lambda: ops.rope(xq, pos1, 1e6), 2 * xq.numel() * elem),
+        ("rope_thd q [1536,16,128]", lambda: ops.rope_thd(xq, pos3, inv, sec), 2 * xq.numel() * elem),
+        ("mrope_cos_sin [1536]", lambda: ops.mrope_cos_sin(pos3, inv, sec[1], sec[2]), 2 * n_prompt * D * 4),
+        ("rope_with_cos_sin k [1536,8,128]", lambda: ops.rope_with_cos_sin(xk, cos, sin), 2 * xk.numel() * elem),
+        ("kv_prefill_write 1536 tokens (+ rope of q, k)", lambda: cache.prefill(0, 0, xq, xk, xv, pos=pos3, inv_freq=inv,
+                                                                                 mrope_section=sec),
+         2 * (xq.numel() + 2 * xk.numel()) * elem),
+        ("concat axis 0: [16384,8,128] ++ [1,8,128]", lambda: ops.concat(big_a, big_b, 0), 2 * big_a.numel() * elem),
+        ("rms_norm q heads [16,16,128]", lambda: ops.rms_norm(xq[:B], wn, 1e-6), 2 * B * HQ * D * elem),
+        ("gqa_decode generic kernel, head_dim 80, 8192 keys", lambda: ops.gqa_decode_attention(q80, k80, v80),
+         2 * k80.numel() * elem),
+        ("gqa_decode fp32, one sequence of 8192 keys", lambda: ops.gqa_decode_attention(qf, kf, vf), 2 * kf.numel() * 4),
+    ]
+    cases.append(("cast f16 -> f32 [16,2048]", lambda: ops.cast(half_src, torch.float32), half_src.numel() * 6))
+    from axono_b200.cuda_graph import CUDAGraph
+
+    rows, launches, per_graph = [], 0, 20
+    if args.ops_once:  # one launch of every operator inside the profiler range, for a per-kernel ncu capture
+        for _, fn, _ in cases:
+            fn()
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        for _, fn, _ in cases:
+            fn()
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        print(json.dumps({"workload": "ops", "ops_once": [c[0] for c in cases]}), flush=True)
+        return
+    torch.cuda.profiler.start()
+    for name, fn, nbytes in cases:
+        for _ in range(max(3, args.warmup)):
+            fn()
+        before = ops.launch_count()
+        fn()
+        per_call = ops.launch_count() - before
+
+        def body(fn=fn):  # twenty calls per graph: replay shows the kernels' cadence without the host's per-call cost
+            out = None
+            for _ in range(per_graph):
+                out = fn()
+            return out
+
+        g = CUDAGraph().capture(body)
+        g.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(args.steps):
+            g.replay_async()
+        e1.record()
+        torch.cuda.synchronize()
+        launches += per_call * per_graph * args.steps
+        us = e0.elapsed_time(e1) / (args.steps * per_graph) * 1e3
+        rows.append({"op": name, "us_per_call": round(us, 2), "kernels_per_call": per_call,
+                     "algorithmic_bytes": int(nbytes), "gbs": round(nbytes / (us * 1e-6) / 1e9, 1)})
+        g.reset()
+    torch.cuda.profiler.stop()
+    err = ops.last_error()
+    if err:
+        raise SystemExit(f"device error word {err:#x}")
+    print(json.dumps({
+        "metric": "operator_latency_us", "value": sum(r["us_per_call"] for r in rows), "unit": "us (sum over the operators)",
+        "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup), "higher_is_better": False, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "ops", "timing": "CUDA-graph replays of 20 calls each between two CUDA events: the "
+                                                 "kernels' cadence inside a graph; small inputs stay in L2"},
+        "operators": rows, "gpu_launches": launches,
+    }), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-cuda"])
-    ap.add_argument("--workload", default="c3_ragged", choices=sorted(WORKLOADS) + ["c2_block", "c5_tower", "prefill"])
+    ap.add_argument("--workload", default="c3_ragged", choices=sorted(WORKLOADS) + ["c2_block", "c5_tower", "prefill", "ops"])
     ap.add_argument("--prefill-len", type=int, default=8192)
+    ap.add_argument("--ops-once", action="store_true",
+                    help="ops: launch every operator once inside the profiler range and exit (for ncu)")
     ap.add_argument("--runtime", default="torch", choices=["torch", "native"],
                     help="c5_tower: torch = torch-tensor mirror (any N); native = libaxono runtime, no PyTorch (N = 1)")
     ap.add_argument("--tower-batch", type=int, default=32, help="c5_tower: batch (default: the configuration's 32)")
@@ -746,12 +846,15 @@ def main():
         if int(os.environ.get("RANK", "0")) == 0:
             run_reference_cuda(args)
     elif args.impl == "reference":
-        if args.workload in ("c2_block", "c5_tower", "prefill"):
+        if args.workload in ("c2_block", "c5_tower", "prefill", "ops"):
             args.workload = "c2_b8_l8k" if args.workload == "c2_block" else "c3_ragged"
         run_reference_arm(args)
     elif args.workload == "prefill":
         if int(os.environ.get("RANK", "0")) == 0:
             run_prefill(args)
+    elif args.workload == "ops":
+        if int(os.environ.get("RANK", "0")) == 0:
+            run_small_ops(args)
     elif args.workload == "c5_tower" and args.runtime == "native":
         if int(os.environ.get("RANK", "0")) == 0:
             run_tower_native(args)

@@ -71,7 +71,9 @@ def test_gqa_fp16_golden_inputs(ops, orc, name):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
 @pytest.mark.parametrize("hq,hkv,d", [(16, 8, 128), (8, 8, 128), (32, 8, 128), (64, 8, 128), (16, 1, 128),
-                                      (24, 2, 128), (6, 2, 128), (4, 2, 8), (8, 4, 64), (4, 4, 256)])
+                                      (24, 2, 128), (6, 2, 128), (4, 2, 8), (8, 4, 64), (4, 4, 256),
+                                      # the generic kernel: other head sizes, groups past one head batch
+                                      (32, 2, 80), (16, 8, 96), (40, 2, 64), (18, 1, 256), (3, 3, 48)])
 @pytest.mark.parametrize("skv", [1, 63, 64, 65, 255, 257, 2049, 8193])
 def test_gqa_shapes(ops, orc, dtype, hq, hkv, d, skv):
     rng = np.random.default_rng(hq * 1000 + hkv * 100 + d + skv)
@@ -549,3 +551,12 @@ def test_sdpa_prefill_then_decode_consistency(ops, orc):
     full = ops.scaled_dot_product_attention(q, k, v, True)
     last = ops.gqa_decode_attention(q[s - 1 : s].contiguous(), k, v)
     assert_close(host(full[s - 1 : s]), host(last), 1e-3)
+
+
+def test_cast_half_float_round_trip(ops):
+    """Tensor.cast_to on the device: float32 -> float16 rounds to nearest even, float16 -> float32 is exact."""
+    a = torch.randn(1000, 37, device="cuda") * 100
+    h = ops.cast(a, torch.float16)
+    assert h.dtype == torch.float16 and torch.equal(h, a.half())
+    assert torch.equal(ops.cast(h, torch.float32), h.float())
+    assert ops.cast(a, torch.float32) is a
