@@ -35,6 +35,47 @@ __device__ __forceinline__ void st<float>(float *p, float v) { *p = v; }
 template <>
 __device__ __forceinline__ void st<__half>(__half *p, float v) { *p = __float2half_rn(v); }
 
+// 16 bytes of T as floats and back (pointers 16-byte aligned): 4 floats or 8 halves.
+template <typename T>
+struct Vec16 {
+  static constexpr int kN = 16 / (int)sizeof(T);
+};
+__device__ __forceinline__ void ld16(const float *p, float (&f)[4]) {
+  const float4 v = *reinterpret_cast<const float4 *>(p);
+  f[0] = v.x, f[1] = v.y, f[2] = v.z, f[3] = v.w;
+}
+__device__ __forceinline__ void ld16(const __half *p, float (&f)[8]) {
+  const uint4 v = *reinterpret_cast<const uint4 *>(p);
+  const __half2 *h = reinterpret_cast<const __half2 *>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __half22float2(h[i]);
+    f[2 * i] = t.x, f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ void st16(float *p, const float (&f)[4]) {
+  *reinterpret_cast<float4 *>(p) = make_float4(f[0], f[1], f[2], f[3]);
+}
+__device__ __forceinline__ void st16(__half *p, const float (&f)[8]) {
+  uint4 v;
+  __half2 *h = reinterpret_cast<__half2 *>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __halves2half2(__float2half_rn(f[2 * i]), __float2half_rn(f[2 * i + 1]));
+  *reinterpret_cast<uint4 *>(p) = v;
+}
+// Rotates kN pairs (a[j], b[j]) = (x[i + j], x[i + j + half]) with the tables at i + j; the same
+// expressions, element by element, as the scalar path.
+template <int kN>
+__device__ __forceinline__ void rotate_vec(float (&a)[kN], float (&b)[kN], const float *c0, const float *s0,
+                                           const float *c1, const float *s1) {
+#pragma unroll
+  for (int j = 0; j < kN; ++j) {
+    const float x = a[j], y = b[j];
+    a[j] = x * c0[j] - y * s0[j];
+    b[j] = y * c1[j] + x * s1[j];
+  }
+}
+
 // Position of rotary pair i: the stride-3 M-RoPE rule (src/ops/cpu/sequence.cpp:222-227).
 __device__ __forceinline__ float pair_position(int i, float pt, float ph, float pw, int h_lim,
                                                int w_lim) {
@@ -84,6 +125,66 @@ rope_kernel(const T *x, T *out, const int64_t *pos, const float *inv_freq_dev,
     }
     st(dst + i, a * c0 - b * s0);
     st(dst + i + half, b * c1 + a * s1);
+  }
+}
+
+// One CTA per row (grid-stride): the row's cos / sin are computed once per rotary pair into shared
+// memory and every head reuses them - with one thread per (row, head, pair) the range-reduced sincosf
+// was evaluated `heads` times over and dominated the kernel.  Same arithmetic per element as
+// rope_kernel; head_dim <= 256.
+template <typename T, int kMode>
+__global__ void __launch_bounds__(128)
+rope_rows_kernel(const T *x, T *out, const int64_t *pos, const float *inv_freq_dev, const InvFreqTable table,
+                 const float *cos_t, const float *sin_t, int64_t rows, int heads, int dim, int h_lim, int w_lim,
+                 int vec) {  // vec: x and out 16-byte aligned and dim / 2 a multiple of 16 bytes' worth of T
+  __shared__ float s_c0[kMaxHalf], s_s0[kMaxHalf], s_c1[kMaxHalf], s_s1[kMaxHalf];
+  const int half = dim / 2;
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    __syncthreads();  // the previous row's pairs are done with the tables
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+      if (kMode == kModeCosSin) {
+        s_c0[i] = cos_t[r * dim + i];
+        s_s0[i] = sin_t[r * dim + i];
+        s_c1[i] = cos_t[r * dim + i + half];
+        s_s1[i] = sin_t[r * dim + i + half];
+      } else {
+        float p, f;
+        if (kMode == kModeMrope) {
+          p = pair_position(i, (float)pos[r], (float)pos[rows + r], (float)pos[2 * rows + r], h_lim, w_lim);
+          f = inv_freq_dev[i];
+        } else {
+          p = (float)pos[r];
+          f = table.f[i];
+        }
+        float sn, cs;
+        sincosf(p * f, &sn, &cs);
+        s_c0[i] = s_c1[i] = cs;
+        s_s0[i] = s_s1[i] = sn;
+      }
+    }
+    __syncthreads();
+    const T *src = x + r * heads * dim;
+    T *dst = out + r * heads * dim;
+    if (vec) {
+      constexpr int kN = Vec16<T>::kN;
+      const int per_head = half / kN;
+      for (int idx = threadIdx.x; idx < heads * per_head; idx += blockDim.x) {
+        const int h = idx / per_head, i = (idx - h * per_head) * kN;
+        float a[kN], b[kN];
+        ld16(src + h * dim + i, a);
+        ld16(src + h * dim + i + half, b);
+        rotate_vec<kN>(a, b, s_c0 + i, s_s0 + i, s_c1 + i, s_s1 + i);
+        st16(dst + h * dim + i, a);
+        st16(dst + h * dim + i + half, b);
+      }
+    } else {
+      for (int idx = threadIdx.x; idx < heads * half; idx += blockDim.x) {
+        const int h = idx / half, i = idx - h * half;
+        const float a = ld(src + h * dim + i), b = ld(src + h * dim + i + half);
+        st(dst + h * dim + i, a * s_c0[i] - b * s_s0[i]);
+        st(dst + h * dim + i + half, b * s_c1[i] + a * s_s1[i]);
+      }
+    }
   }
 }
 
@@ -231,6 +332,7 @@ struct PrefillWriteParams {
   const float *inv_freq_dev;
   int rotate, mrope, h_lim, w_lim;
   int n, hq, hkv, d, page_tokens, max_blocks, num_pages, start;
+  int vec;  // every pointer 16-byte aligned and d / 2 a multiple of 16 bytes' worth of T
 };
 
 template <typename T>
@@ -269,6 +371,34 @@ kv_prefill_write_kernel(const PrefillWriteParams p, const InvFreqTable table) {
   T *q = p.q ? reinterpret_cast<T *>(p.q) + (size_t)i_tok * p.hq * p.d : nullptr;
   const T *kn = reinterpret_cast<const T *>(p.k) + (size_t)i_tok * p.hkv * p.d;
   const T *vn = reinterpret_cast<const T *>(p.v) + (size_t)i_tok * p.hkv * p.d;
+  if (p.vec) {  // 16 bytes per access: the same arithmetic per element as below
+    constexpr int kN = Vec16<T>::kN;
+    const int per_head = half / kN;
+    const int q_items = (q && p.rotate) ? p.hq * per_head : 0, k_items = page_ok ? p.hkv * per_head : 0;
+    for (int idx = threadIdx.x; idx < q_items + k_items; idx += blockDim.x) {
+      const bool is_q = idx < q_items;
+      const int j = is_q ? idx : idx - q_items;
+      const int h = j / per_head, i = (j - h * per_head) * kN;
+      const T *src = is_q ? q + (size_t)h * p.d : kn + (size_t)h * p.d;
+      T *dst = is_q ? q + (size_t)h * p.d
+                    : reinterpret_cast<T *>(p.k_pages) + (((size_t)page * p.hkv + h) * p.page_tokens + tok) * p.d;
+      float a[kN], b[kN];
+      ld16(src + i, a);
+      ld16(src + i + half, b);
+      if (p.rotate) rotate_vec<kN>(a, b, s_cos + i, s_sin + i, s_cos + i, s_sin + i);
+      st16(dst + i, a);
+      st16(dst + i + half, b);
+    }
+    if (page_ok) {
+      const int per_row = p.d / kN;
+      for (int idx = threadIdx.x; idx < p.hkv * per_row; idx += blockDim.x) {
+        const int h = idx / per_row, c = (idx - h * per_row) * kN;
+        *reinterpret_cast<uint4 *>(reinterpret_cast<T *>(p.v_pages) + (((size_t)page * p.hkv + h) * p.page_tokens + tok) * p.d + c) =
+            *reinterpret_cast<const uint4 *>(vn + (size_t)h * p.d + c);
+      }
+    }
+    return;
+  }
   const int q_pairs = q ? p.hq * half : 0, k_pairs = p.hkv * half;
   for (int idx = threadIdx.x; idx < q_pairs + k_pairs; idx += blockDim.x) {
     const bool is_q = idx < q_pairs;
@@ -437,6 +567,21 @@ int rope_dispatch(const void *x, void *out, const int64_t *pos, const float *inv
                   int heads, int dim, int h_lim, int w_lim, int dtype, cudaStream_t st) {
   const int64_t total = rows * heads * (dim / 2);
   if (total == 0) return AXB200_OK;
+  if (dim / 2 <= kMaxHalf) {  // cos / sin once per (row, pair)
+    const int grid = (int)(rows < 148 * 16 ? rows : 148 * 16);
+    const int es = dtype == AXB200_FLOAT32 ? 4 : 2;
+    const int vec = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0 &&
+                    ((dim / 2) * es) % 16 == 0;
+    if (dtype == AXB200_FLOAT32)
+      rope_rows_kernel<float, kMode><<<grid, 128, 0, st>>>(
+          reinterpret_cast<const float *>(x), reinterpret_cast<float *>(out), pos, inv_freq, table,
+          cos_t, sin_t, rows, heads, dim, h_lim, w_lim, vec);
+    else
+      rope_rows_kernel<__half, kMode><<<grid, 128, 0, st>>>(
+          reinterpret_cast<const __half *>(x), reinterpret_cast<__half *>(out), pos, inv_freq, table,
+          cos_t, sin_t, rows, heads, dim, h_lim, w_lim, vec);
+    return launch_status();
+  }
   const int grid = grid_for(total);
   if (dtype == AXB200_FLOAT32)
     rope_kernel<float, kMode><<<grid, 256, 0, st>>>(
@@ -589,6 +734,10 @@ int axb200_kv_prefill_write(void *q, const void *k, const void *v, void *k_pages
   p.max_blocks = max_blocks;
   p.num_pages = num_pages;
   p.start = (int)start;
+  const int es = dtype == AXB200_FLOAT32 ? 4 : 2;
+  p.vec = ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+            reinterpret_cast<uintptr_t>(k_pages) | reinterpret_cast<uintptr_t>(v_pages)) & 15u) == 0 &&
+          ((d / 2) * es) % 16 == 0;
   axb::InvFreqTable table{};
   if (rotate && !inv_freq) axb::fill_table(&table, theta, d);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
