@@ -562,13 +562,17 @@ __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(
 
 constexpr int kGenThreads = 128, kGenMaxHeads = 16, kGenMaxAcc = 16, kGenLoadBatch = 8;
 __host__ __device__ inline int gen_tile_tokens(int d) { return d <= 128 ? 64 : 32; }
+// Row stride of the staged tiles in floats: d + 4 when head_dim is a multiple of 8 - rows stay 16-byte
+// aligned and "thread = key" float4 reads are conflict-free ((d + 4) / 4 is odd) - else d + 1.
+__host__ __device__ inline int gen_row_stride(int d) { return d % 8 == 0 ? d + 4 : d + 1; }
 __host__ __device__ inline int gen_head_batch(int d, int group) {
   const int cap = d <= 128 ? kGenMaxHeads : kGenMaxHeads / 2;
   return group < cap ? group : cap;
 }
 inline size_t gen_smem_bytes(int d, int group) {
   const int tt = gen_tile_tokens(d), gb = gen_head_batch(d, group);
-  return sizeof(float) * ((size_t)2 * tt * (d + 1) + (size_t)gb * d + (size_t)gb * tt + 3 * kGenMaxHeads) +
+  return sizeof(float) * ((size_t)2 * tt * gen_row_stride(d) + (((size_t)gb * d + 3) & ~size_t(3)) + (size_t)gb * tt +
+                          3 * kGenMaxHeads) +
          sizeof(long long) * 64 + 8;
 }
 
@@ -586,11 +590,24 @@ __device__ __forceinline__ void gen_scores(const float *Ks, const float *q_s, fl
   }
   if (key < nt) {
     const float *kr = Ks + key * dp;
-#pragma unroll 4
-    for (int c = 0; c < d; ++c) {
-      const float kv = kr[c];
+    if (d % 8 == 0) {  // 16-byte reads, the same order of additions
+      const float4 *kr4 = reinterpret_cast<const float4 *>(kr);
+#pragma unroll 2
+      for (int c4 = 0; c4 < d / 4; ++c4) {
+        const float4 kv = kr4[c4];
 #pragma unroll
-      for (int hh = 0; hh < kNh; ++hh) sc[hh] = fmaf(qr[hh][c], kv, sc[hh]);
+        for (int hh = 0; hh < kNh; ++hh) {
+          const float4 qv = reinterpret_cast<const float4 *>(qr[hh])[c4];
+          sc[hh] = fmaf(qv.w, kv.w, fmaf(qv.z, kv.z, fmaf(qv.y, kv.y, fmaf(qv.x, kv.x, sc[hh]))));
+        }
+      }
+    } else {
+#pragma unroll 4
+      for (int c = 0; c < d; ++c) {
+        const float kv = kr[c];
+#pragma unroll
+        for (int hh = 0; hh < kNh; ++hh) sc[hh] = fmaf(qr[hh][c], kv, sc[hh]);
+      }
     }
   }
 #pragma unroll
@@ -609,8 +626,16 @@ __device__ __forceinline__ void gen_pv(const float *Vs, const float *p_s, const 
     pr[hh] = p_s + r * tt;
     acc[hh] *= corr_s[r];
   }
-#pragma unroll 4
-  for (int t = 0; t < nt; ++t) {
+  int t = 0;
+  for (; t + 4 <= nt; t += 4) {  // four keys per step: the weights come as one 16-byte read per head
+    const float v0 = Vs[t * dp + c], v1 = Vs[(t + 1) * dp + c], v2 = Vs[(t + 2) * dp + c], v3 = Vs[(t + 3) * dp + c];
+#pragma unroll
+    for (int hh = 0; hh < kNh; ++hh) {
+      const float4 pw = *reinterpret_cast<const float4 *>(pr[hh] + t);
+      acc[hh] = fmaf(pw.w, v3, fmaf(pw.z, v2, fmaf(pw.y, v1, fmaf(pw.x, v0, acc[hh]))));
+    }
+  }
+  for (; t < nt; ++t) {
     const float vv = Vs[t * dp + c];
 #pragma unroll
     for (int hh = 0; hh < kNh; ++hh) acc[hh] = fmaf(pr[hh][t], vv, acc[hh]);
@@ -618,7 +643,7 @@ __device__ __forceinline__ void gen_pv(const float *Vs, const float *p_s, const 
 }
 
 template <typename T, bool kPaged>
-__global__ void __launch_bounds__(kGenThreads)
+__global__ void __launch_bounds__(kGenThreads, 3)
 gqa_split_generic_kernel(const T *k, const T *v, const DecodeParams p, int d) {
   extern __shared__ float gsm[];
   const int chunk = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
@@ -630,8 +655,8 @@ gqa_split_generic_kernel(const T *k, const T *v, const DecodeParams p, int d) {
   if (end <= first) return;
   if (start < first) start = first;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int tt = gen_tile_tokens(d), gb_max = gen_head_batch(d, p.group), dp = d + 1;
-  float *Ks = gsm, *Vs = Ks + tt * dp, *q_s = Vs + tt * dp, *p_s = q_s + gb_max * d;
+  const int tt = gen_tile_tokens(d), gb_max = gen_head_batch(d, p.group), dp = gen_row_stride(d);
+  float *Ks = gsm, *Vs = Ks + tt * dp, *q_s = Vs + tt * dp, *p_s = q_s + ((gb_max * d + 3) & ~3);  // all 16-byte aligned
   float *m_s = p_s + gb_max * tt, *l_s = m_s + kGenMaxHeads, *corr_s = l_s + kGenMaxHeads;
   long long *row_s = reinterpret_cast<long long *>(
       (reinterpret_cast<uintptr_t>(corr_s + kGenMaxHeads) + 7) & ~uintptr_t(7));  // [tt] element offsets of the tile's rows
