@@ -31,6 +31,11 @@ int sdpa_rows_fallback(const void *q, const void *k, const void *v, void *out, i
                        int d, int64_t skv, int is_causal, int dtype, void *workspace,
                        size_t workspace_bytes, cudaStream_t st);
 size_t sdpa_rows_workspace_bytes(int sq, int hq, int hkv, int d, int64_t skv);
+// Tiled evaluation on the FMA pipe (prefill_tiled.cu): FLOAT32 and the head sizes the tensor-core kernels
+// do not take.
+bool sdpa_tiled_supported(int sq, int hq, int hkv, int d, int64_t skv);
+int sdpa_tiled(const void *q, const void *k, const void *v, void *out, int sq, int hq, int hkv, int d, int64_t skv,
+               int is_causal, int dtype, cudaStream_t st);
 
 namespace {
 
@@ -706,8 +711,11 @@ int axb200_sdpa(const void *q, const void *k, const void *v, void *out, int sq, 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool tensor_path = dtype == AXB200_FLOAT16 && d == axb::kD && hq <= 65535 && axb::aligned16(q) &&
                            axb::aligned16(k) && axb::aligned16(v) && axb::aligned16(out) && axb::encoder();
-  if (!tensor_path)
+  if (!tensor_path) {
+    if (axb::sdpa_tiled_supported(sq, hq, hkv, d, skv))
+      return axb::sdpa_tiled(q, k, v, out, sq, hq, hkv, d, skv, is_causal, dtype, st);
     return axb::sdpa_rows_fallback(q, k, v, out, sq, hq, hkv, d, skv, is_causal, dtype, workspace, workspace_bytes, st);
+  }
   // 256 query rows per CTA once there are that many; the 128-row form below that
   const bool pair = sq >= 2 * axb::kBlockM;
   const int kv_box = pair ? axb::kPairN : axb::kBlockN;

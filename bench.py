@@ -675,8 +675,10 @@ def run_reference_cuda(args):
 
 
 def run_prefill(args):
-    """`prefill`: causal fp16 prefill attention (sq = skv = 8192, 16 q / 8 kv heads, head_dim 128) on the
-    tcgen05 kernel; a tensor-bound kernel, so the roofline is the measured dense GEMM peak."""
+    """`prefill`: causal prefill attention (sq = skv = --prefill-len, 16 q / 8 kv heads, head_dim 128).
+    fp16 runs on the tcgen05 kernel: tensor-bound, the roofline is the measured dense GEMM peak.
+    `--dtype f32` (the reference's own type) runs on the tiled FMA kernel: the bound is the fp32 FMA
+    pipe, 148 SMs x 128 lanes x 2 flop x the maximum SM clock (nominal; no measured figure exists)."""
     import torch
 
     from axono_b200 import ops
@@ -684,9 +686,11 @@ def run_prefill(args):
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
     S = args.prefill_len
     gen = torch.Generator(device="cuda").manual_seed(11)
-    q = torch.randn((S, HQ, D), generator=gen, device="cuda").half()
-    k = torch.randn((S, HKV, D), generator=gen, device="cuda").half()
-    v = torch.randn((S, HKV, D), generator=gen, device="cuda").half()
+    f32 = args.dtype == "f32"
+    cast = (lambda t: t) if f32 else (lambda t: t.half())
+    q = cast(torch.randn((S, HQ, D), generator=gen, device="cuda"))
+    k = cast(torch.randn((S, HKV, D), generator=gen, device="cuda"))
+    v = cast(torch.randn((S, HKV, D), generator=gen, device="cuda"))
     for _ in range(max(3, args.warmup)):
         ops.scaled_dot_product_attention(q, k, v, True)
     sampler = ClockSampler(torch.cuda.current_device())
@@ -709,14 +713,18 @@ def run_prefill(args):
             peak, kind = float(json.load(f)["bf16_tflops"]), "measured"
     except Exception:
         peak, kind = 1590.0, "fallback"
+    kernel = "prefill_attn_f16_pair_kernel" if S >= 256 else "prefill_attn_f16_kernel"
+    bound = "tensor"
+    if f32:
+        peak, kind, kernel, bound = 148 * 128 * 2 * 1.965e9 / 1e12, "nominal fp32 FMA", "sdpa_tiled_kernel<float>", "fma"
     err = ops.last_error()
     print(json.dumps({
         "metric": "prefill_attention_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f16", "data": "synthetic",
+        "dtype": args.dtype, "data": "synthetic",
         "config": {"workload": "prefill", "sq": S, "skv": S, "hq": HQ, "hkv": HKV, "head_dim": D, "causal": True},
         "tokens_per_s": S / (ms / 1e3), "gpu_launches": args.steps, "error_word": err, "clocks": sampler.summary(),
-        "roofline": {"bound": "tensor", "kernel": "prefill_attn_f16_kernel", "achieved": tflops, "peak": peak,
+        "roofline": {"bound": bound, "kernel": kernel, "achieved": tflops, "peak": peak,
                      "unit": "TFLOP/s", "frac": tflops / peak, "peak_source": f"of {kind}", "traffic": None},
     }), flush=True)
 

@@ -322,6 +322,15 @@ class _ReferenceCuda:
                        skv, iters=iters)
         return out, ms
 
+    def sdpa(self, q, k, v, is_causal=False, iters=0):
+        q, k, v = _f32(q), _f32(k), _f32(v)
+        sq, hq, d = q.shape
+        skv, hkv, _ = k.shape
+        out = np.empty_like(q)
+        ms = self._run("sdpa_f32", [_f32p, _f32p, _f32p, _f32p, _sz, _sz, _sz, _sz, _sz, C.c_int], q, k, v, out, sq, hq,
+                       hkv, d, skv, int(bool(is_causal)), iters=iters)
+        return out, ms
+
     def add_rms_norm(self, x, residual, weight, eps=1e-6, iters=0):
         x, residual, weight = _f32(x), _f32(residual), _f32(weight)
         hidden = x.shape[-1]

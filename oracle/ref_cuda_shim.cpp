@@ -73,6 +73,23 @@ int refcu_gqa_decode_f32(const float *q, const float *k, const float *v, float *
   return 0;
 }
 
+// ScaledDotProductAttention (src/ops/cuda/sequence.cu:451-472): q (sq,hq,d), k/v (skv,hkv,d) fp32 host
+// buffers; the reference's kernel keeps skv scores per query in shared memory.
+int refcu_sdpa_f32(const float *q, const float *k, const float *v, float *out, size_t sq, size_t hq, size_t hkv,
+                   size_t d, size_t skv, int is_causal, int iters, double *ms_per_call) {
+  Context ctx;
+  Tensor tq = ToCuda(DataType::FLOAT32, {sq, hq, d}, q);
+  Tensor tk = ToCuda(DataType::FLOAT32, {skv, hkv, d}, k);
+  Tensor tv = ToCuda(DataType::FLOAT32, {skv, hkv, d}, v);
+  Tensor res(DataType::FLOAT32, {sq, hq, d}, "cuda");
+  int rc = Timed([&] { return axono::ops::cuda::ScaledDotProductAttention(ctx, tq, tk, tv, is_causal != 0, res); },
+                 iters, ms_per_call);
+  if (rc != 0) return rc;
+  Tensor host = res.to("cpu");
+  std::memcpy(out, host.data(), sq * hq * d * sizeof(float));
+  return 0;
+}
+
 // AddRmsNorm (src/ops/cuda/fused.cu:91-110).
 int refcu_add_rms_norm_f32(const float *x, const float *res_in, const float *w, float eps, float *y,
                            float *out, size_t rows, size_t hidden, int iters, double *ms_per_call) {

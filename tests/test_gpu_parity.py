@@ -540,6 +540,26 @@ def test_sdpa_row_fallback(ops, orc, dtype, hq, hkv, d):
         assert_close(out, orc.sdpa(q, k, v, causal), F32_TOL if dtype == torch.float32 else F16_TOL)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("hq,hkv,d", [(16, 8, 128), (4, 4, 64), (6, 2, 80), (16, 2, 96), (3, 1, 8), (8, 8, 192)])
+@pytest.mark.parametrize("sq,skv", [(16, 16), (70, 300), (300, 70), (257, 257), (1000, 1000), (33, 2049)])
+def test_sdpa_tiled_fma_path(ops, orc, dtype, hq, hkv, d, sq, skv):
+    """The tiled FMA prefill kernel (FLOAT32, and head sizes other than 128): both mask modes, query
+    blocks that do not divide sq, groups 1 / 2 / 3 / 8, more queries than keys and the reverse."""
+    rng = np.random.default_rng(sq * 31 + skv * 7 + d + hq)
+    q = rng.standard_normal((sq, hq, d)).astype(np.float32)
+    k = rng.standard_normal((skv, hkv, d)).astype(np.float32)
+    v = rng.standard_normal((skv, hkv, d)).astype(np.float32)
+    if dtype == torch.float16:
+        if d == 128:
+            pytest.skip("fp16 at head_dim 128 runs on the tensor-core kernel")
+        q, k, v = widen(q), widen(k), widen(v)
+    for causal in (False, True):
+        out = host(ops.scaled_dot_product_attention(dev(q, dtype), dev(k, dtype), dev(v, dtype), causal))
+        assert_close(out, orc.sdpa(q, k, v, causal), F32_TOL if dtype == torch.float32 else F16_TOL)
+    assert ops.last_error() == 0
+
+
 def test_sdpa_prefill_then_decode_consistency(ops, orc):
     """Prefill's last causal row equals decode attention of that query over the same cache
     (tests/nn/test_kv_cache.py:117-148 of the reference, at a length its SDPA kernel cannot reach)."""
