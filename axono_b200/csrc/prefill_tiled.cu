@@ -7,11 +7,11 @@
 //
 // One CTA per (block of query rows, KV head): the `group` query heads of the KV head times the rows
 // of the block make 64 virtual rows that share every staged K / V tile.  Per tile of 64 keys:
-//   stage    K and V rows into shared memory as fp32 (plain coalesced loads, eight in flight per
+//   stage    K and V rows into shared memory as fp32 (plain coalesced loads, four of each in flight per
 //            thread before the first store)
-//   scores   thread = 4 rows x 4 keys, 16-byte reads of Q and K rows: 8 shared-memory reads per 64 FMAs
-//   softmax  warp = 8 rows: maximum and sum by shuffles, the causal rule applied here
-//   P.V      thread = 4 rows x (head_dim / 16) columns, accumulators in registers
+//   scores   thread = 2 rows x 4 keys, 16-byte reads of Q and K rows: 6 shared-memory reads per 32 FMAs
+//   softmax  warp = 4 rows: maximum and sum by shuffles, the causal rule applied here
+//   P.V      thread = 2 rows x (head_dim / 16) columns, accumulators in registers
 // Semantics as the reference's CPU op (src/ops/cpu/sequence.cpp:236-301): q (sq,hq,d), k / v
 // (skv,hkv,d) token-major, head h reads KV head h / (hq / hkv), scale 1/sqrt(d); with is_causal row t
 // sees keys [0, min(t + 1, skv)).
@@ -29,7 +29,8 @@
 namespace axb {
 namespace {
 
-constexpr int kTpThreads = 256, kTpRows = 64, kTpKeys = 64, kTpLoadBatch = 8;
+constexpr int kTpRpt = 2;  // query rows per thread: 2 gives 16 warps per CTA, which hides the shared-memory latency
+constexpr int kTpRows = 64, kTpKeys = 64, kTpThreads = (kTpRows / kTpRpt) * 16, kTpLoadBatch = 4;
 constexpr float kTpLog2e = 1.4426950408889634f;
 
 struct TiledParams {
@@ -85,11 +86,11 @@ sdpa_tiled_kernel(const TiledParams p) {
     l_s[tid] = 0.f;
     corr_s[tid] = 1.f;
   }
-  // thread tile: rows 4 * ty .. + 3; keys tx + 16 * j (scores); columns (tx + 16 * j) * 4 .. + 3 (output)
+  // thread tile: rows kTpRpt * ty ..; keys tx + 16 * j (scores); columns (tx + 16 * j) * 4 .. + 3 (output)
   const int ty = tid >> 4, tx = tid & 15;
-  float acc[4][kCols * 4];
+  float acc[kTpRpt][kCols * 4];
 #pragma unroll
-  for (int a = 0; a < 4; ++a)
+  for (int a = 0; a < kTpRpt; ++a)
 #pragma unroll
     for (int c = 0; c < kCols * 4; ++c) acc[a][c] = 0.f;
   const float dom = p.scale * kTpLog2e;
@@ -135,37 +136,38 @@ sdpa_tiled_kernel(const TiledParams p) {
       }
     }
     __syncthreads();
-    // ---- scores: 4 rows x 4 keys per thread ----
+    // ---- scores: kTpRpt rows x 4 keys per thread ----
     {
-      float sc[4][4];
+      float sc[kTpRpt][4];
 #pragma unroll
-      for (int a = 0; a < 4; ++a)
+      for (int a = 0; a < kTpRpt; ++a)
 #pragma unroll
         for (int b = 0; b < 4; ++b) sc[a][b] = 0.f;
-      const float4 *q4 = reinterpret_cast<const float4 *>(Qs + (4 * ty) * d);
+      const float4 *q4 = reinterpret_cast<const float4 *>(Qs + (kTpRpt * ty) * d);
       const float4 *k4 = reinterpret_cast<const float4 *>(Ks + tx * dp);
       const int qs4 = d / 4, ks4 = (16 * dp) / 4;
 #pragma unroll 2
       for (int c4 = 0; c4 < d / 4; ++c4) {
-        float4 qv[4], kv[4];
+        float4 qv[kTpRpt], kv[4];
 #pragma unroll
-        for (int a = 0; a < 4; ++a) qv[a] = q4[a * qs4 + c4];
+        for (int a = 0; a < kTpRpt; ++a) qv[a] = q4[a * qs4 + c4];
 #pragma unroll
         for (int b = 0; b < 4; ++b) kv[b] = k4[b * ks4 + c4];
 #pragma unroll
-        for (int a = 0; a < 4; ++a)
+        for (int a = 0; a < kTpRpt; ++a)
 #pragma unroll
           for (int b = 0; b < 4; ++b)
             sc[a][b] = fmaf(qv[a].w, kv[b].w, fmaf(qv[a].z, kv[b].z, fmaf(qv[a].y, kv[b].y, fmaf(qv[a].x, kv[b].x, sc[a][b]))));
       }
 #pragma unroll
-      for (int a = 0; a < 4; ++a)
+      for (int a = 0; a < kTpRpt; ++a)
 #pragma unroll
-        for (int b = 0; b < 4; ++b) Ps[(4 * ty + a) * pp + tx + 16 * b] = sc[a][b];
+        for (int b = 0; b < 4; ++b) Ps[(kTpRpt * ty + a) * pp + tx + 16 * b] = sc[a][b];
     }
     __syncthreads();
-    // ---- online softmax: 8 rows per warp, the causal rule per row ----
-    for (int r = warp * 8; r < warp * 8 + 8; ++r) {
+    // ---- online softmax: kTpRows / warps rows per warp, the causal rule per row ----
+    constexpr int kRowsPerWarp = kTpRows / (kTpThreads / 32);
+    for (int r = warp * kRowsPerWarp; r < warp * kRowsPerWarp + kRowsPerWarp; ++r) {
       const int g = r / p.bq, i = r - g * p.bq;
       const int t_row = q0 + i;
       const int kv_end = (r < n_rows && t_row < p.sq) ? (p.causal ? min(t_row + 1, p.skv) : p.skv) : 0;
@@ -192,18 +194,18 @@ sdpa_tiled_kernel(const TiledParams p) {
       }
     }
     __syncthreads();
-    // ---- O = O * corr + P . V: 4 rows x kCols chunks of 4 columns per thread ----
+    // ---- O = O * corr + P . V: kTpRpt rows x kCols chunks of 4 columns per thread ----
     {
 #pragma unroll
-      for (int a = 0; a < 4; ++a) {
-        const float cr = corr_s[4 * ty + a];
+      for (int a = 0; a < kTpRpt; ++a) {
+        const float cr = corr_s[kTpRpt * ty + a];
 #pragma unroll
         for (int c = 0; c < kCols * 4; ++c) acc[a][c] *= cr;
       }
       for (int t = 0; t < nt; t += 4) {  // Ps and Vs rows past nt hold zeros
-        float4 pw[4];
+        float4 pw[kTpRpt];
 #pragma unroll
-        for (int a = 0; a < 4; ++a) pw[a] = *reinterpret_cast<const float4 *>(Ps + (4 * ty + a) * pp + t);
+        for (int a = 0; a < kTpRpt; ++a) pw[a] = *reinterpret_cast<const float4 *>(Ps + (kTpRpt * ty + a) * pp + t);
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
 #pragma unroll
@@ -212,7 +214,7 @@ sdpa_tiled_kernel(const TiledParams p) {
             if (c < d) {
               const float4 vv = *reinterpret_cast<const float4 *>(Vs + (t + u) * dp + c);
 #pragma unroll
-              for (int a = 0; a < 4; ++a) {
+              for (int a = 0; a < kTpRpt; ++a) {
                 const float w = u == 0 ? pw[a].x : u == 1 ? pw[a].y : u == 2 ? pw[a].z : pw[a].w;
                 acc[a][j * 4 + 0] = fmaf(w, vv.x, acc[a][j * 4 + 0]);
                 acc[a][j * 4 + 1] = fmaf(w, vv.y, acc[a][j * 4 + 1]);
@@ -229,8 +231,8 @@ sdpa_tiled_kernel(const TiledParams p) {
   // ---- O / l -> out ----
   T *og = reinterpret_cast<T *>(p.out);
 #pragma unroll
-  for (int a = 0; a < 4; ++a) {
-    const int r = 4 * ty + a;
+  for (int a = 0; a < kTpRpt; ++a) {
+    const int r = kTpRpt * ty + a;
     const int g = r / p.bq, i = r - g * p.bq;
     if (r >= n_rows || q0 + i >= p.sq) continue;
     const float l = l_s[r];

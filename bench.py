@@ -18,6 +18,12 @@ library) against the measured HBM peak.  `cpu_baseline` = the reference's CPU SD
 host cores, on a bounded sample of the same sequences.
 
 `--impl reference` times only that CPU path (oracle/_ref when built, else the C restatement).
+
+Other workloads, each with its own JSON line: `c2_block` (the fused decode block, batch 8, KV 8192, one
+CUDA graph), `c5_tower` (the 28-layer text-tower decode step; `--runtime native` runs it on the native
+runtime with no PyTorch in the process), `prefill` (causal prefill attention; `--dtype f32` for the
+reference's own type), `ops` (the standalone operators at the multimodal prompt's shapes);
+`--impl reference-cuda` times the reference's own CUDA kernels compiled for sm_100.
 """
 from __future__ import annotations
 
