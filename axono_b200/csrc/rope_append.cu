@@ -448,7 +448,7 @@ struct FusedQkvParams {
 };
 
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 qkv_norm_rope_append_kernel(const AppendParams p, const FusedQkvParams f, const InvFreqTable table) {
   __shared__ int s_len;
   const int b = blockIdx.x;
@@ -792,10 +792,14 @@ int axb200_qkv_norm_rope_append(const void *qkv, int64_t ld, const void *q_norm_
   axb::InvFreqTable table{};
   if (rotate && !inv_freq) axb::fill_table(&table, theta, d);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // one warp per head (q, k and v heads) up to the block limit: the heads of a row are independent and
+  // the kernel is a chain of dependent loads, so looping a warp over several heads only adds latency
+  const int heads = hq + 2 * hkv;
+  const int threads = heads >= 32 ? 1024 : (heads < 2 ? 64 : heads * 32);
   if (dtype == AXB200_FLOAT32)
-    axb::qkv_norm_rope_append_kernel<float><<<batch, 256, 0, st>>>(p, f, table);
+    axb::qkv_norm_rope_append_kernel<float><<<batch, threads, 0, st>>>(p, f, table);
   else
-    axb::qkv_norm_rope_append_kernel<__half><<<batch, 256, 0, st>>>(p, f, table);
+    axb::qkv_norm_rope_append_kernel<__half><<<batch, threads, 0, st>>>(p, f, table);
   return axb::launch_status();
 }
 
