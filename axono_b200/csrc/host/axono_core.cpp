@@ -132,6 +132,9 @@ bool Available() {
 }
 
 Status DeviceSynchronize() { return cudaDeviceSynchronize() == cudaSuccess ? Status::OK : Status::DEVICE_ERROR; }
+Status MemInfo(size_t *free_bytes, size_t *total_bytes) {
+  return cudaMemGetInfo(free_bytes, total_bytes) == cudaSuccess ? Status::OK : Status::DEVICE_ERROR;
+}
 Status CopyToHost(void *dst, const void *device_src, size_t bytes) {
   return cudaMemcpy(dst, device_src, bytes, cudaMemcpyDeviceToHost) == cudaSuccess ? Status::OK : Status::DEVICE_ERROR;
 }

@@ -84,6 +84,7 @@ namespace cuda {
 
 bool Available();
 Status DeviceSynchronize();
+Status MemInfo(size_t *free_bytes, size_t *total_bytes);  // of the current device
 Status CopyToHost(void *dst, const void *device_src, size_t bytes);  // blocking, legacy default stream
 Status CopyToDevice(void *device_dst, const void *src, size_t bytes);  // blocking, legacy default stream
 Status CopyOnDevice(void *device_dst, const void *device_src, size_t bytes);  // blocking, legacy default stream

@@ -198,6 +198,11 @@ PYBIND11_MODULE(libaxono, m) {
   m.def("set_cache_budget", &acuda::SetCacheBudget, py::arg("bytes"));
   m.def("cache_budget", &acuda::GetCacheBudget);
   m.def("clear_cache", &acuda::ClearDeviceCache);
+  m.def("mem_info", []() {  // (free, total) bytes of the current device
+    size_t f = 0, t = 0;
+    Check("mem_info", acuda::MemInfo(&f, &t));
+    return py::make_tuple(f, t);
+  });
   m.def("device_error_bits", []() { return axb200_last_error(); });
   m.def("version", []() { return std::string(axb200_version()); });
 

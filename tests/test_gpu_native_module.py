@@ -333,3 +333,36 @@ def test_native_tower_matches_torch_tower():
         assert oracle.rel_err(nt.last_logits.numpy().astype(np.float32), tt.last_logits.float().cpu().numpy()) <= 2e-2
         assert np.array_equal(g.output.numpy(), t_ids)
     assert g.replay_timed(5) > 0
+
+
+def test_runtime_returns_its_memory(lx):
+    """Allocate / free cycles and capture / replay / reset cycles leave the device where it was: blocks go
+    back to the pool (bounded by the budget), the capture pool is released by reset, graphs are destroyed."""
+    rng = np.random.default_rng(11)
+    a, b = dev(lx, rng.standard_normal((64, 1024), dtype=np.float32)), dev(lx, rng.standard_normal((64, 1024), dtype=np.float32))
+    w = dev(lx, np.ones(1024, np.float32))
+
+    def body():
+        y, xn = lx.add_rms_norm(a, b, w, 1e-6)
+        return lx.silu_mul(xn, y)
+
+    def cycle():
+        for n in (1 << 20, 3 << 20, 1 << 20, 5 << 20):
+            t = lx.Tensor(lx.DataType.INT8, [n], "cuda")
+            del t
+        g = native.CUDAGraph().capture(body)
+        for _ in range(3):
+            g.replay()
+        ref = g.output.numpy().copy()
+        g.reset()
+        return ref
+
+    first = cycle()  # warms the pool and every lazily created handle
+    lx.clear_cache()
+    free0, _ = lx.mem_info()
+    for _ in range(20):
+        assert np.array_equal(cycle(), first)
+    lx.clear_cache()
+    free1, _ = lx.mem_info()
+    assert abs(free0 - free1) <= (8 << 20), (free0, free1)  # nothing accumulates over 20 cycles
+    assert lx.cached_bytes() == 0
