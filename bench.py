@@ -816,7 +816,7 @@ def run_small_ops(args):
         torch.cuda.synchronize()
         launches += per_call * per_graph * args.steps
         us = e0.elapsed_time(e1) / (args.steps * per_graph) * 1e3
-        rows.append({"op": name, "us_per_call": round(us, 2), "kernels_per_call": per_call,
+        rows.append({"op": name, "us_per_call": round(us, 2), "abi_calls_per_call": per_call,
                      "algorithmic_bytes": int(nbytes), "gbs": round(nbytes / (us * 1e-6) / 1e9, 1)})
         g.reset()
     torch.cuda.profiler.stop()
