@@ -49,3 +49,16 @@ def test_status_to_runtime_error():
     _capi.check(0, "op")
     with pytest.raises(RuntimeError):
         _capi.check(4, "op")
+
+
+def test_bench_cli_parses_without_a_gpu():
+    """bench.py's command line loads on a CPU-only host (no CUDA call before a workload starts)."""
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--help"], capture_output=True, text=True,
+                         timeout=120)
+    assert out.returncode == 0, out.stderr
+    for word in ("--gpus", "--steps", "--warmup", "--impl", "--workload", "c5_tower", "prefill", "ops"):
+        assert word in out.stdout
