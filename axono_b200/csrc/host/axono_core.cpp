@@ -107,12 +107,12 @@ void CacheRelease(int dev, size_t bytes, void *p) {
 thread_local cudaStream_t t_capture_stream = nullptr;
 thread_local bool t_capturing = false;
 thread_local uint64_t t_capture_gen = 0;  // which capture of this thread an in-graph allocation belongs to
+thread_local std::vector<void *> t_capture_owned;  // pool blocks the running capture has taken
 
 struct PoolEntry {
   int dev;
   size_t bytes;
   void *ptr;
-  bool used;
 };
 struct CapturePool {
   std::mutex mu;
@@ -179,7 +179,6 @@ void SetCapturePoolRecording(bool on) {
   CapturePool &p = pool();
   std::lock_guard<std::mutex> lock(p.mu);
   p.recording = on;
-  for (auto &e : p.entries) e.used = false;
 }
 
 std::shared_ptr<void> AllocateStorage(size_t bytes, const std::string &device, bool zero) {
@@ -194,12 +193,16 @@ std::shared_ptr<void> AllocateStorage(size_t bytes, const std::string &device, b
   if (IsCapturing()) {
     // same sizes in the same order as the warm-up run: the addresses repeat
     std::lock_guard<std::mutex> lock(cp.mu);
-    for (auto &e : cp.entries)
-      if (!e.used && e.dev == dev && e.bytes == bytes) {
-        e.used = true;
-        if (zero) cudaMemsetAsync(e.ptr, 0, bytes, st);  // a memset node: storage starts at zero on every replay
-        return std::shared_ptr<void>(e.ptr, [](void *) {});  // pool-owned
+    for (size_t i = 0; i < cp.entries.size(); ++i) {
+      PoolEntry &e = cp.entries[i];
+      if (e.dev == dev && e.bytes == bytes) {
+        void *ptr = e.ptr;
+        cp.entries.erase(cp.entries.begin() + i);  // first match: the warm-up run's order
+        t_capture_owned.push_back(ptr);            // from now on it belongs to the graph being captured
+        if (zero) cudaMemsetAsync(ptr, 0, bytes, st);  // a memset node: storage starts at zero on every replay
+        return std::shared_ptr<void>(ptr, [](void *) {});
       }
+    }
   }
   if (IsCapturing()) {
     // No pool entry (the block form of capture has no warm-up run): a stream-ordered allocation,
@@ -235,7 +238,7 @@ std::shared_ptr<void> AllocateStorage(size_t bytes, const std::string &device, b
   {
     std::lock_guard<std::mutex> lock(cp.mu);
     if (cp.recording) {
-      cp.entries.push_back(PoolEntry{dev, bytes, p, false});
+      cp.entries.push_back(PoolEntry{dev, bytes, p});
       recorded = true;
     }
   }
@@ -244,6 +247,13 @@ std::shared_ptr<void> AllocateStorage(size_t bytes, const std::string &device, b
 }
 
 // ---- graph capture ----
+namespace {
+void DropCaptureOwned() {  // a capture that did not become a graph gives its pool blocks back to the device
+  for (void *ptr : t_capture_owned) cudaFree(ptr);
+  t_capture_owned.clear();
+}
+}  // namespace
+
 Status BeginGraphCapture(void **stream_out) {
   if (t_capturing) return Status::INVALID_ARGUMENT;
   cudaStream_t st = nullptr;
@@ -269,6 +279,7 @@ Status EndGraphCapture(void *stream, GraphExec *out) {
   if (cudaStreamEndCapture(st, &graph) != cudaSuccess || !graph) {
     cudaGetLastError();
     cudaStreamDestroy(st);
+    DropCaptureOwned();
     return Status::INTERNAL_ERROR;
   }
   size_t n = 0;
@@ -276,6 +287,7 @@ Status EndGraphCapture(void *stream, GraphExec *out) {
   if (n == 0) {  // nothing was launched: an empty graph is an error
     cudaGraphDestroy(graph);
     cudaStreamDestroy(st);
+    DropCaptureOwned();
     return Status::INVALID_ARGUMENT;
   }
   cudaGraphExec_t exec = nullptr;
@@ -284,12 +296,14 @@ Status EndGraphCapture(void *stream, GraphExec *out) {
   if (e != cudaSuccess) {
     cudaGetLastError();
     cudaStreamDestroy(st);
+    DropCaptureOwned();
     return Status::INTERNAL_ERROR;
   }
   out->Reset();
   out->exec_ = exec;
   out->stream_ = st;
   out->num_nodes_ = n;
+  out->owned_.swap(t_capture_owned);
   return Status::OK;
 }
 
@@ -302,12 +316,16 @@ void AbortGraphCapture(void *stream) {
   cudaGetLastError();
   if (graph) cudaGraphDestroy(graph);
   cudaStreamDestroy(st);
+  DropCaptureOwned();
 }
 
 GraphExec::~GraphExec() { Reset(); }
 void GraphExec::Reset() {
+  if (stream_) cudaStreamSynchronize(static_cast<cudaStream_t>(stream_));
   if (exec_) cudaGraphExecDestroy(static_cast<cudaGraphExec_t>(exec_));
   if (stream_) cudaStreamDestroy(static_cast<cudaStream_t>(stream_));
+  for (void *ptr : owned_) cudaFree(ptr);
+  owned_.clear();
   exec_ = nullptr;
   stream_ = nullptr;
   num_nodes_ = 0;

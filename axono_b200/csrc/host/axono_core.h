@@ -120,6 +120,10 @@ class GraphExec {
   void *exec_ = nullptr;    // cudaGraphExec_t
   void *stream_ = nullptr;  // cudaStream_t the graph was captured on
   size_t num_nodes_ = 0;
+  // Device blocks the captured run took from the capture pool: the graph's nodes and its output
+  // tensors point into them, so they live exactly as long as the graph (Reset frees them).  Another
+  // capture never touches them, so several graphs can be alive at once.
+  std::vector<void *> owned_;
 };
 
 Status BeginGraphCapture(void **stream_out);

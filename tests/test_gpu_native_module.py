@@ -366,3 +366,41 @@ def test_runtime_returns_its_memory(lx):
     free1, _ = lx.mem_info()
     assert abs(free0 - free1) <= (8 << 20), (free0, free1)  # nothing accumulates over 20 cycles
     assert lx.cached_bytes() == 0
+
+
+def test_several_graphs_alive_at_once(lx):
+    """A later capture must not touch the buffers of an earlier graph: each graph owns the pool blocks
+    its captured run took (compile() keeps one graph per call signature alive)."""
+    rng = np.random.default_rng(12)
+    w = dev(lx, np.ones(256, np.float32))
+
+    def block(x, r):
+        y, xn = lx.add_rms_norm(x, r, w, 1e-6)
+        return lx.silu_mul(xn, y)
+
+    m = native.compile(block)
+    xs = {n: (rng.standard_normal((n, 256), dtype=np.float32), rng.standard_normal((n, 256), dtype=np.float32)) for n in (4, 9, 17)}
+    ref = {}
+    for n, (x, r) in xs.items():  # three signatures -> three live graphs
+        ref[n] = m(dev(lx, x), dev(lx, r)).numpy().copy()
+    assert m.num_graphs == 3
+    for _ in range(3):
+        for n, (x, r) in xs.items():  # replay them in turn, with scratch allocations in between
+            junk = lx.Tensor(lx.DataType.FLOAT32, [n * 256], "cuda")
+            junk.copy_from_numpy(np.full(n * 256, 7.0, np.float32))
+            out = m(dev(lx, x), dev(lx, r)).numpy()
+            assert np.array_equal(out, ref[n])
+            del junk
+    a4, b4, a9, b9 = (dev(lx, t) for t in (*xs[4], *xs[9]))  # inputs are made outside the captured bodies
+    g1 = native.CUDAGraph().capture(lambda: block(a4, b4))
+    g1.replay()
+    first = g1.output.numpy().copy()
+    assert np.array_equal(first, ref[4])
+    g2 = native.CUDAGraph().capture(lambda: block(a9, b9))
+    g2.replay()
+    g1.replay()
+    assert np.array_equal(g1.output.numpy(), first)
+    g2.reset()  # releasing one graph leaves the other intact
+    g1.replay()
+    assert np.array_equal(g1.output.numpy(), first)
+    g1.reset()
