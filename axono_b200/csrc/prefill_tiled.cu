@@ -29,15 +29,17 @@
 namespace axb {
 namespace {
 
-constexpr int kTpRpt = 2;  // query rows per thread: 2 gives 16 warps per CTA, which hides the shared-memory latency
-constexpr int kTpRows = 64, kTpKeys = 64, kTpThreads = (kTpRows / kTpRpt) * 16, kTpLoadBatch = 4;
+// Two CTA shapes, both 512 threads (16 warps hide the shared-memory latency): 64 virtual rows with 2
+// rows per thread, and 128 virtual rows with 4 rows per thread - twice the FMAs per shared-memory byte -
+// where its 166 KB of shared memory (head_dim 128) fit and the problem has that many rows.
+constexpr int kTpKeys = 64, kTpThreads = 512, kTpLoadBatch = 4;
 constexpr float kTpLog2e = 1.4426950408889634f;
 
 struct TiledParams {
   const void *q, *k, *v;
   void *out;
   int sq, hq, hkv, group, skv, causal, d;
-  int bq;  // query rows per CTA: 64 / group
+  int bq;  // query rows per CTA: virtual rows / group
   float scale;
 };
 
@@ -51,14 +53,17 @@ __device__ __forceinline__ float tp_f32<__half>(__half v) { return __half2float(
 // Row stride of the staged tiles in floats: rows stay 16-byte aligned; (d + 4) / 4 is odd when d is a
 // multiple of 8, which keeps "thread = key" 16-byte reads conflict-free.
 __host__ __device__ inline int tp_stride(int d) { return d + 4; }
-inline size_t tp_smem_bytes(int d) {
-  return sizeof(float) * ((size_t)kTpRows * d + 2 * (size_t)kTpKeys * tp_stride(d) + (size_t)kTpRows * (kTpKeys + 4) +
-                          3 * kTpRows);
+inline size_t tp_smem_bytes(int d, int rows) {
+  return sizeof(float) * ((size_t)rows * d + 2 * (size_t)kTpKeys * tp_stride(d) + (size_t)rows * (kTpKeys + 4) +
+                          3 * (size_t)rows);
 }
 
-template <typename T, int kCols>  // kCols: 16-byte column chunks per thread = head_dim / 64, rounded up
+// kCols: 16-byte column chunks per thread = head_dim / 64, rounded up; kTpRows virtual rows per CTA,
+// kTpRpt of them per thread.
+template <typename T, int kCols, int kTpRows, int kTpRpt>
 __global__ void __launch_bounds__(kTpThreads)
 sdpa_tiled_kernel(const TiledParams p) {
+  static_assert((kTpRows / kTpRpt) * 16 == kTpThreads, "thread tile does not cover the CTA tile");
   extern __shared__ __align__(16) float tsm[];
   const int d = p.d, dp = tp_stride(d), pp = kTpKeys + 4;
   float *Qs = tsm, *Ks = Qs + kTpRows * d, *Vs = Ks + kTpKeys * dp, *Ps = Vs + kTpKeys * dp;
@@ -261,10 +266,10 @@ bool tp_set_smem(const void *kernel, int bytes) {
   return true;
 }
 
-template <typename T, int kCols>
+template <typename T, int kCols, int kRows, int kRpt>
 int tp_launch(const TiledParams &p, cudaStream_t st) {
-  auto kern = sdpa_tiled_kernel<T, kCols>;
-  const int smem = (int)tp_smem_bytes(p.d);
+  auto kern = sdpa_tiled_kernel<T, kCols, kRows, kRpt>;
+  const int smem = (int)tp_smem_bytes(p.d, kRows);
   if (!tp_set_smem(reinterpret_cast<const void *>(kern), 200 * 1024)) return AXB200_DEVICE_ERROR;
   const dim3 grid((p.sq + p.bq - 1) / p.bq, p.hkv);
   kern<<<grid, kTpThreads, smem, st>>>(p);
@@ -277,9 +282,21 @@ int tp_launch(const TiledParams &p, cudaStream_t st) {
 // Whether the tiled kernel takes this problem; otherwise the caller runs it row by row.
 bool sdpa_tiled_supported(int sq, int hq, int hkv, int d, int64_t skv) {
   const int group = hkv > 0 ? hq / hkv : 0;
-  return sq >= 16 && d % 4 == 0 && d >= 4 && d <= 256 && group >= 1 && group <= kTpRows && hkv <= 65535 &&
-         skv <= 0x7fffffff - kTpKeys && tp_smem_bytes(d) <= 200 * 1024;
+  return sq >= 16 && d % 4 == 0 && d >= 4 && d <= 256 && group >= 1 && group <= 64 && hkv <= 65535 &&
+         skv <= 0x7fffffff - kTpKeys && tp_smem_bytes(d, 64) <= 200 * 1024;
 }
+
+namespace {
+template <typename T, int kRows, int kRpt>
+int tp_dispatch_cols(const TiledParams &p, cudaStream_t st) {
+  switch ((p.d + 63) / 64) {  // 16-byte chunks per thread
+    case 1: return tp_launch<T, 1, kRows, kRpt>(p, st);
+    case 2: return tp_launch<T, 2, kRows, kRpt>(p, st);
+    case 3: return tp_launch<T, 3, kRows, kRpt>(p, st);
+    default: return tp_launch<T, 4, kRows, kRpt>(p, st);
+  }
+}
+}  // namespace
 
 int sdpa_tiled(const void *q, const void *k, const void *v, void *out, int sq, int hq, int hkv, int d, int64_t skv,
                int is_causal, int dtype, cudaStream_t st) {
@@ -295,23 +312,13 @@ int sdpa_tiled(const void *q, const void *k, const void *v, void *out, int sq, i
   p.skv = (int)skv;
   p.causal = is_causal != 0;
   p.d = d;
-  p.bq = kTpRows / p.group;
   p.scale = 1.0f / sqrtf((float)d);
-  const int cols = (d + 63) / 64;  // 16-byte chunks per thread
-  if (dtype == AXB200_FLOAT32) {
-    switch (cols) {
-      case 1: return tp_launch<float, 1>(p, st);
-      case 2: return tp_launch<float, 2>(p, st);
-      case 3: return tp_launch<float, 3>(p, st);
-      default: return tp_launch<float, 4>(p, st);
-    }
-  }
-  switch (cols) {
-    case 1: return tp_launch<__half, 1>(p, st);
-    case 2: return tp_launch<__half, 2>(p, st);
-    case 3: return tp_launch<__half, 3>(p, st);
-    default: return tp_launch<__half, 4>(p, st);
-  }
+  // 128 virtual rows per CTA where they fit in shared memory and the problem fills them
+  const bool big = tp_smem_bytes(d, 128) <= 200 * 1024 && (int64_t)sq * p.group >= 128 && d <= 128;
+  p.bq = (big ? 128 : 64) / p.group;
+  if (dtype == AXB200_FLOAT32)
+    return big ? tp_dispatch_cols<float, 128, 4>(p, st) : tp_dispatch_cols<float, 64, 2>(p, st);
+  return big ? tp_dispatch_cols<__half, 128, 4>(p, st) : tp_dispatch_cols<__half, 64, 2>(p, st);
 }
 
 }  // namespace axb
