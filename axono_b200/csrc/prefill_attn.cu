@@ -698,7 +698,10 @@ bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 extern "C" {
 
 size_t axb200_sdpa_workspace_bytes(int sq, int hq, int hkv, int d, int64_t skv, int dtype) {
-  if (dtype == AXB200_FLOAT16 && d == axb::kD) return 0;
+  // the tensor-core kernels and the tiled FMA kernel keep everything on chip; only the row-by-row
+  // evaluation on the decode kernels needs room for partials
+  // (whatever the tensor-core path does not take - unaligned pointers, say - the tiled kernel does)
+  if (hkv > 0 && hq % hkv == 0 && axb::sdpa_tiled_supported(sq, hq, hkv, d, skv)) return 0;
   return axb::sdpa_rows_workspace_bytes(sq, hq, hkv, d, skv);
 }
 

@@ -143,8 +143,10 @@ int axb200_gqa_decode_paged_window(const void *q, void *out, const void *k_pages
  * src/ops/cuda/sequence.cu:105-163,451-472): q (sq,hq,d), k/v (skv,hkv,d) token-major, out (sq,hq,d);
  * scale 1/sqrt(d); head h reads KV head h/(hq/hkv); with is_causal row t sees keys [0, t] when
  * skv >= t+1 and every key otherwise (src/ops/cpu/sequence.cpp:269-270).  fp16 with d == 128 runs on
- * the tcgen05 tensor cores (no scratch needed); other cases run row by row on the decode kernels and
- * need axb200_sdpa_workspace_bytes of scratch.  There is no shared-memory limit on skv. */
+ * the tcgen05 tensor cores; FLOAT32 and other head sizes (d a multiple of 4 up to 192, sq >= 16) on a
+ * tiled FMA kernel with fp32 arithmetic; neither needs scratch.  The remaining cases run row by row
+ * on the decode kernels and need axb200_sdpa_workspace_bytes of scratch (0 for the first two).
+ * There is no shared-memory limit on skv. */
 size_t axb200_sdpa_workspace_bytes(int sq, int hq, int hkv, int d, int64_t skv, int dtype);
 int axb200_sdpa(const void *q, const void *k, const void *v, void *out,
                 int sq, int hq, int hkv, int d, int64_t skv, int is_causal, int dtype,
