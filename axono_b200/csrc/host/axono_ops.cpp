@@ -290,13 +290,47 @@ Status LinearNoBias(const Context &, const Tensor &x, const Tensor &w, Tensor &r
     ok = ok && api.PrefCreate(&pref) == CUBLAS_STATUS_SUCCESS;
     ok = ok && api.PrefSet(pref, CUBLASLT_MATMUL_PREF_MAX_WORKSPACE_BYTES, &lt.workspace_bytes,
                                                     sizeof(lt.workspace_bytes)) == CUBLAS_STATUS_SUCCESS;
-    cublasLtMatmulHeuristicResult_t heur{};
+    // Up to eight candidates from the heuristic, each timed on the real operands (beta = 0, so the
+    // trial runs are idempotent): at a few dozen rows the first candidate is often not the fastest.
+    constexpr int kCandidates = 8;
+    cublasLtMatmulHeuristicResult_t heur[kCandidates];
     int found = 0;
-    ok = ok && api.Heuristic(lt.handle, pl.op, pl.a, pl.b, pl.c, pl.c, pref, 1, &heur, &found) ==
+    ok = ok && api.Heuristic(lt.handle, pl.op, pl.a, pl.b, pl.c, pl.c, pref, kCandidates, heur, &found) ==
                    CUBLAS_STATUS_SUCCESS && found > 0;
     if (pref) api.PrefDestroy(pref);
     if (!ok) return Status::INTERNAL_ERROR;
-    pl.algo = heur.algo;
+    int best = 0;
+    if (found > 1) {
+      const float one = 1.f, zero = 0.f;
+      cudaStream_t ts = static_cast<cudaStream_t>(Stream());
+      cudaEvent_t e0 = nullptr, e1 = nullptr;
+      float best_ms = -1.f;
+      if (cudaEventCreate(&e0) == cudaSuccess && cudaEventCreate(&e1) == cudaSuccess) {
+        for (int c = 0; c < found; ++c) {
+          if (heur[c].state != CUBLAS_STATUS_SUCCESS || heur[c].workspaceSize > lt.workspace_bytes) continue;
+          bool run_ok = true;
+          for (int rep = 0; rep < 13 && run_ok; ++rep) {
+            if (rep == 3) cudaEventRecord(e0, ts);  // three warm-up runs, ten timed
+            run_ok = api.Matmul(lt.handle, pl.op, &one, w.data(), pl.a, x.data(), pl.b, &zero, result.data(), pl.c,
+                                result.data(), pl.c, &heur[c].algo, lt.workspace, lt.workspace_bytes, ts) ==
+                     CUBLAS_STATUS_SUCCESS;
+          }
+          float ms = 0.f;
+          if (!run_ok || cudaEventRecord(e1, ts) != cudaSuccess || cudaEventSynchronize(e1) != cudaSuccess ||
+              cudaEventElapsedTime(&ms, e0, e1) != cudaSuccess) {
+            cudaGetLastError();
+            continue;
+          }
+          if (best_ms < 0.f || ms < best_ms) {
+            best_ms = ms;
+            best = c;
+          }
+        }
+      }
+      if (e0) cudaEventDestroy(e0);
+      if (e1) cudaEventDestroy(e1);
+    }
+    pl.algo = heur[best].algo;
     it = lt.plans.emplace(key, pl).first;
   }
   const LtState::Plan &pl = it->second;
