@@ -67,6 +67,7 @@ SIGNATURES = {
     "axb200_rms_norm": (_i, [_vp, _vp, _f, _vp, _i64, _i, _i, _vp]),
     "axb200_embedding": (_i, [_vp, _i, _vp, _vp, _i64, _i64, _i, _i, _vp]),
     "axb200_argmax_last_dim": (_i, [_vp, _vp, _i64, _i, _i, _vp]),
+    "axb200_linear_nobias": (_i, [_vp, _vp, _vp, _i64, _i64, _i64, _i, _vp]),
     "axb200_cast": (_i, [_vp, _i, _vp, _i, _i64, _vp]),
     "axb200_concat": (_i, [_vp, _vp, _vp, _i64, _sz, _sz, _vp]),
 }

@@ -47,7 +47,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     cmd = [nvcc, *NVCC_FLAGS, "-I", os.path.join(ROOT, "include"), "-I", CSRC]
     if verbose:
         cmd += ["-Xptxas", "-v"]
-    cmd += ["-o", LIB, *sources()]
+    cmd += ["-o", LIB, *sources(), "-ldl"]
     subprocess.check_call(cmd)
     return LIB
 

@@ -2,14 +2,6 @@
 
 #include <algorithm>
 
-#include <cublasLt.h>
-#include <cuda_runtime.h>
-#include <dlfcn.h>
-
-#include <map>
-#include <mutex>
-#include <tuple>
-
 #include "axono_b200.h"
 
 namespace axono {
@@ -193,152 +185,14 @@ Status ArgmaxLastDim(const Context &, const Tensor &x, Tensor &result) {
   return St(axb200_argmax_last_dim(x.data(), result.data<int64_t>(), (int64_t)rows, (int)cols, Dt(x.dtype()), Stream()));
 }
 
-namespace {
-
-// cuBLASLt is opened on first use, by its soname first: a process that also holds PyTorch then shares
-// the copy PyTorch loaded (two different builds under one soname cannot live side by side - import
-// torch before the first projection in such a process), and a process without it gets the toolkit's.
-struct LtApi {
-  decltype(&cublasLtCreate) Create = nullptr;
-  decltype(&cublasLtMatmulDescCreate) DescCreate = nullptr;
-  decltype(&cublasLtMatmulDescSetAttribute) DescSet = nullptr;
-  decltype(&cublasLtMatrixLayoutCreate) LayoutCreate = nullptr;
-  decltype(&cublasLtMatmulPreferenceCreate) PrefCreate = nullptr;
-  decltype(&cublasLtMatmulPreferenceSetAttribute) PrefSet = nullptr;
-  decltype(&cublasLtMatmulPreferenceDestroy) PrefDestroy = nullptr;
-  decltype(&cublasLtMatmulAlgoGetHeuristic) Heuristic = nullptr;
-  decltype(&cublasLtMatmul) Matmul = nullptr;
-  bool ok = false;
-};
-const LtApi &lt_api() {
-  static LtApi api = [] {
-    LtApi a;
-    void *h = dlopen("libcublasLt.so.12", RTLD_NOW | RTLD_GLOBAL);
-    if (!h) h = dlopen("/usr/local/cuda/lib64/libcublasLt.so.12", RTLD_NOW | RTLD_GLOBAL);
-    if (!h) return a;
-#define AXONO_LT_SYM(field, name) a.field = reinterpret_cast<decltype(a.field)>(dlsym(h, #name))
-    AXONO_LT_SYM(Create, cublasLtCreate);
-    AXONO_LT_SYM(DescCreate, cublasLtMatmulDescCreate);
-    AXONO_LT_SYM(DescSet, cublasLtMatmulDescSetAttribute);
-    AXONO_LT_SYM(LayoutCreate, cublasLtMatrixLayoutCreate);
-    AXONO_LT_SYM(PrefCreate, cublasLtMatmulPreferenceCreate);
-    AXONO_LT_SYM(PrefSet, cublasLtMatmulPreferenceSetAttribute);
-    AXONO_LT_SYM(PrefDestroy, cublasLtMatmulPreferenceDestroy);
-    AXONO_LT_SYM(Heuristic, cublasLtMatmulAlgoGetHeuristic);
-    AXONO_LT_SYM(Matmul, cublasLtMatmul);
-#undef AXONO_LT_SYM
-    a.ok = a.Create && a.DescCreate && a.DescSet && a.LayoutCreate && a.PrefCreate && a.PrefSet && a.PrefDestroy &&
-           a.Heuristic && a.Matmul;
-    return a;
-  }();
-  return api;
-}
-
-// One cuBLASLt handle and one 32 MB workspace per device, made on first use (outside graph capture:
-// the warm-up run of CUDAGraph.capture makes that first call); one matmul plan per (rows, out, in, dtype).
-struct LtState {
-  cublasLtHandle_t handle = nullptr;
-  void *workspace = nullptr;
-  size_t workspace_bytes = size_t(32) << 20;
-  struct Plan {
-    cublasLtMatmulDesc_t op = nullptr;
-    cublasLtMatrixLayout_t a = nullptr, b = nullptr, c = nullptr;
-    cublasLtMatmulAlgo_t algo;
-  };
-  std::map<std::tuple<int64_t, int64_t, int64_t, int>, Plan> plans;
-};
-std::mutex g_lt_mu;
-LtState g_lt[64];
-
-}  // namespace
-
 Status LinearNoBias(const Context &, const Tensor &x, const Tensor &w, Tensor &result) {
   if (x.ndim() != 2 || w.ndim() != 2 || x.shape()[1] != w.shape()[1]) return Status::SHAPE_MISMATCH;
   if (!Float(x.dtype()) || w.dtype() != x.dtype()) return Status::UNSUPPORTED_TYPE;
   if (!Cuda(x) || !Cuda(w)) return Status::DEVICE_MISMATCH;
-  const int64_t rows = (int64_t)x.shape()[0], in = (int64_t)x.shape()[1], out = (int64_t)w.shape()[0];
-  Status st = result.Resize({(size_t)rows, (size_t)out});
+  Status st = result.Resize({x.shape()[0], w.shape()[0]});
   if (st != Status::OK) return st;
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return Status::DEVICE_ERROR;
-  const LtApi &api = lt_api();
-  if (!api.ok) return Status::INTERNAL_ERROR;
-  std::lock_guard<std::mutex> lock(g_lt_mu);
-  LtState &lt = g_lt[dev];
-  if (!lt.handle) {
-    if (core::cuda::IsCapturing()) return Status::INVALID_ARGUMENT;  // first use must be outside a capture
-    if (api.Create(&lt.handle) != CUBLAS_STATUS_SUCCESS) return Status::DEVICE_ERROR;
-    if (cudaMalloc(&lt.workspace, lt.workspace_bytes) != cudaSuccess) return Status::OUT_OF_MEMORY;
-  }
-  const bool half = x.dtype() == DataType::FLOAT16;
-  const cudaDataType_t dt = half ? CUDA_R_16F : CUDA_R_32F;
-  auto key = std::make_tuple(rows, out, in, (int)half);
-  auto it = lt.plans.find(key);
-  if (it == lt.plans.end()) {
-    if (core::cuda::IsCapturing()) return Status::INVALID_ARGUMENT;  // plans are made in the warm-up run
-    // Row-major result (rows, out) = x . w^T is column-major (out, rows) = w_cm^T . x_cm, where the
-    // row-major buffers read column-major are w_cm (in, out) and x_cm (in, rows).
-    LtState::Plan pl;
-    const cublasOperation_t ta = CUBLAS_OP_T, tb = CUBLAS_OP_N;
-    bool ok = api.DescCreate(&pl.op, CUBLAS_COMPUTE_32F, CUDA_R_32F) == CUBLAS_STATUS_SUCCESS;
-    ok = ok && api.DescSet(pl.op, CUBLASLT_MATMUL_DESC_TRANSA, &ta, sizeof(ta)) == CUBLAS_STATUS_SUCCESS;
-    ok = ok && api.DescSet(pl.op, CUBLASLT_MATMUL_DESC_TRANSB, &tb, sizeof(tb)) == CUBLAS_STATUS_SUCCESS;
-    ok = ok && api.LayoutCreate(&pl.a, dt, in, out, in) == CUBLAS_STATUS_SUCCESS;    // w_cm
-    ok = ok && api.LayoutCreate(&pl.b, dt, in, rows, in) == CUBLAS_STATUS_SUCCESS;   // x_cm
-    ok = ok && api.LayoutCreate(&pl.c, dt, out, rows, out) == CUBLAS_STATUS_SUCCESS; // result_cm
-    cublasLtMatmulPreference_t pref = nullptr;
-    ok = ok && api.PrefCreate(&pref) == CUBLAS_STATUS_SUCCESS;
-    ok = ok && api.PrefSet(pref, CUBLASLT_MATMUL_PREF_MAX_WORKSPACE_BYTES, &lt.workspace_bytes,
-                                                    sizeof(lt.workspace_bytes)) == CUBLAS_STATUS_SUCCESS;
-    // Up to eight candidates from the heuristic, each timed on the real operands (beta = 0, so the
-    // trial runs are idempotent): at a few dozen rows the first candidate is often not the fastest.
-    constexpr int kCandidates = 8;
-    cublasLtMatmulHeuristicResult_t heur[kCandidates];
-    int found = 0;
-    ok = ok && api.Heuristic(lt.handle, pl.op, pl.a, pl.b, pl.c, pl.c, pref, kCandidates, heur, &found) ==
-                   CUBLAS_STATUS_SUCCESS && found > 0;
-    if (pref) api.PrefDestroy(pref);
-    if (!ok) return Status::INTERNAL_ERROR;
-    int best = 0;
-    if (found > 1) {
-      const float one = 1.f, zero = 0.f;
-      cudaStream_t ts = static_cast<cudaStream_t>(Stream());
-      cudaEvent_t e0 = nullptr, e1 = nullptr;
-      float best_ms = -1.f;
-      if (cudaEventCreate(&e0) == cudaSuccess && cudaEventCreate(&e1) == cudaSuccess) {
-        for (int c = 0; c < found; ++c) {
-          if (heur[c].state != CUBLAS_STATUS_SUCCESS || heur[c].workspaceSize > lt.workspace_bytes) continue;
-          bool run_ok = true;
-          for (int rep = 0; rep < 13 && run_ok; ++rep) {
-            if (rep == 3) cudaEventRecord(e0, ts);  // three warm-up runs, ten timed
-            run_ok = api.Matmul(lt.handle, pl.op, &one, w.data(), pl.a, x.data(), pl.b, &zero, result.data(), pl.c,
-                                result.data(), pl.c, &heur[c].algo, lt.workspace, lt.workspace_bytes, ts) ==
-                     CUBLAS_STATUS_SUCCESS;
-          }
-          float ms = 0.f;
-          if (!run_ok || cudaEventRecord(e1, ts) != cudaSuccess || cudaEventSynchronize(e1) != cudaSuccess ||
-              cudaEventElapsedTime(&ms, e0, e1) != cudaSuccess) {
-            cudaGetLastError();
-            continue;
-          }
-          if (best_ms < 0.f || ms < best_ms) {
-            best_ms = ms;
-            best = c;
-          }
-        }
-      }
-      if (e0) cudaEventDestroy(e0);
-      if (e1) cudaEventDestroy(e1);
-    }
-    pl.algo = heur[best].algo;
-    it = lt.plans.emplace(key, pl).first;
-  }
-  const LtState::Plan &pl = it->second;
-  const float alpha = 1.f, beta = 0.f;
-  const cublasStatus_t cs = api.Matmul(lt.handle, pl.op, &alpha, w.data(), pl.a, x.data(), pl.b, &beta, result.data(),
-                                           pl.c, result.data(), pl.c, &pl.algo, lt.workspace, lt.workspace_bytes,
-                                           static_cast<cudaStream_t>(Stream()));
-  return cs == CUBLAS_STATUS_SUCCESS ? Status::OK : Status::DEVICE_ERROR;
+  return St(axb200_linear_nobias(x.data(), w.data(), result.data(), (int64_t)x.shape()[0], (int64_t)w.shape()[0],
+                                 (int64_t)x.shape()[1], Dt(x.dtype()), Stream()));
 }
 
 Status SiluMulRows(const Context &, const Tensor &gate_up, int n, Tensor &result) {

@@ -6,7 +6,8 @@ RoPE on q/k -> KV-cache append -> gqa_decode_attention -> silu_mul.
 `TextTower` is the decode step of the reference's only consumer of the path, the Qwen3-VL text
 tower (axono/python/examples/vlm/qwen3vl/model.py:330-373 attention, :408-436 layer, :483-486 final
 norm + tied lm_head, :729-761 decode_step), extended from one sequence to a batch of rows.  Its
-projections are library GEMMs (torch.matmul -> cuBLASLt), which stay outside the rewritten path;
+projections are library GEMMs (one cuBLASLt call each through `ops.linear_nobias`, whose algorithm is
+timed per shape on first use; `lt_gemm=False` takes torch.matmul), which stay outside the rewritten path;
 everything between them is this package's kernels.  Two fusions the reference's layer does not have:
 the residual add that ends a layer is folded into the next layer's input norm (one add_rms_norm),
 and rope + append is one launch.  KV heads shard across ranks (`world`, `rank`): each rank projects
@@ -42,9 +43,10 @@ class TextTower:
 
     def __init__(self, cfg: TextTowerConfig, batch: int, max_seq_len: int, device="cuda",
                  dtype=torch.float16, world: int = 1, rank: int = 0, seed: int = 0, page_tokens: int = 64,
-                 fused_gather: bool = True, fused_qkv: bool = True):
+                 fused_gather: bool = True, fused_qkv: bool = True, lt_gemm: bool = True):
         self.cfg, self.batch, self.device, self.dtype = cfg, batch, torch.device(device), dtype
         self.fused_qkv = fused_qkv
+        self._linear = ops.linear_nobias if lt_gemm else (lambda x, w: torch.matmul(x, w.t()))
         self.world, self.rank = world, rank
         self.peer_gather = None
         if world > 1 and fused_gather:
@@ -93,7 +95,7 @@ class TextTower:
     # ---------------------------------------------------------------------------------------------
     def _attention(self, li: int, xn: torch.Tensor) -> torch.Tensor:
         cfg, lw, d = self.cfg, self.layers[li], self.cfg.head_dim
-        qkv = torch.matmul(xn, lw["qkv"].t())  # library GEMM
+        qkv = self._linear(xn, lw["qkv"])  # library GEMM
         if self.fused_qkv:  # per-head norms + rope + append in one launch, straight from the GEMM output
             q = self.cache.append_qkv(li, qkv, self.local_q, lw["q_norm"] if cfg.qk_norm else None,
                                       lw["k_norm"] if cfg.qk_norm else None, cfg.eps,
@@ -121,7 +123,7 @@ class TextTower:
             attn = self.cache.attend(li, q)  # (batch, local_q, d)
             if self.world > 1:
                 attn = sharding.all_gather_heads(attn)  # library collective (NCCL): the baseline
-        return torch.matmul(attn.reshape(self.batch, cfg.n_q_heads * d), lw["o"].t())
+        return self._linear(attn.reshape(self.batch, cfg.n_q_heads * d), lw["o"])
 
     def decode_step(self) -> torch.Tensor:
         """One token for every row: reads `token_ids` / `pos3`, appends to every layer's cache, writes
@@ -136,14 +138,14 @@ class TextTower:
                 h, xn = ops.add_rms_norm(mlp_out, h, lw["input_ln"], cfg.eps)
             attn_out = self._attention(li, xn)
             h, xn2 = ops.add_rms_norm(attn_out, h, lw["post_ln"], cfg.eps)
-            gu = torch.matmul(xn2, lw["gate_up"].t())
+            gu = self._linear(xn2, lw["gate_up"])
             if self.fused_qkv:
                 act = ops.silu_mul_rows(gu, cfg.intermediate)
             else:
                 act = ops.silu_mul(gu[:, :cfg.intermediate].contiguous(), gu[:, cfg.intermediate:].contiguous())
-            mlp_out = torch.matmul(act, lw["down"].t())
+            mlp_out = self._linear(act, lw["down"])
         _, xf = ops.add_rms_norm(mlp_out, h, self.final_ln, cfg.eps)
-        logits = torch.matmul(xf, self.embed.t())
+        logits = self._linear(xf, self.embed)
         self.last_logits = logits
         nxt = ops.argmax_last_dim(logits)
         self.token_ids.copy_(nxt)

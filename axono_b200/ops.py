@@ -379,6 +379,20 @@ def rms_norm(x, weight, eps: float = 1e-5):
     return out
 
 
+def linear_nobias(x, weight):
+    """x (rows, in) . weight (out, in)^T -> (rows, out): one cuBLASLt call whose algorithm is timed and
+    chosen on the first use of a shape (so call it once eagerly before capturing it)."""
+    op = "linear_nobias"
+    dt = _dt(x, op)
+    if x.dim() != 2 or weight.dim() != 2 or x.shape[1] != weight.shape[1] or weight.dtype != x.dtype:
+        _capi.check(4, op)  # SHAPE_MISMATCH
+    x, weight = _c(x), _c(weight)
+    out = torch.empty((x.shape[0], weight.shape[0]), dtype=x.dtype, device=x.device)
+    _call(_capi.lib().axb200_linear_nobias(x.data_ptr(), weight.data_ptr(), out.data_ptr(), x.shape[0], weight.shape[0],
+                                           x.shape[1], dt, _stream(x)), op)
+    return out
+
+
 def cast(x, dtype):
     """Tensor.cast_to on the device (src/core/cuda/tensor/kernel.cu:175-193): float16 <-> float32."""
     op = "cast"

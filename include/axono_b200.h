@@ -332,6 +332,14 @@ int axb200_argmax_last_dim(const void *x, int64_t *out, int64_t rows, int cols, 
  * Tensor::CastTo: FLOAT16 <-> FLOAT32, IEEE round to nearest even. */
 int axb200_cast(const void *src, int src_dtype, void *dst, int dst_dtype, int64_t n, void *stream);
 
+/* The tower's projection: out (rows, out_features) = x (rows, in_features) . w (out_features,
+ * in_features)^T as ONE cuBLASLt call (FLOAT16 with fp32 accumulation, or FLOAT32) - a library GEMM, as
+ * the reference's LinearNoBias is (src/ops/cuda/linear.cu:105-203); outside the rewritten path.  The
+ * first call of a shape (outside any stream capture) times up to eight heuristic candidates on the
+ * operands given and keeps the fastest; later calls, captured or not, reuse it. */
+int axb200_linear_nobias(const void *x, const void *w, void *out, int64_t rows, int64_t out_features,
+                         int64_t in_features, int dtype, void *stream);
+
 /* axono::ops::cuda::Concat, src/ops/cuda/sequence.cu:474-521, on bytes: out (outer, a_bytes +
  * b_bytes) = a (outer, a_bytes) ++ b (outer, b_bytes).  Axis 0 is outer == 1. */
 int axb200_concat(const void *a, const void *b, void *out, int64_t outer,

@@ -580,3 +580,17 @@ def test_cast_half_float_round_trip(ops):
     assert h.dtype == torch.float16 and torch.equal(h, a.half())
     assert torch.equal(ops.cast(h, torch.float32), h.float())
     assert ops.cast(a, torch.float32) is a
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-4), (torch.float16, 4e-3)])
+def test_linear_nobias_is_x_wT(ops, dtype, tol):
+    """The tower's projection through the C ABI: one cuBLASLt call, algorithm timed on first use."""
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn((32, 384), generator=g, device="cuda").to(dtype)
+    w = (0.05 * torch.randn((640, 384), generator=g, device="cuda")).to(dtype)
+    for _ in range(2):  # the second call reuses the chosen plan
+        y = ops.linear_nobias(x, w)
+        ref = x.float() @ w.float().t()
+        assert y.shape == (32, 640) and oracle.rel_err(y.float().cpu().numpy(), ref.cpu().numpy()) <= tol
+    with pytest.raises(RuntimeError):
+        ops.linear_nobias(x, w[:, :100].contiguous())
