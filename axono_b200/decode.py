@@ -16,10 +16,9 @@ collective of the step.
 """
 from __future__ import annotations
 
-from typing import Optional, Tuple
+from typing import Optional
 
 import torch
-import torch.distributed as dist
 
 from . import ops, sharding
 from .kv_cache import PagedKVCache

@@ -53,7 +53,6 @@ def test_arena_backed_cache_matches_plain_paged_cache():
     and the results stay exact because the kernels mask by length."""
     import oracle
     from axono_b200 import ops
-    from axono_b200.kv_cache import PagedKVCache
 
     orc = oracle.best()
     rng = np.random.default_rng(71)

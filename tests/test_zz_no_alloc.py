@@ -5,9 +5,6 @@ allocator, or a cudaMalloc in the decode loop would synchronise the whole device
 library carries a fixed 4 MiB scratch array of its own.  This file is named to be collected last,
 and it must pass both on its own in a fresh process and after every other GPU test has run.
 """
-import ctypes
-
-import numpy as np
 import pytest
 import torch
 
