@@ -594,3 +594,19 @@ def test_linear_nobias_is_x_wT(ops, dtype, tol):
         assert y.shape == (32, 640) and oracle.rel_err(y.float().cpu().numpy(), ref.cpu().numpy()) <= tol
     with pytest.raises(RuntimeError):
         ops.linear_nobias(x, w[:, :100].contiguous())
+
+
+def test_sdpa_long_prefill_rows_match_decode(ops):
+    """Full-size property: at 16384 tokens (128 key tiles per query block, both query tiles of a CTA, the
+    heaviest-first block order) every sampled causal row equals decode attention of that query over its
+    prefix of the same K / V."""
+    g = torch.Generator(device="cuda").manual_seed(77)
+    s = 16384
+    q = torch.randn((s, 16, 128), generator=g, device="cuda").half()
+    k = (0.5 * torch.randn((s, 8, 128), generator=g, device="cuda")).half()
+    v = (0.5 * torch.randn((s, 8, 128), generator=g, device="cuda")).half()
+    full = ops.scaled_dot_product_attention(q, k, v, True)
+    for t in (0, 1, 127, 128, 255, 256, 383, 4095, 8191, 8192, 16255, 16383):
+        row = ops.gqa_decode_attention(q[t : t + 1].contiguous(), k[: t + 1].contiguous(), v[: t + 1].contiguous())
+        assert_close(host(full[t : t + 1]), host(row), 2e-3)
+    assert ops.last_error() == 0
