@@ -610,3 +610,19 @@ def test_sdpa_long_prefill_rows_match_decode(ops):
         row = ops.gqa_decode_attention(q[t : t + 1].contiguous(), k[: t + 1].contiguous(), v[: t + 1].contiguous())
         assert_close(host(full[t : t + 1]), host(row), 2e-3)
     assert ops.last_error() == 0
+
+
+@pytest.mark.parametrize("d", [128, 64])
+def test_sdpa_tiled_long_rows_match_decode(ops, d):
+    """The tiled FMA prefill kernel at 3000 tokens in FLOAT32 (both CTA shapes: 128 virtual rows at
+    head_dim 128, and the same at 64): sampled causal rows against decode attention over their prefixes."""
+    g = torch.Generator(device="cuda").manual_seed(78 + d)
+    s = 3000
+    q = torch.randn((s, 16, d), generator=g, device="cuda")
+    k = torch.randn((s, 8, d), generator=g, device="cuda")
+    v = torch.randn((s, 8, d), generator=g, device="cuda")
+    full = ops.scaled_dot_product_attention(q, k, v, True)
+    for t in (0, 31, 32, 63, 64, 127, 1000, 2047, 2048, 2999):
+        row = ops.gqa_decode_attention(q[t : t + 1].contiguous(), k[: t + 1].contiguous(), v[: t + 1].contiguous())
+        assert_close(host(full[t : t + 1]), host(row), 2e-5)
+    assert ops.last_error() == 0
