@@ -16,6 +16,9 @@ _vp, _i, _i64, _sz, _f = C.c_void_p, C.c_int, C.c_int64, C.c_size_t, C.c_float
 SIGNATURES = {
     "axb200_version": (C.c_char_p, []),
     "axb200_last_error": (C.c_uint, []),
+    "axb200_set_wait_limit_ns": (_i, [C.c_uint64]),
+    "axb200_set_fused_merge": (_i, [_i]),
+    "axb200_gqa_chunk_plan": (_i, [_vp, _i, _i, _i, _i, _i64, _vp, _vp, _vp, _vp]),
     "axb200_profile_enable": (_i, [_i]),
     "axb200_profile_collect": (_i, [C.POINTER(C.c_double), C.POINTER(C.c_int)]),
     "axb200_gqa_workspace_bytes": (_sz, [_i, _i, _i, _i, _i64, _i]),
@@ -49,6 +52,7 @@ SIGNATURES = {
     "axb200_kv_arena_destroy": (_i, [_vp]),
     "axb200_kv_arena_alloc_seq": (_i, [_vp, _i64, C.POINTER(_i)]),
     "axb200_kv_arena_reserve": (_i, [_vp, _i, _i64]),
+    "axb200_kv_arena_shuffle_free": (_i, [_vp, C.c_uint64]),
     "axb200_kv_arena_free_seq": (_i, [_vp, _i, _vp]),
     "axb200_kv_arena_sync": (_i, [_vp, _vp]),
     "axb200_kv_arena_stats": (_i, [_vp, C.POINTER(_i64), C.POINTER(_i64), C.POINTER(_i64), C.POINTER(_i64)]),
@@ -68,6 +72,7 @@ SIGNATURES = {
     "axb200_embedding": (_i, [_vp, _i, _vp, _vp, _i64, _i64, _i, _i, _vp]),
     "axb200_argmax_last_dim": (_i, [_vp, _vp, _i64, _i, _i, _vp]),
     "axb200_linear_nobias": (_i, [_vp, _vp, _vp, _i64, _i64, _i64, _i, _vp]),
+    "axb200_randn": (_i, [_vp, _i64, _i, _f, _f, C.c_uint64, _vp]),
     "axb200_cast": (_i, [_vp, _i, _vp, _i, _i64, _vp]),
     "axb200_concat": (_i, [_vp, _vp, _vp, _i64, _sz, _sz, _vp]),
 }

@@ -47,10 +47,12 @@ inline int launch_status() {
 }
 
 // ---- bounded waiting ---------------------------------------------------------------------
-// Every spin in these kernels is limited: a waiter that has polled for kWaitNanos of wall time
+// Every spin in these kernels is limited: a waiter that has polled for the wait limit of wall time
 // records AXB200_ERR_WAIT_TIMEOUT, raises the CTA's abort flag and the kernel winds down
-// instead of hanging the GPU.
-constexpr unsigned long long kWaitNanos = 2000000000ull;  // 2 s
+// instead of hanging the GPU.  The limit is a host-side setting (axb200_set_wait_limit_ns, 2 s by
+// default) that the launchers pass to their kernels by value.
+constexpr unsigned long long kWaitNanos = 2000000000ull;  // 2 s, the default limit
+unsigned long long wait_limit_ns();                        // defined beside axb200_set_wait_limit_ns
 
 __device__ __forceinline__ unsigned long long global_timer_ns() {
   unsigned long long t;
@@ -98,14 +100,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 // Waits for the phase with the given parity to complete, or until the time limit or the
 // CTA's abort flag ends the wait.  Returns false when it gave up.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity,
-                                                  volatile int *abort_flag) {
+                                                  volatile int *abort_flag,
+                                                  unsigned long long limit_ns = kWaitNanos) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = global_timer_ns();
   for (uint32_t spin = 1;; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((spin & 255u) == 0u) {
       if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > kWaitNanos) break;
+      if (global_timer_ns() - t0 > limit_ns) break;
     }
   }
   *abort_flag = 1;

@@ -17,6 +17,8 @@
 #include <math.h>
 #include <string.h>
 
+#include <algorithm>
+#include <map>
 #include <mutex>
 #include <set>
 #include <utility>
@@ -56,23 +58,353 @@ struct DecodeParams {
   const int32_t *block_table;
   const int32_t *seq_lens;  // device lengths, or null -> fixed_len
   int fixed_len;
-  int batch, hq, hkv, group;
+  int batch, hq, hkv, group, d;
   int page_tokens, max_blocks, num_pages;
   int chunk_tokens, max_chunks;
+  // balanced != 0: the problem fits one wave of CTAs, so the chunk length is chosen by every CTA from
+  // the lengths in device memory - the smallest one for which all sequences' chunks fit the `budget`
+  // CTAs a KV head has - and the grid is (budget, hkv): CTA x finds its (sequence, chunk) by a prefix
+  // sum of the chunk counts.  Every CTA of the wave then streams about the same number of bytes.
+  int balanced, budget;
   float scale;  // 1/sqrt(d)
-  int write_final;  // max_chunks == 1: normalise and write `out` directly
   int window;       // > 0: only the last `window` tokens of each sequence are visible (sliding window)
   int causal_rows;  // rows are the queries of one sequence: row b sees min(b + 1, fixed_len) keys
+  // arrival_region >= 0: the CTA that finishes a (sequence, KV head) last merges its chunk partials and
+  // writes the result itself (no combine kernel); the arrival counters are that region of g_arrival.
+  // direct_ok: a sequence with a single chunk is normalised and written by its CTA, no partial.
+  int arrival_region, direct_ok;
+  unsigned long long wait_ns;  // limit of every bounded wait in the launch
 };
 
-__device__ __forceinline__ int seq_len_of(const DecodeParams &p, int b) {
+// Peers of a launch whose result goes to other GPUs' memory (KV heads sharded, or one sequence's
+// tokens spread over the GPUs).  world == 0: single GPU, the result goes to p.out.
+constexpr int kMaxPeers = 8;
+struct GatherParams {
+  void *peer_out[kMaxPeers];           // each rank's gathered buffer for this call's slot
+  unsigned int *peer_flags[kMaxPeers]; // each rank's flag array [world]; entry r = rank r's generation
+  unsigned int *local_state;           // [0] items finished in this call, [1] this rank's generation
+  int world, rank, hq_total;
+  int mode;  // 0: all-gather of head outputs; 1: context-parallel exchange of (O, m, l) records
+};
+
+// Arrival counters of the fused merge: kArrivalRegions regions of kArrivalSlots counters, one counter
+// per (sequence, KV head) of a launch.  Zero when the library is loaded; the CTA that completes a
+// count resets it, so every launch finds and leaves zeros.  Launches that may overlap on the GPU use
+// different regions (the host assigns a region per workspace pointer).
+constexpr int kArrivalRegions = 64, kArrivalSlots = 4096;
+static __device__ unsigned int g_arrival[kArrivalRegions * kArrivalSlots];
+
+__global__ void zero_arrival_kernel() {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < kArrivalRegions * kArrivalSlots;
+       i += gridDim.x * blockDim.x)
+    g_arrival[i] = 0u;
+}
+
+__device__ __forceinline__ int seq_len_raw(const DecodeParams &p, int b) {
   if (p.seq_lens) return p.seq_lens[b];
   return p.causal_rows ? min(b + 1, p.fixed_len) : p.fixed_len;
+}
+
+// Tokens a launch can reach in one sequence: what its pages hold and, with a host-planned chunk
+// length, what the grid's chunks cover.
+__device__ __forceinline__ int covered_tokens(const DecodeParams &p) {
+  long long cover = p.seq_lens ? (long long)p.max_blocks * p.page_tokens : (long long)p.fixed_len;
+  if (!p.balanced) cover = min(cover, (long long)p.max_chunks * p.chunk_tokens);
+  return (int)min(cover, (long long)INT32_MAX - 4096);
+}
+
+// Length of sequence b as the launch sees it.  A length beyond what the launch covers (the host's
+// bound was too small, or the length is corrupt) is cut there and AXB200_ERR_CAPACITY is recorded.
+__device__ __forceinline__ int seq_len_of(const DecodeParams &p, int b) {
+  const int L = seq_len_raw(p, b), cover = covered_tokens(p);
+  if (L > cover) {
+    atomicOr(&g_error_word, AXB200_ERR_CAPACITY);
+    return cover;
+  }
+  return L < 0 ? 0 : L;
 }
 
 // First visible token of a sequence of length L: 0, or L - window under a sliding window.
 __device__ __forceinline__ int first_visible(const DecodeParams &p, int L) {
   return (p.window > 0 && L > p.window) ? L - p.window : 0;
+}
+
+// ---- which (sequence, chunk) a CTA works on -----------------------------------------------------
+constexpr int kMaxBalancedBatch = 320;  // sequences a balanced launch can have (148 SMs x 2 CTAs)
+constexpr int kMinChunkTiles = 4;       // a chunk is at least 256 tokens
+constexpr int kPlanWords = kMaxBalancedBatch + 4;
+
+struct CtaWork {
+  int b, chunk;  // sequence and chunk of this CTA
+  int L;         // the sequence's length
+  int ct;        // the sequence's chunk length in tokens (a multiple of 64)
+  int n;         // the sequence's chunk count (>= 1: chunk 0 of an empty sequence writes the zero row)
+};
+
+__host__ __device__ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// Chunk count of a sequence of `tiles` 64-token tiles under chunk length `c` tiles.
+__host__ __device__ inline int chunks_at(int tiles, int c) { return tiles <= c ? 1 : ceil_div(tiles, c); }
+
+// Chunk length (tokens) and count of one sequence once the launch's chunk length c is known: the
+// sequence's tiles are spread evenly over its ceil(tiles / c) chunks.
+__host__ __device__ inline void sequence_chunks(int L, int c, int *ct, int *n) {
+  const int tiles = ceil_div(L, 64);
+  const int n0 = chunks_at(tiles, c);
+  const int per = tiles > 0 ? ceil_div(tiles, n0) : 1;
+  *ct = per * 64;
+  *n = tiles > 0 ? ceil_div(tiles, per) : 1;
+}
+
+// Smallest chunk length (in tiles, >= kMinChunkTiles) for which the sequences' chunks fit `budget`
+// CTAs with at most max_chunks per sequence - host-side statement of what the CTAs compute.
+inline int balanced_chunk_tiles_host(const int *lens, int batch, int budget, int max_chunks) {
+  int hi = kMinChunkTiles;
+  for (int i = 0; i < batch; ++i) hi = std::max(hi, ceil_div(std::max(lens[i], 0), 64));
+  int lo = kMinChunkTiles;
+  while (lo < hi) {
+    const int mid = (lo + hi) / 2;
+    long long sum = 0;
+    int most = 0;
+    for (int i = 0; i < batch; ++i) {
+      const int n = chunks_at(ceil_div(std::max(lens[i], 0), 64), mid);
+      sum += n;
+      most = std::max(most, n);
+    }
+    if (sum <= budget && most <= max_chunks) hi = mid; else lo = mid + 1;
+  }
+  return lo;
+}
+
+// The same search by warp 0 of a CTA over the lengths staged in s_plan[0 .. batch); the result is
+// left in s_plan[kMaxBalancedBatch].  All threads of the CTA call it (two __syncthreads).
+__device__ __forceinline__ int balanced_chunk_tiles(const DecodeParams &p, int *s_plan) {
+  for (int i = threadIdx.x; i < p.batch; i += blockDim.x) s_plan[i] = seq_len_of(p, i);
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    int hi = kMinChunkTiles;
+    for (int i = lane; i < p.batch; i += 32) hi = max(hi, ceil_div(s_plan[i], 64));
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, off));
+    int lo = kMinChunkTiles;
+    while (lo < hi) {  // uniform across the warp
+      const int mid = (lo + hi) >> 1;
+      int sum = 0, most = 0;
+      for (int i = lane; i < p.batch; i += 32) {
+        const int n = chunks_at(ceil_div(s_plan[i], 64), mid);
+        sum += n;
+        most = max(most, n);
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) {
+        sum += __shfl_xor_sync(0xffffffffu, sum, off);
+        most = max(most, __shfl_xor_sync(0xffffffffu, most, off));
+      }
+      if (sum <= p.budget && most <= p.max_chunks) hi = mid; else lo = mid + 1;
+    }
+    if (lane == 0) s_plan[kMaxBalancedBatch] = lo;
+  }
+  __syncthreads();
+  return s_plan[kMaxBalancedBatch];
+}
+
+// Fills `w` for this CTA; false when the CTA has nothing to do.  All threads call it.
+__device__ __forceinline__ bool cta_work(const DecodeParams &p, int *s_plan, CtaWork &w) {
+  if (!p.balanced) {
+    w.b = blockIdx.z;
+    w.chunk = blockIdx.x;
+    w.L = seq_len_of(p, w.b);
+    w.ct = p.chunk_tokens;
+    w.n = max(1, ceil_div(w.L, w.ct));
+    return w.chunk < w.n;
+  }
+  const int c = balanced_chunk_tiles(p, s_plan);
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x, x = blockIdx.x;
+    if (lane == 0) s_plan[kMaxBalancedBatch + 1] = -1;
+    __syncwarp();
+    int base = 0;
+    for (int i0 = 0; i0 < p.batch; i0 += 32) {  // prefix sum of the chunk counts, 32 sequences a step
+      const int i = i0 + lane;
+      const int n = i < p.batch ? chunks_at(ceil_div(s_plan[i], 64), c) : 0;
+      int incl = n;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += up;
+      }
+      const int excl = base + incl - n;
+      if (n > 0 && x >= excl && x < excl + n) {
+        s_plan[kMaxBalancedBatch + 1] = i;
+        s_plan[kMaxBalancedBatch + 2] = x - excl;
+      }
+      base += __shfl_sync(0xffffffffu, incl, 31);
+    }
+  }
+  __syncthreads();
+  w.b = s_plan[kMaxBalancedBatch + 1];
+  if (w.b < 0) return false;
+  w.chunk = s_plan[kMaxBalancedBatch + 2];
+  w.L = s_plan[w.b];
+  sequence_chunks(w.L, c, &w.ct, &w.n);
+  return w.chunk < w.n;
+}
+
+// Chunk length and count of sequence b for a kernel that merges (all threads call it).
+__device__ __forceinline__ void sequence_plan(const DecodeParams &p, int b, int *s_plan, int *L, int *ct, int *n) {
+  if (!p.balanced) {
+    *L = seq_len_of(p, b);
+    *ct = p.chunk_tokens;
+    *n = max(1, ceil_div(*L, *ct));
+    return;
+  }
+  const int c = balanced_chunk_tiles(p, s_plan);
+  *L = s_plan[b];
+  sequence_chunks(*L, c, ct, n);
+}
+
+// ---- the end of a (sequence, head): merge of the chunk partials and the final store ---------------
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int *p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned int *p, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Log-sum-exp merge of chunk partials [c0, n) of one (sequence, head) for output dim t: the
+// un-normalised value relative to the maximum M, and the sum Ls.  `dom` is the exponent domain of
+// the stored maxima.  Partials were written by other CTAs: read them past L1.
+__device__ __forceinline__ void merge_row(const DecodeParams &p, size_t base, int c0, int n, int t,
+                                          float dom, float &val, float &M, float &Ls) {
+  M = -INFINITY;
+  for (int c = c0; c < n; ++c) M = fmaxf(M, __ldcg(p.part_ml + (base + c) * 2));
+  val = 0.f;
+  Ls = 0.f;
+  for (int c = c0; c < n; ++c) {
+    const float m = __ldcg(p.part_ml + (base + c) * 2);
+    const float wgt = m == -INFINITY ? 0.f : exp2f((m - M) * dom);
+    Ls = fmaf(__ldcg(p.part_ml + (base + c) * 2 + 1), wgt, Ls);
+    val = fmaf(wgt, __ldcg(p.part_o + (base + c) * p.d + t), val);
+  }
+}
+
+// Final store of (sequence b, local head h), dim t.  val is un-normalised relative to the maximum M
+// with sum Ls (an empty sequence: 0, -inf, 0).  Single GPU: out = val / Ls.  Heads sharded: the row
+// goes into every rank's gathered buffer (batch, hq_total, d) at head rank*hq + h, plain stores over
+// NVLink to peer-mapped pointers.  Context parallel: the un-normalised record [O(d), m, l] goes into
+// every rank's record buffer (batch, hq, world, d + 2) at index `rank`.
+template <typename OutT>
+__device__ __forceinline__ void emit_final(const DecodeParams &p, const GatherParams &g, int b, int h,
+                                           int t, float val, float M, float Ls) {
+  if (g.world == 0) {
+    reinterpret_cast<OutT *>(p.out)[((size_t)b * p.hq + h) * p.d + t] =
+        static_cast<OutT>(Ls > 0.f ? val / Ls : 0.f);
+  } else if (g.mode == 0) {
+    const OutT v = static_cast<OutT>(Ls > 0.f ? val / Ls : 0.f);
+    const size_t at = ((size_t)b * g.hq_total + (size_t)g.rank * p.hq + h) * p.d + t;
+    for (int r = 0; r < g.world; ++r) reinterpret_cast<OutT *>(g.peer_out[r])[at] = v;
+  } else {
+    const size_t rec = (((size_t)b * p.hq + h) * g.world + g.rank) * (p.d + 2);
+    for (int r = 0; r < g.world; ++r) {
+      float *dst = reinterpret_cast<float *>(g.peer_out[r]) + rec;
+      dst[t] = val;
+      if (t == 0) {
+        dst[p.d] = M;
+        dst[p.d + 1] = Ls;
+      }
+    }
+  }
+}
+
+// Tail of a CTA that has stored a finished item into every peer's buffer.  Called by all `bar`
+// threads of the CTA (thread index tid): every thread fences its stores system-wide, the CTA counts
+// the item in, and the CTA that completes the launch's `total` items publishes this rank's new
+// generation to every peer and waits (bounded by wait_ns) until every peer's generation has arrived
+// here, so that when the kernel completes the local buffer is whole.  s_word: two shared words.
+template <typename Bar>
+__device__ __forceinline__ void publish_and_wait(const GatherParams &g, unsigned int total,
+                                                 unsigned long long wait_ns, int tid,
+                                                 volatile unsigned int *s_word, Bar bar) {
+  __threadfence_system();
+  bar();
+  if (tid == 0) {
+    const unsigned int last = atomicAdd(&g.local_state[0], 1u) == total - 1 ? 1u : 0u;
+    s_word[0] = last;
+    if (last) {
+      __threadfence_system();
+      const unsigned int gen = g.local_state[1] + 1;  // only the last CTA of a call touches the generation
+      g.local_state[0] = 0;
+      g.local_state[1] = gen;
+      s_word[1] = gen;
+    }
+  }
+  bar();
+  if (!s_word[0]) return;
+  const unsigned int gen = s_word[1];
+  if (tid < g.world) {
+    st_release_sys(g.peer_flags[tid] + g.rank, gen);
+    const unsigned int *flag = g.peer_flags[g.rank] + tid;
+    const unsigned long long t0 = global_timer_ns();
+    // generations only grow; the signed difference keeps the comparison right across wrap-around
+    while ((int)(ld_acquire_sys(flag) - gen) < 0) {
+      if (global_timer_ns() - t0 > wait_ns) {
+        atomicOr(&g_error_word, AXB200_ERR_WAIT_TIMEOUT);
+        break;
+      }
+    }
+  }
+}
+
+// What the `nthreads` compute threads of a split CTA do once the chunk's work is stored.  `direct`:
+// the sequence had a single visible chunk and the CTA has already emitted the final rows.  Otherwise
+// the partial is in the workspace: with arrival counters the CTA counts itself in and, when it is the
+// last of its (sequence, KV head), merges the partials of the group's heads and emits the rows;
+// without counters a combine kernel follows.  With peers, a finished item then joins the exchange.
+template <typename OutT, typename Bar>
+__device__ __forceinline__ void finish_item(const DecodeParams &p, const GatherParams &g,
+                                            const CtaWork &w, int hk, int c_first, bool direct,
+                                            float dom, int tid, int nthreads,
+                                            volatile unsigned int *s_word, Bar bar) {
+  if (!direct) {
+    if (p.arrival_region < 0) return;  // the combine kernel merges
+    __threadfence();
+    bar();
+    if (tid == 0) {
+      unsigned int *cnt = g_arrival + (size_t)p.arrival_region * kArrivalSlots + (size_t)w.b * p.hkv + hk;
+      const unsigned int expected = (unsigned int)(w.n - c_first);
+      const unsigned int last = atomicAdd(cnt, 1u) + 1 == expected ? 1u : 0u;
+      if (last) *cnt = 0u;  // every other CTA of the item has arrived: leave zero for the next launch
+      s_word[0] = last;
+    }
+    bar();
+    if (!s_word[0]) return;
+    __threadfence();
+    for (int r = 0; r < p.group; ++r) {
+      const int h = hk * p.group + r;
+      const size_t base = ((size_t)w.b * p.hq + h) * p.max_chunks;
+      for (int t = tid; t < p.d; t += nthreads) {
+        float val, M, Ls;
+        merge_row(p, base, c_first, w.n, t, dom, val, M, Ls);
+        emit_final<OutT>(p, g, w.b, h, t, val, M, Ls);
+      }
+    }
+  }
+  if (g.world) publish_and_wait(g, (unsigned int)(p.batch * p.hkv), p.wait_ns, tid, s_word, bar);
+}
+
+// An empty sequence: its one CTA (chunk 0) writes the zero rows.  Called by all threads of the CTA.
+template <typename OutT>
+__device__ __forceinline__ void emit_empty_item(const DecodeParams &p, const GatherParams &g, int b, int hk,
+                                                volatile unsigned int *s_word) {
+  if (p.arrival_region < 0 && !p.direct_ok) return;  // the combine kernel writes the zero rows
+  for (int r = 0; r < p.group; ++r)
+    for (int t = threadIdx.x; t < p.d; t += blockDim.x)
+      emit_final<OutT>(p, g, b, hk * p.group + r, t, 0.f, -INFINITY, 0.f);
+  if (g.world)
+    publish_and_wait(g, (unsigned int)(p.batch * p.hkv), p.wait_ns, threadIdx.x, s_word, [] { __syncthreads(); });
 }
 
 // ---- producer ---------------------------------------------------------------------------
@@ -108,7 +440,7 @@ __device__ __forceinline__ void produce_tiles(const CUtensorMap *tmK, const CUte
       tok_in_page = tok0 % p.page_tokens;
     }
     if (lane == 0) {
-      if (mbar_wait_bounded(&empty[s], phase ^ 1u, abort_flag)) {
+      if (mbar_wait_bounded(&empty[s], phase ^ 1u, abort_flag, p.wait_ns)) {
         mbar_arrive_expect_tx(&full[s], kStageBytes);
         uint8_t *st = stages + (size_t)s * kStageBytes;
 #pragma unroll
@@ -133,11 +465,13 @@ __device__ __forceinline__ void produce_tiles(const CUtensorMap *tmK, const CUte
 // ---- chunk epilogue shared by both dtypes ---------------------------------------------------
 // Consumer warps have written their per-warp (m, l, O) for each query head of the group into
 // shared memory; thread t owns output dim t.  m is in the exponent domain `dom` (so weights
-// are exp2((m_w - M) * dom)).
+// are exp2((m_w - M) * dom)).  direct: the chunk is the whole sequence - emit the final rows;
+// otherwise store the chunk's partial.
 template <typename OutT>
-__device__ __forceinline__ void finalize_chunk(const DecodeParams &p, const float *mO,
-                                               const float *mM, const float *mL, int b, int hk,
-                                               int chunk, int t, float dom) {
+__device__ __forceinline__ void finalize_chunk(const DecodeParams &p, const GatherParams &gp,
+                                               const float *mO, const float *mM, const float *mL,
+                                               int b, int hk, int chunk, int t, float dom,
+                                               bool direct) {
   for (int r = 0; r < p.group; ++r) {
     float M = -INFINITY;
 #pragma unroll
@@ -151,9 +485,8 @@ __device__ __forceinline__ void finalize_chunk(const DecodeParams &p, const floa
       acc += mO[(w * kMaxGroupMma + r) * kHeadDim + t] * wgt;
     }
     const int h = hk * p.group + r;
-    if (p.write_final) {
-      reinterpret_cast<OutT *>(p.out)[((size_t)b * p.hq + h) * kHeadDim + t] =
-          static_cast<OutT>(acc / L);
+    if (direct) {
+      emit_final<OutT>(p, gp, b, h, t, acc, M, L);
     } else {
       const size_t slot = ((size_t)b * p.hq + h) * p.max_chunks + chunk;
       p.part_o[slot * kHeadDim + t] = acc;
@@ -165,8 +498,8 @@ __device__ __forceinline__ void finalize_chunk(const DecodeParams &p, const floa
   }
 }
 
-// Shared-memory carve-up: [stages][full barriers][empty barriers][abort flag]; the merge
-// buffers alias the first two stages once the pipeline has drained.
+// Shared-memory carve-up: [stages][full barriers][empty barriers][abort flag, 3 words for the end
+// of the item]; the merge buffers alias the first two stages once the pipeline has drained.
 template <int kStages>
 struct SmemLayout {
   static constexpr int kBarOffset = kStages * kStageBytes;
@@ -188,25 +521,18 @@ __device__ __forceinline__ uint32_t swz_off(int row, int c16) {
 template <bool kPaged, int kStages, int kMinCtas>
 __global__ void __launch_bounds__(kThreads, kMinCtas)
 gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
-                     const __grid_constant__ CUtensorMap tmV, const DecodeParams p) {
+                     const __grid_constant__ CUtensorMap tmV, const DecodeParams p,
+                     const GatherParams gp) {
   extern __shared__ uint8_t smem_raw[];
+  __shared__ int s_plan[kPlanWords];
   uint8_t *smem = align_1024(smem_raw);
   uint64_t *full = reinterpret_cast<uint64_t *>(smem + SmemLayout<kStages>::kBarOffset);
   uint64_t *empty = full + kStages;
   volatile int *abort_flag = reinterpret_cast<volatile int *>(empty + kStages);
-
-  const int chunk = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
-  const int L = seq_len_of(p, b);
-  const int first = first_visible(p, L);
-  int start = chunk * p.chunk_tokens;
-  if (start >= L) return;
-  const int end = min(L, start + p.chunk_tokens);
-  if (end <= first) return;  // the whole chunk lies before the window
-  if (start < first) start = first / kTileTokensF16 * kTileTokensF16;  // skip whole tiles before it
-  const int ntiles = (end - start + kTileTokensF16 - 1) / kTileTokensF16;
+  volatile unsigned int *s_word = reinterpret_cast<volatile unsigned int *>(abort_flag + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (threadIdx.x == 0) {
+  if (threadIdx.x == kConsumerThreads) {  // the producer's first lane, while warp 0 plans
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], kConsumerWarps);
@@ -214,7 +540,23 @@ gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
     *abort_flag = 0;
     mbar_fence_init();
   }
+  CtaWork w;
+  const bool active = cta_work(p, s_plan, w);
   __syncthreads();
+  if (!active) return;
+  const int chunk = w.chunk, hk = blockIdx.y, b = w.b, L = w.L;
+  if (L == 0) {
+    emit_empty_item<__half>(p, gp, b, hk, s_word);
+    return;
+  }
+  const int first = first_visible(p, L);
+  const int c_first = first / w.ct;  // chunks before it lie wholly outside the window
+  int start = chunk * w.ct;
+  const int end = min(L, start + w.ct);
+  if (end <= first) return;  // the whole chunk lies before the window
+  if (start < first) start = first / kTileTokensF16 * kTileTokensF16;  // skip whole tiles before it
+  const int ntiles = (end - start + kTileTokensF16 - 1) / kTileTokensF16;
+  const bool direct = p.direct_ok && w.n - c_first == 1;
 
   if (warp == kConsumerWarps) {
     if (lane == 0) {
@@ -265,7 +607,7 @@ gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
   for (int i = 0; i < ntiles && ok; ++i) {
     const int s = i % kStages;
     const uint32_t phase = (i / kStages) & 1;
-    ok = mbar_wait_bounded(&full[s], phase, abort_flag);
+    ok = mbar_wait_bounded(&full[s], phase, abort_flag, p.wait_ns);
     if (!ok) break;
     const uint32_t kbase = smem_u32(smem + (size_t)s * kStageBytes);
     const uint32_t vbase = kbase + kStageBytes / 2;
@@ -390,7 +732,9 @@ gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
     }
   }
   named_bar_sync(1, kConsumerThreads);
-  finalize_chunk<__half>(p, mO, mM, mL, b, hk, chunk, threadIdx.x, 1.0f);
+  finalize_chunk<__half>(p, gp, mO, mM, mL, b, hk, chunk, threadIdx.x, 1.0f, direct);
+  finish_item<__half>(p, gp, w, hk, c_first, direct, 1.0f, threadIdx.x, kConsumerThreads, s_word,
+                      [] { named_bar_sync(1, kConsumerThreads); });
 }
 
 // ---- fp32 split kernel: FMA on unswizzled tiles ----------------------------------------------
@@ -398,25 +742,18 @@ gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
 template <bool kPaged, int kStages, int kGroup>
 __global__ void __launch_bounds__(kThreads, 2)
 gqa_split_f32_kernel(const __grid_constant__ CUtensorMap tmK,
-                     const __grid_constant__ CUtensorMap tmV, const DecodeParams p) {
+                     const __grid_constant__ CUtensorMap tmV, const DecodeParams p,
+                     const GatherParams gp) {
   extern __shared__ uint8_t smem_raw[];
+  __shared__ int s_plan[kPlanWords];
   uint8_t *smem = align_1024(smem_raw);
   uint64_t *full = reinterpret_cast<uint64_t *>(smem + SmemLayout<kStages>::kBarOffset);
   uint64_t *empty = full + kStages;
   volatile int *abort_flag = reinterpret_cast<volatile int *>(empty + kStages);
-
-  const int chunk = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
-  const int L = seq_len_of(p, b);
-  const int first = first_visible(p, L);
-  int start = chunk * p.chunk_tokens;
-  if (start >= L) return;
-  const int end = min(L, start + p.chunk_tokens);
-  if (end <= first) return;  // the whole chunk lies before the window
-  if (start < first) start = first / kTileTokensF32 * kTileTokensF32;  // skip whole tiles before it
-  const int ntiles = (end - start + kTileTokensF32 - 1) / kTileTokensF32;
+  volatile unsigned int *s_word = reinterpret_cast<volatile unsigned int *>(abort_flag + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (threadIdx.x == 0) {
+  if (threadIdx.x == kConsumerThreads) {  // the producer's first lane, while warp 0 plans
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], kConsumerWarps);
@@ -424,7 +761,23 @@ gqa_split_f32_kernel(const __grid_constant__ CUtensorMap tmK,
     *abort_flag = 0;
     mbar_fence_init();
   }
+  CtaWork w;
+  const bool active = cta_work(p, s_plan, w);
   __syncthreads();
+  if (!active) return;
+  const int chunk = w.chunk, hk = blockIdx.y, b = w.b, L = w.L;
+  if (L == 0) {
+    emit_empty_item<float>(p, gp, b, hk, s_word);
+    return;
+  }
+  const int first = first_visible(p, L);
+  const int c_first = first / w.ct;  // chunks before it lie wholly outside the window
+  int start = chunk * w.ct;
+  const int end = min(L, start + w.ct);
+  if (end <= first) return;  // the whole chunk lies before the window
+  if (start < first) start = first / kTileTokensF32 * kTileTokensF32;  // skip whole tiles before it
+  const int ntiles = (end - start + kTileTokensF32 - 1) / kTileTokensF32;
+  const bool direct = p.direct_ok && w.n - c_first == 1;
 
   if (warp == kConsumerWarps) {
     if (lane == 0) {
@@ -457,7 +810,7 @@ gqa_split_f32_kernel(const __grid_constant__ CUtensorMap tmK,
   for (int i = 0; i < ntiles && ok; ++i) {
     const int s = i % kStages;
     const uint32_t phase = (i / kStages) & 1;
-    ok = mbar_wait_bounded(&full[s], phase, abort_flag);
+    ok = mbar_wait_bounded(&full[s], phase, abort_flag, p.wait_ns);
     if (!ok) break;
     const float *Ks = reinterpret_cast<const float *>(smem + (size_t)s * kStageBytes);
     const float *Vs = Ks + kTileTokensF32 * kHeadDim;
@@ -541,7 +894,9 @@ gqa_split_f32_kernel(const __grid_constant__ CUtensorMap tmK,
     }
   }
   named_bar_sync(1, kConsumerThreads);
-  finalize_chunk<float>(p, mO, mM, mL, b, hk, chunk, threadIdx.x, sl2);
+  finalize_chunk<float>(p, gp, mO, mM, mL, b, hk, chunk, threadIdx.x, sl2, direct);
+  finish_item<float>(p, gp, w, hk, c_first, direct, sl2, threadIdx.x, kConsumerThreads, s_word,
+                     [] { named_bar_sync(1, kConsumerThreads); });
 }
 
 // ---- generic split kernel: any head_dim <= 256, any group, any alignment ---------------------------
@@ -644,16 +999,26 @@ __device__ __forceinline__ void gen_pv(const float *Vs, const float *p_s, const 
 
 template <typename T, bool kPaged>
 __global__ void __launch_bounds__(kGenThreads, 3)
-gqa_split_generic_kernel(const T *k, const T *v, const DecodeParams p, int d) {
+gqa_split_generic_kernel(const T *k, const T *v, const DecodeParams p, const GatherParams gp, int d) {
   extern __shared__ float gsm[];
-  const int chunk = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
-  const int L = seq_len_of(p, b);
+  __shared__ int s_plan[kPlanWords];
+  __shared__ unsigned int s_word[2];
+  CtaWork w;
+  const bool active = cta_work(p, s_plan, w);
+  __syncthreads();
+  if (!active) return;
+  const int chunk = w.chunk, hk = blockIdx.y, b = w.b, L = w.L;
+  if (L == 0) {
+    emit_empty_item<T>(p, gp, b, hk, s_word);
+    return;
+  }
   const int first = first_visible(p, L);
-  int start = chunk * p.chunk_tokens;
-  if (start >= L) return;
-  const int end = min(L, start + p.chunk_tokens);
+  const int c_first = first / w.ct;  // chunks before it lie wholly outside the window
+  int start = chunk * w.ct;
+  const int end = min(L, start + w.ct);
   if (end <= first) return;
   if (start < first) start = first;
+  const bool direct = p.direct_ok && w.n - c_first == 1;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int tt = gen_tile_tokens(d), gb_max = gen_head_batch(d, p.group), dp = gen_row_stride(d);
   float *Ks = gsm, *Vs = Ks + tt * dp, *q_s = Vs + tt * dp, *p_s = q_s + ((gb_max * d + 3) & ~3);  // all 16-byte aligned
@@ -798,8 +1163,8 @@ gqa_split_generic_kernel(const T *k, const T *v, const DecodeParams p, int d) {
     if (pv_active) {
       auto emit = [&](int r, int c, float a) {
         const int h = hk * p.group + h0 + r;
-        if (p.write_final) {
-          reinterpret_cast<T *>(p.out)[((size_t)b * p.hq + h) * d + c] = static_cast<T>(a / l_s[r]);
+        if (direct) {
+          emit_final<T>(p, gp, b, h, c, a, m_s[r], l_s[r]);
         } else {
           const size_t slot = ((size_t)b * p.hq + h) * p.max_chunks + chunk;
           p.part_o[slot * d + c] = a;
@@ -821,195 +1186,46 @@ gqa_split_generic_kernel(const T *k, const T *v, const DecodeParams p, int d) {
         }
       }
     }
-    if (!p.write_final && tid < gb) {
+    if (!direct && tid < gb) {
       const size_t slot = ((size_t)b * p.hq + hk * p.group + h0 + tid) * p.max_chunks + chunk;
       p.part_ml[slot * 2 + 0] = m_s[tid];
       p.part_ml[slot * 2 + 1] = l_s[tid];
     }
   }
-}
-
-// Merge weights of a (sequence, head)'s chunk partials c0..n-1 (chunks before c0 lie wholly before a
-// sliding window and were never written), computed once by the CTA: w_c = 2^((m_c - M) * dom) /
-// sum_c l_c 2^((m_c - M) * dom), left in s_w[c0..n).  n <= kMaxChunks.
-__device__ __forceinline__ void combine_weights(const float *part_ml, size_t base, int c0, int n,
-                                                float dom, float *s_w, float *s_red) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  float m_loc = -INFINITY;
-  for (int c = c0 + threadIdx.x; c < n; c += blockDim.x) m_loc = fmaxf(m_loc, part_ml[(base + c) * 2]);
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) m_loc = fmaxf(m_loc, __shfl_xor_sync(0xffffffffu, m_loc, off));
-  if (lane == 0) s_red[warp] = m_loc;
-  __syncthreads();
-  float M = s_red[0];
-  for (int w = 1; w < nwarps; ++w) M = fmaxf(M, s_red[w]);
-  __syncthreads();
-  float l_loc = 0.f;
-  for (int c = c0 + threadIdx.x; c < n; c += blockDim.x) {
-    const float w = exp2f((part_ml[(base + c) * 2] - M) * dom);
-    s_w[c] = w;
-    l_loc = fmaf(part_ml[(base + c) * 2 + 1], w, l_loc);
-  }
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) l_loc += __shfl_xor_sync(0xffffffffu, l_loc, off);
-  if (lane == 0) s_red[warp] = l_loc;
-  __syncthreads();
-  float Lsum = 0.f;
-  for (int w = 0; w < nwarps; ++w) Lsum += s_red[w];
-  const float inv = 1.0f / Lsum;
-  for (int c = c0 + threadIdx.x; c < n; c += blockDim.x) s_w[c] *= inv;
-  __syncthreads();
+  finish_item<T>(p, gp, w, hk, c_first, direct, dom, tid, kGenThreads, s_word, [] { __syncthreads(); });
 }
 
 // ---- combine: log-sum-exp merge of a sequence's chunk partials --------------------------------
-// One CTA per (sequence, query head); thread t owns output dims t, t+blockDim, ...  `dom` is the
-// exponent domain of the stored maxima.  A sequence of length 0 yields zeros.
+// The separate form of the merge, used when a launch has no arrival counters (the fused merge is
+// switched off, no counter region is free, or the launch has more items than a region holds).  One
+// CTA per (sequence, query head); thread t owns output dims t, t + 128.  `dom` is the exponent domain
+// of the stored maxima.  Same arithmetic, through the same functions, as the fused merge.  With
+// peers, every CTA is an item of the exchange.
 template <typename OutT>
 __global__ void __launch_bounds__(128)
-gqa_combine_kernel(const DecodeParams p, int d, float dom) {
+gqa_combine_kernel(const DecodeParams p, const GatherParams gp, float dom) {
+  __shared__ int s_plan[kPlanWords];
+  __shared__ unsigned int s_word[2];
   const int h = blockIdx.x, b = blockIdx.y;
-  const int L = seq_len_of(p, b);
-  int n = (L + p.chunk_tokens - 1) / p.chunk_tokens;
-  n = max(0, min(n, p.max_chunks));
+  int L, ct, n;
+  sequence_plan(p, b, s_plan, &L, &ct, &n);
   const size_t base = ((size_t)b * p.hq + h) * p.max_chunks;
-  OutT *out = reinterpret_cast<OutT *>(p.out) + ((size_t)b * p.hq + h) * d;
-  if (n == 0) {
-    for (int c = threadIdx.x; c < d; c += blockDim.x) out[c] = static_cast<OutT>(0.f);
-    return;
+  const int c_first = first_visible(p, L) / ct;  // first chunk that holds visible tokens
+  for (int t = threadIdx.x; t < p.d; t += blockDim.x) {
+    float val = 0.f, M = -INFINITY, Ls = 0.f;
+    if (L > 0) merge_row(p, base, c_first, n, t, dom, val, M, Ls);
+    emit_final<OutT>(p, gp, b, h, t, val, M, Ls);
   }
-  __shared__ float s_w[kMaxChunks], s_red[4];
-  const int cf = first_visible(p, L) / p.chunk_tokens;  // first chunk that holds visible tokens
-  combine_weights(p.part_ml, base, cf, n, dom, s_w, s_red);
-  for (int c0 = threadIdx.x; c0 < d; c0 += blockDim.x) {
-    float acc = 0.f;
-    for (int c = cf; c < n; ++c) acc = fmaf(s_w[c], p.part_o[(base + c) * d + c0], acc);
-    out[c0] = static_cast<OutT>(acc);
-  }
-}
-
-// ---- combine fused with the all-gather of per-head outputs (KV heads sharded across GPUs) ----------
-// Each rank attends its own heads; before the output projection every rank needs all heads.  This
-// kernel is the combine kernel with its store redirected: the merged row of (sequence b, local head
-// h) is written straight into every rank's gathered buffer (batch, hq_total, d) at head
-// rank*hq + h, over NVLink with plain stores to peer-mapped pointers.  The last CTA to finish then
-// publishes this rank's generation number in every peer's flag array and waits (bounded) until all
-// peers have published theirs, so when the kernel completes the local gathered buffer is whole
-// and the next kernel in the stream may read it.  Only local memory is ever read.
-constexpr int kMaxPeers = 8;
-struct GatherParams {
-  void *peer_out[kMaxPeers];           // each rank's gathered buffer for this call's slot
-  unsigned int *peer_flags[kMaxPeers]; // each rank's flag array [world]; entry r = rank r's generation
-  unsigned int *local_state;           // [0] CTAs finished in this call, [1] this rank's generation
-  int world, rank, hq_total;
-  int mode;  // 0: all-gather of head outputs; 1: context-parallel exchange of (O, m, l) records
-};
-
-__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int *p) {
-  unsigned int v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_release_sys(unsigned int *p, unsigned int v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-
-// Tail of a kernel that has stored into every peer's buffer: every thread fences its stores
-// system-wide, the CTA counts itself in, and the last CTA of the call publishes this rank's new
-// generation to every peer and waits (bounded) until every peer's generation has arrived here.
-__device__ __forceinline__ void publish_and_wait(const GatherParams &g) {
-  __shared__ int s_last;
-  __shared__ unsigned int s_gen;
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    const unsigned int total = gridDim.x * gridDim.y;
-    s_last = atomicAdd(&g.local_state[0], 1u) == total - 1;
-    if (s_last) {
-      __threadfence_system();
-      s_gen = g.local_state[1] + 1;  // only the last CTA of a call touches the generation
-      g.local_state[0] = 0;
-      g.local_state[1] = s_gen;
-    }
-  }
-  __syncthreads();
-  if (!s_last) return;
-  const unsigned int gen = s_gen;
-  if (threadIdx.x < g.world) {
-    st_release_sys(g.peer_flags[threadIdx.x] + g.rank, gen);
-    const unsigned int *flag = g.peer_flags[g.rank] + threadIdx.x;
-    const unsigned long long t0 = global_timer_ns();
-    // generations only grow; the signed difference keeps the comparison right across wrap-around
-    while ((int)(ld_acquire_sys(flag) - gen) < 0) {
-      if (global_timer_ns() - t0 > kWaitNanos) {
-        atomicOr(&g_error_word, AXB200_ERR_WAIT_TIMEOUT);
-        break;
-      }
-    }
-  }
-}
-
-template <typename OutT>
-__global__ void __launch_bounds__(128)
-gqa_combine_gather_kernel(const DecodeParams p, const GatherParams g, int d, float dom) {
-  const int h = blockIdx.x, b = blockIdx.y;
-  const int L = seq_len_of(p, b);
-  int n = (L + p.chunk_tokens - 1) / p.chunk_tokens;
-  n = max(0, min(n, p.max_chunks));
-  const size_t base = ((size_t)b * p.hq + h) * p.max_chunks;
-  const size_t row = ((size_t)b * g.hq_total + (size_t)g.rank * p.hq + h) * d;
-  __shared__ float s_w[kMaxChunks], s_red[4];
-  const int cf = first_visible(p, L) / p.chunk_tokens;  // first chunk that holds visible tokens
-  if (n > 0) combine_weights(p.part_ml, base, cf, n, dom, s_w, s_red);
-  for (int c0 = threadIdx.x; c0 < d; c0 += blockDim.x) {
-    float acc = 0.f;
-    for (int c = cf; c < n; ++c) acc = fmaf(s_w[c], p.part_o[(base + c) * d + c0], acc);
-    const OutT val = static_cast<OutT>(acc);
-    for (int r = 0; r < g.world; ++r) reinterpret_cast<OutT *>(g.peer_out[r])[row + c0] = val;
-  }
-  publish_and_wait(g);
+  if (gp.world)
+    publish_and_wait(gp, gridDim.x * gridDim.y, p.wait_ns, threadIdx.x, s_word, [] { __syncthreads(); });
 }
 
 // ---- context-parallel decode: one sequence's tokens spread over the GPUs --------------------------
 // Each rank caches a share of every sequence's tokens (softmax does not care which) and attends its
-// share.  Exchange kernel: merges the local chunk partials of (sequence b, head h) WITHOUT normalising
-// - O_loc = sum_c w_c O_c, l_loc = sum_c w_c l_c relative to the local maximum m_loc - and stores the
-// record [O_loc(d), m_loc, l_loc] into every rank's record buffer (batch, hq, world, d + 2) at index
-// `rank`, then exchanges generation flags as above.  Merge kernel (next launch, local reads only):
-// the log-sum-exp merge of the `world` records gives the same output on every rank.
-template <typename OutT>
-__global__ void __launch_bounds__(128)
-gqa_combine_exchange_kernel(const DecodeParams p, const GatherParams g, int d, float dom) {
-  const int h = blockIdx.x, b = blockIdx.y;
-  const int L = seq_len_of(p, b);
-  int n = (L + p.chunk_tokens - 1) / p.chunk_tokens;
-  n = max(0, min(n, p.max_chunks));
-  const size_t base = ((size_t)b * p.hq + h) * p.max_chunks;
-  const size_t rec = (((size_t)b * p.hq + h) * g.world + g.rank) * (d + 2);
-  __shared__ float s_w[kMaxChunks], s_red[4];
-  const int cf = first_visible(p, L) / p.chunk_tokens;
-  float m_loc = -INFINITY, l_loc = 0.f;
-  if (n > cf) {
-    // un-normalised weights: w_c = 2^((m_c - M) dom); combine_weights divides by l, so undo it
-    combine_weights(p.part_ml, base, cf, n, dom, s_w, s_red);
-    for (int c = cf; c < n; ++c) m_loc = fmaxf(m_loc, p.part_ml[(base + c) * 2]);
-    for (int c = cf; c < n; ++c)
-      l_loc = fmaf(p.part_ml[(base + c) * 2 + 1], exp2f((p.part_ml[(base + c) * 2] - m_loc) * dom), l_loc);
-  }
-  for (int c0 = threadIdx.x; c0 < d; c0 += blockDim.x) {
-    float acc = 0.f;
-    for (int c = cf; c < n; ++c) acc = fmaf(s_w[c], p.part_o[(base + c) * d + c0], acc);
-    acc *= l_loc;  // back to the un-normalised sum
-    for (int r = 0; r < g.world; ++r) reinterpret_cast<float *>(g.peer_out[r])[rec + c0] = acc;
-  }
-  if (threadIdx.x == 0) {
-    for (int r = 0; r < g.world; ++r) {
-      reinterpret_cast<float *>(g.peer_out[r])[rec + d] = m_loc;
-      reinterpret_cast<float *>(g.peer_out[r])[rec + d + 1] = l_loc;
-    }
-  }
-  publish_and_wait(g);
-}
-
+// share; the end of each (sequence, head) stores the un-normalised record [O_loc(d), m_loc, l_loc]
+// into every rank's record buffer (emit_final) and the ranks exchange generation flags.  Merge kernel
+// (next launch, local reads only): the log-sum-exp merge of the `world` records gives the same output
+// on every rank.
 template <typename OutT>
 __global__ void __launch_bounds__(128)
 cp_merge_kernel(const float *records, OutT *out, int world, int d, float dom) {
@@ -1097,13 +1313,24 @@ bool make_map(CUtensorMap *map, const void *base, int dtype, bool paged, int d, 
   return r == CUDA_SUCCESS;
 }
 
-// Chunk length (tokens) from the context length and the SM count.  `slots` CTAs are resident at
-// once (2 per SM).  A large problem is cut so that about 8 waves of CTAs, each 16..64 tiles long,
-// cover it: long enough to amortise a CTA's pipeline fill, many enough for the hardware scheduler
-// to balance ragged lengths.  A small problem (less than that) is cut into at most one wave, so
-// each CTA streams as long a run as possible.  At most kMaxChunks chunks per sequence; always a
-// multiple of 64 tokens.
-int pick_chunk_tokens(int batch, int hkv, int64_t max_len) {
+// ---- the chunk plan: "a split count chosen from the context length and SM count" -----------------
+// `slots` CTAs are resident at once (2 per SM).  A large problem (more than about 8 waves of CTAs of
+// 16 tiles) is cut on the host into chunks of 16..64 tiles of 64 tokens, one length for the whole
+// launch: long enough to amortise a CTA's pipeline fill, many enough for the hardware scheduler to
+// balance ragged lengths; CTAs past a sequence's end exit at once.  A problem whose (sequence, head)
+// items fit one wave is planned on the device instead (`balanced`): the CTAs read the actual lengths
+// and pick the smallest chunk length for which all chunks fit the wave, so every CTA of the wave
+// streams about the same number of bytes whatever the mix of lengths.  In between (more items than
+// slots, little work each) every sequence is one chunk.  At most kMaxChunks chunks per sequence.
+struct Plan {
+  int chunk_tokens, max_chunks;
+  int balanced, budget;
+  size_t part_o_bytes, part_ml_bytes;
+};
+
+Plan make_plan(int batch, int hq, int hkv, int d, int64_t max_len) {
+  if (max_len < 1) max_len = 1;
+  Plan pl{};
   const int64_t tiles = (max_len + 63) / 64;
   const int64_t slots = (int64_t)sm_count() * 2;
   const int64_t items = (int64_t)batch * hkv;
@@ -1113,25 +1340,17 @@ int pick_chunk_tokens(int batch, int hkv, int64_t max_len) {
     chunk_tiles = (total + 8 * slots - 1) / (8 * slots);
     if (chunk_tiles < 16) chunk_tiles = 16;
     if (chunk_tiles > 64) chunk_tiles = 64;
+  } else if (items <= slots && batch <= kMaxBalancedBatch) {
+    pl.balanced = 1;
+    pl.budget = (int)(slots / hkv);
+    chunk_tiles = kMinChunkTiles;
   } else {
-    int64_t per_item = slots / items;  // chunks each (sequence, head) may have within one wave
-    if (per_item < 1) per_item = 1;
-    chunk_tiles = (tiles + per_item - 1) / per_item;
-    if (chunk_tiles < 4) chunk_tiles = 4;
+    chunk_tiles = tiles < kMinChunkTiles ? kMinChunkTiles : tiles;
   }
   while ((tiles + chunk_tiles - 1) / chunk_tiles > kMaxChunks) chunk_tiles *= 2;
-  return (int)(chunk_tiles * 64);
-}
-
-struct Plan {
-  int chunk_tokens, max_chunks;
-  size_t part_o_bytes, part_ml_bytes;
-};
-
-Plan make_plan(int batch, int hq, int hkv, int d, int64_t max_len) {
-  Plan pl;
-  pl.chunk_tokens = pick_chunk_tokens(batch, hkv, max_len < 1 ? 1 : max_len);
+  pl.chunk_tokens = (int)(chunk_tiles * 64);
   pl.max_chunks = (int)((max_len + pl.chunk_tokens - 1) / pl.chunk_tokens);
+  if (pl.balanced && pl.max_chunks > pl.budget) pl.max_chunks = pl.budget;  // one sequence cannot have more
   if (pl.max_chunks < 1) pl.max_chunks = 1;
   pl.part_o_bytes = (size_t)batch * hq * pl.max_chunks * d * sizeof(float);
   pl.part_ml_bytes = (size_t)batch * hq * pl.max_chunks * 2 * sizeof(float);
@@ -1156,33 +1375,33 @@ bool set_smem(const void *kernel, int bytes) {
 constexpr int kStagesDefault = 3;
 
 template <bool kPaged>
-int launch_f16(const CUtensorMap &mk, const CUtensorMap &mv, const DecodeParams &p, dim3 grid,
-               cudaStream_t st) {
+int launch_f16(const CUtensorMap &mk, const CUtensorMap &mv, const DecodeParams &p,
+               const GatherParams &g, dim3 grid, cudaStream_t st) {
   auto kern = gqa_split_f16_kernel<kPaged, kStagesDefault, 2>;
   constexpr int smem = SmemLayout<kStagesDefault>::kDynamicBytes;
   if (!set_smem(reinterpret_cast<const void *>(kern), smem)) return AXB200_DEVICE_ERROR;
-  kern<<<grid, kThreads, smem, st>>>(mk, mv, p);
+  kern<<<grid, kThreads, smem, st>>>(mk, mv, p, g);
   return launch_status();
 }
 
 template <bool kPaged, int kGroup>
-int launch_f32_g(const CUtensorMap &mk, const CUtensorMap &mv, const DecodeParams &p, dim3 grid,
-                 cudaStream_t st) {
+int launch_f32_g(const CUtensorMap &mk, const CUtensorMap &mv, const DecodeParams &p,
+                 const GatherParams &g, dim3 grid, cudaStream_t st) {
   auto kern = gqa_split_f32_kernel<kPaged, kStagesDefault, kGroup>;
   constexpr int smem = SmemLayout<kStagesDefault>::kDynamicBytes;
   if (!set_smem(reinterpret_cast<const void *>(kern), smem)) return AXB200_DEVICE_ERROR;
-  kern<<<grid, kThreads, smem, st>>>(mk, mv, p);
+  kern<<<grid, kThreads, smem, st>>>(mk, mv, p, g);
   return launch_status();
 }
 
 template <bool kPaged>
-int launch_f32(const CUtensorMap &mk, const CUtensorMap &mv, const DecodeParams &p, dim3 grid,
-               cudaStream_t st) {
+int launch_f32(const CUtensorMap &mk, const CUtensorMap &mv, const DecodeParams &p,
+               const GatherParams &g, dim3 grid, cudaStream_t st) {
   switch (p.group) {
-    case 1: return launch_f32_g<kPaged, 1>(mk, mv, p, grid, st);
-    case 2: return launch_f32_g<kPaged, 2>(mk, mv, p, grid, st);
-    case 4: return launch_f32_g<kPaged, 4>(mk, mv, p, grid, st);
-    case 8: return launch_f32_g<kPaged, 8>(mk, mv, p, grid, st);
+    case 1: return launch_f32_g<kPaged, 1>(mk, mv, p, g, grid, st);
+    case 2: return launch_f32_g<kPaged, 2>(mk, mv, p, g, grid, st);
+    case 4: return launch_f32_g<kPaged, 4>(mk, mv, p, g, grid, st);
+    case 8: return launch_f32_g<kPaged, 8>(mk, mv, p, g, grid, st);
     default: return AXB200_UNSUPPORTED_TYPE;
   }
 }
@@ -1210,6 +1429,30 @@ int profile_slot() {
 
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// ---- host settings -------------------------------------------------------------------------------
+std::mutex g_settings_mu;
+unsigned long long g_wait_limit_ns = kWaitNanos;
+bool g_fused_merge = true;
+
+// Counter region of the fused merge for launches that use `workspace` on the current device.  Two
+// launches may overlap on the GPU only if they use different workspaces (they would race on the
+// partials otherwise), so a region per workspace pointer keeps their counters apart.  -1: none free.
+int arrival_region_for(const void *workspace, int64_t items) {
+  if (items > kArrivalSlots) return -1;
+  static std::map<std::pair<int, const void *>, int> table;
+  static int used[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+  std::lock_guard<std::mutex> lock(g_settings_mu);
+  if (!g_fused_merge) return -1;
+  auto it = table.find({dev, workspace});
+  if (it != table.end()) return it->second;
+  if (used[dev] >= kArrivalRegions) return -1;
+  const int region = used[dev]++;
+  table[{dev, workspace}] = region;
+  return region;
+}
+
 // Common launcher.  `paged` selects the cache layout; for the token-major layout `tokens` is skv.
 int decode_impl(bool paged, const void *q, void *out, const void *k, const void *v,
                 const int32_t *block_table, const int32_t *seq_lens, int fixed_len, int batch,
@@ -1227,6 +1470,7 @@ int decode_impl(bool paged, const void *q, void *out, const void *k, const void 
     return AXB200_INVALID_ARGUMENT;
   if (paged && (int64_t)max_blocks * page_tokens < max_len) return AXB200_INVALID_ARGUMENT;
   if (batch > 65535 || hkv > 65535) return AXB200_INVALID_ARGUMENT;
+  if (window < 0) return AXB200_INVALID_ARGUMENT;
 
   const Plan pl = make_plan(batch, hq, hkv, d, max_len);
   DecodeParams p{};
@@ -1239,24 +1483,38 @@ int decode_impl(bool paged, const void *q, void *out, const void *k, const void 
   p.hq = hq;
   p.hkv = hkv;
   p.group = hq / hkv;
+  p.d = d;
   p.page_tokens = paged ? page_tokens : 1;
   p.max_blocks = max_blocks;
   p.num_pages = num_pages;
   p.chunk_tokens = pl.chunk_tokens;
   p.max_chunks = pl.max_chunks;
+  p.balanced = pl.balanced;
+  p.budget = pl.budget;
   p.scale = 1.0f / sqrtf((float)d);
-  if (window < 0) return AXB200_INVALID_ARGUMENT;
   p.window = window;
   p.causal_rows = causal_rows;
-  p.write_final = pl.max_chunks == 1 && !gather;  // the gather epilogue lives in the combine kernel
-  if (!p.write_final) {
+  {
+    std::lock_guard<std::mutex> lock(g_settings_mu);
+    p.wait_ns = g_wait_limit_ns;
+  }
+  const bool need_ws = pl.max_chunks > 1;
+  if (need_ws) {
     if (!workspace || workspace_bytes < pl.part_o_bytes + pl.part_ml_bytes)
       return AXB200_INVALID_ARGUMENT;
     if (!aligned16(workspace)) return AXB200_INVALID_PTR;
     p.part_o = reinterpret_cast<float *>(workspace);
     p.part_ml = reinterpret_cast<float *>(static_cast<uint8_t *>(workspace) + pl.part_o_bytes);
   }
-  const dim3 grid(pl.max_chunks, hkv, batch);
+  // Who writes the result.  One chunk per sequence at most: the split CTA itself.  Else the last CTA
+  // of each (sequence, KV head) when a counter region is to be had, else a combine kernel - which
+  // then also emits the single-chunk sequences, so that every item passes through one place.
+  p.arrival_region = need_ws ? arrival_region_for(workspace, (int64_t)batch * hkv) : -1;
+  const bool combine_kernel = need_ws && p.arrival_region < 0;
+  p.direct_ok = !combine_kernel;
+  GatherParams g{};
+  if (gather) g = *gather;
+  const dim3 grid = pl.balanced ? dim3(pl.budget, hkv, 1) : dim3(pl.max_chunks, hkv, batch);
   const bool f16 = dtype == AXB200_FLOAT16;
   const float dom = p.scale * kLog2e;
 
@@ -1265,20 +1523,22 @@ int decode_impl(bool paged, const void *q, void *out, const void *k, const void 
   if (tiled && !f16 && !(p.group == 1 || p.group == 2 || p.group == 4 || p.group == 8))
     tiled = false;
 
-  int status;
-  const int prof = profile_slot();
-  if (prof >= 0) cudaEventRecord(g_profile.start[prof], st);
+  CUtensorMap mk, mv;
   if (tiled) {
-    CUtensorMap mk, mv;
     const int tile = f16 ? kTileTokensF16 : kTileTokensF32;
     const int64_t tok = paged ? page_tokens : max_len;
     if (!make_map(&mk, k, dtype, paged, d, hkv, tok, num_pages, tile) ||
         !make_map(&mv, v, dtype, paged, d, hkv, tok, num_pages, tile))
       return AXB200_INTERNAL_ERROR;
+  }
+  int status;
+  const int prof = profile_slot();
+  if (prof >= 0) cudaEventRecord(g_profile.start[prof], st);
+  if (tiled) {
     if (f16)
-      status = paged ? launch_f16<true>(mk, mv, p, grid, st) : launch_f16<false>(mk, mv, p, grid, st);
+      status = paged ? launch_f16<true>(mk, mv, p, g, grid, st) : launch_f16<false>(mk, mv, p, g, grid, st);
     else
-      status = paged ? launch_f32<true>(mk, mv, p, grid, st) : launch_f32<false>(mk, mv, p, grid, st);
+      status = paged ? launch_f32<true>(mk, mv, p, g, grid, st) : launch_f32<false>(mk, mv, p, g, grid, st);
   } else {
     const int gsmem = (int)gen_smem_bytes(d, p.group);
     bool ok_attr = true;
@@ -1287,50 +1547,42 @@ int decode_impl(bool paged, const void *q, void *out, const void *k, const void 
       if (paged) {
         auto kern = gqa_split_generic_kernel<__half, true>;
         ok_attr = set_smem(reinterpret_cast<const void *>(kern), 100 * 1024);
-        if (ok_attr) kern<<<grid, kGenThreads, gsmem, st>>>(kk, vv, p, d);
+        if (ok_attr) kern<<<grid, kGenThreads, gsmem, st>>>(kk, vv, p, g, d);
       } else {
         auto kern = gqa_split_generic_kernel<__half, false>;
         ok_attr = set_smem(reinterpret_cast<const void *>(kern), 100 * 1024);
-        if (ok_attr) kern<<<grid, kGenThreads, gsmem, st>>>(kk, vv, p, d);
+        if (ok_attr) kern<<<grid, kGenThreads, gsmem, st>>>(kk, vv, p, g, d);
       }
     } else {
       auto kk = reinterpret_cast<const float *>(k), vv = reinterpret_cast<const float *>(v);
       if (paged) {
         auto kern = gqa_split_generic_kernel<float, true>;
         ok_attr = set_smem(reinterpret_cast<const void *>(kern), 100 * 1024);
-        if (ok_attr) kern<<<grid, kGenThreads, gsmem, st>>>(kk, vv, p, d);
+        if (ok_attr) kern<<<grid, kGenThreads, gsmem, st>>>(kk, vv, p, g, d);
       } else {
         auto kern = gqa_split_generic_kernel<float, false>;
         ok_attr = set_smem(reinterpret_cast<const void *>(kern), 100 * 1024);
-        if (ok_attr) kern<<<grid, kGenThreads, gsmem, st>>>(kk, vv, p, d);
+        if (ok_attr) kern<<<grid, kGenThreads, gsmem, st>>>(kk, vv, p, g, d);
       }
     }
-    if (!ok_attr) return AXB200_DEVICE_ERROR;
-    status = launch_status();
+    status = ok_attr ? launch_status() : AXB200_DEVICE_ERROR;
   }
-  if (prof >= 0) cudaEventRecord(g_profile.stop[prof], st);
+  if (prof >= 0) cudaEventRecord(g_profile.stop[prof], st);  // recorded on every path once the start is
   if (status != AXB200_OK) return status;
-  if (!p.write_final) {
-    // The fp16 tiled kernel keeps its maxima in the log2 domain (already scaled); the fp32 and
-    // generic kernels keep raw dot products and scale inside the exponent.
-    const float cdom = (tiled && f16) ? 1.0f : dom;
-    const dim3 cgrid(hq, batch);
-    if (gather && gather->mode == 1) {
-      const float *records = static_cast<const float *>(gather->peer_out[gather->rank]);
-      if (f16) {
-        gqa_combine_exchange_kernel<__half><<<cgrid, 128, 0, st>>>(p, *gather, d, cdom);
-        cp_merge_kernel<__half><<<cgrid, 128, 0, st>>>(records, static_cast<__half *>(out), gather->world, d, cdom);
-      } else {
-        gqa_combine_exchange_kernel<float><<<cgrid, 128, 0, st>>>(p, *gather, d, cdom);
-        cp_merge_kernel<float><<<cgrid, 128, 0, st>>>(records, static_cast<float *>(out), gather->world, d, cdom);
-      }
-    } else if (gather) {
-      if (f16) gqa_combine_gather_kernel<__half><<<cgrid, 128, 0, st>>>(p, *gather, d, cdom);
-      else gqa_combine_gather_kernel<float><<<cgrid, 128, 0, st>>>(p, *gather, d, cdom);
-    } else {
-      if (f16) gqa_combine_kernel<__half><<<cgrid, 128, 0, st>>>(p, d, cdom);
-      else gqa_combine_kernel<float><<<cgrid, 128, 0, st>>>(p, d, cdom);
-    }
+  // The fp16 tiled kernel keeps its maxima in the log2 domain (already scaled); the fp32 and
+  // generic kernels keep raw dot products and scale inside the exponent.
+  const float cdom = (tiled && f16) ? 1.0f : dom;
+  const dim3 cgrid(hq, batch);
+  if (combine_kernel) {
+    if (f16) gqa_combine_kernel<__half><<<cgrid, 128, 0, st>>>(p, g, cdom);
+    else gqa_combine_kernel<float><<<cgrid, 128, 0, st>>>(p, g, cdom);
+    status = launch_status();
+    if (status != AXB200_OK) return status;
+  }
+  if (gather && gather->mode == 1) {  // every rank's records are here: merge them (local reads only)
+    const float *records = static_cast<const float *>(gather->peer_out[gather->rank]);
+    if (f16) cp_merge_kernel<__half><<<cgrid, 128, 0, st>>>(records, static_cast<__half *>(out), gather->world, d, cdom);
+    else cp_merge_kernel<float><<<cgrid, 128, 0, st>>>(records, static_cast<float *>(out), gather->world, d, cdom);
     status = launch_status();
   }
   return status;
@@ -1381,9 +1633,53 @@ int sdpa_rows_fallback(const void *q, const void *k, const void *v, void *out, i
                      workspace, workspace_bytes, st, nullptr, 0, is_causal ? 1 : 0);
 }
 
+unsigned long long wait_limit_ns() {
+  std::lock_guard<std::mutex> lock(g_settings_mu);
+  return g_wait_limit_ns;
+}
+
 }  // namespace axb
 
 extern "C" {
+
+int axb200_set_wait_limit_ns(uint64_t ns) {
+  if (ns == 0) return AXB200_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> lock(axb::g_settings_mu);
+  axb::g_wait_limit_ns = ns;
+  return AXB200_OK;
+}
+
+int axb200_set_fused_merge(int on) {
+  std::lock_guard<std::mutex> lock(axb::g_settings_mu);
+  axb::g_fused_merge = on != 0;
+  return AXB200_OK;
+}
+
+int axb200_gqa_chunk_plan(const int32_t *lens_host, int batch, int hq, int hkv, int d, int64_t max_seq_len,
+                          int32_t *chunk_tokens_out, int32_t *n_chunks_out, int32_t *max_chunks_out,
+                          int32_t *grid_ctas_out) {
+  if (!lens_host || !chunk_tokens_out || !n_chunks_out) return AXB200_INVALID_PTR;
+  if (batch <= 0 || hq <= 0 || hkv <= 0 || d <= 0 || max_seq_len <= 0) return AXB200_INVALID_ARGUMENT;
+  const axb::Plan pl = axb::make_plan(batch, hq, hkv, d, max_seq_len);
+  if (max_chunks_out) *max_chunks_out = pl.max_chunks;
+  if (grid_ctas_out) *grid_ctas_out = pl.balanced ? pl.budget * hkv : pl.max_chunks * hkv * batch;
+  const int c = pl.balanced ? axb::balanced_chunk_tiles_host(lens_host, batch, pl.budget, pl.max_chunks) : 0;
+  for (int b = 0; b < batch; ++b) {
+    int L = lens_host[b] < 0 ? 0 : lens_host[b];
+    if (pl.balanced) {
+      int ct, n;
+      axb::sequence_chunks(L, c, &ct, &n);
+      chunk_tokens_out[b] = ct;
+      n_chunks_out[b] = n;
+    } else {
+      const int64_t cover = (int64_t)pl.max_chunks * pl.chunk_tokens;
+      if (L > cover) L = (int)cover;
+      chunk_tokens_out[b] = pl.chunk_tokens;
+      n_chunks_out[b] = std::max(1, axb::ceil_div(L, pl.chunk_tokens));
+    }
+  }
+  return AXB200_OK;
+}
 
 size_t axb200_static_scratch_bytes(void) { return axb::kStaticScratchBytes; }
 
@@ -1467,7 +1763,10 @@ int axb200_p2p_alloc(size_t bytes, void **dev_ptr, void *handle64) {
   static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
   void *ptr = nullptr;
   if (cudaMalloc(&ptr, bytes) != cudaSuccess) return AXB200_OUT_OF_MEMORY;
-  if (cudaMemset(ptr, 0, bytes) != cudaSuccess) return AXB200_DEVICE_ERROR;
+  if (cudaMemset(ptr, 0, bytes) != cudaSuccess) {
+    cudaFree(ptr);
+    return AXB200_DEVICE_ERROR;
+  }
   cudaIpcMemHandle_t h;
   if (cudaIpcGetMemHandle(&h, ptr) != cudaSuccess) {
     cudaFree(ptr);
@@ -1499,12 +1798,17 @@ int axb200_p2p_free(void *dev_ptr) {
   return cudaFree(dev_ptr) == cudaSuccess ? AXB200_OK : AXB200_DEVICE_ERROR;
 }
 
-const char *axb200_version(void) { return "axono_b200 0.1 (sm_100a)"; }
+const char *axb200_version(void) { return "axono_b200 0.2 (sm_100a)"; }
 
 unsigned int axb200_last_error(void) {
   if (cudaDeviceSynchronize() != cudaSuccess) return 0x80000000u;
   unsigned int word = 0;
   for (int i = 0; i < axb::g_num_error_readers; ++i) word |= axb::g_error_readers[i]();
+  if (word & AXB200_ERR_WAIT_TIMEOUT) {
+    // a CTA that gave up never counted itself in: put the fused merge's counters back to zero
+    axb::zero_arrival_kernel<<<64, 256>>>();
+    cudaDeviceSynchronize();
+  }
   return word;
 }
 

@@ -131,6 +131,60 @@ bool Available() {
   return cudaGetDeviceCount(&n) == cudaSuccess && n > 0;
 }
 
+Status SetDevice(int index) { return cudaSetDevice(index) == cudaSuccess ? Status::OK : Status::DEVICE_ERROR; }
+int CurrentDevice() {
+  int dev = -1;
+  return cudaGetDevice(&dev) == cudaSuccess ? dev : -1;
+}
+std::string DevicePciBusId(int index) {
+  char buf[32] = {0};
+  if (cudaDeviceGetPCIBusId(buf, sizeof(buf), index) != cudaSuccess) {
+    cudaGetLastError();
+    return "";
+  }
+  return buf;
+}
+void *AllocatePinnedHost(size_t bytes) {
+  void *p = nullptr;
+  if (cudaHostAlloc(&p, bytes ? bytes : 1, cudaHostAllocDefault) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  return p;
+}
+void FreePinnedHost(void *ptr) {
+  if (ptr) cudaFreeHost(ptr);
+}
+EventTimer::EventTimer() {
+  cudaEvent_t a = nullptr, b = nullptr;
+  if (cudaEventCreate(&a) == cudaSuccess && cudaEventCreate(&b) == cudaSuccess) {
+    start_ = a;
+    stop_ = b;
+  } else {
+    if (a) cudaEventDestroy(a);
+    cudaGetLastError();
+  }
+}
+EventTimer::~EventTimer() {
+  if (start_) cudaEventDestroy(static_cast<cudaEvent_t>(start_));
+  if (stop_) cudaEventDestroy(static_cast<cudaEvent_t>(stop_));
+}
+Status EventTimer::Start() {
+  if (!start_) return Status::DEVICE_ERROR;
+  return cudaEventRecord(static_cast<cudaEvent_t>(start_), static_cast<cudaStream_t>(CurrentStream())) == cudaSuccess
+             ? Status::OK : Status::DEVICE_ERROR;
+}
+Status EventTimer::Stop() {
+  if (!stop_) return Status::DEVICE_ERROR;
+  return cudaEventRecord(static_cast<cudaEvent_t>(stop_), static_cast<cudaStream_t>(CurrentStream())) == cudaSuccess
+             ? Status::OK : Status::DEVICE_ERROR;
+}
+Status EventTimer::ElapsedMs(float *ms) {
+  if (!start_ || !stop_ || !ms) return Status::DEVICE_ERROR;
+  if (cudaEventSynchronize(static_cast<cudaEvent_t>(stop_)) != cudaSuccess) return Status::DEVICE_ERROR;
+  return cudaEventElapsedTime(ms, static_cast<cudaEvent_t>(start_), static_cast<cudaEvent_t>(stop_)) == cudaSuccess
+             ? Status::OK : Status::DEVICE_ERROR;
+}
 Status DeviceSynchronize() { return cudaDeviceSynchronize() == cudaSuccess ? Status::OK : Status::DEVICE_ERROR; }
 Status MemInfo(size_t *free_bytes, size_t *total_bytes) {
   return cudaMemGetInfo(free_bytes, total_bytes) == cudaSuccess ? Status::OK : Status::DEVICE_ERROR;
@@ -397,6 +451,16 @@ Tensor Tensor::FromBorrowed(DataType dtype, const Shape &shape, const void *data
   t.shape_ = shape;
   t.num_elements_ = CalculateNumElements(shape);
   t.data_ = std::shared_ptr<void>(const_cast<void *>(data), [](void *) {});
+  return t;
+}
+
+Tensor Tensor::FromBorrowedDevice(DataType dtype, const Shape &shape, void *device_ptr, const std::string &device) {
+  Tensor t(dtype);
+  t.device_ = device;
+  t.zero_fill_ = false;
+  t.shape_ = shape;
+  t.num_elements_ = CalculateNumElements(shape);
+  t.data_ = std::shared_ptr<void>(device_ptr, [](void *) {});
   return t;
 }
 

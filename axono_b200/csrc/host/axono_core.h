@@ -42,6 +42,8 @@ class Tensor {
   // copy = share storage; move = take storage (defaults do exactly that)
 
   static Tensor FromBorrowed(DataType dtype, const Shape &shape, const void *data);  // host memory, not owned
+  // Device memory owned by somebody else (a peer-mapped buffer, a KV pool): a view, never freed here.
+  static Tensor FromBorrowedDevice(DataType dtype, const Shape &shape, void *device_ptr, const std::string &device);
   // Device storage without the zero fill, for results an operator overwrites completely (the binding
   // layer's outputs): the fill would be one more memset per operator in every captured graph.  Storage
   // the tensor takes later through Resize is not filled either.
@@ -83,7 +85,25 @@ class Tensor {
 namespace cuda {
 
 bool Available();
+Status SetDevice(int index);  // makes the device current for this thread (one process per GPU picks its own)
+int CurrentDevice();          // -1 without a device
+std::string DevicePciBusId(int index);  // "" on failure; lets a monitor find the same GPU through NVML
 Status DeviceSynchronize();
+void *AllocatePinnedHost(size_t bytes);  // page-locked host memory for asynchronous copies; nullptr on failure
+void FreePinnedHost(void *ptr);
+// A pair of events on the current stream: Start / Stop bracket a region, ElapsedMs waits for Stop.
+class EventTimer {
+ public:
+  EventTimer();
+  ~EventTimer();
+  EventTimer(const EventTimer &) = delete;
+  EventTimer &operator=(const EventTimer &) = delete;
+  Status Start();
+  Status Stop();
+  Status ElapsedMs(float *ms);
+ private:
+  void *start_ = nullptr, *stop_ = nullptr;  // cudaEvent_t
+};
 Status MemInfo(size_t *free_bytes, size_t *total_bytes);  // of the current device
 Status CopyToHost(void *dst, const void *device_src, size_t bytes);  // blocking, legacy default stream
 Status CopyToDevice(void *device_dst, const void *src, size_t bytes);  // blocking, legacy default stream

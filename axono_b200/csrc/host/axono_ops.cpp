@@ -1,6 +1,7 @@
 #include "axono_ops.h"
 
 #include <algorithm>
+#include <initializer_list>
 
 #include "axono_b200.h"
 
@@ -18,6 +19,20 @@ void *Stream() { return core::cuda::CurrentStream(); }
 bool Float(DataType t) { return t == DataType::FLOAT32 || t == DataType::FLOAT16; }
 bool Cuda(const Tensor &t) { return t.is_cuda(); }
 
+// Every operand in device memory of one GPU: a host pointer (or another GPU's) handed to a kernel is a
+// fault that takes the context with it, so this is checked before anything is resized or launched.
+// Null operands (optional arguments) are skipped.
+bool OneDevice(std::initializer_list<const Tensor *> ts) {
+  int dev = -2;
+  for (const Tensor *t : ts) {
+    if (!t) continue;
+    if (!t->is_cuda()) return false;
+    if (dev == -2) dev = t->device_index();
+    else if (t->device_index() != dev) return false;
+  }
+  return true;
+}
+
 // Scratch comes from the caching pool, like the reference's three workspace tensors
 // (src/ops/cuda/gqa.cu:166-168); after the first call of a shape it is a pool hit.
 Tensor Scratch(size_t bytes, const std::string &device) {
@@ -27,6 +42,7 @@ Tensor Scratch(size_t bytes, const std::string &device) {
 }  // namespace
 
 Status GqaDecodeAttention(const Context &, const Tensor &q, const Tensor &k, const Tensor &v, Tensor &result) {
+  if (!OneDevice({&q, &k, &v})) return Status::DEVICE_MISMATCH;
   if (q.ndim() != 3 || k.ndim() != 3 || v.ndim() != 3 || !Float(q.dtype())) return Status::UNSUPPORTED_TYPE;
   if (k.dtype() != q.dtype() || v.dtype() != q.dtype()) return Status::UNSUPPORTED_TYPE;
   if (!Cuda(q) || !Cuda(k) || !Cuda(v)) return Status::DEVICE_MISMATCH;
@@ -45,6 +61,7 @@ Status GqaDecodeAttention(const Context &, const Tensor &q, const Tensor &k, con
 
 Status ScaledDotProductAttention(const Context &, const Tensor &q, const Tensor &k, const Tensor &v, bool is_causal,
                                  Tensor &result) {
+  if (!OneDevice({&q, &k, &v})) return Status::DEVICE_MISMATCH;
   if (q.ndim() != 3 || k.ndim() != 3 || v.ndim() != 3) return Status::INVALID_ARGUMENT;
   if (!Float(q.dtype()) || k.dtype() != q.dtype() || v.dtype() != q.dtype()) return Status::UNSUPPORTED_TYPE;
   const size_t sq = q.shape()[0], hq = q.shape()[1], d = q.shape()[2];
@@ -60,6 +77,7 @@ Status ScaledDotProductAttention(const Context &, const Tensor &q, const Tensor 
 }
 
 Status SiluMul(const Context &, const Tensor &gate, const Tensor &up, Tensor &result) {
+  if (!OneDevice({&gate, &up})) return Status::DEVICE_MISMATCH;
   if (!Float(gate.dtype()) || gate.dtype() != up.dtype() || gate.shape() != up.shape()) return Status::SHAPE_MISMATCH;
   Status st = result.Resize(gate.shape());
   if (st != Status::OK) return st;
@@ -68,6 +86,7 @@ Status SiluMul(const Context &, const Tensor &gate, const Tensor &up, Tensor &re
 
 Status AddRmsNorm(const Context &, const Tensor &x, const Tensor &residual, const Tensor &weight, float eps, Tensor &y,
                   Tensor &out) {
+  if (!OneDevice({&x, &residual, &weight})) return Status::DEVICE_MISMATCH;
   if (!Float(x.dtype()) || x.shape() != residual.shape() || residual.dtype() != x.dtype()) return Status::SHAPE_MISMATCH;
   if (x.ndim() < 1) return Status::INVALID_ARGUMENT;
   const size_t hidden = x.shape().back();
@@ -81,6 +100,7 @@ Status AddRmsNorm(const Context &, const Tensor &x, const Tensor &residual, cons
 }
 
 Status RmsNorm(const Context &, const Tensor &x, const Tensor &weight, float eps, Tensor &result) {
+  if (!OneDevice({&x, weight.num_elements() ? &weight : nullptr})) return Status::DEVICE_MISMATCH;
   if (x.ndim() < 1) return Status::INVALID_ARGUMENT;
   const size_t cols = x.shape().back();
   Status st = result.Resize(x.shape());
@@ -94,6 +114,7 @@ Status RmsNorm(const Context &, const Tensor &x, const Tensor &weight, float eps
 }
 
 Status Rope(const Context &, const Tensor &x, const Tensor &pos_ids, float theta, Tensor &result) {
+  if (!OneDevice({&x, &pos_ids})) return Status::DEVICE_MISMATCH;
   if (x.ndim() != 3 || !Float(x.dtype())) return Status::UNSUPPORTED_TYPE;
   const size_t rows = x.shape()[0], heads = x.shape()[1], dim = x.shape()[2];
   if (dim % 2 != 0) return Status::INVALID_ARGUMENT;
@@ -106,6 +127,7 @@ Status Rope(const Context &, const Tensor &x, const Tensor &pos_ids, float theta
 
 Status RopeThd(const Context &, const Tensor &x, const Tensor &pos, const Tensor &inv_freq, int t_sec, int h_sec,
                int w_sec, Tensor &result) {
+  if (!OneDevice({&x, &pos, &inv_freq})) return Status::DEVICE_MISMATCH;
   if (x.ndim() != 3 || !Float(x.dtype())) return Status::UNSUPPORTED_TYPE;
   const size_t rows = x.shape()[0], heads = x.shape()[1], dim = x.shape()[2];
   if (dim % 2 != 0) return Status::INVALID_ARGUMENT;
@@ -120,6 +142,7 @@ Status RopeThd(const Context &, const Tensor &x, const Tensor &pos, const Tensor
 }
 
 Status RopeWithCosSin(const Context &, const Tensor &x, const Tensor &cos, const Tensor &sin, Tensor &result) {
+  if (!OneDevice({&x, &cos, &sin})) return Status::DEVICE_MISMATCH;
   if (x.ndim() != 3 || !Float(x.dtype())) return Status::UNSUPPORTED_TYPE;
   const size_t rows = x.shape()[0], heads = x.shape()[1], dim = x.shape()[2];
   if (dim % 2 != 0) return Status::INVALID_ARGUMENT;
@@ -134,6 +157,7 @@ Status RopeWithCosSin(const Context &, const Tensor &x, const Tensor &cos, const
 
 Status MropeCosSin(const Context &, const Tensor &pos, const Tensor &inv_freq, int h_sec, int w_sec, Tensor &cos_out,
                    Tensor &sin_out) {
+  if (!OneDevice({&pos, &inv_freq})) return Status::DEVICE_MISMATCH;
   if (pos.ndim() != 2 || pos.shape()[0] != 3 || pos.dtype() != DataType::INT64) return Status::SHAPE_MISMATCH;
   const size_t rows = pos.shape()[1], half = inv_freq.ndim() ? inv_freq.shape()[0] : 0;
   if (half == 0) return Status::INVALID_ARGUMENT;
@@ -146,6 +170,7 @@ Status MropeCosSin(const Context &, const Tensor &pos, const Tensor &inv_freq, i
 }
 
 Status Concat(const Context &, const Tensor &a, const Tensor &b, int axis, Tensor &result) {
+  if (!OneDevice({&a, &b})) return Status::DEVICE_MISMATCH;
   if (a.ndim() < 1 || a.ndim() != b.ndim() || a.dtype() != b.dtype()) return Status::INVALID_ARGUMENT;
   const size_t nd = a.ndim();
   const size_t ax = axis < 0 ? nd + axis : (size_t)axis;
@@ -164,6 +189,7 @@ Status Concat(const Context &, const Tensor &a, const Tensor &b, int axis, Tenso
 }
 
 Status Embedding(const Context &, const Tensor &ids, const Tensor &table, Tensor &result) {
+  if (!OneDevice({&ids, &table})) return Status::DEVICE_MISMATCH;
   if (ids.ndim() < 1 || table.ndim() != 2) return Status::INVALID_ARGUMENT;
   if (!Float(table.dtype())) return Status::UNSUPPORTED_TYPE;
   if (ids.dtype() != DataType::INT32 && ids.dtype() != DataType::INT64) return Status::UNSUPPORTED_TYPE;
@@ -176,6 +202,7 @@ Status Embedding(const Context &, const Tensor &ids, const Tensor &table, Tensor
 }
 
 Status ArgmaxLastDim(const Context &, const Tensor &x, Tensor &result) {
+  if (!OneDevice({&x})) return Status::DEVICE_MISMATCH;
   if (x.ndim() < 1) return Status::INVALID_ARGUMENT;
   const size_t cols = x.shape().back();
   const size_t rows = cols ? x.num_elements() / cols : 0;
@@ -186,6 +213,7 @@ Status ArgmaxLastDim(const Context &, const Tensor &x, Tensor &result) {
 }
 
 Status LinearNoBias(const Context &, const Tensor &x, const Tensor &w, Tensor &result) {
+  if (!OneDevice({&x, &w})) return Status::DEVICE_MISMATCH;
   if (x.ndim() != 2 || w.ndim() != 2 || x.shape()[1] != w.shape()[1]) return Status::SHAPE_MISMATCH;
   if (!Float(x.dtype()) || w.dtype() != x.dtype()) return Status::UNSUPPORTED_TYPE;
   if (!Cuda(x) || !Cuda(w)) return Status::DEVICE_MISMATCH;
@@ -196,6 +224,7 @@ Status LinearNoBias(const Context &, const Tensor &x, const Tensor &w, Tensor &r
 }
 
 Status SiluMulRows(const Context &, const Tensor &gate_up, int n, Tensor &result) {
+  if (!OneDevice({&gate_up})) return Status::DEVICE_MISMATCH;
   if (gate_up.ndim() != 2 || n <= 0 || gate_up.shape()[1] != (size_t)(2 * n)) return Status::SHAPE_MISMATCH;
   if (!Float(gate_up.dtype())) return Status::UNSUPPORTED_TYPE;
   Status st = result.Resize({gate_up.shape()[0], (size_t)n});
@@ -208,6 +237,7 @@ Status QkvNormRopeAppend(const Context &, const Tensor &qkv, int hq, const Tenso
                          float eps, axb200_kv_arena *arena, int layer, const Tensor *pos, const Tensor *inv_freq,
                          float theta, bool rotate, bool mrope, int h_sec, int w_sec, int slot_delta, bool advance,
                          Tensor &q_out) {
+  if (!OneDevice({&qkv, q_norm_w, k_norm_w, pos, inv_freq})) return Status::DEVICE_MISMATCH;
   if (!arena || qkv.ndim() != 2 || !Float(qkv.dtype())) return Status::UNSUPPORTED_TYPE;
   int n_layers, num_pages, hkv, page_tokens, d, dtype, max_seqs, max_blocks;
   if (axb200_kv_arena_geometry(arena, &n_layers, &num_pages, &hkv, &page_tokens, &d, &dtype, &max_seqs, &max_blocks) != 0)
@@ -229,6 +259,7 @@ Status QkvNormRopeAppend(const Context &, const Tensor &qkv, int hq, const Tenso
 Status KvAppendRope(const Context &, Tensor *q, const Tensor &k_new, const Tensor &v_new, axb200_kv_arena *arena,
                     int layer, const Tensor *pos, const Tensor *inv_freq, float theta, bool rotate, bool mrope, int h_sec,
                     int w_sec, int slot_delta, bool advance) {
+  if (!OneDevice({q, &k_new, &v_new, pos, inv_freq})) return Status::DEVICE_MISMATCH;
   if (!arena || k_new.ndim() != 3 || v_new.shape() != k_new.shape() || !Float(k_new.dtype())) return Status::SHAPE_MISMATCH;
   int n_layers, num_pages, hkv, page_tokens, d, dtype, max_seqs, max_blocks;
   if (axb200_kv_arena_geometry(arena, &n_layers, &num_pages, &hkv, &page_tokens, &d, &dtype, &max_seqs, &max_blocks) != 0)
@@ -247,6 +278,7 @@ Status KvAppendRope(const Context &, Tensor *q, const Tensor &k_new, const Tenso
 
 Status GqaDecodeAttentionPaged(const Context &, const Tensor &q, axb200_kv_arena *arena, int layer, int64_t max_seq_len,
                                Tensor &result) {
+  if (!OneDevice({&q})) return Status::DEVICE_MISMATCH;
   if (!arena || q.ndim() != 3 || !Float(q.dtype())) return Status::UNSUPPORTED_TYPE;
   int n_layers, num_pages, hkv, page_tokens, d, dtype, max_seqs, max_blocks;
   if (axb200_kv_arena_geometry(arena, &n_layers, &num_pages, &hkv, &page_tokens, &d, &dtype, &max_seqs, &max_blocks) != 0)

@@ -6,8 +6,10 @@
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
+#include <algorithm>
 #include <cstring>
 #include <stdexcept>
+#include <vector>
 
 #include "axono_b200.h"
 #include "axono_core.h"
@@ -144,6 +146,13 @@ PYBIND11_MODULE(libaxono, m) {
             return Tensor::FromBorrowed(DataType::INT64, ShapeOf(arr), arr.data());
           },
           py::arg("array"), py::keep_alive<0, 1>())
+      .def_static(
+          "from_device_ptr",  // a view of device memory that somebody else owns (peer-mapped buffers, KV pools)
+          [](uintptr_t ptr, DataType dtype, const Shape &shape, const std::string &device) {
+            if (!ptr) throw std::runtime_error("from_device_ptr: null pointer");
+            return Tensor::FromBorrowedDevice(dtype, shape, reinterpret_cast<void *>(ptr), device);
+          },
+          py::arg("ptr"), py::arg("dtype"), py::arg("shape"), py::arg("device") = "cuda")
       .def("to", &Tensor::to, py::arg("device"))
       .def("to_", &Tensor::to_, py::arg("device"))
       .def("copy_from", [](Tensor &self, const Tensor &src) { Check("copy_from", self.CopyFrom(src)); }, py::arg("src"))
@@ -203,6 +212,54 @@ PYBIND11_MODULE(libaxono, m) {
     Check("mem_info", acuda::MemInfo(&f, &t));
     return py::make_tuple(f, t);
   });
+  m.def("set_device", [](int index) { Check("set_device", acuda::SetDevice(index)); }, py::arg("index"));
+  m.def("current_device", &acuda::CurrentDevice);
+  m.def("device_pci_bus_id", &acuda::DevicePciBusId, py::arg("index"));
+  m.def("synchronize", []() { Check("synchronize", acuda::DeviceSynchronize()); });
+  m.def("current_stream", []() {  // cudaStream_t as an integer: 0 = legacy default stream, else the capture stream
+    return reinterpret_cast<uintptr_t>(acuda::CurrentStream());
+  });
+  m.def("set_fused_merge", [](bool on) { axb200_set_fused_merge(on ? 1 : 0); }, py::arg("on"));
+  m.def("set_wait_limit_ns", [](uint64_t ns) { Check("set_wait_limit_ns", static_cast<Status>(axb200_set_wait_limit_ns(ns))); },
+        py::arg("ns"));
+  m.def("profile_enable", [](bool on) { Check("profile_enable", static_cast<Status>(axb200_profile_enable(on ? 1 : 0))); },
+        py::arg("on"));
+  m.def("profile_collect", []() {  // (summed milliseconds of the split kernel, launches) since the last collect
+    double ms = 0.0;
+    int launches = 0;
+    Check("profile_collect", static_cast<Status>(axb200_profile_collect(&ms, &launches)));
+    return py::make_tuple(ms, launches);
+  });
+  m.def(
+      "pinned_empty",  // a numpy array in page-locked host memory (asynchronous copies need it)
+      [](const std::vector<py::ssize_t> &shape, DataType dtype) {
+        size_t n = 1;
+        for (auto d : shape) n *= (size_t)d;
+        void *p = acuda::AllocatePinnedHost(n * axono::core::GetDataTypeSize(dtype));
+        if (!p) throw std::runtime_error("pinned_empty: allocation failed");
+        py::capsule owner(p, [](void *q) { acuda::FreePinnedHost(q); });
+        return py::array(NumpyDtype(dtype), shape, p, owner);
+      },
+      py::arg("shape"), py::arg("dtype"));
+  m.def(
+      "randn",  // seeded N(mean, std) on the device; values depend only on (seed, element index)
+      [](const Shape &shape, DataType dtype, const std::string &device, uint64_t seed, float mean, float stddev) {
+        Tensor out = Tensor::Uninitialized(dtype, shape, device);
+        Check("randn", static_cast<Status>(axb200_randn(out.data(), (int64_t)out.num_elements(), static_cast<int>(dtype), mean,
+                                                        stddev, seed, acuda::CurrentStream())));
+        return out;
+      },
+      py::arg("shape"), py::arg("dtype"), py::arg("device") = "cuda", py::arg("seed") = 0, py::arg("mean") = 0.f,
+      py::arg("std") = 1.f);
+  py::class_<acuda::EventTimer>(m, "EventTimer")
+      .def(py::init<>())
+      .def("start", [](acuda::EventTimer &t) { Check("EventTimer.start", t.Start()); })
+      .def("stop", [](acuda::EventTimer &t) { Check("EventTimer.stop", t.Stop()); })
+      .def("elapsed_ms", [](acuda::EventTimer &t) {
+        float ms = 0.f;
+        Check("EventTimer.elapsed_ms", t.ElapsedMs(&ms));
+        return ms;
+      });
   m.def("device_error_bits", []() { return axb200_last_error(); });
   m.def("version", []() { return std::string(axb200_version()); });
 
@@ -361,6 +418,62 @@ PYBIND11_MODULE(libaxono, m) {
              d["device_bytes"] = bytes;
              return d;
            })
+      .def_property_readonly("handle", [](Arena &a) { return reinterpret_cast<uintptr_t>(a.h); })
+      .def("geometry",
+           [](Arena &a) {
+             int nl, np, hkv, pt, d, dt, ms, mb;
+             axb200_kv_arena_geometry(a.h, &nl, &np, &hkv, &pt, &d, &dt, &ms, &mb);
+             py::dict g;
+             g["n_layers"] = nl; g["num_pages"] = np; g["hkv"] = hkv; g["page_tokens"] = pt; g["d"] = d;
+             g["dtype"] = static_cast<DataType>(dt); g["max_seqs"] = ms; g["max_blocks"] = mb;
+             return g;
+           })
+      .def("k_pages_ptr", [](Arena &a, int layer) { return reinterpret_cast<uintptr_t>(axb200_kv_arena_k_pages(a.h, layer)); })
+      .def("v_pages_ptr", [](Arena &a, int layer) { return reinterpret_cast<uintptr_t>(axb200_kv_arena_v_pages(a.h, layer)); })
+      .def_property_readonly("block_table_ptr", [](Arena &a) { return reinterpret_cast<uintptr_t>(axb200_kv_arena_block_table(a.h)); })
+      .def_property_readonly("seq_lens_ptr", [](Arena &a) { return reinterpret_cast<uintptr_t>(axb200_kv_arena_seq_lens(a.h)); })
+      .def("shuffle_free", [](Arena &a, uint64_t seed) {
+        Check("shuffle_free", static_cast<Status>(axb200_kv_arena_shuffle_free(a.h, seed)));
+      }, py::arg("seed"))
+      .def("fill_normal",  // every K and V pool of every layer <- std * N(0,1), seeded per pool
+           [](Arena &a, uint64_t seed, float stddev) {
+             int nl, np, hkv, pt, d, dt, ms, mb;
+             axb200_kv_arena_geometry(a.h, &nl, &np, &hkv, &pt, &d, &dt, &ms, &mb);
+             const int64_t n = (int64_t)np * hkv * pt * d;
+             for (int l = 0; l < nl; ++l)
+               for (int kv = 0; kv < 2; ++kv)
+                 Check("fill_normal", static_cast<Status>(axb200_randn(
+                                          kv ? axb200_kv_arena_v_pages(a.h, l) : axb200_kv_arena_k_pages(a.h, l), n, dt, 0.f,
+                                          stddev, seed * 1000003ull + (uint64_t)(2 * l + kv), acuda::CurrentStream())));
+           },
+           py::arg("seed"), py::arg("std") = 1.f)
+      .def("gather",  // the first n cached tokens of one sequence as token-major (n, hkv, d) host arrays (for checks)
+           [](Arena &a, int layer, int seq, int64_t n) {
+             int nl, np, hkv, pt, d, dt, ms, mb;
+             axb200_kv_arena_geometry(a.h, &nl, &np, &hkv, &pt, &d, &dt, &ms, &mb);
+             if (layer < 0 || layer >= nl || n < 0) throw std::runtime_error("gather: bad layer or length");
+             std::vector<int32_t> pages(mb);
+             const int have = axb200_kv_arena_seq_pages(a.h, seq, pages.data(), mb);
+             if (have < 0 || (int64_t)have * pt < n) throw std::runtime_error("gather: the sequence holds fewer pages");
+             const size_t es = dt == static_cast<int>(DataType::FLOAT16) ? 2 : 4;
+             const DataType dtype = static_cast<DataType>(dt);
+             std::vector<py::ssize_t> shp{(py::ssize_t)n, hkv, d};
+             py::array k_out(NumpyDtype(dtype), shp), v_out(NumpyDtype(dtype), shp);
+             std::vector<char> page((size_t)hkv * pt * d * es);
+             for (int kv = 0; kv < 2; ++kv) {
+               const char *pool = static_cast<const char *>(kv ? axb200_kv_arena_v_pages(a.h, layer) : axb200_kv_arena_k_pages(a.h, layer));
+               char *dst = static_cast<char *>(kv ? v_out.mutable_data() : k_out.mutable_data());
+               for (int64_t blk = 0; blk * pt < n; ++blk) {
+                 Check("gather", acuda::CopyToHost(page.data(), pool + (size_t)pages[blk] * page.size(), page.size()));
+                 const int64_t toks = std::min<int64_t>(pt, n - blk * pt);
+                 for (int64_t t = 0; t < toks; ++t)
+                   for (int h = 0; h < hkv; ++h)
+                     std::memcpy(dst + (((blk * pt + t) * hkv + h) * d) * es, page.data() + (((size_t)h * pt + t) * d) * es, d * es);
+               }
+             }
+             return py::make_tuple(k_out, v_out);
+           },
+           py::arg("layer"), py::arg("seq"), py::arg("n"))
       .def("fill_pages",  // every K and V pool of every layer <- repetitions of `chunk` (benchmarks: non-zero cache contents)
            [](Arena &a, py::array chunk) {
              int nl, np, hkv, pt, d, dt, ms, mb;
@@ -443,12 +556,41 @@ PYBIND11_MODULE(libaxono, m) {
         py::arg("inv_freq") = py::none(), py::arg("theta") = 1e6f, py::arg("rotate") = true,
         py::arg("mrope_section") = py::none(), py::arg("slot_delta") = 0, py::arg("advance") = true);
   m.def("gqa_decode_attention_paged",
-        [](const Tensor &q, Arena &arena, int layer, int64_t max_seq_len) {
-          Tensor result = Tensor::Uninitialized(q.dtype(), q.shape(), q.device());
+        [](const Tensor &q, Arena &arena, int layer, int64_t max_seq_len, py::object out) {
+          Tensor result = out.is_none() ? Tensor::Uninitialized(q.dtype(), q.shape(), q.device()) : out.cast<Tensor>();
+          if (!out.is_none() && (result.dtype() != q.dtype() || result.shape() != q.shape() || result.device() != q.device()))
+            throw std::runtime_error("gqa_decode_attention_paged: out must match q in dtype, shape and device");
           Check("gqa_decode_attention_paged", aops::GqaDecodeAttentionPaged(Context(), q, arena.h, layer, max_seq_len, result));
           return result;
         },
-        py::arg("q"), py::arg("arena"), py::arg("layer"), py::arg("max_seq_len"));
+        py::arg("q"), py::arg("arena"), py::arg("layer"), py::arg("max_seq_len"), py::arg("out") = py::none());
+  m.def(
+      "decode_step_host",  // one decode step with HOST activations (pinned arrays): copies in, rope + append, attention, copy out, wait
+      [](Arena &arena, int layer, py::array q_host, py::array k_host, py::array v_host, py::array out_host, Tensor &q_dev,
+         Tensor &k_dev, Tensor &v_dev, Tensor &out_dev, Tensor &scratch, int64_t max_seq_len, float theta) {
+        int nl, np, hkv, pt, d, dt, ms, mb;
+        axb200_kv_arena_geometry(arena.h, &nl, &np, &hkv, &pt, &d, &dt, &ms, &mb);
+        if (q_dev.ndim() != 3 || (int)q_dev.shape()[0] != ms || (int)q_dev.shape()[2] != d || k_dev.ndim() != 3 ||
+            (int)k_dev.shape()[1] != hkv || static_cast<int>(q_dev.dtype()) != dt || layer < 0 || layer >= nl)
+          throw std::runtime_error("decode_step_host: staging tensors do not match the arena");
+        const size_t qb = q_dev.num_bytes(), kb = k_dev.num_bytes();
+        if ((size_t)q_host.nbytes() != qb || (size_t)out_host.nbytes() != qb || (size_t)k_host.nbytes() != kb ||
+            (size_t)v_host.nbytes() != kb || v_dev.num_bytes() != kb || out_dev.num_bytes() != qb)
+          throw std::runtime_error("decode_step_host: host and staging buffers differ in size");
+        const int hq = (int)q_dev.shape()[1];
+        Check("decode_step_host",
+              static_cast<Status>(axb200_decode_step_host(
+                  q_host.data(), k_host.data(), v_host.data(), out_host.mutable_data(), q_dev.data(), k_dev.data(), v_dev.data(),
+                  out_dev.data(), axb200_kv_arena_k_pages(arena.h, layer), axb200_kv_arena_v_pages(arena.h, layer),
+                  axb200_kv_arena_block_table(arena.h), axb200_kv_arena_seq_lens(arena.h), nullptr, nullptr, theta, 1, 0, 0, 0,
+                  ms, hq, hkv, d, pt, mb, np, max_seq_len, dt, scratch.data(), scratch.num_bytes(), acuda::CurrentStream())));
+      },
+      py::arg("arena"), py::arg("layer"), py::arg("q_host"), py::arg("k_new_host"), py::arg("v_new_host"), py::arg("out_host"),
+      py::arg("q_dev"), py::arg("k_new_dev"), py::arg("v_new_dev"), py::arg("out_dev"), py::arg("scratch"),
+      py::arg("max_seq_len"), py::arg("theta") = 1e6f);
+  m.def("gqa_workspace_bytes", [](int batch, int hq, int hkv, int d, int64_t max_seq_len, DataType dtype) {
+    return axb200_gqa_workspace_bytes(batch, hq, hkv, d, max_seq_len, static_cast<int>(dtype));
+  });
 
   // ---- CUDA graph ----
   m.def("_graph_begin_capture", []() {

@@ -14,6 +14,7 @@
 // CPU tests drive.
 #include <mutex>
 #include <new>
+#include <utility>
 #include <vector>
 
 #include "common.cuh"
@@ -110,6 +111,20 @@ int axb200_kv_arena_create(int n_layers, int num_pages, int hkv, int page_tokens
     }
   }
   *out = a;
+  return AXB200_OK;
+}
+
+int axb200_kv_arena_shuffle_free(axb200_kv_arena *a, uint64_t seed) {
+  if (!a) return AXB200_INVALID_PTR;
+  std::lock_guard<std::mutex> lock(a->mu);
+  // Fisher-Yates over the free stack with a fixed 64-bit LCG stream (Knuth's MMIX constants), so the
+  // same seed gives the same order everywhere
+  uint64_t x = seed * 6364136223846793005ull + 1442695040888963407ull;
+  for (size_t i = a->free_pages.size(); i > 1; --i) {
+    x = x * 6364136223846793005ull + 1442695040888963407ull;
+    const size_t j = (size_t)((x >> 33) % i);
+    std::swap(a->free_pages[i - 1], a->free_pages[j]);
+  }
   return AXB200_OK;
 }
 

@@ -223,30 +223,45 @@ struct AppendParams {
   int advance;
 };
 
-// One CTA per sequence: rotates q in place, rotates k and copies v into slot seq_lens[b] of the
-// sequence's pages (page layout (hkv, page_tokens, d)), then - as the CTA's last act - bumps
-// seq_lens[b].  The slot index is read before any thread of the CTA can have bumped it.  In a
-// multi-layer step the first layer appends with slot_delta 0 and advances, so that every layer's
-// attention sees the new token; the later layers append with slot_delta -1 and do not advance.
+// One CTA per sequence, one warp per head (query heads, then key heads, then value heads): rotates q
+// in place, rotates k and copies v into slot seq_lens[b] + slot_delta of the sequence's pages (page
+// layout (hkv, page_tokens, d)), then bumps seq_lens[b].  The kernel is a chain of dependent loads
+// (length -> page id -> store address) over a few KB, so it is built for latency: every thread reads
+// the length itself, each warp has its head's row in flight before the page id is known, cos / sin are
+// computed once per sequence while those loads fly, and there is one block-wide barrier - which is
+// also what orders every thread's read of the length before the bump.  In a multi-layer step the
+// first layer appends with slot_delta 0 and advances, so that every layer's attention sees the new
+// token; the later layers append with slot_delta -1 and do not advance.
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 kv_append_rope_kernel(const AppendParams p, const InvFreqTable table) {
-  __shared__ int s_len;
+  __shared__ float s_cos[kMaxHalf], s_sin[kMaxHalf];
   const int b = blockIdx.x;
-  if (threadIdx.x == 0) s_len = p.seq_lens[b] + p.slot_delta;
-  __syncthreads();
-  const int len = s_len;  // slot of the new token = number of tokens cached before it
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   const int half = p.d / 2;
+  const int q_heads = p.rotate ? p.hq : 0;  // without rotation q is left as it is
+  const int n_heads = q_heads + 2 * p.hkv;
+  const int len = p.seq_lens[b] + p.slot_delta;  // slot of the new token = tokens cached before it
 
-  float pt, ph, pw;
-  if (p.pos == nullptr) {
-    pt = ph = pw = (float)len;
-  } else if (p.mrope) {
-    pt = (float)p.pos[b];
-    ph = (float)p.pos[p.batch + b];
-    pw = (float)p.pos[2 * p.batch + b];
-  } else {
-    pt = ph = pw = (float)p.pos[b];
+  // this warp's first head: its row on the way before anything else is known
+  T *q = reinterpret_cast<T *>(p.q) + (size_t)b * p.hq * p.d;
+  const T *kn = reinterpret_cast<const T *>(p.k_new) + (size_t)b * p.hkv * p.d;
+  const T *vn = reinterpret_cast<const T *>(p.v_new) + (size_t)b * p.hkv * p.d;
+  auto row_of = [&](int head) -> const T * {
+    if (head < q_heads) return q + (size_t)head * p.d;
+    if (head < q_heads + p.hkv) return kn + (size_t)(head - q_heads) * p.d;
+    return vn + (size_t)(head - q_heads - p.hkv) * p.d;
+  };
+  constexpr int kPer = kMaxHalf / 32;  // pairs (i, i + half) per lane, i = lane + 32 j
+  float a[kPer], bb[kPer];
+  if (warp < n_heads) {
+    const T *src = row_of(warp);
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+      const int i = lane + 32 * j;
+      a[j] = i < half ? ld(src + i) : 0.f;
+      bb[j] = i < half ? ld(src + i + half) : 0.f;
+    }
   }
 
   const int slot = len / p.page_tokens;
@@ -258,63 +273,62 @@ kv_append_rope_kernel(const AppendParams p, const InvFreqTable table) {
                                                               : AXB200_ERR_CAPACITY);
   const int tok = len % p.page_tokens;
 
-  T *q = reinterpret_cast<T *>(p.q) + (size_t)b * p.hq * p.d;
-  const T *kn = reinterpret_cast<const T *>(p.k_new) + (size_t)b * p.hkv * p.d;
-  const T *vn = reinterpret_cast<const T *>(p.v_new) + (size_t)b * p.hkv * p.d;
-
-  // cos/sin of each rotary pair once per sequence; every head reuses them
-  __shared__ float s_cos[kMaxHalf], s_sin[kMaxHalf];
-  if (p.rotate) {
+  if (p.rotate) {  // cos/sin of each rotary pair once per sequence; every head reuses them
+    float pt, ph, pw;
+    if (p.pos == nullptr) {
+      pt = ph = pw = (float)len;
+    } else if (p.mrope) {
+      pt = (float)p.pos[b];
+      ph = (float)p.pos[p.batch + b];
+      pw = (float)p.pos[2 * p.batch + b];
+    } else {
+      pt = ph = pw = (float)p.pos[b];
+    }
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
       const float f = p.mrope || p.inv_freq_dev ? p.inv_freq_dev[i] : table.f[i];
       const float posv = p.mrope ? pair_position(i, pt, ph, pw, p.h_lim, p.w_lim) : pt;
       sincosf(posv * f, &s_sin[i], &s_cos[i]);
     }
-    __syncthreads();
   }
+  __syncthreads();  // tables ready; every thread has read the length
 
-  const int q_pairs = p.hq * half, k_pairs = p.hkv * half;
-  for (int idx = threadIdx.x; idx < q_pairs + k_pairs; idx += blockDim.x) {
-    const bool is_q = idx < q_pairs;
-    const int j = is_q ? idx : idx - q_pairs;
-    const int h = j / half, i = j % half;
-    float c = 1.f, s = 0.f;
-    if (p.rotate) {
-      c = s_cos[i];
-      s = s_sin[i];
+  for (int head = warp; head < n_heads; head += nwarps) {
+    if (head != warp) {  // more heads than warps: fetch the next row
+      const T *src = row_of(head);
+#pragma unroll
+      for (int j = 0; j < kPer; ++j) {
+        const int i = lane + 32 * j;
+        a[j] = i < half ? ld(src + i) : 0.f;
+        bb[j] = i < half ? ld(src + i + half) : 0.f;
+      }
     }
+    const bool is_q = head < q_heads, is_k = !is_q && head < q_heads + p.hkv;
+    T *dst;
     if (is_q) {
-      if (p.rotate) {
-        T *row = q + (size_t)h * p.d;
-        const float a = ld(row + i), bb = ld(row + i + half);
-        st(row + i, a * c - bb * s);
-        st(row + i + half, bb * c + a * s);
-      }
-    } else if (page_ok) {
-      const T *row = kn + (size_t)h * p.d;
-      T *dst = reinterpret_cast<T *>(p.k_pages) +
-               (((size_t)page * p.hkv + h) * p.page_tokens + tok) * p.d;
-      if (p.rotate) {
-        const float a = ld(row + i), bb = ld(row + i + half);
-        st(dst + i, a * c - bb * s);
-        st(dst + i + half, bb * c + a * s);
-      } else {
-        dst[i] = row[i];
-        dst[i + half] = row[i + half];
+      dst = q + (size_t)head * p.d;
+    } else {
+      if (!page_ok) continue;
+      const int h = is_k ? head - q_heads : head - q_heads - p.hkv;
+      dst = reinterpret_cast<T *>(is_k ? p.k_pages : p.v_pages) +
+            (((size_t)page * p.hkv + h) * p.page_tokens + tok) * p.d;
+    }
+    const bool rot = p.rotate && (is_q || is_k);
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+      const int i = lane + 32 * j;
+      if (i >= half) continue;
+      if (rot) {
+        const float c = s_cos[i], s = s_sin[i];
+        st(dst + i, a[j] * c - bb[j] * s);
+        st(dst + i + half, bb[j] * c + a[j] * s);
+      } else {  // a value row, or a key row without rotation: the bits as they came
+        const T *src = row_of(head);
+        dst[i] = src[i];
+        dst[i + half] = src[i + half];
       }
     }
   }
-  if (page_ok) {
-    for (int idx = threadIdx.x; idx < p.hkv * p.d; idx += blockDim.x) {
-      const int h = idx / p.d, c = idx % p.d;
-      reinterpret_cast<T *>(p.v_pages)[(((size_t)page * p.hkv + h) * p.page_tokens + tok) * p.d + c] =
-          vn[idx];
-    }
-  }
-  if (p.advance && page_ok) {
-    __syncthreads();
-    if (threadIdx.x == 0) p.seq_lens[b] = len - p.slot_delta + 1;
-  }
+  if (p.advance && page_ok && threadIdx.x == 0) p.seq_lens[b] = len - p.slot_delta + 1;
 }
 
 // ---- prefill write: many tokens of ONE sequence into its pages -------------------------------------
@@ -694,10 +708,12 @@ int axb200_kv_append_rope(void *q, const void *k_new, const void *v_new, void *k
   axb::InvFreqTable table{};
   if (rotate && !inv_freq) axb::fill_table(&table, theta, d);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int heads = (rotate ? p.hq : 0) + 2 * hkv;  // one warp per head, up to the block limit
+  const int threads = heads >= 32 ? 1024 : (heads < 2 ? 64 : heads * 32);
   if (dtype == AXB200_FLOAT32)
-    axb::kv_append_rope_kernel<float><<<batch, 256, 0, st>>>(p, table);
+    axb::kv_append_rope_kernel<float><<<batch, threads, 0, st>>>(p, table);
   else
-    axb::kv_append_rope_kernel<__half><<<batch, 256, 0, st>>>(p, table);
+    axb::kv_append_rope_kernel<__half><<<batch, threads, 0, st>>>(p, table);
   return axb::launch_status();
 }
 

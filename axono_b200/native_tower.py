@@ -4,7 +4,12 @@ written over its own (axono/python/examples/vlm/qwen3vl/model.py:330-373 attenti
 :483-486 final norm + tied lm_head, :729-761 decode_step), batched, with the two fusions of this
 library (per-head norm + rope + append in one launch after the QKV projection; the residual add that
 ends a layer folded into the next add_rms_norm).  Projections are cuBLASLt calls (`linear_nobias`).
-One GPU; the multi-GPU tower lives in `axono_b200.decode` on torch.distributed plumbing."""
+
+On several GPUs (one process each, `rdv` = their host rendezvous) the KV heads are sharded: rank r
+projects and caches heads [r * hkv / world, ...) and attends them; the attention kernel stores its
+rows into every rank's gathered buffer over peer memory (axono_b200.native_multi), so the output
+projection that follows reads local memory only.  Everything else is replicated, as the
+configuration states."""
 from __future__ import annotations
 
 import numpy as np
@@ -14,14 +19,20 @@ from .tower_config import TextTowerConfig
 
 
 class NativeTextTower:
-    """Random-init weights (numpy, fp16), KV pages in an arena, one token per row and step.
-    `decode_step()` is capturable: positions are the cache lengths on the device, the next token ids are
-    written back into `token_ids` on the device."""
+    """Random-init weights (numpy, fp16; the same on every rank), KV pages in an arena, one token per
+    row and step.  `decode_step()` is capturable: positions are the cache lengths on the device, the
+    next token ids are written back into `token_ids` on the device."""
 
     def __init__(self, cfg: TextTowerConfig, batch: int, max_seq_len: int, seed: int = 0, page_tokens: int = 64,
-                 weights=None):
+                 weights=None, device: str = "cuda", rdv=None):
         lx = native.load()
-        self.lx, self.cfg, self.batch, self.max_seq_len = lx, cfg, batch, max_seq_len
+        self.lx, self.cfg, self.batch, self.max_seq_len, self.device = lx, cfg, batch, max_seq_len, device
+        self.world = rdv.world if rdv is not None else 1
+        self.rank = rdv.rank if rdv is not None else 0
+        if cfg.n_kv_heads % self.world:
+            raise ValueError(f"cannot shard {cfg.n_kv_heads} KV heads over {self.world} ranks")
+        self.local_kv = cfg.n_kv_heads // self.world
+        self.local_q = cfg.n_q_heads // self.world
         d = cfg.head_dim
         rng = np.random.default_rng(seed)
         pool = (0.02 * rng.standard_normal(1 << 24, dtype=np.float32)).astype(np.float16)
@@ -48,19 +59,38 @@ class NativeTextTower:
         self.host_weights = weights
 
         def dev(a):
-            return lx.Tensor.from_numpy(np.ascontiguousarray(a), "cuda")
+            return lx.Tensor.from_numpy(np.ascontiguousarray(a), device)
+
+        def local_qkv(full):  # column-parallel: the rows of this rank's query, key and value heads
+            nq, nk = cfg.n_q_heads * d, cfg.n_kv_heads * d
+            q0, k0 = self.rank * self.local_q * d, self.rank * self.local_kv * d
+            return np.concatenate([full[q0:q0 + self.local_q * d], full[nq + k0:nq + k0 + self.local_kv * d],
+                                   full[nq + nk + k0:nq + nk + k0 + self.local_kv * d]])
 
         self.embed, self.final_ln = dev(weights["embed"]), dev(weights["final_ln"])
-        self.layers = [{k: dev(v) for k, v in lw.items()} for lw in weights["layers"]]
+        self.layers = []
+        self._weight_elems = weights["embed"].size + weights["final_ln"].size
+        for lw in weights["layers"]:
+            dl = {k: dev(local_qkv(v) if k == "qkv" and self.world > 1 else v) for k, v in lw.items()}
+            self._weight_elems += sum(int(t.num_elements) for t in dl.values())
+            self.layers.append(dl)
         self.inv_freq = dev((1.0 / (cfg.rope_theta ** (np.arange(0, d, 2, dtype=np.float32) / d))).astype(np.float32))
         blocks = (max_seq_len + page_tokens - 1) // page_tokens
-        self.arena = lx.KVArena(cfg.n_layers, batch * blocks, cfg.n_kv_heads, page_tokens, d, lx.DataType.FLOAT16,
+        self.arena = lx.KVArena(cfg.n_layers, batch * blocks, self.local_kv, page_tokens, d, lx.DataType.FLOAT16,
                                 batch, blocks)
         for _ in range(batch):
             self.arena.alloc_seq(max_seq_len)
         self.arena.sync()
         self.token_ids = dev(np.zeros(batch, np.int64))
         self.last_logits = None
+        self.bufs = self.scratch = None
+        if self.world > 1:
+            from .native_multi import PeerBuffers, Scratch
+
+            # one gathered buffer per layer (at least two): successive calls never share a buffer
+            self.bufs = PeerBuffers(rdv, batch, cfg.n_q_heads, d, lx.DataType.FLOAT16, slots=max(2, cfg.n_layers),
+                                    device=device)
+            self.scratch = Scratch(batch, self.local_q, self.local_kv, d, max_seq_len, lx.DataType.FLOAT16, device)
 
     def set_state(self, token_ids, lens) -> None:
         """Starts decoding at cache lengths `lens` (one per row); positions are the lengths."""
@@ -78,12 +108,19 @@ class NativeTextTower:
                 h, xn = lx.add_rms_norm(mlp_out, h, lw["input_ln"], cfg.eps)
             qkv = lx.linear_nobias(xn, lw["qkv"])
             q = lx.qkv_norm_rope_append(
-                self.arena, li, qkv, cfg.n_q_heads, lw["q_norm"] if cfg.qk_norm else None,
+                self.arena, li, qkv, self.local_q, lw["q_norm"] if cfg.qk_norm else None,
                 lw["k_norm"] if cfg.qk_norm else None, cfg.eps, inv_freq=self.inv_freq, theta=cfg.rope_theta,
                 mrope_section=list(cfg.mrope_section) if cfg.use_mrope else None,
                 slot_delta=0 if li == 0 else -1, advance=li == 0)
-            attn = lx.gqa_decode_attention_paged(q, self.arena, li, self.max_seq_len)
-            attn.reshape([self.batch, cfg.n_q_heads * cfg.head_dim])
+            if self.bufs is not None:  # attention fused with the all-gather of head outputs over peer memory
+                from .native_multi import attend_gather
+
+                attn = attend_gather(q, self.arena, li, self.max_seq_len, self.bufs, li % self.bufs.slots, self.scratch)
+                attn = lx.Tensor.from_device_ptr(attn.data_ptr, attn.dtype, [self.batch, cfg.n_q_heads * cfg.head_dim],
+                                                 self.device)
+            else:
+                attn = lx.gqa_decode_attention_paged(q, self.arena, li, self.max_seq_len)
+                attn.reshape([self.batch, cfg.n_q_heads * cfg.head_dim])
             h, xn2 = lx.add_rms_norm(lx.linear_nobias(attn, lw["o"]), h, lw["post_ln"], cfg.eps)
             act = lx.silu_mul_rows(lx.linear_nobias(xn2, lw["gate_up"]), cfg.intermediate)
             mlp_out = lx.linear_nobias(act, lw["down"])
@@ -94,11 +131,14 @@ class NativeTextTower:
         return nxt
 
     def kv_bytes_per_step(self, lens) -> float:
-        """Algorithmic KV bytes attention reads in one step at cache lengths `lens`."""
-        return float(2 * sum(int(n) + 1 for n in lens) * self.cfg.n_kv_heads * self.cfg.head_dim * 2 * self.cfg.n_layers)
+        """Algorithmic KV bytes this rank's attention reads in one step at cache lengths `lens`."""
+        return float(2 * sum(int(n) + 1 for n in lens) * self.local_kv * self.cfg.head_dim * 2 * self.cfg.n_layers)
 
     def weight_bytes(self) -> float:
-        n = self.host_weights["embed"].size + self.host_weights["final_ln"].size
-        for lw in self.host_weights["layers"]:
-            n += sum(v.size for v in lw.values())
-        return float(2 * n)
+        """Bytes of weights this rank holds and reads once per step."""
+        return float(2 * self._weight_elems)
+
+    def close(self) -> None:
+        if self.bufs is not None:
+            self.bufs.close()
+            self.bufs = None

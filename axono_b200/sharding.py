@@ -9,37 +9,11 @@ with gloo on CPU.
 """
 from __future__ import annotations
 
-from typing import List, Sequence, Tuple
-
 import torch
 import torch.distributed as dist
 
 
-def shard_sequences(lens: Sequence[int], world: int) -> List[List[int]]:
-    """Assigns sequences to ranks so that KV bytes (proportional to length), not sequence counts,
-    are balanced: longest first onto the least-loaded rank.  Returns, per rank, the sorted indices
-    it owns.  Deterministic; every rank computes the same plan."""
-    if world <= 0:
-        raise ValueError("world must be positive")
-    order = sorted(range(len(lens)), key=lambda i: (-int(lens[i]), i))
-    loads = [0] * world
-    owned: List[List[int]] = [[] for _ in range(world)]
-    for i in order:
-        r = min(range(world), key=lambda j: (loads[j], j))
-        owned[r].append(i)
-        loads[r] += int(lens[i])
-    return [sorted(o) for o in owned]
-
-
-def shard_kv_heads(hq: int, hkv: int, world: int, rank: int) -> Tuple[range, range]:
-    """KV heads and query heads owned by `rank` when heads are sharded: hkv must divide evenly.
-    Query head h reads KV head h // (hq // hkv), so a rank's query heads are contiguous."""
-    if hkv % world != 0 or hq % hkv != 0:
-        raise ValueError(f"cannot shard {hkv} KV heads over {world} ranks")
-    per = hkv // world
-    group = hq // hkv
-    kv = range(rank * per, (rank + 1) * per)
-    return kv, range(kv.start * group, kv.stop * group)
+from .partition import shard_kv_heads, shard_sequences  # noqa: E402,F401 - the plans themselves need no framework
 
 
 def _device_for_backend() -> torch.device:

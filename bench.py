@@ -271,7 +271,11 @@ def run_ours(args):
     tdtype = torch.float16 if args.dtype == "f16" else torch.float32
     elem = 2 if args.dtype == "f16" else 4
     w = WORKLOADS[args.workload]
-    if args.scaling == "strong":
+    if args.shard_of > 1:
+        # one rank's share of a batch sharded over `shard_of` GPUs, run alone (the ranks are independent)
+        all_lens = seq_lengths(args.workload, 0)
+        lens = all_lens[sharding.shard_sequences(all_lens.tolist(), args.shard_of)[0]]
+    elif args.scaling == "strong":
         # one global batch, sequences assigned to ranks by KV bytes (longest first)
         all_lens = seq_lengths(args.workload, 0)
         lens = all_lens[sharding.shard_sequences(all_lens.tolist(), world)[rank]]
@@ -849,6 +853,8 @@ def main():
     ap.add_argument("--tower-len", type=int, default=16384, help="c5_tower: context length (default 16384)")
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="weak: every GPU gets its own batch; strong: one batch sharded over the GPUs")
+    ap.add_argument("--shard-of", type=int, default=1,
+                    help="run, on one GPU, rank 0's share of the batch sharded over this many GPUs")
     ap.add_argument("--dtype", default="f16", choices=["f16", "f32"], help="storage type of q/K/V (fp32 accumulation either way)")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="c5_tower on >1 GPU: fused = attention kernel writes into peers' buffers; nccl = library all-gather")

@@ -50,9 +50,10 @@ enum {
 
 /* Bits of the device error word returned by axb200_last_error(). */
 enum {
-  AXB200_ERR_WAIT_TIMEOUT = 1u,   /* a bounded mbarrier wait inside a kernel gave up */
+  AXB200_ERR_WAIT_TIMEOUT = 1u,   /* a bounded wait inside a kernel (barrier, peer flag) gave up */
   AXB200_ERR_BAD_PAGE = 2u,       /* a block-table entry was outside [0, num_pages) */
-  AXB200_ERR_CAPACITY = 4u,       /* an append found its sequence at capacity */
+  AXB200_ERR_CAPACITY = 4u,       /* an append found its sequence at capacity, or a decode call found
+                                     seq_lens[b] above max_seq_len / the pages (the excess is not read) */
   AXB200_ERR_BAD_INDEX = 8u       /* an embedding id was outside [0, vocab) */
 };
 
@@ -62,6 +63,32 @@ const char *axb200_version(void);
  * out, page ids out of range).  Synchronises the device.  No counterpart in the reference,
  * whose kernels never report (src/ops/cuda/gqa.cu:132-135 ignores launch errors). */
 unsigned int axb200_last_error(void);
+
+/* Limit, in nanoseconds of wall time, of every bounded wait inside this library's kernels (a wait
+ * on a shared-memory barrier, on a peer GPU's generation flag): a waiter that has polled that long
+ * gives up, records AXB200_ERR_WAIT_TIMEOUT and the kernel returns - nothing hangs.  Default 2 s.
+ * Launches made afterwards carry the new limit (it travels in the kernel parameters, so a captured
+ * graph keeps the limit it was captured with).  After a timeout in a call with peers the ranks'
+ * generation counters no longer agree: zero local_state and the flag arrays on every rank before the
+ * next such call.  No counterpart in the reference, whose kernels have no waits. */
+int axb200_set_wait_limit_ns(uint64_t ns);
+
+/* Who merges the chunk partials of the decode calls.  on (default): the CTA that finishes a
+ * (sequence, KV head) last merges and writes the result - one kernel per call; the arrival counters
+ * are library-owned device memory (64 regions of 4096 counters, one region per workspace pointer in
+ * use, always left zero).  off, or when a call has more than 4096 (sequence, KV head) items or no
+ * region is free: a separate combine kernel, as the reference's GqaDecodeMergeKernel
+ * (src/ops/cuda/gqa.cu:95-129).  Both forms run the same arithmetic and give identical bits. */
+int axb200_set_fused_merge(int on);
+
+/* The chunk plan of a decode call, evaluated on the host for lengths given in host memory - the same
+ * functions the kernels run on the device lengths.  For each sequence its chunk length in tokens and
+ * its number of chunks; max_chunks = partial slots per (sequence, head); grid_ctas = CTAs launched.
+ * For tests and capacity planning; the decode calls do not need it.  The reference's plan is
+ * n_splits = clamp(ceil(skv / 64), 1, 256) (src/ops/cuda/gqa.cu:157-160). */
+int axb200_gqa_chunk_plan(const int32_t *lens_host, int batch, int hq, int hkv, int d, int64_t max_seq_len,
+                          int32_t *chunk_tokens_out, int32_t *n_chunks_out, int32_t *max_chunks_out,
+                          int32_t *grid_ctas_out);
 
 /* Timing of the dominant kernel alone, for the benchmark's roofline figure: while enabled,
  * every decode call records a CUDA-event pair around its split-kernel launch on the launching
@@ -117,8 +144,9 @@ int axb200_gqa_decode_static(const void *q, const void *k, const void *v, void *
  * multiple of 64.  block_table int32 (batch, max_blocks): page ids of each sequence in
  * token order.  seq_lens int32 (batch), device memory, read by the kernel (so a captured
  * graph follows a growing cache).  max_seq_len: host-side upper bound of seq_lens, sizes
- * the grid and the scratch.  Result b equals axb200_gqa_decode on sequence b's first
- * seq_lens[b] tokens. */
+ * the grid and the scratch; a seq_lens[b] beyond what that bound covers sets AXB200_ERR_CAPACITY
+ * and only the covered tokens are attended.  Result b equals axb200_gqa_decode on sequence b's
+ * first seq_lens[b] tokens. */
 int axb200_gqa_decode_paged(const void *q, void *out, const void *k_pages, const void *v_pages,
                             const int32_t *block_table, const int32_t *seq_lens,
                             int batch, int hq, int hkv, int d,
@@ -332,6 +360,11 @@ int axb200_argmax_last_dim(const void *x, int64_t *out, int64_t rows, int cols, 
  * Tensor::CastTo: FLOAT16 <-> FLOAT32, IEEE round to nearest even. */
 int axb200_cast(const void *src, int src_dtype, void *dst, int dst_dtype, int64_t n, void *stream);
 
+/* out[i] = mean + stddev * N(0,1), i < n, from a counter-based generator: the values depend only on
+ * (seed, i).  Stands where the reference has its randn operator (src/ops/cuda/randn.cu:13-32, cuRAND
+ * seeded from std::random_device - not repeatable); used to fill KV pages for benchmarks and tests. */
+int axb200_randn(void *out, int64_t n, int dtype, float mean, float stddev, uint64_t seed, void *stream);
+
 /* The tower's projection: out (rows, out_features) = x (rows, in_features) . w (out_features,
  * in_features)^T as ONE cuBLASLt call (FLOAT16 with fp32 accumulation, or FLOAT32) - a library GEMM, as
  * the reference's LinearNoBias is (src/ops/cuda/linear.cu:105-203); outside the rewritten path.  The
@@ -364,6 +397,10 @@ int axb200_kv_arena_destroy(axb200_kv_arena *arena);
 int axb200_kv_arena_alloc_seq(axb200_kv_arena *arena, int64_t reserve_tokens, int *seq_id);
 /* Grows the sequence to hold `tokens` tokens in total (all or nothing). */
 int axb200_kv_arena_reserve(axb200_kv_arena *arena, int seq_id, int64_t tokens);
+/* Permutes the free list with a seeded generator, so that the pages handed out next are scattered over
+ * the pools the way they are in an arena that has served many sequences.  Benchmarks and tests use it
+ * to run on non-contiguous page tables. */
+int axb200_kv_arena_shuffle_free(axb200_kv_arena *arena, uint64_t seed);
 /* Returns the pages to the free list and zeroes the device-side length on `stream`. */
 int axb200_kv_arena_free_seq(axb200_kv_arena *arena, int seq_id, void *stream);
 /* Uploads the block-table rows changed since the last sync (one H2D copy on `stream`). */

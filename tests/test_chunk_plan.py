@@ -1,0 +1,83 @@
+"""The decode calls' chunk plan, evaluated on the host (no GPU): the library exports the functions its
+kernels run on the device-resident lengths (axb200_gqa_chunk_plan), so the index arithmetic - how many
+chunks each sequence gets, how long they are, that they fit one wave of CTAs - is checked here."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from axono_b200 import _capi
+
+SLOTS = 2 * 148  # CTAs resident at once on the part the plan is made for (the library's default without a GPU)
+
+
+def plan(lens, hq=16, hkv=8, d=128, max_len=None):
+    lens = np.ascontiguousarray(lens, dtype=np.int32)
+    ct = np.zeros(len(lens), np.int32)
+    n = np.zeros(len(lens), np.int32)
+    mc, grid = C.c_int32(0), C.c_int32(0)
+    st = _capi.lib().axb200_gqa_chunk_plan(lens.ctypes.data, len(lens), hq, hkv, d, int(max_len or max(1, lens.max())),
+                                           ct.ctypes.data, n.ctypes.data, C.byref(mc), C.byref(grid))
+    assert st == 0
+    return ct, n, mc.value, grid.value
+
+
+def test_one_wave_plan_balances_bytes_per_cta():
+    rng = np.random.default_rng(3000)
+    lens = rng.integers(16384, 32769, 8)
+    ct, n, max_chunks, grid = plan(lens, max_len=32768)
+    budget = SLOTS // 8
+    assert grid == budget * 8 and n.sum() <= budget and n.max() <= max_chunks
+    assert np.all(ct % 64 == 0) and np.all(ct * n >= lens) and np.all(ct * (n - 1) < lens)
+    # every CTA of the wave streams about the same run: the longest chunk is within one tile of the
+    # smallest chunk length that fits the wave at all
+    tiles = -(-lens // 64)
+    best = next(c for c in range(4, tiles.max() + 1) if np.maximum(1, -(-tiles // c)).sum() <= budget)
+    assert ct.max() <= best * 64 and ct.max() >= best * 64 - 64 * 2
+    # the old one-length-for-all rule gave ceil(512 / 4) = 128 tiles to every sequence
+    assert ct.max() < 128 * 64
+
+
+def test_one_wave_plan_edge_lengths():
+    ct, n, max_chunks, _ = plan([0, 1, 63, 64, 65, 300, 32768], max_len=32768)
+    assert n[0] == 1  # an empty sequence keeps one CTA: it writes the zero rows
+    assert list(n[1:5]) == [1, 1, 1, 1]
+    assert n.sum() <= SLOTS // 8 and n.max() <= max_chunks
+    assert np.all(ct >= 64) and ct[6] * n[6] >= 32768
+    # a chunk is never shorter than four tiles unless the sequence is
+    assert all(c >= 256 or k == 1 for c, k in zip(ct, n))
+
+
+def test_lengths_above_the_bound_are_still_covered_in_one_wave():
+    # the device plans from the real lengths: a bound that was too small costs nothing here
+    ct, n, max_chunks, _ = plan([20000, 100], max_len=4096)
+    assert ct[0] * n[0] >= 20000 and n[0] <= max_chunks
+
+
+def test_many_sequences_single_kv_head():
+    lens = np.full(32, 16385)
+    ct, n, max_chunks, grid = plan(lens, hq=2, hkv=1, max_len=16448)
+    assert grid == SLOTS and n.sum() <= SLOTS and np.all(n == n[0]) and n[0] == SLOTS // 32
+
+
+def test_large_problem_keeps_one_host_planned_length():
+    rng = np.random.default_rng(1)
+    lens = rng.integers(16384, 32769, 64)
+    ct, n, max_chunks, grid = plan(lens, max_len=32768)
+    assert np.all(ct == 4096) and np.all(n == -(-lens // 4096)) and max_chunks == 8 and grid == 8 * 8 * 64
+    # a length beyond what the grid covers is cut at the cover (the kernel also raises AXB200_ERR_CAPACITY)
+    ct2, n2, mc2, _ = plan([40000] + [30000] * 63, max_len=32768)
+    assert n2[0] == mc2
+
+
+@pytest.mark.parametrize("seed", range(5))
+def test_plan_invariants_random(seed):
+    rng = np.random.default_rng(seed)
+    batch = int(rng.integers(1, 30))
+    hkv = int(rng.choice([1, 2, 4, 8]))
+    lens = rng.integers(0, 40000, batch)
+    ct, n, max_chunks, grid = plan(lens, hq=hkv * 2, hkv=hkv, max_len=40000)
+    assert np.all(n >= 1) and np.all(n <= max_chunks) and np.all(ct % 64 == 0)
+    assert np.all(ct.astype(np.int64) * n >= np.minimum(lens, ct.astype(np.int64) * max_chunks))
+    if grid == (SLOTS // hkv) * hkv:  # planned on the device lengths
+        assert n.sum() <= SLOTS // hkv
