@@ -152,3 +152,104 @@ def attend_context_parallel(q, out, arena, layer: int, max_seq_len: int, bufs: P
         g["num_pages"], int(max_seq_len), _dtype_code(lx, q.dtype), scratch.ptr, scratch.nbytes, bufs.out_ptrs(slot),
         bufs.flag_ptrs, bufs.state_ptr, bufs.world, bufs.rank, lx.current_stream()), "gqa_decode_paged_cp")
     return out
+
+
+def write_tokens(arena, layer: int, seq: int, k, v, start: int = 0) -> None:
+    """Stores k, v - host arrays (n, hkv, d) of the arena's dtype - as tokens start .. start+n-1 of
+    sequence `seq`, as they are (no rotation).  The block table must be on the device (arena.sync())
+    and the sequence must hold the pages.  The caller sets the lengths."""
+    import numpy as np
+
+    lx = native.load()
+    g = arena.geometry()
+    n, hkv, d = k.shape
+    if hkv != g["hkv"] or d != g["d"] or v.shape != k.shape:
+        raise RuntimeError("write_tokens: k / v do not match the arena")
+    if n == 0:
+        return
+    dev = "cuda:%d" % lx.current_device()
+    kd = lx.Tensor.from_numpy(np.ascontiguousarray(k), dev)
+    vd = lx.Tensor.from_numpy(np.ascontiguousarray(v), dev)
+    if kd.dtype != g["dtype"]:
+        raise RuntimeError("write_tokens: dtype differs from the arena's")
+    row = arena.block_table_ptr + seq * g["max_blocks"] * 4
+    _capi.check(_capi.lib().axb200_kv_prefill_write(
+        None, kd.data_ptr, vd.data_ptr, arena.k_pages_ptr(layer), arena.v_pages_ptr(layer), row, None, None, 1.0, 0, 0,
+        0, 0, n, 0, hkv, d, g["page_tokens"], g["max_blocks"], g["num_pages"], int(start), _dtype_code(lx, kd.dtype),
+        lx.current_stream()), "kv_prefill_write")
+    lx.synchronize()  # kd / vd may go back to the pool now
+
+
+def multi_gpu_parity(rdv: Rendezvous, device: str, iterations: int = 6) -> dict:
+    """The two cross-GPU forms of decode attention against the same attention computed locally, on small
+    seeded inputs: (gather) KV heads sharded, rows stored into every rank's buffer - against attention
+    over all heads of an unsharded copy of the cache; (cp) every sequence's pages dealt round-robin to
+    the ranks, partials exchanged and merged - against the unsharded cache.  Returns the largest
+    normalised errors over all ranks.  Every rank of the job must call it."""
+    import numpy as np
+
+    from . import partition
+
+    lx = native.load()
+    f16 = lx.DataType.FLOAT16
+    world, rank = rdv.world, rdv.rank
+    rng = np.random.default_rng(7000)
+    hq, hkv, d, page = 16, 8, 128, 64
+    lens = [3000, 2999, 64, 1000, 2049]
+    B, L = len(lens), max(lens)
+    q = rng.standard_normal((B, hq, d)).astype(np.float16)
+    k = (0.5 * rng.standard_normal((B, L, hkv, d))).astype(np.float16)
+    v = (0.5 * rng.standard_normal((B, L, hkv, d))).astype(np.float16)
+
+    def arena_of(n_heads, rows_k, rows_v, lengths):
+        blocks = (L + page - 1) // page
+        a = lx.KVArena(1, B * blocks, n_heads, page, d, f16, B, blocks)
+        for _ in range(B):
+            a.alloc_seq(L)
+        a.sync()
+        for b in range(B):
+            write_tokens(a, 0, b, rows_k[b], rows_v[b])
+        a.set_seq_lens(np.asarray(lengths, np.int32))
+        return a
+
+    def rel(got, want):
+        got, want = got.astype(np.float32), want.astype(np.float32)
+        return float(np.abs(got - want).max() / max(np.abs(want).max(), 1e-30))
+
+    full = arena_of(hkv, [k[b, : lens[b]] for b in range(B)], [v[b, : lens[b]] for b in range(B)], lens)
+    to_dev = lambda a: lx.Tensor.from_numpy(np.ascontiguousarray(a), device)  # noqa: E731
+
+    # ---- KV heads sharded, attention fused with the all-gather ----
+    kvh, qh = partition.shard_kv_heads(hq, hkv, world, rank)
+    local = arena_of(len(kvh), [k[b, : lens[b], kvh.start:kvh.stop] for b in range(B)],
+                     [v[b, : lens[b], kvh.start:kvh.stop] for b in range(B)], lens)
+    bufs = PeerBuffers(rdv, B, hq, d, f16, slots=2, device=device)
+    scratch = Scratch(B, len(qh), len(kvh), d, L, f16, device)
+    err_gather = 0.0
+    for it in range(iterations):  # several generations, alternating buffers, another q every time
+        qi = (q.astype(np.float32) * (1.0 + 0.01 * it)).astype(np.float16)
+        want = lx.gqa_decode_attention_paged(to_dev(qi), full, 0, L).numpy()
+        got = attend_gather(to_dev(qi[:, qh.start:qh.stop]), local, 0, L, bufs, it % 2, scratch)
+        lx.synchronize()
+        err_gather = max(err_gather, rel(got.numpy(), want))
+    bufs.close()
+
+    # ---- context parallel: pages dealt round-robin, one sequence of which some ranks hold nothing ----
+    lens_cp = [3000, 2999, 40, 1000, 2049]
+    full_cp = arena_of(hkv, [k[b, : lens_cp[b]] for b in range(B)], [v[b, : lens_cp[b]] for b in range(B)], lens_cp)
+    mine = [partition.shard_tokens_by_page(lens_cp[b], page, world, rank) for b in range(B)]
+    part = arena_of(hkv, [k[b, mine[b]] for b in range(B)], [v[b, mine[b]] for b in range(B)], [len(m) for m in mine])
+    recs = PeerBuffers(rdv, B, hq, d, f16, slots=2, kind="records", device=device)
+    scratch_cp = Scratch(B, hq, hkv, d, L, f16, device)
+    out = lx.Tensor(f16, [B, hq, d], device)
+    err_cp = 0.0
+    for it in range(iterations):
+        qi = (q.astype(np.float32) * (1.0 + 0.01 * it)).astype(np.float16)
+        want = lx.gqa_decode_attention_paged(to_dev(qi), full_cp, 0, L).numpy()
+        attend_context_parallel(to_dev(qi), out, part, 0, L, recs, it % 2, scratch_cp)
+        lx.synchronize()
+        err_cp = max(err_cp, rel(out.numpy(), want))
+    recs.close()
+    bits = int(lx.device_error_bits())
+    return {"gather": rdv.max(err_gather), "cp": rdv.max(err_cp), "ranks": world, "device_error_bits": int(rdv.max(bits)),
+            "tolerance": 1e-3}

@@ -3,27 +3,37 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
 Workload (default `c3_ragged`): long-context split-K decode attention in fp16 with fp32
-accumulation - batch 64 per GPU, 16 query / 8 KV heads, head_dim 128, per-sequence KV lengths
-uniform in [16384, 32768], K/V = 0.5 * N(0,1), q = N(0,1), all seeded and synthetic.  `b64_l32k`
-is the same with every sequence at 32768 tokens.  A step is one decode step of the path for the
-whole batch: RoPE + KV-cache append of the new token (1 kernel), then the split-K decode attention
-(split kernel + combine kernel) over the paged cache.
+accumulation - one batch of 64 sequences, 16 query / 8 KV heads, head_dim 128, per-sequence KV lengths
+uniform in [16384, 32768], K/V = 0.5 * N(0,1), q = N(0,1), all seeded and synthetic.  On N GPUs that
+batch is sharded over the ranks by KV bytes (`--scaling strong`, the default; `weak` gives every GPU
+its own batch of 64).  `b64_l32k` is the same with every sequence at 32768 tokens.  A step is one
+decode step of the path for the whole batch: RoPE + KV-cache append of the new token (1 kernel), then
+the split-K decode attention over the paged cache (1 kernel: the CTA that finishes a sequence's last
+chunk merges the partials).
+
+The default arm runs on the native runtime - libaxono tensors, the KV arena, the C ABI - with no
+PyTorch in the process at any N; ranks meet over a local socket (axono_b200.rendezvous).
 
 One JSON line on rank 0.  `value` = KV-cache GB/s of the whole job with inputs resident in HBM:
 algorithmic bytes (K and V read once, q read, out written) of all ranks / device time of the timed
-steps (CUDA events, max over ranks).  `e2e` = the same metric through the public API with host
-buffers: each step copies q, k_new, v_new from pinned host memory and reads the attention output
-back.  `roofline` = the split kernel alone (event pairs recorded around its launches by the
-library) against the measured HBM peak.  `cpu_baseline` = the reference's CPU SDPA-GQA on the
-host cores, on a bounded sample of the same sequences.
+steps (CUDA events, max over ranks).  `e2e` = the same metric through the host-buffer entry point:
+each step copies q, k_new, v_new from pinned host memory and reads the attention output back.
+`roofline` = the split kernel alone (event pairs recorded around its launches by the library) against
+the measured HBM peak.  `cpu_baseline` = the reference's CPU SDPA-GQA on the host cores, on a bounded
+sample of the same sequences.  `extra` carries, for the record: a check of the timed output against the
+CPU checker, the batch-64 x 32 K case, the 28-layer text-tower step (`c5_tower`, KV heads sharded over
+the GPUs with the attention kernel storing into every rank's gathered buffer) and, on several GPUs,
+the weak-scaling figure with identical lengths on every rank; `parity` (N > 1) = the two cross-GPU
+forms of attention against the same attention computed locally.
 
-`--impl reference` times only that CPU path (oracle/_ref when built, else the C restatement).
+`--impl reference` times only the CPU path (oracle/_ref when built, else the C restatement), the whole
+batch of 64 sequences per step.
 
 Other workloads, each with its own JSON line: `c2_block` (the fused decode block, batch 8, KV 8192, one
-CUDA graph), `c5_tower` (the 28-layer text-tower decode step; `--runtime native` runs it on the native
-runtime with no PyTorch in the process), `prefill` (causal prefill attention; `--dtype f32` for the
-reference's own type), `ops` (the standalone operators at the multimodal prompt's shapes);
-`--impl reference-cuda` times the reference's own CUDA kernels compiled for sm_100.
+CUDA graph), `c5_tower` (the text-tower step by itself; `--runtime torch` runs it on the torch-tensor
+mirror), `prefill` (causal prefill attention; `--dtype f32` for the reference's own type), `ops` (the
+standalone operators at the multimodal prompt's shapes); `--impl reference-cuda` times the reference's
+own CUDA kernels compiled for sm_100; `--runtime torch` runs the attention workload on the torch mirror.
 """
 from __future__ import annotations
 
@@ -48,9 +58,9 @@ METRIC = "gqa_decode_kv_cache_bandwidth"
 UNIT = "GB/s"
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
-# DRAM bytes moved per algorithmic byte by the split kernel, from the ncu capture summarised in
-# profiles/gqa_split_f16_paged.c2_b8_l8k.ncu.md: (dram read + write) / algorithmic bytes on a small case
-# of the same kernel, taken to scale in proportion to the tokens a launch processes.
+# DRAM bytes moved per algorithmic byte by the split kernel, from an ncu capture of a batch-8 case of the
+# same kernel: (dram read + write) / algorithmic bytes, taken to scale in proportion to the tokens a
+# launch processes.
 TRAFFIC_PER_ALGO_BYTE = 1.026
 
 WORKLOADS = {
@@ -60,10 +70,23 @@ WORKLOADS = {
 }
 
 
-def seq_lengths(workload: str, rank: int) -> np.ndarray:
+def seq_lengths(workload: str, rank: int = 0) -> np.ndarray:
+    """The workload's batch of lengths (seeded).  Every rank draws the same batch: under strong scaling
+    it is sharded, under weak scaling every GPU runs a copy, so that nothing but the hardware can make
+    the ranks differ."""
     w = WORKLOADS[workload]
-    rng = np.random.default_rng(3000 + rank)
+    rng = np.random.default_rng(3000)
     return rng.integers(w["lo"], w["hi"] + 1, w["batch"]).astype(np.int64)
+
+
+def common_config(workload: str, world: int, scaling: str) -> dict:
+    """The workload as both arms describe it."""
+    w = WORKLOADS[workload]
+    return {"workload": workload, "global_batch": w["batch"] * (world if scaling == "weak" else 1), "hq": HQ, "hkv": HKV,
+            "head_dim": D, "kv_len": [int(w["lo"]), int(w["hi"])], "page_tokens": PAGE_TOKENS,
+            "sharding": f"batch x{world}, no collective on the attention path",
+            "l2": "inputs larger than L2 (several GB of KV per step)",
+            "step": "kv_append_rope + gqa_decode_paged"}
 
 
 def algo_bytes(lens: np.ndarray, elem: int = 2) -> float:
@@ -87,7 +110,7 @@ class ClockSampler:
     REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
                0x4: "sw_power_cap", 0x80: "hw_power_brake_slowdown"}
 
-    def __init__(self, torch_index: int, use_torch: bool = True):
+    def __init__(self, torch_index: int, use_torch: bool = True, pci_bus_id: str = ""):
         self.samples, self.reasons, self.max_mhz = [], set(), None
         self._stop = threading.Event()
         self._active = threading.Event()
@@ -98,6 +121,9 @@ class ClockSampler:
             pynvml.nvmlInit()
             self.nv = pynvml
             try:
+                if pci_bus_id:  # the CUDA runtime's name for the GPU: the same device whatever NVML's order
+                    self.h = pynvml.nvmlDeviceGetHandleByPciBusId(pci_bus_id.encode())
+                    raise StopIteration
                 if not use_torch:  # a process without PyTorch: NVML's own index (no CUDA_VISIBLE_DEVICES remapping)
                     raise LookupError
                 import torch
@@ -106,6 +132,8 @@ class ClockSampler:
                 if not uuid.startswith("GPU-"):
                     uuid = "GPU-" + uuid
                 self.h = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            except StopIteration:
+                pass
             except Exception:
                 self.h = pynvml.nvmlDeviceGetHandleByIndex(torch_index)
             self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
@@ -193,25 +221,28 @@ def cpu_attention_sample(workload: str, budget_s: float, max_seqs: int):
 
 
 def run_reference_arm(args):
+    """The reference's CPU SDPA-GQA over the whole batch: a step = one fp32 SDPA call per sequence of the
+    workload's batch (the reference's op takes one sequence), all host threads, tensors wrapped once
+    outside the timed region.  Rank 0 alone runs it."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    # a step = the first `per_step` sequences of the batch, one CPU SDPA call each
     import oracle
 
     orc = oracle.best()
     cores = use_all_host_threads()
-    lens = seq_lengths(args.workload, 0)
-    per_step = 2
+    lens = seq_lengths(args.workload)
     rng = np.random.default_rng(4000)
+    pool_k = (0.5 * rng.standard_normal((int(lens.max()) + 4096, HKV, D))).astype(np.float32)
+    pool_v = (0.5 * rng.standard_normal((int(lens.max()) + 4096, HKV, D))).astype(np.float32)
     calls = []
-    for b in range(per_step):
-        L = int(lens[b])
-        calls.append(orc.prepare_sdpa(rng.standard_normal((1, HQ, D)).astype(np.float32),
-                                      (0.5 * rng.standard_normal((L, HKV, D))).astype(np.float32),
-                                      (0.5 * rng.standard_normal((L, HKV, D))).astype(np.float32)))
-    step_bytes = algo_bytes(lens[:per_step])
-    for _ in range(args.warmup):
+    for b, L in enumerate(lens):  # every sequence its own memory; contents = the pools at a per-sequence offset
+        off = int(rng.integers(0, 4096))
+        k = np.ascontiguousarray(pool_k[off : off + int(L)])
+        v = np.ascontiguousarray(pool_v[off : off + int(L)])
+        calls.append(orc.prepare_sdpa(rng.standard_normal((1, HQ, D)).astype(np.float32), k, v))
+    step_bytes = algo_bytes(lens)
+    for _ in range(min(args.warmup, 2)):  # a CPU pass needs no more warming than that
         for run, _, _ in calls:
             run()
     t0 = time.perf_counter()
@@ -222,25 +253,330 @@ def run_reference_arm(args):
     for _, _, release in calls:
         release()
     value = step_bytes * args.steps / dt / 1e9
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    scaling = args.scaling or "strong"
+    sample = (f"all {len(lens)} sequences of workload {args.workload} per step (lengths {int(lens.min())}..{int(lens.max())}), "
+              f"one fp32 SDPA call each; bytes counted as the workload's fp16 KV bytes; the reference parallelises over "
+              f"its 16 query heads only; warm-up passes capped at 2")
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic",
-        "config": {"workload": args.workload, "batch_per_gpu": WORKLOADS[args.workload]["batch"],
-                   "hq": HQ, "hkv": HKV, "head_dim": D,
-                   "note": "CPU reference: each step = the first 2 sequences of the batch, one fp32 SDPA call each, tensors wrapped once outside the timed region"},
-        "tokens_per_s": per_step * args.steps / dt,
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": orc.kind,
-                         "sample": f"{per_step} sequences per step (lengths {lens[:per_step].tolist()}), fp32 SDPA, "
-                                   f"bytes counted as the workload's fp16 KV bytes"},
+        "higher_is_better": True, "scaling": scaling, "vs_baseline": None, "dtype": args.dtype,
+        "data": "synthetic", "config": common_config(args.workload, world, scaling),
+        "arithmetic": "fp32 on the CPU (the only type the reference's op takes)",
+        "tokens_per_s": len(lens) * args.steps / dt,
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": orc.kind, "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
 
 
-# ---- our arm ---------------------------------------------------------------------------------------
+# ---- our arm on the native runtime (no PyTorch in the process) ---------------------------------------
+class NativeStep:
+    """One rank's decode step of the attention workload on the native runtime: a KV arena with `lens`
+    cached tokens per sequence on scattered pages (contents 0.5 * N(0,1), seeded), q / k_new / v_new
+    resident on the device, and `step()` = kv_append_rope + gqa_decode_attention_paged."""
+
+    def __init__(self, lx, device, lens, capacity, dtype_name, seed):
+        self.lx, self.device = lx, device
+        self.lens = np.asarray(lens, np.int64)
+        self.B = len(self.lens)
+        self.dtype = lx.DataType.FLOAT16 if dtype_name == "f16" else lx.DataType.FLOAT32
+        self.np_dtype = np.float16 if dtype_name == "f16" else np.float32
+        self.elem = 2 if dtype_name == "f16" else 4
+        blocks = (capacity + PAGE_TOKENS - 1) // PAGE_TOKENS
+        self.capacity = blocks * PAGE_TOKENS
+        self.arena = lx.KVArena(1, self.B * blocks, HKV, PAGE_TOKENS, D, self.dtype, self.B, blocks)
+        self.arena.shuffle_free(99 + seed)  # sequences do not own contiguous runs of pages
+        for _ in range(self.B):
+            self.arena.alloc_seq(self.capacity)
+        self.arena.sync()
+        self.arena.fill_normal(1234 + seed, 0.5)  # K, V = 0.5 * N(0,1), generated on the device
+        rng = np.random.default_rng(4321 + seed)
+        mk = lambda h, s: lx.Tensor.from_numpy((s * rng.standard_normal((self.B, h, D))).astype(self.np_dtype), device)  # noqa: E731
+        self.q, self.k_new, self.v_new = mk(HQ, 1.0), mk(HKV, 0.5), mk(HKV, 0.5)
+        self.out = lx.Tensor(self.dtype, [self.B, HQ, D], device)
+        self.bound = 0
+        self.set_lengths(self.lens)
+
+    def set_lengths(self, lens):
+        self.cur = np.asarray(lens, np.int64).copy()
+        self.arena.set_seq_lens(self.cur.astype(np.int32))
+        self.bound = int(self.cur.max())
+
+    def step(self):
+        self.lx.kv_append_rope(self.arena, 0, self.q, self.k_new, self.v_new, theta=1e6)
+        self.cur += 1
+        self.bound = min(self.capacity, self.bound + 1)
+        self.lx.gqa_decode_attention_paged(self.q, self.arena, 0, self.bound, out=self.out)
+
+    def attend(self):
+        self.lx.gqa_decode_attention_paged(self.q, self.arena, 0, max(self.bound, 1), out=self.out)
+
+    def bytes_of_steps(self, count):
+        """Algorithmic bytes of the next `count` steps from the current lengths."""
+        return sum(algo_bytes(self.cur + s + 1, self.elem) for s in range(count))
+
+    def timed_steps(self, rdv, steps, sampler=None):
+        """K steps between two CUDA events, a barrier and a device synchronisation on both sides;
+        returns (max over ranks of the device milliseconds, this rank's algorithmic bytes)."""
+        lx = self.lx
+        my_bytes = self.bytes_of_steps(steps)
+        timer = lx.EventTimer()
+        lx.synchronize()
+        rdv.barrier()
+        if sampler:
+            sampler.start()
+        timer.start()
+        for _ in range(steps):
+            self.step()
+        timer.stop()
+        ms = timer.elapsed_ms()
+        lx.synchronize()
+        rdv.barrier()
+        if sampler:
+            sampler.pause()
+        return rdv.max(ms), my_bytes
+
+    def kernel_alone(self, steps):
+        """The split kernel by itself: event pairs the library records around its launches."""
+        lx = self.lx
+        lx.profile_enable(True)
+        for _ in range(steps):
+            self.attend()
+        ms_total, launches = lx.profile_collect()
+        lx.profile_enable(False)
+        return ms_total / max(launches, 1), launches
+
+    def host_steps(self, rdv, steps, warmup):
+        """The same step through the host-buffer entry point: q, k_new, v_new come from pinned host
+        memory and the attention output goes back to it, every step, inside the timed region."""
+        lx = self.lx
+        shape_q, shape_k = [self.B, HQ, D], [self.B, HKV, D]
+        q_h, out_h = lx.pinned_empty(shape_q, self.dtype), lx.pinned_empty(shape_q, self.dtype)
+        k_h, v_h = lx.pinned_empty(shape_k, self.dtype), lx.pinned_empty(shape_k, self.dtype)
+        q_h[...] = self.q.numpy()
+        k_h[...] = self.k_new.numpy()
+        v_h[...] = self.v_new.numpy()
+        q_d, o_d = lx.Tensor(self.dtype, shape_q, self.device), lx.Tensor(self.dtype, shape_q, self.device)
+        k_d, v_d = lx.Tensor(self.dtype, shape_k, self.device), lx.Tensor(self.dtype, shape_k, self.device)
+        ws = lx.Tensor(lx.DataType.INT8, [max(256, lx.gqa_workspace_bytes(self.B, HQ, HKV, D, self.capacity, self.dtype))],
+                       self.device)
+
+        def one():
+            self.cur += 1
+            self.bound = min(self.capacity, self.bound + 1)
+            lx.decode_step_host(self.arena, 0, q_h, k_h, v_h, out_h, q_d, k_d, v_d, o_d, ws, self.bound, 1e6)
+
+        for _ in range(warmup):
+            one()
+        my_bytes = self.bytes_of_steps(steps)
+        lx.synchronize()
+        rdv.barrier()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            one()
+        dt = time.perf_counter() - t0
+        rdv.barrier()
+        return rdv.max(dt), my_bytes, (q_h.nbytes + k_h.nbytes + v_h.nbytes), out_h.nbytes
+
+    def check_output(self, rows):
+        """The attention output of the last step against the CPU checker on `rows` of this batch."""
+        import oracle
+
+        orc = oracle.best()
+        q = self.q.numpy().astype(np.float32)
+        out = self.out.numpy().astype(np.float32)
+        worst = 0.0
+        for b in rows:
+            k, v = self.arena.gather(0, int(b), int(self.cur[b]))
+            ref = orc.gqa_decode(q[b : b + 1], k.astype(np.float32), v.astype(np.float32))
+            worst = max(worst, float(oracle.rel_err(out[b : b + 1], ref)))
+        return {"rows": [int(b) for b in rows], "lengths": [int(self.cur[b]) for b in rows], "rel_err": worst,
+                "checker": orc.kind, "tolerance": 2e-3 if self.elem == 2 else 1e-5}
+
+    def close(self):
+        self.arena = None
+
+
+def tower_figures(args, lx, rdv, device, sampler=None):
+    """The 28-layer text-tower decode step (batch 32, context 16384, random fp16 weights) as one captured
+    graph on the native runtime, KV heads sharded over the ranks with the attention kernel storing into
+    every rank's gathered buffer.  Returns the figures for `extra.c5_tower`."""
+    from axono_b200 import native
+    from axono_b200.native_tower import NativeTextTower
+    from axono_b200.tower_config import TextTowerConfig
+
+    B, L = args.tower_batch, args.tower_len
+    cfg = TextTowerConfig()
+    steps = max(3, min(args.steps, 20))
+    warm = max(3, min(args.warmup, 5))
+    tower = NativeTextTower(cfg, B, L + 2 * (steps + warm) + 72, seed=5, device=device, rdv=rdv)
+    tower.arena.fill_normal(77 + rdv.rank, 0.5)
+    lens = [L] * B
+    tower.set_state(np.arange(B) % cfg.vocab, lens)
+    g = native.CUDAGraph().capture(tower.decode_step)
+    tower.set_state(np.arange(B) % cfg.vocab, lens)  # the capture's warm-up run was a real step
+    for _ in range(warm):
+        g.replay()
+    lx.synchronize()
+    rdv.barrier()
+    step_ms = rdv.max(g.replay_timed(steps))  # CUDA events on the capture stream around the replays
+    rdv.barrier()
+    tokens = g.output.numpy()
+    same = rdv.all_gather_object(tokens.tolist())
+    bits = int(rdv.max(lx.device_error_bits()))
+    kv_bytes, w_bytes = tower.kv_bytes_per_step(lens), tower.weight_bytes()
+    peak, kind = measured_peak()
+    out = {"tokens_per_s": B / (step_ms / 1e3), "ms_per_step": step_ms, "batch": B, "kv_len": L, "steps": steps,
+           "hbm_floor_ms": (kv_bytes + w_bytes) / (peak * 1e9) * 1e3, "peak_source": f"of {kind}",
+           "graph_nodes": int(g.num_nodes), "nodes_per_layer": round((int(g.num_nodes) - 5) / cfg.n_layers, 2),
+           "kv_gb_per_gpu": kv_bytes / 1e9, "weights_gb_per_gpu": w_bytes / 1e9,
+           "sharding": f"KV heads x{rdv.world}" + (", attention kernel stores into every rank's buffer over NVLink"
+                                                   if rdv.world > 1 else ""),
+           "ranks_agree_on_tokens": all(t == same[0] for t in same), "device_error_bits": bits}
+    g.reset()
+    tower.close()
+    return out
+
+
+def run_native(args):
+    """The attention workload on the native runtime; no PyTorch is imported at any N."""
+    from axono_b200 import native, partition
+    from axono_b200.rendezvous import Rendezvous
+
+    lx = native.load()
+    if not lx.cuda_available():
+        raise SystemExit("bench.py needs a CUDA device: the decode path has no CPU fallback")
+    rdv = Rendezvous.from_env()
+    world, rank = rdv.world, rdv.rank
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    lx.set_device(local_rank)
+    device = f"cuda:{local_rank}"
+    scaling = args.scaling or "strong"
+    w = WORKLOADS[args.workload]
+    elem = 2 if args.dtype == "f16" else 4
+    all_lens = seq_lengths(args.workload)
+    if args.shard_of > 1:  # one rank's share of the batch sharded over `shard_of` GPUs, run alone
+        lens = all_lens[partition.shard_sequences(all_lens.tolist(), args.shard_of)[0]]
+    elif scaling == "strong":  # one global batch, sequences assigned to ranks by KV bytes (longest first)
+        lens = all_lens[partition.shard_sequences(all_lens.tolist(), world)[rank]]
+    else:
+        lens = all_lens
+    total_steps = 2 * (args.warmup + args.steps) + 2100
+    capacity = int(w["hi"]) + total_steps + 64
+    sampler = ClockSampler(local_rank, use_torch=False, pci_bus_id=lx.device_pci_bus_id(local_rank))
+    peak, peak_kind = measured_peak()
+
+    parity = None
+    if world > 1:  # the cross-GPU forms of attention against the same attention computed locally
+        from axono_b200.native_multi import multi_gpu_parity
+
+        parity = multi_gpu_parity(rdv, device)
+        if max(parity["gather"], parity["cp"]) > parity["tolerance"] or parity["device_error_bits"]:
+            raise SystemExit(f"multi-GPU parity failed: {parity}")
+
+    run = NativeStep(lx, device, lens, capacity, args.dtype, seed=rank)
+    B = run.B
+    # ---- value: inputs resident, CUDA events around K steps ----
+    for _ in range(args.warmup):
+        run.step()
+    dev_ms, my_bytes = run.timed_steps(rdv, args.steps, sampler)
+    all_bytes = rdv.sum(my_bytes)
+    value = all_bytes / (dev_ms / 1e3) / 1e9
+    total_seqs = rdv.sum(B)
+    tokens_per_s = total_seqs * args.steps / (dev_ms / 1e3)
+    err = lx.device_error_bits()
+    if err:
+        raise SystemExit(f"device error word {err:#x} after the timed steps")
+    check = run.check_output([0, B - 1] if B > 1 else [0]) if rank == 0 and not args.no_check else None
+    if check and check["rel_err"] > check["tolerance"]:
+        raise SystemExit(f"the timed output differs from the CPU checker: {check}")
+
+    # ---- roofline: the split kernel alone, event pairs around its launches ----
+    run.set_lengths(lens)
+    kern_ms, launches = run.kernel_alone(min(args.steps, 2000))
+    launch_bytes = algo_bytes(lens, elem)
+    achieved = launch_bytes / (kern_ms / 1e3) / 1e9
+    roofline = {"bound": "hbm", "kernel": f"gqa_split_{args.dtype}_kernel<paged>", "achieved": achieved, "peak": peak,
+                "unit": "GB/s", "frac": achieved / peak, "peak_source": f"of {peak_kind}",
+                "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS, "kernel_ms": kern_ms,
+                "launches_timed": launches, "algorithmic_bytes_per_launch": launch_bytes,
+                "traffic": None if TRAFFIC_PER_ALGO_BYTE is None else TRAFFIC_PER_ALGO_BYTE * launch_bytes}
+
+    # ---- e2e: the host-buffer entry point, copies inside the timed region ----
+    run.set_lengths(lens)
+    e2e_s, e2e_my_bytes, h2d, d2h = run.host_steps(rdv, args.steps, max(3, args.warmup // 2))
+    e2e_bytes = rdv.sum(e2e_my_bytes)
+    e2e = {"value": e2e_bytes / e2e_s / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+           "ms_per_step": e2e_s / args.steps * 1e3, "tokens_per_s": total_seqs * args.steps / e2e_s}
+    clocks = sampler.summary()
+
+    extra = {}
+    if check:
+        extra["output_check"] = check
+    full = args.workload == "c3_ragged" and not args.no_extra and args.dtype == "f16" and args.shard_of == 1
+    if full and world == 1:
+        # the target case, batch 64 x 32 K: the kernel alone, the step, and the step with host buffers
+        lens32 = np.full(B, 32768, np.int64)
+        run.set_lengths(lens32)
+        for _ in range(3):
+            run.step()
+        run.set_lengths(lens32)
+        ms32, b32 = run.timed_steps(rdv, 20)
+        run.set_lengths(lens32)
+        k32, _ = run.kernel_alone(100)
+        run.set_lengths(lens32)
+        s32, eb32, _, _ = run.host_steps(rdv, 20, 3)
+        gbs = algo_bytes(lens32) / (k32 / 1e3) / 1e9
+        extra["b64_l32k"] = {"split_kernel_ms": k32, "kv_gbs": gbs, "frac_of_measured": gbs / peak,
+                             "frac_of_nominal_8TBs": gbs / NOMINAL_HBM_GBS,
+                             "step_ms": ms32 / 20, "step_kv_gbs": b32 / (ms32 / 1e3) / 1e9,
+                             "step_frac_of_nominal_8TBs": b32 / (ms32 / 1e3) / 1e9 / NOMINAL_HBM_GBS,
+                             "tokens_per_s": B * 20 / (ms32 / 1e3),
+                             "e2e_ms_per_step": s32 / 20 * 1e3, "e2e_kv_gbs": eb32 / s32 / 1e9}
+    run.close()
+    del run
+    if full and world > 1:
+        # weak scaling for the record: every GPU runs the same batch of 64 with the same lengths, so the
+        # figure can only fall below N times one GPU's if the hardware makes it
+        wk = NativeStep(lx, device, all_lens, capacity, args.dtype, seed=0)
+        for _ in range(args.warmup):
+            wk.step()
+        wms, wbytes = wk.timed_steps(rdv, args.steps)
+        extra["weak"] = {"value": rdv.sum(wbytes) / (wms / 1e3) / 1e9, "unit": UNIT, "ms_per_step": wms / args.steps,
+                         "batch_per_gpu": int(wk.B), "lengths": "identical on every rank"}
+        wk.close()
+        del wk
+    if full and not args.no_tower:
+        extra["c5_tower"] = tower_figures(args, lx, rdv, device)
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        gbs, tps, spent, info = cpu_attention_sample(args.workload, args.cpu_budget, 64)
+        cpu = {"value": gbs, "unit": UNIT, "tokens_per_s": tps, "seconds": spent, **info}
+
+    assert "torch" not in sys.modules, "the native arm must not pull PyTorch into the process"
+    seqs_per_gpu = [int(x) for x in rdv.all_gather_object(B)]
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True,
+            "scaling": scaling, "vs_baseline": None, "dtype": args.dtype, "data": "synthetic",
+            "config": common_config(args.workload, world, scaling),
+            "runtime": "native (libaxono tensors, KV arena, C ABI; no PyTorch in the process)",
+            "sequences_per_gpu": seqs_per_gpu,
+            "tokens_per_s": tokens_per_s,
+            "frac_of_nominal_8TBs": value / (NOMINAL_HBM_GBS * world),
+            "e2e": e2e, "gpu_launches": 2 * args.steps, "clocks": clocks, "roofline": roofline,
+            "cpu_baseline": cpu, "parity": parity, "extra": extra,
+        }
+        print(json.dumps(line), flush=True)
+    rdv.close()
+
+
+# ---- the same workload on the torch-tensor mirror (--runtime torch) ------------------------------------
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -579,58 +915,33 @@ def run_tower(args):
 
 
 def run_tower_native(args):
-    """`c5_tower --runtime native`: the same 28-layer decode step on the native runtime - libaxono tensors,
-    cuBLASLt projections, one captured graph - with no PyTorch in the process.  One GPU."""
+    """`c5_tower`: the 28-layer decode step on the native runtime - libaxono tensors, cuBLASLt projections,
+    one captured graph, KV heads sharded over the ranks - with no PyTorch in the process."""
     from axono_b200 import native
-    from axono_b200.native_tower import NativeTextTower
-    from axono_b200.tower_config import TextTowerConfig
+    from axono_b200.rendezvous import Rendezvous
 
-    if int(os.environ.get("WORLD_SIZE", "1")) != 1:
-        raise SystemExit("--runtime native runs on one GPU")
     lx = native.load()
-    B, L = args.tower_batch, args.tower_len
-    cfg = TextTowerConfig()
-    total_steps = args.warmup + 2 * args.steps + 4
-    tower = NativeTextTower(cfg, B, L + total_steps + 64, seed=5)
-    rng = np.random.default_rng(77)
-    tower.arena.fill_pages((0.5 * rng.standard_normal(1 << 22, dtype=np.float32)).astype(np.float16))
-    lens = [L] * B
-    tower.set_state(np.arange(B) % cfg.vocab, lens)
-    g = native.CUDAGraph().capture(tower.decode_step)
-    tower.set_state(np.arange(B) % cfg.vocab, lens)  # the capture's warm-up run was a real step
-    for _ in range(args.warmup):
-        g.replay()
-    sampler = ClockSampler(0, use_torch=False)
+    rdv = Rendezvous.from_env()
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    lx.set_device(local_rank)
+    sampler = ClockSampler(local_rank, use_torch=False, pci_bus_id=lx.device_pci_bus_id(local_rank))
     sampler.start()
-    step_ms = g.replay_timed(args.steps)  # CUDA events on the capture stream around the K replays
+    fig = tower_figures(args, lx, rdv, f"cuda:{local_rank}")
     sampler.pause()
-    err = lx.device_error_bits()
-    if err:
-        raise SystemExit(f"device error word {err:#x}")
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        g.replay()
-        out = g.output.numpy()  # the host reads the next token ids after every step
-    e2e_s = time.perf_counter() - t0
     assert "torch" not in sys.modules
-    kv_bytes, other_bytes = tower.kv_bytes_per_step(lens), tower.weight_bytes()
-    peak, kind = measured_peak()
-    line = {
-        "metric": "decode_tokens_per_s", "value": B / (step_ms / 1e3), "unit": "tokens/s", "n_gpus": 1,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": args.workload, "runtime": "native (libaxono tensors, cuBLASLt projections, no PyTorch)",
-                   "batch": B, "kv_len": L, "cuda_graph": True, "graph_nodes": g.num_nodes, "sharding": "KV heads x1",
-                   "l2": "KV per step larger than L2"},
-        "kv_cache_gbs": kv_bytes / (step_ms / 1e3) / 1e9,
-        "kv_frac_of_measured_peak": kv_bytes / (step_ms / 1e3) / 1e9 / peak,
-        "hbm_bytes_per_step": {"kv": kv_bytes, "weights_per_gpu": other_bytes},
-        "hbm_floor_ms": (kv_bytes + other_bytes) / (peak * 1e9) * 1e3,
-        "e2e": {"value": B * args.steps / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": 0,
-                "d2h_bytes_per_step": int(out.nbytes), "ms_per_step": e2e_s / args.steps * 1e3},
-        "gpu_launches": g.num_nodes * args.steps, "clocks": sampler.summary(),
-    }
-    print(json.dumps(line), flush=True)
+    if rdv.rank == 0:
+        line = {
+            "metric": "decode_tokens_per_s", "value": fig["tokens_per_s"], "unit": "tokens/s", "n_gpus": rdv.world,
+            "steps": fig["steps"], "warmup": max(3, min(args.warmup, 5)), "ms_per_step": fig["ms_per_step"],
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": args.workload, "runtime": "native (libaxono tensors, cuBLASLt projections, no PyTorch)",
+                       "batch": fig["batch"], "kv_len": fig["kv_len"], "cuda_graph": True, "graph_nodes": fig["graph_nodes"],
+                       "sharding": fig["sharding"], "l2": "KV per step larger than L2"},
+            "hbm_floor_ms": fig["hbm_floor_ms"], "details": fig,
+            "gpu_launches": fig["graph_nodes"] * fig["steps"], "clocks": sampler.summary(),
+        }
+        print(json.dumps(line), flush=True)
+    rdv.close()
 
 
 def run_reference_cuda(args):
@@ -847,12 +1158,12 @@ def main():
     ap.add_argument("--prefill-len", type=int, default=8192)
     ap.add_argument("--ops-once", action="store_true",
                     help="ops: launch every operator once inside the profiler range and exit (for ncu)")
-    ap.add_argument("--runtime", default="torch", choices=["torch", "native"],
-                    help="c5_tower: torch = torch-tensor mirror (any N); native = libaxono runtime, no PyTorch (N = 1)")
+    ap.add_argument("--runtime", default="native", choices=["native", "torch"],
+                    help="native = libaxono runtime, no PyTorch in the process (default); torch = the torch-tensor mirror")
     ap.add_argument("--tower-batch", type=int, default=32, help="c5_tower: batch (default: the configuration's 32)")
     ap.add_argument("--tower-len", type=int, default=16384, help="c5_tower: context length (default 16384)")
-    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
-                    help="weak: every GPU gets its own batch; strong: one batch sharded over the GPUs")
+    ap.add_argument("--scaling", default=None, choices=["weak", "strong"],
+                    help="strong (default): one batch of 64 sharded over the GPUs; weak: every GPU gets its own batch")
     ap.add_argument("--shard-of", type=int, default=1,
                     help="run, on one GPU, rank 0's share of the batch sharded over this many GPUs")
     ap.add_argument("--dtype", default="f16", choices=["f16", "f32"], help="storage type of q/K/V (fp32 accumulation either way)")
@@ -861,27 +1172,33 @@ def main():
     ap.add_argument("--cpu-budget", type=float, default=10.0, help="seconds of CPU work for cpu_baseline")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-extra", action="store_true")
+    ap.add_argument("--no-check", action="store_true", help="skip the check of the timed output against the CPU checker")
+    ap.add_argument("--no-tower", action="store_true", help="skip the text-tower figures in `extra`")
     args = ap.parse_args()
+    rank0 = int(os.environ.get("RANK", "0")) == 0
     if args.impl == "reference-cuda":
-        if int(os.environ.get("RANK", "0")) == 0:
+        if rank0:
             run_reference_cuda(args)
     elif args.impl == "reference":
         if args.workload in ("c2_block", "c5_tower", "prefill", "ops"):
             args.workload = "c2_b8_l8k" if args.workload == "c2_block" else "c3_ragged"
         run_reference_arm(args)
     elif args.workload == "prefill":
-        if int(os.environ.get("RANK", "0")) == 0:
+        if rank0:
             run_prefill(args)
     elif args.workload == "ops":
-        if int(os.environ.get("RANK", "0")) == 0:
+        if rank0:
             run_small_ops(args)
     elif args.workload == "c5_tower" and args.runtime == "native":
-        if int(os.environ.get("RANK", "0")) == 0:
-            run_tower_native(args)
+        run_tower_native(args)
     elif args.workload in ("c2_block", "c5_tower"):
+        args.scaling = args.scaling or "strong"
         run_tower(args)
-    else:
+    elif args.runtime == "torch":
+        args.scaling = args.scaling or "strong"
         run_ours(args)
+    else:
+        run_native(args)
 
 
 if __name__ == "__main__":
