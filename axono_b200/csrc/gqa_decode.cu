@@ -68,7 +68,8 @@ struct DecodeParams {
   int balanced, budget;
   float scale;  // 1/sqrt(d)
   int window;       // > 0: only the last `window` tokens of each sequence are visible (sliding window)
-  int causal_rows;  // rows are the queries of one sequence: row b sees min(b + 1, fixed_len) keys
+  int causal_rows;  // rows are the queries of one sequence: row b sees min(row_offset + b + 1, fixed_len) keys
+  int row_offset;   // index of the launch's first row within that sequence
   // arrival_region >= 0: the CTA that finishes a (sequence, KV head) last merges its chunk partials and
   // writes the result itself (no combine kernel); the arrival counters are that region of g_arrival.
   // direct_ok: a sequence with a single chunk is normalised and written by its CTA, no partial.
@@ -102,7 +103,7 @@ __global__ void zero_arrival_kernel() {
 
 __device__ __forceinline__ int seq_len_raw(const DecodeParams &p, int b) {
   if (p.seq_lens) return p.seq_lens[b];
-  return p.causal_rows ? min(b + 1, p.fixed_len) : p.fixed_len;
+  return p.causal_rows ? min(p.row_offset + b + 1, p.fixed_len) : p.fixed_len;
 }
 
 // Tokens a launch can reach in one sequence: what its pages hold and, with a host-planned chunk
@@ -1340,12 +1341,15 @@ Plan make_plan(int batch, int hq, int hkv, int d, int64_t max_len) {
     chunk_tiles = (total + 8 * slots - 1) / (8 * slots);
     if (chunk_tiles < 16) chunk_tiles = 16;
     if (chunk_tiles > 64) chunk_tiles = 64;
-  } else if (items <= slots && batch <= kMaxBalancedBatch) {
+  } else if (items <= slots && batch <= kMaxBalancedBatch && g_device_plan) {
     pl.balanced = 1;
     pl.budget = (int)(slots / hkv);
     chunk_tiles = kMinChunkTiles;
   } else {
-    chunk_tiles = tiles < kMinChunkTiles ? kMinChunkTiles : tiles;
+    int64_t per_item = slots / items;  // chunks each (sequence, head) may have within one wave
+    if (per_item < 1) per_item = 1;
+    chunk_tiles = (tiles + per_item - 1) / per_item;
+    if (chunk_tiles < kMinChunkTiles) chunk_tiles = kMinChunkTiles;
   }
   while ((tiles + chunk_tiles - 1) / chunk_tiles > kMaxChunks) chunk_tiles *= 2;
   pl.chunk_tokens = (int)(chunk_tiles * 64);
@@ -1433,6 +1437,7 @@ bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 std::mutex g_settings_mu;
 unsigned long long g_wait_limit_ns = kWaitNanos;
 bool g_fused_merge = true;
+bool g_device_plan = true;
 
 // Counter region of the fused merge for launches that use `workspace` on the current device.  Two
 // launches may overlap on the GPU only if they use different workspaces (they would race on the
@@ -1459,7 +1464,7 @@ int decode_impl(bool paged, const void *q, void *out, const void *k, const void 
                 int hq, int hkv, int d, int page_tokens, int max_blocks, int num_pages,
                 int64_t max_len, int dtype, void *workspace, size_t workspace_bytes,
                 cudaStream_t st, const GatherParams *gather = nullptr, int window = 0,
-                int causal_rows = 0) {
+                int causal_rows = 0, int row_offset = 0) {
   if (dtype != AXB200_FLOAT16 && dtype != AXB200_FLOAT32) return AXB200_UNSUPPORTED_TYPE;
   if (!q || (!out && !(gather && gather->mode == 0)) || !k || !v) return AXB200_INVALID_PTR;
   if (batch <= 0 || hq <= 0 || hkv <= 0 || d <= 0 || max_len <= 0) return AXB200_INVALID_ARGUMENT;
@@ -1494,6 +1499,7 @@ int decode_impl(bool paged, const void *q, void *out, const void *k, const void 
   p.scale = 1.0f / sqrtf((float)d);
   p.window = window;
   p.causal_rows = causal_rows;
+  p.row_offset = row_offset;
   {
     std::lock_guard<std::mutex> lock(g_settings_mu);
     p.wait_ns = g_wait_limit_ns;
@@ -1622,20 +1628,25 @@ void *static_scratch_ptr() {
 // the parity path, not the fast one.
 size_t sdpa_rows_workspace_bytes(int sq, int hq, int hkv, int d, int64_t skv) {
   if (sq <= 0 || hq <= 0 || hkv <= 0 || d <= 0 || skv <= 0) return 0;
-  const Plan pl = make_plan(sq, hq, hkv, d, skv);
+  const Plan pl = make_plan(sq < 65535 ? sq : 65535, hq, hkv, d, skv);  // the largest slice
   return pl.part_o_bytes + pl.part_ml_bytes;
 }
 
 int sdpa_rows_fallback(const void *q, const void *k, const void *v, void *out, int sq, int hq, int hkv,
                        int d, int64_t skv, int is_causal, int dtype, void *workspace,
                        size_t workspace_bytes, cudaStream_t st) {
-  return decode_impl(false, q, out, k, v, nullptr, nullptr, (int)skv, sq, hq, hkv, d, 0, 0, 1, skv, dtype,
-                     workspace, workspace_bytes, st, nullptr, 0, is_causal ? 1 : 0);
-}
-
-unsigned long long wait_limit_ns() {
-  std::lock_guard<std::mutex> lock(g_settings_mu);
-  return g_wait_limit_ns;
+  // the rows are the launch's batch dimension (at most 65535 to a grid): long prompts go in slices
+  constexpr int kSlice = 65535;
+  const size_t row_bytes = (size_t)hq * d * dtype_size(dtype);
+  for (int r0 = 0; r0 < sq; r0 += kSlice) {
+    const int n = sq - r0 < kSlice ? sq - r0 : kSlice;
+    const int status = decode_impl(false, static_cast<const uint8_t *>(q) + r0 * row_bytes,
+                                   static_cast<uint8_t *>(out) + r0 * row_bytes, k, v, nullptr, nullptr, (int)skv, n,
+                                   hq, hkv, d, 0, 0, 1, skv, dtype, workspace, workspace_bytes, st, nullptr, 0,
+                                   is_causal ? 1 : 0, r0);
+    if (status != AXB200_OK) return status;
+  }
+  return AXB200_OK;
 }
 
 }  // namespace axb
@@ -1646,6 +1657,12 @@ int axb200_set_wait_limit_ns(uint64_t ns) {
   if (ns == 0) return AXB200_INVALID_ARGUMENT;
   std::lock_guard<std::mutex> lock(axb::g_settings_mu);
   axb::g_wait_limit_ns = ns;
+  return AXB200_OK;
+}
+
+int axb200_set_device_plan(int on) {
+  std::lock_guard<std::mutex> lock(axb::g_settings_mu);
+  axb::g_device_plan = on != 0;
   return AXB200_OK;
 }
 

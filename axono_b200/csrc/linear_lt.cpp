@@ -57,7 +57,9 @@ const LtApi &lt_api() {
 }
 
 // One cuBLASLt handle and one 32 MB workspace per device, made on first use (outside graph capture:
-// the warm-up run of CUDAGraph.capture makes that first call); one matmul plan per (rows, out, in, dtype).
+// the warm-up run of CUDAGraph.capture makes that first call); one matmul plan per (rows, out, in, dtype,
+// alignment class).  The workspace is shared by every call on the device: calls that may overlap on the
+// GPU (different streams) would race on it - keep the projections of one device on one stream.
 struct LtState {
   cublasLtHandle_t handle = nullptr;
   void *workspace = nullptr;
@@ -92,13 +94,29 @@ extern "C" int axb200_linear_nobias(const void *x, const void *w, void *out, int
   LtState &lt = g_lt[dev];
   if (!lt.handle) {
     if (capturing) return AXB200_INVALID_ARGUMENT;  // first use must be outside a capture
-    if (api.Create(&lt.handle) != CUBLAS_STATUS_SUCCESS) return AXB200_DEVICE_ERROR;
-    if (cudaMalloc(&lt.workspace, lt.workspace_bytes) != cudaSuccess) return AXB200_OUT_OF_MEMORY;
+    // the workspace first: a handle is only published together with the memory every later call assumes
+    void *ws = nullptr;
+    if (cudaMalloc(&ws, lt.workspace_bytes) != cudaSuccess) {
+      cudaGetLastError();
+      return AXB200_OUT_OF_MEMORY;
+    }
+    cublasLtHandle_t h = nullptr;
+    if (api.Create(&h) != CUBLAS_STATUS_SUCCESS) {
+      cudaFree(ws);
+      return AXB200_DEVICE_ERROR;
+    }
+    lt.workspace = ws;
+    lt.handle = h;
   }
   const bool half = dtype == AXB200_FLOAT16;
   const cudaDataType_t dt = half ? CUDA_R_16F : CUDA_R_32F;
   const int64_t in = in_features, outf = out_features;
-  auto key = std::make_tuple(rows, outf, in, (int)half);
+  // The algorithm is chosen for the operands' alignment too: a plan made for 256-byte aligned pointers
+  // may not be valid for less aligned ones, so alignment classes (16 bytes and up, or less) are
+  // separate plans.
+  const uintptr_t bits = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out);
+  const int align_class = (bits & 255u) == 0 ? 2 : (bits & 15u) == 0 ? 1 : 0;
+  auto key = std::make_tuple(rows, outf, in, (int)half * 4 + align_class);
   auto it = lt.plans.find(key);
   if (it == lt.plans.end()) {
     if (capturing) return AXB200_INVALID_ARGUMENT;  // plans are made (and timed) in a warm-up run
@@ -125,7 +143,10 @@ extern "C" int axb200_linear_nobias(const void *x, const void *w, void *out, int
                    CUBLAS_STATUS_SUCCESS && found > 0;
     if (pref) api.PrefDestroy(pref);
     if (!ok) return AXB200_INTERNAL_ERROR;
-    int best = 0;
+    int best = -1;
+    for (int c = 0; c < found && best < 0; ++c)  // the first usable candidate, unless a timed one beats it
+      if (heur[c].state == CUBLAS_STATUS_SUCCESS && heur[c].workspaceSize <= lt.workspace_bytes) best = c;
+    if (best < 0) return AXB200_INTERNAL_ERROR;  // nothing the library offers fits
     if (found > 1) {
       const float one = 1.f, zero = 0.f;
       cudaStream_t ts = st;

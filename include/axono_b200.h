@@ -81,6 +81,13 @@ int axb200_set_wait_limit_ns(uint64_t ns);
  * (src/ops/cuda/gqa.cu:95-129).  Both forms run the same arithmetic and give identical bits. */
 int axb200_set_fused_merge(int on);
 
+/* How a decode call that fits one wave of CTAs is cut into chunks.  on (default): on the device, from
+ * the lengths in device memory (the smallest chunk length for which all chunks fit the wave; every CTA
+ * streams about the same bytes).  off: on the host from max_seq_len alone, one length for all sequences
+ * (wave slots / (batch x hkv) chunks each) - the rule the reference's launcher follows in spirit
+ * (one split count per call, src/ops/cuda/gqa.cu:157-160).  Both are exact; they differ in speed. */
+int axb200_set_device_plan(int on);
+
 /* The chunk plan of a decode call, evaluated on the host for lengths given in host memory - the same
  * functions the kernels run on the device lengths.  For each sequence its chunk length in tokens and
  * its number of chunks; max_chunks = partial slots per (sequence, head); grid_ctas = CTAs launched.
@@ -369,7 +376,8 @@ int axb200_randn(void *out, int64_t n, int dtype, float mean, float stddev, uint
  * in_features)^T as ONE cuBLASLt call (FLOAT16 with fp32 accumulation, or FLOAT32) - a library GEMM, as
  * the reference's LinearNoBias is (src/ops/cuda/linear.cu:105-203); outside the rewritten path.  The
  * first call of a shape (outside any stream capture) times up to eight heuristic candidates on the
- * operands given and keeps the fastest; later calls, captured or not, reuse it. */
+ * operands given and keeps the fastest; later calls, captured or not, reuse it.  All calls on a device
+ * share one library workspace: keep them ordered on one stream per device. */
 int axb200_linear_nobias(const void *x, const void *w, void *out, int64_t rows, int64_t out_features,
                          int64_t in_features, int dtype, void *stream);
 

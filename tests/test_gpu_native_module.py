@@ -168,7 +168,7 @@ def test_cuda_graph_capture_replay(lx, chk):
     x, r, w, q, k, v = (dev(lx, a) for a in (x_np, r_np, w_np, q_np, k_np, v_np))
     g = native.CUDAGraph()
     g.capture(lambda: _decode_chain(lx, x, r, w, q, k, v))
-    assert g.is_captured and g.num_nodes >= 4
+    assert g.is_captured and g.num_nodes >= 3  # norm, attention (split + merge in one kernel), silu
     y, xn, attn, act = g.outputs
     for _ in range(3):
         g.replay()

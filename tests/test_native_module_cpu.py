@@ -87,6 +87,45 @@ def test_operators_refuse_cpu_tensors(lx):
         lx.gqa_decode_attention(q, kv, kv)
 
 
+def test_every_operator_checks_every_operand_before_launching(lx):
+    """A host pointer handed to a kernel would be an illegal-address fault that takes the context with
+    it.  No operator gets that far: each one refuses unless every tensor operand is in device memory
+    (status 8, DEVICE_MISMATCH, or the binding's own message) - nothing is launched, so this needs no GPU.
+    The reference checks the first operand at most (its ops ignore ctx, e.g. src/ops/cuda/fused.cu:78)."""
+    f32, i64 = np.float32, np.int64
+    T = lx.Tensor.from_numpy
+    x3 = T(np.ones((2, 4, 8), f32))
+    x2 = T(np.ones((2, 8), f32))
+    w = T(np.ones(8, f32))
+    pos = T(np.zeros(2, i64))
+    pos3 = T(np.zeros((3, 2), i64))
+    inv = T(np.ones(4, f32))
+    cs = T(np.ones((2, 8), f32))
+    ids = T(np.zeros(3, i64))
+    calls = {
+        "gqa_decode_attention": lambda: lx.gqa_decode_attention(T(np.ones((1, 4, 8), f32)), x3, x3),
+        "scaled_dot_product_attention": lambda: lx.scaled_dot_product_attention(x3, x3, x3, True),
+        "silu_mul": lambda: lx.silu_mul(x2, x2),
+        "add_rms_norm": lambda: lx.add_rms_norm(x2, x2, w, 1e-6),
+        "rms_norm": lambda: lx.rms_norm(x2, w, 1e-6),
+        "rope": lambda: lx.rope(x3, pos, 1e4),
+        "rope_thd": lambda: lx.rope_thd(x3, pos3, inv, 1, 1, 1),
+        "rope_with_cos_sin": lambda: lx.rope_with_cos_sin(x3, cs, cs),
+        "mrope_cos_sin": lambda: lx.mrope_cos_sin(pos3, inv, 1, 1),
+        "concat": lambda: lx.concat(x2, x2, 0),
+        "embedding": lambda: lx.embedding(ids, x2),
+        "argmax": lambda: lx.argmax(x2),
+        "linear_nobias": lambda: lx.linear_nobias(x2, x2),
+        "silu_mul_rows": lambda: lx.silu_mul_rows(x2, 4),
+    }
+    for name, call in calls.items():
+        with pytest.raises(RuntimeError):
+            call()
+    for name in ("linear_nobias", "gqa_decode_attention"):  # these reach the operator layer: its own status
+        with pytest.raises(RuntimeError, match="status 8"):
+            calls[name]()
+
+
 def test_axono_compat_package_host_side():
     """`import axono` resolves to the compatibility package; host tensors, default device and the
     KV-cache contract need no GPU; operators on host tensors raise instead of falling back."""
