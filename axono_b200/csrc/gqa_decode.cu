@@ -1314,6 +1314,12 @@ bool make_map(CUtensorMap *map, const void *base, int dtype, bool paged, int d, 
   return r == CUDA_SUCCESS;
 }
 
+// ---- host settings -------------------------------------------------------------------------------
+std::mutex g_settings_mu;
+unsigned long long g_wait_limit_ns = kWaitNanos;
+bool g_fused_merge = true;
+bool g_device_plan = true;
+
 // ---- the chunk plan: "a split count chosen from the context length and SM count" -----------------
 // `slots` CTAs are resident at once (2 per SM).  A large problem (more than about 8 waves of CTAs of
 // 16 tiles) is cut on the host into chunks of 16..64 tiles of 64 tokens, one length for the whole
@@ -1433,11 +1439,6 @@ int profile_slot() {
 
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-// ---- host settings -------------------------------------------------------------------------------
-std::mutex g_settings_mu;
-unsigned long long g_wait_limit_ns = kWaitNanos;
-bool g_fused_merge = true;
-bool g_device_plan = true;
 
 // Counter region of the fused merge for launches that use `workspace` on the current device.  Two
 // launches may overlap on the GPU only if they use different workspaces (they would race on the
