@@ -1318,7 +1318,8 @@ bool make_map(CUtensorMap *map, const void *base, int dtype, bool paged, int d, 
 std::mutex g_settings_mu;
 unsigned long long g_wait_limit_ns = kWaitNanos;
 bool g_fused_merge = true;
-bool g_device_plan = true;
+bool g_device_plan = false;  // measured slower than the host plan on every one-wave case tried (see make_plan)
+int g_forced_chunk_tiles = 0;  // > 0: overrides the planned chunk length (tuning and tests)
 
 // ---- the chunk plan: "a split count chosen from the context length and SM count" -----------------
 // `slots` CTAs are resident at once (2 per SM).  A large problem (more than about 8 waves of CTAs of
@@ -1356,6 +1357,10 @@ Plan make_plan(int batch, int hq, int hkv, int d, int64_t max_len) {
     if (per_item < 1) per_item = 1;
     chunk_tiles = (tiles + per_item - 1) / per_item;
     if (chunk_tiles < kMinChunkTiles) chunk_tiles = kMinChunkTiles;
+  }
+  if (g_forced_chunk_tiles > 0) {
+    pl.balanced = 0;
+    chunk_tiles = g_forced_chunk_tiles;
   }
   while ((tiles + chunk_tiles - 1) / chunk_tiles > kMaxChunks) chunk_tiles *= 2;
   pl.chunk_tokens = (int)(chunk_tiles * 64);
@@ -1658,6 +1663,13 @@ int axb200_set_wait_limit_ns(uint64_t ns) {
   if (ns == 0) return AXB200_INVALID_ARGUMENT;
   std::lock_guard<std::mutex> lock(axb::g_settings_mu);
   axb::g_wait_limit_ns = ns;
+  return AXB200_OK;
+}
+
+int axb200_set_chunk_tiles(int tiles) {
+  if (tiles < 0) return AXB200_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> lock(axb::g_settings_mu);
+  axb::g_forced_chunk_tiles = tiles;
   return AXB200_OK;
 }
 

@@ -81,12 +81,18 @@ int axb200_set_wait_limit_ns(uint64_t ns);
  * (src/ops/cuda/gqa.cu:95-129).  Both forms run the same arithmetic and give identical bits. */
 int axb200_set_fused_merge(int on);
 
-/* How a decode call that fits one wave of CTAs is cut into chunks.  on (default): on the device, from
+/* How a decode call that fits one wave of CTAs is cut into chunks.  on: on the device, from
  * the lengths in device memory (the smallest chunk length for which all chunks fit the wave; every CTA
- * streams about the same bytes).  off: on the host from max_seq_len alone, one length for all sequences
+ * streams about the same bytes).  off (default - it measured faster, the planning costs each CTA
+ * about 5 us that nothing hides in a single wave): on the host from max_seq_len alone, one length for all sequences
  * (wave slots / (batch x hkv) chunks each) - the rule the reference's launcher follows in spirit
  * (one split count per call, src/ops/cuda/gqa.cu:157-160).  Both are exact; they differ in speed. */
 int axb200_set_device_plan(int on);
+
+/* Overrides the chunk length of the decode calls: `tiles` 64-token tiles per chunk (doubled until a
+ * sequence of max_seq_len has at most 256 chunks); 0 gives the choice back to the library.  A tuning
+ * and test knob: the result does not depend on it beyond rounding.  No counterpart in the reference. */
+int axb200_set_chunk_tiles(int tiles);
 
 /* The chunk plan of a decode call, evaluated on the host for lengths given in host memory - the same
  * functions the kernels run on the device lengths.  For each sequence its chunk length in tokens and

@@ -8,6 +8,16 @@ import pytest
 
 from axono_b200 import _capi
 
+@pytest.fixture(autouse=True)
+def device_plan():
+    """These tests are about the plan made from the device-resident lengths, an option that is off by
+    default (the host plan measured faster); the last test covers the default."""
+    _capi.lib().axb200_set_device_plan(1)
+    yield
+    _capi.lib().axb200_set_device_plan(0)
+    _capi.lib().axb200_set_chunk_tiles(0)
+
+
 SLOTS = 2 * 148  # CTAs resident at once on the part the plan is made for (the library's default without a GPU)
 
 
@@ -81,3 +91,20 @@ def test_plan_invariants_random(seed):
     assert np.all(ct.astype(np.int64) * n >= np.minimum(lens, ct.astype(np.int64) * max_chunks))
     if grid == (SLOTS // hkv) * hkv:  # planned on the device lengths
         assert n.sum() <= SLOTS // hkv
+
+
+def test_default_host_plan_and_the_override():
+    lib = _capi.lib()
+    lib.axb200_set_device_plan(0)
+    lens = np.asarray([16384, 32768, 20000, 100] + [24000] * 4)
+    ct, n, max_chunks, grid = plan(lens, max_len=32768)
+    # one wave: 296 slots / 64 (sequence, head) items = 4 chunks for a sequence at the bound
+    assert np.all(ct == 8192) and list(n[:4]) == [2, 4, 3, 1] and max_chunks == 4 and grid == 4 * 8 * 8
+    assert lib.axb200_set_chunk_tiles(32) == 0
+    ct, n, max_chunks, _ = plan(lens, max_len=32768)
+    assert np.all(ct == 2048) and max_chunks == 16 and n[1] == 16
+    assert lib.axb200_set_chunk_tiles(1) == 0  # doubled until a sequence has at most 256 chunks
+    ct, _, max_chunks, _ = plan(lens, max_len=32768)
+    assert np.all(ct == 128) and max_chunks == 256
+    assert lib.axb200_set_chunk_tiles(-1) == 1
+    lib.axb200_set_chunk_tiles(0)

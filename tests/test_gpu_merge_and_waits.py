@@ -29,6 +29,15 @@ def lib():
     return _capi.lib()
 
 
+@pytest.fixture(params=["host_plan", "device_plan"])
+def plan_mode(request, lib):
+    """Both ways a one-wave call can be cut into chunks: on the host from the bound (default), on the
+    device from the lengths in device memory."""
+    lib.axb200_set_device_plan(1 if request.param == "device_plan" else 0)
+    yield request.param
+    lib.axb200_set_device_plan(0)
+
+
 @pytest.fixture()
 def both_merges(lib):
     """Runs a callable once with the merge fused into the split kernel and once with the separate
@@ -69,7 +78,7 @@ def _cache(dtype, lens, hq, hkv, d, seed, capacity=None):
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
 @pytest.mark.parametrize("hq,hkv,d", [(16, 8, 128), (6, 2, 80), (16, 1, 128)])
-def test_fused_merge_equals_combine_kernel_bit_for_bit(both_merges, dtype, hq, hkv, d):
+def test_fused_merge_equals_combine_kernel_bit_for_bit(both_merges, plan_mode, dtype, hq, hkv, d):
     from axono_b200 import ops
 
     lens = [9000, 0, 1, 300, 4097, 64, 2500]
@@ -94,7 +103,7 @@ def test_fused_merge_equals_combine_kernel_bit_for_bit(both_merges, dtype, hq, h
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
-def test_fused_merge_reference_layout(both_merges, dtype):
+def test_fused_merge_reference_layout(both_merges, plan_mode, dtype):
     """One sequence in the reference's layout: the host-visible op, long enough for many chunks."""
     from axono_b200 import ops
 
@@ -110,7 +119,7 @@ def test_fused_merge_reference_layout(both_merges, dtype):
     assert ops.last_error() == 0
 
 
-def test_one_wave_of_very_ragged_lengths():
+def test_one_wave_of_very_ragged_lengths(plan_mode):
     """Lengths from 1 to 32768 in one small batch: the device picks the chunk length from them; results
     against the oracle, and bit-identical when the same sequences sit in other batch rows (another
     prefix sum, the same chunks)."""
@@ -173,10 +182,12 @@ def test_length_beyond_the_host_bound_sets_the_capacity_flag():
     assert oracle.rel_err(out[5:6].float().cpu().numpy(), orc.gqa_decode(q[5:6], *kv(5, cover))) <= 2e-3
     assert oracle.rel_err(out[6:7].float().cpu().numpy(), orc.gqa_decode(q[6:7], *kv(6, 6000))) <= 2e-3
     assert ops.last_error() == 0
-    # four sequences only: one wave, planned from the lengths in device memory
+    # four sequences only, planned on the device from the real lengths: the bound does not matter
+    _capi.lib().axb200_set_device_plan(1)
     small = ops.gqa_decode_attention_paged(qd[4:8].contiguous(), cache.k_pages[0], cache.v_pages[0],
                                            cache.block_table[4:8].contiguous(), cache.seq_lens[4:8].contiguous(), bound)
     assert ops.last_error() == 0
+    _capi.lib().axb200_set_device_plan(0)
     assert oracle.rel_err(small[1:2].float().cpu().numpy(), orc.gqa_decode(q[5:6], *kv(5, 11000))) <= 2e-3
 
 
@@ -232,3 +243,20 @@ def test_peer_wait_runs_out_and_the_context_survives(lib):
 def test_setting_validation(lib):
     assert lib.axb200_set_wait_limit_ns(0) == 1  # INVALID_ARGUMENT
     assert lib.axb200_set_wait_limit_ns(2_000_000_000) == 0
+
+
+def test_chunk_length_override_changes_nothing_but_rounding(lib):
+    from axono_b200 import ops
+
+    lens = [5000, 300, 2049]
+    cache, q, k, v = _cache(torch.float32, lens, 16, 8, 128, seed=36)
+    qd = dev(q)
+    base = cache.attend(0, qd).clone()
+    try:
+        for tiles in (4, 7, 64):
+            assert lib.axb200_set_chunk_tiles(tiles) == 0
+            got = cache.attend(0, qd)
+            assert oracle.rel_err(got.cpu().numpy(), base.cpu().numpy()) <= 2e-6
+    finally:
+        lib.axb200_set_chunk_tiles(0)
+    assert ops.last_error() == 0

@@ -138,3 +138,80 @@ def test_fused_gather_and_sharded_tower_two_gpus(tmp_path):
     world = 2
     mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     assert all((tmp_path / f"ok{r}").exists() for r in range(world))
+
+
+def _native_worker(rank, world, key, out_dir):
+    """The same two cross-GPU forms on the native runtime: no PyTorch in the child, ranks joined by the
+    package's own host rendezvous, then the head-sharded native tower against the unsharded one."""
+    import sys
+
+    from axono_b200 import native
+    from axono_b200.native_multi import multi_gpu_parity
+    from axono_b200.native_tower import NativeTextTower
+    from axono_b200.rendezvous import Rendezvous
+    from axono_b200.tower_config import TextTowerConfig
+
+    lx = native.load()
+    lx.set_device(rank)
+    device = f"cuda:{rank}"
+    rdv = Rendezvous(rank, world, key, timeout=120.0)
+    res = multi_gpu_parity(rdv, device)
+    assert res["gather"] <= 1e-3 and res["cp"] <= 1e-3 and res["device_error_bits"] == 0, res
+
+    cfg = TextTowerConfig(hidden=256, intermediate=512, n_q_heads=8, n_kv_heads=4, head_dim=128, vocab=1000, n_layers=3)
+    Bt, L0 = 4, 300
+    lens = [L0, L0 - 7, 64, 129]
+    tok = np.random.default_rng(7001).integers(0, cfg.vocab, Bt)
+    shard = NativeTextTower(cfg, Bt, 512, seed=3, device=device, rdv=rdv)
+    single = NativeTextTower(cfg, Bt, 512, seed=3, device=device, weights=shard.host_weights)
+    # the same cache contents in both: the sharded arena holds this rank's KV heads of the full one
+    full_seed, per = 11, cfg.n_kv_heads // world
+    single.arena.fill_normal(full_seed, 0.5)
+    from axono_b200.native_multi import write_tokens
+
+    for li in range(cfg.n_layers):
+        for b in range(Bt):
+            kf, vf = single.arena.gather(li, b, lens[b])
+            write_tokens(shard.arena, li, b, np.ascontiguousarray(kf[:, rank * per:(rank + 1) * per]),
+                         np.ascontiguousarray(vf[:, rank * per:(rank + 1) * per]))
+    shard.set_state(tok, lens)
+    single.set_state(tok, lens)
+    g = None
+    for step in range(4):
+        if step == 0:
+            shard.decode_step()  # eager
+        else:
+            if g is None:
+                g = native.CUDAGraph().capture(shard.decode_step)  # its warm-up run is a real step
+            else:
+                g.replay()
+        single.decode_step()
+        lx.synchronize()
+        a, b_ = shard.last_logits.numpy().astype(np.float32), single.last_logits.numpy().astype(np.float32)
+        err = float(np.abs(a - b_).max() / np.abs(b_).max())
+        assert err <= 2e-2, f"rank {rank} step {step}: logits differ {err:.3e}"
+        toks = rdv.all_gather_object(shard.token_ids.numpy().tolist())
+        assert all(t == toks[0] for t in toks), "ranks disagree on the next tokens"
+        single.token_ids.copy_from(shard.token_ids)  # keep the two on the same trajectory
+    assert lx.device_error_bits() == 0
+    shard.close()
+    assert "torch" not in sys.modules
+    rdv.close()
+    open(os.path.join(out_dir, f"native_ok{rank}"), "w").close()
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.timeout(300)
+def test_native_runtime_two_gpus(tmp_path):
+    import multiprocessing
+
+    world = 2
+    ctx = multiprocessing.get_context("spawn")
+    key = f"test.{os.getpid()}.{_free_port()}"
+    procs = [ctx.Process(target=_native_worker, args=(r, world, key, str(tmp_path))) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(280)
+    assert all(p.exitcode == 0 for p in procs)
+    assert all((tmp_path / f"native_ok{r}").exists() for r in range(world))
