@@ -280,15 +280,21 @@ __device__ __forceinline__ void st_release_sys(unsigned int *p, unsigned int v) 
 // the stored maxima.  Partials were written by other CTAs: read them past L1.
 __device__ __forceinline__ void merge_row(const DecodeParams &p, size_t base, int c0, int n, int t,
                                           float dom, float &val, float &M, float &Ls) {
+  // one pass with a running maximum: the loads of a step do not depend on the running state, so
+  // several steps' loads are in flight together and the merge costs about one trip to L2
   M = -INFINITY;
-  for (int c = c0; c < n; ++c) M = fmaxf(M, __ldcg(p.part_ml + (base + c) * 2));
   val = 0.f;
   Ls = 0.f;
+#pragma unroll 4
   for (int c = c0; c < n; ++c) {
-    const float m = __ldcg(p.part_ml + (base + c) * 2);
-    const float wgt = m == -INFINITY ? 0.f : exp2f((m - M) * dom);
-    Ls = fmaf(__ldcg(p.part_ml + (base + c) * 2 + 1), wgt, Ls);
-    val = fmaf(wgt, __ldcg(p.part_o + (base + c) * p.d + t), val);
+    const float2 ml = __ldcg(reinterpret_cast<const float2 *>(p.part_ml) + base + c);
+    const float o = __ldcg(p.part_o + (base + c) * p.d + t);
+    const float Mn = fmaxf(M, ml.x);
+    const float keep = M == -INFINITY ? 0.f : exp2f((M - Mn) * dom);
+    const float wgt = ml.x == -INFINITY ? 0.f : exp2f((ml.x - Mn) * dom);
+    val = fmaf(wgt, o, val * keep);
+    Ls = fmaf(wgt, ml.y, Ls * keep);
+    M = Mn;
   }
 }
 
@@ -416,7 +422,7 @@ __device__ __forceinline__ void produce_tiles(const CUtensorMap *tmK, const CUte
                                               const DecodeParams &p, uint8_t *stages,
                                               uint64_t *full, uint64_t *empty,
                                               volatile int *abort_flag, int b, int hk, int start,
-                                              int ntiles, int lane) {
+                                              int ntiles, int lane, int spec_start, int spec_page) {
   constexpr int kBoxBytes = (kStageBytes / 2) / kBoxes;
   int page_cache = 0;
   for (int i = 0; i < ntiles; ++i) {
@@ -430,7 +436,9 @@ __device__ __forceinline__ void produce_tiles(const CUtensorMap *tmK, const CUte
         const int slot = (start + t * kTile) / p.page_tokens;
         page_cache = 0;
         if (t < ntiles && slot < p.max_blocks) {
-          page_cache = p.block_table[(size_t)b * p.max_blocks + slot];
+          // the first 32 page ids may have been fetched while the length was still on its way
+          page_cache = (i == 0 && start == spec_start) ? spec_page
+                                                       : p.block_table[(size_t)b * p.max_blocks + slot];
           if (page_cache < 0 || page_cache >= p.num_pages) {
             atomicOr(&g_error_word, AXB200_ERR_BAD_PAGE);
             page_cache = p.num_pages;  // out of range: the copy zero-fills
@@ -541,6 +549,21 @@ gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
     *abort_flag = 0;
     mbar_fence_init();
   }
+  // The producer warp asks for its first page ids (and the tensor maps) before the sequence's length
+  // is known: with a host-planned chunk length the chunk's first token does not depend on it, and the
+  // two trips to memory overlap instead of following one another.
+  int spec_start = -1, spec_page = 0;
+  if (warp == kConsumerWarps) {
+    if (lane == 0) {
+      tma_prefetch_descriptor(&tmK);
+      tma_prefetch_descriptor(&tmV);
+    }
+    if (kPaged && !p.balanced) {
+      spec_start = blockIdx.x * p.chunk_tokens;
+      const int slot = (spec_start + lane * kTileTokensF16) / p.page_tokens;
+      if (slot < p.max_blocks) spec_page = p.block_table[(size_t)blockIdx.z * p.max_blocks + slot];
+    }
+  }
   CtaWork w;
   const bool active = cta_work(p, s_plan, w);
   __syncthreads();
@@ -560,12 +583,8 @@ gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
   const bool direct = p.direct_ok && w.n - c_first == 1;
 
   if (warp == kConsumerWarps) {
-    if (lane == 0) {
-      tma_prefetch_descriptor(&tmK);
-      tma_prefetch_descriptor(&tmV);
-    }
-    produce_tiles<kPaged, kStages, kTileTokensF16, 2, 64>(&tmK, &tmV, p, smem, full, empty,
-                                                          abort_flag, b, hk, start, ntiles, lane);
+    produce_tiles<kPaged, kStages, kTileTokensF16, 2, 64>(&tmK, &tmV, p, smem, full, empty, abort_flag, b, hk,
+                                                          start, ntiles, lane, spec_start, spec_page);
     return;
   }
 
@@ -762,6 +781,21 @@ gqa_split_f32_kernel(const __grid_constant__ CUtensorMap tmK,
     *abort_flag = 0;
     mbar_fence_init();
   }
+  // The producer warp asks for its first page ids (and the tensor maps) before the sequence's length
+  // is known: with a host-planned chunk length the chunk's first token does not depend on it, and the
+  // two trips to memory overlap instead of following one another.
+  int spec_start = -1, spec_page = 0;
+  if (warp == kConsumerWarps) {
+    if (lane == 0) {
+      tma_prefetch_descriptor(&tmK);
+      tma_prefetch_descriptor(&tmV);
+    }
+    if (kPaged && !p.balanced) {
+      spec_start = blockIdx.x * p.chunk_tokens;
+      const int slot = (spec_start + lane * kTileTokensF32) / p.page_tokens;
+      if (slot < p.max_blocks) spec_page = p.block_table[(size_t)blockIdx.z * p.max_blocks + slot];
+    }
+  }
   CtaWork w;
   const bool active = cta_work(p, s_plan, w);
   __syncthreads();
@@ -781,12 +815,8 @@ gqa_split_f32_kernel(const __grid_constant__ CUtensorMap tmK,
   const bool direct = p.direct_ok && w.n - c_first == 1;
 
   if (warp == kConsumerWarps) {
-    if (lane == 0) {
-      tma_prefetch_descriptor(&tmK);
-      tma_prefetch_descriptor(&tmV);
-    }
-    produce_tiles<kPaged, kStages, kTileTokensF32, 1, 128>(&tmK, &tmV, p, smem, full, empty,
-                                                           abort_flag, b, hk, start, ntiles, lane);
+    produce_tiles<kPaged, kStages, kTileTokensF32, 1, 128>(&tmK, &tmV, p, smem, full, empty, abort_flag, b, hk,
+                                                           start, ntiles, lane, spec_start, spec_page);
     return;
   }
 
@@ -1367,7 +1397,7 @@ Plan make_plan(int batch, int hq, int hkv, int d, int64_t max_len) {
   pl.max_chunks = (int)((max_len + pl.chunk_tokens - 1) / pl.chunk_tokens);
   if (pl.balanced && pl.max_chunks > pl.budget) pl.max_chunks = pl.budget;  // one sequence cannot have more
   if (pl.max_chunks < 1) pl.max_chunks = 1;
-  pl.part_o_bytes = (size_t)batch * hq * pl.max_chunks * d * sizeof(float);
+  pl.part_o_bytes = ((size_t)batch * hq * pl.max_chunks * d * sizeof(float) + 15) & ~size_t(15);  // (m, l) pairs are read as 8 bytes
   pl.part_ml_bytes = (size_t)batch * hq * pl.max_chunks * 2 * sizeof(float);
   return pl;
 }
