@@ -37,6 +37,11 @@ SIGNATURES = {
                                             _vp, _vp, _vp, _i, _i, _i, _vp]),
     "axb200_gqa_decode_paged_cp": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i64, _i, _vp, _sz,
                                         _vp, _vp, _vp, _i, _i, _vp]),
+    "axb200_nccl_unique_id": (_i, [_vp]),
+    "axb200_nccl_init": (_i, [_vp, _i, _i, C.POINTER(_vp)]),
+    "axb200_nccl_all_gather": (_i, [_vp, _vp, _vp, _sz, _vp]),
+    "axb200_nccl_destroy": (_i, [_vp]),
+    "axb200_swap_leading_dims": (_i, [_vp, _vp, _i, _i, _sz, _vp]),
     "axb200_p2p_alloc": (_i, [_sz, C.POINTER(_vp), _vp]),
     "axb200_p2p_open": (_i, [_vp, C.POINTER(_vp)]),
     "axb200_p2p_close": (_i, [_vp]),

@@ -25,15 +25,43 @@ from .kv_cache import PagedKVCache
 from .tower_config import TextTowerConfig  # noqa: F401 - re-exported
 
 
+_side_streams: dict = {}
+
+
+def _side_stream(device) -> "torch.cuda.Stream":
+    key = torch.device(device)
+    if key not in _side_streams:
+        _side_streams[key] = torch.cuda.Stream(device=key)
+    return _side_streams[key]
+
+
 def decode_block(x, residual, norm_weight, q, k_new, v_new, cache: PagedKVCache, layer: int, gate, up,
-                 eps: float = 1e-6, theta: float = 1e6, pos=None, inv_freq=None, mrope_section=None):
+                 eps: float = 1e-6, theta: float = 1e6, pos=None, inv_freq=None, mrope_section=None,
+                 parallel: bool = False):
     """One fused decode block.  Returns (y, xn, attn, act): the residual sum and its norm, the attention
-    output of q (rotated in place) over the cache including the appended token, and silu(gate)*up."""
-    y, xn = ops.add_rms_norm(x, residual, norm_weight, eps)
+    output of q (rotated in place) over the cache including the appended token, and silu(gate)*up.
+
+    In this block the three parts do not depend on one another (the norm's and the activation's inputs
+    are given), so with `parallel` the two launch-latency kernels go to a second stream while
+    append -> attention runs on the current one; under CUDA-graph capture that makes them parallel
+    branches of the graph and the block's time that of its attention chain."""
+    if not parallel:
+        y, xn = ops.add_rms_norm(x, residual, norm_weight, eps)
+        cache.append_rope(layer, q, k_new, v_new, pos=pos, inv_freq=inv_freq, theta=theta,
+                          mrope_section=mrope_section)
+        attn = cache.attend(layer, q)
+        act = ops.silu_mul(gate, up)
+        return y, xn, attn, act
+    cur = torch.cuda.current_stream(x.device)
+    side = _side_stream(x.device)
+    side.wait_stream(cur)
+    with torch.cuda.stream(side):
+        y, xn = ops.add_rms_norm(x, residual, norm_weight, eps)
+        act = ops.silu_mul(gate, up)
     cache.append_rope(layer, q, k_new, v_new, pos=pos, inv_freq=inv_freq, theta=theta,
                       mrope_section=mrope_section)
     attn = cache.attend(layer, q)
-    act = ops.silu_mul(gate, up)
+    cur.wait_stream(side)
     return y, xn, attn, act
 
 

@@ -100,6 +100,48 @@ class PeerBuffers:
             self.local_ptr = 0
 
 
+class NcclGather:
+    """All-gather of per-head attention outputs through NCCL - the library form of what `attend_gather`
+    fuses into the attention kernel.  The communicator is created here (every rank constructs one,
+    before any stream capture); `gather(local)` enqueues ncclAllGather and a re-layout on the current
+    stream and returns (batch, hq_total, d), so it can be recorded into a CUDA graph."""
+
+    def __init__(self, rdv: Rendezvous, batch: int, hq_local: int, d: int, dtype, device: str = "cuda"):
+        lx = native.load()
+        lib = _capi.lib()
+        self.lx, self.rdv, self.world, self.device = lx, rdv, rdv.world, device
+        self.batch, self.hq_local, self.d, self.dtype = batch, hq_local, d, dtype
+        uid = C.create_string_buffer(128)
+        if rdv.rank == 0:
+            _capi.check(lib.axb200_nccl_unique_id(uid), "nccl_unique_id")
+        uid = C.create_string_buffer(rdv.all_gather(bytes(uid.raw))[0], 128)
+        comm = C.c_void_p()
+        _capi.check(lib.axb200_nccl_init(uid, rdv.world, rdv.rank, C.byref(comm)), "nccl_init")
+        self._comm = comm
+        self._tmp = lx.Tensor(dtype, [self.world, batch, hq_local, d], device)
+        self._out = lx.Tensor(dtype, [batch, self.world * hq_local, d], device)
+        rdv.barrier()
+
+    def gather(self, local):
+        """local (batch, hq_local, d) of this rank -> this rank's copy of (batch, hq_total, d)."""
+        lx, lib = self.lx, _capi.lib()
+        if tuple(local.shape) != (self.batch, self.hq_local, self.d) or local.dtype != self.dtype:
+            raise RuntimeError("NcclGather.gather: tensor does not match the communicator's buffers")
+        st = lx.current_stream()
+        _capi.check(lib.axb200_nccl_all_gather(self._comm, local.data_ptr, self._tmp.data_ptr, local.num_bytes, st),
+                    "nccl_all_gather")
+        _capi.check(lib.axb200_swap_leading_dims(self._tmp.data_ptr, self._out.data_ptr, self.world, self.batch,
+                                                 local.num_bytes // self.batch, st), "swap_leading_dims")
+        return self._out
+
+    def close(self) -> None:
+        if self._comm:
+            self.lx.synchronize()
+            self.rdv.barrier()
+            _capi.lib().axb200_nccl_destroy(self._comm)
+            self._comm = None
+
+
 class Scratch:
     """The decode calls' workspace as one tensor that lives as long as its user (a graph that was
     captured with it keeps its address)."""

@@ -24,7 +24,7 @@ class NativeTextTower:
     next token ids are written back into `token_ids` on the device."""
 
     def __init__(self, cfg: TextTowerConfig, batch: int, max_seq_len: int, seed: int = 0, page_tokens: int = 64,
-                 weights=None, device: str = "cuda", rdv=None):
+                 weights=None, device: str = "cuda", rdv=None, gather: str = "fused"):
         lx = native.load()
         self.lx, self.cfg, self.batch, self.max_seq_len, self.device = lx, cfg, batch, max_seq_len, device
         self.world = rdv.world if rdv is not None else 1
@@ -83,8 +83,14 @@ class NativeTextTower:
         self.arena.sync()
         self.token_ids = dev(np.zeros(batch, np.int64))
         self.last_logits = None
-        self.bufs = self.scratch = None
-        if self.world > 1:
+        self.bufs = self.scratch = self.nccl = None
+        if gather not in ("fused", "nccl"):
+            raise ValueError(gather)
+        if self.world > 1 and gather == "nccl":  # the library collective: attention, ncclAllGather, projection
+            from .native_multi import NcclGather
+
+            self.nccl = NcclGather(rdv, batch, self.local_q, d, lx.DataType.FLOAT16, device)
+        elif self.world > 1:
             from .native_multi import PeerBuffers, Scratch
 
             # one gathered buffer per layer (at least two): successive calls never share a buffer
@@ -120,7 +126,12 @@ class NativeTextTower:
                                                  self.device)
             else:
                 attn = lx.gqa_decode_attention_paged(q, self.arena, li, self.max_seq_len)
-                attn.reshape([self.batch, cfg.n_q_heads * cfg.head_dim])
+                if self.nccl is not None:
+                    attn = self.nccl.gather(attn)
+                    attn = lx.Tensor.from_device_ptr(attn.data_ptr, attn.dtype, [self.batch, cfg.n_q_heads * cfg.head_dim],
+                                                     self.device)
+                else:
+                    attn.reshape([self.batch, cfg.n_q_heads * cfg.head_dim])
             h, xn2 = lx.add_rms_norm(lx.linear_nobias(attn, lw["o"]), h, lw["post_ln"], cfg.eps)
             act = lx.silu_mul_rows(lx.linear_nobias(xn2, lw["gate_up"]), cfg.intermediate)
             mlp_out = lx.linear_nobias(act, lw["down"])
@@ -142,3 +153,6 @@ class NativeTextTower:
         if self.bufs is not None:
             self.bufs.close()
             self.bufs = None
+        if self.nccl is not None:
+            self.nccl.close()
+            self.nccl = None

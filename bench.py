@@ -401,7 +401,7 @@ class NativeStep:
         self.arena = None
 
 
-def tower_figures(args, lx, rdv, device, sampler=None):
+def tower_figures(args, lx, rdv, device, sampler=None, gather="fused"):
     """The 28-layer text-tower decode step (batch 32, context 16384, random fp16 weights) as one captured
     graph on the native runtime, KV heads sharded over the ranks with the attention kernel storing into
     every rank's gathered buffer.  Returns the figures for `extra.c5_tower`."""
@@ -413,7 +413,7 @@ def tower_figures(args, lx, rdv, device, sampler=None):
     cfg = TextTowerConfig()
     steps = max(3, min(args.steps, 20))
     warm = max(3, min(args.warmup, 5))
-    tower = NativeTextTower(cfg, B, L + 2 * (steps + warm) + 72, seed=5, device=device, rdv=rdv)
+    tower = NativeTextTower(cfg, B, L + 2 * (steps + warm) + 72, seed=5, device=device, rdv=rdv, gather=gather)
     tower.arena.fill_normal(77 + rdv.rank, 0.5)
     lens = [L] * B
     tower.set_state(np.arange(B) % cfg.vocab, lens)
@@ -442,8 +442,10 @@ def tower_figures(args, lx, rdv, device, sampler=None):
            "hbm_floor_ms": (kv_bytes + w_bytes) / (peak * 1e9) * 1e3, "peak_source": f"of {kind}",
            "graph_nodes": int(g.num_nodes), "nodes_per_layer": round((int(g.num_nodes) - 5) / cfg.n_layers, 2),
            "kv_gb_per_gpu": kv_bytes / 1e9, "weights_gb_per_gpu": w_bytes / 1e9,
-           "sharding": f"KV heads x{rdv.world}" + (", attention kernel stores into every rank's buffer over NVLink"
-                                                   if rdv.world > 1 else ""),
+           "sharding": f"KV heads x{rdv.world}" + ("" if rdv.world == 1 else
+                                                   ", attention kernel stores into every rank's buffer over NVLink"
+                                                   if gather == "fused" else
+                                                   ", NCCL all-gather of attention outputs inside the captured graph"),
            "gathered_layer0_identical_on_all_ranks": gathered_same, "first_step_token_agreement": token_agreement,
            "device_error_bits": bits}
     if not gathered_same or bits:
@@ -492,9 +494,10 @@ def run_native(args):
     run = NativeStep(lx, device, lens, capacity, args.dtype, seed=rank)
     B = run.B
     # ---- value: inputs resident, CUDA events around K steps ----
+    sampler.start()  # sampled from here to the end of the host-buffer phase: the GPU is under this load throughout
     for _ in range(args.warmup):
         run.step()
-    dev_ms, my_bytes = run.timed_steps(rdv, args.steps, sampler)
+    dev_ms, my_bytes = run.timed_steps(rdv, args.steps)
     all_bytes = rdv.sum(my_bytes)
     value = all_bytes / (dev_ms / 1e3) / 1e9
     total_seqs = rdv.sum(B)
@@ -523,6 +526,7 @@ def run_native(args):
     e2e_bytes = rdv.sum(e2e_my_bytes)
     e2e = {"value": e2e_bytes / e2e_s / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
            "ms_per_step": e2e_s / args.steps * 1e3, "tokens_per_s": total_seqs * args.steps / e2e_s}
+    sampler.pause()
     clocks = sampler.summary()
 
     extra = {}
@@ -845,10 +849,13 @@ def run_tower(args):
         ops.workspace(device, ops.gqa_workspace_bytes(B, HQ, HKV, D, cache.max_seq_len))
 
         def body():
-            return decode_block(x, res, w, q0.clone(), kn, vn, cache, 0, gate, up, theta=1e6)
+            # q is rotated in place, replay after replay (a rotation keeps its norm): in the model it
+            # comes fresh from the QKV projection every step, so no copy belongs to the block
+            return decode_block(x, res, w, q0, kn, vn, cache, 0, gate, up, theta=1e6, parallel=not args.no_fork)
 
         kv_bytes = algo_bytes(np.asarray(lens) + 1)
-        launches_note = "add_rms_norm, q copy, kv_append_rope, split, combine, silu_mul"
+        launches_note = ("kv_append_rope -> attention (split + merge in one kernel), with add_rms_norm and silu_mul "
+                         + ("on a second stream: parallel branches of the graph" if not args.no_fork else "in line"))
         other_bytes = 0.0
 
     use_graph = not (world > 1 and args.workload == "c5_tower" and args.gather == "nccl")
@@ -938,7 +945,7 @@ def run_tower_native(args):
     lx.set_device(local_rank)
     sampler = ClockSampler(local_rank, use_torch=False, pci_bus_id=lx.device_pci_bus_id(local_rank))
     sampler.start()
-    fig = tower_figures(args, lx, rdv, f"cuda:{local_rank}")
+    fig = tower_figures(args, lx, rdv, f"cuda:{local_rank}", gather=args.gather)
     sampler.pause()
     assert "torch" not in sys.modules
     if rdv.rank == 0:
@@ -1185,6 +1192,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-extra", action="store_true")
     ap.add_argument("--no-check", action="store_true", help="skip the check of the timed output against the CPU checker")
+    ap.add_argument("--no-fork", action="store_true", help="c2_block: all kernels on one stream (no parallel graph branches)")
     ap.add_argument("--no-tower", action="store_true", help="skip the text-tower figures in `extra`")
     args = ap.parse_args()
     rank0 = int(os.environ.get("RANK", "0")) == 0

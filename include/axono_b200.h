@@ -232,6 +232,26 @@ int axb200_gqa_decode_paged_cp(const void *q, void *out, const void *k_pages, co
                                void *const *peer_records, void *const *peer_flags, void *local_state,
                                int world, int rank, void *stream);
 
+/* ---- the same gather as a library collective (NCCL) ---------------------------------------------------
+ * "Attention, then all-gather of the per-head outputs, then the output projection" with ncclAllGather:
+ * the plain form of KV-head sharding and the baseline of the fused kernel above.  One process per GPU.
+ *   unique_id: rank 0 draws 128 bytes and sends them to the other ranks by any host-side means;
+ *   init: creates this rank's communicator and runs one small collective on it - it allocates and
+ *     synchronises, so every rank calls it before any stream capture;
+ *   all_gather: every rank contributes bytes_per_rank bytes at `send` and receives world x that at
+ *     `recv`, rank-major; only enqueues on `stream`, so it may be captured into a CUDA graph (every
+ *     rank must then replay its graph the same number of times);
+ *   swap_leading_dims: dst (n1, n0, row) = src (n0, n1, row), rows of row_bytes (a multiple of 16,
+ *     pointers 16-byte aligned) - turns the gathered (world, batch, heads x d) into the
+ *     (batch, world, heads x d) rows the projection reads.
+ * NCCL is opened by soname (libnccl.so.2) on first use.  No counterpart in the reference, whose
+ * WITH_NCCL option is reserved and unused (CMakeLists.txt:78,91-92). */
+int axb200_nccl_unique_id(void *id128);
+int axb200_nccl_init(const void *id128, int world, int rank, void **comm_out);
+int axb200_nccl_all_gather(void *comm, const void *send, void *recv, size_t bytes_per_rank, void *stream);
+int axb200_nccl_destroy(void *comm);
+int axb200_swap_leading_dims(const void *src, void *dst, int n0, int n1, size_t row_bytes, void *stream);
+
 /* Peer-mappable device memory for the calls above (CUDA IPC): alloc returns zero-filled memory and a
  * 64-byte handle to send to the other processes of the node; open maps a peer's handle; close
  * unmaps it; free releases an allocation.  These four are set-up calls: they allocate and
