@@ -34,6 +34,13 @@ struct ErrorReaderRegistration {
 static ErrorReaderRegistration g_error_reader_registration;
 }  // namespace
 
+// axb200_kv_append_rope with q read from q_src (null: in place); defined in rope_append.cu.
+int kv_append_rope_from(void *q, const void *q_src, const void *k_new, const void *v_new, void *k_pages,
+                        void *v_pages, const int32_t *block_table, int32_t *seq_lens, const int64_t *pos,
+                        const float *inv_freq, float theta, int rotate, int mrope, int h_sec, int w_sec,
+                        int batch, int hq, int hkv, int d, int page_tokens, int max_blocks, int num_pages,
+                        int dtype, int slot_delta, int advance, void *stream);
+
 inline size_t dtype_size(int dtype) {
   switch (dtype) {
     case AXB200_FLOAT16: return 2;

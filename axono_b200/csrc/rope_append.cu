@@ -210,6 +210,7 @@ mrope_cos_sin_kernel(const int64_t *pos, const float *inv_freq, float *cos_out, 
 // ---- append + rotate ------------------------------------------------------------------------
 struct AppendParams {
   void *q;
+  const void *q_src;  // where q is read from; null = q itself (rotated in place)
   const void *k_new, *v_new;
   void *k_pages, *v_pages;
   const int32_t *block_table;
@@ -247,8 +248,9 @@ kv_append_rope_kernel(const AppendParams p, const InvFreqTable table) {
   T *q = reinterpret_cast<T *>(p.q) + (size_t)b * p.hq * p.d;
   const T *kn = reinterpret_cast<const T *>(p.k_new) + (size_t)b * p.hkv * p.d;
   const T *vn = reinterpret_cast<const T *>(p.v_new) + (size_t)b * p.hkv * p.d;
+  const T *q_in = p.q_src ? reinterpret_cast<const T *>(p.q_src) + (size_t)b * p.hq * p.d : q;
   auto row_of = [&](int head) -> const T * {
-    if (head < q_heads) return q + (size_t)head * p.d;
+    if (head < q_heads) return q_in + (size_t)head * p.d;
     if (head < q_heads + p.hkv) return kn + (size_t)(head - q_heads) * p.d;
     return vn + (size_t)(head - q_heads - p.hkv) * p.d;
   };
@@ -674,6 +676,21 @@ int axb200_kv_append_rope(void *q, const void *k_new, const void *v_new, void *k
                           int mrope, int h_sec, int w_sec, int batch, int hq, int hkv, int d,
                           int page_tokens, int max_blocks, int num_pages, int dtype, int slot_delta,
                           int advance, void *stream) {
+  return axb::kv_append_rope_from(q, nullptr, k_new, v_new, k_pages, v_pages, block_table, seq_lens, pos, inv_freq,
+                                  theta, rotate, mrope, h_sec, w_sec, batch, hq, hkv, d, page_tokens, max_blocks,
+                                  num_pages, dtype, slot_delta, advance, stream);
+}
+
+}  // extern "C"
+
+// The append with q read from somewhere else than where it is written (q_src; null = in place): the
+// host-buffer step reads q, k_new and v_new straight from page-locked host memory.
+int axb::kv_append_rope_from(void *q, const void *q_src, const void *k_new, const void *v_new, void *k_pages,
+                             void *v_pages, const int32_t *block_table, int32_t *seq_lens,
+                             const int64_t *pos, const float *inv_freq, float theta, int rotate,
+                             int mrope, int h_sec, int w_sec, int batch, int hq, int hkv, int d,
+                             int page_tokens, int max_blocks, int num_pages, int dtype, int slot_delta,
+                             int advance, void *stream) {
   if (dtype != AXB200_FLOAT32 && dtype != AXB200_FLOAT16) return AXB200_UNSUPPORTED_TYPE;
   if (!k_new || !v_new || !k_pages || !v_pages || !block_table || !seq_lens)
     return AXB200_INVALID_PTR;
@@ -684,6 +701,7 @@ int axb200_kv_append_rope(void *q, const void *k_new, const void *v_new, void *k
   if (rotate && mrope && !inv_freq) return AXB200_INVALID_PTR;
   axb::AppendParams p{};
   p.q = q;
+  p.q_src = (q && rotate) ? q_src : nullptr;
   p.k_new = k_new;
   p.v_new = v_new;
   p.k_pages = k_pages;
@@ -716,6 +734,8 @@ int axb200_kv_append_rope(void *q, const void *k_new, const void *v_new, void *k
     axb::kv_append_rope_kernel<__half><<<batch, threads, 0, st>>>(p, table);
   return axb::launch_status();
 }
+
+extern "C" {
 
 int axb200_kv_prefill_write(void *q, const void *k, const void *v, void *k_pages, void *v_pages,
                             const int32_t *block_row, const int64_t *pos, const float *inv_freq,

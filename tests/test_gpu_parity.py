@@ -412,9 +412,11 @@ def test_concat_bit_exact(ops, golden):
     assert np.array_equal(ops.concat(dev(a), dev(b1), 1).cpu().numpy(), np.concatenate([a, b1], 1))
 
 
-def test_decode_step_host_matches_separate_calls(ops):
-    """The host-buffer step (one C-ABI call: copy in, rope + append, attend, copy out, wait) gives the
-    same bits as the device-resident calls it composes."""
+@pytest.mark.parametrize("pinned", [True, False])
+def test_decode_step_host_matches_separate_calls(ops, pinned):
+    """The host-buffer step (one C-ABI call: inputs in, rope + append, attend, output out, wait) gives the
+    same bits as the device-resident calls it composes - with page-locked buffers, which the kernels read
+    and write directly, and with pageable ones, which go through copies."""
     from axono_b200.kv_cache import PagedKVCache
 
     rng = np.random.default_rng(61)
@@ -427,15 +429,18 @@ def test_decode_step_host_matches_separate_calls(ops):
         c = PagedKVCache(1, B, hkv, d, L + 64, dtype=torch.float16)
         c.fill(0, k0, v0, lens)
         caches.append(c)
-    host = lambda *s: torch.from_numpy(rng.standard_normal(s).astype(np.float16)).pin_memory()  # noqa: E731
+    pin = (lambda t: t.pin_memory()) if pinned else (lambda t: t)
+    host = lambda *s: pin(torch.from_numpy(rng.standard_normal(s).astype(np.float16)))  # noqa: E731
     for step in range(3):
         q_h, k_h, v_h = host(B, hq, d), host(B, hkv, d), host(B, hkv, d)
-        out_h = torch.empty_like(q_h).pin_memory()
+        q_before = q_h.clone()
+        out_h = pin(torch.empty_like(q_h))
         caches[0].step_host(q_h, k_h, v_h, out_h, theta=1e6)
         qd = q_h.cuda()
         caches[1].append_rope(0, qd, k_h.cuda(), v_h.cuda(), theta=1e6)
         want = caches[1].attend(0, qd).cpu()
         assert torch.equal(out_h, want), f"step {step}"
+        assert torch.equal(q_h, q_before)  # the host's q is an input: it is not rotated in place
     assert torch.equal(caches[0].seq_lens, caches[1].seq_lens)
     assert ops.last_error() == 0
 
