@@ -33,19 +33,18 @@ _u8p = np.ctypeslib.ndpointer(np.uint8, flags="C_CONTIGUOUS")
 
 def build(ref_root: str = "") -> None:
     """Compile the C restatement, and the reference libraries when its sources are present (their
-    location: argument, else $AXONO_REFERENCE_ROOT, else the Makefile's default)."""
-    ref_root = ref_root or os.environ.get("AXONO_REFERENCE_ROOT", "") or _makefile_default_ref()
+    location: argument, else $AXONO_REFERENCE_ROOT, else a checkout named `reference` beside this
+    repository)."""
+    ref_root = ref_root or os.environ.get("AXONO_REFERENCE_ROOT", "") or _sibling_reference()
     subprocess.check_call(["make", "-s", "-C", _HERE, "oracle"])
-    if os.path.isdir(os.path.join(ref_root, "src")):
+    if ref_root and os.path.isdir(os.path.join(ref_root, "src")):
         subprocess.check_call(["make", "-s", "-C", _HERE, "ref", f"REF={ref_root}"])
         subprocess.check_call(["make", "-s", "-C", _HERE, "refcuda", f"REF={ref_root}"])
 
 
-def _makefile_default_ref() -> str:
-    for line in open(os.path.join(_HERE, "Makefile")):
-        if line.startswith("REF ?="):
-            return line.split("=", 1)[1].strip()
-    return ""
+def _sibling_reference() -> str:
+    path = os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+    return path if os.path.isdir(path) else ""
 
 
 def _f32(a):

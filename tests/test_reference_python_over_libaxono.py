@@ -6,8 +6,8 @@ and `axono/core/compile.py` from a reference checkout by path (they are never co
 repository) after registering this library's module as `libaxono`, and drive the operators, the
 `CUDAGraph` wrapper and `compile()` through them.
 
-They need the reference's sources (`$AXONO_REFERENCE_ROOT`, default /root/reference) and are skipped
-where those are absent.  Without a GPU the import surface and the error behaviour are checked; with a
+They need the reference's sources (`$AXONO_REFERENCE_ROOT`, else a checkout named `reference` beside this
+repository) and are skipped where those are absent.  Without a GPU the import surface and the error behaviour are checked; with a
 GPU the same files run the decode-path operators against the CPU checker.
 """
 import importlib
@@ -18,7 +18,8 @@ import types
 import numpy as np
 import pytest
 
-REF = os.environ.get("AXONO_REFERENCE_ROOT", "/root/reference")
+REF = os.environ.get("AXONO_REFERENCE_ROOT") or os.path.join(
+    os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
 PKG = os.path.join(REF, "axono", "python", "axono")
 
 pytestmark = pytest.mark.skipif(not os.path.isfile(os.path.join(PKG, "gqa.py")),
