@@ -417,13 +417,13 @@ __device__ __forceinline__ void emit_empty_item(const DecodeParams &p, const Gat
 // ---- producer ---------------------------------------------------------------------------
 // Streams tiles [0, ntiles) of this CTA's chunk.  All 32 lanes run the loop (the page ids of
 // the next 32 tiles are fetched one per lane); lane 0 issues the copies.
-template <bool kPaged, int kStages, int kTile, int kBoxes, int kBoxElems>
+template <bool kPaged, int kStages, int kTile, int kBoxes, int kBoxElems, int kStage = kStageBytes>
 __device__ __forceinline__ void produce_tiles(const CUtensorMap *tmK, const CUtensorMap *tmV,
                                               const DecodeParams &p, uint8_t *stages,
                                               uint64_t *full, uint64_t *empty,
                                               volatile int *abort_flag, int b, int hk, int start,
                                               int ntiles, int lane, int spec_start, int spec_page) {
-  constexpr int kBoxBytes = (kStageBytes / 2) / kBoxes;
+  constexpr int kBoxBytes = (kStage / 2) / kBoxes;
   int page_cache = 0;
   for (int i = 0; i < ntiles; ++i) {
     const int s = i % kStages;
@@ -450,17 +450,17 @@ __device__ __forceinline__ void produce_tiles(const CUtensorMap *tmK, const CUte
     }
     if (lane == 0) {
       if (mbar_wait_bounded(&empty[s], phase ^ 1u, abort_flag, p.wait_ns)) {
-        mbar_arrive_expect_tx(&full[s], kStageBytes);
-        uint8_t *st = stages + (size_t)s * kStageBytes;
+        mbar_arrive_expect_tx(&full[s], kStage);
+        uint8_t *st = stages + (size_t)s * kStage;
 #pragma unroll
         for (int bx = 0; bx < kBoxes; ++bx) {
           if (kPaged) {
             tma_load_4d(st + bx * kBoxBytes, tmK, &full[s], bx * kBoxElems, tok_in_page, hk, page);
-            tma_load_4d(st + kStageBytes / 2 + bx * kBoxBytes, tmV, &full[s], bx * kBoxElems,
+            tma_load_4d(st + kStage / 2 + bx * kBoxBytes, tmV, &full[s], bx * kBoxElems,
                         tok_in_page, hk, page);
           } else {
             tma_load_4d(st + bx * kBoxBytes, tmK, &full[s], bx * kBoxElems, hk, tok0, 0);
-            tma_load_4d(st + kStageBytes / 2 + bx * kBoxBytes, tmV, &full[s], bx * kBoxElems, hk,
+            tma_load_4d(st + kStage / 2 + bx * kBoxBytes, tmV, &full[s], bx * kBoxElems, hk,
                         tok0, 0);
           }
         }
@@ -476,11 +476,12 @@ __device__ __forceinline__ void produce_tiles(const CUtensorMap *tmK, const CUte
 // shared memory; thread t owns output dim t.  m is in the exponent domain `dom` (so weights
 // are exp2((m_w - M) * dom)).  direct: the chunk is the whole sequence - emit the final rows;
 // otherwise store the chunk's partial.
-template <typename OutT>
+template <typename OutT, int kD>
 __device__ __forceinline__ void finalize_chunk(const DecodeParams &p, const GatherParams &gp,
                                                const float *mO, const float *mM, const float *mL,
                                                int b, int hk, int chunk, int t, float dom,
                                                bool direct) {
+  if (t >= kD) return;  // head_dim 64: half of the consumer threads own no output dim
   for (int r = 0; r < p.group; ++r) {
     float M = -INFINITY;
 #pragma unroll
@@ -491,14 +492,14 @@ __device__ __forceinline__ void finalize_chunk(const DecodeParams &p, const Gath
       const float mw = mM[w * kMaxGroupMma + r];
       const float wgt = (mw == -INFINITY) ? 0.f : exp2f((mw - M) * dom);
       L += mL[w * kMaxGroupMma + r] * wgt;
-      acc += mO[(w * kMaxGroupMma + r) * kHeadDim + t] * wgt;
+      acc += mO[(w * kMaxGroupMma + r) * kD + t] * wgt;
     }
     const int h = hk * p.group + r;
     if (direct) {
       emit_final<OutT>(p, gp, b, h, t, acc, M, L);
     } else {
       const size_t slot = ((size_t)b * p.hq + h) * p.max_chunks + chunk;
-      p.part_o[slot * kHeadDim + t] = acc;
+      p.part_o[slot * kD + t] = acc;
       if (t == 0) {
         p.part_ml[slot * 2 + 0] = M;
         p.part_ml[slot * 2 + 1] = L;
@@ -509,9 +510,9 @@ __device__ __forceinline__ void finalize_chunk(const DecodeParams &p, const Gath
 
 // Shared-memory carve-up: [stages][full barriers][empty barriers][abort flag, 3 words for the end
 // of the item]; the merge buffers alias the first two stages once the pipeline has drained.
-template <int kStages>
+template <int kStages, int kStage = kStageBytes>
 struct SmemLayout {
-  static constexpr int kBarOffset = kStages * kStageBytes;
+  static constexpr int kBarOffset = kStages * kStage;
   static constexpr int kBytes = kBarOffset + 2 * kStages * 8 + 16;
   static constexpr int kDynamicBytes = kBytes + 1024;  // room to align the base to 1024 B
 };
@@ -527,15 +528,18 @@ __device__ __forceinline__ uint32_t swz_off(int row, int c16) {
   return (uint32_t)((c16 >> 3) * 8192 + row * 128 + (((c16 & 7) ^ (row & 7)) << 4));
 }
 
-template <bool kPaged, int kStages, int kMinCtas>
+// kD: head_dim, 128 or 64.  A stage is a 64-token K tile and V tile of kD halves each (256 * kD bytes);
+// a tile is kD / 64 boxes of [64 tokens][64 halves], 128-byte swizzled.
+template <bool kPaged, int kStages, int kMinCtas, int kD>
 __global__ void __launch_bounds__(kThreads, kMinCtas)
 gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, const DecodeParams p,
                      const GatherParams gp) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ int s_plan[kPlanWords];
+  constexpr int kStage = 256 * kD, kKSteps = kD / 16, kNTiles = kD / 8;
   uint8_t *smem = align_1024(smem_raw);
-  uint64_t *full = reinterpret_cast<uint64_t *>(smem + SmemLayout<kStages>::kBarOffset);
+  uint64_t *full = reinterpret_cast<uint64_t *>(smem + SmemLayout<kStages, kStage>::kBarOffset);
   uint64_t *empty = full + kStages;
   volatile int *abort_flag = reinterpret_cast<volatile int *>(empty + kStages);
   volatile unsigned int *s_word = reinterpret_cast<volatile unsigned int *>(abort_flag + 1);
@@ -583,7 +587,7 @@ gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
   const bool direct = p.direct_ok && w.n - c_first == 1;
 
   if (warp == kConsumerWarps) {
-    produce_tiles<kPaged, kStages, kTileTokensF16, 2, 64>(&tmK, &tmV, p, smem, full, empty, abort_flag, b, hk,
+    produce_tiles<kPaged, kStages, kTileTokensF16, kD / 64, 64, kStage>(&tmK, &tmV, p, smem, full, empty, abort_flag, b, hk,
                                                           start, ntiles, lane, spec_start, spec_page);
     return;
   }
@@ -593,14 +597,14 @@ gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
   const bool use_hi = p.group > 8;  // rows 8..15 of the M dimension carry query heads too
   const __half *qh = reinterpret_cast<const __half *>(p.q);
 
-  // Q as the A operand, resident in registers: 8 k-steps x 4 regs.
-  uint32_t qa[8][4];
+  // Q as the A operand, resident in registers: kD / 16 k-steps x 4 regs.
+  uint32_t qa[kKSteps][4];
   {
-    const __half *q0 = qh + ((size_t)b * p.hq + (size_t)hk * p.group + g) * kHeadDim;
-    const __half *q1 = q0 + 8 * kHeadDim;
+    const __half *q0 = qh + ((size_t)b * p.hq + (size_t)hk * p.group + g) * kD;
+    const __half *q1 = q0 + 8 * kD;
     const bool v0 = g < p.group, v1 = g + 8 < p.group;
 #pragma unroll
-    for (int ks = 0; ks < 8; ++ks) {
+    for (int ks = 0; ks < kKSteps; ++ks) {
       const int c = ks * 16 + tq * 2;
       qa[ks][0] = v0 ? *reinterpret_cast<const uint32_t *>(q0 + c) : 0u;
       qa[ks][1] = v1 ? *reinterpret_cast<const uint32_t *>(q1 + c) : 0u;
@@ -609,9 +613,9 @@ gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
     }
   }
 
-  float o[16][4];
+  float o[kNTiles][4];
 #pragma unroll
-  for (int nt = 0; nt < 16; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
+  for (int nt = 0; nt < kNTiles; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
   float m0 = -INFINITY, m1 = -INFINITY;  // running max (log2 domain) of rows g, g+8
   float l0 = 0.f, l1 = 0.f;              // this thread's share of the running sums
   const float sl2 = p.scale * kLog2e;
@@ -629,15 +633,15 @@ gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
     const uint32_t phase = (i / kStages) & 1;
     ok = mbar_wait_bounded(&full[s], phase, abort_flag, p.wait_ns);
     if (!ok) break;
-    const uint32_t kbase = smem_u32(smem + (size_t)s * kStageBytes);
-    const uint32_t vbase = kbase + kStageBytes / 2;
+    const uint32_t kbase = smem_u32(smem + (size_t)s * kStage);
+    const uint32_t vbase = kbase + kStage / 2;
 
     // S(16 heads x 16 tokens) = Q . K^T
     float sc[2][4];
 #pragma unroll
     for (int j = 0; j < 2; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
 #pragma unroll
-    for (int ks = 0; ks < 8; ++ks) {
+    for (int ks = 0; ks < kKSteps; ++ks) {
       uint32_t b0, b1, b2, b3;
       ldmatrix_x4(b0, b1, b2, b3, kbase + swz_off(k_row, ks * 2 + k_c16));
       mma_16816(sc[0], qa[ks], b0, b1);
@@ -684,7 +688,7 @@ gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
     const bool rescale = use_hi ? (corr0 != 1.f || corr1 != 1.f) : (corr0 != 1.f);
     if (__any_sync(0xffffffffu, rescale)) {
 #pragma unroll
-      for (int nt = 0; nt < 16; ++nt) {
+      for (int nt = 0; nt < kNTiles; ++nt) {
         o[nt][0] *= corr0;
         o[nt][1] *= corr0;
         o[nt][2] *= corr1;
@@ -699,7 +703,7 @@ gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
     pa[2] = pack_half2(pr[1][0], pr[1][1]);
     pa[3] = pack_half2(pr[1][2], pr[1][3]);
 #pragma unroll
-    for (int np = 0; np < 8; ++np) {
+    for (int np = 0; np < kNTiles / 2; ++np) {
       uint32_t b0, b1, b2, b3;
       ldmatrix_x4_trans(b0, b1, b2, b3, vbase + swz_off(v_row, np * 2 + v_c16));
       if (edge) {
@@ -728,13 +732,13 @@ gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
   l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
   named_bar_sync(1, kConsumerThreads);  // every stage has been consumed: reuse stage memory
   if (*abort_flag) return;
-  float *mO = reinterpret_cast<float *>(smem);                     // [4][16][128]
-  float *mM = reinterpret_cast<float *>(smem + kStageBytes);       // [4][16]
+  float *mO = reinterpret_cast<float *>(smem);                // [4][16][kD]: 256 * kD bytes, one stage
+  float *mM = reinterpret_cast<float *>(smem + kStage);       // [4][16]
   float *mL = mM + kConsumerWarps * kMaxGroupMma;                  // [4][16]
   if (g < p.group) {
-    float *dst = mO + (warp * kMaxGroupMma + g) * kHeadDim + tq * 2;
+    float *dst = mO + (warp * kMaxGroupMma + g) * kD + tq * 2;
 #pragma unroll
-    for (int nt = 0; nt < 16; ++nt)
+    for (int nt = 0; nt < kNTiles; ++nt)
       *reinterpret_cast<float2 *>(dst + nt * 8) = make_float2(o[nt][0], o[nt][1]);
     if (tq == 0) {
       mM[warp * kMaxGroupMma + g] = m0;
@@ -742,9 +746,9 @@ gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
     }
   }
   if (g + 8 < p.group) {
-    float *dst = mO + (warp * kMaxGroupMma + g + 8) * kHeadDim + tq * 2;
+    float *dst = mO + (warp * kMaxGroupMma + g + 8) * kD + tq * 2;
 #pragma unroll
-    for (int nt = 0; nt < 16; ++nt)
+    for (int nt = 0; nt < kNTiles; ++nt)
       *reinterpret_cast<float2 *>(dst + nt * 8) = make_float2(o[nt][2], o[nt][3]);
     if (tq == 0) {
       mM[warp * kMaxGroupMma + g + 8] = m1;
@@ -752,7 +756,7 @@ gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
     }
   }
   named_bar_sync(1, kConsumerThreads);
-  finalize_chunk<__half>(p, gp, mO, mM, mL, b, hk, chunk, threadIdx.x, 1.0f, direct);
+  finalize_chunk<__half, kD>(p, gp, mO, mM, mL, b, hk, chunk, threadIdx.x, 1.0f, direct);
   finish_item<__half>(p, gp, w, hk, c_first, direct, 1.0f, threadIdx.x, kConsumerThreads, s_word,
                       [] { named_bar_sync(1, kConsumerThreads); });
 }
@@ -925,7 +929,7 @@ gqa_split_f32_kernel(const __grid_constant__ CUtensorMap tmK,
     }
   }
   named_bar_sync(1, kConsumerThreads);
-  finalize_chunk<float>(p, gp, mO, mM, mL, b, hk, chunk, threadIdx.x, sl2, direct);
+  finalize_chunk<float, kHeadDim>(p, gp, mO, mM, mL, b, hk, chunk, threadIdx.x, sl2, direct);
   finish_item<float>(p, gp, w, hk, c_first, direct, sl2, threadIdx.x, kConsumerThreads, s_word,
                      [] { named_bar_sync(1, kConsumerThreads); });
 }
@@ -1419,14 +1423,22 @@ bool set_smem(const void *kernel, int bytes) {
 
 constexpr int kStagesDefault = 3;
 
-template <bool kPaged>
-int launch_f16(const CUtensorMap &mk, const CUtensorMap &mv, const DecodeParams &p,
-               const GatherParams &g, dim3 grid, cudaStream_t st) {
-  auto kern = gqa_split_f16_kernel<kPaged, kStagesDefault, 2>;
-  constexpr int smem = SmemLayout<kStagesDefault>::kDynamicBytes;
+// head_dim 64 has half the bytes per stage: twice the stages keep the same 96 KB per CTA in flight
+template <bool kPaged, int kD>
+int launch_f16_d(const CUtensorMap &mk, const CUtensorMap &mv, const DecodeParams &p,
+                 const GatherParams &g, dim3 grid, cudaStream_t st) {
+  constexpr int kStages = kStagesDefault * 128 / kD;
+  auto kern = gqa_split_f16_kernel<kPaged, kStages, 2, kD>;
+  constexpr int smem = SmemLayout<kStages, 256 * kD>::kDynamicBytes;
   if (!set_smem(reinterpret_cast<const void *>(kern), smem)) return AXB200_DEVICE_ERROR;
   kern<<<grid, kThreads, smem, st>>>(mk, mv, p, g);
   return launch_status();
+}
+
+template <bool kPaged>
+int launch_f16(const CUtensorMap &mk, const CUtensorMap &mv, const DecodeParams &p,
+               const GatherParams &g, dim3 grid, cudaStream_t st) {
+  return p.d == 64 ? launch_f16_d<kPaged, 64>(mk, mv, p, g, grid, st) : launch_f16_d<kPaged, 128>(mk, mv, p, g, grid, st);
 }
 
 template <bool kPaged, int kGroup>
@@ -1560,7 +1572,8 @@ int decode_impl(bool paged, const void *q, void *out, const void *k, const void 
   const bool f16 = dtype == AXB200_FLOAT16;
   const float dom = p.scale * kLog2e;
 
-  bool tiled = d == kHeadDim && aligned16(k) && aligned16(v) && aligned16(q) && encode_fn();
+  const bool f16_in = dtype == AXB200_FLOAT16;
+  bool tiled = (d == kHeadDim || (d == 64 && f16_in)) && aligned16(k) && aligned16(v) && aligned16(q) && encode_fn();
   if (tiled && f16 && p.group > kMaxGroupMma) tiled = false;
   if (tiled && !f16 && !(p.group == 1 || p.group == 2 || p.group == 4 || p.group == 8))
     tiled = false;

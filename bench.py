@@ -59,10 +59,9 @@ METRIC = "gqa_decode_kv_cache_bandwidth"
 UNIT = "GB/s"
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
-# DRAM bytes moved per algorithmic byte by the split kernel, from an ncu capture of a batch-8 case of the
-# same kernel: (dram read + write) / algorithmic bytes, taken to scale in proportion to the tokens a
-# launch processes.
-TRAFFIC_PER_ALGO_BYTE = 1.026
+# DRAM bytes moved per algorithmic byte by the split kernel: (dram read + write) / algorithmic bytes of one
+# launch of this workload's full batch of 64 under ncu (a one-pass capture of the two DRAM byte counters).
+TRAFFIC_PER_ALGO_BYTE = 1.003
 
 WORKLOADS = {
     "c3_ragged": dict(batch=64, lo=16384, hi=32768),
@@ -1097,6 +1096,7 @@ def run_small_ops(args):
     big_a, big_b = rn(16384, HKV, D), rn(1, HKV, D)            # the reference's cache.update at 16 K tokens
     half_src, wn = rn(B, 2048), torch.ones(D, dtype=torch.float16, device="cuda")
     q80, k80, v80 = rn(1, 16, 80), rn(8192, 8, 80), rn(8192, 8, 80)  # a head size the TMA kernels do not take
+    q64, k64, v64 = rn(1, 16, 64), rn(32768, 8, 64), rn(32768, 8, 64)  # head_dim 64: the TMA kernel's second shape
     qf, kf, vf = rn(1, HQ, D, dt=torch.float32), rn(8192, HKV, D, dt=torch.float32), rn(8192, HKV, D, dt=torch.float32)
     elem = 2
     cases = [
@@ -1111,6 +1111,8 @@ def run_small_ops(args):
         ("rms_norm q heads [16,16,128]", lambda: ops.rms_norm(xq[:B], wn, 1e-6), 2 * B * HQ * D * elem),
         ("gqa_decode generic kernel, head_dim 80, 8192 keys", lambda: ops.gqa_decode_attention(q80, k80, v80),
          2 * k80.numel() * elem),
+        ("gqa_decode TMA kernel, head_dim 64, 32768 keys", lambda: ops.gqa_decode_attention(q64, k64, v64),
+         2 * k64.numel() * elem),
         ("gqa_decode fp32, one sequence of 8192 keys", lambda: ops.gqa_decode_attention(qf, kf, vf), 2 * kf.numel() * 4),
     ]
     cases.append(("cast f16 -> f32 [16,2048]", lambda: ops.cast(half_src, torch.float32), half_src.numel() * 6))

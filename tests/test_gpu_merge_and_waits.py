@@ -77,7 +77,7 @@ def _cache(dtype, lens, hq, hkv, d, seed, capacity=None):
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
-@pytest.mark.parametrize("hq,hkv,d", [(16, 8, 128), (6, 2, 80), (16, 1, 128)])
+@pytest.mark.parametrize("hq,hkv,d", [(16, 8, 128), (6, 2, 80), (16, 1, 128), (8, 2, 64)])
 def test_fused_merge_equals_combine_kernel_bit_for_bit(both_merges, plan_mode, dtype, hq, hkv, d):
     from axono_b200 import ops
 
@@ -259,4 +259,30 @@ def test_chunk_length_override_changes_nothing_but_rounding(lib):
             assert oracle.rel_err(got.cpu().numpy(), base.cpu().numpy()) <= 2e-6
     finally:
         lib.axb200_set_chunk_tiles(0)
+    assert ops.last_error() == 0
+
+
+@pytest.mark.parametrize("hq,hkv", [(16, 8), (32, 8), (8, 8), (12, 4)])
+def test_head_dim_64_on_the_tma_kernel(hq, hkv):
+    """fp16 with head_dim 64 runs on the TMA / tensor-core split kernel (one 64 x 64 box per tile): ragged
+    paged batch against the oracle, page-permutation invariance, and the reference layout."""
+    from axono_b200 import ops
+
+    lens = [4100, 1, 63, 64, 65, 9000, 2500]
+    cache, q, k, v = _cache(torch.float16, lens, hq, hkv, 64, seed=37)
+    qd = dev(q, torch.float16)
+    out = cache.attend(0, qd)
+    orc = oracle.best()
+    for b in range(len(lens)):
+        ref = orc.gqa_decode(q[b : b + 1], k[b, : lens[b]], v[b, : lens[b]])
+        assert oracle.rel_err(out[b : b + 1].float().cpu().numpy(), ref) <= 2e-3, b
+    cache2, _, _, _ = _cache(torch.float16, lens, hq, hkv, 64, seed=37)
+    perm = torch.randperm(cache2.num_pages, generator=torch.Generator().manual_seed(5)).to(torch.int32)
+    from axono_b200.kv_cache import PagedKVCache
+
+    cache3 = PagedKVCache(1, len(lens), hkv, 64, max(lens), dtype=torch.float16, page_order=perm)
+    cache3.fill(0, dev(k, torch.float16), dev(v, torch.float16), lens)
+    assert torch.equal(cache3.attend(0, qd), out)
+    single = ops.gqa_decode_attention(qd[5:6].contiguous(), dev(k[5, :9000], torch.float16), dev(v[5, :9000], torch.float16))
+    assert oracle.rel_err(single.float().cpu().numpy(), orc.gqa_decode(q[5:6], k[5, :9000], v[5, :9000])) <= 2e-3
     assert ops.last_error() == 0
