@@ -264,6 +264,7 @@ def run_reference_arm(args):
         "higher_is_better": True, "scaling": scaling, "vs_baseline": None, "dtype": args.dtype,
         "data": "synthetic", "config": common_config(args.workload, world, scaling),
         "arithmetic": "fp32 on the CPU (the only type the reference's op takes)",
+        "bytes_actually_read_gbs": 2.0 * value,  # the CPU code streams fp32 K/V: twice the workload's fp16 bytes
         "tokens_per_s": len(lens) * args.steps / dt,
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": orc.kind, "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},

@@ -404,3 +404,77 @@ def test_several_graphs_alive_at_once(lx):
     g1.replay()
     assert np.array_equal(g1.output.numpy(), first)
     g1.reset()
+
+
+def test_framework_free_services(lx, chk):
+    """What a program without any framework takes from the module besides the operators: device choice,
+    the seeded device fill, page-locked arrays, event timing, views of foreign device memory, and the
+    arena's read-back - exercised the way bench.py's default arm uses them."""
+    assert lx.current_device() == 0 and isinstance(lx.device_pci_bus_id(0), str) and lx.device_pci_bus_id(0)
+    assert lx.current_stream() == 0  # legacy default stream outside capture
+    f16 = lx.DataType.FLOAT16
+    a = lx.randn([1 << 16], f16, "cuda", 7, 0.0, 0.5).numpy().astype(np.float32)
+    b = lx.randn([1 << 16], f16, "cuda", 7, 0.0, 0.5).numpy().astype(np.float32)
+    c = lx.randn([1 << 16], f16, "cuda", 8, 0.0, 0.5).numpy().astype(np.float32)
+    assert np.array_equal(a, b) and not np.array_equal(a, c)  # (seed, index) decides the value
+    assert abs(a.mean()) < 0.01 and abs(a.std() - 0.5) < 0.01 and np.isfinite(a).all()
+    short = lx.randn([1000], f16, "cuda", 7, 0.0, 0.5).numpy().astype(np.float32)
+    assert np.array_equal(short, a[:1000])  # the launch shape does not matter
+    p = lx.pinned_empty([4, 8], lx.DataType.FLOAT32)
+    assert p.shape == (4, 8) and p.dtype == np.float32
+    p[...] = 3.0
+    t = lx.Tensor.from_numpy(p, "cuda")
+    view = lx.Tensor.from_device_ptr(t.data_ptr, lx.DataType.FLOAT32, [32], "cuda")
+    assert np.array_equal(view.numpy(), np.full(32, 3.0, np.float32))
+    timer = lx.EventTimer()
+    timer.start()
+    lx.randn([1 << 24], f16, "cuda", 1)
+    timer.stop()
+    assert 0.0 < timer.elapsed_ms() < 100.0
+
+    # an arena with scattered pages, filled on the device, read back token-major
+    hkv, d, page, cap, B = 2, 128, 64, 1000, 3
+    blocks = (cap + page - 1) // page
+    arena = lx.KVArena(1, B * blocks, hkv, page, d, f16, B, blocks)
+    arena.shuffle_free(5)
+    for _ in range(B):
+        arena.alloc_seq(cap)
+    arena.sync()
+    arena.fill_normal(3, 0.5)
+    lens = np.asarray([1000, 70, 0], np.int32)
+    arena.set_seq_lens(lens)
+    rng = np.random.default_rng(1)
+    q = rng.standard_normal((B, 4, d)).astype(np.float16)
+    out = lx.Tensor(f16, [B, 4, d], "cuda")
+    got = lx.gqa_decode_attention_paged(dev(lx, q), arena, 0, cap, out=out)
+    assert got.data_ptr == out.data_ptr  # written in place
+    res = out.numpy().astype(np.float32)
+    for b in (0, 1):
+        k, v = arena.gather(0, b, int(lens[b]))
+        assert k.shape == (lens[b], hkv, d)
+        assert oracle.rel_err(res[b : b + 1], chk.gqa_decode(f32(q[b : b + 1]), f32(k), f32(v))) <= 2e-3
+    assert np.all(res[2] == 0)
+
+    # the host-buffer step on page-locked arrays: same bits as append + attention on device tensors
+    twin = lx.KVArena(1, B * blocks, hkv, page, d, f16, B, blocks)
+    twin.shuffle_free(5)
+    for _ in range(B):
+        twin.alloc_seq(cap)
+    twin.sync()
+    twin.fill_normal(3, 0.5)
+    twin.set_seq_lens(lens)
+    qh, oh = lx.pinned_empty([B, 4, d], f16), lx.pinned_empty([B, 4, d], f16)
+    kh, vh = lx.pinned_empty([B, hkv, d], f16), lx.pinned_empty([B, hkv, d], f16)
+    qh[...] = q
+    kh[...] = rng.standard_normal((B, hkv, d)).astype(np.float16)
+    vh[...] = rng.standard_normal((B, hkv, d)).astype(np.float16)
+    stage = [lx.Tensor(f16, [B, 4, d], "cuda"), lx.Tensor(f16, [B, hkv, d], "cuda"), lx.Tensor(f16, [B, hkv, d], "cuda"),
+             lx.Tensor(f16, [B, 4, d], "cuda")]
+    ws = lx.Tensor(lx.DataType.INT8, [max(256, lx.gqa_workspace_bytes(B, 4, hkv, d, cap, f16))], "cuda")
+    lx.decode_step_host(arena, 0, qh, kh, vh, oh, stage[0], stage[1], stage[2], stage[3], ws, cap, 1e6)
+    qd = dev(lx, qh.copy())
+    lx.kv_append_rope(twin, 0, qd, dev(lx, kh.copy()), dev(lx, vh.copy()), theta=1e6)
+    want = lx.gqa_decode_attention_paged(qd, twin, 0, cap).numpy()
+    assert np.array_equal(oh, want)
+    assert np.array_equal(arena.seq_lens(), lens + 1)
+    assert lx.device_error_bits() == 0
