@@ -463,7 +463,7 @@ def run_native(args):
     lx = native.load()
     if not lx.cuda_available():
         raise SystemExit("bench.py needs a CUDA device: the decode path has no CPU fallback")
-    rdv = Rendezvous.from_env()
+    rdv = Rendezvous.from_env(timeout=600.0)  # set-up of a rank (weights, tens of GB of cache) may take minutes
     world, rank = rdv.world, rdv.rank
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     lx.set_device(local_rank)
@@ -943,7 +943,7 @@ def run_tower_native(args):
     from axono_b200.rendezvous import Rendezvous
 
     lx = native.load()
-    rdv = Rendezvous.from_env()
+    rdv = Rendezvous.from_env(timeout=600.0)  # set-up of a rank (weights, tens of GB of cache) may take minutes
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     lx.set_device(local_rank)
     sampler = ClockSampler(local_rank, use_torch=False, pci_bus_id=lx.device_pci_bus_id(local_rank))
