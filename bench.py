@@ -86,7 +86,7 @@ def common_config(workload: str, world: int, scaling: str) -> dict:
             "head_dim": D, "kv_len": [int(w["lo"]), int(w["hi"])], "page_tokens": PAGE_TOKENS,
             "sharding": f"batch x{world}, no collective on the attention path",
             "l2": "inputs larger than L2 (several GB of KV per step)",
-            "step": "kv_append_rope + gqa_decode_paged"}
+            "step": "kv_append_rope + gqa_decode_paged, one CUDA graph per step"}
 
 
 def algo_bytes(lens: np.ndarray, elem: int = 2) -> float:
@@ -154,7 +154,7 @@ class ClockSampler:
                             self.reasons.add(name)
                 except Exception:
                     pass
-            time.sleep(0.004)
+            time.sleep(0.01)
 
     def start(self):
         self._active.set()
@@ -340,6 +340,37 @@ class NativeStep:
             sampler.pause()
         return rdv.max(ms), my_bytes
 
+    def capture_step(self):
+        """The step as one CUDA graph (append + attention, sized for the cache's capacity so that replays
+        follow the growing cache).  Capturing runs the step once for real."""
+        from axono_b200 import native
+
+        def body():
+            self.lx.kv_append_rope(self.arena, 0, self.q, self.k_new, self.v_new, theta=1e6)
+            self.lx.gqa_decode_attention_paged(self.q, self.arena, 0, self.capacity, out=self.out)
+            return self.out
+
+        g = native.CUDAGraph().capture(body)
+        self.cur += 1
+        self.bound = min(self.capacity, self.bound + 1)
+        return g
+
+    def timed_replays(self, rdv, g, steps):
+        """K replays of the captured step, launched back to back from native code between two CUDA events
+        on the graph's stream, a barrier and a device synchronisation on both sides.  Returns (max over
+        ranks of the device milliseconds, this rank's algorithmic bytes, every rank's milliseconds)."""
+        lx = self.lx
+        my_bytes = self.bytes_of_steps(steps)
+        lx.synchronize()
+        rdv.barrier()
+        ms = g.replay_timed(steps) * steps
+        self.cur += steps
+        self.bound = min(self.capacity, self.bound + steps)
+        lx.synchronize()
+        rdv.barrier()
+        per_rank = [float(x) for x in rdv.all_gather_object(ms)]
+        return max(per_rank), my_bytes, per_rank
+
     def kernel_alone(self, steps):
         """The split kernel by itself: event pairs the library records around its launches."""
         lx = self.lx
@@ -495,9 +526,15 @@ def run_native(args):
     B = run.B
     # ---- value: inputs resident, CUDA events around K steps ----
     sampler.start()  # sampled from here to the end of the host-buffer phase: the GPU is under this load throughout
-    for _ in range(args.warmup):
-        run.step()
-    dev_ms, my_bytes = run.timed_steps(rdv, args.steps)
+    # The step is captured once as a CUDA graph and the K timed steps are K replays launched from native
+    # code: at several GPUs a step lasts 0.1-0.2 ms and the whole timed region a few milliseconds, which a
+    # single scheduling hiccup of the Python thread on any one rank would otherwise double (max over ranks).
+    graph = run.capture_step()
+    if args.warmup > 1:
+        graph.replay_timed(args.warmup - 1)
+        run.cur += args.warmup - 1
+        run.bound = min(run.capacity, run.bound + args.warmup - 1)
+    dev_ms, my_bytes, ms_by_rank = run.timed_replays(rdv, graph, args.steps)
     all_bytes = rdv.sum(my_bytes)
     value = all_bytes / (dev_ms / 1e3) / 1e9
     total_seqs = rdv.sum(B)
@@ -508,6 +545,15 @@ def run_native(args):
     check = run.check_output([0, B - 1] if B > 1 else [0]) if rank == 0 and not args.no_check else None
     if check and check["rel_err"] > check["tolerance"]:
         raise SystemExit(f"the timed output differs from the CPU checker: {check}")
+
+    # the same K steps launched one by one from Python (two operator calls a step), for the record
+    run.set_lengths(lens)
+    for _ in range(min(args.warmup, 3)):
+        run.step()
+    eager_ms, eager_bytes = run.timed_steps(rdv, args.steps)
+    eager = {"value": rdv.sum(eager_bytes) / (eager_ms / 1e3) / 1e9, "unit": UNIT, "ms_per_step": eager_ms / args.steps,
+             "launch": "two operator calls per step from Python"}
+    graph.reset()
 
     # ---- roofline: the split kernel alone, event pairs around its launches ----
     run.set_lengths(lens)
@@ -532,7 +578,7 @@ def run_native(args):
     sampler.pause()
     clocks = sampler.summary()
 
-    extra = {}
+    extra = {"eager_steps": eager, "timed_ms_by_rank": [round(x, 4) for x in ms_by_rank]}
     if check:
         extra["output_check"] = check
     full = args.workload == "c3_ragged" and not args.no_extra and args.dtype == "f16" and args.shard_of == 1
