@@ -193,6 +193,31 @@ def _native_worker(rank, world, key, out_dir):
         single.token_ids.copy_from(shard.token_ids)  # keep the two on the same trajectory
     assert lx.device_error_bits() == 0
     shard.close()
+
+    # the library form of the gather (ncclAllGather + re-layout, recorded into the step's graph): the
+    # same step from the same state as the unsharded tower
+    coll = NativeTextTower(cfg, Bt, 512, seed=3, device=device, rdv=rdv, weights=single.host_weights, gather="nccl")
+    ref = NativeTextTower(cfg, Bt, 512, seed=3, device=device, weights=single.host_weights)
+    ref.arena.fill_normal(full_seed, 0.5)
+    for li in range(cfg.n_layers):
+        for b in range(Bt):
+            kf, vf = ref.arena.gather(li, b, lens[b])
+            write_tokens(coll.arena, li, b, np.ascontiguousarray(kf[:, rank * per:(rank + 1) * per]),
+                         np.ascontiguousarray(vf[:, rank * per:(rank + 1) * per]))
+    coll.set_state(tok, lens)
+    ref.set_state(tok, lens)
+    gc = native.CUDAGraph().capture(coll.decode_step)  # warm-up run = step 1, then captured with the collective inside
+    ref.decode_step()
+    for step in range(2):
+        lx.synchronize()
+        a, b_ = coll.last_logits.numpy().astype(np.float32), ref.last_logits.numpy().astype(np.float32)
+        err = float(np.abs(a - b_).max() / np.abs(b_).max())
+        assert err <= 2e-2, f"rank {rank} NCCL step {step}: logits differ {err:.3e}"
+        ref.token_ids.copy_from(coll.token_ids)
+        gc.replay()
+        ref.decode_step()
+    assert gc.num_nodes > 0 and lx.device_error_bits() == 0
+    coll.close()
     rdv.close()
     open(os.path.join(out_dir, f"native_ok{rank}"), "w").close()
 
