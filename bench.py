@@ -615,7 +615,12 @@ def run_native(args):
         wk.close()
         del wk
     if full and not args.no_tower:
-        extra["c5_tower"] = tower_figures(args, lx, rdv, device)
+        # for the record, after everything the line's own figures need: a failure here (or a rank lost in
+        # it) is reported in place and does not take the attention figures with it
+        try:
+            extra["c5_tower"] = tower_figures(args, lx, rdv, device)
+        except (Exception, SystemExit) as e:  # noqa: BLE001
+            extra["c5_tower"] = {"error": f"{type(e).__name__}: {e}"[:400]}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:

@@ -286,3 +286,56 @@ def test_head_dim_64_on_the_tma_kernel(hq, hkv):
     single = ops.gqa_decode_attention(qd[5:6].contiguous(), dev(k[5, :9000], torch.float16), dev(v[5, :9000], torch.float16))
     assert oracle.rel_err(single.float().cpu().numpy(), orc.gqa_decode(q[5:6], k[5, :9000], v[5, :9000])) <= 2e-3
     assert ops.last_error() == 0
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_random_paged_batches_against_the_oracle(seed, lib):
+    """Seeded random configurations of the batched decode call - batch, head counts, head_dim (both TMA
+    shapes and a generic one), dtype, page size, ragged lengths with empty and one-token sequences, an
+    optional sliding window, either chunk plan, either merge - every sequence against the oracle."""
+    from axono_b200 import ops
+    from axono_b200.kv_cache import PagedKVCache
+
+    rng = np.random.default_rng(9000 + seed)
+    d = int(rng.choice([128, 128, 64, 80]))
+    hkv = int(rng.choice([1, 2, 4, 8]))
+    group = int(rng.choice([1, 2, 4]) if d != 80 else rng.choice([1, 3]))
+    hq = hkv * group
+    dtype = torch.float16 if (d == 64 or rng.random() < 0.6) else torch.float32
+    B = int(rng.integers(1, 7))
+    lens = [int(x) for x in rng.choice([0, 1, 63, 64, 65, 700, 2049, 5000, 9000], B)]
+    if max(lens) == 0:
+        lens[0] = 300
+    page_tokens = int(rng.choice([64, 128]))
+    window = int(rng.choice([0, 0, 100, 1000]))
+    lib.axb200_set_device_plan(int(rng.integers(0, 2)))
+    lib.axb200_set_fused_merge(int(rng.integers(0, 2)))
+    try:
+        Lmax = max(lens)
+        q = rng.standard_normal((B, hq, d)).astype(np.float32)
+        k = (0.5 * rng.standard_normal((B, Lmax, hkv, d))).astype(np.float32)
+        v = (0.5 * rng.standard_normal((B, Lmax, hkv, d))).astype(np.float32)
+        if dtype == torch.float16:
+            q, k, v = widen(q), widen(k), widen(v)
+        cache = PagedKVCache(1, B, hkv, d, Lmax, dtype=dtype, page_tokens=page_tokens)
+        perm = torch.from_numpy(rng.permutation(cache.num_pages).astype(np.int32))
+        cache.block_table = perm.reshape(B, cache.max_blocks).contiguous().cuda()
+        cache.k_pages[0].fill_(float("nan"))
+        cache.v_pages[0].fill_(float("nan"))
+        cache.fill(0, dev(k, dtype), dev(v, dtype), lens)
+        out = cache.attend(0, dev(q, dtype), window=window).float().cpu().numpy()
+        torch.cuda.synchronize()
+    finally:
+        lib.axb200_set_device_plan(0)
+        lib.axb200_set_fused_merge(1)
+    assert ops.last_error() == 0
+    orc = oracle.best()
+    tol = 1e-5 if dtype == torch.float32 else 2e-3
+    for b, n in enumerate(lens):
+        if n == 0:
+            assert np.all(out[b] == 0)
+            continue
+        lo = max(0, n - window) if window else 0
+        ref = orc.gqa_decode(q[b : b + 1], k[b, lo:n], v[b, lo:n])
+        err = oracle.rel_err(out[b : b + 1], ref)
+        assert err <= tol, f"seed {seed} d={d} hq={hq} hkv={hkv} {dtype} lens={lens} window={window} b={b}: {err:.3e}"
