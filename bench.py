@@ -39,6 +39,7 @@ from __future__ import annotations
 
 import argparse
 import ctypes
+import gc
 import json
 import os
 import statistics
@@ -261,7 +262,7 @@ def run_reference_arm(args):
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
-        "higher_is_better": True, "scaling": scaling, "vs_baseline": None, "dtype": args.dtype,
+        "higher_is_better": True, "scaling": scaling, "vs_baseline": None, "dtype": "f32",
         "data": "synthetic", "config": common_config(args.workload, world, scaling),
         "arithmetic": "fp32 on the CPU (the only type the reference's op takes)",
         "bytes_actually_read_gbs": 2.0 * value,  # the CPU code streams fp32 K/V: twice the workload's fp16 bytes
@@ -406,10 +407,12 @@ class NativeStep:
         my_bytes = self.bytes_of_steps(steps)
         lx.synchronize()
         rdv.barrier()
+        gc.disable()  # a collection in the middle of a few-millisecond region would be most of it
         t0 = time.perf_counter()
         for _ in range(steps):
             one()
         dt = time.perf_counter() - t0
+        gc.enable()
         rdv.barrier()
         return rdv.max(dt), my_bytes, (q_h.nbytes + k_h.nbytes + v_h.nbytes), out_h.nbytes
 
