@@ -481,7 +481,7 @@ __device__ __forceinline__ void finalize_chunk(const DecodeParams &p, const Gath
                                                const float *mO, const float *mM, const float *mL,
                                                int b, int hk, int chunk, int t, float dom,
                                                bool direct) {
-  if (t >= kD) return;  // head_dim 64: half of the consumer threads own no output dim
+  if (t >= p.d) return;  // threads past the head size own no output dim (kD is the padded tile width)
   for (int r = 0; r < p.group; ++r) {
     float M = -INFINITY;
 #pragma unroll
@@ -499,7 +499,7 @@ __device__ __forceinline__ void finalize_chunk(const DecodeParams &p, const Gath
       emit_final<OutT>(p, gp, b, h, t, acc, M, L);
     } else {
       const size_t slot = ((size_t)b * p.hq + h) * p.max_chunks + chunk;
-      p.part_o[slot * kD + t] = acc;
+      p.part_o[slot * p.d + t] = acc;
       if (t == 0) {
         p.part_ml[slot * 2 + 0] = M;
         p.part_ml[slot * 2 + 1] = L;
@@ -528,8 +528,11 @@ __device__ __forceinline__ uint32_t swz_off(int row, int c16) {
   return (uint32_t)((c16 >> 3) * 8192 + row * 128 + (((c16 & 7) ^ (row & 7)) << 4));
 }
 
-// kD: head_dim, 128 or 64.  A stage is a 64-token K tile and V tile of kD halves each (256 * kD bytes);
-// a tile is kD / 64 boxes of [64 tokens][64 halves], 128-byte swizzled.
+// kD: width of the staged tiles, 128 or 64 halves; the head size p.d is any multiple of 8 up to kD.  A
+// stage is a 64-token K tile and V tile of kD halves each (256 * kD bytes); a tile is kD / 64 boxes of
+// [64 tokens][64 halves], 128-byte swizzled.  Columns at and past p.d lie outside the tensor map, so the
+// copy engine fills them with zeros (and reads nothing for them); q is padded with zeros in registers;
+// zero columns add nothing to a dot product, and the output columns past p.d are never stored.
 template <bool kPaged, int kStages, int kMinCtas, int kD>
 __global__ void __launch_bounds__(kThreads, kMinCtas)
 gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
@@ -600,16 +603,17 @@ gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
   // Q as the A operand, resident in registers: kD / 16 k-steps x 4 regs.
   uint32_t qa[kKSteps][4];
   {
-    const __half *q0 = qh + ((size_t)b * p.hq + (size_t)hk * p.group + g) * kD;
-    const __half *q1 = q0 + 8 * kD;
+    const __half *q0 = qh + ((size_t)b * p.hq + (size_t)hk * p.group + g) * p.d;
+    const __half *q1 = q0 + 8 * p.d;
     const bool v0 = g < p.group, v1 = g + 8 < p.group;
 #pragma unroll
     for (int ks = 0; ks < kKSteps; ++ks) {
-      const int c = ks * 16 + tq * 2;
-      qa[ks][0] = v0 ? *reinterpret_cast<const uint32_t *>(q0 + c) : 0u;
-      qa[ks][1] = v1 ? *reinterpret_cast<const uint32_t *>(q1 + c) : 0u;
-      qa[ks][2] = v0 ? *reinterpret_cast<const uint32_t *>(q0 + c + 8) : 0u;
-      qa[ks][3] = v1 ? *reinterpret_cast<const uint32_t *>(q1 + c + 8) : 0u;
+      const int c = ks * 16 + tq * 2;  // even, and p.d is a multiple of 8: a pair is inside or outside as a whole
+      const bool in0 = c < p.d, in1 = c + 8 < p.d;
+      qa[ks][0] = v0 && in0 ? *reinterpret_cast<const uint32_t *>(q0 + c) : 0u;
+      qa[ks][1] = v1 && in0 ? *reinterpret_cast<const uint32_t *>(q1 + c) : 0u;
+      qa[ks][2] = v0 && in1 ? *reinterpret_cast<const uint32_t *>(q0 + c + 8) : 0u;
+      qa[ks][3] = v1 && in1 ? *reinterpret_cast<const uint32_t *>(q1 + c + 8) : 0u;
     }
   }
 
@@ -1438,7 +1442,7 @@ int launch_f16_d(const CUtensorMap &mk, const CUtensorMap &mv, const DecodeParam
 template <bool kPaged>
 int launch_f16(const CUtensorMap &mk, const CUtensorMap &mv, const DecodeParams &p,
                const GatherParams &g, dim3 grid, cudaStream_t st) {
-  return p.d == 64 ? launch_f16_d<kPaged, 64>(mk, mv, p, g, grid, st) : launch_f16_d<kPaged, 128>(mk, mv, p, g, grid, st);
+  return p.d <= 64 ? launch_f16_d<kPaged, 64>(mk, mv, p, g, grid, st) : launch_f16_d<kPaged, 128>(mk, mv, p, g, grid, st);
 }
 
 template <bool kPaged, int kGroup>
@@ -1573,7 +1577,10 @@ int decode_impl(bool paged, const void *q, void *out, const void *k, const void 
   const float dom = p.scale * kLog2e;
 
   const bool f16_in = dtype == AXB200_FLOAT16;
-  bool tiled = (d == kHeadDim || (d == 64 && f16_in)) && aligned16(k) && aligned16(v) && aligned16(q) && encode_fn();
+  // fp16: any head size that is a multiple of 8 up to 128 (rows stay 16-byte multiples for the tensor
+  // map; narrower heads ride in the 64- or 128-wide tile with zero fill); fp32: 128
+  bool tiled = (d == kHeadDim || (f16_in && d % 8 == 0 && d <= kHeadDim)) && aligned16(k) && aligned16(v) &&
+               aligned16(q) && encode_fn();
   if (tiled && f16 && p.group > kMaxGroupMma) tiled = false;
   if (tiled && !f16 && !(p.group == 1 || p.group == 2 || p.group == 4 || p.group == 8))
     tiled = false;

@@ -339,3 +339,23 @@ def test_random_paged_batches_against_the_oracle(seed, lib):
         ref = orc.gqa_decode(q[b : b + 1], k[b, lo:n], v[b, lo:n])
         err = oracle.rel_err(out[b : b + 1], ref)
         assert err <= tol, f"seed {seed} d={d} hq={hq} hkv={hkv} {dtype} lens={lens} window={window} b={b}: {err:.3e}"
+
+
+@pytest.mark.parametrize("d,hq,hkv", [(8, 4, 2), (48, 6, 2), (72, 8, 8), (80, 32, 2), (96, 16, 8), (120, 4, 4)])
+def test_fp16_head_sizes_below_the_tile_width(d, hq, hkv):
+    """fp16 head sizes that are multiples of 8 up to 128 ride in the 64- or 128-wide TMA tile: the columns
+    past the head size lie outside the tensor map and read as zeros.  Paged and reference layout, against
+    the oracle; NaN poison in every unused slot shows that nothing beyond a row's own bytes is read."""
+    from axono_b200 import ops
+
+    lens = [3000, 65, 1, 8200]
+    cache, q, k, v = _cache(torch.float16, lens, hq, hkv, d, seed=38)
+    qd = dev(q, torch.float16)
+    out = cache.attend(0, qd).float().cpu().numpy()
+    orc = oracle.best()
+    for b in range(len(lens)):
+        ref = orc.gqa_decode(q[b : b + 1], k[b, : lens[b]], v[b, : lens[b]])
+        assert oracle.rel_err(out[b : b + 1], ref) <= 2e-3, (d, b)
+    single = ops.gqa_decode_attention(qd[3:4].contiguous(), dev(k[3, :8200], torch.float16), dev(v[3, :8200], torch.float16))
+    assert oracle.rel_err(single.float().cpu().numpy(), orc.gqa_decode(q[3:4], k[3, :8200], v[3, :8200])) <= 2e-3
+    assert np.isfinite(out).all() and ops.last_error() == 0
