@@ -1150,7 +1150,8 @@ def run_small_ops(args):
     cache = PagedKVCache(1, 2, HKV, D, 2048, dtype=torch.float16, device="cuda")
     big_a, big_b = rn(16384, HKV, D), rn(1, HKV, D)            # the reference's cache.update at 16 K tokens
     half_src, wn = rn(B, 2048), torch.ones(D, dtype=torch.float16, device="cuda")
-    q80, k80, v80 = rn(1, 16, 80), rn(8192, 8, 80), rn(8192, 8, 80)  # a head size the TMA kernels do not take
+    q80, k80, v80 = rn(1, 16, 80), rn(8192, 8, 80), rn(8192, 8, 80)  # rides in the 128-wide TMA tile, zero-filled
+    q84, k84, v84 = rn(1, 16, 84), rn(8192, 8, 84), rn(8192, 8, 84)  # not a multiple of 8: the generic kernel
     q64, k64, v64 = rn(1, 16, 64), rn(32768, 8, 64), rn(32768, 8, 64)  # head_dim 64: the TMA kernel's second shape
     qf, kf, vf = rn(1, HQ, D, dt=torch.float32), rn(8192, HKV, D, dt=torch.float32), rn(8192, HKV, D, dt=torch.float32)
     elem = 2
@@ -1164,8 +1165,10 @@ def run_small_ops(args):
          2 * (xq.numel() + 2 * xk.numel()) * elem),
         ("concat axis 0: [16384,8,128] ++ [1,8,128]", lambda: ops.concat(big_a, big_b, 0), 2 * big_a.numel() * elem),
         ("rms_norm q heads [16,16,128]", lambda: ops.rms_norm(xq[:B], wn, 1e-6), 2 * B * HQ * D * elem),
-        ("gqa_decode generic kernel, head_dim 80, 8192 keys", lambda: ops.gqa_decode_attention(q80, k80, v80),
+        ("gqa_decode TMA kernel, head_dim 80 (zero-filled to 128), 8192 keys", lambda: ops.gqa_decode_attention(q80, k80, v80),
          2 * k80.numel() * elem),
+        ("gqa_decode generic kernel, head_dim 84, 8192 keys", lambda: ops.gqa_decode_attention(q84, k84, v84),
+         2 * k84.numel() * elem),
         ("gqa_decode TMA kernel, head_dim 64, 32768 keys", lambda: ops.gqa_decode_attention(q64, k64, v64),
          2 * k64.numel() * elem),
         ("gqa_decode fp32, one sequence of 8192 keys", lambda: ops.gqa_decode_attention(qf, kf, vf), 2 * kf.numel() * 4),
