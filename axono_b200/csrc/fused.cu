@@ -274,15 +274,56 @@ __device__ __forceinline__ ArgBest arg_better(ArgBest a, ArgBest b) {
   return (b.v > a.v || (b.v == a.v && b.i < a.i)) ? b : a;
 }
 
+// 16 bytes of a row as floats (4 floats or 8 halves)
+__device__ __forceinline__ void arg_ld16(const float *p, float (&f)[4]) {
+  const float4 v = *reinterpret_cast<const float4 *>(p);
+  f[0] = v.x, f[1] = v.y, f[2] = v.z, f[3] = v.w;
+}
+__device__ __forceinline__ void arg_ld16(const __half *p, float (&f)[8]) {
+  const uint4 v = *reinterpret_cast<const uint4 *>(p);
+  const __half2 *h = reinterpret_cast<const __half2 *>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __half22float2(h[i]);
+    f[2 * i] = t.x, f[2 * i + 1] = t.y;
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(1024)
-argmax_kernel(const T *x, int64_t *out, int cols) {
+argmax_kernel(const T *x, int64_t *out, int cols, int vec) {  // vec: rows are 16-byte aligned multiples of 16 bytes
   __shared__ ArgBest s_best[32];
   const T *row = x + (size_t)blockIdx.x * cols;
   ArgBest best{-INFINITY, 0x7fffffff};
-  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
-    const float v = ldf(row + c);
-    if (v > best.v || (v == best.v && c < best.i)) best = ArgBest{v, c};  // NaN never wins
+  if (vec) {
+    // a vocabulary-sized row is hundreds of KB per CTA: 16-byte loads, four in flight per thread
+    constexpr int kN = 16 / (int)sizeof(T), kUnroll = 4;
+    const int nvec = cols / kN;
+    for (int v0 = threadIdx.x; v0 < nvec; v0 += blockDim.x * kUnroll) {
+      float f[kUnroll][kN];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int vi = v0 + u * blockDim.x;
+        if (vi < nvec) arg_ld16(row + (size_t)vi * kN, f[u]);
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int vi = v0 + u * blockDim.x;
+        if (vi < nvec) {
+#pragma unroll
+          for (int j = 0; j < kN; ++j) {
+            const float v = f[u][j];
+            const int c = vi * kN + j;
+            if (v > best.v || (v == best.v && c < best.i)) best = ArgBest{v, c};  // NaN never wins
+          }
+        }
+      }
+    }
+  } else {
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+      const float v = ldf(row + c);
+      if (v > best.v || (v == best.v && c < best.i)) best = ArgBest{v, c};  // NaN never wins
+    }
   }
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) {
@@ -458,10 +499,12 @@ int axb200_argmax_last_dim(const void *x, int64_t *out, int64_t rows, int cols, 
   if (rows < 0 || cols <= 0 || rows > 0x7fffffff) return AXB200_INVALID_ARGUMENT;
   if (rows == 0) return AXB200_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t row_bytes = (size_t)cols * (dtype == AXB200_FLOAT32 ? 4 : 2);
+  const int vec = (reinterpret_cast<uintptr_t>(x) & 15u) == 0 && row_bytes % 16 == 0;
   if (dtype == AXB200_FLOAT32)
-    axb::argmax_kernel<float><<<(unsigned)rows, cols >= 8192 ? 1024 : 256, 0, st>>>(static_cast<const float *>(x), out, cols);
+    axb::argmax_kernel<float><<<(unsigned)rows, cols >= 8192 ? 1024 : 256, 0, st>>>(static_cast<const float *>(x), out, cols, vec);
   else
-    axb::argmax_kernel<__half><<<(unsigned)rows, cols >= 8192 ? 1024 : 256, 0, st>>>(static_cast<const __half *>(x), out, cols);
+    axb::argmax_kernel<__half><<<(unsigned)rows, cols >= 8192 ? 1024 : 256, 0, st>>>(static_cast<const __half *>(x), out, cols, vec);
   return axb::launch_status();
 }
 

@@ -468,6 +468,13 @@ def test_embedding_and_argmax(ops, orc):
     assert np.array_equal(ops.argmax_last_dim(dev(x)).cpu().numpy(), want)
     x16 = widen(x)
     assert np.array_equal(ops.argmax_last_dim(dev(x16, torch.float16)).cpu().numpy(), orc.argmax_last_dim(x16))
+    # rows that are not 16-byte multiples take the element-wise loop; ties at both ends of a row
+    y = rng.standard_normal((5, 1001)).astype(np.float32)
+    y[0, 0] = y[0, 1000] = 50.0
+    y[1, 999] = y[1, 1000] = 50.0
+    assert np.array_equal(ops.argmax_last_dim(dev(y)).cpu().numpy(), orc.argmax_last_dim(y))
+    y16 = widen(y)
+    assert np.array_equal(ops.argmax_last_dim(dev(y16, torch.float16)).cpu().numpy(), orc.argmax_last_dim(y16))
     assert ops.last_error() == 0
 
 
