@@ -326,6 +326,86 @@ __device__ __forceinline__ void emit_final(const DecodeParams &p, const GatherPa
   }
 }
 
+// The merge of one (sequence, head): chunk partials [c_first, n) -> the final row, by the `nthreads`
+// (a multiple of 32, at most 128) threads of a CTA.  The chunks are dealt to the warps and every lane owns
+// four output dims, so that a warp's loads - one 16-byte read of O and one 8-byte read of (m, l) per
+// chunk, up to four chunks in flight - are independent of one another: a sequence cut into dozens of
+// chunks (one long sequence on an otherwise empty GPU) merges in a couple of trips to L2 instead of one
+// trip per chunk.  The warps' running (M, sum, O) meet in `s_merge` (nwarps x 132 floats of shared
+// memory, 16-byte aligned), and thread t < 128 finishes dim t.  Head sizes that are not a multiple of 4 take the
+// element-wise loop.  Both the fused merge and the combine kernel come through here: identical bits.
+constexpr int kMergeSlab = 128, kMergeRow = kMergeSlab + 4;  // rows stay 16-byte aligned
+template <typename OutT, typename Bar>
+__device__ __forceinline__ void merge_head(const DecodeParams &p, const GatherParams &g, int b, int h,
+                                           int c_first, int n, float dom, int tid, int nthreads,
+                                           float *s_merge, Bar bar) {
+  const int d = p.d;
+  const size_t base = ((size_t)b * p.hq + h) * p.max_chunks;
+  if (d % 4 != 0) {
+    for (int t = tid; t < d; t += nthreads) {
+      float val, M, Ls;
+      merge_row(p, base, c_first, n, t, dom, val, M, Ls);
+      emit_final<OutT>(p, g, b, h, t, val, M, Ls);
+    }
+    return;
+  }
+  const int warp = tid >> 5, lane = tid & 31, nwarps = nthreads >> 5;
+  const float2 *ml_g = reinterpret_cast<const float2 *>(p.part_ml) + base;
+  for (int d0 = 0; d0 < d; d0 += kMergeSlab) {  // one pass per 128 dims (two for head_dim 256)
+    const int t4 = d0 + lane * 4;
+    const bool act = t4 < d;
+    float M = -INFINITY, Ls = 0.f;
+    float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int c = c_first + warp; c < n; c += nwarps * 4) {
+      float2 ml[4];
+      float4 o[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int cc = c + u * nwarps;
+        ml[u] = make_float2(-INFINITY, 0.f);
+        o[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (cc < n) {
+          ml[u] = __ldcg(ml_g + cc);
+          if (act) o[u] = __ldcg(reinterpret_cast<const float4 *>(p.part_o + (base + cc) * d + t4));
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (c + u * nwarps >= n) continue;
+        const float Mn = fmaxf(M, ml[u].x);
+        const float keep = M == -INFINITY ? 0.f : exp2f((M - Mn) * dom);
+        const float wgt = ml[u].x == -INFINITY ? 0.f : exp2f((ml[u].x - Mn) * dom);
+        val.x = fmaf(wgt, o[u].x, val.x * keep);
+        val.y = fmaf(wgt, o[u].y, val.y * keep);
+        val.z = fmaf(wgt, o[u].z, val.z * keep);
+        val.w = fmaf(wgt, o[u].w, val.w * keep);
+        Ls = fmaf(wgt, ml[u].y, Ls * keep);
+        M = Mn;
+      }
+    }
+    float *mine = s_merge + warp * kMergeRow;
+    if (act) *reinterpret_cast<float4 *>(mine + lane * 4) = val;
+    if (lane == 0) {
+      mine[kMergeSlab] = M;
+      mine[kMergeSlab + 1] = Ls;
+    }
+    bar();
+    if (tid < kMergeSlab && d0 + tid < d) {
+      float Mx = -INFINITY;
+      for (int w = 0; w < nwarps; ++w) Mx = fmaxf(Mx, s_merge[w * kMergeRow + kMergeSlab]);
+      float v = 0.f, L = 0.f;
+      for (int w = 0; w < nwarps; ++w) {
+        const float mw = s_merge[w * kMergeRow + kMergeSlab];
+        const float wgt = mw == -INFINITY ? 0.f : exp2f((mw - Mx) * dom);
+        v = fmaf(wgt, s_merge[w * kMergeRow + tid], v);
+        L = fmaf(wgt, s_merge[w * kMergeRow + kMergeSlab + 1], L);
+      }
+      emit_final<OutT>(p, g, b, h, d0 + tid, v, Mx, L);
+    }
+    bar();  // s_merge is free for the next slab or head
+  }
+}
+
 // Tail of a CTA that has stored a finished item into every peer's buffer.  Called by all `bar`
 // threads of the CTA (thread index tid): every thread fences its stores system-wide, the CTA counts
 // the item in, and the CTA that completes the launch's `total` items publishes this rank's new
@@ -374,7 +454,7 @@ template <typename OutT, typename Bar>
 __device__ __forceinline__ void finish_item(const DecodeParams &p, const GatherParams &g,
                                             const CtaWork &w, int hk, int c_first, bool direct,
                                             float dom, int tid, int nthreads,
-                                            volatile unsigned int *s_word, Bar bar) {
+                                            volatile unsigned int *s_word, float *s_merge, Bar bar) {
   if (!direct) {
     if (p.arrival_region < 0) return;  // the combine kernel merges
     __threadfence();
@@ -389,15 +469,8 @@ __device__ __forceinline__ void finish_item(const DecodeParams &p, const GatherP
     bar();
     if (!s_word[0]) return;
     __threadfence();
-    for (int r = 0; r < p.group; ++r) {
-      const int h = hk * p.group + r;
-      const size_t base = ((size_t)w.b * p.hq + h) * p.max_chunks;
-      for (int t = tid; t < p.d; t += nthreads) {
-        float val, M, Ls;
-        merge_row(p, base, c_first, w.n, t, dom, val, M, Ls);
-        emit_final<OutT>(p, g, w.b, h, t, val, M, Ls);
-      }
-    }
+    for (int r = 0; r < p.group; ++r)
+      merge_head<OutT>(p, g, w.b, hk * p.group + r, c_first, w.n, dom, tid, nthreads, s_merge, bar);
   }
   if (g.world) publish_and_wait(g, (unsigned int)(p.batch * p.hkv), p.wait_ns, tid, s_word, bar);
 }
@@ -761,7 +834,7 @@ gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
   }
   named_bar_sync(1, kConsumerThreads);
   finalize_chunk<__half, kD>(p, gp, mO, mM, mL, b, hk, chunk, threadIdx.x, 1.0f, direct);
-  finish_item<__half>(p, gp, w, hk, c_first, direct, 1.0f, threadIdx.x, kConsumerThreads, s_word,
+  finish_item<__half>(p, gp, w, hk, c_first, direct, 1.0f, threadIdx.x, kConsumerThreads, s_word, mO,
                       [] { named_bar_sync(1, kConsumerThreads); });
 }
 
@@ -934,7 +1007,7 @@ gqa_split_f32_kernel(const __grid_constant__ CUtensorMap tmK,
   }
   named_bar_sync(1, kConsumerThreads);
   finalize_chunk<float, kHeadDim>(p, gp, mO, mM, mL, b, hk, chunk, threadIdx.x, sl2, direct);
-  finish_item<float>(p, gp, w, hk, c_first, direct, sl2, threadIdx.x, kConsumerThreads, s_word,
+  finish_item<float>(p, gp, w, hk, c_first, direct, sl2, threadIdx.x, kConsumerThreads, s_word, mO,
                      [] { named_bar_sync(1, kConsumerThreads); });
 }
 
@@ -1039,7 +1112,7 @@ __device__ __forceinline__ void gen_pv(const float *Vs, const float *p_s, const 
 template <typename T, bool kPaged>
 __global__ void __launch_bounds__(kGenThreads, 3)
 gqa_split_generic_kernel(const T *k, const T *v, const DecodeParams p, const GatherParams gp, int d) {
-  extern __shared__ float gsm[];
+  extern __shared__ __align__(16) float gsm[];
   __shared__ int s_plan[kPlanWords];
   __shared__ unsigned int s_word[2];
   CtaWork w;
@@ -1231,7 +1304,7 @@ gqa_split_generic_kernel(const T *k, const T *v, const DecodeParams p, const Gat
       p.part_ml[slot * 2 + 1] = l_s[tid];
     }
   }
-  finish_item<T>(p, gp, w, hk, c_first, direct, dom, tid, kGenThreads, s_word, [] { __syncthreads(); });
+  finish_item<T>(p, gp, w, hk, c_first, direct, dom, tid, kGenThreads, s_word, Ks, [] { __syncthreads(); });
 }
 
 // ---- combine: log-sum-exp merge of a sequence's chunk partials --------------------------------
@@ -1245,15 +1318,15 @@ __global__ void __launch_bounds__(128)
 gqa_combine_kernel(const DecodeParams p, const GatherParams gp, float dom) {
   __shared__ int s_plan[kPlanWords];
   __shared__ unsigned int s_word[2];
+  __shared__ __align__(16) float s_merge[4 * kMergeRow];
   const int h = blockIdx.x, b = blockIdx.y;
   int L, ct, n;
   sequence_plan(p, b, s_plan, &L, &ct, &n);
-  const size_t base = ((size_t)b * p.hq + h) * p.max_chunks;
   const int c_first = first_visible(p, L) / ct;  // first chunk that holds visible tokens
-  for (int t = threadIdx.x; t < p.d; t += blockDim.x) {
-    float val = 0.f, M = -INFINITY, Ls = 0.f;
-    if (L > 0) merge_row(p, base, c_first, n, t, dom, val, M, Ls);
-    emit_final<OutT>(p, gp, b, h, t, val, M, Ls);
+  if (L > 0) {
+    merge_head<OutT>(p, gp, b, h, c_first, n, dom, threadIdx.x, blockDim.x, s_merge, [] { __syncthreads(); });
+  } else {
+    for (int t = threadIdx.x; t < p.d; t += blockDim.x) emit_final<OutT>(p, gp, b, h, t, 0.f, -INFINITY, 0.f);
   }
   if (gp.world)
     publish_and_wait(gp, gridDim.x * gridDim.y, p.wait_ns, threadIdx.x, s_word, [] { __syncthreads(); });
