@@ -585,8 +585,16 @@ def run_native(args):
     if check:
         extra["output_check"] = check
     full = args.workload == "c3_ragged" and not args.no_extra and args.dtype == "f16" and args.shard_of == 1
-    if full and world == 1:
-        # the target case, batch 64 x 32 K: the kernel alone, the step, and the step with host buffers
+    def for_the_record(name, fn):
+        """An entry of `extra`: measured after everything the line's own figures need; a failure in it is
+        reported in place and does not take the line with it."""
+        try:
+            extra[name] = fn()
+        except (Exception, SystemExit) as e:  # noqa: BLE001
+            extra[name] = {"error": f"{type(e).__name__}: {e}"[:400]}
+
+    def target_case():
+        # batch 64 x 32 K: the kernel alone, the step, and the step with host buffers
         lens32 = np.full(B, 32768, np.int64)
         run.set_lengths(lens32)
         for _ in range(3):
@@ -598,32 +606,34 @@ def run_native(args):
         run.set_lengths(lens32)
         s32, eb32, _, _ = run.host_steps(rdv, 20, 3)
         gbs = algo_bytes(lens32) / (k32 / 1e3) / 1e9
-        extra["b64_l32k"] = {"split_kernel_ms": k32, "kv_gbs": gbs, "frac_of_measured": gbs / peak,
-                             "frac_of_nominal_8TBs": gbs / NOMINAL_HBM_GBS,
-                             "step_ms": ms32 / 20, "step_kv_gbs": b32 / (ms32 / 1e3) / 1e9,
-                             "step_frac_of_nominal_8TBs": b32 / (ms32 / 1e3) / 1e9 / NOMINAL_HBM_GBS,
-                             "tokens_per_s": B * 20 / (ms32 / 1e3),
-                             "e2e_ms_per_step": s32 / 20 * 1e3, "e2e_kv_gbs": eb32 / s32 / 1e9}
+        return {"split_kernel_ms": k32, "kv_gbs": gbs, "frac_of_measured": gbs / peak,
+                "frac_of_nominal_8TBs": gbs / NOMINAL_HBM_GBS,
+                "step_ms": ms32 / 20, "step_kv_gbs": b32 / (ms32 / 1e3) / 1e9,
+                "step_frac_of_nominal_8TBs": b32 / (ms32 / 1e3) / 1e9 / NOMINAL_HBM_GBS,
+                "tokens_per_s": B * 20 / (ms32 / 1e3),
+                "e2e_ms_per_step": s32 / 20 * 1e3, "e2e_kv_gbs": eb32 / s32 / 1e9}
+
+    if full and world == 1:
+        for_the_record("b64_l32k", target_case)
     run.close()
     del run
-    if full and world > 1:
-        # weak scaling for the record: every GPU runs the same batch of 64 with the same lengths, so the
-        # figure can only fall below N times one GPU's if the hardware makes it
+
+    def weak_scaling():
+        # every GPU runs the same batch of 64 with the same lengths, so the figure can only fall below N times
+        # one GPU's if the hardware makes it
         wk = NativeStep(lx, device, all_lens, capacity, args.dtype, seed=0)
         for _ in range(args.warmup):
             wk.step()
         wms, wbytes = wk.timed_steps(rdv, args.steps)
-        extra["weak"] = {"value": rdv.sum(wbytes) / (wms / 1e3) / 1e9, "unit": UNIT, "ms_per_step": wms / args.steps,
-                         "batch_per_gpu": int(wk.B), "lengths": "identical on every rank"}
+        res = {"value": rdv.sum(wbytes) / (wms / 1e3) / 1e9, "unit": UNIT, "ms_per_step": wms / args.steps,
+               "batch_per_gpu": int(wk.B), "lengths": "identical on every rank"}
         wk.close()
-        del wk
+        return res
+
+    if full and world > 1:
+        for_the_record("weak", weak_scaling)
     if full and not args.no_tower:
-        # for the record, after everything the line's own figures need: a failure here (or a rank lost in
-        # it) is reported in place and does not take the attention figures with it
-        try:
-            extra["c5_tower"] = tower_figures(args, lx, rdv, device)
-        except (Exception, SystemExit) as e:  # noqa: BLE001
-            extra["c5_tower"] = {"error": f"{type(e).__name__}: {e}"[:400]}
+        for_the_record("c5_tower", lambda: tower_figures(args, lx, rdv, device))
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
