@@ -20,6 +20,7 @@ SIGNATURES = {
     "axb200_set_fused_merge": (_i, [_i]),
     "axb200_set_device_plan": (_i, [_i]),
     "axb200_set_chunk_tiles": (_i, [_i]),
+    "axb200_set_dependent_launch": (_i, [_i]),
     "axb200_gqa_chunk_plan": (_i, [_vp, _i, _i, _i, _i, _i64, _vp, _vp, _vp, _vp]),
     "axb200_profile_enable": (_i, [_i]),
     "axb200_profile_collect": (_i, [C.POINTER(C.c_double), C.POINTER(C.c_int)]),

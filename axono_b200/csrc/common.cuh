@@ -123,6 +123,15 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity
   return false;
 }
 
+// ---- programmatic dependent launch ------------------------------------------------------------
+// A kernel launched with the programmatic-stream-serialization attribute may be scheduled while the
+// kernel before it in the stream is still running; grid_dependency_wait() blocks until that kernel has
+// completed and its writes are visible, so everything above the call (barrier set-up, descriptor
+// prefetch) overlaps the predecessor's tail and the launch latency.  Without the attribute the call
+// returns at once.  grid_dependency_launch() in the predecessor lets the dependents be scheduled early.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- TMA (cp.async.bulk.tensor), 4-D tiled load, completion on an mbarrier -----------------
 // The innermost coordinate c0 times the element size must be a multiple of 16 bytes.
 __device__ __forceinline__ void tma_load_4d(void *smem_dst, const CUtensorMap *map, uint64_t *bar,

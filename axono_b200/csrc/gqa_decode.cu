@@ -633,11 +633,12 @@ gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
   // is known: with a host-planned chunk length the chunk's first token does not depend on it, and the
   // two trips to memory overlap instead of following one another.
   int spec_start = -1, spec_page = 0;
+  if (warp == kConsumerWarps && lane == 0) {
+    tma_prefetch_descriptor(&tmK);
+    tma_prefetch_descriptor(&tmV);
+  }
+  grid_dependency_wait();  // nothing above reads what the kernel before this one writes
   if (warp == kConsumerWarps) {
-    if (lane == 0) {
-      tma_prefetch_descriptor(&tmK);
-      tma_prefetch_descriptor(&tmV);
-    }
     if (kPaged && !p.balanced) {
       spec_start = blockIdx.x * p.chunk_tokens;
       const int slot = (spec_start + lane * kTileTokensF16) / p.page_tokens;
@@ -866,11 +867,12 @@ gqa_split_f32_kernel(const __grid_constant__ CUtensorMap tmK,
   // is known: with a host-planned chunk length the chunk's first token does not depend on it, and the
   // two trips to memory overlap instead of following one another.
   int spec_start = -1, spec_page = 0;
+  if (warp == kConsumerWarps && lane == 0) {
+    tma_prefetch_descriptor(&tmK);
+    tma_prefetch_descriptor(&tmV);
+  }
+  grid_dependency_wait();  // nothing above reads what the kernel before this one writes
   if (warp == kConsumerWarps) {
-    if (lane == 0) {
-      tma_prefetch_descriptor(&tmK);
-      tma_prefetch_descriptor(&tmV);
-    }
     if (kPaged && !p.balanced) {
       spec_start = blockIdx.x * p.chunk_tokens;
       const int slot = (spec_start + lane * kTileTokensF32) / p.page_tokens;
@@ -1115,6 +1117,7 @@ gqa_split_generic_kernel(const T *k, const T *v, const DecodeParams p, const Gat
   extern __shared__ __align__(16) float gsm[];
   __shared__ int s_plan[kPlanWords];
   __shared__ unsigned int s_word[2];
+  grid_dependency_wait();
   CtaWork w;
   const bool active = cta_work(p, s_plan, w);
   __syncthreads();
@@ -1429,6 +1432,7 @@ bool make_map(CUtensorMap *map, const void *base, int dtype, bool paged, int d, 
 std::mutex g_settings_mu;
 unsigned long long g_wait_limit_ns = kWaitNanos;
 bool g_fused_merge = true;
+bool g_dependent_launch = true;
 bool g_device_plan = false;  // measured slower than the host plan on every one-wave case tried (see make_plan)
 int g_forced_chunk_tiles = 0;  // > 0: overrides the planned chunk length (tuning and tests)
 
@@ -1500,6 +1504,24 @@ bool set_smem(const void *kernel, int bytes) {
 
 constexpr int kStagesDefault = 3;
 
+// Launches a split kernel; with `dependent` the launch carries the programmatic-stream-serialization
+// attribute, so its CTAs may be scheduled while the kernel before it in the stream (the append, in a
+// decode step) is finishing - they stop at grid_dependency_wait() until that kernel is complete.
+template <typename Kern, typename... Args>
+int launch_split(Kern kern, dim3 grid, int threads, int smem, cudaStream_t st, bool dependent, Args... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(threads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = dependent ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, args...) == cudaSuccess ? launch_status() : AXB200_DEVICE_ERROR;
+}
+
 // head_dim 64 has half the bytes per stage: twice the stages keep the same 96 KB per CTA in flight
 template <bool kPaged, int kD>
 int launch_f16_d(const CUtensorMap &mk, const CUtensorMap &mv, const DecodeParams &p,
@@ -1508,8 +1530,7 @@ int launch_f16_d(const CUtensorMap &mk, const CUtensorMap &mv, const DecodeParam
   auto kern = gqa_split_f16_kernel<kPaged, kStages, 2, kD>;
   constexpr int smem = SmemLayout<kStages, 256 * kD>::kDynamicBytes;
   if (!set_smem(reinterpret_cast<const void *>(kern), smem)) return AXB200_DEVICE_ERROR;
-  kern<<<grid, kThreads, smem, st>>>(mk, mv, p, g);
-  return launch_status();
+  return launch_split(kern, grid, kThreads, smem, st, g_dependent_launch, mk, mv, p, g);
 }
 
 template <bool kPaged>
@@ -1524,8 +1545,7 @@ int launch_f32_g(const CUtensorMap &mk, const CUtensorMap &mv, const DecodeParam
   auto kern = gqa_split_f32_kernel<kPaged, kStagesDefault, kGroup>;
   constexpr int smem = SmemLayout<kStagesDefault>::kDynamicBytes;
   if (!set_smem(reinterpret_cast<const void *>(kern), smem)) return AXB200_DEVICE_ERROR;
-  kern<<<grid, kThreads, smem, st>>>(mk, mv, p, g);
-  return launch_status();
+  return launch_split(kern, grid, kThreads, smem, st, g_dependent_launch, mk, mv, p, g);
 }
 
 template <bool kPaged>
@@ -1786,6 +1806,12 @@ int axb200_set_wait_limit_ns(uint64_t ns) {
   if (ns == 0) return AXB200_INVALID_ARGUMENT;
   std::lock_guard<std::mutex> lock(axb::g_settings_mu);
   axb::g_wait_limit_ns = ns;
+  return AXB200_OK;
+}
+
+int axb200_set_dependent_launch(int on) {
+  std::lock_guard<std::mutex> lock(axb::g_settings_mu);
+  axb::g_dependent_launch = on != 0;
   return AXB200_OK;
 }
 

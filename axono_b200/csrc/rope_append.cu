@@ -237,6 +237,7 @@ template <typename T>
 __global__ void __launch_bounds__(1024)
 kv_append_rope_kernel(const AppendParams p, const InvFreqTable table) {
   __shared__ float s_cos[kMaxHalf], s_sin[kMaxHalf];
+  grid_dependency_launch();  // the attention kernel that follows may be scheduled; it waits for this one's end
   const int b = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   const int half = p.d / 2;

@@ -341,16 +341,18 @@ class NativeStep:
             sampler.pause()
         return rdv.max(ms), my_bytes
 
-    def capture_step(self):
-        """The step as one CUDA graph (append + attention, sized for the cache's capacity so that replays
-        follow the growing cache).  Capturing runs the step once for real."""
+    def capture_step(self, replays):
+        """The step as one CUDA graph (append + attention; the attention's grid is sized for the lengths the
+        sequences can reach within `replays` replays, so the graph follows the growing cache that far).
+        Capturing runs the step once for real."""
         from axono_b200 import native
 
         def body():
             self.lx.kv_append_rope(self.arena, 0, self.q, self.k_new, self.v_new, theta=1e6)
-            self.lx.gqa_decode_attention_paged(self.q, self.arena, 0, self.capacity, out=self.out)
+            self.lx.gqa_decode_attention_paged(self.q, self.arena, 0, bound, out=self.out)
             return self.out
 
+        bound = min(self.capacity, int(self.bound) + int(replays) + 1)  # what the lengths can reach under this graph
         g = native.CUDAGraph().capture(body)
         self.cur += 1
         self.bound = min(self.capacity, self.bound + 1)
@@ -497,6 +499,10 @@ def run_native(args):
     lx = native.load()
     if not lx.cuda_available():
         raise SystemExit("bench.py needs a CUDA device: the decode path has no CPU fallback")
+    if args.no_dependent_launch:
+        from axono_b200 import _capi
+
+        _capi.lib().axb200_set_dependent_launch(0)
     rdv = Rendezvous.from_env(timeout=600.0)  # set-up of a rank (weights, tens of GB of cache) may take minutes
     world, rank = rdv.world, rdv.rank
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -532,7 +538,7 @@ def run_native(args):
     # The step is captured once as a CUDA graph and the K timed steps are K replays launched from native
     # code: at several GPUs a step lasts 0.1-0.2 ms and the whole timed region a few milliseconds, which a
     # single scheduling hiccup of the Python thread on any one rank would otherwise double (max over ranks).
-    graph = run.capture_step()
+    graph = run.capture_step(args.warmup + args.steps)
     if args.warmup > 1:
         graph.replay_timed(args.warmup - 1)
         run.cur += args.warmup - 1
@@ -1266,6 +1272,8 @@ def main():
     ap.add_argument("--no-extra", action="store_true")
     ap.add_argument("--no-check", action="store_true", help="skip the check of the timed output against the CPU checker")
     ap.add_argument("--no-fork", action="store_true", help="c2_block: all kernels on one stream (no parallel graph branches)")
+    ap.add_argument("--no-dependent-launch", action="store_true",
+                    help="launch the attention kernel in plain stream order (A/B of the programmatic dependent launch)")
     ap.add_argument("--no-tower", action="store_true", help="skip the text-tower figures in `extra`")
     args = ap.parse_args()
     rank0 = int(os.environ.get("RANK", "0")) == 0

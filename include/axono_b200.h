@@ -89,6 +89,13 @@ int axb200_set_fused_merge(int on);
  * (one split count per call, src/ops/cuda/gqa.cu:157-160).  Both are exact; they differ in speed. */
 int axb200_set_device_plan(int on);
 
+/* Whether the decode calls launch their attention kernel as a programmatic dependent of the kernel
+ * before it in the stream (default on): its CTAs may then be scheduled while that kernel - the append,
+ * in a decode step - is finishing, and stop at a grid-dependency wait until it is complete and its
+ * writes are visible; what they do before the wait touches no global memory.  Off: plain stream order.
+ * The result is the same either way.  No counterpart in the reference. */
+int axb200_set_dependent_launch(int on);
+
 /* Overrides the chunk length of the decode calls: `tiles` 64-token tiles per chunk (doubled until a
  * sequence of max_seq_len has at most 256 chunks); 0 gives the choice back to the library.  A tuning
  * and test knob: the result does not depend on it beyond rounding.  No counterpart in the reference. */
