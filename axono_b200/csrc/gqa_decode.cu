@@ -74,6 +74,7 @@ struct DecodeParams {
   // writes the result itself (no combine kernel); the arrival counters are that region of g_arrival.
   // direct_ok: a sequence with a single chunk is normalised and written by its CTA, no partial.
   int arrival_region, direct_ok;
+  int merge_pairs;  // the merging CTA takes a group's heads two at a time
   unsigned long long wait_ns;  // limit of every bounded wait in the launch
 };
 
@@ -333,77 +334,112 @@ __device__ __forceinline__ void emit_final(const DecodeParams &p, const GatherPa
 // chunks (one long sequence on an otherwise empty GPU) merges in a couple of trips to L2 instead of one
 // trip per chunk.  The warps' running (M, sum, O) meet in `s_merge` (nwarps x 132 floats of shared
 // memory, 16-byte aligned), and thread t < 128 finishes dim t.  Head sizes that are not a multiple of 4 take the
-// element-wise loop.  Both the fused merge and the combine kernel come through here: identical bits.
+// element-wise loop.  Both the fused merge and the combine kernel come through here, and a head's
+// arithmetic does not depend on which heads it is merged beside: identical bits.
 constexpr int kMergeSlab = 128, kMergeRow = kMergeSlab + 4;  // rows stay 16-byte aligned
-template <typename OutT, typename Bar>
-__device__ __forceinline__ void merge_head(const DecodeParams &p, const GatherParams &g, int b, int h,
-                                           int c_first, int n, float dom, int tid, int nthreads,
-                                           float *s_merge, Bar bar) {
+// kH heads (h, h + 1, ...) at once: their loads fly together and the two barriers are paid once.
+template <typename OutT, int kH, typename Bar>
+__device__ __forceinline__ void merge_heads(const DecodeParams &p, const GatherParams &g, int b, int h,
+                                            int c_first, int n, float dom, int tid, int nthreads,
+                                            float *s_merge, Bar bar) {
   const int d = p.d;
-  const size_t base = ((size_t)b * p.hq + h) * p.max_chunks;
   if (d % 4 != 0) {
-    for (int t = tid; t < d; t += nthreads) {
-      float val, M, Ls;
-      merge_row(p, base, c_first, n, t, dom, val, M, Ls);
-      emit_final<OutT>(p, g, b, h, t, val, M, Ls);
+#pragma unroll
+    for (int r = 0; r < kH; ++r) {
+      const size_t base = ((size_t)b * p.hq + h + r) * p.max_chunks;
+      for (int t = tid; t < d; t += nthreads) {
+        float val, M, Ls;
+        merge_row(p, base, c_first, n, t, dom, val, M, Ls);
+        emit_final<OutT>(p, g, b, h + r, t, val, M, Ls);
+      }
     }
     return;
   }
   const int warp = tid >> 5, lane = tid & 31, nwarps = nthreads >> 5;
-  const float2 *ml_g = reinterpret_cast<const float2 *>(p.part_ml) + base;
   for (int d0 = 0; d0 < d; d0 += kMergeSlab) {  // one pass per 128 dims (two for head_dim 256)
     const int t4 = d0 + lane * 4;
     const bool act = t4 < d;
-    float M = -INFINITY, Ls = 0.f;
-    float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int c = c_first + warp; c < n; c += nwarps * 4) {
-      float2 ml[4];
-      float4 o[4];
+    float M[kH], Ls[kH];
+    float4 val[kH];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int cc = c + u * nwarps;
-        ml[u] = make_float2(-INFINITY, 0.f);
-        o[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (cc < n) {
-          ml[u] = __ldcg(ml_g + cc);
-          if (act) o[u] = __ldcg(reinterpret_cast<const float4 *>(p.part_o + (base + cc) * d + t4));
+    for (int r = 0; r < kH; ++r) {
+      M[r] = -INFINITY;
+      Ls[r] = 0.f;
+      val[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    for (int c = c_first + warp; c < n; c += nwarps * 4) {
+      float2 ml[kH][4];
+      float4 o[kH][4];
+#pragma unroll
+      for (int r = 0; r < kH; ++r) {
+        const size_t base = ((size_t)b * p.hq + h + r) * p.max_chunks;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int cc = c + u * nwarps;
+          ml[r][u] = make_float2(-INFINITY, 0.f);
+          o[r][u] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (cc < n) {
+            ml[r][u] = __ldcg(reinterpret_cast<const float2 *>(p.part_ml) + base + cc);
+            if (act) o[r][u] = __ldcg(reinterpret_cast<const float4 *>(p.part_o + (base + cc) * d + t4));
+          }
         }
       }
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        if (c + u * nwarps >= n) continue;
-        const float Mn = fmaxf(M, ml[u].x);
-        const float keep = M == -INFINITY ? 0.f : exp2f((M - Mn) * dom);
-        const float wgt = ml[u].x == -INFINITY ? 0.f : exp2f((ml[u].x - Mn) * dom);
-        val.x = fmaf(wgt, o[u].x, val.x * keep);
-        val.y = fmaf(wgt, o[u].y, val.y * keep);
-        val.z = fmaf(wgt, o[u].z, val.z * keep);
-        val.w = fmaf(wgt, o[u].w, val.w * keep);
-        Ls = fmaf(wgt, ml[u].y, Ls * keep);
-        M = Mn;
+      for (int r = 0; r < kH; ++r) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (c + u * nwarps >= n) continue;
+          const float Mn = fmaxf(M[r], ml[r][u].x);
+          const float keep = M[r] == -INFINITY ? 0.f : exp2f((M[r] - Mn) * dom);
+          const float wgt = ml[r][u].x == -INFINITY ? 0.f : exp2f((ml[r][u].x - Mn) * dom);
+          val[r].x = fmaf(wgt, o[r][u].x, val[r].x * keep);
+          val[r].y = fmaf(wgt, o[r][u].y, val[r].y * keep);
+          val[r].z = fmaf(wgt, o[r][u].z, val[r].z * keep);
+          val[r].w = fmaf(wgt, o[r][u].w, val[r].w * keep);
+          Ls[r] = fmaf(wgt, ml[r][u].y, Ls[r] * keep);
+          M[r] = Mn;
+        }
       }
     }
-    float *mine = s_merge + warp * kMergeRow;
-    if (act) *reinterpret_cast<float4 *>(mine + lane * 4) = val;
-    if (lane == 0) {
-      mine[kMergeSlab] = M;
-      mine[kMergeSlab + 1] = Ls;
+#pragma unroll
+    for (int r = 0; r < kH; ++r) {
+      float *mine = s_merge + (r * nwarps + warp) * kMergeRow;
+      if (act) *reinterpret_cast<float4 *>(mine + lane * 4) = val[r];
+      if (lane == 0) {
+        mine[kMergeSlab] = M[r];
+        mine[kMergeSlab + 1] = Ls[r];
+      }
     }
     bar();
     if (tid < kMergeSlab && d0 + tid < d) {
-      float Mx = -INFINITY;
-      for (int w = 0; w < nwarps; ++w) Mx = fmaxf(Mx, s_merge[w * kMergeRow + kMergeSlab]);
-      float v = 0.f, L = 0.f;
-      for (int w = 0; w < nwarps; ++w) {
-        const float mw = s_merge[w * kMergeRow + kMergeSlab];
-        const float wgt = mw == -INFINITY ? 0.f : exp2f((mw - Mx) * dom);
-        v = fmaf(wgt, s_merge[w * kMergeRow + tid], v);
-        L = fmaf(wgt, s_merge[w * kMergeRow + kMergeSlab + 1], L);
+#pragma unroll
+      for (int r = 0; r < kH; ++r) {
+        const float *rows = s_merge + r * nwarps * kMergeRow;
+        float Mx = -INFINITY;
+        for (int w = 0; w < nwarps; ++w) Mx = fmaxf(Mx, rows[w * kMergeRow + kMergeSlab]);
+        float v = 0.f, L = 0.f;
+        for (int w = 0; w < nwarps; ++w) {
+          const float mw = rows[w * kMergeRow + kMergeSlab];
+          const float wgt = mw == -INFINITY ? 0.f : exp2f((mw - Mx) * dom);
+          v = fmaf(wgt, rows[w * kMergeRow + tid], v);
+          L = fmaf(wgt, rows[w * kMergeRow + kMergeSlab + 1], L);
+        }
+        emit_final<OutT>(p, g, b, h + r, d0 + tid, v, Mx, L);
       }
-      emit_final<OutT>(p, g, b, h, d0 + tid, v, Mx, L);
     }
-    bar();  // s_merge is free for the next slab or head
+    bar();  // s_merge is free for the next slab or heads
   }
+}
+
+// All `count` heads starting at h: in pairs, then a last single one.  s_merge: 2 x nwarps x 132 floats.
+template <typename OutT, typename Bar>
+__device__ __forceinline__ void merge_head_range(const DecodeParams &p, const GatherParams &g, int b, int h,
+                                                 int count, int c_first, int n, float dom, int tid,
+                                                 int nthreads, float *s_merge, Bar bar) {
+  int r = 0;
+  if (p.merge_pairs)
+    for (; r + 2 <= count; r += 2) merge_heads<OutT, 2>(p, g, b, h + r, c_first, n, dom, tid, nthreads, s_merge, bar);
+  for (; r < count; ++r) merge_heads<OutT, 1>(p, g, b, h + r, c_first, n, dom, tid, nthreads, s_merge, bar);
 }
 
 // Tail of a CTA that has stored a finished item into every peer's buffer.  Called by all `bar`
@@ -469,8 +505,7 @@ __device__ __forceinline__ void finish_item(const DecodeParams &p, const GatherP
     bar();
     if (!s_word[0]) return;
     __threadfence();
-    for (int r = 0; r < p.group; ++r)
-      merge_head<OutT>(p, g, w.b, hk * p.group + r, c_first, w.n, dom, tid, nthreads, s_merge, bar);
+    merge_head_range<OutT>(p, g, w.b, hk * p.group, p.group, c_first, w.n, dom, tid, nthreads, s_merge, bar);
   }
   if (g.world) publish_and_wait(g, (unsigned int)(p.batch * p.hkv), p.wait_ns, tid, s_word, bar);
 }
@@ -1321,13 +1356,13 @@ __global__ void __launch_bounds__(128)
 gqa_combine_kernel(const DecodeParams p, const GatherParams gp, float dom) {
   __shared__ int s_plan[kPlanWords];
   __shared__ unsigned int s_word[2];
-  __shared__ __align__(16) float s_merge[4 * kMergeRow];
+  __shared__ __align__(16) float s_merge[2 * 4 * kMergeRow];
   const int h = blockIdx.x, b = blockIdx.y;
   int L, ct, n;
   sequence_plan(p, b, s_plan, &L, &ct, &n);
   const int c_first = first_visible(p, L) / ct;  // first chunk that holds visible tokens
   if (L > 0) {
-    merge_head<OutT>(p, gp, b, h, c_first, n, dom, threadIdx.x, blockDim.x, s_merge, [] { __syncthreads(); });
+    merge_head_range<OutT>(p, gp, b, h, 1, c_first, n, dom, threadIdx.x, blockDim.x, s_merge, [] { __syncthreads(); });
   } else {
     for (int t = threadIdx.x; t < p.d; t += blockDim.x) emit_final<OutT>(p, gp, b, h, t, 0.f, -INFINITY, 0.f);
   }
@@ -1432,6 +1467,7 @@ bool make_map(CUtensorMap *map, const void *base, int dtype, bool paged, int d, 
 std::mutex g_settings_mu;
 unsigned long long g_wait_limit_ns = kWaitNanos;
 bool g_fused_merge = true;
+bool g_merge_pairs = true;
 bool g_dependent_launch = true;
 bool g_device_plan = false;  // measured slower than the host plan on every one-wave case tried (see make_plan)
 int g_forced_chunk_tiles = 0;  // > 0: overrides the planned chunk length (tuning and tests)
@@ -1663,6 +1699,7 @@ int decode_impl(bool paged, const void *q, void *out, const void *k, const void 
   p.arrival_region = need_ws ? arrival_region_for(workspace, (int64_t)batch * hkv) : -1;
   const bool combine_kernel = need_ws && p.arrival_region < 0;
   p.direct_ok = !combine_kernel;
+  p.merge_pairs = g_merge_pairs;
   GatherParams g{};
   if (gather) g = *gather;
   const dim3 grid = pl.balanced ? dim3(pl.budget, hkv, 1) : dim3(pl.max_chunks, hkv, batch);
@@ -1831,6 +1868,7 @@ int axb200_set_device_plan(int on) {
 int axb200_set_fused_merge(int on) {
   std::lock_guard<std::mutex> lock(axb::g_settings_mu);
   axb::g_fused_merge = on != 0;
+  axb::g_merge_pairs = on != 2;
   return AXB200_OK;
 }
 

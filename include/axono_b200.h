@@ -78,7 +78,9 @@ int axb200_set_wait_limit_ns(uint64_t ns);
  * are library-owned device memory (64 regions of 4096 counters, one region per workspace pointer in
  * use, always left zero).  off, or when a call has more than 4096 (sequence, KV head) items or no
  * region is free: a separate combine kernel, as the reference's GqaDecodeMergeKernel
- * (src/ops/cuda/gqa.cu:95-129).  Both forms run the same arithmetic and give identical bits. */
+ * (src/ops/cuda/gqa.cu:95-129).  Both forms run the same arithmetic and give identical bits.
+ * on == 2: as 1, but the merging CTA takes the query heads of its KV head one at a time instead of
+ * two at a time (a tuning switch; same bits again). */
 int axb200_set_fused_merge(int on);
 
 /* How a decode call that fits one wave of CTAs is cut into chunks.  on: on the device, from
