@@ -54,6 +54,12 @@ SIGNATURES = {
     "axb200_qkv_norm_rope_append": (_i, [_vp, _i64, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i, _i,
                                          _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "axb200_silu_mul_rows": (_i, [_vp, _i64, _i, _i64, _vp, _i, _vp]),
+    "axb200_decode_step_workspace_bytes": (_sz, [_i, _i, _i, _i, _i64, _i]),
+    "axb200_decode_step_launches": (_i, [_i, _i, _i, _i, _i64, _i]),
+    "axb200_set_step_fused": (_i, [_i]),
+    # q, k_new, v_new, out, k_pages, v_pages, block_table, seq_lens, pos, inv_freq | theta | rotate, mrope, h_sec,
+    # w_sec, batch, hq, hkv, d, page_tokens, max_blocks, num_pages | max_seq_len | dtype | workspace, bytes, stream
+    "axb200_decode_step_paged": (_i, [_vp] * 10 + [_f] + [_i] * 11 + [_i64, _i, _vp, _sz, _vp]),
     "axb200_decode_step_host": (_i, [_vp] * 12 + [_vp, _vp, _f, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i64, _i,
                                           _vp, _sz, _vp]),
     "axb200_kv_arena_create": (_i, [_i, _i, _i, _i, _i, _i, _i, _i, _i, C.POINTER(_vp)]),

@@ -41,6 +41,16 @@ int kv_append_rope_from(void *q, const void *q_src, const void *k_new, const voi
                         int batch, int hq, int hkv, int d, int page_tokens, int max_blocks, int num_pages,
                         int dtype, int slot_delta, int advance, void *stream);
 
+// The decode step as one launch when that form applies, else kStepNotFused with nothing launched;
+// defined in gqa_decode.cu.
+constexpr int kStepNotFused = -1000;
+int decode_step_try_fused(const void *q, const void *k_new, const void *v_new, void *out, void *k_pages,
+                          void *v_pages, const int32_t *block_table, int32_t *seq_lens, const int64_t *pos,
+                          const float *inv_freq, float theta, int rotate, int mrope, int h_sec, int w_sec,
+                          int batch, int hq, int hkv, int d, int page_tokens, int max_blocks, int num_pages,
+                          int64_t max_seq_len, int dtype, void *workspace, size_t workspace_bytes,
+                          void *stream);
+
 inline size_t dtype_size(int dtype) {
   switch (dtype) {
     case AXB200_FLOAT16: return 2;
@@ -131,6 +141,25 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity
 // returns at once.  grid_dependency_launch() in the predecessor lets the dependents be scheduled early.
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_dependency_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// ---- rotary position embedding: the arithmetic every kernel that rotates shares ------------------
+// Pair (a, b) = (x[i], x[i + half]) turned by the angle whose cosine and sine are (c, s).  The
+// roundings are spelled out (one product rounded, then one fused multiply-add) so that the append
+// kernel, the prefill write, the standalone rope kernels and the decode step that rotates inside the
+// attention kernel produce the same bits whatever the compiler would contract on its own.
+__device__ __forceinline__ float rope_lo(float a, float b, float c, float s) { return __fmaf_rn(a, c, -__fmul_rn(b, s)); }
+__device__ __forceinline__ float rope_hi(float a, float b, float c, float s) { return __fmaf_rn(b, c, __fmul_rn(a, s)); }
+
+// Position of rotary pair i under M-RoPE: the stride-3 rule (src/ops/cpu/sequence.cpp:222-227).
+__device__ __forceinline__ float mrope_pair_position(int i, float pt, float ph, float pw, int h_lim, int w_lim) {
+  if (i % 3 == 1 && i < h_lim) return ph;
+  if (i % 3 == 2 && i < w_lim) return pw;
+  return pt;
+}
+
+// theta^(-2i/dim) for i < dim/2 with the host C library's powf (src/ops/cpu/sequence.cpp:83-84);
+// defined in rope_append.cu.
+void rope_inv_freq_host(float theta, int dim, float *out);
 
 // ---- TMA (cp.async.bulk.tensor), 4-D tiled load, completion on an mbarrier -----------------
 // The innermost coordinate c0 times the element size must be a multiple of 16 bytes.

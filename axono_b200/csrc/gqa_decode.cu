@@ -78,6 +78,20 @@ struct DecodeParams {
   unsigned long long wait_ns;  // limit of every bounded wait in the launch
 };
 
+// The decode step in one launch (axb200_decode_step_paged): what the attention kernel needs to do the
+// append itself - rotate q in registers, rotate the new key and put it and the new value into the
+// cache and into the staged tile that holds their token, and leave seq_lens[b] + 1 behind.
+constexpr int kStepHalfMax = 64;  // head_dim <= 128
+struct StepParams {
+  const void *k_new, *v_new;  // (batch, hkv, d)
+  void *k_pages, *v_pages;
+  int32_t *seq_lens;          // read once per CTA, bumped by the last CTA of a sequence to have read it
+  const int64_t *pos;         // (batch), (3, batch) under M-RoPE, or null: position = tokens cached before
+  const float *inv_freq_dev;  // (d / 2), or null: `table`
+  int rotate, mrope, h_lim, w_lim;
+  float table[kStepHalfMax];  // theta^(-2i/d), from the host's powf
+};
+
 // Peers of a launch whose result goes to other GPUs' memory (KV heads sharded, or one sequence's
 // tokens spread over the GPUs).  world == 0: single GPU, the result goes to p.out.
 constexpr int kMaxPeers = 8;
@@ -95,11 +109,14 @@ struct GatherParams {
 // different regions (the host assigns a region per workspace pointer).
 constexpr int kArrivalRegions = 64, kArrivalSlots = 4096;
 static __device__ unsigned int g_arrival[kArrivalRegions * kArrivalSlots];
+// Readers of seq_lens[b] in a one-launch decode step, same regions: every CTA of sequence b counts
+// itself in after it has read the length; the one that completes the count stores the new length.
+static __device__ unsigned int g_step_readers[kArrivalRegions * kArrivalSlots];
 
 __global__ void zero_arrival_kernel() {
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < kArrivalRegions * kArrivalSlots;
        i += gridDim.x * blockDim.x)
-    g_arrival[i] = 0u;
+    g_arrival[i] = g_step_readers[i] = 0u;
 }
 
 __device__ __forceinline__ int seq_len_raw(const DecodeParams &p, int b) {
@@ -650,13 +667,21 @@ __device__ __forceinline__ uint32_t swz_off(int row, int c16) {
 // [64 tokens][64 halves], 128-byte swizzled.  Columns at and past p.d lie outside the tensor map, so the
 // copy engine fills them with zeros (and reads nothing for them); q is padded with zeros in registers;
 // zero columns add nothing to a dot product, and the output columns past p.d are never stored.
-template <bool kPaged, int kStages, int kMinCtas, int kD>
+//
+// kStep (paged, p.d == kD, host-planned chunks, no window): the launch is a whole decode step.  Thread 0
+// reads the old length, every thread works with old + 1, and the CTA counts itself in as a reader of the
+// length; the new token's K and V rows never come through the copy engine - the consumer warp that owns
+// the token's row of the last tile rotates k_new, stores both rows to the sequence's page for the steps
+// to come, and writes them over the staged tile once it has landed (whatever the page held there is
+// replaced before any thread reads it).  q is rotated in registers; the caller's q is left as it is.
+template <bool kPaged, int kStages, int kMinCtas, int kD, bool kStep = false>
 __global__ void __launch_bounds__(kThreads, kMinCtas)
 gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, const DecodeParams p,
-                     const GatherParams gp) {
+                     const GatherParams gp, const __grid_constant__ StepParams sp) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ int s_plan[kPlanWords];
+  __shared__ float s_rope[kStep ? 2 * kStepHalfMax : 1];  // cos [0, 64), sin [64, 128) of the step's position
   constexpr int kStage = 256 * kD, kKSteps = kD / 16, kNTiles = kD / 8;
   uint8_t *smem = align_1024(smem_raw);
   uint64_t *full = reinterpret_cast<uint64_t *>(smem + SmemLayout<kStages, kStage>::kBarOffset);
@@ -690,11 +715,55 @@ gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
     }
   }
   CtaWork w;
-  const bool active = cta_work(p, s_plan, w);
-  __syncthreads();
-  if (!active) return;
+  bool active;
+  int appended = 0;  // kStep: 1 when this launch adds a token to the sequence
+  if (kStep) {
+    if (threadIdx.x == 0) {  // one read of the length per CTA: every thread works with the same value
+      int len = sp.seq_lens[blockIdx.z];
+      const int cover = covered_tokens(p);
+      len = len < 0 ? 0 : len;
+      int add = 1;
+      if (len + 1 > cover) {  // no room for the token: nothing is appended, the old tokens are attended
+        atomicOr(&g_error_word, AXB200_ERR_CAPACITY);
+        len = min(len, cover);
+        add = 0;
+      }
+      s_plan[0] = len + add;
+      s_plan[1] = add;
+    }
+    __syncthreads();
+    w.b = blockIdx.z;
+    w.chunk = blockIdx.x;
+    w.L = s_plan[0];
+    appended = s_plan[1];
+    w.ct = p.chunk_tokens;
+    w.n = max(1, ceil_div(w.L, w.ct));
+    active = w.chunk < w.n;
+  } else {
+    active = cta_work(p, s_plan, w);
+    __syncthreads();
+  }
+  // kStep: thread 0 counts the CTA in as a reader of the length (release: after its read); the answer
+  // is looked at later, when it has long arrived - by `settle`, before the thread's every way out.
+  unsigned int readers_before = 0;
+  unsigned int *readers = nullptr;
+  if (kStep && threadIdx.x == 0) {
+    readers = g_step_readers + (size_t)p.arrival_region * kArrivalSlots + blockIdx.z;
+    readers_before = atom_add_acq_rel_gpu(readers, 1u);
+  }
+  auto settle = [&]() {
+    if (kStep && threadIdx.x == 0 && readers_before + 1 == gridDim.x * gridDim.y) {
+      *readers = 0u;  // every CTA of the sequence has read the old length
+      if (appended) sp.seq_lens[blockIdx.z] = w.L;
+    }
+  };
+  if (!active) {
+    settle();
+    return;
+  }
   const int chunk = w.chunk, hk = blockIdx.y, b = w.b, L = w.L;
   if (L == 0) {
+    settle();
     emit_empty_item<__half>(p, gp, b, hk, s_word);
     return;
   }
@@ -702,7 +771,10 @@ gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
   const int c_first = first / w.ct;  // chunks before it lie wholly outside the window
   int start = chunk * w.ct;
   const int end = min(L, start + w.ct);
-  if (end <= first) return;  // the whole chunk lies before the window
+  if (end <= first) {  // the whole chunk lies before the window
+    settle();
+    return;
+  }
   if (start < first) start = first / kTileTokensF16 * kTileTokensF16;  // skip whole tiles before it
   const int ntiles = (end - start + kTileTokensF16 - 1) / kTileTokensF16;
   const bool direct = p.direct_ok && w.n - c_first == 1;
@@ -735,6 +807,83 @@ gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
     }
   }
 
+  // ---- kStep: rotate q, prepare the new token's rows ----
+  constexpr int kHalf = kD / 2, kPairs = kHalf / 32;  // rotary pairs per lane of the warp that appends
+  const int new_row = L - 1 - (start + (ntiles - 1) * kTileTokensF16);  // the token's row in the last tile
+  const bool patch = kStep && appended && chunk == w.n - 1 && warp == (new_row >> 4);
+  __half k_lo[kPairs], k_hi[kPairs], v_lo[kPairs], v_hi[kPairs];
+  if constexpr (kStep) {
+    const __half *kn = reinterpret_cast<const __half *>(sp.k_new) + ((size_t)b * p.hkv + hk) * kD;
+    const __half *vn = reinterpret_cast<const __half *>(sp.v_new) + ((size_t)b * p.hkv + hk) * kD;
+    int page = 0;
+    if (patch) {  // the rows and the page id on their way while the angles are worked out
+#pragma unroll
+      for (int j = 0; j < kPairs; ++j) {
+        const int i = lane + 32 * j;
+        k_lo[j] = kn[i], k_hi[j] = kn[i + kHalf], v_lo[j] = vn[i], v_hi[j] = vn[i + kHalf];
+      }
+      page = p.block_table[(size_t)b * p.max_blocks + (L - 1) / p.page_tokens];
+    }
+    if (sp.rotate) {
+      if (threadIdx.x < kHalf) {  // one angle per rotary pair, once per CTA
+        const int i = threadIdx.x;
+        float pt, ph, pw;
+        if (sp.pos == nullptr) {
+          pt = ph = pw = (float)(L - appended);  // tokens cached before this one
+        } else if (sp.mrope) {
+          pt = (float)sp.pos[b];
+          ph = (float)sp.pos[p.batch + b];
+          pw = (float)sp.pos[2 * p.batch + b];
+        } else {
+          pt = ph = pw = (float)sp.pos[b];
+        }
+        const float f = sp.mrope || sp.inv_freq_dev ? sp.inv_freq_dev[i] : sp.table[i];
+        const float posv = sp.mrope ? mrope_pair_position(i, pt, ph, pw, sp.h_lim, sp.w_lim) : pt;
+        sincosf(posv * f, &s_rope[kStepHalfMax + i], &s_rope[i]);
+      }
+      named_bar_sync(1, kConsumerThreads);
+      // q: pair (c, c + kHalf) sits in k-steps ks and ks + kKSteps / 2 of the same thread
+#pragma unroll
+      for (int ks = 0; ks < kKSteps / 2; ++ks) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int c = ks * 16 + tq * 2 + (j >> 1) * 8;
+          const float2 lo = __half22float2(*reinterpret_cast<const __half2 *>(&qa[ks][j]));
+          const float2 hi = __half22float2(*reinterpret_cast<const __half2 *>(&qa[ks + kKSteps / 2][j]));
+          const float c0 = s_rope[c], s0 = s_rope[kStepHalfMax + c], c1 = s_rope[c + 1], s1 = s_rope[kStepHalfMax + c + 1];
+          const __half2 rl = __halves2half2(__float2half_rn(rope_lo(lo.x, hi.x, c0, s0)), __float2half_rn(rope_lo(lo.y, hi.y, c1, s1)));
+          const __half2 rh = __halves2half2(__float2half_rn(rope_hi(lo.x, hi.x, c0, s0)), __float2half_rn(rope_hi(lo.y, hi.y, c1, s1)));
+          qa[ks][j] = *reinterpret_cast<const uint32_t *>(&rl);
+          qa[ks + kKSteps / 2][j] = *reinterpret_cast<const uint32_t *>(&rh);
+        }
+      }
+    }
+    if (patch) {
+      if (sp.rotate) {
+#pragma unroll
+        for (int j = 0; j < kPairs; ++j) {
+          const int i = lane + 32 * j;
+          const float a = __half2float(k_lo[j]), bb = __half2float(k_hi[j]);
+          const float c = s_rope[i], sn = s_rope[kStepHalfMax + i];
+          k_lo[j] = __float2half_rn(rope_lo(a, bb, c, sn));
+          k_hi[j] = __float2half_rn(rope_hi(a, bb, c, sn));
+        }
+      }
+      if (page >= 0 && page < p.num_pages) {  // the rows in the cache, for the steps to come
+        const size_t row = (((size_t)page * p.hkv + hk) * p.page_tokens + (L - 1) % p.page_tokens) * kD;
+        __half *kd = reinterpret_cast<__half *>(sp.k_pages) + row, *vd = reinterpret_cast<__half *>(sp.v_pages) + row;
+#pragma unroll
+        for (int j = 0; j < kPairs; ++j) {
+          const int i = lane + 32 * j;
+          kd[i] = k_lo[j], kd[i + kHalf] = k_hi[j], vd[i] = v_lo[j], vd[i + kHalf] = v_hi[j];
+        }
+      } else if (lane == 0) {
+        atomicOr(&g_error_word, AXB200_ERR_BAD_PAGE);
+      }
+    }
+    settle();  // the count went out before the rows were asked for: its answer is here by now
+  }
+
   float o[kNTiles][4];
 #pragma unroll
   for (int nt = 0; nt < kNTiles; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
@@ -757,6 +906,19 @@ gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
     if (!ok) break;
     const uint32_t kbase = smem_u32(smem + (size_t)s * kStage);
     const uint32_t vbase = kbase + kStage / 2;
+    if constexpr (kStep) if (patch && i == ntiles - 1) {  // the new token's rows over whatever the page held
+      uint8_t *kt = smem + (size_t)s * kStage, *vt = kt + kStage / 2;
+#pragma unroll
+      for (int j = 0; j < kPairs; ++j) {
+        const int e0 = lane + 32 * j, e1 = e0 + kHalf;
+        const uint32_t o0 = swz_off(new_row, e0 >> 3) + (e0 & 7) * 2, o1 = swz_off(new_row, e1 >> 3) + (e1 & 7) * 2;
+        *reinterpret_cast<__half *>(kt + o0) = k_lo[j];
+        *reinterpret_cast<__half *>(kt + o1) = k_hi[j];
+        *reinterpret_cast<__half *>(vt + o0) = v_lo[j];
+        *reinterpret_cast<__half *>(vt + o1) = v_hi[j];
+      }
+      __syncwarp();
+    }
 
     // S(16 heads x 16 tokens) = Q . K^T
     float sc[2][4];
@@ -1477,6 +1639,7 @@ std::mutex g_settings_mu;
 unsigned long long g_wait_limit_ns = kWaitNanos;
 bool g_fused_merge = true;
 bool g_merge_pairs = true;
+bool g_step_fused = true;  // axb200_decode_step_paged may use the one-launch form
 bool g_dependent_launch = true;
 bool g_device_plan = false;  // measured slower than the host plan on every one-wave case tried (see make_plan)
 int g_forced_chunk_tiles = 0;  // > 0: overrides the planned chunk length (tuning and tests)
@@ -1568,20 +1731,26 @@ int launch_split(Kern kern, dim3 grid, int threads, int smem, cudaStream_t st, b
 }
 
 // head_dim 64 has half the bytes per stage: twice the stages keep the same 96 KB per CTA in flight
-template <bool kPaged, int kD>
+template <bool kPaged, int kD, bool kStep>
 int launch_f16_d(const CUtensorMap &mk, const CUtensorMap &mv, const DecodeParams &p,
-                 const GatherParams &g, dim3 grid, cudaStream_t st) {
+                 const GatherParams &g, dim3 grid, cudaStream_t st, const StepParams &sp) {
   constexpr int kStages = kStagesDefault * 128 / kD;
-  auto kern = gqa_split_f16_kernel<kPaged, kStages, 2, kD>;
+  auto kern = gqa_split_f16_kernel<kPaged, kStages, 2, kD, kStep>;
   constexpr int smem = SmemLayout<kStages, 256 * kD>::kDynamicBytes;
   if (!set_smem(reinterpret_cast<const void *>(kern), smem)) return AXB200_DEVICE_ERROR;
-  return launch_split(kern, grid, kThreads, smem, st, g_dependent_launch, mk, mv, p, g);
+  return launch_split(kern, grid, kThreads, smem, st, g_dependent_launch, mk, mv, p, g, sp);
 }
 
+// step: the launch appends the step's token itself (paged, head_dim 64 or 128 exactly)
 template <bool kPaged>
 int launch_f16(const CUtensorMap &mk, const CUtensorMap &mv, const DecodeParams &p,
-               const GatherParams &g, dim3 grid, cudaStream_t st) {
-  return p.d <= 64 ? launch_f16_d<kPaged, 64>(mk, mv, p, g, grid, st) : launch_f16_d<kPaged, 128>(mk, mv, p, g, grid, st);
+               const GatherParams &g, dim3 grid, cudaStream_t st, const StepParams *step) {
+  if (kPaged && step)
+    return p.d == 64 ? launch_f16_d<true, 64, true>(mk, mv, p, g, grid, st, *step)
+                     : launch_f16_d<true, 128, true>(mk, mv, p, g, grid, st, *step);
+  static const StepParams none{};
+  return p.d <= 64 ? launch_f16_d<kPaged, 64, false>(mk, mv, p, g, grid, st, none)
+                   : launch_f16_d<kPaged, 128, false>(mk, mv, p, g, grid, st, none);
 }
 
 template <bool kPaged, int kGroup>
@@ -1654,7 +1823,7 @@ int decode_impl(bool paged, const void *q, void *out, const void *k, const void 
                 int hq, int hkv, int d, int page_tokens, int max_blocks, int num_pages,
                 int64_t max_len, int dtype, void *workspace, size_t workspace_bytes,
                 cudaStream_t st, const GatherParams *gather = nullptr, int window = 0,
-                int causal_rows = 0, int row_offset = 0) {
+                int causal_rows = 0, int row_offset = 0, const StepParams *step = nullptr) {
   if (dtype != AXB200_FLOAT16 && dtype != AXB200_FLOAT32) return AXB200_UNSUPPORTED_TYPE;
   if (!q || (!out && !(gather && gather->mode == 0)) || !k || !v) return AXB200_INVALID_PTR;
   if (batch <= 0 || hq <= 0 || hkv <= 0 || d <= 0 || max_len <= 0) return AXB200_INVALID_ARGUMENT;
@@ -1705,7 +1874,7 @@ int decode_impl(bool paged, const void *q, void *out, const void *k, const void 
   // Who writes the result.  One chunk per sequence at most: the split CTA itself.  Else the last CTA
   // of each (sequence, KV head) when a counter region is to be had, else a combine kernel - which
   // then also emits the single-chunk sequences, so that every item passes through one place.
-  p.arrival_region = need_ws ? arrival_region_for(workspace, (int64_t)batch * hkv) : -1;
+  p.arrival_region = need_ws || step ? arrival_region_for(workspace, (int64_t)batch * hkv) : -1;
   const bool combine_kernel = need_ws && p.arrival_region < 0;
   p.direct_ok = !combine_kernel;
   p.merge_pairs = g_merge_pairs;
@@ -1723,6 +1892,11 @@ int decode_impl(bool paged, const void *q, void *out, const void *k, const void 
   if (tiled && f16 && p.group > kMaxGroupMma) tiled = false;
   if (tiled && !f16 && !(p.group == 1 || p.group == 2 || p.group == 4 || p.group == 8))
     tiled = false;
+  // The step in one launch needs the fp16 TMA kernel at its full tile width, host-planned chunks and a
+  // counter region (which is looked up by workspace pointer); nothing has been launched at this point.
+  if (step && !(paged && f16 && tiled && (d == 64 || d == 128) && !pl.balanced && window == 0 && workspace &&
+                aligned16(workspace) && p.arrival_region >= 0 && aligned16(step->k_new) && aligned16(step->v_new)))
+    return kStepNotFused;
 
   CUtensorMap mk, mv;
   if (tiled) {
@@ -1737,7 +1911,7 @@ int decode_impl(bool paged, const void *q, void *out, const void *k, const void 
   if (prof >= 0) cudaEventRecord(g_profile.start[prof], st);
   if (tiled) {
     if (f16)
-      status = paged ? launch_f16<true>(mk, mv, p, g, grid, st) : launch_f16<false>(mk, mv, p, g, grid, st);
+      status = paged ? launch_f16<true>(mk, mv, p, g, grid, st, step) : launch_f16<false>(mk, mv, p, g, grid, st, nullptr);
     else
       status = paged ? launch_f32<true>(mk, mv, p, g, grid, st) : launch_f32<false>(mk, mv, p, g, grid, st);
   } else {
@@ -1844,9 +2018,105 @@ int sdpa_rows_fallback(const void *q, const void *k, const void *v, void *out, i
   return AXB200_OK;
 }
 
+// The decode step as ONE launch when that form applies (see the kStep notes at the fp16 kernel), else
+// kStepNotFused with nothing launched.  q, k_new, v_new may live in page-locked host memory that the
+// device can address; out too.
+int decode_step_try_fused(const void *q, const void *k_new, const void *v_new, void *out, void *k_pages,
+                          void *v_pages, const int32_t *block_table, int32_t *seq_lens, const int64_t *pos,
+                          const float *inv_freq, float theta, int rotate, int mrope, int h_sec, int w_sec,
+                          int batch, int hq, int hkv, int d, int page_tokens, int max_blocks, int num_pages,
+                          int64_t max_seq_len, int dtype, void *workspace, size_t workspace_bytes,
+                          void *stream) {
+  {
+    std::lock_guard<std::mutex> lock(g_settings_mu);
+    if (!g_step_fused) return kStepNotFused;
+  }
+  if (dtype != AXB200_FLOAT16 || !(d == 64 || d == 128) || batch > kArrivalSlots) return kStepNotFused;
+  if (!k_new || !v_new || !seq_lens) return AXB200_INVALID_PTR;
+  if (rotate && mrope && !inv_freq) return AXB200_INVALID_PTR;
+  StepParams sp{};
+  sp.k_new = k_new;
+  sp.v_new = v_new;
+  sp.k_pages = k_pages;
+  sp.v_pages = v_pages;
+  sp.seq_lens = seq_lens;
+  sp.pos = pos;
+  sp.inv_freq_dev = inv_freq;
+  sp.rotate = rotate;
+  sp.mrope = mrope;
+  sp.h_lim = h_sec * 3;
+  sp.w_lim = w_sec * 3;
+  if (rotate && !inv_freq) rope_inv_freq_host(theta, d, sp.table);
+  return decode_impl(true, q, out, k_pages, v_pages, block_table, seq_lens, 0, batch, hq, hkv, d, page_tokens,
+                     max_blocks, num_pages, max_seq_len, dtype, workspace, workspace_bytes,
+                     static_cast<cudaStream_t>(stream), nullptr, 0, 0, 0, &sp);
+}
+
 }  // namespace axb
 
 extern "C" {
+
+int axb200_set_step_fused(int on) {
+  std::lock_guard<std::mutex> lock(axb::g_settings_mu);
+  axb::g_step_fused = on != 0;
+  return AXB200_OK;
+}
+
+size_t axb200_decode_step_workspace_bytes(int batch, int hq, int hkv, int d, int64_t max_seq_len, int dtype) {
+  const size_t es = axb::dtype_size(dtype);
+  if (es == 0 || batch <= 0 || hq <= 0 || hkv <= 0 || d <= 0 || max_seq_len <= 0) return 0;
+  const size_t attn = (axb200_gqa_workspace_bytes(batch, hq, hkv, d, max_seq_len, dtype) + 255) & ~size_t(255);
+  return attn + (((size_t)batch * hq * d * es + 255) & ~size_t(255));  // + the rotated q of the two-launch form
+}
+
+int axb200_decode_step_launches(int batch, int hq, int hkv, int d, int64_t max_seq_len, int dtype) {
+  if (batch <= 0 || hq <= 0 || hkv <= 0 || d <= 0 || max_seq_len <= 0 || hq % hkv != 0) return 0;
+  bool fused;
+  {
+    std::lock_guard<std::mutex> lock(axb::g_settings_mu);
+    fused = axb::g_step_fused && axb::g_fused_merge;
+  }
+  const axb::Plan pl = axb::make_plan(batch, hq, hkv, d, max_seq_len);
+  fused = fused && dtype == AXB200_FLOAT16 && (d == 64 || d == 128) && hq / hkv <= axb::kMaxGroupMma &&
+          !pl.balanced && (int64_t)batch * hkv <= axb::kArrivalSlots;
+  return fused ? 1 : 2;
+}
+
+int axb200_decode_step_paged(const void *q, const void *k_new, const void *v_new, void *out, void *k_pages,
+                             void *v_pages, const int32_t *block_table, int32_t *seq_lens,
+                             const int64_t *pos, const float *inv_freq, float theta, int rotate, int mrope,
+                             int h_sec, int w_sec, int batch, int hq, int hkv, int d, int page_tokens,
+                             int max_blocks, int num_pages, int64_t max_seq_len, int dtype, void *workspace,
+                             size_t workspace_bytes, void *stream) {
+  const size_t es = axb::dtype_size(dtype);
+  if (es == 0) return AXB200_UNSUPPORTED_TYPE;
+  if (!q || !k_new || !v_new || !out || !k_pages || !v_pages || !block_table || !seq_lens || !workspace)
+    return AXB200_INVALID_PTR;
+  if (batch <= 0 || hq <= 0 || hkv <= 0 || d <= 0 || max_seq_len <= 0) return AXB200_INVALID_ARGUMENT;
+  if (workspace_bytes < axb200_decode_step_workspace_bytes(batch, hq, hkv, d, max_seq_len, dtype))
+    return AXB200_INVALID_ARGUMENT;
+  const size_t attn_bytes = (axb200_gqa_workspace_bytes(batch, hq, hkv, d, max_seq_len, dtype) + 255) & ~size_t(255);
+  int rc = axb::decode_step_try_fused(q, k_new, v_new, out, k_pages, v_pages, block_table, seq_lens, pos, inv_freq,
+                                      theta, rotate, mrope, h_sec, w_sec, batch, hq, hkv, d, page_tokens, max_blocks,
+                                      num_pages, max_seq_len, dtype, workspace, attn_bytes, stream);
+  if (rc != axb::kStepNotFused) return rc;
+  // two launches: the append leaves the rotated q in the workspace (the caller's q stays as it is)
+  void *q_rot = static_cast<uint8_t *>(workspace) + attn_bytes;
+  const void *q_attn = q;
+  if (rotate) {
+    rc = axb::kv_append_rope_from(q_rot, q, k_new, v_new, k_pages, v_pages, block_table, seq_lens, pos, inv_freq, theta,
+                                  1, mrope, h_sec, w_sec, batch, hq, hkv, d, page_tokens, max_blocks, num_pages,
+                                  dtype, 0, 1, stream);
+    q_attn = q_rot;
+  } else {
+    rc = axb::kv_append_rope_from(nullptr, nullptr, k_new, v_new, k_pages, v_pages, block_table, seq_lens, pos,
+                                  inv_freq, theta, 0, mrope, h_sec, w_sec, batch, 0, hkv, d, page_tokens, max_blocks,
+                                  num_pages, dtype, 0, 1, stream);
+  }
+  if (rc != AXB200_OK) return rc;
+  return axb200_gqa_decode_paged(q_attn, out, k_pages, v_pages, block_table, seq_lens, batch, hq, hkv, d, page_tokens,
+                                 max_blocks, num_pages, max_seq_len, dtype, workspace, attn_bytes, stream);
+}
 
 int axb200_set_wait_limit_ns(uint64_t ns) {
   if (ns == 0) return AXB200_INVALID_ARGUMENT;

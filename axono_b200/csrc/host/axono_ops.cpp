@@ -296,6 +296,31 @@ Status GqaDecodeAttentionPaged(const Context &, const Tensor &q, axb200_kv_arena
                                     num_pages, max_seq_len, dtype, scratch.data(), scratch.num_bytes(), Stream()));
 }
 
+Status DecodeStepPaged(const Context &, const Tensor &q, const Tensor &k_new, const Tensor &v_new, axb200_kv_arena *arena,
+                       int layer, const Tensor *pos, const Tensor *inv_freq, float theta, bool rotate, bool mrope, int h_sec,
+                       int w_sec, int64_t max_seq_len, Tensor &result) {
+  if (!OneDevice({&q, &k_new, &v_new, pos, inv_freq})) return Status::DEVICE_MISMATCH;
+  if (!arena || q.ndim() != 3 || k_new.ndim() != 3 || v_new.shape() != k_new.shape() || !Float(q.dtype()))
+    return Status::SHAPE_MISMATCH;
+  int n_layers, num_pages, hkv, page_tokens, d, dtype, max_seqs, max_blocks;
+  if (axb200_kv_arena_geometry(arena, &n_layers, &num_pages, &hkv, &page_tokens, &d, &dtype, &max_seqs, &max_blocks) != 0)
+    return Status::INVALID_PTR;
+  const int hq = (int)q.shape()[1];
+  if ((int)q.shape()[0] != max_seqs || (int)q.shape()[2] != d || Dt(q.dtype()) != dtype || (int)k_new.shape()[0] != max_seqs ||
+      (int)k_new.shape()[1] != hkv || (int)k_new.shape()[2] != d || k_new.dtype() != q.dtype() || layer < 0 || layer >= n_layers)
+    return Status::SHAPE_MISMATCH;
+  Status st = result.Resize(q.shape());
+  if (st != Status::OK) return st;
+  const size_t ws = axb200_decode_step_workspace_bytes(max_seqs, hq, hkv, d, max_seq_len, dtype);
+  Tensor scratch = Scratch(ws, q.device());
+  return St(axb200_decode_step_paged(q.data(), k_new.data(), v_new.data(), result.data(), axb200_kv_arena_k_pages(arena, layer),
+                                     axb200_kv_arena_v_pages(arena, layer), axb200_kv_arena_block_table(arena),
+                                     axb200_kv_arena_seq_lens(arena), pos ? pos->data<int64_t>() : nullptr,
+                                     inv_freq ? inv_freq->data<float>() : nullptr, theta, rotate, mrope, h_sec, w_sec, max_seqs,
+                                     hq, hkv, d, page_tokens, max_blocks, num_pages, max_seq_len, dtype, scratch.data(),
+                                     scratch.num_bytes(), Stream()));
+}
+
 }  // namespace cuda
 }  // namespace ops
 }  // namespace axono

@@ -46,6 +46,11 @@ Status QkvNormRopeAppend(const Context &ctx, const Tensor &qkv, int hq, const Te
                          Tensor &q_out);
 
 // Paged cache (new operators; the cache lives in a KV arena).
+// kv_append_rope followed by gqa_decode_attention_paged as one operator (one launch where the library's
+// one-launch step applies): q is read, not rotated in place; the arena's lengths grow by one.
+Status DecodeStepPaged(const Context &ctx, const Tensor &q, const Tensor &k_new, const Tensor &v_new, axb200_kv_arena *arena,
+                       int layer, const Tensor *pos, const Tensor *inv_freq, float theta, bool rotate, bool mrope, int h_sec,
+                       int w_sec, int64_t max_seq_len, Tensor &result);
 Status KvAppendRope(const Context &ctx, Tensor *q, const Tensor &k_new, const Tensor &v_new, axb200_kv_arena *arena,
                     int layer, const Tensor *pos, const Tensor *inv_freq, float theta, bool rotate, bool mrope,
                     int h_sec, int w_sec, int slot_delta, bool advance);

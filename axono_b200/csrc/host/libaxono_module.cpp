@@ -564,6 +564,33 @@ PYBIND11_MODULE(libaxono, m) {
           return result;
         },
         py::arg("q"), py::arg("arena"), py::arg("layer"), py::arg("max_seq_len"), py::arg("out") = py::none());
+  m.def("decode_step_paged",  // rope(q), rope(k_new), append, attention: one operator, one launch where the library can
+        [](const Tensor &q, const Tensor &k_new, const Tensor &v_new, Arena &arena, int layer, int64_t max_seq_len,
+           py::object out, py::object pos, py::object inv_freq, float theta, bool rotate, py::object mrope_section) {
+          const Tensor *pp = pos.is_none() ? nullptr : pos.cast<const Tensor *>();
+          const Tensor *fp = inv_freq.is_none() ? nullptr : inv_freq.cast<const Tensor *>();
+          int h_sec = 0, w_sec = 0;
+          const bool mrope = !mrope_section.is_none();
+          if (mrope) {
+            auto sec = mrope_section.cast<std::vector<int>>();
+            if (sec.size() != 3) throw std::runtime_error("mrope_section: (t, h, w)");
+            h_sec = sec[1];
+            w_sec = sec[2];
+          }
+          Tensor result = out.is_none() ? Tensor::Uninitialized(q.dtype(), q.shape(), q.device()) : out.cast<Tensor>();
+          if (!out.is_none() && (result.dtype() != q.dtype() || result.shape() != q.shape() || result.device() != q.device()))
+            throw std::runtime_error("decode_step_paged: out must match q in dtype, shape and device");
+          Check("decode_step_paged", aops::DecodeStepPaged(Context(), q, k_new, v_new, arena.h, layer, pp, fp, theta, rotate,
+                                                           mrope, h_sec, w_sec, max_seq_len, result));
+          return result;
+        },
+        py::arg("q"), py::arg("k_new"), py::arg("v_new"), py::arg("arena"), py::arg("layer"), py::arg("max_seq_len"),
+        py::arg("out") = py::none(), py::arg("pos") = py::none(), py::arg("inv_freq") = py::none(),
+        py::arg("theta") = 1e6f, py::arg("rotate") = true, py::arg("mrope_section") = py::none());
+  m.def("decode_step_launches", [](int batch, int hq, int hkv, int d, int64_t max_seq_len, DataType dtype) {
+    return axb200_decode_step_launches(batch, hq, hkv, d, max_seq_len, static_cast<int>(dtype));
+  });
+  m.def("set_step_fused", [](bool on) { axb200_set_step_fused(on ? 1 : 0); }, py::arg("on"));
   m.def(
       "decode_step_host",  // one decode step with HOST activations (pinned arrays): copies in, rope + append, attention, copy out, wait
       [](Arena &arena, int layer, py::array q_host, py::array k_host, py::array v_host, py::array out_host, Tensor &q_dev,

@@ -10,7 +10,8 @@
 // involved at all: the append kernel reads q / k_new / v_new from host memory itself (a few KB per
 // sequence, each byte read once; the rotated q goes to the device staging buffer, where the attention
 // kernel reads it many times), and the attention kernel's final rows are stored straight into the host
-// output buffer.  Each copy saved is a separate DMA operation with its own few microseconds of latency
+// output buffer; where the one-launch step applies (fp16, head_dim 64 or 128) there is no append kernel
+// either.  Each copy saved is a separate DMA operation with its own few microseconds of latency
 // on a step that is itself tens to hundreds of microseconds.  Pageable memory takes the copying path.
 #include "common.cuh"
 
@@ -43,7 +44,14 @@ extern "C" int axb200_decode_step_host(
   const size_t qb = (size_t)batch * hq * d * es, kb = (size_t)batch * hkv * d * es;
   if (rotate && device_addressable_host(q_host) && device_addressable_host(k_new_host) &&
       device_addressable_host(v_new_host) && device_addressable_host(out_host)) {
-    int rc = axb::kv_append_rope_from(q_dev, q_host, k_new_host, v_new_host, k_pages, v_pages, block_table, seq_lens,
+    // one launch when that form applies: the attention kernel reads q, k_new, v_new from host memory itself
+    int rc = axb::decode_step_try_fused(q_host, k_new_host, v_new_host, out_host, k_pages, v_pages, block_table,
+                                        seq_lens, pos, inv_freq, theta, rotate, mrope, h_sec, w_sec, batch, hq, hkv, d,
+                                        page_tokens, max_blocks, num_pages, max_seq_len, dtype, workspace,
+                                        workspace_bytes, stream);
+    if (rc == AXB200_OK) return cudaStreamSynchronize(st) == cudaSuccess ? AXB200_OK : AXB200_DEVICE_ERROR;
+    if (rc != axb::kStepNotFused) return rc;
+    rc = axb::kv_append_rope_from(q_dev, q_host, k_new_host, v_new_host, k_pages, v_pages, block_table, seq_lens,
                                       pos, inv_freq, theta, rotate, mrope, h_sec, w_sec, batch, hq, hkv, d,
                                       page_tokens, max_blocks, num_pages, dtype, 0, 1, stream);
     if (rc != AXB200_OK) return rc;

@@ -71,17 +71,13 @@ __device__ __forceinline__ void rotate_vec(float (&a)[kN], float (&b)[kN], const
 #pragma unroll
   for (int j = 0; j < kN; ++j) {
     const float x = a[j], y = b[j];
-    a[j] = x * c0[j] - y * s0[j];
-    b[j] = y * c1[j] + x * s1[j];
+    a[j] = rope_lo(x, y, c0[j], s0[j]);
+    b[j] = rope_hi(x, y, c1[j], s1[j]);
   }
 }
 
-// Position of rotary pair i: the stride-3 M-RoPE rule (src/ops/cpu/sequence.cpp:222-227).
-__device__ __forceinline__ float pair_position(int i, float pt, float ph, float pw, int h_lim,
-                                               int w_lim) {
-  if (i % 3 == 1 && i < h_lim) return ph;
-  if (i % 3 == 2 && i < w_lim) return pw;
-  return pt;
+__device__ __forceinline__ float pair_position(int i, float pt, float ph, float pw, int h_lim, int w_lim) {
+  return mrope_pair_position(i, pt, ph, pw, h_lim, w_lim);
 }
 
 enum RopeMode { kModeTheta = 0, kModeMrope = 1, kModeCosSin = 2 };
@@ -123,8 +119,8 @@ rope_kernel(const T *x, T *out, const int64_t *pos, const float *inv_freq_dev,
       c1 = c0;
       s1 = s0;
     }
-    st(dst + i, a * c0 - b * s0);
-    st(dst + i + half, b * c1 + a * s1);
+    st(dst + i, rope_lo(a, b, c0, s0));
+    st(dst + i + half, rope_hi(a, b, c1, s1));
   }
 }
 
@@ -181,8 +177,8 @@ rope_rows_kernel(const T *x, T *out, const int64_t *pos, const float *inv_freq_d
       for (int idx = threadIdx.x; idx < heads * half; idx += blockDim.x) {
         const int h = idx / half, i = idx - h * half;
         const float a = ld(src + h * dim + i), b = ld(src + h * dim + i + half);
-        st(dst + h * dim + i, a * s_c0[i] - b * s_s0[i]);
-        st(dst + h * dim + i + half, b * s_c1[i] + a * s_s1[i]);
+        st(dst + h * dim + i, rope_lo(a, b, s_c0[i], s_s0[i]));
+        st(dst + h * dim + i + half, rope_hi(a, b, s_c1[i], s_s1[i]));
       }
     }
   }
@@ -322,8 +318,8 @@ kv_append_rope_kernel(const AppendParams p, const InvFreqTable table) {
       if (i >= half) continue;
       if (rot) {
         const float c = s_cos[i], s = s_sin[i];
-        st(dst + i, a[j] * c - bb[j] * s);
-        st(dst + i + half, bb[j] * c + a[j] * s);
+        st(dst + i, rope_lo(a[j], bb[j], c, s));
+        st(dst + i + half, rope_hi(a[j], bb[j], c, s));
       } else {  // a value row, or a key row without rotation: the bits as they came
         const T *src = row_of(head);
         dst[i] = src[i];
@@ -426,16 +422,16 @@ kv_prefill_write_kernel(const PrefillWriteParams p, const InvFreqTable table) {
       if (p.rotate) {
         T *row = q + (size_t)h * p.d;
         const float a = ld(row + i), bb = ld(row + i + half);
-        st(row + i, a * c - bb * sn);
-        st(row + i + half, bb * c + a * sn);
+        st(row + i, rope_lo(a, bb, c, sn));
+        st(row + i + half, rope_hi(a, bb, c, sn));
       }
     } else if (page_ok) {
       const T *row = kn + (size_t)h * p.d;
       T *dst = reinterpret_cast<T *>(p.k_pages) + (((size_t)page * p.hkv + h) * p.page_tokens + tok) * p.d;
       if (p.rotate) {
         const float a = ld(row + i), bb = ld(row + i + half);
-        st(dst + i, a * c - bb * sn);
-        st(dst + i + half, bb * c + a * sn);
+        st(dst + i, rope_lo(a, bb, c, sn));
+        st(dst + i + half, rope_hi(a, bb, c, sn));
       } else {
         dst[i] = row[i];
         dst[i + half] = row[i + half];
@@ -551,7 +547,7 @@ qkv_norm_rope_append_kernel(const AppendParams p, const FusedQkvParams f, const 
       }
       if (p.rotate) {
         const float sn = s_sin[i], cs = s_cos[i];
-        const float r0 = x0 * cs - x1 * sn, r1 = x1 * cs + x0 * sn;
+        const float r0 = rope_lo(x0, x1, cs, sn), r1 = rope_hi(x0, x1, cs, sn);
         x0 = r0;
         x1 = r1;
       }
@@ -570,6 +566,13 @@ void fill_table(InvFreqTable *t, float theta, int dim) {
   for (int i = 0; i < dim / 2 && i < kMaxHalf; ++i)
     t->f[i] = powf(theta, -2.0f * static_cast<float>(i) / static_cast<float>(dim));
 }
+}  // namespace
+
+void rope_inv_freq_host(float theta, int dim, float *out) {
+  for (int i = 0; i < dim / 2; ++i) out[i] = powf(theta, -2.0f * static_cast<float>(i) / static_cast<float>(dim));
+}
+
+namespace {
 
 int grid_for(int64_t total) {
   int64_t blocks = (total + 255) / 256;

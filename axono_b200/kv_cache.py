@@ -121,6 +121,17 @@ class PagedKVCache(KVCache):
             self._host_len_bound += 1
         return q
 
+    def step(self, layer_idx: int, q, k_new, v_new, out=None, pos=None, inv_freq=None, theta=10000.0,
+             mrope_section=None):
+        """append_rope + attend as one operator (one launch where the library can); q is not modified."""
+        bound = self.max_seq_len if torch.cuda.is_current_stream_capturing() else min(self.max_seq_len,
+                                                                                      self._host_len_bound + 1)
+        out = ops.decode_step_paged(q, k_new, v_new, self.k_pages[layer_idx], self.v_pages[layer_idx], self.block_table,
+                                    self.seq_lens, max(bound, 1), out=out, pos=pos, inv_freq=inv_freq, theta=theta,
+                                    mrope_section=mrope_section)
+        self._host_len_bound += 1
+        return out
+
     def get(self, layer_idx: int):
         """(k_pages, v_pages, block_table, seq_lens) of the layer - the paged equivalent of the
         reference's (k_full, v_full)."""

@@ -188,6 +188,34 @@ def kv_append_rope(q, k_new, v_new, k_pages, v_pages, block_table, seq_lens, pos
     return q
 
 
+def decode_step_paged(q, k_new, v_new, k_pages, v_pages, block_table, seq_lens, max_seq_len, out=None, pos=None,
+                      inv_freq=None, theta=10000.0, mrope_section=None, rotate=True):
+    """One decode step as one operator: rope(q), rope(k_new), append of (k_new, v_new), attention of q over
+    the cache including the new token.  q is read, not rotated in place; seq_lens grows by one.  One launch
+    where the library's one-launch step applies (fp16, head_dim 64 or 128), else the two kernels.
+    max_seq_len bounds the lengths after the append."""
+    op = "decode_step_paged"
+    dt = _dt(q, op)
+    batch, hq, d = q.shape
+    hkv = k_new.shape[1]
+    num_pages, _, page_tokens, _ = k_pages.shape
+    mrope = mrope_section is not None
+    h_sec, w_sec = (mrope_section[1], mrope_section[2]) if mrope else (0, 0)
+    for t in (q, k_new, v_new):
+        if not t.is_contiguous():
+            raise RuntimeError(f"{op}: tensors must be contiguous")
+    if out is None:
+        out = torch.empty_like(q)
+    lib = _capi.lib()
+    ws = workspace(q.device, lib.axb200_decode_step_workspace_bytes(batch, hq, hkv, d, int(max_seq_len), dt))
+    _call(lib.axb200_decode_step_paged(
+        q.data_ptr(), k_new.data_ptr(), v_new.data_ptr(), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(),
+        block_table.data_ptr(), seq_lens.data_ptr(), _ptr(pos), _ptr(inv_freq), float(theta), int(rotate), int(mrope),
+        h_sec, w_sec, batch, hq, hkv, d, page_tokens, block_table.shape[1], num_pages, int(max_seq_len), dt,
+        ws.data_ptr(), ws.numel(), _stream(q)), op)
+    return out
+
+
 def kv_prefill_write(q, k, v, k_pages, v_pages, block_row, start=0, pos=None, inv_freq=None, theta=10000.0,
                      mrope_section=None, rotate=True):
     """Writes the n tokens k, v (n,hkv,d) of one sequence into its pages at slots start.., rotating k (and

@@ -280,8 +280,9 @@ class NativeStep:
     cached tokens per sequence on scattered pages (contents 0.5 * N(0,1), seeded), q / k_new / v_new
     resident on the device, and `step()` = kv_append_rope + gqa_decode_attention_paged."""
 
-    def __init__(self, lx, device, lens, capacity, dtype_name, seed):
+    def __init__(self, lx, device, lens, capacity, dtype_name, seed, one_op=True):
         self.lx, self.device = lx, device
+        self.one_op = one_op  # the step as the one operator decode_step_paged; False: append, then attention
         self.lens = np.asarray(lens, np.int64)
         self.B = len(self.lens)
         self.dtype = lx.DataType.FLOAT16 if dtype_name == "f16" else lx.DataType.FLOAT32
@@ -308,10 +309,18 @@ class NativeStep:
         self.bound = int(self.cur.max())
 
     def step(self):
-        self.lx.kv_append_rope(self.arena, 0, self.q, self.k_new, self.v_new, theta=1e6)
         self.cur += 1
         self.bound = min(self.capacity, self.bound + 1)
-        self.lx.gqa_decode_attention_paged(self.q, self.arena, 0, self.bound, out=self.out)
+        if self.one_op:
+            self.lx.decode_step_paged(self.q, self.k_new, self.v_new, self.arena, 0, self.bound, out=self.out, theta=1e6)
+        else:
+            self.lx.kv_append_rope(self.arena, 0, self.q, self.k_new, self.v_new, theta=1e6)
+            self.lx.gqa_decode_attention_paged(self.q, self.arena, 0, self.bound, out=self.out)
+
+    def launches_per_step(self):
+        if not self.one_op:
+            return 2
+        return int(self.lx.decode_step_launches(self.B, HQ, HKV, D, max(self.bound, 1), self.dtype))
 
     def attend(self):
         self.lx.gqa_decode_attention_paged(self.q, self.arena, 0, max(self.bound, 1), out=self.out)
@@ -342,14 +351,17 @@ class NativeStep:
         return rdv.max(ms), my_bytes
 
     def capture_step(self, replays):
-        """The step as one CUDA graph (append + attention; the attention's grid is sized for the lengths the
+        """The step as one CUDA graph (the step operator, or append + attention; the grid is sized for the lengths the
         sequences can reach within `replays` replays, so the graph follows the growing cache that far).
         Capturing runs the step once for real."""
         from axono_b200 import native
 
         def body():
-            self.lx.kv_append_rope(self.arena, 0, self.q, self.k_new, self.v_new, theta=1e6)
-            self.lx.gqa_decode_attention_paged(self.q, self.arena, 0, bound, out=self.out)
+            if self.one_op:
+                self.lx.decode_step_paged(self.q, self.k_new, self.v_new, self.arena, 0, bound, out=self.out, theta=1e6)
+            else:
+                self.lx.kv_append_rope(self.arena, 0, self.q, self.k_new, self.v_new, theta=1e6)
+                self.lx.gqa_decode_attention_paged(self.q, self.arena, 0, bound, out=self.out)
             return self.out
 
         bound = min(self.capacity, int(self.bound) + int(replays) + 1)  # what the lengths can reach under this graph
@@ -428,7 +440,12 @@ class NativeStep:
         worst = 0.0
         for b in rows:
             k, v = self.arena.gather(0, int(b), int(self.cur[b]))
-            ref = orc.gqa_decode(q[b : b + 1], k.astype(np.float32), v.astype(np.float32))
+            qb = q[b : b + 1]
+            if self.one_op:  # the operator leaves q as it was: the checker rotates it (position = tokens cached before)
+                qb = orc.rope(qb, [int(self.cur[b]) - 1], 1e6)
+                if self.elem == 2:
+                    qb = qb.astype(np.float16).astype(np.float32)
+            ref = orc.gqa_decode(qb, k.astype(np.float32), v.astype(np.float32))
             worst = max(worst, float(oracle.rel_err(out[b : b + 1], ref)))
         return {"rows": [int(b) for b in rows], "lengths": [int(self.cur[b]) for b in rows], "rel_err": worst,
                 "checker": orc.kind, "tolerance": 2e-3 if self.elem == 2 else 1e-5}
@@ -531,8 +548,9 @@ def run_native(args):
         if max(parity["gather"], parity["cp"]) > parity["tolerance"] or parity["device_error_bits"]:
             raise SystemExit(f"multi-GPU parity failed: {parity}")
 
-    run = NativeStep(lx, device, lens, capacity, args.dtype, seed=rank)
+    run = NativeStep(lx, device, lens, capacity, args.dtype, seed=rank, one_op=not args.two_kernel_step)
     B = run.B
+    launches_per_step = run.launches_per_step()
     # ---- value: inputs resident, CUDA events around K steps ----
     sampler.start()  # sampled from here to the end of the host-buffer phase: the GPU is under this load throughout
     # The step is captured once as a CUDA graph and the K timed steps are K replays launched from native
@@ -561,7 +579,7 @@ def run_native(args):
         run.step()
     eager_ms, eager_bytes = run.timed_steps(rdv, args.steps)
     eager = {"value": rdv.sum(eager_bytes) / (eager_ms / 1e3) / 1e9, "unit": UNIT, "ms_per_step": eager_ms / args.steps,
-             "launch": "two operator calls per step from Python"}
+             "launch": "one operator call per step from Python" if run.one_op else "two operator calls per step from Python"}
     graph.reset()
 
     # ---- roofline: the split kernel alone, event pairs around its launches ----
@@ -581,9 +599,9 @@ def run_native(args):
     e2e_bytes = rdv.sum(e2e_my_bytes)
     e2e = {"value": e2e_bytes / e2e_s / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
            "ms_per_step": e2e_s / args.steps * 1e3, "tokens_per_s": total_seqs * args.steps / e2e_s,
-           "transfer": "q, k_new, v_new and the output live in page-locked host memory; the append kernel reads the "
-                       "inputs from it and the attention kernel stores the output into it (the bytes cross the bus "
-                       "every step, no copy-engine operation), then the host waits for the stream"}
+           "transfer": "q, k_new, v_new and the output live in page-locked host memory; the kernels read the inputs "
+                       "from it and the attention kernel stores the output into it (the bytes cross the bus every "
+                       "step, no copy-engine operation), then the host waits for the stream"}
     sampler.pause()
     clocks = sampler.summary()
 
@@ -627,7 +645,7 @@ def run_native(args):
     def weak_scaling():
         # every GPU runs the same batch of 64 with the same lengths, so the figure can only fall below N times
         # one GPU's if the hardware makes it
-        wk = NativeStep(lx, device, all_lens, capacity, args.dtype, seed=0)
+        wk = NativeStep(lx, device, all_lens, capacity, args.dtype, seed=0, one_op=not args.two_kernel_step)
         for _ in range(args.warmup):
             wk.step()
         wms, wbytes = wk.timed_steps(rdv, args.steps)
@@ -658,7 +676,8 @@ def run_native(args):
             "sequences_per_gpu": seqs_per_gpu,
             "tokens_per_s": tokens_per_s,
             "frac_of_nominal_8TBs": value / (NOMINAL_HBM_GBS * world),
-            "e2e": e2e, "gpu_launches": 2 * args.steps, "clocks": clocks, "roofline": roofline,
+            "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "launches_per_step": launches_per_step,
+            "clocks": clocks, "roofline": roofline,
             "cpu_baseline": cpu, "parity": parity, "extra": extra,
         }
         print(json.dumps(line), flush=True)
@@ -1275,6 +1294,8 @@ def main():
     ap.add_argument("--no-dependent-launch", action="store_true",
                     help="launch the attention kernel in plain stream order (A/B of the programmatic dependent launch)")
     ap.add_argument("--no-tower", action="store_true", help="skip the text-tower figures in `extra`")
+    ap.add_argument("--two-kernel-step", action="store_true",
+                    help="the step as kv_append_rope + gqa_decode_attention_paged instead of the one operator (A/B)")
     args = ap.parse_args()
     rank0 = int(os.environ.get("RANK", "0")) == 0
     if args.impl == "reference-cuda":

@@ -325,6 +325,31 @@ int axb200_qkv_norm_rope_append(const void *qkv, int64_t ld, const void *q_norm_
                                 int page_tokens, int max_blocks, int num_pages,
                                 int dtype, int slot_delta, int advance, void *stream);
 
+/* One decode step of one layer as one operator: what the reference's layer does with three calls per
+ * token - rope on q and k, cache.update, gqa_decode_attention
+ * (axono/python/examples/vlm/qwen3vl/model.py:358-366) - i.e. axb200_kv_append_rope (slot_delta 0,
+ * advance 1) followed by axb200_gqa_decode_paged, with the same arguments and the same results bit for
+ * bit, except that q is only read: the rotated q never leaves the kernel (or, in the two-launch form,
+ * goes to the workspace).  For fp16 with head_dim 64 or 128 this is ONE launch: the attention kernel reads
+ * the old length, works with length + 1, rotates q in registers, and the CTA that owns the new token's
+ * row rotates k_new, stores k and v to the page and puts them into its staged tile; the last CTA of a
+ * sequence to have read the old length stores the new one.  Other types and head sizes run the two
+ * kernels.  max_seq_len bounds the lengths AFTER the append.  A sequence without room for the token sets
+ * AXB200_ERR_CAPACITY, appends nothing and attends its old tokens.  workspace: at least
+ * axb200_decode_step_workspace_bytes, 16-byte aligned; calls that may overlap on the GPU use different
+ * workspaces.  axb200_decode_step_launches: 1 or 2, how many kernels the call launches for these sizes
+ * (aligned pointers assumed).  axb200_set_step_fused(0) forces the two-launch form (A/B, tests). */
+size_t axb200_decode_step_workspace_bytes(int batch, int hq, int hkv, int d, int64_t max_seq_len, int dtype);
+int axb200_decode_step_launches(int batch, int hq, int hkv, int d, int64_t max_seq_len, int dtype);
+int axb200_set_step_fused(int on);
+int axb200_decode_step_paged(const void *q, const void *k_new, const void *v_new, void *out,
+                             void *k_pages, void *v_pages, const int32_t *block_table, int32_t *seq_lens,
+                             const int64_t *pos, const float *inv_freq, float theta,
+                             int rotate, int mrope, int h_sec, int w_sec,
+                             int batch, int hq, int hkv, int d,
+                             int page_tokens, int max_blocks, int num_pages, int64_t max_seq_len,
+                             int dtype, void *workspace, size_t workspace_bytes, void *stream);
+
 /* One decode step with HOST activations: copies q (batch,hq,d), k_new, v_new (batch,hkv,d) from host
  * (pinned memory for asynchronous copies) into the device staging buffers q_dev / k_new_dev /
  * v_new_dev, runs axb200_kv_append_rope (slot_delta 0, advance 1) and axb200_gqa_decode_paged, copies
