@@ -37,9 +37,12 @@ def _side_stream(device) -> "torch.cuda.Stream":
 
 def decode_block(x, residual, norm_weight, q, k_new, v_new, cache: PagedKVCache, layer: int, gate, up,
                  eps: float = 1e-6, theta: float = 1e6, pos=None, inv_freq=None, mrope_section=None,
-                 parallel: bool = False):
+                 parallel: bool = False, one_op: bool = True):
     """One fused decode block.  Returns (y, xn, attn, act): the residual sum and its norm, the attention
-    output of q (rotated in place) over the cache including the appended token, and silu(gate)*up.
+    output of the rotated q over the cache including the appended token, and silu(gate)*up.  With
+    `one_op` (default) rope, append and attention are the one operator `cache.step` (one launch for fp16
+    with head_dim 64 or 128; q is left as it is); without it, `append_rope` (q rotated in place) followed
+    by `attend`.
 
     In this block the three parts do not depend on one another (the norm's and the activation's inputs
     are given), so with `parallel` the two launch-latency kernels go to a second stream while
@@ -47,9 +50,7 @@ def decode_block(x, residual, norm_weight, q, k_new, v_new, cache: PagedKVCache,
     branches of the graph and the block's time that of its attention chain."""
     if not parallel:
         y, xn = ops.add_rms_norm(x, residual, norm_weight, eps)
-        cache.append_rope(layer, q, k_new, v_new, pos=pos, inv_freq=inv_freq, theta=theta,
-                          mrope_section=mrope_section)
-        attn = cache.attend(layer, q)
+        attn = _rope_append_attend(cache, layer, q, k_new, v_new, pos, inv_freq, theta, mrope_section, one_op)
         act = ops.silu_mul(gate, up)
         return y, xn, attn, act
     cur = torch.cuda.current_stream(x.device)
@@ -58,11 +59,16 @@ def decode_block(x, residual, norm_weight, q, k_new, v_new, cache: PagedKVCache,
     with torch.cuda.stream(side):
         y, xn = ops.add_rms_norm(x, residual, norm_weight, eps)
         act = ops.silu_mul(gate, up)
-    cache.append_rope(layer, q, k_new, v_new, pos=pos, inv_freq=inv_freq, theta=theta,
-                      mrope_section=mrope_section)
-    attn = cache.attend(layer, q)
+    attn = _rope_append_attend(cache, layer, q, k_new, v_new, pos, inv_freq, theta, mrope_section, one_op)
     cur.wait_stream(side)
     return y, xn, attn, act
+
+
+def _rope_append_attend(cache, layer, q, k_new, v_new, pos, inv_freq, theta, mrope_section, one_op):
+    if one_op:
+        return cache.step(layer, q, k_new, v_new, pos=pos, inv_freq=inv_freq, theta=theta, mrope_section=mrope_section)
+    cache.append_rope(layer, q, k_new, v_new, pos=pos, inv_freq=inv_freq, theta=theta, mrope_section=mrope_section)
+    return cache.attend(layer, q)
 
 
 class TextTower:

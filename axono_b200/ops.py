@@ -82,6 +82,11 @@ def gqa_workspace_bytes(batch, hq, hkv, d, max_seq_len, dtype=torch.float16) -> 
     return int(_capi.lib().axb200_gqa_workspace_bytes(batch, hq, hkv, d, int(max_seq_len), _DTYPES[dtype]))
 
 
+def decode_step_workspace_bytes(batch, hq, hkv, d, max_seq_len, dtype=torch.float16) -> int:
+    """Scratch of `decode_step_paged` (the attention partials plus room for a rotated q)."""
+    return int(_capi.lib().axb200_decode_step_workspace_bytes(batch, hq, hkv, d, int(max_seq_len), _DTYPES[dtype]))
+
+
 def gqa_decode_attention(q, k, v):
     """q (1, n_q_heads, head_dim); k/v (seq_len, n_kv_heads, head_dim) -> (1, n_q_heads, head_dim).
     Equals scaled_dot_product_attention(q, k, v, is_causal=False); scale 1/sqrt(head_dim)."""

@@ -938,15 +938,15 @@ def run_tower(args):
         rn = lambda *s: torch.randn(s, generator=gen, device=device).half()  # noqa: E731
         x, res, w = rn(B, 2048), rn(B, 2048), (1 + 0.02 * torch.randn(2048, generator=gen, device=device)).half()
         q0, kn, vn, gate, up = rn(B, HQ, D), rn(B, HKV, D), rn(B, HKV, D), rn(B, 6144), rn(B, 6144)
-        ops.workspace(device, ops.gqa_workspace_bytes(B, HQ, HKV, D, cache.max_seq_len))
+        ops.workspace(device, ops.decode_step_workspace_bytes(B, HQ, HKV, D, cache.max_seq_len))
 
         def body():
-            # q is rotated in place, replay after replay (a rotation keeps its norm): in the model it
-            # comes fresh from the QKV projection every step, so no copy belongs to the block
-            return decode_block(x, res, w, q0, kn, vn, cache, 0, gate, up, theta=1e6, parallel=not args.no_fork)
+            return decode_block(x, res, w, q0, kn, vn, cache, 0, gate, up, theta=1e6, parallel=not args.no_fork,
+                                one_op=not args.two_kernel_step)
 
         kv_bytes = algo_bytes(np.asarray(lens) + 1)
-        launches_note = ("kv_append_rope -> attention (split + merge in one kernel), with add_rms_norm and silu_mul "
+        launches_note = (("rope + append + attention + merge in one kernel" if not args.two_kernel_step
+                          else "kv_append_rope -> attention (split + merge in one kernel)") + ", with add_rms_norm and silu_mul "
                          + ("on a second stream: parallel branches of the graph" if not args.no_fork else "in line"))
         other_bytes = 0.0
 
