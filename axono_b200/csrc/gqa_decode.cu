@@ -89,6 +89,7 @@ struct StepParams {
   const int64_t *pos;         // (batch), (3, batch) under M-RoPE, or null: position = tokens cached before
   const float *inv_freq_dev;  // (d / 2), or null: `table`
   int rotate, mrope, h_lim, w_lim;
+  int stage_q;                // q lives in host memory: fetch it once per CTA through shared memory
   float table[kStepHalfMax];  // theta^(-2i/d), from the host's powf
 };
 
@@ -682,6 +683,7 @@ gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
   extern __shared__ uint8_t smem_raw[];
   __shared__ int s_plan[kPlanWords];
   __shared__ float s_rope[kStep ? 2 * kStepHalfMax : 1];  // cos [0, 64), sin [64, 128) of the step's position
+  __shared__ __align__(16) __half s_q[kStep ? kMaxGroupMma * kD : 8];  // the group's q rows as they came
   constexpr int kStage = 256 * kD, kKSteps = kD / 16, kNTiles = kD / 8;
   uint8_t *smem = align_1024(smem_raw);
   uint64_t *full = reinterpret_cast<uint64_t *>(smem + SmemLayout<kStages, kStage>::kBarOffset);
@@ -790,10 +792,10 @@ gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
   const bool use_hi = p.group > 8;  // rows 8..15 of the M dimension carry query heads too
   const __half *qh = reinterpret_cast<const __half *>(p.q);
 
-  // Q as the A operand, resident in registers: kD / 16 k-steps x 4 regs.
+  // Q as the A operand, resident in registers: kD / 16 k-steps x 4 regs.  Asked for first: the loads fly
+  // while everything below up to the first use is worked out.
   uint32_t qa[kKSteps][4];
-  {
-    const __half *q0 = qh + ((size_t)b * p.hq + (size_t)hk * p.group + g) * p.d;
+  auto load_q = [&](const __half *q0) {
     const __half *q1 = q0 + 8 * p.d;
     const bool v0 = g < p.group, v1 = g + 8 < p.group;
 #pragma unroll
@@ -805,44 +807,74 @@ gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
       qa[ks][2] = v0 && in1 ? *reinterpret_cast<const uint32_t *>(q0 + c + 8) : 0u;
       qa[ks][3] = v1 && in1 ? *reinterpret_cast<const uint32_t *>(q1 + c + 8) : 0u;
     }
-  }
+  };
+  if (!(kStep && sp.stage_q)) load_q(qh + ((size_t)b * p.hq + (size_t)hk * p.group + g) * p.d);
 
-  // ---- kStep: rotate q, prepare the new token's rows ----
+  // ---- kStep, first half: what has to come from memory is asked for, the angles are worked out ----
   constexpr int kHalf = kD / 2, kPairs = kHalf / 32;  // rotary pairs per lane of the warp that appends
   const int new_row = L - 1 - (start + (ntiles - 1) * kTileTokensF16);  // the token's row in the last tile
   const bool patch = kStep && appended && chunk == w.n - 1 && warp == (new_row >> 4);
   __half k_lo[kPairs], k_hi[kPairs], v_lo[kPairs], v_hi[kPairs];
+  int new_page = 0;
   if constexpr (kStep) {
-    const __half *kn = reinterpret_cast<const __half *>(sp.k_new) + ((size_t)b * p.hkv + hk) * kD;
-    const __half *vn = reinterpret_cast<const __half *>(sp.v_new) + ((size_t)b * p.hkv + hk) * kD;
-    int page = 0;
-    if (patch) {  // the rows and the page id on their way while the angles are worked out
+    if (patch) {  // the token's rows and its page id on their way while the angles are worked out
+      const __half *kn = reinterpret_cast<const __half *>(sp.k_new) + ((size_t)b * p.hkv + hk) * kD;
+      const __half *vn = reinterpret_cast<const __half *>(sp.v_new) + ((size_t)b * p.hkv + hk) * kD;
 #pragma unroll
       for (int j = 0; j < kPairs; ++j) {
         const int i = lane + 32 * j;
         k_lo[j] = kn[i], k_hi[j] = kn[i + kHalf], v_lo[j] = vn[i], v_hi[j] = vn[i + kHalf];
       }
-      page = p.block_table[(size_t)b * p.max_blocks + (L - 1) / p.page_tokens];
+      new_page = p.block_table[(size_t)b * p.max_blocks + (L - 1) / p.page_tokens];
     }
-    if (sp.rotate) {
-      if (threadIdx.x < kHalf) {  // one angle per rotary pair, once per CTA
-        const int i = threadIdx.x;
-        float pt, ph, pw;
-        if (sp.pos == nullptr) {
-          pt = ph = pw = (float)(L - appended);  // tokens cached before this one
-        } else if (sp.mrope) {
-          pt = (float)sp.pos[b];
-          ph = (float)sp.pos[p.batch + b];
-          pw = (float)sp.pos[2 * p.batch + b];
-        } else {
-          pt = ph = pw = (float)sp.pos[b];
-        }
-        const float f = sp.mrope || sp.inv_freq_dev ? sp.inv_freq_dev[i] : sp.table[i];
-        const float posv = sp.mrope ? mrope_pair_position(i, pt, ph, pw, sp.h_lim, sp.w_lim) : pt;
-        sincosf(posv * f, &s_rope[kStepHalfMax + i], &s_rope[i]);
+    // q in host memory (sp.stage_q): the group's rows come through shared memory, 16 bytes a thread, every
+    // byte asked for once per CTA.  Fragment loads straight from q ask for each 32-byte sector from all
+    // four warps; over PCIe every such request is a read transaction, and a launch of thousands of CTAs
+    // saturates the link's request rate long before its bandwidth (measured: 0.35 ms instead of 0.27 ms
+    // per host-buffer step for a quarter of the batch).  The loads are asked for here and stored after
+    // the angles, so the two overlap.
+    uint4 q_piece[2];
+    const int q_pieces = p.group * (kD / 8);  // at most 16 heads x 16 pieces: two per thread
+    if (sp.stage_q) {
+      const uint4 *src = reinterpret_cast<const uint4 *>(qh + ((size_t)b * p.hq + (size_t)hk * p.group) * kD);
+#pragma unroll
+      for (int u = 0; u < 2; ++u)
+        if ((int)threadIdx.x + u * kConsumerThreads < q_pieces) q_piece[u] = src[threadIdx.x + u * kConsumerThreads];
+    }
+    if (sp.rotate && threadIdx.x < kHalf) {  // one angle per rotary pair, once per CTA
+      const int i = threadIdx.x;
+      float pt, ph, pw;
+      if (sp.pos == nullptr) {
+        pt = ph = pw = (float)(L - appended);  // tokens cached before this one
+      } else if (sp.mrope) {
+        pt = (float)sp.pos[b];
+        ph = (float)sp.pos[p.batch + b];
+        pw = (float)sp.pos[2 * p.batch + b];
+      } else {
+        pt = ph = pw = (float)sp.pos[b];
       }
-      named_bar_sync(1, kConsumerThreads);
-      // q: pair (c, c + kHalf) sits in k-steps ks and ks + kKSteps / 2 of the same thread
+      const float f = sp.mrope || sp.inv_freq_dev ? sp.inv_freq_dev[i] : sp.table[i];
+      const float posv = sp.mrope ? mrope_pair_position(i, pt, ph, pw, sp.h_lim, sp.w_lim) : pt;
+      sincosf(posv * f, &s_rope[kStepHalfMax + i], &s_rope[i]);
+    }
+    if (sp.stage_q) {
+#pragma unroll
+      for (int u = 0; u < 2; ++u)
+        if ((int)threadIdx.x + u * kConsumerThreads < q_pieces)
+          reinterpret_cast<uint4 *>(s_q)[threadIdx.x + u * kConsumerThreads] = q_piece[u];
+    }
+  }
+
+  if (kStep && sp.stage_q) {
+    named_bar_sync(1, kConsumerThreads);  // the staged rows (and the angles) are there
+    load_q(s_q + g * kD);
+  }
+
+  // ---- kStep, second half: rotate q in registers, rotate and store the new token's rows ----
+  if constexpr (kStep) {
+    if (!sp.stage_q) named_bar_sync(1, kConsumerThreads);  // the angles are there (q's loads flew meanwhile)
+    if (sp.rotate) {
+      // pair (c, c + kHalf) sits in k-steps ks and ks + kKSteps / 2 of the same thread
 #pragma unroll
       for (int ks = 0; ks < kKSteps / 2; ++ks) {
 #pragma unroll
@@ -869,8 +901,8 @@ gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
           k_hi[j] = __float2half_rn(rope_hi(a, bb, c, sn));
         }
       }
-      if (page >= 0 && page < p.num_pages) {  // the rows in the cache, for the steps to come
-        const size_t row = (((size_t)page * p.hkv + hk) * p.page_tokens + (L - 1) % p.page_tokens) * kD;
+      if (new_page >= 0 && new_page < p.num_pages) {  // the rows in the cache, for the steps to come
+        const size_t row = (((size_t)new_page * p.hkv + hk) * p.page_tokens + (L - 1) % p.page_tokens) * kD;
         __half *kd = reinterpret_cast<__half *>(sp.k_pages) + row, *vd = reinterpret_cast<__half *>(sp.v_pages) + row;
 #pragma unroll
         for (int j = 0; j < kPairs; ++j) {
@@ -2047,6 +2079,14 @@ int decode_step_try_fused(const void *q, const void *k_new, const void *v_new, v
   sp.h_lim = h_sec * 3;
   sp.w_lim = w_sec * 3;
   if (rotate && !inv_freq) rope_inv_freq_host(theta, d, sp.table);
+  {
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, q) != cudaSuccess) {
+      cudaGetLastError();
+    } else {
+      sp.stage_q = attr.type == cudaMemoryTypeHost;
+    }
+  }
   return decode_impl(true, q, out, k_pages, v_pages, block_table, seq_lens, 0, batch, hq, hkv, d, page_tokens,
                      max_blocks, num_pages, max_seq_len, dtype, workspace, workspace_bytes,
                      static_cast<cudaStream_t>(stream), nullptr, 0, 0, 0, &sp);
