@@ -108,3 +108,28 @@ def test_default_host_plan_and_the_override():
     assert np.all(ct == 128) and max_chunks == 256
     assert lib.axb200_set_chunk_tiles(-1) == 1
     lib.axb200_set_chunk_tiles(0)
+
+
+def test_how_many_launches_a_decode_step_takes():
+    """`axb200_decode_step_paged` is one launch where the attention kernel can append the token itself
+    (fp16, head_dim 64 or 128, at most 16 query heads per KV head, host-planned chunks), two otherwise."""
+    lib = _capi.lib()
+    lib.axb200_set_device_plan(0)
+    launches = lib.axb200_decode_step_launches
+    assert launches(64, 16, 8, 128, 32768, _capi.FLOAT16) == 1
+    assert launches(8, 8, 2, 64, 8192, _capi.FLOAT16) == 1
+    assert launches(1, 32, 2, 128, 100, _capi.FLOAT16) == 1
+    assert launches(64, 16, 8, 128, 32768, _capi.FLOAT32) == 2  # the fp32 kernels do not append
+    assert launches(8, 6, 2, 80, 8192, _capi.FLOAT16) == 2      # rides in a wider tile: not the step form
+    assert launches(8, 32, 1, 128, 8192, _capi.FLOAT16) == 2    # 32 query heads per KV head: generic kernel
+    assert launches(8, 16, 8, 128, 0, _capi.FLOAT16) == 0 and launches(8, 16, 5, 128, 64, _capi.FLOAT16) == 0
+    lib.axb200_set_device_plan(1)  # a launch planned on the device lengths reads them in every CTA's prologue
+    assert launches(8, 16, 8, 128, 8192, _capi.FLOAT16) == 2
+    lib.axb200_set_device_plan(0)
+    try:
+        lib.axb200_set_step_fused(0)
+        assert launches(64, 16, 8, 128, 32768, _capi.FLOAT16) == 2
+    finally:
+        lib.axb200_set_step_fused(1)
+    assert lib.axb200_decode_step_workspace_bytes(8, 16, 8, 128, 8192, _capi.FLOAT16) >= \
+        lib.axb200_gqa_workspace_bytes(8, 16, 8, 128, 8192, _capi.FLOAT16) + 8 * 16 * 128 * 2
