@@ -464,6 +464,7 @@ template <typename T>
 __global__ void __launch_bounds__(1024)
 qkv_norm_rope_append_kernel(const AppendParams p, const FusedQkvParams f, const InvFreqTable table) {
   __shared__ int s_len;
+  grid_dependency_launch();  // the layer's attention kernel may be scheduled; it waits for this one's end
   const int b = blockIdx.x;
   if (threadIdx.x == 0) s_len = p.seq_lens[b] + p.slot_delta;
   __syncthreads();

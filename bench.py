@@ -7,9 +7,10 @@ accumulation - one batch of 64 sequences, 16 query / 8 KV heads, head_dim 128, p
 uniform in [16384, 32768], K/V = 0.5 * N(0,1), q = N(0,1), all seeded and synthetic.  On N GPUs that
 batch is sharded over the ranks by KV bytes (`--scaling strong`, the default; `weak` gives every GPU
 its own batch of 64).  `b64_l32k` is the same with every sequence at 32768 tokens.  A step is one
-decode step of the path for the whole batch: RoPE + KV-cache append of the new token (1 kernel), then
-the split-K decode attention over the paged cache (1 kernel: the CTA that finishes a sequence's last
-chunk merges the partials).
+decode step of the path for the whole batch - RoPE of q and of the new key, KV-cache append of the new
+token, split-K decode attention over the paged cache, merge of the partials by the CTA that finishes a
+sequence's last chunk - as the one operator `decode_step_paged`, which is ONE kernel launch;
+`--two-kernel-step` runs it as `kv_append_rope` + `gqa_decode_attention_paged` (two launches).
 
 The default arm runs on the native runtime - libaxono tensors, the KV arena, the C ABI - with no
 PyTorch in the process at any N; ranks meet over a local socket (axono_b200.rendezvous).
@@ -18,8 +19,8 @@ One JSON line on rank 0.  `value` = KV-cache GB/s of the whole job with inputs r
 algorithmic bytes (K and V read once, q read, out written) of all ranks / device time of the timed
 steps (CUDA events, max over ranks).  `e2e` = the same metric through the host-buffer entry point:
 each step copies q, k_new, v_new from pinned host memory and reads the attention output back.
-`roofline` = the split kernel alone (event pairs recorded around its launches by the library) against
-the measured HBM peak.  `cpu_baseline` = the reference's CPU SDPA-GQA on the host cores, on a bounded
+`roofline` = the dominant kernel alone - with the one-launch step that is the step kernel itself (event
+pairs recorded around its launches by the library) - against the measured HBM peak.  `cpu_baseline` = the reference's CPU SDPA-GQA on the host cores, on a bounded
 sample of the same sequences.  `extra` carries, for the record: a check of the timed output against the
 CPU checker, the batch-64 x 32 K case, the 28-layer text-tower step (`c5_tower`, KV heads sharded over
 the GPUs with the attention kernel storing into every rank's gathered buffer) and, on several GPUs,
@@ -387,14 +388,21 @@ class NativeStep:
         return max(per_rank), my_bytes, per_rank
 
     def kernel_alone(self, steps):
-        """The split kernel by itself: event pairs the library records around its launches."""
+        """The dominant kernel by itself: event pairs the library records around its launches.  With the
+        one-operator step that kernel IS the step (the same launches the timed region replays, lengths growing
+        by one a launch); with the two-kernel step it is the attention call.  Returns (average milliseconds,
+        launches, average algorithmic bytes per launch)."""
         lx = self.lx
+        total_bytes = self.bytes_of_steps(steps) if self.one_op else steps * algo_bytes(self.cur, self.elem)
         lx.profile_enable(True)
         for _ in range(steps):
-            self.attend()
+            if self.one_op:
+                self.step()
+            else:
+                self.attend()
         ms_total, launches = lx.profile_collect()
         lx.profile_enable(False)
-        return ms_total / max(launches, 1), launches
+        return ms_total / max(launches, 1), launches, total_bytes / max(steps, 1)
 
     def host_steps(self, rdv, steps, warmup):
         """The same step through the host-buffer entry point: q, k_new, v_new come from pinned host
@@ -584,10 +592,10 @@ def run_native(args):
 
     # ---- roofline: the split kernel alone, event pairs around its launches ----
     run.set_lengths(lens)
-    kern_ms, launches = run.kernel_alone(min(args.steps, 2000))
-    launch_bytes = algo_bytes(lens, elem)
+    kern_ms, launches, launch_bytes = run.kernel_alone(min(args.steps, 2000))
     achieved = launch_bytes / (kern_ms / 1e3) / 1e9
-    roofline = {"bound": "hbm", "kernel": f"gqa_split_{args.dtype}_kernel<paged>", "achieved": achieved, "peak": peak,
+    roofline = {"bound": "hbm", "kernel": f"gqa_split_{args.dtype}_kernel<paged" + (", step>" if launches_per_step == 1 else ">"),
+                "achieved": achieved, "peak": peak,
                 "unit": "GB/s", "frac": achieved / peak, "peak_source": f"of {peak_kind}",
                 "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS, "kernel_ms": kern_ms,
                 "launches_timed": launches, "algorithmic_bytes_per_launch": launch_bytes,
@@ -626,10 +634,10 @@ def run_native(args):
         run.set_lengths(lens32)
         ms32, b32 = run.timed_steps(rdv, 20)
         run.set_lengths(lens32)
-        k32, _ = run.kernel_alone(100)
+        k32, _, kb32 = run.kernel_alone(100)
         run.set_lengths(lens32)
         s32, eb32, _, _ = run.host_steps(rdv, 20, 3)
-        gbs = algo_bytes(lens32) / (k32 / 1e3) / 1e9
+        gbs = kb32 / (k32 / 1e3) / 1e9
         return {"split_kernel_ms": k32, "kv_gbs": gbs, "frac_of_measured": gbs / peak,
                 "frac_of_nominal_8TBs": gbs / NOMINAL_HBM_GBS,
                 "step_ms": ms32 / 20, "step_kv_gbs": b32 / (ms32 / 1e3) / 1e9,
