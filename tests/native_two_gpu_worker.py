@@ -92,10 +92,13 @@ def nccl(rank, world, key):
     _fill_shard(ref, coll, cfg, rank, world)
     coll.set_state(tok, LENS)
     ref.set_state(tok, LENS)
+    print("towers ready", flush=True)
     gc = native.CUDAGraph().capture(coll.decode_step)  # warm-up run = step 1, then captured with the collective inside
+    print("captured", gc.num_nodes, flush=True)
     ref.decode_step()
     for step in range(2):
         lx.synchronize()
+        print("step", step, "synchronised", flush=True)
         a, b_ = coll.last_logits.numpy().astype(np.float32), ref.last_logits.numpy().astype(np.float32)
         err = float(np.abs(a - b_).max() / np.abs(b_).max())
         assert err <= 2e-2, f"rank {rank} NCCL step {step}: logits differ {err:.3e}"
@@ -110,6 +113,11 @@ def nccl(rank, world, key):
 
 
 if __name__ == "__main__":
+    import faulthandler
+
+    # a rank that is stuck says where (the Python frame of the call that does not return) and ends by itself,
+    # before the parent's limit ends it without a word
+    faulthandler.dump_traceback_later(100, exit=True)
     phase, rank, world, key, out_dir = sys.argv[1], int(sys.argv[2]), int(sys.argv[3]), sys.argv[4], sys.argv[5]
     {"fused": fused, "nccl": nccl}[phase](rank, world, key)
     open(os.path.join(out_dir, f"native_{phase}_ok{rank}"), "w").close()
