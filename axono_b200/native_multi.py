@@ -135,6 +135,8 @@ class NcclGather:
         return self._out
 
     def close(self) -> None:
+        """Destroys the communicator.  Reset every graph that recorded `gather` first: NCCL's destroy waits
+        for graphs that hold the communicator's work, for good if one is still alive."""
         if self._comm:
             self.lx.synchronize()
             self.rdv.barrier()

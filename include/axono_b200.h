@@ -253,6 +253,8 @@ int axb200_gqa_decode_paged_cp(const void *q, void *out, const void *k_pages, co
  *   swap_leading_dims: dst (n1, n0, row) = src (n0, n1, row), rows of row_bytes (a multiple of 16,
  *     pointers 16-byte aligned) - turns the gathered (world, batch, heads x d) into the
  *     (batch, world, heads x d) rows the projection reads.
+ * Destroy a communicator only after every CUDA graph that recorded one of its all-gathers has been
+ * destroyed: ncclCommDestroy waits for them (a live graph makes the call block for good).
  * NCCL is opened by soname (libnccl.so.2) on first use.  No counterpart in the reference, whose
  * WITH_NCCL option is reserved and unused (CMakeLists.txt:78,91-92). */
 int axb200_nccl_unique_id(void *id128);

@@ -76,6 +76,8 @@ def fused(rank, world, key):
         assert all(t == toks[0] for t in toks), "ranks disagree on the next tokens"
         single.token_ids.copy_from(shard.token_ids)  # keep the two on the same trajectory
     assert lx.device_error_bits() == 0
+    if g is not None:
+        g.reset()
     shard.close()
     rdv.close()
     assert "torch" not in sys.modules
@@ -107,6 +109,7 @@ def nccl(rank, world, key):
         ref.decode_step()
     lx.synchronize()
     assert gc.num_nodes > 0 and lx.device_error_bits() == 0
+    gc.reset()  # ncclCommDestroy waits for every graph that recorded work of the communicator to be gone
     coll.close()
     rdv.close()
     assert "torch" not in sys.modules
