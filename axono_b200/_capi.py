@@ -60,6 +60,11 @@ SIGNATURES = {
     # q, k_new, v_new, out, k_pages, v_pages, block_table, seq_lens, pos, inv_freq | theta | rotate, mrope, h_sec,
     # w_sec, batch, hq, hkv, d, page_tokens, max_blocks, num_pages | max_seq_len | dtype | workspace, bytes, stream
     "axb200_decode_step_paged": (_i, [_vp] * 10 + [_f] + [_i] * 11 + [_i64, _i, _vp, _sz, _vp]),
+    # qkv, ld, q_norm_w, k_norm_w, eps, out, k_pages, v_pages, block_table, seq_lens, pos, inv_freq, theta, rotate,
+    # mrope, h_sec, w_sec, batch, hq, hkv, d, page_tokens, max_blocks, num_pages, max_seq_len, dtype, slot_delta,
+    # advance, workspace, bytes, peer_out, peer_flags, local_state, world, rank, hq_total, stream
+    "axb200_qkv_decode_step_paged": (_i, [_vp, _i64, _vp, _vp, _f] + [_vp] * 7 + [_f] + [_i] * 11 + [_i64] + [_i] * 3 +
+                                     [_vp, _sz, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "axb200_decode_step_host": (_i, [_vp] * 12 + [_vp, _vp, _f, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i64, _i,
                                           _vp, _sz, _vp]),
     "axb200_kv_arena_create": (_i, [_i, _i, _i, _i, _i, _i, _i, _i, _i, C.POINTER(_vp)]),

@@ -90,6 +90,15 @@ struct StepParams {
   const float *inv_freq_dev;  // (d / 2), or null: `table`
   int rotate, mrope, h_lim, w_lim;
   int stage_q;                // q lives in host memory: fetch it once per CTA through shared memory
+  // The step straight from a QKV projection's output (the text tower's layer): row b of qkv holds hq query
+  // heads, hkv key heads, hkv value heads of d elements, `ld` elements apart; q and k get a per-head RMS
+  // norm (weights of d elements, or null) before the rotation.  qkv == null: q / k_new / v_new as above.
+  const void *qkv;
+  long long ld;
+  const void *q_norm_w, *k_norm_w;
+  float eps;
+  int advance;                // 1: the launch adds the token's slot (first layer of a step); 0: the length
+                              // already counts it (later layers: the token goes to slot length - 1)
   float table[kStepHalfMax];  // theta^(-2i/d), from the host's powf
 };
 
@@ -725,12 +734,21 @@ gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
       const int cover = covered_tokens(p);
       len = len < 0 ? 0 : len;
       int add = 1;
-      if (len + 1 > cover) {  // no room for the token: nothing is appended, the old tokens are attended
-        atomicOr(&g_error_word, AXB200_ERR_CAPACITY);
-        len = min(len, cover);
-        add = 0;
+      if (!sp.advance) {  // a later layer of the step: the length already counts the token
+        if (len > cover || len == 0) {
+          atomicOr(&g_error_word, AXB200_ERR_CAPACITY);
+          len = min(len, cover);
+          add = 0;
+        }
+        s_plan[0] = len;
+      } else {
+        if (len + 1 > cover) {  // no room for the token: nothing is appended, the old tokens are attended
+          atomicOr(&g_error_word, AXB200_ERR_CAPACITY);
+          len = min(len, cover);
+          add = 0;
+        }
+        s_plan[0] = len + add;
       }
-      s_plan[0] = len + add;
       s_plan[1] = add;
     }
     __syncthreads();
@@ -749,12 +767,12 @@ gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
   // is looked at later, when it has long arrived - by `settle`, before the thread's every way out.
   unsigned int readers_before = 0;
   unsigned int *readers = nullptr;
-  if (kStep && threadIdx.x == 0) {
+  if (kStep && threadIdx.x == 0 && sp.advance) {  // (a launch that does not advance leaves the length alone)
     readers = g_step_readers + (size_t)p.arrival_region * kArrivalSlots + blockIdx.z;
     readers_before = atom_add_acq_rel_gpu(readers, 1u);
   }
   auto settle = [&]() {
-    if (kStep && threadIdx.x == 0 && readers_before + 1 == gridDim.x * gridDim.y) {
+    if (kStep && threadIdx.x == 0 && sp.advance && readers_before + 1 == gridDim.x * gridDim.y) {
       *readers = 0u;  // every CTA of the sequence has read the old length
       if (appended) sp.seq_lens[blockIdx.z] = w.L;
     }
@@ -808,7 +826,8 @@ gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
       qa[ks][3] = v1 && in1 ? *reinterpret_cast<const uint32_t *>(q1 + c + 8) : 0u;
     }
   };
-  if (!(kStep && sp.stage_q)) load_q(qh + ((size_t)b * p.hq + (size_t)hk * p.group + g) * p.d);
+  const bool staged = kStep && (sp.stage_q || sp.qkv != nullptr);  // q comes through shared memory
+  if (!staged) load_q(qh + ((size_t)b * p.hq + (size_t)hk * p.group + g) * p.d);
 
   // ---- kStep, first half: what has to come from memory is asked for, the angles are worked out ----
   constexpr int kHalf = kD / 2, kPairs = kHalf / 32;  // rotary pairs per lane of the warp that appends
@@ -817,9 +836,12 @@ gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
   __half k_lo[kPairs], k_hi[kPairs], v_lo[kPairs], v_hi[kPairs];
   int new_page = 0;
   if constexpr (kStep) {
+    const __half *qkv_row = reinterpret_cast<const __half *>(sp.qkv) + (size_t)b * sp.ld;
     if (patch) {  // the token's rows and its page id on their way while the angles are worked out
-      const __half *kn = reinterpret_cast<const __half *>(sp.k_new) + ((size_t)b * p.hkv + hk) * kD;
-      const __half *vn = reinterpret_cast<const __half *>(sp.v_new) + ((size_t)b * p.hkv + hk) * kD;
+      const __half *kn = sp.qkv ? qkv_row + (size_t)(p.hq + hk) * kD
+                                : reinterpret_cast<const __half *>(sp.k_new) + ((size_t)b * p.hkv + hk) * kD;
+      const __half *vn = sp.qkv ? qkv_row + (size_t)(p.hq + p.hkv + hk) * kD
+                                : reinterpret_cast<const __half *>(sp.v_new) + ((size_t)b * p.hkv + hk) * kD;
 #pragma unroll
       for (int j = 0; j < kPairs; ++j) {
         const int i = lane + 32 * j;
@@ -835,8 +857,9 @@ gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
     // the angles, so the two overlap.
     uint4 q_piece[2];
     const int q_pieces = p.group * (kD / 8);  // at most 16 heads x 16 pieces: two per thread
-    if (sp.stage_q) {
-      const uint4 *src = reinterpret_cast<const uint4 *>(qh + ((size_t)b * p.hq + (size_t)hk * p.group) * kD);
+    if (staged) {
+      const uint4 *src = reinterpret_cast<const uint4 *>(sp.qkv ? qkv_row + (size_t)hk * p.group * kD
+                                                                : qh + ((size_t)b * p.hq + (size_t)hk * p.group) * kD);
 #pragma unroll
       for (int u = 0; u < 2; ++u)
         if ((int)threadIdx.x + u * kConsumerThreads < q_pieces) q_piece[u] = src[threadIdx.x + u * kConsumerThreads];
@@ -857,23 +880,65 @@ gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
       const float posv = sp.mrope ? mrope_pair_position(i, pt, ph, pw, sp.h_lim, sp.w_lim) : pt;
       sincosf(posv * f, &s_rope[kStepHalfMax + i], &s_rope[i]);
     }
-    if (sp.stage_q) {
+    if (staged) {
 #pragma unroll
       for (int u = 0; u < 2; ++u)
         if ((int)threadIdx.x + u * kConsumerThreads < q_pieces)
           reinterpret_cast<uint4 *>(s_q)[threadIdx.x + u * kConsumerThreads] = q_piece[u];
     }
+    if (sp.qkv) {
+      // The per-head RMS norm and the rotation of q where the rows lie, one warp per head, lane i and
+      // i + 32 of each half as in the kernel that does this on its own (qkv_norm_rope_append_kernel): the
+      // same sums in the same order, hence the same bits.  The rows go back as fp16, as that kernel's q_out.
+      named_bar_sync(1, kConsumerThreads);  // rows and angles are in shared memory
+      for (int r = warp; r < p.group; r += kConsumerWarps) {
+        __half *row = s_q + r * kD;
+        float a[kPairs], bb[kPairs], ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < kPairs; ++j) {
+          const int i = lane + 32 * j;
+          a[j] = __half2float(row[i]);
+          bb[j] = __half2float(row[i + kHalf]);
+          ss = fmaf(a[j], a[j], ss);
+          ss = fmaf(bb[j], bb[j], ss);
+        }
+        const __half *wq = reinterpret_cast<const __half *>(sp.q_norm_w);
+        float inv = 1.f;
+        if (wq) {
+#pragma unroll
+          for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+          inv = 1.0f / sqrtf(ss / (float)kD + sp.eps);
+        }
+#pragma unroll
+        for (int j = 0; j < kPairs; ++j) {
+          const int i = lane + 32 * j;
+          float x0 = a[j], x1 = bb[j];
+          if (wq) {
+            x0 = x0 * inv * __half2float(wq[i]);
+            x1 = x1 * inv * __half2float(wq[i + kHalf]);
+          }
+          if (sp.rotate) {
+            const float sn = s_rope[kStepHalfMax + i], cs = s_rope[i];
+            const float r0 = rope_lo(x0, x1, cs, sn), r1 = rope_hi(x0, x1, cs, sn);
+            x0 = r0;
+            x1 = r1;
+          }
+          row[i] = __float2half_rn(x0);
+          row[i + kHalf] = __float2half_rn(x1);
+        }
+      }
+    }
   }
 
-  if (kStep && sp.stage_q) {
+  if (staged) {
     named_bar_sync(1, kConsumerThreads);  // the staged rows (and the angles) are there
     load_q(s_q + g * kD);
   }
 
   // ---- kStep, second half: rotate q in registers, rotate and store the new token's rows ----
   if constexpr (kStep) {
-    if (!sp.stage_q) named_bar_sync(1, kConsumerThreads);  // the angles are there (q's loads flew meanwhile)
-    if (sp.rotate) {
+    if (!staged) named_bar_sync(1, kConsumerThreads);  // the angles are there (q's loads flew meanwhile)
+    if (sp.rotate && !sp.qkv) {
       // pair (c, c + kHalf) sits in k-steps ks and ks + kKSteps / 2 of the same thread
 #pragma unroll
       for (int ks = 0; ks < kKSteps / 2; ++ks) {
@@ -891,14 +956,38 @@ gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
       }
     }
     if (patch) {
-      if (sp.rotate) {
+      if (sp.rotate || (sp.qkv && sp.k_norm_w)) {
+        float a[kPairs], bb[kPairs], ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < kPairs; ++j) {
+          a[j] = __half2float(k_lo[j]);
+          bb[j] = __half2float(k_hi[j]);
+          ss = fmaf(a[j], a[j], ss);
+          ss = fmaf(bb[j], bb[j], ss);
+        }
+        const __half *wk = sp.qkv ? reinterpret_cast<const __half *>(sp.k_norm_w) : nullptr;
+        float inv = 1.f;
+        if (wk) {  // the key's RMS norm, summed as qkv_norm_rope_append_kernel sums it
+#pragma unroll
+          for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+          inv = 1.0f / sqrtf(ss / (float)kD + sp.eps);
+        }
 #pragma unroll
         for (int j = 0; j < kPairs; ++j) {
           const int i = lane + 32 * j;
-          const float a = __half2float(k_lo[j]), bb = __half2float(k_hi[j]);
-          const float c = s_rope[i], sn = s_rope[kStepHalfMax + i];
-          k_lo[j] = __float2half_rn(rope_lo(a, bb, c, sn));
-          k_hi[j] = __float2half_rn(rope_hi(a, bb, c, sn));
+          float x0 = a[j], x1 = bb[j];
+          if (wk) {
+            x0 = x0 * inv * __half2float(wk[i]);
+            x1 = x1 * inv * __half2float(wk[i + kHalf]);
+          }
+          if (sp.rotate) {
+            const float c = s_rope[i], sn = s_rope[kStepHalfMax + i];
+            const float r0 = rope_lo(x0, x1, c, sn), r1 = rope_hi(x0, x1, c, sn);
+            x0 = r0;
+            x1 = r1;
+          }
+          k_lo[j] = __float2half_rn(x0);
+          k_hi[j] = __float2half_rn(x1);
         }
       }
       if (new_page >= 0 && new_page < p.num_pages) {  // the rows in the cache, for the steps to come
@@ -2078,6 +2167,7 @@ int decode_step_try_fused(const void *q, const void *k_new, const void *v_new, v
   sp.mrope = mrope;
   sp.h_lim = h_sec * 3;
   sp.w_lim = w_sec * 3;
+  sp.advance = 1;
   if (rotate && !inv_freq) rope_inv_freq_host(theta, d, sp.table);
   {
     cudaPointerAttributes attr;
@@ -2095,6 +2185,84 @@ int decode_step_try_fused(const void *q, const void *k_new, const void *v_new, v
 }  // namespace axb
 
 extern "C" {
+
+int axb200_qkv_decode_step_paged(const void *qkv, int64_t ld, const void *q_norm_w, const void *k_norm_w, float eps,
+                                 void *out, void *k_pages, void *v_pages, const int32_t *block_table,
+                                 int32_t *seq_lens, const int64_t *pos, const float *inv_freq, float theta,
+                                 int rotate, int mrope, int h_sec, int w_sec, int batch, int hq, int hkv, int d,
+                                 int page_tokens, int max_blocks, int num_pages, int64_t max_seq_len, int dtype,
+                                 int slot_delta, int advance, void *workspace, size_t workspace_bytes,
+                                 void *const *peer_out, void *const *peer_flags, void *local_state, int world,
+                                 int rank, int hq_total, void *stream) {
+  using namespace axb;
+  const size_t es = dtype_size(dtype);
+  if (es == 0) return AXB200_UNSUPPORTED_TYPE;
+  if (!qkv || !k_pages || !v_pages || !block_table || !seq_lens || !workspace) return AXB200_INVALID_PTR;
+  if (batch <= 0 || hq <= 0 || hkv <= 0 || d <= 0 || max_seq_len <= 0 || ld < (int64_t)(hq + 2 * hkv) * d)
+    return AXB200_INVALID_ARGUMENT;
+  if (!((slot_delta == 0 && advance == 1) || (slot_delta == -1 && advance == 0))) return AXB200_INVALID_ARGUMENT;
+  if (rotate && mrope && !inv_freq) return AXB200_INVALID_PTR;
+  if (workspace_bytes < axb200_decode_step_workspace_bytes(batch, hq, hkv, d, max_seq_len, dtype))
+    return AXB200_INVALID_ARGUMENT;
+  GatherParams g{};
+  const bool peers = world > 0;
+  if (peers) {
+    if (!peer_out || !peer_flags || !local_state) return AXB200_INVALID_PTR;
+    if (world > kMaxPeers || rank < 0 || rank >= world || hq_total != hq * world) return AXB200_INVALID_ARGUMENT;
+    for (int r = 0; r < world; ++r) {
+      if (!peer_out[r] || !peer_flags[r]) return AXB200_INVALID_PTR;
+      g.peer_out[r] = peer_out[r];
+      g.peer_flags[r] = static_cast<unsigned int *>(peer_flags[r]);
+    }
+    g.local_state = static_cast<unsigned int *>(local_state);
+    g.world = world;
+    g.rank = rank;
+    g.hq_total = hq_total;
+  } else if (!out) {
+    return AXB200_INVALID_PTR;
+  }
+  const size_t attn_bytes = (axb200_gqa_workspace_bytes(batch, hq, hkv, d, max_seq_len, dtype) + 255) & ~size_t(255);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  bool fused;
+  {
+    std::lock_guard<std::mutex> lock(g_settings_mu);
+    fused = g_step_fused;
+  }
+  fused = fused && dtype == AXB200_FLOAT16 && (d == 64 || d == 128) && batch <= kArrivalSlots && ld % 8 == 0 &&
+          aligned16(qkv);
+  if (fused) {
+    StepParams sp{};
+    sp.k_pages = k_pages;
+    sp.v_pages = v_pages;
+    sp.seq_lens = seq_lens;
+    sp.pos = pos;
+    sp.inv_freq_dev = inv_freq;
+    sp.rotate = rotate;
+    sp.mrope = mrope;
+    sp.h_lim = h_sec * 3;
+    sp.w_lim = w_sec * 3;
+    sp.qkv = qkv;
+    sp.ld = ld;
+    sp.q_norm_w = q_norm_w;
+    sp.k_norm_w = k_norm_w;
+    sp.eps = eps;
+    sp.advance = advance;
+    if (rotate && !inv_freq) rope_inv_freq_host(theta, d, sp.table);
+    const int rc = decode_impl(true, qkv, peers ? nullptr : out, k_pages, v_pages, block_table, seq_lens, 0, batch, hq,
+                               hkv, d, page_tokens, max_blocks, num_pages, max_seq_len, dtype, workspace, attn_bytes,
+                               st, peers ? &g : nullptr, 0, 0, 0, &sp);
+    if (rc != kStepNotFused) return rc;
+  }
+  // two launches: the per-head norm + rotation + append kernel leaves q in the workspace, then attention
+  void *q_rot = static_cast<uint8_t *>(workspace) + attn_bytes;
+  int rc = axb200_qkv_norm_rope_append(qkv, ld, q_norm_w, k_norm_w, eps, q_rot, k_pages, v_pages, block_table, seq_lens,
+                                       pos, inv_freq, theta, rotate, mrope, h_sec, w_sec, batch, hq, hkv, d, page_tokens,
+                                       max_blocks, num_pages, dtype, slot_delta, advance, stream);
+  if (rc != AXB200_OK) return rc;
+  return decode_impl(true, q_rot, peers ? nullptr : out, k_pages, v_pages, block_table, seq_lens, 0, batch, hq, hkv, d,
+                     page_tokens, max_blocks, num_pages, max_seq_len, dtype, workspace, attn_bytes, st,
+                     peers ? &g : nullptr);
+}
 
 int axb200_set_step_fused(int on) {
   std::lock_guard<std::mutex> lock(axb::g_settings_mu);

@@ -148,9 +148,12 @@ class Scratch:
     """The decode calls' workspace as one tensor that lives as long as its user (a graph that was
     captured with it keeps its address)."""
 
-    def __init__(self, batch, hq, hkv, d, max_seq_len, dtype, device: str = "cuda"):
+    def __init__(self, batch, hq, hkv, d, max_seq_len, dtype, device: str = "cuda", step: bool = False):
         lx = native.load()
-        n = int(lx.gqa_workspace_bytes(batch, hq, hkv, d, int(max_seq_len), dtype))
+        if step:  # the one-operator step: the partials plus room for a rotated q
+            n = int(_capi.lib().axb200_decode_step_workspace_bytes(batch, hq, hkv, d, int(max_seq_len), _dtype_code(lx, dtype)))
+        else:
+            n = int(lx.gqa_workspace_bytes(batch, hq, hkv, d, int(max_seq_len), dtype))
         self.tensor = lx.Tensor(lx.DataType.INT8, [max(n, 256)], device)
 
     @property
@@ -181,6 +184,39 @@ def attend_gather(q, arena, layer: int, max_seq_len: int, bufs: PeerBuffers, slo
         int(max_seq_len), _dtype_code(lx, q.dtype), scratch.ptr, scratch.nbytes, bufs.out_ptrs(slot), bufs.flag_ptrs,
         bufs.state_ptr, bufs.world, bufs.rank, bufs.hq_total, lx.current_stream()), "gqa_decode_paged_gather")
     return bufs.tensor(slot)
+
+
+def qkv_decode_step(qkv, hq: int, arena, layer: int, max_seq_len: int, scratch: Scratch, q_norm_w=None, k_norm_w=None,
+                    eps: float = 1e-6, inv_freq=None, theta: float = 1e6, rotate: bool = True, mrope_section=None,
+                    slot_delta: int = 0, advance: bool = True, out=None, bufs: PeerBuffers = None, slot: int = 0):
+    """The tower layer's decode step as one operator, straight from the QKV projection's output qkv (batch, ld):
+    per-head RMS norm of q and k, rotation, append, attention - one launch where the library can
+    (`axb200_qkv_decode_step_paged`).  Without `bufs` the result goes to `out` (batch, hq, d), which is
+    returned; with `bufs` (heads sharded over the ranks) the rows go into every rank's gathered buffer `slot`
+    and this rank's buffer (batch, hq_total, d) is returned.  `scratch` must be a `Scratch(..., step=True)`."""
+    lx = native.load()
+    g, (kp, vp, bt, sl) = _arena_args(lx, arena, layer)
+    batch, ld = qkv.shape
+    d = g["d"]
+    mrope = mrope_section is not None
+    h_sec, w_sec = (int(mrope_section[1]), int(mrope_section[2])) if mrope else (0, 0)
+    if bufs is not None:
+        if bufs.kind != "heads" or bufs.batch != batch or bufs.d != d or bufs.hq_total != hq * bufs.world:
+            raise RuntimeError("qkv_decode_step: buffers do not match the call")
+        peers = (bufs.out_ptrs(slot), bufs.flag_ptrs, bufs.state_ptr, bufs.world, bufs.rank, bufs.hq_total)
+        out_ptr = None
+    else:
+        if out is None:
+            out = lx.Tensor(qkv.dtype, [batch, hq, d], qkv.device)
+        peers = (None, None, None, 0, 0, hq)
+        out_ptr = out.data_ptr
+    _capi.check(_capi.lib().axb200_qkv_decode_step_paged(
+        qkv.data_ptr, int(ld), q_norm_w.data_ptr if q_norm_w is not None else None,
+        k_norm_w.data_ptr if k_norm_w is not None else None, float(eps), out_ptr, kp, vp, bt, sl, None,
+        inv_freq.data_ptr if inv_freq is not None else None, float(theta), int(rotate), int(mrope), h_sec, w_sec, batch, hq,
+        g["hkv"], d, g["page_tokens"], g["max_blocks"], g["num_pages"], int(max_seq_len), _dtype_code(lx, qkv.dtype),
+        int(slot_delta), int(advance), scratch.ptr, scratch.nbytes, *peers, lx.current_stream()), "qkv_decode_step_paged")
+    return bufs.tensor(slot) if bufs is not None else out
 
 
 def attend_context_parallel(q, out, arena, layer: int, max_seq_len: int, bufs: PeerBuffers, slot: int, scratch: Scratch):

@@ -24,7 +24,7 @@ class NativeTextTower:
     next token ids are written back into `token_ids` on the device."""
 
     def __init__(self, cfg: TextTowerConfig, batch: int, max_seq_len: int, seed: int = 0, page_tokens: int = 64,
-                 weights=None, device: str = "cuda", rdv=None, gather: str = "fused"):
+                 weights=None, device: str = "cuda", rdv=None, gather: str = "fused", fused_step: bool = True):
         lx = native.load()
         self.lx, self.cfg, self.batch, self.max_seq_len, self.device = lx, cfg, batch, max_seq_len, device
         self.world = rdv.world if rdv is not None else 1
@@ -96,7 +96,21 @@ class NativeTextTower:
             # one gathered buffer per layer (at least two): successive calls never share a buffer
             self.bufs = PeerBuffers(rdv, batch, cfg.n_q_heads, d, lx.DataType.FLOAT16, slots=max(2, cfg.n_layers),
                                     device=device)
-            self.scratch = Scratch(batch, self.local_q, self.local_kv, d, max_seq_len, lx.DataType.FLOAT16, device)
+            self.scratch = Scratch(batch, self.local_q, self.local_kv, d, max_seq_len, lx.DataType.FLOAT16, device,
+                                   step=True)
+        # fused_step: a layer's norm + rope + append + attention (+ gather) is the one operator qkv_decode_step
+        # (one launch); without it, qkv_norm_rope_append followed by the attention call.  The NCCL form keeps
+        # the two calls: its gather is a library call after the attention kernel either way.
+        self.fused_step = fused_step and self.nccl is None
+        if self.fused_step and self.scratch is None:
+            from .native_multi import Scratch
+
+            self.scratch = Scratch(batch, self.local_q, self.local_kv, d, max_seq_len, lx.DataType.FLOAT16, device,
+                                   step=True)
+        # the step operator's output when it is not a gathered buffer: one buffer for all layers (a layer's
+        # projection has read it before the next layer's attention writes it)
+        self.attn_out = lx.Tensor(lx.DataType.FLOAT16, [batch, self.local_q, d], device) if self.fused_step and \
+            self.bufs is None else None
 
     def set_state(self, token_ids, lens) -> None:
         """Starts decoding at cache lengths `lens` (one per row); positions are the lengths."""
@@ -113,6 +127,22 @@ class NativeTextTower:
             else:  # previous layer's h + mlp folded into this layer's input norm
                 h, xn = lx.add_rms_norm(mlp_out, h, lw["input_ln"], cfg.eps)
             qkv = lx.linear_nobias(xn, lw["qkv"])
+            if self.fused_step:
+                from .native_multi import qkv_decode_step
+
+                attn = qkv_decode_step(
+                    qkv, self.local_q, self.arena, li, self.max_seq_len, self.scratch,
+                    lw["q_norm"] if cfg.qk_norm else None, lw["k_norm"] if cfg.qk_norm else None, cfg.eps,
+                    inv_freq=self.inv_freq, theta=cfg.rope_theta,
+                    mrope_section=list(cfg.mrope_section) if cfg.use_mrope else None,
+                    slot_delta=0 if li == 0 else -1, advance=li == 0, out=self.attn_out, bufs=self.bufs,
+                    slot=li % self.bufs.slots if self.bufs is not None else 0)
+                attn = lx.Tensor.from_device_ptr(attn.data_ptr, attn.dtype, [self.batch, cfg.n_q_heads * cfg.head_dim],
+                                                 self.device)
+                h, xn2 = lx.add_rms_norm(lx.linear_nobias(attn, lw["o"]), h, lw["post_ln"], cfg.eps)
+                act = lx.silu_mul_rows(lx.linear_nobias(xn2, lw["gate_up"]), cfg.intermediate)
+                mlp_out = lx.linear_nobias(act, lw["down"])
+                continue
             q = lx.qkv_norm_rope_append(
                 self.arena, li, qkv, self.local_q, lw["q_norm"] if cfg.qk_norm else None,
                 lw["k_norm"] if cfg.qk_norm else None, cfg.eps, inv_freq=self.inv_freq, theta=cfg.rope_theta,

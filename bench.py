@@ -474,7 +474,8 @@ def tower_figures(args, lx, rdv, device, sampler=None, gather="fused"):
     cfg = TextTowerConfig()
     steps = max(3, min(args.steps, 20))
     warm = max(3, min(args.warmup, 5))
-    tower = NativeTextTower(cfg, B, L + 2 * (steps + warm) + 72, seed=5, device=device, rdv=rdv, gather=gather)
+    tower = NativeTextTower(cfg, B, L + 2 * (steps + warm) + 72, seed=5, device=device, rdv=rdv, gather=gather,
+                            fused_step=not args.two_kernel_step)
     tower.arena.fill_normal(77 + rdv.rank, 0.5)
     lens = [L] * B
     tower.set_state(np.arange(B) % cfg.vocab, lens)

@@ -352,6 +352,24 @@ int axb200_decode_step_paged(const void *q, const void *k_new, const void *v_new
                              int page_tokens, int max_blocks, int num_pages, int64_t max_seq_len,
                              int dtype, void *workspace, size_t workspace_bytes, void *stream);
 
+/* The same one-operator step taken straight from the QKV projection's output, for the text tower's layer
+ * (axono/python/examples/vlm/qwen3vl/model.py:353-366: reshape, rms_norm(q), rms_norm(k), rope on both,
+ * cache.update, gqa_decode_attention): axb200_qkv_norm_rope_append followed by the paged decode attention,
+ * same arguments, same results bit for bit - one launch for fp16 with head_dim 64 / 128, the two kernels
+ * otherwise (the normed, rotated q then goes to the workspace).  slot_delta / advance: (0, 1) for the first
+ * layer of a step, (-1, 0) for the later ones, as in axb200_kv_append_rope.  world == 0: the result goes to
+ * out (batch,hq,d).  world > 0: heads are sharded over `world` ranks and the rows go into every rank's
+ * gathered buffer with the flag exchange of axb200_gqa_decode_paged_gather (same peer arguments; out unused).
+ * workspace: at least axb200_decode_step_workspace_bytes. */
+int axb200_qkv_decode_step_paged(const void *qkv, int64_t ld, const void *q_norm_w, const void *k_norm_w, float eps,
+                                 void *out, void *k_pages, void *v_pages, const int32_t *block_table,
+                                 int32_t *seq_lens, const int64_t *pos, const float *inv_freq, float theta,
+                                 int rotate, int mrope, int h_sec, int w_sec, int batch, int hq, int hkv, int d,
+                                 int page_tokens, int max_blocks, int num_pages, int64_t max_seq_len, int dtype,
+                                 int slot_delta, int advance, void *workspace, size_t workspace_bytes,
+                                 void *const *peer_out, void *const *peer_flags, void *local_state, int world,
+                                 int rank, int hq_total, void *stream);
+
 /* One decode step with HOST activations: copies q (batch,hq,d), k_new, v_new (batch,hkv,d) from host
  * (pinned memory for asynchronous copies) into the device staging buffers q_dev / k_new_dev /
  * v_new_dev, runs axb200_kv_append_rope (slot_delta 0, advance 1) and axb200_gqa_decode_paged, copies

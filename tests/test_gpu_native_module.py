@@ -478,3 +478,86 @@ def test_framework_free_services(lx, chk):
     assert np.array_equal(oh, want)
     assert np.array_equal(arena.seq_lens(), lens + 1)
     assert lx.device_error_bits() == 0
+
+
+def test_decode_step_operator(lx, chk):
+    """`decode_step_paged` on the native runtime: one launch, the bits of kv_append_rope + attention, q left
+    as it was, lengths advanced - over several steps on scattered pages."""
+    f16 = lx.DataType.FLOAT16
+    hq, hkv, d, page, cap, B = 16, 8, 128, 64, 2200, 3
+    blocks = (cap + page - 1) // page
+    arenas = []
+    for _ in range(2):
+        a = lx.KVArena(1, B * blocks, hkv, page, d, f16, B, blocks)
+        a.shuffle_free(9)
+        for _ in range(B):
+            a.alloc_seq(cap)
+        a.sync()
+        a.fill_normal(4, 0.5)
+        a.set_seq_lens(np.asarray([2100, 63, 0], np.int32))
+        arenas.append(a)
+    one, two = arenas
+    assert lx.decode_step_launches(B, hq, hkv, d, cap, f16) == 1
+    rng = np.random.default_rng(2)
+    for step in range(3):
+        q = rng.standard_normal((B, hq, d)).astype(np.float16)
+        kn = (0.5 * rng.standard_normal((B, hkv, d))).astype(np.float16)
+        vn = (0.5 * rng.standard_normal((B, hkv, d))).astype(np.float16)
+        qd = dev(lx, q)
+        got = lx.decode_step_paged(qd, dev(lx, kn), dev(lx, vn), one, 0, cap, theta=1e6)
+        assert np.array_equal(qd.numpy(), q)  # only read
+        q2 = dev(lx, q)
+        lx.kv_append_rope(two, 0, q2, dev(lx, kn), dev(lx, vn), theta=1e6)
+        want = lx.gqa_decode_attention_paged(q2, two, 0, cap)
+        assert np.array_equal(got.numpy(), want.numpy()), f"step {step}"
+        assert np.array_equal(one.seq_lens(), two.seq_lens())
+    for b in range(B):
+        n = int(one.seq_lens()[b])
+        k1, v1 = one.gather(0, b, n)
+        k2, v2 = two.gather(0, b, n)
+        assert np.array_equal(k1, k2) and np.array_equal(v1, v2)
+    k, v = one.gather(0, 1, 66)
+    ref = chk.gqa_decode(q2.numpy()[1:2].astype(np.float32), k.astype(np.float32), v.astype(np.float32))
+    assert oracle.rel_err(got.numpy()[1:2].astype(np.float32), ref) <= 2e-3
+    assert lx.device_error_bits() == 0
+
+
+@pytest.mark.parametrize("use_mrope,qk_norm,heads", [(True, True, (4, 2)), (False, False, (16, 8)), (True, False, (8, 1))])
+def test_native_tower_one_launch_layer_step_equals_the_two_kernels(use_mrope, qk_norm, heads):
+    """The tower with each layer's norm + rope + append + attention as the one operator (one launch) against
+    the same tower running qkv_norm_rope_append and the attention call: identical logits, tokens and pages,
+    eagerly and as a captured graph, with lengths on tile and page edges."""
+    from axono_b200.native_tower import NativeTextTower
+    from axono_b200.tower_config import TextTowerConfig
+
+    cfg = TextTowerConfig(hidden=256, intermediate=512, n_q_heads=heads[0], n_kv_heads=heads[1], head_dim=128, vocab=1000,
+                          n_layers=3, use_mrope=use_mrope, qk_norm=qk_norm)
+    batch, lens = 4, [70, 63, 127, 1200]
+    one = NativeTextTower(cfg, batch, 1408, seed=5)
+    two = NativeTextTower(cfg, batch, 1408, seed=5, weights=one.host_weights, fused_step=False)
+    assert one.fused_step and not two.fused_step
+    for t in (one, two):
+        t.arena.fill_normal(21, 0.5)
+        t.set_state([7, 8, 9, 10], lens)
+    for step in range(3):
+        a, b = one.decode_step().numpy(), two.decode_step().numpy()
+        assert np.array_equal(one.last_logits.numpy(), two.last_logits.numpy()), f"step {step}"
+        assert np.array_equal(a, b)
+    g = native.CUDAGraph().capture(one.decode_step)  # its warm-up run is a real step
+    two.decode_step()
+    for step in range(3):
+        g.replay()
+        two.decode_step()
+        assert np.array_equal(one.last_logits.numpy(), two.last_logits.numpy()), f"replay {step}"
+    assert list(one.arena.seq_lens()) == list(two.arena.seq_lens()) == [n + 7 for n in lens]
+    for li in range(cfg.n_layers):
+        for bi in range(batch):
+            k1, v1 = one.arena.gather(li, bi, lens[bi] + 7)
+            k2, v2 = two.arena.gather(li, bi, lens[bi] + 7)
+            assert np.array_equal(k1, k2) and np.array_equal(v1, v2)
+    lx = native.load()
+    assert lx.device_error_bits() == 0
+    g2 = native.CUDAGraph().capture(two.decode_step)
+    assert g.num_nodes == g2.num_nodes - cfg.n_layers  # one launch less per layer: the operator really is one launch
+    g.reset()
+    g2.reset()
