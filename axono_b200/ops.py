@@ -270,6 +270,45 @@ def qkv_norm_rope_append(qkv, n_q_heads, q_norm_weight, k_norm_weight, eps, k_pa
     return q_out
 
 
+def qkv_decode_step_paged(qkv, n_q_heads, q_norm_weight, k_norm_weight, eps, k_pages, v_pages, block_table, seq_lens,
+                          max_seq_len, out=None, pos=None, inv_freq=None, theta=10000.0, mrope_section=None, rotate=True,
+                          advance=True, slot_delta=0, gather=None):
+    """`qkv_norm_rope_append` followed by `gqa_decode_attention_paged` as one operator (one launch for fp16
+    with head_dim 64 / 128): the tower layer's step straight from the QKV projection output qkv
+    (batch, (hq + 2*hkv) * d), rows may be strided.  Returns the attention output (batch, hq, d), or with
+    gather=(PeerGather, slot) this rank's gathered (batch, hq_total, d)."""
+    op = "qkv_decode_step_paged"
+    dt = _dt(qkv, op)
+    if qkv.dim() != 2 or qkv.stride(1) != 1:
+        _capi.check(4, op)
+    num_pages, hkv, page_tokens, d = k_pages.shape
+    batch = qkv.shape[0]
+    if qkv.shape[1] != (n_q_heads + 2 * hkv) * d:
+        _capi.check(4, op)
+    for w in (q_norm_weight, k_norm_weight):
+        if w is not None and (w.dtype != qkv.dtype or tuple(w.shape) != (d,) or not w.is_contiguous()):
+            _capi.check(4, op)
+    mrope = mrope_section is not None
+    h_sec, w_sec = (mrope_section[1], mrope_section[2]) if mrope else (0, 0)
+    lib = _capi.lib()
+    ws = workspace(qkv.device, lib.axb200_decode_step_workspace_bytes(batch, n_q_heads, hkv, d, int(max_seq_len), dt))
+    if gather is not None:
+        pg, slot = gather
+        if pg.batch != batch or pg.d != d or pg.hq_total != n_q_heads * pg.world or pg.dtype != qkv.dtype:
+            _capi.check(4, op)
+        peers, out_ptr = (pg.out_ptrs(slot), pg.flag_ptrs, pg.state_ptr, pg.world, pg.rank, pg.hq_total), None
+    else:
+        if out is None:
+            out = torch.empty((batch, n_q_heads, d), dtype=qkv.dtype, device=qkv.device)
+        peers, out_ptr = (None, None, None, 0, 0, n_q_heads), out.data_ptr()
+    _call(lib.axb200_qkv_decode_step_paged(
+        qkv.data_ptr(), qkv.stride(0), _ptr(q_norm_weight), _ptr(k_norm_weight), float(eps), out_ptr, k_pages.data_ptr(),
+        v_pages.data_ptr(), block_table.data_ptr(), seq_lens.data_ptr(), _ptr(pos), _ptr(inv_freq), float(theta),
+        int(rotate), int(mrope), h_sec, w_sec, batch, n_q_heads, hkv, d, page_tokens, block_table.shape[1], num_pages,
+        int(max_seq_len), dt, int(slot_delta), int(advance), ws.data_ptr(), ws.numel(), *peers, _stream(qkv)), op)
+    return pg.tensor(slot) if gather is not None else out
+
+
 def silu_mul_rows(gate_up, n: int):
     """silu(gate) * up for gate = gate_up[:, :n], up = gate_up[:, n:2n] (one fused gate|up projection
     output, rows may be strided) -> (rows, n)."""

@@ -182,3 +182,43 @@ def test_step_captured_in_a_graph_follows_the_growing_cache(lib):
         assert torch.equal(one.seq_lens, two.seq_lens)
         assert _same_bytes(out, want)
     assert _same_bytes(one.k_pages[0], two.k_pages[0])
+
+
+@pytest.mark.parametrize("dtype,hq,hkv,d,launches", [(torch.float16, 16, 8, 128, 1), (torch.float16, 8, 2, 64, 1),
+                                                     (torch.float16, 6, 2, 80, 2), (torch.float32, 16, 8, 128, 2)])
+@pytest.mark.parametrize("norms,mrope", [(True, True), (False, False)])
+def test_step_from_the_qkv_projection_output(lib, dtype, hq, hkv, d, launches, norms, mrope):
+    """`axb200_qkv_decode_step_paged` (per-head norms + rope + append + attention from one QKV row) against
+    qkv_norm_rope_append followed by the attention call: bit for bit, as the first layer of a step (slot =
+    length, the length advances) and as a later one (slot = length - 1, it does not), with strided rows."""
+    from axono_b200 import _capi, ops
+
+    lens = [0, 63, 64, 127, 300, 2100]
+    one, two = _two_caches(dtype, lens, hkv, d, seed=31, capacity=2176)
+    B = len(lens)
+    code = _capi.FLOAT16 if dtype == torch.float16 else _capi.FLOAT32
+    assert lib.axb200_decode_step_launches(B, hq, hkv, d, one.max_seq_len, code) == launches
+    rng = np.random.default_rng(32)
+    width = (hq + 2 * hkv) * d
+    wq = dev((1 + 0.1 * rng.standard_normal(d)).astype(np.float32), dtype) if norms else None
+    wk = dev((1 + 0.1 * rng.standard_normal(d)).astype(np.float32), dtype) if norms else None
+    kw = {"theta": 1e6}
+    if mrope:
+        kw = {"inv_freq": dev((1e6 ** (-np.arange(d // 2, dtype=np.float32) * 2 / d)).astype(np.float32)),
+              "mrope_section": (d // 2 - 2 * (d // 6), d // 6, d // 6)}
+    for step in range(2):
+        for advance, slot_delta in ((True, 0), (False, -1)):  # first layer, then a later layer, of the same step
+            wide = dev(rng.standard_normal((B, width + 64)).astype(np.float32), dtype)
+            qkv = wide[:, :width]  # rows 64 elements apart from dense
+            bound = min(one.max_seq_len, max(lens) + step + 1)
+            got = ops.qkv_decode_step_paged(qkv, hq, wq, wk, 1e-6, one.k_pages[0], one.v_pages[0], one.block_table,
+                                            one.seq_lens, bound, advance=advance, slot_delta=slot_delta, **kw)
+            q2 = ops.qkv_norm_rope_append(qkv, hq, wq, wk, 1e-6, two.k_pages[0], two.v_pages[0], two.block_table,
+                                          two.seq_lens, advance=advance, slot_delta=slot_delta, **kw)
+            want = ops.gqa_decode_attention_paged(q2, two.k_pages[0], two.v_pages[0], two.block_table, two.seq_lens, bound)
+            torch.cuda.synchronize()
+            assert ops.last_error() == 0
+            assert torch.equal(one.seq_lens, two.seq_lens)
+            assert _same_bytes(one.k_pages[0], two.k_pages[0]) and _same_bytes(one.v_pages[0], two.v_pages[0])
+            assert _same_bytes(got, want), f"step {step}, advance {advance}"
+    assert one.seq_lens.tolist() == [n + 2 for n in lens]
