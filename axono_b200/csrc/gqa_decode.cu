@@ -718,6 +718,9 @@ gqa_split_f16_kernel(const __grid_constant__ CUtensorMap tmK,
     tma_prefetch_descriptor(&tmV);
   }
   grid_dependency_wait();  // nothing above reads what the kernel before this one writes
+  // A step kernel lets the next step's kernel be scheduled behind it: that kernel's CTAs take the slots this
+  // one's leave, set up their barriers and descriptors, and wait at the line above until this grid is done.
+  if (kStep) grid_dependency_launch();
   if (warp == kConsumerWarps) {
     if (kPaged && !p.balanced) {
       spec_start = blockIdx.x * p.chunk_tokens;

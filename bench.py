@@ -351,24 +351,28 @@ class NativeStep:
             sampler.pause()
         return rdv.max(ms), my_bytes
 
-    def capture_step(self, replays):
-        """The step as one CUDA graph (the step operator, or append + attention; the grid is sized for the lengths the
-        sequences can reach within `replays` replays, so the graph follows the growing cache that far).
-        Capturing runs the step once for real."""
+    def capture_step(self, total_steps, per_graph=1):
+        """`per_graph` consecutive steps as one CUDA graph (each the step operator, or append + attention; the
+        grid is sized for the lengths the sequences can reach within `total_steps` steps, so the graph follows
+        the growing cache that far).  Consecutive step kernels in one graph are joined by programmatic edges:
+        the next step's CTAs are scheduled while the last ones of this step finish.  Capturing runs the
+        steps once for real."""
         from axono_b200 import native
 
         def body():
-            if self.one_op:
-                self.lx.decode_step_paged(self.q, self.k_new, self.v_new, self.arena, 0, bound, out=self.out, theta=1e6)
-            else:
-                self.lx.kv_append_rope(self.arena, 0, self.q, self.k_new, self.v_new, theta=1e6)
-                self.lx.gqa_decode_attention_paged(self.q, self.arena, 0, bound, out=self.out)
+            for _ in range(per_graph):
+                if self.one_op:
+                    self.lx.decode_step_paged(self.q, self.k_new, self.v_new, self.arena, 0, bound, out=self.out, theta=1e6)
+                else:
+                    self.lx.kv_append_rope(self.arena, 0, self.q, self.k_new, self.v_new, theta=1e6)
+                    self.lx.gqa_decode_attention_paged(self.q, self.arena, 0, bound, out=self.out)
             return self.out
 
-        bound = min(self.capacity, int(self.bound) + int(replays) + 1)  # what the lengths can reach under this graph
+        bound = min(self.capacity, int(self.bound) + int(total_steps) + per_graph)  # what the lengths can reach under this graph
         g = native.CUDAGraph().capture(body)
-        self.cur += 1
-        self.bound = min(self.capacity, self.bound + 1)
+        self.per_graph = per_graph
+        self.cur += per_graph
+        self.bound = min(self.capacity, self.bound + per_graph)
         return g
 
     def timed_replays(self, rdv, g, steps):
@@ -379,7 +383,8 @@ class NativeStep:
         my_bytes = self.bytes_of_steps(steps)
         lx.synchronize()
         rdv.barrier()
-        ms = g.replay_timed(steps) * steps
+        replays = steps // self.per_graph
+        ms = g.replay_timed(replays) * replays
         self.cur += steps
         self.bound = min(self.capacity, self.bound + steps)
         lx.synchronize()
@@ -562,14 +567,17 @@ def run_native(args):
     launches_per_step = run.launches_per_step()
     # ---- value: inputs resident, CUDA events around K steps ----
     sampler.start()  # sampled from here to the end of the host-buffer phase: the GPU is under this load throughout
-    # The step is captured once as a CUDA graph and the K timed steps are K replays launched from native
+    # The steps are captured as a CUDA graph (`per_graph` consecutive steps, the way a serving loop submits
+    # several decode steps at once) and the K timed steps are K / per_graph replays launched from native
     # code: at several GPUs a step lasts 0.1-0.2 ms and the whole timed region a few milliseconds, which a
     # single scheduling hiccup of the Python thread on any one rank would otherwise double (max over ranks).
-    graph = run.capture_step(args.warmup + args.steps)
-    if args.warmup > 1:
-        graph.replay_timed(args.warmup - 1)
-        run.cur += args.warmup - 1
-        run.bound = min(run.capacity, run.bound + args.warmup - 1)
+    per_graph = args.steps_per_graph if args.steps_per_graph > 0 and args.steps % args.steps_per_graph == 0 else 1
+    graph = run.capture_step(args.warmup + args.steps + per_graph, per_graph)  # its warm-up run: per_graph real steps
+    more_warm = max(0, -(-(args.warmup - per_graph) // per_graph))  # replays that complete the W warm-up steps
+    if more_warm:
+        graph.replay_timed(more_warm)
+        run.cur += more_warm * per_graph
+        run.bound = min(run.capacity, run.bound + more_warm * per_graph)
     dev_ms, my_bytes, ms_by_rank = run.timed_replays(rdv, graph, args.steps)
     all_bytes = rdv.sum(my_bytes)
     value = all_bytes / (dev_ms / 1e3) / 1e9
@@ -698,6 +706,7 @@ def run_native(args):
             "tokens_per_s": tokens_per_s,
             "frac_of_nominal_8TBs": value / (NOMINAL_HBM_GBS * world),
             "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "launches_per_step": launches_per_step,
+            "steps_per_graph": per_graph,
             "clocks": clocks, "roofline": roofline,
             "cpu_baseline": cpu, "parity": parity, "extra": extra,
         }
@@ -1315,6 +1324,9 @@ def main():
     ap.add_argument("--no-dependent-launch", action="store_true",
                     help="launch the attention kernel in plain stream order (A/B of the programmatic dependent launch)")
     ap.add_argument("--no-tower", action="store_true", help="skip the text-tower figures in `extra`")
+    ap.add_argument("--steps-per-graph", type=int, default=5,
+                    help="consecutive steps captured into one CUDA graph, joined by programmatic edges "
+                         "(used when it divides --steps, else 1)")
     ap.add_argument("--two-kernel-step", action="store_true",
                     help="the step as kv_append_rope + gqa_decode_attention_paged instead of the one operator (A/B)")
     args = ap.parse_args()
