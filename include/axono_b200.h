@@ -94,8 +94,10 @@ int axb200_set_device_plan(int on);
 /* Whether the decode calls launch their attention kernel as a programmatic dependent of the kernel
  * before it in the stream (default on): its CTAs may then be scheduled while that kernel - the append,
  * in a decode step - is finishing, and stop at a grid-dependency wait until it is complete and its
- * writes are visible; what they do before the wait touches no global memory.  Off: plain stream order.
- * The result is the same either way.  No counterpart in the reference. */
+ * writes are visible; what they do before the wait touches no global memory.  The one-launch decode step
+ * (axb200_decode_step_paged) in turn lets the kernel after it be scheduled early, so consecutive steps in a
+ * stream or a captured graph overlap launch and set-up with the previous step's tail.  Off: plain stream
+ * order.  The result is the same either way.  No counterpart in the reference. */
 int axb200_set_dependent_launch(int on);
 
 /* Overrides the chunk length of the decode calls: `tiles` 64-token tiles per chunk (doubled until a
