@@ -144,7 +144,7 @@ def _run_native_ranks(phase, tmp_path, limit):
     """The ranks of tests/native_two_gpu_worker.py as clean interpreter processes (no PyTorch in them), each
     with a hard time limit: a rank that is still running when the limit is up is ended by its PID and the
     test fails - nothing is left waiting.  NVLS is switched off in the library the workers may load: a rank
-    that is ended must not hold a multicast binding."""
+    that is ended must not hold memory bound to an in-switch reduction group."""
     import subprocess
     import sys
     import time
