@@ -133,3 +133,36 @@ def test_how_many_launches_a_decode_step_takes():
         lib.axb200_set_step_fused(1)
     assert lib.axb200_decode_step_workspace_bytes(8, 16, 8, 128, 8192, _capi.FLOAT16) >= \
         lib.axb200_gqa_workspace_bytes(8, 16, 8, 128, 8192, _capi.FLOAT16) + 8 * 16 * 128 * 2
+
+
+def test_step_entry_points_refuse_bad_arguments_before_touching_the_device():
+    """Argument checks of the step operators come before any CUDA call, so they can be exercised without a
+    GPU: status codes as the reference's enum (3 UNSUPPORTED_TYPE, 7 INVALID_PTR, 1 INVALID_ARGUMENT)."""
+    lib = _capi.lib()
+    buf = (C.c_char * 4096)()
+    ptr = C.addressof(buf)
+    F16 = _capi.FLOAT16
+    ok_ws = lib.axb200_decode_step_workspace_bytes(2, 4, 2, 128, 256, F16)
+    assert ok_ws > 0 and lib.axb200_decode_step_workspace_bytes(2, 4, 2, 128, 256, 99) == 0
+
+    def step(q=ptr, k=ptr, v=ptr, out=ptr, dtype=F16, batch=2, ws=ptr, ws_bytes=ok_ws, max_len=256):
+        return lib.axb200_decode_step_paged(q, k, v, out, ptr, ptr, ptr, ptr, None, None, 1e6, 1, 0, 0, 0, batch, 4, 2, 128,
+                                            64, 4, 8, max_len, dtype, ws, ws_bytes, None)
+
+    assert step(dtype=99) == 3
+    assert step(q=None) == 7 and step(out=None) == 7 and step(ws=None) == 7
+    assert step(batch=0) == 1 and step(max_len=0) == 1
+    assert step(ws_bytes=ok_ws - 1) == 1
+
+    def qkv_step(qkv=ptr, ld=(4 + 4) * 128, slot_delta=0, advance=1, world=0, out=ptr, peer=None, hq_total=4, dtype=F16):
+        return lib.axb200_qkv_decode_step_paged(qkv, ld, None, None, 1e-6, out, ptr, ptr, ptr, ptr, None, None, 1e6, 1, 0, 0, 0,
+                                                2, 4, 2, 128, 64, 4, 8, 256, dtype, slot_delta, advance, ptr, ok_ws, peer, peer,
+                                                peer, world, 0, hq_total, None)
+
+    assert qkv_step(dtype=99) == 3
+    assert qkv_step(qkv=None) == 7 and qkv_step(out=None) == 7
+    assert qkv_step(ld=100) == 1                      # a row must hold hq + 2 hkv heads
+    assert qkv_step(slot_delta=-1, advance=1) == 1    # first layer: (0, 1); later layers: (-1, 0)
+    assert qkv_step(slot_delta=0, advance=0) == 1
+    assert qkv_step(world=2) == 7                     # peers asked for, none given
+    assert qkv_step(world=9, peer=ptr) == 1 and qkv_step(world=2, peer=ptr, hq_total=5) == 1
